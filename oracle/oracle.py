@@ -1,0 +1,237 @@
+"""Python face of the CPU oracle (``plif_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY: imported by the test suite, by the smoke check and by
+the benchmark's CPU-baseline leg, never by the shipped package. Parity of the
+C restatement against the reference is pinned by the committed golden vectors
+(see ``tests/golden/make_golden.py``); the arctangent surrogate is unpinned.
+
+Every function takes and returns ``numpy.float32`` arrays in the reference's
+layouts: scans are time-major ``[T, ...]`` with the trailing dims flattened to
+columns, codec frames are ``[S*16, B, D]``, codec values are ``[B, S, D]``.
+Low-precision inputs must be widened to fp32 by the caller (exact), which is
+what the reference's kernels do per load (atomic_ops/parallel_scan.py:223-225).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_SRC = _HERE / "plif_oracle.c"
+_LIB = _HERE / "liborc.so"
+
+SURR_SIGMOID = 0
+SURR_ATAN = 1
+
+_lib = None
+
+
+def build(force: bool = False) -> Path:
+    """Compile the C restatement with gcc (no FMA contraction, OpenMP)."""
+    if force or not _LIB.exists() or _LIB.stat().st_mtime < _SRC.stat().st_mtime:
+        cmd = ["gcc", "-O3", "-mavx2", "-ffp-contract=off", "-fopenmp", "-shared",
+               "-fPIC", "-Wall", "-o", str(_LIB), str(_SRC), "-lm"]
+        subprocess.run(cmd, check=True)
+    return _LIB
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not _LIB.exists():
+            build()
+        _lib = ctypes.CDLL(str(_LIB))
+        _lib.orc_max_threads.restype = ctypes.c_int
+    return _lib
+
+
+def max_threads() -> int:
+    return int(lib().orc_max_threads())
+
+
+def set_threads(n: int) -> None:
+    lib().orc_set_threads(ctypes.c_int(int(n)))
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+
+
+def _p(a):
+    if a is None:
+        return ctypes.c_void_p(0)
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _i64(x) -> ctypes.c_int64:
+    return ctypes.c_int64(int(x))
+
+
+def _tc(a: np.ndarray):
+    T = a.shape[0]
+    cols = int(np.prod(a.shape[1:])) if a.ndim > 1 else 1
+    return T, cols
+
+
+# ---------------------------------------------------------------- scans
+
+
+def plif_selective_fwd(beta, u, vth, v_init, want_vpost=True):
+    """(spike [T,...], V_post [T,...] or None, V_last [...]) — u-form."""
+    beta, u, vth, v_init = _f32(beta), _f32(u), _f32(vth), _f32(v_init)
+    T, cols = _tc(u)
+    spike = np.empty_like(u)
+    vpost = np.empty_like(u) if want_vpost else None
+    vlast = np.empty_like(v_init)
+    lib().orc_plif_selective_fwd(_p(beta), _p(u), _p(vth), _p(v_init), _p(spike),
+                                 _p(vpost), _p(vlast), _i64(T), _i64(cols))
+    return spike, vpost, vlast
+
+
+def plif_selective_ai_fwd(beta, cur, gain, vth, v_init, want_vpost=True):
+    """Selective scan with separate write gain and current (alpha*I form)."""
+    beta, cur, gain, vth, v_init = map(_f32, (beta, cur, gain, vth, v_init))
+    T, cols = _tc(cur)
+    spike = np.empty_like(cur)
+    vpost = np.empty_like(cur) if want_vpost else None
+    vlast = np.empty_like(v_init)
+    lib().orc_plif_selective_ai_fwd(_p(beta), _p(cur), _p(gain), _p(vth), _p(v_init),
+                                    _p(spike), _p(vpost), _p(vlast), _i64(T), _i64(cols))
+    return spike, vpost, vlast
+
+
+def plif_rowparam_fwd(beta_row, u, vth_row, v_init, want_vpost=True):
+    beta_row, u, vth_row, v_init = map(_f32, (beta_row, u, vth_row, v_init))
+    T, cols = _tc(u)
+    assert beta_row.size == cols and vth_row.size == cols and v_init.size == cols
+    spike = np.empty_like(u)
+    vpost = np.empty_like(u) if want_vpost else None
+    vlast = np.empty_like(v_init)
+    lib().orc_plif_rowparam_fwd(_p(beta_row), _p(u), _p(vth_row), _p(v_init), _p(spike),
+                                _p(vpost), _p(vlast), _i64(T), _i64(cols))
+    return spike, vpost, vlast
+
+
+def plif_selective_bwd(beta, u, vth, v_init, g_spike, g_vpost, alpha, kind=SURR_SIGMOID):
+    """(g_beta, g_u, g_vth, g_vinit). g_spike / g_vpost may be None."""
+    beta, u, vth, v_init = map(_f32, (beta, u, vth, v_init))
+    g_spike = None if g_spike is None else _f32(g_spike)
+    g_vpost = None if g_vpost is None else _f32(g_vpost)
+    T, cols = _tc(u)
+    gb, gu, gt = np.empty_like(u), np.empty_like(u), np.empty_like(u)
+    gv = np.empty_like(v_init)
+    lib().orc_plif_selective_bwd(_p(beta), _p(u), _p(vth), _p(v_init), _p(g_spike),
+                                 _p(g_vpost), _p(gb), _p(gu), _p(gt), _p(gv), _i64(T),
+                                 _i64(cols), ctypes.c_double(alpha), ctypes.c_int(kind))
+    return gb, gu, gt, gv
+
+
+def plif_selective_ai_bwd(beta, cur, gain, vth, v_init, g_spike, g_vpost, alpha,
+                          kind=SURR_SIGMOID):
+    """(g_beta, g_cur, g_gain, g_vth, g_vinit)."""
+    beta, cur, gain, vth, v_init = map(_f32, (beta, cur, gain, vth, v_init))
+    g_spike = None if g_spike is None else _f32(g_spike)
+    g_vpost = None if g_vpost is None else _f32(g_vpost)
+    T, cols = _tc(cur)
+    gb, gc, gg, gt = (np.empty_like(cur) for _ in range(4))
+    gv = np.empty_like(v_init)
+    lib().orc_plif_selective_ai_bwd(_p(beta), _p(cur), _p(gain), _p(vth), _p(v_init),
+                                    _p(g_spike), _p(g_vpost), _p(gb), _p(gc), _p(gg),
+                                    _p(gt), _p(gv), _i64(T), _i64(cols),
+                                    ctypes.c_double(alpha), ctypes.c_int(kind))
+    return gb, gc, gg, gt, gv
+
+
+def plif_rowparam_bwd(beta_row, u, vth_row, v_init, g_spike, g_vpost, alpha,
+                      kind=SURR_SIGMOID):
+    """(g_beta_row, g_u, g_vth_row, g_vinit)."""
+    beta_row, u, vth_row, v_init = map(_f32, (beta_row, u, vth_row, v_init))
+    g_spike = None if g_spike is None else _f32(g_spike)
+    g_vpost = None if g_vpost is None else _f32(g_vpost)
+    T, cols = _tc(u)
+    gb, gt, gv = np.empty_like(v_init), np.empty_like(v_init), np.empty_like(v_init)
+    gu = np.empty_like(u)
+    lib().orc_plif_rowparam_bwd(_p(beta_row), _p(u), _p(vth_row), _p(v_init), _p(g_spike),
+                                _p(g_vpost), _p(gb), _p(gu), _p(gt), _p(gv), _i64(T),
+                                _i64(cols), ctypes.c_double(alpha), ctypes.c_int(kind))
+    return gb, gu, gt, gv
+
+
+# ---------------------------------------------------------------- codec
+
+
+def fp16_encode(emb):
+    """[B,S,D] values -> [S*16,B,D] frames in {0,1}."""
+    emb = _f32(emb)
+    B, S, D = emb.shape
+    frames = np.empty((S * 16, B, D), np.float32)
+    lib().orc_fp16_encode(_p(emb), _p(frames), _i64(B), _i64(S), _i64(D))
+    return frames
+
+
+def fp16_decode(frames, bf16_intermediates=False):
+    """[S*16,B,D] frames -> [B,S,D] values."""
+    frames = _f32(frames)
+    TK, B, D = frames.shape
+    S = TK // 16
+    out = np.empty((B, S, D), np.float32)
+    lib().orc_fp16_decode(_p(frames), _p(out), _i64(B), _i64(S), _i64(D),
+                          ctypes.c_int(1 if bf16_intermediates else 0))
+    return out
+
+
+def fp16_decode_bwd(frames, g_out):
+    frames, g_out = _f32(frames), _f32(g_out)
+    TK, B, D = frames.shape
+    S = TK // 16
+    g = np.empty_like(frames)
+    lib().orc_fp16_decode_bwd(_p(frames), _p(g_out), _p(g), _i64(B), _i64(S), _i64(D))
+    return g
+
+
+def binary_residual(fa, fb, bf16_intermediates=False):
+    fa, fb = _f32(fa), _f32(fb)
+    TK, B, D = fa.shape
+    out = np.empty_like(fa)
+    lib().orc_binary_residual(_p(fa), _p(fb), _p(out), _i64(B), _i64(TK // 16), _i64(D),
+                              ctypes.c_int(1 if bf16_intermediates else 0))
+    return out
+
+
+def encode_ste_bwd(g_frames):
+    g_frames = _f32(g_frames)
+    TK, B, D = g_frames.shape
+    S = TK // 16
+    g = np.empty((B, S, D), np.float32)
+    lib().orc_encode_ste_bwd(_p(g_frames), _p(g), _i64(B), _i64(S), _i64(D))
+    return g
+
+
+# ---------------------------------------------------------------- normaliser
+
+
+def li_fwd(x, gain, eps=1e-6):
+    x, gain = _f32(x), _f32(gain)
+    D = x.shape[-1]
+    out = np.empty_like(x)
+    lib().orc_li_fwd(_p(x), _p(gain), _p(out), _i64(x.size // D), _i64(D),
+                     ctypes.c_double(eps))
+    return out
+
+
+def li_bwd(g_out, x, gain, eps=1e-6):
+    g_out, x, gain = _f32(g_out), _f32(x), _f32(gain)
+    D = x.shape[-1]
+    gx = np.empty_like(x)
+    gg = np.empty(D, np.float64)
+    lib().orc_li_bwd(_p(g_out), _p(x), _p(gain), _p(gx), _p(gg), _i64(x.size // D),
+                     _i64(D), ctypes.c_double(eps))
+    return gx, gg
+
+
+if __name__ == "__main__":
+    print(build(force=True))

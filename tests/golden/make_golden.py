@@ -1,0 +1,247 @@
+"""Generate the golden vectors under tests/golden/ from the reference's own code.
+
+Run once, in a container that has the reference checkout (path given by
+NEURONSPARK_REF, default /root/reference) and PyTorch on CPU:
+
+    python tests/golden/make_golden.py
+
+The reference's ``atomic_ops`` package cannot be imported as a package here
+(it depends on SpikingJelly, which is not installed), so the two files that
+matter are loaded by path: ``parallel_scan.py`` and ``fp16_codec.py`` import
+only torch at module level.
+
+What each fixture is produced by:
+  scan_fwd_*      rf_plif_parallel_forward(..., omega=0, w_init=0,
+                  surrogate_function=None): the reference's executable CPU time
+                  loop (atomic_ops/parallel_scan.py:1655-1683), which with
+                  omega = 0 is the first-order selective scan.
+  scan_bwd_*      torch autograd through the loop the reference's own test
+                  uses as ground truth (exp/verify_fused_plif.py:111-124: hard
+                  spike detached in the reset, surrogate spike as output), with
+                  a local sigmoid surrogate that restates SpikingJelly's
+                  (heaviside forward, alpha*sig*(1-sig) backward).
+  scan_ai_*       the same loop with v_pre = beta*v + alpha*x
+                  (atomic_ops/selective_plif.py:127).
+  rowparam_*      the same loops with per-column beta / v_th.
+  codec_*         fp16_encode, fp16_decode (+ autograd), _binary_residual_fwd,
+                  _binary_residual_naive, _BinaryEncodeSTE from
+                  atomic_ops/fp16_codec.py, in fp32 and bf16.
+  li_*            the PyTorch fallback of LateralInhibition.forward
+                  (atomic_ops/lateral_inhibition.py:208-212) + autograd.
+"""
+import importlib.util
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+REF = Path(os.environ.get("NEURONSPARK_REF", "/root/reference"))
+OUT = Path(__file__).resolve().parent
+
+
+def load(name, rel):
+    spec = importlib.util.spec_from_file_location(name, REF / rel)
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    return m
+
+
+class SigmoidSurrogate(torch.autograd.Function):
+    """heaviside(x) forward, alpha*sigmoid(alpha x)(1-sigmoid(alpha x)) backward."""
+
+    @staticmethod
+    def forward(ctx, x, alpha):
+        ctx.save_for_backward(x)
+        ctx.alpha = alpha
+        return (x >= 0).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        s = torch.sigmoid(ctx.alpha * x)
+        return g * ctx.alpha * s * (1 - s), None
+
+
+def seq_loop(beta, u, vth, v_init, alpha, rowparam=False, gain=None, cur=None):
+    """The reference test's ground-truth loop (exp/verify_fused_plif.py:111-124)."""
+    v = v_init
+    T = (u if u is not None else cur).shape[0]
+    S, V = [], []
+    for k in range(T):
+        b = beta if rowparam else beta[k]
+        th = vth if rowparam else vth[k]
+        drive = u[k] if u is not None else gain[k] * cur[k]
+        v_pre = b * v + drive
+        sp = (v_pre.detach() >= th.detach()).to(v_pre.dtype)
+        v = v_pre - th * sp
+        S.append(SigmoidSurrogate.apply(v_pre - th, alpha))
+        V.append(v)
+    return torch.stack(S), torch.stack(V)
+
+
+def npz(name, **arrs):
+    out = {}
+    for k, v in arrs.items():
+        if isinstance(v, torch.Tensor):
+            v = v.detach().float().numpy()
+        out[k] = np.asarray(v)
+    np.savez_compressed(OUT / f"{name}.npz", **out)
+    print(f"wrote {name}.npz", {k: v.shape for k, v in out.items()})
+
+
+def main():
+    torch.set_num_threads(1)
+    ps = load("ref_parallel_scan", "atomic_ops/parallel_scan.py")
+    codec = load("ref_fp16_codec", "atomic_ops/fp16_codec.py")
+
+    # ---- forward, the distribution of exp/verify_fused_plif.py:41-46 (seed 42)
+    for tag, (T, B, D) in {"a": (64, 2, 32), "b": (200, 3, 20)}.items():
+        torch.manual_seed(42)
+        beta = torch.sigmoid(torch.randn(T, B, D))
+        u = torch.randn(T, B, D) * 0.1
+        vth = 0.1 + torch.abs(torch.randn(T, B, D)) * 0.5
+        v0 = torch.randn(B, D) * 0.1
+        z = torch.zeros(B, D)
+        s, V, _ = ps.rf_plif_parallel_forward(beta, torch.zeros_like(beta), u, vth, v0, z, None)
+        npz(f"scan_fwd_{tag}", beta=beta, u=u, vth=vth, v_init=v0, spike=s, vpost=V)
+
+    # ---- forward, BASELINE config-0 distribution at reduced size
+    g = torch.Generator().manual_seed(1234)
+    T, B, D = 256, 2, 40
+    cur = torch.randn(T, B, D, generator=g)
+    beta = torch.sigmoid(2 + 0.5 * torch.randn(T, B, D, generator=g))
+    gain = torch.nn.functional.softplus(torch.randn(T, B, D, generator=g))
+    vth = 0.1 + torch.nn.functional.softplus(torch.randn(T, B, D, generator=g))
+    z = torch.zeros(B, D)
+    u = gain * cur
+    s, V, _ = ps.rf_plif_parallel_forward(beta, torch.zeros_like(beta), u, vth, z, z, None)
+    with torch.no_grad():
+        s_ai, V_ai = seq_loop(beta, None, vth, z, 4.0, gain=gain, cur=cur)
+    assert torch.equal(s, s_ai) and torch.equal(V, V_ai)
+    npz("scan_fwd_c0", beta=beta, cur=cur, gain=gain, vth=vth, v_init=z, spike=s, vpost=V)
+
+    # ---- backward (sigmoid alpha=4), loss = sum(spike*gS) + sum(V*gV)
+    torch.manual_seed(42)
+    T, B, D = 64, 2, 32
+    beta = torch.sigmoid(torch.randn(T, B, D)).requires_grad_()
+    u = (torch.randn(T, B, D) * 0.3).requires_grad_()
+    vth = (0.1 + torch.abs(torch.randn(T, B, D)) * 0.5).requires_grad_()
+    v0 = (torch.randn(B, D) * 0.1).requires_grad_()
+    gS = torch.randn(T, B, D)
+    gV = torch.randn(T, B, D)
+    S, V = seq_loop(beta, u, vth, v0, 4.0)
+    ((S * gS).sum() + (V * gV).sum()).backward()
+    npz("scan_bwd_a", beta=beta, u=u, vth=vth, v_init=v0, g_spike=gS, g_vpost=gV,
+        alpha=np.float64(4.0), g_beta=beta.grad, g_u=u.grad, g_vth=vth.grad, g_vinit=v0.grad)
+    # the reference test's own loss: spike.sum() + V_post.sum()
+    for t in (beta, u, vth, v0):
+        t.grad = None
+    S, V = seq_loop(beta, u, vth, v0, 4.0)
+    (S.sum() + V.sum()).backward()
+    npz("scan_bwd_ones", beta=beta, u=u, vth=vth, v_init=v0, alpha=np.float64(4.0),
+        g_beta=beta.grad, g_u=u.grad, g_vth=vth.grad, g_vinit=v0.grad)
+
+    # ---- alpha*I form backward
+    torch.manual_seed(7)
+    T, B, D = 48, 2, 24
+    cur = torch.randn(T, B, D).requires_grad_()
+    beta = torch.sigmoid(2 + 0.5 * torch.randn(T, B, D)).requires_grad_()
+    gain = torch.nn.functional.softplus(torch.randn(T, B, D)).requires_grad_()
+    vth = (0.1 + torch.nn.functional.softplus(torch.randn(T, B, D))).requires_grad_()
+    v0 = (torch.randn(B, D) * 0.1).requires_grad_()
+    gS = torch.randn(T, B, D) * 0.1
+    S, V = seq_loop(beta, None, vth, v0, 4.0, gain=gain, cur=cur)
+    (S * gS).sum().backward()
+    npz("scan_ai_bwd", beta=beta, cur=cur, gain=gain, vth=vth, v_init=v0, g_spike=gS,
+        alpha=np.float64(4.0), spike=S, vpost=V, g_beta=beta.grad, g_cur=cur.grad,
+        g_gain=gain.grad, g_vth=vth.grad, g_vinit=v0.grad)
+
+    # ---- row-param, the inputs of test_recompute.py:27-31 (K=16,B=2,dim=256, seed 42)
+    torch.manual_seed(42)
+    K, B, D = 16, 2, 256
+    beta_row = torch.sigmoid(torch.randn(B, D)).requires_grad_()
+    u = torch.randn(K, B, D).requires_grad_()
+    vth_row = (torch.abs(torch.randn(B, D)) + 0.1).requires_grad_()
+    v0 = torch.randn(B, D).requires_grad_()
+    S, V = seq_loop(beta_row, u, vth_row, v0, 4.0, rowparam=True)
+    S.sum().backward()
+    npz("rowparam_a", beta_row=beta_row, u=u, vth_row=vth_row, v_init=v0, alpha=np.float64(4.0),
+        spike=S, vpost=V, g_beta_row=beta_row.grad, g_u=u.grad, g_vth_row=vth_row.grad,
+        g_vinit=v0.grad)
+
+    # ---- row-param, BASELINE config-1 distribution at reduced size, with gV
+    g = torch.Generator().manual_seed(1234)
+    T, B, D = 160, 3, 24
+    bd = torch.sigmoid(2 + 0.5 * torch.randn(D, generator=g))
+    td = (0.5 + 0.1 * torch.randn(D, generator=g)).clamp(min=0.05)
+    beta_row = bd.expand(B, D).contiguous().requires_grad_()
+    vth_row = td.expand(B, D).contiguous().requires_grad_()
+    cur = torch.randn(T, B, D, generator=g)
+    u = ((1 - bd) * cur).requires_grad_()
+    v0 = torch.zeros(B, D).requires_grad_()
+    gS = torch.randn(T, B, D, generator=g)
+    gV = torch.randn(T, B, D, generator=g) * 0.1
+    S, V = seq_loop(beta_row, u, vth_row, v0, 4.0, rowparam=True)
+    ((S * gS).sum() + (V * gV).sum()).backward()
+    npz("rowparam_c1", beta_row=beta_row, u=u, vth_row=vth_row, v_init=v0, g_spike=gS, g_vpost=gV,
+        alpha=np.float64(4.0), spike=S, vpost=V, g_beta_row=beta_row.grad, g_u=u.grad,
+        g_vth_row=vth_row.grad, g_vinit=v0.grad)
+
+    # ---- codec: the inputs of test_binary_residual.py (seed 42) + edge values
+    torch.manual_seed(42)
+    B, S_, D = 2, 4, 8
+    xa = torch.randn(B, S_, D).clamp(-100, 100)
+    xb = torch.randn(B, S_, D).clamp(-100, 100)
+    fa, fb = codec.fp16_encode(xa, 16), codec.fp16_encode(xb, 16)
+    res = codec._binary_residual_fwd(fa, fb)
+    assert torch.equal(res, codec._binary_residual_naive(fa, fb))
+    dec = codec.fp16_decode(res, S_, 16)
+    fr = fa.clone().requires_grad_()
+    gout = torch.randn(B, S_, D)
+    (codec.fp16_decode(fr, S_, 16) * gout).sum().backward()
+    gfr = torch.randn(S_ * 16, B, D)
+    xe = xa.clone().requires_grad_()
+    (codec.binary_encode_ste(xe) * gfr).sum().backward()
+    npz("codec_a", xa=xa, xb=xb, frames_a=fa, frames_b=fb, residual=res, decoded_residual=dec,
+        decoded_a=codec.fp16_decode(fa, S_, 16), g_out=gout, g_frames=fr.grad,
+        g_frames_in=gfr, g_ste=xe.grad)
+
+    edge = torch.tensor([0.0, -0.0, 1.0, -1.0, 65504.0, -65504.0, 70000.0, -1e9, 6.1035e-05,
+                         6.0e-05, 5.9605e-08, 2.9e-08, 3.0e-08, 1e-10, 0.33333334, 2049.0,
+                         2051.0, 1.00048828125, 1.0009765625, 65519.9, 100.06, -3.1415927,
+                         1e-5, 33000.0], dtype=torch.float32)
+    edge = torch.cat([edge, torch.randn(40) * torch.logspace(-8, 4, 40)]).reshape(1, 4, 16)
+    fe = codec.fp16_encode(edge, 16)
+    fe2 = codec.fp16_encode(edge.flip(2) * 0.75, 16)
+    # frames with an all-ones exponent (never produced by encode, legal to decode)
+    f31 = fe.clone()
+    f31[1:6] = 1.0
+    npz("codec_edge", x=edge, frames=fe, decoded=codec.fp16_decode(fe, 4, 16),
+        frames_b=fe2, residual=codec._binary_residual_fwd(fe, fe2),
+        frames_e31=f31, decoded_e31=codec.fp16_decode(f31, 4, 16),
+        residual_e31=codec._binary_residual_fwd(f31, fe2))
+
+    # bf16 frames: the reference computes the decode formula in bf16
+    fab, fbb = fa.bfloat16(), fb.bfloat16()
+    npz("codec_bf16", frames_a=fab, frames_b=fbb, decoded_a=codec.fp16_decode(fab, S_, 16),
+        residual=codec._binary_residual_fwd(fab, fbb),
+        frames_e=fe.bfloat16(), decoded_e=codec.fp16_decode(fe.bfloat16(), 4, 16),
+        residual_e=codec._binary_residual_fwd(fe.bfloat16(), fe2.bfloat16()))
+
+    # ---- lateral inhibition fallback (atomic_ops/lateral_inhibition.py:208-212)
+    torch.manual_seed(42)
+    x = (torch.randn(6, 5, 48) * 2).requires_grad_()
+    gain = (1 + 0.1 * torch.randn(48)).requires_grad_()
+    eps = 1e-6
+    variance = x.pow(2).mean(-1, keepdim=True)
+    out = gain * (x * torch.rsqrt(variance + eps))
+    go = torch.randn_like(out)
+    (out * go).sum().backward()
+    npz("li_a", x=x, gain=gain, eps=np.float64(eps), out=out, g_out=go, g_x=x.grad,
+        g_gain=gain.grad)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

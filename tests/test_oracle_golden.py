@@ -1,0 +1,122 @@
+"""The CPU oracle against the golden vectors produced by the reference's code.
+
+This is what pins the oracle: forward scans and the codec must agree bit for
+bit, the backward passes and the normaliser to 1e-5 relative (fp32)."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from conftest import rel_err
+
+TOL = 1e-5  # relative, fp32
+
+
+@pytest.mark.parametrize("name", ["scan_fwd_a", "scan_fwd_b"])
+def test_selective_fwd_bit_exact(golden, name):
+    g = golden(name)
+    s, v, vl = orc.plif_selective_fwd(g["beta"], g["u"], g["vth"], g["v_init"])
+    assert np.array_equal(s, g["spike"])
+    assert np.array_equal(v, g["vpost"])
+    assert np.array_equal(vl, g["vpost"][-1])
+
+
+def test_selective_ai_fwd_bit_exact(golden):
+    g = golden("scan_fwd_c0")
+    s, v, vl = orc.plif_selective_ai_fwd(g["beta"], g["cur"], g["gain"], g["vth"], g["v_init"])
+    assert np.array_equal(s, g["spike"])
+    assert np.array_equal(v, g["vpost"])
+    # u-form on the pre-multiplied drive gives the same thing
+    u = (g["gain"] * g["cur"]).astype(np.float32)
+    s2, v2, _ = orc.plif_selective_fwd(g["beta"], u, g["vth"], g["v_init"])
+    assert np.array_equal(s2, s) and np.array_equal(v2, v)
+    assert 0.01 < s.mean() < 0.99
+
+
+def test_selective_bwd(golden):
+    g = golden("scan_bwd_a")
+    gb, gu, gt, gv = orc.plif_selective_bwd(g["beta"], g["u"], g["vth"], g["v_init"],
+                                            g["g_spike"], g["g_vpost"], float(g["alpha"]))
+    for mine, ref in ((gb, "g_beta"), (gu, "g_u"), (gt, "g_vth"), (gv, "g_vinit")):
+        assert rel_err(mine, g[ref]) < TOL, ref
+
+
+def test_selective_bwd_reference_loss(golden):
+    """Loss = spike.sum() + V_post.sum(), as in exp/verify_fused_plif.py:101."""
+    g = golden("scan_bwd_ones")
+    ones = np.ones_like(g["u"])
+    gb, gu, gt, gv = orc.plif_selective_bwd(g["beta"], g["u"], g["vth"], g["v_init"],
+                                            ones, ones, float(g["alpha"]))
+    for mine, ref in ((gb, "g_beta"), (gu, "g_u"), (gt, "g_vth"), (gv, "g_vinit")):
+        assert rel_err(mine, g[ref]) < TOL, ref
+
+
+def test_selective_ai_bwd(golden):
+    g = golden("scan_ai_bwd")
+    s, v, _ = orc.plif_selective_ai_fwd(g["beta"], g["cur"], g["gain"], g["vth"], g["v_init"])
+    assert np.array_equal(s, g["spike"]) and np.array_equal(v, g["vpost"])
+    out = orc.plif_selective_ai_bwd(g["beta"], g["cur"], g["gain"], g["vth"], g["v_init"],
+                                    g["g_spike"], None, float(g["alpha"]))
+    for mine, ref in zip(out, ("g_beta", "g_cur", "g_gain", "g_vth", "g_vinit")):
+        assert rel_err(mine, g[ref]) < TOL, ref
+
+
+@pytest.mark.parametrize("name", ["rowparam_a", "rowparam_c1"])
+def test_rowparam(golden, name):
+    g = golden(name)
+    s, v, vl = orc.plif_rowparam_fwd(g["beta_row"], g["u"], g["vth_row"], g["v_init"])
+    assert np.array_equal(s, g["spike"])
+    assert np.array_equal(v, g["vpost"])
+    gS = g.get("g_spike", np.ones_like(g["u"]))
+    out = orc.plif_rowparam_bwd(g["beta_row"], g["u"], g["vth_row"], g["v_init"], gS,
+                                g.get("g_vpost"), float(g["alpha"]))
+    for mine, ref in zip(out, ("g_beta_row", "g_u", "g_vth_row", "g_vinit")):
+        assert rel_err(mine, g[ref]) < TOL, ref
+
+
+def test_codec(golden):
+    g = golden("codec_a")
+    fa, fb = orc.fp16_encode(g["xa"]), orc.fp16_encode(g["xb"])
+    assert np.array_equal(fa, g["frames_a"]) and np.array_equal(fb, g["frames_b"])
+    assert np.array_equal(orc.fp16_decode(fa), g["decoded_a"])
+    res = orc.binary_residual(fa, fb)
+    assert np.array_equal(res, g["residual"])
+    assert set(np.unique(res)) <= {0.0, 1.0}
+    assert np.array_equal(orc.fp16_decode(res), g["decoded_residual"])
+    # the reference's own acceptance checks (test_binary_residual.py:24-31, 90-95)
+    half = lambda x: x.astype(np.float16).astype(np.float32)
+    assert np.abs(g["decoded_residual"] - half(half(g["xa"]) + half(g["xb"]))).max() < 1e-2
+    assert np.abs(g["decoded_a"] - half(g["xa"])).max() < 1e-3
+    assert rel_err(orc.fp16_decode_bwd(fa, g["g_out"]), g["g_frames"]) < 1e-6
+    assert rel_err(orc.encode_ste_bwd(g["g_frames_in"]), g["g_ste"]) < 1e-6
+
+
+def test_codec_edges(golden):
+    g = golden("codec_edge")
+    f = orc.fp16_encode(g["x"])
+    assert np.array_equal(f, g["frames"])
+    assert np.array_equal(orc.fp16_decode(f), g["decoded"])
+    assert np.array_equal(orc.binary_residual(f, g["frames_b"]), g["residual"])
+    # exponent pattern 31 decodes as a normal number, no inf/nan
+    assert np.array_equal(orc.fp16_decode(g["frames_e31"]), g["decoded_e31"])
+    assert np.isfinite(g["decoded_e31"]).all()
+    assert np.array_equal(orc.binary_residual(g["frames_e31"], g["frames_b"]), g["residual_e31"])
+    # 70000 clamps to 65504
+    assert orc.fp16_decode(orc.fp16_encode(np.full((1, 1, 1), 70000.0)))[0, 0, 0] == 65504.0
+
+
+def test_codec_bf16_frames(golden):
+    g = golden("codec_bf16")
+    assert np.array_equal(orc.fp16_decode(g["frames_a"], True), g["decoded_a"])
+    assert np.array_equal(orc.fp16_decode(g["frames_e"], True), g["decoded_e"])
+    assert np.array_equal(orc.binary_residual(g["frames_a"], g["frames_b"], True), g["residual"])
+    fb = golden("codec_edge")["frames_b"]
+    assert np.array_equal(orc.binary_residual(g["frames_e"], fb, True), g["residual_e"])
+
+
+def test_lateral_inhibition(golden):
+    g = golden("li_a")
+    out = orc.li_fwd(g["x"], g["gain"], float(g["eps"]))
+    assert rel_err(out, g["out"]) < TOL
+    gx, gg = orc.li_bwd(g["g_out"], g["x"], g["gain"], float(g["eps"]))
+    assert rel_err(gx, g["g_x"]) < TOL
+    assert rel_err(gg, g["g_gain"]) < TOL
