@@ -1,0 +1,200 @@
+/*
+ * neuronspark_b200 — C ABI of the B200 (sm_100a) PLIF scan path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t), returns an int status (0 = NSB_OK),
+ * never throws and never exits. Nothing here allocates device memory unless
+ * its comment says so. All kernels are asynchronous on the given stream.
+ *
+ * Layouts follow the reference project (Brain2nd/NeuronSpark):
+ *   scan tensors   time-major [T, cols], cols = product of the trailing dims
+ *                  (batch * channels), contiguous
+ *                  (atomic_ops/parallel_scan.py:713-714)
+ *   per-column     [cols] vectors, always fp32 on this ABI
+ *   codec frames   [S*16, B, D]; codec values [B, S, D]
+ *                  (atomic_ops/fp16_codec.py:17-46)
+ *
+ * "stream dtype" is the element type of the big [T, cols] tensors of one call
+ * (all of them share it). The arithmetic is always fp32 with one rounded
+ * multiply and one rounded add per state update (no fused multiply-add), so
+ * spikes agree bit for bit with the reference's eager PyTorch time loop.
+ */
+#ifndef NEURONSPARK_B200_H_
+#define NEURONSPARK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ---- */
+#define NSB_OK 0
+#define NSB_ERR_INVALID_ARG 1   /* null/misaligned pointer, bad size or enum   */
+#define NSB_ERR_UNSUPPORTED 2   /* device is not sm_100, or option unavailable */
+#define NSB_ERR_CUDA 3          /* a CUDA runtime/driver call failed           */
+#define NSB_ERR_DEVICE_TIMEOUT 4 /* a bounded device-side wait ran out         */
+#define NSB_ERR_TOO_LARGE 5     /* size exceeds a documented fixed maximum     */
+
+/* ---- element types of streamed tensors ---- */
+#define NSB_F32 0
+#define NSB_BF16 1
+#define NSB_F16 2
+
+/* ---- surrogate gradients ---- */
+#define NSB_SURR_SIGMOID 0 /* a*sig(ax)*(1-sig(ax)), exp argument clamped at 88
+                              (atomic_ops/parallel_scan.py:291-296)            */
+#define NSB_SURR_ATAN 1    /* (a/2)/(1+(pi/2*a*x)^2); no counterpart in the
+                              reference's fused kernels                        */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int nsb_version(void);
+
+/* Human-readable text for a status code; never NULL. */
+const char* nsb_status_string(int status);
+
+/* Text of the last CUDA error this library saw on the calling thread. */
+const char* nsb_last_cuda_error(void);
+
+/* Reads and clears the device-side error word (set when a bounded wait inside
+ * a kernel gave up). Synchronises nothing: the word lives in mapped host
+ * memory; call after synchronising the stream you care about. */
+int nsb_device_error_word(uint32_t* out);
+
+/* Tuning override for the scan kernels, used by sweeps and tests. Any field
+ * <= 0 keeps the built-in heuristic. warps_per_cta: warps of one CTA (each
+ * warp owns 32*lanes_per_thread columns and its own TMA pipeline); stages:
+ * depth of each warp's shared-memory ring; lanes_per_thread: 1, 2 or 4;
+ * force_direct: 1 = never use the TMA path. Process-global. */
+int nsb_set_tuning(int warps_per_cta, int stages, int lanes_per_thread, int force_direct);
+
+/* How the last scan launch on this thread was configured (for benchmarks):
+ * out[0]=used_tma, out[1]=warps_per_cta, out[2]=stages, out[3]=lanes_per_thread,
+ * out[4]=grid, out[5]=dynamic smem bytes per CTA, out[6]=steps per tile,
+ * out[7]=kernel launches issued by the call. */
+int nsb_last_launch_info(int32_t out[8]);
+
+/*
+ * Selective PLIF forward scan. Replaces _TritonPLIFForward.forward /
+ * _fused_plif_fwd_kernel (atomic_ops/parallel_scan.py:196-232, 706-735).
+ *
+ *   v = v_init; for k in [0,T):  v_pre = beta[k]*v + drive[k]
+ *                                s = (v_pre >= v_th[k]);  v = v_pre - v_th[k]*s
+ *   drive[k] = u[k]                    when gain == NULL  (reference signature)
+ *            = gain[k]*cur[k]          otherwise (SelectivePLIFNode form,
+ *                                       atomic_ops/selective_plif.py:127)
+ *
+ * beta, u_or_cur, gain, v_th : [T, cols] in `dtype`
+ * v_init                     : [cols] fp32
+ * spike_dense  (optional)    : [T, cols] in `dtype`, values {0,1}
+ * spike_packed (optional)    : [T, ceil(cols/32)] uint32, bit i of word w is
+ *                              column 32*w+i, tail bits zero
+ * v_post       (optional)    : [T, cols] in `dtype`
+ * v_ckpt       (optional)    : [ceil(T/ckpt_interval), cols] fp32; row j holds
+ *                              the membrane state BEFORE step j*ckpt_interval
+ *                              (row 0 = v_init). Needed by the backward.
+ * v_last                     : [cols] fp32, state after the last step
+ * ckpt_interval              : 8 or 16 (also the time-tile of the pipeline)
+ */
+int nsb_plif_selective_fwd(const void* beta, const void* u_or_cur, const void* gain,
+                           const void* v_th, const float* v_init, void* spike_dense,
+                           uint32_t* spike_packed, void* v_post, float* v_ckpt,
+                           float* v_last, int64_t T, int64_t cols, int dtype,
+                           int ckpt_interval, void* stream);
+
+/*
+ * Reverse-time surrogate-gradient pass of the selective scan. Replaces
+ * _TritonPLIFForward.backward / _fused_plif_bwd_kernel
+ * (atomic_ops/parallel_scan.py:234-307, 737-768) with the same recurrence:
+ *   tot = g_vpost[k] + acc;  gpre = g_spike[k]*sg(x_k) + tot
+ *   g_beta[k] = gpre*V[k-1]; g_u[k] = gpre; g_vth[k] = -g_spike[k]*sg - tot*s[k]
+ *   acc = gpre*beta[k];      g_vinit = acc after k = 0
+ * and for the gain*cur form g_cur = gpre*gain, g_gain = gpre*cur.
+ * Instead of reading a stored V_post it recomputes each time tile from v_ckpt
+ * with the forward's exact arithmetic, so spikes and states are identical.
+ *
+ * g_vpost may be NULL (treated as zero). g_gain is ignored when gain == NULL.
+ * Any of the gradient outputs may be NULL (not written).
+ */
+int nsb_plif_selective_bwd(const void* beta, const void* u_or_cur, const void* gain,
+                           const void* v_th, const float* v_ckpt, const void* g_spike,
+                           const void* g_vpost, void* g_beta, void* g_u_or_cur,
+                           void* g_gain, void* g_vth, float* g_vinit, int64_t T,
+                           int64_t cols, int dtype, int ckpt_interval, int surrogate,
+                           float alpha, void* stream);
+
+/*
+ * Row-parameter PLIF forward scan (beta and v_th constant over time, one fp32
+ * value per column). Replaces _fused_plif_fwd_rowparam_kernel and
+ * _fused_plif_fwd_rowparam_noV_kernel (atomic_ops/parallel_scan.py:314-343,
+ * 496-523) — pass v_post = NULL for the latter. Outputs as in
+ * nsb_plif_selective_fwd.
+ */
+int nsb_plif_rowparam_fwd(const float* beta_row, const void* u, const float* vth_row,
+                          const float* v_init, void* spike_dense, uint32_t* spike_packed,
+                          void* v_post, float* v_ckpt, float* v_last, int64_t T,
+                          int64_t cols, int dtype, int ckpt_interval, void* stream);
+
+/*
+ * Reverse pass of the row-parameter scan. Replaces
+ * _fused_plif_bwd_rowparam_kernel and _fused_plif_bwd_rowparam_recomp_kernel
+ * (atomic_ops/parallel_scan.py:345-413, 525-612): g_u per step, g_beta_row and
+ * g_vth_row reduced over time per column (fp32 [cols]). g_vpost may be NULL.
+ */
+int nsb_plif_rowparam_bwd(const float* beta_row, const void* u, const float* vth_row,
+                          const float* v_ckpt, const void* g_spike, const void* g_vpost,
+                          float* g_beta_row, void* g_u, float* g_vth_row, float* g_vinit,
+                          int64_t T, int64_t cols, int dtype, int ckpt_interval,
+                          int surrogate, float alpha, void* stream);
+
+/*
+ * FP16 boundary codec (atomic_ops/fp16_codec.py).
+ *
+ * nsb_fp16_encode        fp16_encode (:17-46): values [B,S,D] in dtype_in ->
+ *                        frames [S*16,B,D] in dtype_out, {0,1}, MSB first.
+ * nsb_fp16_decode_fwd    fp16_decode (:49-98): frames -> values [B,S,D], same
+ *                        dtype; an all-ones exponent decodes as a normal
+ *                        number. With bf16 frames the mantissa sum, 1+m and the
+ *                        result are rounded to bf16 as the reference's eager
+ *                        arithmetic does.
+ * nsb_fp16_decode_bwd    autograd of that formula: g_values [B,S,D] and the
+ *                        frames -> g_frames [S*16,B,D].
+ * nsb_binary_residual    _binary_residual_fwd (:115-164):
+ *                        encode(decode(a)+decode(b)).
+ * nsb_encode_ste_bwd     _BinaryEncodeSTE.backward (:220-224): mean over the 16
+ *                        frames of each token.
+ */
+int nsb_fp16_encode(const void* values, void* frames, int64_t B, int64_t S, int64_t D,
+                    int dtype_in, int dtype_out, void* stream);
+int nsb_fp16_decode_fwd(const void* frames, void* values, int64_t B, int64_t S, int64_t D,
+                        int dtype, void* stream);
+int nsb_fp16_decode_bwd(const void* frames, const void* g_values, void* g_frames,
+                        int64_t B, int64_t S, int64_t D, int dtype, void* stream);
+int nsb_binary_residual(const void* frames_a, const void* frames_b, void* frames_out,
+                        int64_t B, int64_t S, int64_t D, int dtype, void* stream);
+int nsb_encode_ste_bwd(const void* g_frames, void* g_values, int64_t B, int64_t S,
+                       int64_t D, int dtype, void* stream);
+
+/*
+ * Lateral inhibition = divisive normalisation = RMSNorm
+ * (atomic_ops/lateral_inhibition.py:50-119, 122-171; atomic_ops/rms_norm.py).
+ *   out = x * rsqrt(mean(x^2) + eps) * gain        rows of D, fp32 math
+ * Backward: g_x as the reference's kernel; g_gain [D] fp32 is reduced over the
+ * rows inside the call (the reference materialises a rows x D tensor and sums
+ * it afterwards). `partial` is caller-provided scratch of
+ * nsb_li_bwd_scratch_floats(rows, D) floats.
+ * gain is [D] in `gain_dtype`; x, out, g_out, g_x in `dtype`.
+ */
+int nsb_lateral_inhibition_fwd(const void* x, const void* gain, void* out, int64_t rows,
+                               int64_t D, float eps, int dtype, int gain_dtype,
+                               void* stream);
+int64_t nsb_li_bwd_scratch_floats(int64_t rows, int64_t D);
+int nsb_lateral_inhibition_bwd(const void* g_out, const void* x, const void* gain,
+                               void* g_x, float* g_gain, float* partial, int64_t rows,
+                               int64_t D, float eps, int dtype, int gain_dtype,
+                               void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NEURONSPARK_B200_H_ */

@@ -1,0 +1,9 @@
+"""neuronspark_b200 — B200 (sm_100a) kernels for NeuronSpark's PLIF scan path.
+
+Submodules mirror the reference's ``atomic_ops`` files for this path:
+``parallel_scan``, ``fp16_codec``, ``lateral_inhibition``. ``install`` rebinds
+the reference's own modules to these implementations.
+"""
+from ._lib import NSBError, set_tuning, last_launch_info, device_error_word, LIB_PATH  # noqa: F401
+
+__version__ = "0.1.0"

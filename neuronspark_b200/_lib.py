@@ -1,0 +1,138 @@
+"""ctypes binding of ``libneuronspark_b200.so`` (the C ABI in
+``include/neuronspark_b200.h``).
+
+There is no CPU or PyTorch fallback: if the shared library is missing, or a
+tensor is not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int32, c_int64, c_uint32, c_void_p
+from pathlib import Path
+
+import torch
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libneuronspark_b200.so"
+
+NSB_OK = 0
+F32, BF16, F16 = 0, 1, 2
+SURR_SIGMOID, SURR_ATAN = 0, 1
+
+_DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+_lib = None
+
+_SIGNATURES = {
+    "nsb_version": (c_int, []),
+    "nsb_status_string": (ctypes.c_char_p, [c_int]),
+    "nsb_last_cuda_error": (ctypes.c_char_p, []),
+    "nsb_device_error_word": (c_int, [ctypes.POINTER(c_uint32)]),
+    "nsb_set_tuning": (c_int, [c_int, c_int, c_int, c_int]),
+    "nsb_last_launch_info": (c_int, [ctypes.POINTER(c_int32)]),
+    "nsb_plif_selective_fwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_plif_selective_bwd": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int,
+                                                          c_float, c_void_p]),
+    "nsb_plif_rowparam_fwd": (c_int, [c_void_p] * 9 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_plif_rowparam_bwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_int,
+                                                         c_float, c_void_p]),
+    "nsb_fp16_encode": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_fp16_decode_fwd": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "nsb_fp16_decode_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                    c_void_p]),
+    "nsb_binary_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                    c_void_p]),
+    "nsb_encode_ste_bwd": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "nsb_lateral_inhibition_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float,
+                                           c_int, c_int, c_void_p]),
+    "nsb_li_bwd_scratch_floats": (c_int64, [c_int64, c_int64]),
+    "nsb_lateral_inhibition_bwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_float, c_int, c_int,
+                                                            c_void_p]),
+}
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+
+class NSBError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the shared library (once). Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise NSBError(
+                f"{LIB_PATH} is missing: build it with `python -m neuronspark_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != NSB_OK:
+        L = lib()
+        msg = L.nsb_status_string(status).decode()
+        if status == 3:
+            msg += " — " + L.nsb_last_cuda_error().decode()
+        raise NSBError(f"{what}: {msg} (status {status})")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPES[dt]
+    except KeyError:
+        raise NSBError(f"unsupported dtype {dt}; expected float32, bfloat16 or float16") from None
+
+
+def ptr(t) -> c_void_p:
+    """Device pointer of a tensor (None -> NULL)."""
+    if t is None:
+        return c_void_p(0)
+    return c_void_p(t.data_ptr())
+
+
+def stream_ptr(device) -> c_void_p:
+    return c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def require_cuda(*tensors) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise NSBError("neuronspark_b200 runs on CUDA tensors only (no CPU fallback)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise NSBError(f"tensors on different devices: {dev} and {t.device}")
+    if dev is None:
+        raise NSBError("no tensor arguments")
+    return dev
+
+
+def set_tuning(warps_per_cta: int = 0, stages: int = 0, lanes_per_thread: int = 0,
+               force_direct: bool = False) -> None:
+    """Overrides the scan launch heuristics (0 = automatic). Process-global."""
+    check(lib().nsb_set_tuning(warps_per_cta, stages, lanes_per_thread, int(force_direct)),
+          "nsb_set_tuning")
+
+
+def last_launch_info() -> dict:
+    out = (c_int32 * 8)()
+    check(lib().nsb_last_launch_info(out), "nsb_last_launch_info")
+    keys = ("used_tma", "warps_per_cta", "stages", "lanes_per_thread", "grid", "smem_bytes",
+            "tile_steps", "launches")
+    return dict(zip(keys, out))
+
+
+def device_error_word() -> int:
+    w = c_uint32(0)
+    check(lib().nsb_device_error_word(ctypes.byref(w)), "nsb_device_error_word")
+    return int(w.value)

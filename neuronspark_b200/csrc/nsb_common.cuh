@@ -1,0 +1,169 @@
+// Shared device/host helpers for the neuronspark_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda.h>  // CUtensorMap (types only; the encoder is fetched at run time)
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/neuronspark_b200.h"
+
+namespace nsb {
+
+// ------------------------------------------------------------------ host side
+
+// Thread-local record of the last CUDA failure, and of the last launch shape.
+void set_cuda_error(cudaError_t e, const char* where);
+void set_driver_error(int cu_result, const char* where);
+struct LaunchInfo {
+  int used_tma, warps_per_cta, stages, lanes_per_thread, grid, smem_bytes, tile_steps, launches;
+};
+LaunchInfo& last_launch();
+
+struct Tuning {
+  int warps_per_cta = 0, stages = 0, lanes_per_thread = 0, force_direct = 0;
+};
+Tuning get_tuning();
+
+// Device properties that the launch heuristics need (cached per device).
+struct DeviceInfo {
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  int max_smem_optin = 0;     // per CTA
+  int smem_per_sm = 0;
+  int reserved_smem_per_cta = 0;
+};
+int get_device_info(DeviceInfo* out);  // returns NSB status
+
+// Pointer to the device-visible error word (mapped pinned host memory, one per
+// process). Returns nullptr if it could not be set up.
+uint32_t* device_error_word_ptr();
+
+// 2-D tiled tensor map over a row-major [rows, cols] tensor; box = [box_rows, box_cols].
+// elem: NSB dtype, or 100 for raw fp32/uint32 words.
+int make_tensor_map_2d(CUtensorMap* out, const void* base, int dtype, uint64_t rows,
+                       uint64_t cols, uint32_t box_rows, uint32_t box_cols);
+
+inline size_t dtype_size(int dt) { return dt == NSB_F32 ? 4 : 2; }
+
+#define NSB_CUDA_TRY(expr, where)                 \
+  do {                                            \
+    cudaError_t _e = (expr);                      \
+    if (_e != cudaSuccess) {                      \
+      ::nsb::set_cuda_error(_e, where);           \
+      return NSB_ERR_CUDA;                        \
+    }                                             \
+  } while (0)
+
+// ---------------------------------------------------------------- device side
+#ifdef __CUDACC__
+
+// Element traits: widening to fp32 is exact; narrowing is round-to-nearest-even.
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static constexpr int kDtype = NSB_F32;
+  __device__ static __forceinline__ float to_f32(float v) { return v; }
+  __device__ static __forceinline__ float from_f32(float v) { return v; }
+  __device__ static __forceinline__ float one() { return 1.0f; }
+  __device__ static __forceinline__ float zero() { return 0.0f; }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static constexpr int kDtype = NSB_BF16;
+  __device__ static __forceinline__ float to_f32(__nv_bfloat16 v) {
+    return __uint_as_float(((uint32_t)__bfloat16_as_ushort(v)) << 16);
+  }
+  __device__ static __forceinline__ __nv_bfloat16 from_f32(float v) {
+    return __float2bfloat16_rn(v);
+  }
+  __device__ static __forceinline__ __nv_bfloat16 one() { return __ushort_as_bfloat16(0x3F80); }
+  __device__ static __forceinline__ __nv_bfloat16 zero() { return __ushort_as_bfloat16(0); }
+};
+template <>
+struct Elem<__half> {
+  static constexpr int kDtype = NSB_F16;
+  __device__ static __forceinline__ float to_f32(__half v) { return __half2float(v); }
+  __device__ static __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+  __device__ static __forceinline__ __half one() { return __ushort_as_half(0x3C00); }
+  __device__ static __forceinline__ __half zero() { return __ushort_as_half(0); }
+};
+
+// A small aligned vector of N elements, moved with one load/store instruction.
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Vec {
+  T v[N];
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void proxy_async_fence() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait on an mbarrier phase: gives up after ~2 s of wall time, records
+// `code` in the error word and returns false. Never spins forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
+                                                  uint32_t* err_word, uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++it & 0xFF) == 0) {
+      if (global_timer_ns() - t0 > 2000000000ull || it > (1u << 28)) {
+        if (err_word) atomicOr(reinterpret_cast<unsigned int*>(err_word), code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// One 2-D TMA tile load into this CTA's shared memory, completion counted in
+// bytes on `bar`. x = innermost (column) coordinate, y = row (time) coordinate.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(tm), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
+}
+
+#endif  // __CUDACC__
+
+}  // namespace nsb

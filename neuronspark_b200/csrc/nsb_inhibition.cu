@@ -1,0 +1,253 @@
+// Lateral inhibition (divisive normalisation, = RMSNorm) forward and backward.
+//
+// out = x * rsqrt(mean(x^2) + eps) * gain over rows of D elements, fp32 math.
+// One warp owns one row at a time and strides over the rows of the problem; a
+// lane owns the fixed set of channels {lane*VE + 32*VE*i}, so the per-channel
+// gain gradient of the backward can be accumulated privately (no atomics):
+// each warp keeps a [D] fp32 accumulator row in shared memory, the warps of a
+// CTA are summed in a fixed order into one partial row per CTA, and a second
+// small kernel sums the partial rows in a fixed order. The result is therefore
+// bit-reproducible from run to run.
+#include "nsb_common.cuh"
+
+namespace nsb {
+namespace {
+
+constexpr int kWarpsPerCta = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename T, typename TG, int VE>
+__global__ void li_fwd_kernel(const T* __restrict__ x, const TG* __restrict__ gain, T* __restrict__ out,
+                              long long rows, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const float inv_d = 1.0f / (float)D;
+  for (long long r = warp; r < rows; r += nwarps) {
+    const T* xr = x + r * D;
+    float ss = 0.0f;
+    for (int d = lane * VE; d < D; d += 32 * VE) {
+      const Vec<T, VE> v = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+#pragma unroll
+      for (int j = 0; j < VE; ++j) {
+        const float f = Elem<T>::to_f32(v.v[j]);
+        ss += f * f;
+      }
+    }
+    ss = warp_sum(ss);
+    const float rrms = 1.0f / sqrtf(ss * inv_d + eps);
+    T* orow = out + r * D;
+    for (int d = lane * VE; d < D; d += 32 * VE) {
+      const Vec<T, VE> v = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+      const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);
+      Vec<T, VE> o;
+#pragma unroll
+      for (int j = 0; j < VE; ++j)
+        o.v[j] = Elem<T>::from_f32(Elem<T>::to_f32(v.v[j]) * rrms * Elem<TG>::to_f32(g.v[j]));
+      *reinterpret_cast<Vec<T, VE>*>(orow + d) = o;
+    }
+  }
+}
+
+// Backward, stage 1: g_x for every row, and one partial g_gain row per CTA.
+template <typename T, typename TG, int VE>
+__global__ void li_bwd_kernel(const T* __restrict__ g_out, const T* __restrict__ x,
+                              const TG* __restrict__ gain, T* __restrict__ g_x,
+                              float* __restrict__ partial, long long rows, int D, float eps) {
+  extern __shared__ float acc_smem[];  // [warps][D]
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int wpc = blockDim.x >> 5;
+  const long long warp = (long long)blockIdx.x * wpc + wib;
+  const long long nwarps = (long long)gridDim.x * wpc;
+  float* acc = acc_smem + (size_t)wib * D;
+  for (int d = lane; d < D; d += 32) acc[d] = 0.0f;
+  __syncwarp();
+  const float inv_d = 1.0f / (float)D;
+  for (long long r = warp; r < rows; r += nwarps) {
+    const T* xr = x + r * D;
+    const T* gr = g_out + r * D;
+    float ss = 0.0f, dot = 0.0f;
+    for (int d = lane * VE; d < D; d += 32 * VE) {
+      const Vec<T, VE> v = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+      const Vec<T, VE> go = *reinterpret_cast<const Vec<T, VE>*>(gr + d);
+      const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);
+#pragma unroll
+      for (int j = 0; j < VE; ++j) {
+        const float f = Elem<T>::to_f32(v.v[j]);
+        ss += f * f;
+        dot += Elem<T>::to_f32(go.v[j]) * Elem<TG>::to_f32(g.v[j]) * f;
+      }
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float rrms = 1.0f / sqrtf(ss * inv_d + eps);
+    // mean(dout*gain*x_hat) = rrms * sum(dout*gain*x) / D
+    const float mean_dot = dot * rrms * inv_d;
+    T* dxr = g_x + r * D;
+    for (int d = lane * VE; d < D; d += 32 * VE) {
+      const Vec<T, VE> v = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+      const Vec<T, VE> go = *reinterpret_cast<const Vec<T, VE>*>(gr + d);
+      const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);
+      Vec<T, VE> o;
+#pragma unroll
+      for (int j = 0; j < VE; ++j) {
+        const float xh = Elem<T>::to_f32(v.v[j]) * rrms;
+        const float dout = Elem<T>::to_f32(go.v[j]);
+        const float dg = dout * Elem<TG>::to_f32(g.v[j]);
+        o.v[j] = Elem<T>::from_f32((dg - xh * mean_dot) * rrms);
+        acc[d + j] += dout * xh;
+      }
+      *reinterpret_cast<Vec<T, VE>*>(dxr + d) = o;
+    }
+  }
+  __syncthreads();
+  float* prow = partial + (size_t)blockIdx.x * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float s = 0.0f;
+    for (int w = 0; w < wpc; ++w) s += acc_smem[(size_t)w * D + d];
+    prow[d] = s;
+  }
+}
+
+// Backward, stage 2: g_gain[d] = sum over partial rows, fixed order.
+__global__ void li_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ g_gain,
+                                     int nparts, int D) {
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  float s = 0.0f;
+  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * D + d];
+  g_gain[d] = s;
+}
+
+int bwd_grid(long long rows, int D, int* wpc_out) {
+  DeviceInfo dev;
+  if (get_device_info(&dev) != NSB_OK) return 0;
+  int wpc = kWarpsPerCta;
+  while (wpc > 1 && (size_t)wpc * D * sizeof(float) > (size_t)dev.max_smem_optin) wpc >>= 1;
+  if ((size_t)wpc * D * sizeof(float) > (size_t)dev.max_smem_optin) return 0;
+  long long g = (rows + wpc - 1) / wpc;
+  const long long cap = (long long)dev.sm_count * 2;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  if (wpc_out) *wpc_out = wpc;
+  return (int)g;
+}
+
+bool dtype_ok(int d) { return d == NSB_F32 || d == NSB_BF16 || d == NSB_F16; }
+
+template <typename F>
+int with_dtype(int dtype, F&& f) {
+  switch (dtype) {
+    case NSB_F32: return f(float{});
+    case NSB_BF16: return f(__nv_bfloat16{});
+    case NSB_F16: return f(__half{});
+    default: return NSB_ERR_INVALID_ARG;
+  }
+}
+
+template <typename T, typename TG>
+bool can_vec(int ve, long long D, std::initializer_list<const void*> tp, const void* gp) {
+  if (D % ve) return false;
+  for (const void* p : tp)
+    if (reinterpret_cast<uintptr_t>(p) % (sizeof(T) * ve)) return false;
+  return reinterpret_cast<uintptr_t>(gp) % (sizeof(TG) * ve) == 0;
+}
+
+}  // namespace
+}  // namespace nsb
+
+using namespace nsb;
+
+extern "C" {
+
+int nsb_lateral_inhibition_fwd(const void* x, const void* gain, void* out, int64_t rows, int64_t D,
+                               float eps, int dtype, int gain_dtype, void* stream) {
+  if (rows < 0 || D < 0 || D >= (1ll << 31) || !dtype_ok(dtype) || !dtype_ok(gain_dtype))
+    return NSB_ERR_INVALID_ARG;
+  if (rows == 0 || D == 0) return NSB_OK;
+  if (!x || !gain || !out) return NSB_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DeviceInfo dev;
+  int r = get_device_info(&dev);
+  if (r != NSB_OK) return r;
+  long long grid = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+  grid = std::min<long long>(grid, (long long)dev.sm_count * 8);
+  return with_dtype(dtype, [&](auto t) {
+    using T = decltype(t);
+    return with_dtype(gain_dtype, [&](auto tg) {
+      using TG = decltype(tg);
+      if (!can_vec<T, TG>(1, D, {x, out}, gain)) return NSB_ERR_INVALID_ARG;
+      const T* xp = static_cast<const T*>(x);
+      const TG* gp = static_cast<const TG*>(gain);
+      T* op = static_cast<T*>(out);
+      if (can_vec<T, TG>(4, D, {x, out}, gain))
+        li_fwd_kernel<T, TG, 4><<<(int)grid, kWarpsPerCta * 32, 0, st>>>(xp, gp, op, rows, (int)D, eps);
+      else if (can_vec<T, TG>(2, D, {x, out}, gain))
+        li_fwd_kernel<T, TG, 2><<<(int)grid, kWarpsPerCta * 32, 0, st>>>(xp, gp, op, rows, (int)D, eps);
+      else
+        li_fwd_kernel<T, TG, 1><<<(int)grid, kWarpsPerCta * 32, 0, st>>>(xp, gp, op, rows, (int)D, eps);
+      NSB_CUDA_TRY(cudaGetLastError(), "launch li_fwd_kernel");
+      return NSB_OK;
+    });
+  });
+}
+
+int64_t nsb_li_bwd_scratch_floats(int64_t rows, int64_t D) {
+  if (rows <= 0 || D <= 0 || D >= (1ll << 31)) return 0;
+  const int g = bwd_grid(rows, (int)D, nullptr);
+  return (int64_t)g * D;
+}
+
+int nsb_lateral_inhibition_bwd(const void* g_out, const void* x, const void* gain, void* g_x,
+                               float* g_gain, float* partial, int64_t rows, int64_t D, float eps,
+                               int dtype, int gain_dtype, void* stream) {
+  if (rows < 0 || D < 0 || D >= (1ll << 31) || !dtype_ok(dtype) || !dtype_ok(gain_dtype))
+    return NSB_ERR_INVALID_ARG;
+  if (D == 0) return NSB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!g_gain || (reinterpret_cast<uintptr_t>(g_gain) & 3u)) return NSB_ERR_INVALID_ARG;
+  if (rows == 0) {
+    NSB_CUDA_TRY(cudaMemsetAsync(g_gain, 0, sizeof(float) * D, st), "memset g_gain");
+    return NSB_OK;
+  }
+  if (!g_out || !x || !gain || !g_x || !partial || (reinterpret_cast<uintptr_t>(partial) & 3u))
+    return NSB_ERR_INVALID_ARG;
+  int wpc = 0;
+  const int grid = bwd_grid(rows, (int)D, &wpc);
+  if (grid == 0) return NSB_ERR_TOO_LARGE;
+  const size_t smem = (size_t)wpc * D * sizeof(float);
+  return with_dtype(dtype, [&](auto t) {
+    using T = decltype(t);
+    return with_dtype(gain_dtype, [&](auto tg) {
+      using TG = decltype(tg);
+      if (!can_vec<T, TG>(1, D, {g_out, x, g_x}, gain)) return NSB_ERR_INVALID_ARG;
+      const T* gop = static_cast<const T*>(g_out);
+      const T* xp = static_cast<const T*>(x);
+      const TG* gp = static_cast<const TG*>(gain);
+      T* gxp = static_cast<T*>(g_x);
+#define NSB_LI_BWD(VE_)                                                                          \
+  {                                                                                              \
+    auto k = li_bwd_kernel<T, TG, VE_>;                                                          \
+    NSB_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), \
+                 "cudaFuncSetAttribute(li_bwd)");                                                \
+    k<<<grid, wpc * 32, smem, st>>>(gop, xp, gp, gxp, partial, rows, (int)D, eps);               \
+  }
+      if (can_vec<T, TG>(4, D, {g_out, x, g_x}, gain)) NSB_LI_BWD(4)
+      else if (can_vec<T, TG>(2, D, {g_out, x, g_x}, gain)) NSB_LI_BWD(2)
+      else NSB_LI_BWD(1)
+#undef NSB_LI_BWD
+      NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_kernel");
+      li_bwd_reduce_kernel<<<(int)((D + 255) / 256), 256, 0, st>>>(partial, g_gain, grid, (int)D);
+      NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_reduce_kernel");
+      return NSB_OK;
+    });
+  });
+}
+
+}  // extern "C"

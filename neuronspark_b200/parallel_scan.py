@@ -1,0 +1,484 @@
+"""PLIF scan operators with the call signatures of NeuronSpark's
+``atomic_ops/parallel_scan.py``, backed by the sm_100a CUDA kernels.
+
+Drop-in surface (same names, argument order, return arity and gradient
+semantics as the reference):
+
+    _TritonPLIFForward.apply(beta, u, v_th, v_init, alpha) -> (spike, V_post)
+        reference: atomic_ops/parallel_scan.py:690-768
+    _TritonPLIFRowParamForward.apply(beta_row, u, v_th_row, v_init, alpha) -> (spike, V_post)
+        reference: :415-486
+    _TritonPLIFRowParamRecompute.apply(beta_row, u, v_th_row, v_init, alpha) -> (spike, V_last)
+        reference: :614-688
+    plif_parallel_forward, plif_rowparam_forward, plif_rowparam_forward_alpha,
+    plif_rowparam_forward_recompute, plif_fixed_param_forward
+        reference: :1309-1412, :1415-1453, :1456-1495, :1499-1535, :1538-1603
+
+Differences, all deliberate:
+  * CUDA only. A CPU tensor raises; nothing falls back to PyTorch ops.
+  * The backward recomputes the membrane trajectory from one fp32 checkpoint
+    per time tile instead of reading a stored V_post, so no [T, ...] state
+    tensor is kept between forward and backward.
+  * The recompute variant returns a freshly allocated grad_u; the reference
+    hands back the saved ``u`` buffer overwritten in place (:687-688).
+  * Arithmetic is fp32 with separately rounded multiply and add, which is what
+    the reference's eager PyTorch time loop computes, so spikes are bit-exact
+    against that loop.
+Extras that the reference does not have: the alpha*I form with separate
+gradients for the write gain and the current (`plif_selective_scan_ai`), an
+arctangent surrogate, and the bit-packed inference scans.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import NSBError
+
+#: Steps per time tile = spacing of the fp32 state checkpoints kept for backward.
+CKPT_INTERVAL = 8
+
+_SURROGATES = {"sigmoid": _lib.SURR_SIGMOID, "atan": _lib.SURR_ATAN}
+
+
+# ----------------------------------------------------------------- helpers
+
+
+def _cols(t: torch.Tensor) -> int:
+    n = 1
+    for s in t.shape[1:]:
+        n *= s
+    return n
+
+
+def _common_stream_dtype(*tensors: torch.Tensor) -> torch.dtype:
+    """The single element type the kernel will stream. Tensors of one low-precision
+    type are streamed as they are; mixed inputs are widened to fp32, which is exact
+    (the reference widens every load to fp32 individually, :223-225)."""
+    dts = {t.dtype for t in tensors if t is not None}
+    if len(dts) == 1:
+        (dt,) = dts
+        if dt in (torch.float32, torch.bfloat16, torch.float16):
+            return dt
+    return torch.float32
+
+
+def _as_stream(t, dt):
+    if t is None:
+        return None
+    if t.dtype != dt:
+        t = t.to(dt)
+    return t.contiguous()
+
+
+def _row_f32(t: torch.Tensor, shape) -> torch.Tensor:
+    """Per-column vector as contiguous fp32 of the given trailing shape."""
+    if tuple(t.shape) != tuple(shape):
+        t = t.expand(shape)
+    return t.detach().to(torch.float32).contiguous()
+
+
+def _surrogate_kind(surrogate) -> int:
+    if isinstance(surrogate, int):
+        return surrogate
+    try:
+        return _SURROGATES[surrogate]
+    except KeyError:
+        raise NSBError(f"unknown surrogate {surrogate!r}; expected 'sigmoid' or 'atan'") from None
+
+
+def _n_tiles(T: int) -> int:
+    return (T + CKPT_INTERVAL - 1) // CKPT_INTERVAL
+
+
+def _launch_selective_fwd(beta, drive, gain, v_th, v_init32, *, want_spike, want_packed, want_vpost,
+                          want_ckpt):
+    """Runs nsb_plif_selective_fwd. Streams must already share dtype and be contiguous."""
+    dev = _lib.require_cuda(beta, drive, gain, v_th, v_init32)
+    T, cols = drive.shape[0], _cols(drive)
+    dt = drive.dtype
+    spike = torch.empty_like(drive) if want_spike else None
+    packed = (torch.empty((T, (cols + 31) // 32), dtype=torch.int32, device=dev)
+              if want_packed else None)
+    vpost = torch.empty_like(drive) if want_vpost else None
+    ckpt = (torch.empty((_n_tiles(T), cols), dtype=torch.float32, device=dev) if want_ckpt else None)
+    v_last = torch.empty(drive.shape[1:], dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_plif_selective_fwd(
+            _lib.ptr(beta), _lib.ptr(drive), _lib.ptr(gain), _lib.ptr(v_th), _lib.ptr(v_init32),
+            _lib.ptr(spike), _lib.ptr(packed), _lib.ptr(vpost), _lib.ptr(ckpt), _lib.ptr(v_last),
+            T, cols, _lib.dtype_code(dt), CKPT_INTERVAL, _lib.stream_ptr(dev)),
+            "nsb_plif_selective_fwd")
+    return spike, packed, vpost, ckpt, v_last
+
+
+def _launch_rowparam_fwd(beta_row32, u, vth_row32, v_init32, *, want_spike, want_packed, want_vpost,
+                         want_ckpt):
+    dev = _lib.require_cuda(beta_row32, u, vth_row32, v_init32)
+    T, cols = u.shape[0], _cols(u)
+    spike = torch.empty_like(u) if want_spike else None
+    packed = (torch.empty((T, (cols + 31) // 32), dtype=torch.int32, device=dev)
+              if want_packed else None)
+    vpost = torch.empty_like(u) if want_vpost else None
+    ckpt = (torch.empty((_n_tiles(T), cols), dtype=torch.float32, device=dev) if want_ckpt else None)
+    v_last = torch.empty(u.shape[1:], dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_plif_rowparam_fwd(
+            _lib.ptr(beta_row32), _lib.ptr(u), _lib.ptr(vth_row32), _lib.ptr(v_init32),
+            _lib.ptr(spike), _lib.ptr(packed), _lib.ptr(vpost), _lib.ptr(ckpt), _lib.ptr(v_last),
+            T, cols, _lib.dtype_code(u.dtype), CKPT_INTERVAL, _lib.stream_ptr(dev)),
+            "nsb_plif_rowparam_fwd")
+    return spike, packed, vpost, ckpt, v_last
+
+
+def _grad_stream(g, like, dt):
+    """An incoming gradient as a contiguous stream tensor (None stays None)."""
+    if g is None:
+        return None
+    if g.dtype != dt:
+        g = g.to(dt)
+    return g.contiguous()
+
+
+# ------------------------------------------------------- selective scan (u-form)
+
+
+class PLIFSelectiveScan(torch.autograd.Function):
+    """Selective PLIF scan with per-step beta / u / v_th.
+
+    Same contract as the reference's ``_TritonPLIFForward``
+    (atomic_ops/parallel_scan.py:690-768): returns ``(spike, V_post)`` in ``u``'s
+    dtype; backward returns ``(grad_beta, grad_u, grad_v_th, grad_v_init, None)``
+    with the hard spike treated as a constant in the reset path.
+    """
+
+    surrogate = _lib.SURR_SIGMOID
+
+    @staticmethod
+    def forward(ctx, beta, u, v_th, v_init, alpha):
+        out_dtype = u.dtype
+        dt = _common_stream_dtype(beta, u, v_th)
+        beta_c, u_c, vth_c = (_as_stream(t, dt) for t in (beta, u, v_th))
+        v0 = _row_f32(v_init, u.shape[1:])
+        needs_grad = any(ctx.needs_input_grad[:4])
+        spike, _, vpost, ckpt, _ = _launch_selective_fwd(
+            beta_c, u_c, None, vth_c, v0, want_spike=True, want_packed=False, want_vpost=True,
+            want_ckpt=needs_grad)
+        if needs_grad:
+            ctx.save_for_backward(beta_c, u_c, vth_c, ckpt)
+        ctx.alpha = float(alpha)
+        ctx.in_dtypes = (beta.dtype, u.dtype, v_th.dtype, v_init.dtype)
+        ctx.v_init_shape = v_init.shape
+        if spike.dtype != out_dtype:
+            spike, vpost = spike.to(out_dtype), vpost.to(out_dtype)
+        return spike, vpost
+
+    @staticmethod
+    def backward(ctx, grad_spike, grad_V_post):
+        beta_c, u_c, vth_c, ckpt = ctx.saved_tensors
+        dt = u_c.dtype
+        dev = u_c.device
+        T, cols = u_c.shape[0], _cols(u_c)
+        if grad_spike is None:
+            grad_spike = torch.zeros_like(u_c)
+        gs = _grad_stream(grad_spike, u_c, dt)
+        gv = _grad_stream(grad_V_post, u_c, dt)
+        g_beta, g_u, g_vth = (torch.empty_like(u_c) for _ in range(3))
+        g_v0 = torch.empty(u_c.shape[1:], dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().nsb_plif_selective_bwd(
+                _lib.ptr(beta_c), _lib.ptr(u_c), None, _lib.ptr(vth_c), _lib.ptr(ckpt), _lib.ptr(gs),
+                _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), None, _lib.ptr(g_vth), _lib.ptr(g_v0),
+                T, cols, _lib.dtype_code(dt), CKPT_INTERVAL, ctx_surrogate(ctx), ctx.alpha,
+                _lib.stream_ptr(dev)), "nsb_plif_selective_bwd")
+        db, du, dth, dv = ctx.in_dtypes
+        return (g_beta.to(db), g_u.to(du), g_vth.to(dth),
+                g_v0.to(dv).reshape(ctx.v_init_shape), None)
+
+
+def ctx_surrogate(ctx) -> int:
+    return getattr(ctx, "surrogate", _lib.SURR_SIGMOID)
+
+
+class PLIFSelectiveScanAI(torch.autograd.Function):
+    """Selective scan with the write gain and the current as separate inputs:
+    ``v_pre = beta*v + gain*cur`` (SelectivePLIFNode.single_step_forward,
+    atomic_ops/selective_plif.py:127). Returns ``(spike, V_last)``; gradients for
+    beta, cur, gain, v_th and v_init. ``surrogate`` is 'sigmoid' or 'atan'."""
+
+    @staticmethod
+    def forward(ctx, beta, cur, gain, v_th, v_init, alpha, surrogate):
+        out_dtype = cur.dtype
+        dt = _common_stream_dtype(beta, cur, gain, v_th)
+        beta_c, cur_c, gain_c, vth_c = (_as_stream(t, dt) for t in (beta, cur, gain, v_th))
+        v0 = _row_f32(v_init, cur.shape[1:])
+        needs_grad = any(ctx.needs_input_grad[:5])
+        spike, _, _, ckpt, v_last = _launch_selective_fwd(
+            beta_c, cur_c, gain_c, vth_c, v0, want_spike=True, want_packed=False, want_vpost=False,
+            want_ckpt=needs_grad)
+        if needs_grad:
+            ctx.save_for_backward(beta_c, cur_c, gain_c, vth_c, ckpt)
+        ctx.alpha = float(alpha)
+        ctx.surrogate = _surrogate_kind(surrogate)
+        ctx.in_dtypes = (beta.dtype, cur.dtype, gain.dtype, v_th.dtype, v_init.dtype)
+        ctx.v_init_shape = v_init.shape
+        ctx.mark_non_differentiable(v_last)
+        if spike.dtype != out_dtype:
+            spike = spike.to(out_dtype)
+        return spike, v_last.to(v_init.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_spike, _grad_v_last):
+        beta_c, cur_c, gain_c, vth_c, ckpt = ctx.saved_tensors
+        dt = cur_c.dtype
+        dev = cur_c.device
+        T, cols = cur_c.shape[0], _cols(cur_c)
+        if grad_spike is None:
+            grad_spike = torch.zeros_like(cur_c)
+        gs = _grad_stream(grad_spike, cur_c, dt)
+        g_beta, g_cur, g_gain, g_vth = (torch.empty_like(cur_c) for _ in range(4))
+        g_v0 = torch.empty(cur_c.shape[1:], dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().nsb_plif_selective_bwd(
+                _lib.ptr(beta_c), _lib.ptr(cur_c), _lib.ptr(gain_c), _lib.ptr(vth_c), _lib.ptr(ckpt),
+                _lib.ptr(gs), None, _lib.ptr(g_beta), _lib.ptr(g_cur), _lib.ptr(g_gain),
+                _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols, _lib.dtype_code(dt), CKPT_INTERVAL,
+                ctx.surrogate, ctx.alpha, _lib.stream_ptr(dev)), "nsb_plif_selective_bwd")
+        db, dc, dg, dth, dv = ctx.in_dtypes
+        return (g_beta.to(db), g_cur.to(dc), g_gain.to(dg), g_vth.to(dth),
+                g_v0.to(dv).reshape(ctx.v_init_shape), None, None)
+
+
+# ------------------------------------------------------------- row-param scans
+
+
+def _rowparam_backward(ctx, grad_spike, grad_V_post):
+    beta32, vth32, u_c, ckpt = ctx.saved_tensors
+    dt = u_c.dtype
+    dev = u_c.device
+    T, cols = u_c.shape[0], _cols(u_c)
+    if grad_spike is None:
+        grad_spike = torch.zeros_like(u_c)
+    gs = _grad_stream(grad_spike, u_c, dt)
+    gv = _grad_stream(grad_V_post, u_c, dt)
+    g_u = torch.empty_like(u_c)
+    g_beta, g_vth, g_v0 = (torch.empty(u_c.shape[1:], dtype=torch.float32, device=dev)
+                           for _ in range(3))
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_plif_rowparam_bwd(
+            _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(ckpt), _lib.ptr(gs),
+            _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols,
+            _lib.dtype_code(dt), CKPT_INTERVAL, ctx_surrogate(ctx), ctx.alpha,
+            _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd")
+    db, du, dth, dv = ctx.in_dtypes
+    return (g_beta.to(db).reshape(ctx.row_shapes[0]), g_u.to(du),
+            g_vth.to(dth).reshape(ctx.row_shapes[1]), g_v0.to(dv).reshape(ctx.row_shapes[2]), None)
+
+
+def _rowparam_forward(ctx, beta_row, u, v_th_row, v_init, alpha, want_vpost):
+    shape = u.shape[1:]
+    for name, t in (("beta_row", beta_row), ("v_th_row", v_th_row), ("v_init", v_init)):
+        if tuple(t.shape) != tuple(shape):
+            raise NSBError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+    dt = _common_stream_dtype(u)
+    u_c = _as_stream(u, dt)
+    beta32, vth32, v0 = (_row_f32(t, shape) for t in (beta_row, v_th_row, v_init))
+    needs_grad = any(ctx.needs_input_grad[:4])
+    spike, _, vpost, ckpt, v_last = _launch_rowparam_fwd(
+        beta32, u_c, vth32, v0, want_spike=True, want_packed=False, want_vpost=want_vpost,
+        want_ckpt=needs_grad)
+    if needs_grad:
+        ctx.save_for_backward(beta32, vth32, u_c, ckpt)
+    ctx.alpha = float(alpha)
+    ctx.in_dtypes = (beta_row.dtype, u.dtype, v_th_row.dtype, v_init.dtype)
+    ctx.row_shapes = (beta_row.shape, v_th_row.shape, v_init.shape)
+    if spike.dtype != u.dtype:
+        spike = spike.to(u.dtype)
+        vpost = None if vpost is None else vpost.to(u.dtype)
+    return spike, vpost, v_last
+
+
+class PLIFRowParamScan(torch.autograd.Function):
+    """Row-parameter PLIF scan returning ``(spike, V_post)``; contract of the
+    reference's ``_TritonPLIFRowParamForward`` (atomic_ops/parallel_scan.py:415-486)."""
+
+    @staticmethod
+    def forward(ctx, beta_row, u, v_th_row, v_init, alpha):
+        spike, vpost, _ = _rowparam_forward(ctx, beta_row, u, v_th_row, v_init, alpha, True)
+        return spike, vpost
+
+    @staticmethod
+    def backward(ctx, grad_spike, grad_V_post):
+        return _rowparam_backward(ctx, grad_spike, grad_V_post)
+
+
+class PLIFRowParamRecomputeScan(torch.autograd.Function):
+    """Row-parameter PLIF scan returning ``(spike, V_last)``; contract of the
+    reference's ``_TritonPLIFRowParamRecompute`` (:614-688): the gradient that
+    arrives for ``V_last`` is ignored (:659)."""
+
+    @staticmethod
+    def forward(ctx, beta_row, u, v_th_row, v_init, alpha):
+        spike, _, v_last = _rowparam_forward(ctx, beta_row, u, v_th_row, v_init, alpha, False)
+        return spike, v_last.to(v_init.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_spike, _grad_V_last_unused):
+        return _rowparam_backward(ctx, grad_spike, None)
+
+
+# Names the reference's callers import (snn_block.py, snn_ffn.py, test_recompute.py ...).
+_TritonPLIFForward = PLIFSelectiveScan
+_TritonPLIFRowParamForward = PLIFRowParamScan
+_TritonPLIFRowParamRecompute = PLIFRowParamRecomputeScan
+_HAS_TRITON = False  # nothing here uses Triton
+
+
+# ------------------------------------------------------------ public functions
+
+
+def _alpha_and_kind(surrogate_function):
+    """(alpha, kind) of a SpikingJelly-style surrogate object, by class name as
+    the reference does (atomic_ops/parallel_scan.py:1347-1349)."""
+    name = type(surrogate_function).__name__
+    if not hasattr(surrogate_function, "alpha"):
+        raise NSBError(f"surrogate {name} has no .alpha")
+    if name == "Sigmoid":
+        return float(surrogate_function.alpha), _lib.SURR_SIGMOID
+    if name == "ATan":
+        return float(surrogate_function.alpha), _lib.SURR_ATAN
+    raise NSBError(f"surrogate {name} is not supported (Sigmoid or ATan)")
+
+
+class _SelectiveScanATan(PLIFSelectiveScan):
+    """u-form selective scan with the arctangent surrogate in the backward."""
+
+    @staticmethod
+    def forward(ctx, beta, u, v_th, v_init, alpha):
+        ctx.surrogate = _lib.SURR_ATAN
+        return PLIFSelectiveScan.forward(ctx, beta, u, v_th, v_init, alpha)
+
+
+def plif_parallel_forward(beta, u, v_th, v_init, max_iter: int = 3, surrogate_function=None):
+    """Selective PLIF forward; returns ``(spike, V_post, None)`` like the reference's
+    fused path (atomic_ops/parallel_scan.py:1309-1352). ``max_iter`` is accepted
+    for signature compatibility and unused: the sequential scan is exact. With
+    ``surrogate_function=None`` the outputs carry no gradient."""
+    del max_iter
+    if surrogate_function is None:
+        with torch.no_grad():
+            spike, vpost = PLIFSelectiveScan.apply(beta, u, v_th, v_init, 0.0)
+        return spike, vpost, None
+    alpha, kind = _alpha_and_kind(surrogate_function)
+    fn = PLIFSelectiveScan if kind == _lib.SURR_SIGMOID else _SelectiveScanATan
+    spike, vpost = fn.apply(beta, u, v_th, v_init, alpha)
+    return spike, vpost, None
+
+
+def _rows(u, *rows):
+    """Per-column arguments may be given per channel ([D]) or already expanded to
+    ``u.shape[1:]``; broadcasting here keeps their gradients flowing through expand."""
+    shape = u.shape[1:]
+    return tuple(r if tuple(r.shape) == tuple(shape) else r.expand(shape) for r in rows)
+
+
+def plif_rowparam_forward(beta_row, u, v_th_row, v_init, surrogate_function=None):
+    """Reference: atomic_ops/parallel_scan.py:1415-1453. Returns ``(spike, V_post)``."""
+    beta_row, v_th_row, v_init = _rows(u, beta_row, v_th_row, v_init)
+    if surrogate_function is None:
+        with torch.no_grad():
+            return PLIFRowParamScan.apply(beta_row, u, v_th_row, v_init, 0.0)
+    alpha, kind = _alpha_and_kind(surrogate_function)
+    if kind != _lib.SURR_SIGMOID:
+        raise NSBError("row-parameter scans support the Sigmoid surrogate only")
+    return PLIFRowParamScan.apply(beta_row, u, v_th_row, v_init, alpha)
+
+
+def plif_rowparam_forward_alpha(beta_row, u, v_th_row, v_init, alpha: float):
+    """Reference: atomic_ops/parallel_scan.py:1456-1495. Returns ``(spike, V_post)``."""
+    beta_row, v_th_row, v_init = _rows(u, beta_row, v_th_row, v_init)
+    return PLIFRowParamScan.apply(beta_row, u, v_th_row, v_init, alpha)
+
+
+def plif_rowparam_forward_recompute(beta_row, u, v_th_row, v_init, alpha: float):
+    """Reference: atomic_ops/parallel_scan.py:1499-1535. Returns ``(spike, V_last)``."""
+    beta_row, v_th_row, v_init = _rows(u, beta_row, v_th_row, v_init)
+    return PLIFRowParamRecomputeScan.apply(beta_row, u, v_th_row, v_init, alpha)
+
+
+def plif_fixed_param_forward(beta, u, v_th, v_init, max_iter: int = 3, surrogate_function=None):
+    """Reference: atomic_ops/parallel_scan.py:1538-1603. Scalar (float or 0-dim
+    tensor) beta and v_th take the row-parameter kernel; anything else is expanded
+    to ``u``'s shape and takes the selective kernel. Returns ``(spike, V_post)``."""
+    K = u.shape[0]
+    shape = u.shape[1:]
+
+    def is_scalar(x):
+        return (not isinstance(x, torch.Tensor)) or x.dim() == 0
+
+    if is_scalar(beta) and is_scalar(v_th):
+        def row(x):
+            if isinstance(x, torch.Tensor):
+                return x.expand(*shape)
+            return torch.full(shape, float(x), device=u.device, dtype=u.dtype)
+        return plif_rowparam_forward(row(beta), u, row(v_th), v_init, surrogate_function)
+
+    def full(x):
+        if isinstance(x, torch.Tensor):
+            return x.expand(K, *shape) if x.dim() == 0 else x
+        return torch.full_like(u, float(x))
+    spike, vpost, _ = plif_parallel_forward(full(beta), u, full(v_th), v_init, max_iter,
+                                            surrogate_function)
+    return spike, vpost
+
+
+# ---------------------------------------------------------- B200-native extras
+
+
+def plif_selective_scan_ai(beta, cur, gain, v_th, v_init, alpha: float = 4.0,
+                           surrogate: str = "sigmoid"):
+    """Selective scan in the alpha*I form with gradients for beta, cur, gain, v_th
+    and v_init. Returns ``(spike, V_last)``."""
+    return PLIFSelectiveScanAI.apply(beta, cur, gain, v_th, v_init, alpha, surrogate)
+
+
+@torch.no_grad()
+def plif_selective_forward_packed(beta, drive, v_th, v_init, gain=None):
+    """Inference scan with bit-packed spikes.
+
+    Returns ``(packed, V_last)``: ``packed`` is int32 ``[T, ceil(cols/32)]`` where
+    bit i of word w is column 32*w+i of the flattened trailing dims (tail bits
+    zero) and ``V_last`` is fp32 — pass it as ``v_init`` of the next call to carry
+    the state across calls (per-token decoding)."""
+    dt = _common_stream_dtype(beta, drive, v_th, gain)
+    beta_c, drive_c, vth_c, gain_c = (_as_stream(t, dt) for t in (beta, drive, v_th, gain))
+    v0 = _row_f32(v_init, drive.shape[1:])
+    _, packed, _, _, v_last = _launch_selective_fwd(
+        beta_c, drive_c, gain_c, vth_c, v0, want_spike=False, want_packed=True, want_vpost=False,
+        want_ckpt=False)
+    return packed, v_last
+
+
+@torch.no_grad()
+def plif_rowparam_forward_packed(beta_row, u, v_th_row, v_init):
+    """Row-parameter inference scan with bit-packed spikes; see
+    :func:`plif_selective_forward_packed` for the layout."""
+    shape = u.shape[1:]
+    u_c = _as_stream(u, _common_stream_dtype(u))
+    beta32, vth32, v0 = (_row_f32(t, shape) for t in (beta_row, v_th_row, v_init))
+    _, packed, _, _, v_last = _launch_rowparam_fwd(
+        beta32, u_c, vth32, v0, want_spike=False, want_packed=True, want_vpost=False,
+        want_ckpt=False)
+    return packed, v_last
+
+
+def unpack_spikes(packed: torch.Tensor, shape, dtype=torch.float32) -> torch.Tensor:
+    """Expands bit-packed spikes ``[T, ceil(cols/32)]`` to a dense ``[T, *shape]``
+    tensor of {0,1}. A convenience for tests and debugging (plain PyTorch ops)."""
+    T = packed.shape[0]
+    cols = 1
+    for s in shape:
+        cols *= s
+    bits = torch.arange(32, device=packed.device, dtype=torch.int32)
+    dense = ((packed.unsqueeze(-1) >> bits) & 1).reshape(T, -1)[:, :cols]
+    return dense.to(dtype).reshape(T, *shape)

@@ -1,0 +1,83 @@
+"""CPU-side checks of the C-ABI library and of the host logic: the shared
+object loads, exports every symbol the header declares, and the Python mirror
+refuses to run without a CUDA device (no fallback)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    from neuronspark_b200 import build
+    return build.build()
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "neuronspark_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nsb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    handle = ctypes.CDLL(str(built_lib))
+    names = declared_symbols()
+    assert len(names) >= 18
+    for n in names:
+        assert hasattr(handle, n), f"{n} is declared in the header but not exported"
+
+
+def test_binding_covers_the_header(built_lib):
+    from neuronspark_b200 import _lib
+    assert sorted(_lib.EXPORTED_SYMBOLS) == declared_symbols()
+    L = _lib.lib()
+    assert L.nsb_version() >= 100
+    assert L.nsb_status_string(0) == b"ok"
+    for code in range(1, 6):
+        assert L.nsb_status_string(code) not in (b"ok", b"unknown status")
+    assert L.nsb_status_string(99) == b"unknown status"
+
+
+def test_argument_validation_needs_no_gpu(built_lib):
+    """Bad sizes / enums are rejected before anything touches CUDA."""
+    from neuronspark_b200 import _lib
+    L = _lib.lib()
+    z = ctypes.c_void_p(0)
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, -1, 8, 0, 8, z) == 1
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 8, 7, 8, z) == 1   # dtype
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 8, 0, 5, z) == 1   # interval
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 8, 0, 8, z) == 1   # nulls
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 0, 0, 8, z) == 0   # empty
+    assert L.nsb_plif_selective_bwd(z, z, z, z, z, z, z, z, z, z, z, z, 8, 8, 0, 8, 9, 1.0, z) == 1
+    assert L.nsb_plif_rowparam_fwd(z, z, z, z, z, z, z, z, z, 4, 4, 0, 8, z) == 1
+    assert L.nsb_fp16_encode(z, z, 1, 1, 0, 0, 0, z) == 0
+    assert L.nsb_fp16_encode(z, z, 1, 1, 4, 0, 0, z) == 1
+    assert L.nsb_set_tuning(64, 0, 0, 0) == 1 and L.nsb_set_tuning(0, 0, 3, 0) == 1
+    assert L.nsb_set_tuning(0, 0, 0, 0) == 0
+
+
+def test_no_cpu_fallback(built_lib):
+    import neuronspark_b200 as nsb
+    from neuronspark_b200 import fp16_codec, lateral_inhibition, parallel_scan
+    with pytest.raises(nsb.NSBError):
+        parallel_scan.plif_rowparam_forward_alpha(torch.ones(2, 4), torch.ones(3, 2, 4),
+                                                  torch.ones(2, 4), torch.zeros(2, 4), 4.0)
+    with pytest.raises(nsb.NSBError):
+        fp16_codec.fp16_encode(torch.ones(1, 2, 4))
+    with pytest.raises(nsb.NSBError):
+        lateral_inhibition.LateralInhibition(4)(torch.ones(2, 4))
+
+
+def test_stream_dtype_rule():
+    from neuronspark_b200.parallel_scan import _common_stream_dtype
+    b, h, f = (torch.empty(1, dtype=d) for d in (torch.bfloat16, torch.float16, torch.float32))
+    assert _common_stream_dtype(b, b, b) == torch.bfloat16
+    assert _common_stream_dtype(h, h) == torch.float16
+    assert _common_stream_dtype(b, f, b) == torch.float32
+    assert _common_stream_dtype(b, h) == torch.float32
+    assert _common_stream_dtype(torch.empty(1, dtype=torch.float64)) == torch.float32
+    assert _common_stream_dtype(b, None, b) == torch.bfloat16
