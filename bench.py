@@ -1,0 +1,460 @@
+#!/usr/bin/env python
+"""Benchmark of the fused selective PLIF scan, forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload ("c2"): B=32 per GPU, T=8192, D=6144, bf16 streams (I, beta, alpha,
+V_th, dL/dspike), fp32 membrane state, arctangent surrogate (alpha=2),
+gradients for I, beta, alpha, V_th and V0. Inputs are seeded synthetic tensors
+with the distributions of the reference's training shapes (no dataset is
+needed or available). One "step" = one forward + one backward over the whole
+batch. Metric: neuron-steps/s = B*T*D / time, whole job (all ranks).
+
+Multi-GPU: one process per GPU under torchrun, the batch is sharded by rank
+(weak scaling: B=32 on every GPU), no collective inside the timed region; NCCL
+is used for the timing barrier, the max-over-ranks reduction and a checksum
+gather after timing.
+
+--impl reference times the CPU restatement of the reference's sequential path
+(oracle/plif_oracle.c, OpenMP over all host cores) on a bounded batch slice of
+the same workload; the reference itself is Python + Triton and has no
+compiled CPU implementation to build.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "PLIF scan neuron-steps/s (B*T*D), selective forward+backward"
+UNIT = "neuron-steps/s"
+ALPHA = 2.0
+WORKLOADS = {
+    # name: (B per GPU, T, D)
+    "c2": (32, 8192, 6144),
+    "c2-short": (32, 512, 6144),   # same grid, 1/16 of the time steps (2.8 GB): profiler captures
+    "c0": (2, 1024, 768),
+}
+# algorithmic bytes per neuron-step with 2-byte streams
+BYTES_FWD = 4 * 2 + 2          # beta, I, alpha, V_th in; spikes out
+BYTES_BWD = 4 * 2 + 2 + 4 * 2  # the four inputs again, dL/dspike in; four gradients out
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    return ap.parse_args()
+
+
+def hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ----------------------------------------------------------------- inputs
+
+
+def make_inputs(B, T, D, device, seed):
+    """bf16 I, beta, alpha(gain), V_th, dL/dspike and fp32 V0 = 0, generated on the device."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+
+    def rn(scale=1.0, shift=0.0):
+        # generated in slices so that no fp32 temporary of the full size is needed
+        out = torch.empty((T, B, D), dtype=torch.bfloat16, device=device)
+        step = max(1, T // 16)
+        for t0 in range(0, T, step):
+            n = min(step, T - t0)
+            out[t0:t0 + n] = (torch.randn((n, B, D), generator=g, device=device) * scale + shift)
+        return out
+
+    def tf(x, fn):
+        step = max(1, T // 16)
+        for t0 in range(0, T, step):
+            sl = slice(t0, min(T, t0 + step))
+            x[sl] = fn(x[sl].float()).to(torch.bfloat16)
+        return x
+
+    import torch.nn.functional as F
+    cur = rn()
+    beta = tf(rn(0.5, 2.0), torch.sigmoid)
+    gain = tf(rn(), F.softplus)
+    vth = tf(rn(), lambda z: 0.1 + F.softplus(z))
+    g_spike = rn(0.1)  # N(0, 1e-2): sigma = 0.1
+    v0 = torch.zeros((B, D), dtype=torch.float32, device=device)
+    return dict(beta=beta, cur=cur, gain=gain, vth=vth, g_spike=g_spike, v0=v0)
+
+
+class ScanStep:
+    """Pre-allocated forward+backward through the C ABI (device-resident buffers)."""
+
+    def __init__(self, inp, B, T, D):
+        import torch
+        from neuronspark_b200 import _lib, parallel_scan as ps
+        self._lib = _lib
+        self.L = _lib.lib()
+        self.inp = inp
+        self.T, self.cols = T, B * D
+        dev = inp["cur"].device
+        self.dev = dev
+        self.C = ps.CKPT_INTERVAL
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self.spike = torch.empty((T, B, D), **bf)
+        self.ckpt = torch.empty(((T + self.C - 1) // self.C, B * D), dtype=torch.float32, device=dev)
+        self.v_last = torch.empty((B, D), dtype=torch.float32, device=dev)
+        self.g_beta, self.g_cur, self.g_gain, self.g_vth = (torch.empty((T, B, D), **bf) for _ in range(4))
+        self.g_v0 = torch.empty((B, D), dtype=torch.float32, device=dev)
+        self.stream = _lib.stream_ptr(dev)
+        self.launch_fwd = self.launch_bwd = None
+
+    def fwd(self):
+        i, p = self.inp, self._lib.ptr
+        self._lib.check(self.L.nsb_plif_selective_fwd(
+            p(i["beta"]), p(i["cur"]), p(i["gain"]), p(i["vth"]), p(i["v0"]), p(self.spike), None, None,
+            p(self.ckpt), p(self.v_last), self.T, self.cols, self._lib.BF16, self.C, self.stream),
+            "nsb_plif_selective_fwd")
+        if self.launch_fwd is None:
+            self.launch_fwd = self._lib.last_launch_info()
+
+    def bwd(self):
+        i, p = self.inp, self._lib.ptr
+        self._lib.check(self.L.nsb_plif_selective_bwd(
+            p(i["beta"]), p(i["cur"]), p(i["gain"]), p(i["vth"]), p(self.ckpt), p(i["g_spike"]), None,
+            p(self.g_beta), p(self.g_cur), p(self.g_gain), p(self.g_vth), p(self.g_v0), self.T,
+            self.cols, self._lib.BF16, self.C, self._lib.SURR_ATAN, ALPHA, self.stream),
+            "nsb_plif_selective_bwd")
+        if self.launch_bwd is None:
+            self.launch_bwd = self._lib.last_launch_info()
+
+
+# ------------------------------------------------------------- clock sampling
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU every few ms on a
+    host thread (NVML), from start() until stop()."""
+
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+               "sw_power_cap": 0x4}
+
+    def __init__(self, gpu_index, period_s=0.004):
+        import threading
+        self.samples = []
+        self.period = period_s
+        self.stop_flag = threading.Event()
+        self.thread = None
+        self.sm_max = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = gpu_index
+            if visible:
+                ids = [x for x in visible.split(",") if x.strip()]
+                if gpu_index < len(ids) and ids[gpu_index].strip().isdigit():
+                    phys = int(ids[gpu_index])
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._run, daemon=True)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                pw = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                self.samples.append((sm, rs, pw))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.thread is not None:
+            self.thread.start()
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0,
+               "power_w_max": None}
+        if self.thread is None:
+            return out
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        if self.samples:
+            out["sm_mhz"] = float(statistics.median(s[0] for s in self.samples))
+            out["samples"] = len(self.samples)
+            out["power_w_max"] = max(s[2] for s in self.samples)
+            bits = 0
+            for s_ in self.samples:
+                bits |= s_[1]
+            out["reasons"] = sorted(n for n, b in self.REASONS.items() if bits & b)
+        return out
+
+
+# ---------------------------------------------------------------- CPU baseline
+
+
+def cpu_sample(B, T, D, seed, slice_b=1):
+    """fp32 host copies of a batch slice of the workload (same distributions)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    shp = (T, slice_b, D)
+    bf = lambda a: (a.astype(np.float32).view(np.uint32) & 0xFFFF0000).view(np.float32)  # bf16-valued
+    sp = lambda z: np.log1p(np.exp(-np.abs(z))) + np.maximum(z, 0)
+    cur = bf(rng.standard_normal(shp, dtype=np.float32))
+    beta = bf(1.0 / (1.0 + np.exp(-(2 + 0.5 * rng.standard_normal(shp, dtype=np.float32)))))
+    gain = bf(sp(rng.standard_normal(shp, dtype=np.float32)))
+    vth = bf(0.1 + sp(rng.standard_normal(shp, dtype=np.float32)))
+    gs = bf(0.1 * rng.standard_normal(shp, dtype=np.float32))
+    v0 = np.zeros((slice_b, D), np.float32)
+    return beta, cur, gain, vth, v0, gs
+
+
+def cpu_step(orc, s):
+    beta, cur, gain, vth, v0, gs = s
+    orc.plif_selective_ai_fwd(beta, cur, gain, vth, v0, want_vpost=False)
+    orc.plif_selective_ai_bwd(beta, cur, gain, vth, v0, gs, None, ALPHA, orc.SURR_ATAN)
+
+
+def cpu_baseline(B, T, D, budget_s=12.0):
+    from oracle import oracle as orc
+    cores = os.cpu_count() or 1
+    orc.set_threads(cores)
+    s = cpu_sample(B, T, D, 99, 1)
+    cpu_step(orc, s)  # warm-up (page faults, thread pool)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        cpu_step(orc, s)
+        n += 1
+        el = time.perf_counter() - t0
+        if el > budget_s or n >= 50:
+            break
+    return {"value": n * T * D / el, "unit": UNIT, "cores": orc.max_threads(), "kind": "port",
+            "sample": f"batch slice B=1 of B={B} (T={T}, D={D}), fwd+bwd, {n} repeats in {el:.1f} s; "
+                      "lanes are independent so work scales linearly in B"}
+
+
+def run_reference(args):
+    """The reference arm: the CPU port of the reference's sequential path."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    B, T, D = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    orc.set_threads(cores)
+    s = cpu_sample(B, T, D, 99, 1)
+    for _ in range(max(1, args.warmup)):
+        cpu_step(orc, s)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(orc, s)
+    el = time.perf_counter() - t0
+    value = args.steps * T * D / el
+    sample = f"each step = batch slice B=1 of B={B} (T={T}, D={D}), forward+backward"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * el / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: selective PLIF fwd+bwd, CPU port of the reference's "
+                               "sequential path, " + sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": orc.max_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------- main
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    import neuronspark_b200 as nsb
+    from neuronspark_b200 import parallel_scan as ps
+
+    B, T, D = WORKLOADS[args.workload]
+    inp = make_inputs(B, T, D, dev, 1234 + rank)
+    step = ScanStep(inp, B, T, D)
+    neuron_steps = B * T * D
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step.fwd()
+        step.bwd()
+    barrier()
+
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    sampler = ClockSampler(local) if rank == 0 else None
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    if sampler:
+        sampler.start()
+    start.record()
+    for k in range(K):
+        ev[k][0].record()
+        step.fwd()
+        ev[k][1].record()
+        step.bwd()
+        ev[k][2].record()
+    end.record()
+    barrier()
+    ms_total = start.elapsed_time(end)
+    clocks = sampler.stop() if sampler else None
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+    if world > 1:
+        t = torch.tensor([ms_total, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, fwd_ms, bwd_ms = (float(x) for x in t)
+    assert nsb.device_error_word() == 0, "a device-side wait timed out"
+    ms_step = ms_total / K
+    value = world * neuron_steps / (ms_step * 1e-3)
+
+    # validation after timing: every rank's checksum travels to rank 0 over NCCL
+    chk = torch.stack([step.spike.float().mean(), step.v_last.abs().mean(), step.g_v0.abs().mean(),
+                       step.g_cur[:64].float().abs().mean()]).to(torch.float64)
+    if world > 1:
+        allchk = [torch.empty_like(chk) for _ in range(world)]
+        dist.all_gather(allchk, chk)
+    else:
+        allchk = [chk]
+    finite = all(bool(torch.isfinite(c).all()) for c in allchk)
+
+    # ---- end-to-end through the public API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        host = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True).copy_(v)
+                for k, v in inp.items()}
+        dev_in = {k: torch.empty_like(v) for k, v in inp.items()}
+        h2d = sum(v.numel() * v.element_size() for v in host.values())
+        res_host = torch.empty((2, B, D), dtype=torch.float32, pin_memory=True)
+
+        def e2e_step():
+            for k in dev_in:
+                dev_in[k].copy_(host[k], non_blocking=True)
+            leaves = [dev_in[k].requires_grad_() for k in ("beta", "cur", "gain", "vth", "v0")]
+            spike, v_last = ps.plif_selective_scan_ai(*leaves, alpha=ALPHA, surrogate="atan")
+            spike.backward(dev_in["g_spike"])
+            res_host[0].copy_(v_last, non_blocking=True)
+            res_host[1].copy_(leaves[4].grad, non_blocking=True)
+            for t in leaves:
+                t.grad = None
+                t.requires_grad_(False)
+
+        ke = min(K, 4)
+        e2e_step()
+        barrier()
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for _ in range(ke):
+            e2e_step()
+        e2.record()
+        barrier()
+        ms_e2e = s2.elapsed_time(e2) / ke
+        if world > 1:
+            t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_e2e = float(t[0])
+        e2e = {"value": world * neuron_steps / (ms_e2e * 1e-3), "unit": UNIT,
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(res_host.numel() * 4),
+               "ms_per_step": ms_e2e, "steps": ke,
+               "api": "neuronspark_b200.parallel_scan.plif_selective_scan_ai + autograd backward, "
+                      "inputs copied from pinned host memory every step, V_last and grad V0 read back"}
+        del host, dev_in
+
+    if rank == 0:
+        peak, peak_src = hbm_peak()
+        gb = 1e-9
+        bwd_ach = BYTES_BWD * neuron_steps * gb / (bwd_ms * 1e-3)
+        fwd_ach = BYTES_FWD * neuron_steps * gb / (fwd_ms * 1e-3)
+        step_ach = (BYTES_FWD + BYTES_BWD) * neuron_steps * gb / ((fwd_ms + bwd_ms) * 1e-3)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": f"{args.workload}: selective PLIF forward+backward, B={B} per GPU "
+                            f"(global {B * world}), T={T}, D={D}, bf16 streams, fp32 state, atan "
+                            f"surrogate alpha={ALPHA}, grads for I/beta/alpha/V_th/V0",
+                "parallelism": f"batch-sharded x{world}, no collective in the timed region",
+                "l2": "inputs (16 GB per GPU) are far larger than L2; no flush needed",
+                "storage_dtype": "bf16", "ckpt_interval": ps.CKPT_INTERVAL,
+                "launch_fwd": step.launch_fwd, "launch_bwd": step.launch_bwd,
+            },
+            "roofline": {
+                "bound": "hbm", "kernel": "plif_bwd_kernel", "achieved": bwd_ach, "peak": peak,
+                "unit": "GB/s", "frac": bwd_ach / peak, "traffic": None, "peak_source": peak_src,
+                "algorithmic_bytes_per_neuron_step": BYTES_BWD, "avg_launch_ms": bwd_ms,
+                "forward": {"kernel": "plif_fwd_kernel", "achieved": fwd_ach, "frac": fwd_ach / peak,
+                            "algorithmic_bytes_per_neuron_step": BYTES_FWD, "avg_launch_ms": fwd_ms},
+                "step": {"achieved": step_ach, "frac": step_ach / peak,
+                         "algorithmic_bytes_per_neuron_step": BYTES_FWD + BYTES_BWD},
+            },
+            "clocks": clocks,
+            "gpu_launches": 2 * K,
+            "validation": {"finite": finite,
+                           "spike_rate": [float(c[0]) for c in allchk],
+                           "mean_abs_v_last": [float(c[1]) for c in allchk]},
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(B, T, D)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -135,7 +135,11 @@ def test_lateral_inhibition_vs_oracle(rows, D, dtype):
     assert_close_lowp(f32(out), want, dtype, "out")
     (out.float() * go.float()).sum().backward()
     gx, gg = orc.li_bwd(f32(go), f32(x), f32(mod.gain))
-    assert_close_lowp(f32(x.grad), gx, dtype, "g_x")
+    # g_x is a difference of two terms of size |g_out*gain|*rrms that cancel almost
+    # completely for tiny D; the tolerance is relative to that size.
+    rrms = 1.0 / np.sqrt((f32(x) ** 2).mean(-1) + 1e-6)
+    term = np.abs(f32(go) * f32(mod.gain)).max() * rrms.max()
+    assert_close_lowp(f32(x.grad), gx, dtype, "g_x", scale=max(term, np.abs(gx).max()))
     assert_close(f32(mod.gain.grad), gg, 2e-5 if dtype == torch.float32 else 1e-4, "g_gain")
     # deterministic: a second backward gives the same bits
     x2 = x.detach().clone().requires_grad_()
