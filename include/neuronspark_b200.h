@@ -74,6 +74,14 @@ int nsb_set_tuning(int warps_per_cta, int stages, int lanes_per_thread, int forc
  * out[7]=kernel launches issued by the call. */
 int nsb_last_launch_info(int32_t out[8]);
 
+/* The launch plan the scan kernels would use on a B200 for a problem, computed on
+ * the host without touching CUDA: out[0]=lanes per thread, out[1]=warps per CTA,
+ * out[2]=ring stages, out[3]=grid, out[4]=dynamic shared memory per CTA.
+ * nstreams = number of streamed [T, cols] inputs (forward: 1 row-param, 3 u-form,
+ * 4 gain*cur form; backward: those + 1 for g_spike + 1 if g_vpost). */
+int nsb_scan_plan_query(int backward, int nstreams, int elem_size, int64_t T, int64_t cols,
+                        int tile, int32_t out[5]);
+
 /*
  * Selective PLIF forward scan. Replaces _TritonPLIFForward.forward /
  * _fused_plif_fwd_kernel (atomic_ops/parallel_scan.py:196-232, 706-735).

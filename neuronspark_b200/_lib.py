@@ -30,6 +30,8 @@ _SIGNATURES = {
     "nsb_device_error_word": (c_int, [ctypes.POINTER(c_uint32)]),
     "nsb_set_tuning": (c_int, [c_int, c_int, c_int, c_int]),
     "nsb_last_launch_info": (c_int, [ctypes.POINTER(c_int32)]),
+    "nsb_scan_plan_query": (c_int, [c_int, c_int, c_int, c_int64, c_int64, c_int,
+                                    ctypes.POINTER(c_int32)]),
     "nsb_plif_selective_fwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_plif_selective_bwd": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int,
                                                           c_float, c_void_p]),
@@ -130,6 +132,14 @@ def last_launch_info() -> dict:
     keys = ("used_tma", "warps_per_cta", "stages", "lanes_per_thread", "grid", "smem_bytes",
             "tile_steps", "launches")
     return dict(zip(keys, out))
+
+
+def scan_plan(backward: bool, nstreams: int, elem_size: int, T: int, cols: int, tile: int = 8) -> dict:
+    """Launch plan the scan kernels would choose on a B200 (host arithmetic only)."""
+    out = (c_int32 * 5)()
+    check(lib().nsb_scan_plan_query(int(backward), nstreams, elem_size, T, cols, tile, out),
+          "nsb_scan_plan_query")
+    return dict(zip(("lanes_per_thread", "warps_per_cta", "stages", "grid", "smem_bytes"), out))
 
 
 def device_error_word() -> int:

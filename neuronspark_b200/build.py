@@ -45,12 +45,17 @@ def _deps_mtime() -> float:
     return max(p.stat().st_mtime for p in hdrs)
 
 
+def _extra_flags() -> list[str]:
+    """Extra nvcc flags for experiments, e.g. NSB_NVCC_FLAGS="-DNSB_X2=0"."""
+    return os.environ.get("NSB_NVCC_FLAGS", "").split()
+
+
 def _compile_one(nvcc: str, src: Path, force: bool, hdr_mtime: float) -> Path:
     obj = OBJ / (src.stem + ".o")
     if (not force and obj.exists() and obj.stat().st_mtime >= src.stat().st_mtime
             and obj.stat().st_mtime >= hdr_mtime):
         return obj
-    cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc, *NVCC_FLAGS, *_extra_flags(), "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")

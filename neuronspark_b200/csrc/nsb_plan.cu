@@ -1,0 +1,145 @@
+// Launch planner of the scan kernels: lanes per thread, warps per CTA, ring depth.
+//
+// The model behind the choice, from measurements on B200 (bf16, 196 608 columns,
+// T = 8192): (1) the scan is bound by HBM bandwidth, so CTAs that are resident
+// together share it and finish together; a launch may therefore run in several
+// "waves" at no cost as long as every wave keeps enough bytes in flight; (2) a
+// small last wave is latency-bound and expensive; (3) the bandwidth a pipeline
+// reaches grows with the bytes moved per TMA tile (512 B: ~0.5 of peak, 1 KB:
+// ~0.78, 2 KB: ~0.92, >= 4 KB: ~1); (4) an SM needs roughly 1000 resident columns
+// to hide the arithmetic latency of the recurrence.
+#include <algorithm>
+#include <cmath>
+
+#include "nsb_scan.cuh"
+
+namespace nsb {
+
+DeviceInfo b200_device_info() {
+  DeviceInfo d;
+  d.device = -1;
+  d.sm_count = 148;
+  d.cc_major = 10;
+  d.cc_minor = 0;
+  d.max_smem_optin = 232448;       // 227 KB per CTA
+  d.smem_per_sm = 233472;          // 228 KB per SM
+  d.reserved_smem_per_cta = 1024;
+  return d;
+}
+
+namespace {
+
+// Registers per thread of the kernel family (upper estimates from ptxas -v; they
+// only bound how many warps fit an SM).
+int regs_estimate(bool backward, int lanes, int tile) {
+  if (!backward) return lanes == 4 ? 72 : (lanes == 2 ? 56 : 48);
+  if (tile * lanes <= 16) return 96;
+  return lanes == 4 ? 200 : 240;
+}
+
+double op_size_factor(double tile_bytes) {
+  // bandwidth fraction reached as a function of bytes per TMA tile
+  if (tile_bytes >= 4096.0) return 1.0;
+  if (tile_bytes <= 256.0) return 0.3;
+  const double pts_x[] = {256.0, 512.0, 1024.0, 2048.0, 4096.0};
+  const double pts_y[] = {0.30, 0.52, 0.78, 0.93, 1.0};
+  for (int i = 0; i < 4; ++i) {
+    if (tile_bytes <= pts_x[i + 1]) {
+      const double t = (std::log2(tile_bytes) - std::log2(pts_x[i])) /
+                       (std::log2(pts_x[i + 1]) - std::log2(pts_x[i]));
+      return pts_y[i] + t * (pts_y[i + 1] - pts_y[i]);
+    }
+  }
+  return 1.0;
+}
+
+}  // namespace
+
+Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
+  Plan best;
+  best.grid = 0;
+  double best_cost = 1e300;
+  const int sms = std::max(1, d.sm_count);
+  const int reserved = d.reserved_smem_per_cta > 0 ? d.reserved_smem_per_cta : 1024;
+  const int ntiles = (int)((q.T + q.tile - 1) / q.tile);
+  const double inflight_needed = 5.0e6;  // bytes in flight chip-wide to cover HBM latency
+  const int lane_opts[3] = {4, 2, 1};
+  for (int lanes : lane_opts) {
+    if (lanes > q.max_lanes) continue;
+    if (tune.lanes_per_thread > 0 && lanes != tune.lanes_per_thread) continue;
+    const long long nwarps = (q.cols + 32LL * lanes - 1) / (32LL * lanes);
+    const size_t tile_bytes = (size_t)q.tile * 32 * lanes * q.elem_size;
+    const size_t stage_bytes = tile_bytes * q.nstreams;
+    const int regs = regs_estimate(q.backward, lanes, q.tile);
+    const int reg_warps = std::max(1, 65536 / (regs * 32));
+    const double f_op = op_size_factor((double)tile_bytes);
+    for (int wpc = 1; wpc <= 8; ++wpc) {
+      if (tune.warps_per_cta > 0 && wpc != tune.warps_per_cta) continue;
+      if (tune.warps_per_cta <= 0 && wpc > 4) continue;
+      for (int st = 2; st <= 6; ++st) {
+        if (tune.stages > 0 && st != tune.stages) continue;
+        if (tune.stages <= 0 && (st > 4 || st > std::max(2, ntiles))) continue;
+        const size_t smem = (size_t)wpc * st * (stage_bytes + 8) + 256;
+        if (smem > (size_t)d.max_smem_optin) continue;
+        long long res = std::min<long long>(32, d.smem_per_sm / (long long)(smem + reserved));
+        res = std::min<long long>(res, 64 / wpc);
+        res = std::min<long long>(res, reg_warps / wpc);
+        if (res < 1) continue;
+        const long long ctas = (nwarps + wpc - 1) / wpc;
+        const long long cap = res * sms;
+        double cost = 0.0;
+        long long remaining = ctas;
+        while (remaining > 0) {
+          const long long w = std::min(cap, remaining);
+          const double warps = (double)w * wpc;
+          const double inflight = warps * (st - 1) * (double)stage_bytes;
+          const double f_mem = std::min(1.0, inflight / inflight_needed);
+          const double lanes_per_sm = warps * 32.0 * lanes / sms;
+          const double f_lat = std::min(1.0, 0.5 + 0.5 * lanes_per_sm / 1024.0);
+          cost += warps * lanes / (std::max(0.02, f_mem) * f_lat * f_op);
+          remaining -= w;
+          if (ctas > 64 * cap) {  // many waves: the rest behaves like this one
+            cost *= (double)ctas / (double)w;
+            break;
+          }
+        }
+        cost *= 1.0 + 0.004 * st + 0.002 * wpc;  // prefer the smaller configuration on ties
+        if (cost < best_cost) {
+          best_cost = cost;
+          best.lanes = lanes;
+          best.wpc = wpc;
+          best.stages = st;
+          best.grid = (int)ctas;
+          best.smem = smem;
+          best.cost = cost;
+        }
+      }
+    }
+  }
+  return best;
+}
+
+}  // namespace nsb
+
+extern "C" int nsb_scan_plan_query(int backward, int nstreams, int elem_size, int64_t T, int64_t cols,
+                                   int tile, int32_t out[5]) {
+  if (!out || T < 0 || cols <= 0 || nstreams < 1 || nstreams > 6 || (elem_size != 2 && elem_size != 4) ||
+      (tile != 8 && tile != 16))
+    return NSB_ERR_INVALID_ARG;
+  nsb::PlanQuery q;
+  q.T = T;
+  q.cols = cols;
+  q.elem_size = elem_size;
+  q.nstreams = nstreams;
+  q.tile = tile;
+  q.backward = backward != 0;
+  q.max_lanes = (backward && tile == 16) ? 2 : 4;
+  const nsb::Plan p = nsb::plan_scan(nsb::b200_device_info(), q, nsb::get_tuning());
+  if (p.grid == 0) return NSB_ERR_UNSUPPORTED;
+  out[0] = p.lanes;
+  out[1] = p.wpc;
+  out[2] = p.stages;
+  out[3] = p.grid;
+  out[4] = (int32_t)p.smem;
+  return NSB_OK;
+}

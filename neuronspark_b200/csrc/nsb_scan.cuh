@@ -22,6 +22,7 @@
 #pragma once
 
 #include <algorithm>
+#include <type_traits>
 
 #include "nsb_common.cuh"
 
@@ -81,60 +82,182 @@ int scan_bwd_f32(const BwdArgs& a);
 int scan_bwd_bf16(const BwdArgs& a);
 int scan_bwd_f16(const BwdArgs& a);
 
-#ifdef __CUDACC__
-
 // ----------------------------------------------------------------- launch plan
 
-struct Plan {
-  int wpc = 1, stages = 2, grid = 0;
-  size_t smem = 0;
+// What the planner needs to know about one scan launch.
+struct PlanQuery {
+  long long T = 0, cols = 0;
+  int elem_size = 2;   // bytes per streamed element
+  int nstreams = 4;    // TMA-loaded [T, cols] streams per stage
+  int tile = 8;        // steps per tile (C)
+  bool backward = false;
+  int max_lanes = 4;   // largest lanes-per-thread the kernel family is built for
 };
 
-// Chooses warps per CTA and ring depth for `nwarps` independent warps.
-// stage_bytes: shared memory of one ring stage of one warp; regs: registers per
-// thread of the kernel. The score models one or more waves of CTAs over the SMs
-// of a bandwidth-bound kernel: a full wave costs its warps per SM, a partial
-// last wave costs the warps of its busiest SM but never less than a latency
-// floor, and configurations that keep too few bytes in flight are penalised.
-inline Plan make_plan(const DeviceInfo& d, long long nwarps, size_t stage_bytes, int regs,
-                      const Tuning& tune, int max_stages_useful) {
-  Plan best;
-  double best_score = 1e300;
-  const int reserved = d.reserved_smem_per_cta > 0 ? d.reserved_smem_per_cta : 1024;
-  const int reg_warps = std::max(1, 65536 / (std::max(regs, 16) * 32));
-  for (int wpc = 1; wpc <= 8; ++wpc) {
-    if (tune.warps_per_cta > 0 && wpc != tune.warps_per_cta) continue;
-    for (int st = 2; st <= 6; ++st) {
-      if (tune.stages > 0 && st != tune.stages) continue;
-      if (tune.stages <= 0 && st > std::max(2, max_stages_useful)) continue;
-      const size_t smem = (size_t)wpc * st * (stage_bytes + 8) + 256;
-      if (smem > (size_t)d.max_smem_optin) continue;
-      long long res = std::min<long long>(32, d.smem_per_sm / (long long)(smem + reserved));
-      res = std::min<long long>(res, 64 / wpc);
-      res = std::min<long long>(res, reg_warps / wpc);
-      if (res < 1) continue;
-      const long long ctas = (nwarps + wpc - 1) / wpc;
-      const long long cap = res * d.sm_count;
-      const long long nf = ctas / cap, rem = ctas % cap;
-      const double floor_warps = 4.0;
-      double units = (double)nf * (double)(res * wpc);
-      if (rem) units += std::max<double>((double)((rem + d.sm_count - 1) / d.sm_count) * wpc, floor_warps);
-      // bytes in flight per SM while streaming (all stages but the one being read)
-      const double resident_warps = (double)std::min<long long>(cap, ctas) * wpc / d.sm_count;
-      const double inflight = resident_warps * (st - 1) * (double)stage_bytes;
-      const double want = 64.0 * 1024.0;
-      double score = units * (inflight >= want ? 1.0 : (0.5 + 0.5 * want / std::max(inflight, 1.0)));
-      score *= 1.0 + 0.002 * st + 0.001 * wpc;  // mild preference for small configs on ties
-      if (score < best_score) {
-        best_score = score;
-        best.wpc = wpc;
-        best.stages = st;
-        best.grid = (int)ctas;
-        best.smem = smem;
+struct Plan {
+  int lanes = 2;  // V: columns per thread; a warp owns 32*V columns
+  int wpc = 1, stages = 2, grid = 0;
+  size_t smem = 0;
+  double cost = 0.0;  // model cost in "warp-times", lower is better
+};
+
+// Chooses lanes per thread, warps per CTA and ring depth. Pure host arithmetic
+// (no CUDA calls), so it can be unit-tested without a GPU.
+Plan plan_scan(const DeviceInfo& dev, const PlanQuery& q, const Tuning& tune);
+
+// Device description of a B200 for planning when no GPU is present.
+DeviceInfo b200_device_info();
+
+#ifdef __CUDACC__
+
+// ------------------------------------------------------- per-thread vector I/O
+
+// Moves the V consecutive elements a thread owns with one instruction and
+// converts them to / from fp32 (widening is exact, narrowing rounds to nearest
+// even; two 16-bit values are converted per instruction).
+template <typename ST, int V>
+struct VecIO {
+  __device__ static __forceinline__ void load(const ST* p, float (&out)[V]) {
+    const Vec<ST, V> t = *reinterpret_cast<const Vec<ST, V>*>(p);
+    if constexpr (sizeof(ST) == 2 && V % 2 == 0) {
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&t);
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) {
+        if constexpr (Elem<ST>::kDtype == NSB_BF16) {
+          out[2 * i] = __uint_as_float(w[i] << 16);
+          out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        } else {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+          out[2 * i] = f.x;
+          out[2 * i + 1] = f.y;
+        }
       }
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) out[j] = Elem<ST>::to_f32(t.v[j]);
     }
   }
-  return best;
+  __device__ static __forceinline__ void store(ST* p, const float (&in)[V]) {
+    Vec<ST, V> t;
+    if constexpr (sizeof(ST) == 2 && V % 2 == 0) {
+      uint32_t* w = reinterpret_cast<uint32_t*>(&t);
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) {
+        if constexpr (Elem<ST>::kDtype == NSB_BF16) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+          w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        } else {
+          const __half2 h = __floats2half2_rn(in[2 * i], in[2 * i + 1]);
+          w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) t.v[j] = Elem<ST>::from_f32(in[j]);
+    }
+    *reinterpret_cast<Vec<ST, V>*>(p) = t;
+  }
+  // {0,1} spikes in the stream dtype
+  __device__ static __forceinline__ void store_spikes(ST* p, const bool (&s)[V]) {
+    Vec<ST, V> t;
+    if constexpr (sizeof(ST) == 2 && V % 2 == 0) {
+      constexpr uint32_t one = Elem<ST>::kDtype == NSB_BF16 ? 0x3F80u : 0x3C00u;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&t);
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) w[i] = (s[2 * i] ? one : 0u) | (s[2 * i + 1] ? (one << 16) : 0u);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) t.v[j] = s[j] ? Elem<ST>::one() : Elem<ST>::zero();
+    }
+    *reinterpret_cast<Vec<ST, V>*>(p) = t;
+  }
+};
+
+// Lane-wise fp32 arithmetic on the V values of a thread.
+//
+// NSB_X2=1 routes pairs through the packed two-wide fp32 instructions of sm_100
+// (mul/add/fma .f32x2). It is OFF by default: measured on B200 with CUDA 12.9, a
+// packed multiply followed by a packed add is contracted into a packed fused
+// multiply-add even when both carry an explicit .rn (as CUDA intrinsics and as
+// inline PTX alike), which changes the last bit of the membrane state in ~30 % of
+// the elements and so breaks bit-exact parity with an eager fp32 time loop. The
+// scalar __fmul_rn / __fadd_rn forms are never contracted.
+#ifndef NSB_X2
+#define NSB_X2 0
+#endif
+
+__device__ __forceinline__ unsigned long long pack_f2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(unsigned long long p, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+
+template <int V>
+__device__ __forceinline__ void vmul(float (&r)[V], const float (&a)[V], const float (&b)[V]) {
+  if constexpr (NSB_X2 && V % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      unsigned long long t;
+      asm("mul.rn.f32x2 %0, %1, %2;"
+          : "=l"(t)
+          : "l"(pack_f2(a[2 * i], a[2 * i + 1])), "l"(pack_f2(b[2 * i], b[2 * i + 1])));
+      unpack_f2(t, r[2 * i], r[2 * i + 1]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) r[j] = __fmul_rn(a[j], b[j]);
+  }
+}
+template <int V>
+__device__ __forceinline__ void vmuls(float (&r)[V], const float (&a)[V], float s) {
+  float b[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) b[j] = s;
+  vmul<V>(r, a, b);
+}
+template <int V>
+__device__ __forceinline__ void vadd(float (&r)[V], const float (&a)[V], const float (&b)[V]) {
+  if constexpr (NSB_X2 && V % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      unsigned long long t;
+      asm("add.rn.f32x2 %0, %1, %2;"
+          : "=l"(t)
+          : "l"(pack_f2(a[2 * i], a[2 * i + 1])), "l"(pack_f2(b[2 * i], b[2 * i + 1])));
+      unpack_f2(t, r[2 * i], r[2 * i + 1]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) r[j] = __fadd_rn(a[j], b[j]);
+  }
+}
+template <int V>
+__device__ __forceinline__ void vsub(float (&r)[V], const float (&a)[V], const float (&b)[V]) {
+  float nb[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) nb[j] = -b[j];
+  vadd<V>(r, a, nb);
+}
+template <int V>
+__device__ __forceinline__ void vfma(float (&r)[V], const float (&a)[V], const float (&b)[V],
+                                     const float (&c)[V]) {
+  if constexpr (NSB_X2 && V % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      unsigned long long t;
+      asm("fma.rn.f32x2 %0, %1, %2, %3;"
+          : "=l"(t)
+          : "l"(pack_f2(a[2 * i], a[2 * i + 1])), "l"(pack_f2(b[2 * i], b[2 * i + 1])),
+            "l"(pack_f2(c[2 * i], c[2 * i + 1])));
+      unpack_f2(t, r[2 * i], r[2 * i + 1]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; ++j) r[j] = fmaf(a[j], b[j], c[j]);
+  }
 }
 
 // ------------------------------------------------------------------- forward
@@ -157,36 +280,45 @@ struct FwdParams {
 template <int MODE>
 struct ModeTraits {
   static constexpr int kFwdStreams = MODE == MODE_ROW ? 1 : (MODE == MODE_AI ? 4 : 3);
-  // index of each role inside the stage / pointer table (-1 = absent)
-  static constexpr int kBeta = MODE == MODE_ROW ? -1 : 0;
+  // index of each role inside the stage / pointer table (roles that a mode
+  // does not stream alias slot 0 and are never read)
+  static constexpr int kBeta = 0;
   static constexpr int kDrive = MODE == MODE_ROW ? 0 : 1;
-  static constexpr int kGain = MODE == MODE_AI ? 2 : -1;
-  static constexpr int kVth = MODE == MODE_ROW ? -1 : (MODE == MODE_AI ? 3 : 2);
+  static constexpr int kGain = MODE == MODE_AI ? 2 : 0;
+  static constexpr int kVth = MODE == MODE_ROW ? 0 : (MODE == MODE_AI ? 3 : 2);
 };
 
-// One charge / fire / soft-reset step. Returns the spike; x_out = v_pre - v_th.
-__device__ __forceinline__ bool plif_step(float& v, float beta, float drive, float vth, float& x_out,
-                                          float& vpre_out) {
-  const float vpre = __fadd_rn(__fmul_rn(beta, v), drive);
-  const float x = __fsub_rn(vpre, vth);
-  const bool s = vpre >= vth;
-  v = s ? x : vpre;
-  x_out = x;
-  vpre_out = vpre;
-  return s;
+// One charge / fire / soft-reset step on the V lanes of a thread:
+//   v_pre = beta*v + drive (multiply and add rounded separately),
+//   x = v_pre - v_th, spike = v_pre >= v_th, v = spike ? x : v_pre.
+template <int V>
+__device__ __forceinline__ void plif_step(float (&v)[V], const float (&beta)[V], const float (&drive)[V],
+                                          const float (&vth)[V], float (&x)[V], bool (&s)[V]) {
+  float bv[V], vpre[V];
+  vmul<V>(bv, beta, v);
+  vadd<V>(vpre, bv, drive);
+  vsub<V>(x, vpre, vth);
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    s[j] = vpre[j] >= vth[j];
+    v[j] = s[j] ? x[j] : vpre[j];
+  }
 }
 
 template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
 __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tm0,
                                 const __grid_constant__ CUtensorMap tm1,
                                 const __grid_constant__ CUtensorMap tm2,
-                                const __grid_constant__ CUtensorMap tm3) {
+                                const __grid_constant__ CUtensorMap tm3,
+                                const __grid_constant__ CUtensorMap tm_spike) {
   using MT = ModeTraits<MODE>;
   using E = Elem<ST>;
+  using IO = VecIO<ST, V>;
   constexpr int NS = MT::kFwdStreams;
   constexpr int TILE_ELEMS = C * 32 * V;
   constexpr uint32_t TILE_BYTES = TILE_ELEMS * sizeof(ST);
   constexpr uint32_t STAGE_BYTES = NS * TILE_BYTES;
+  constexpr bool VEC = !PACKED && TMA;  // a thread's V columns are contiguous and aligned
   extern __shared__ __align__(128) uint8_t smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -248,47 +380,41 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     }
   }
 
-  // Fetches element (stream, step k, lane-slot j) of the current tile as fp32.
   // The direct path stages KB steps of every stream in registers at a time.
   constexpr int KB = TMA ? C : 8;
-  const ST* stage_ptr = nullptr;
+  const ST* sp = nullptr;  // this thread's first element inside the current stage
   ST regs[TMA ? 1 : NS * KB * V] = {};
-  auto get = [&](int stream, int k, int j) -> float {
-    if constexpr (TMA) {
-      const int idx = PACKED ? (k * 32 * V + 32 * j + lane) : (k * 32 * V + V * lane + j);
-      return E::to_f32(stage_ptr[stream * TILE_ELEMS + idx]);
+  auto fetch = [&](int stream, int k, float (&out)[V]) {
+    if constexpr (VEC) {
+      IO::load(sp + stream * TILE_ELEMS + k * (32 * V), out);
+    } else if constexpr (TMA) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) out[j] = E::to_f32(sp[stream * TILE_ELEMS + k * (32 * V) + 32 * j]);
     } else {
-      return E::to_f32(regs[(stream * KB + (k % KB)) * V + j]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) out[j] = E::to_f32(regs[(stream * KB + (k % KB)) * V + j]);
     }
   };
 
+  const long long row_elems = p.cols;
+  long long t0 = 0;
   int s_idx = 0;
   uint32_t phase = 0;
   bool failed = false;
-  for (int i = 0; i < ntiles; ++i) {
-    const long long t0 = (long long)i * C;
-    const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
-    if constexpr (TMA) {
-      const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 1u);
-      if (!__any_sync(0xffffffffu, ok)) {
-        failed = true;
-        break;
-      }
-      stage_ptr = reinterpret_cast<const ST*>(data_ptr + (size_t)s_idx * STAGE_BYTES);
-    }
 
-    if (p.ckpt) {
-#pragma unroll
-      for (int j = 0; j < V; ++j)
-        if (valid[j]) p.ckpt[(long long)i * p.cols + colj[j]] = v[j];
-    }
-
+  auto tile = [&](auto full_tag, int nsteps) {
+    constexpr bool FULL = decltype(full_tag)::value;
+    // On the vector path dense spikes are written over the consumed drive tile in
+    // shared memory and leave through one TMA store per tile (which also clips the
+    // ragged edges), so the step loop carries no global address arithmetic for them.
+    ST* o_spike = (!VEC && p.spike) ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
+    ST* o_vpost = p.vpost ? static_cast<ST*>(p.vpost) + t0 * row_elems + colj[0] : nullptr;
     uint32_t words[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) words[j] = 0u;
-
 #pragma unroll
     for (int k = 0; k < C; ++k) {
+      if (!FULL && k >= nsteps) break;
       if constexpr (!TMA) {
         if (k % KB == 0) {
 #pragma unroll
@@ -299,57 +425,52 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
 #pragma unroll
               for (int j = 0; j < V; ++j)
                 regs[(st * KB + kk) * V + j] =
-                    (k + kk < nsteps && valid[j]) ? g[(t0 + k + kk) * p.cols + colj[j]] : E::zero();
+                    (k + kk < nsteps && valid[j]) ? g[(t0 + k + kk) * row_elems + colj[j]] : E::zero();
           }
         }
       }
-      if (k < nsteps) {
-        bool sp[V];
+      float b[V], th[V], dr[V], x[V];
+      bool sp_[V];
+      fetch(MT::kDrive, k, dr);
+      if constexpr (MODE == MODE_ROW) {
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float b = MODE == MODE_ROW ? brow[j] : get(MT::kBeta < 0 ? 0 : MT::kBeta, k, j);
-          const float th = MODE == MODE_ROW ? trow[j] : get(MT::kVth < 0 ? 0 : MT::kVth, k, j);
-          float drive = get(MT::kDrive, k, j);
-          if (MODE == MODE_AI) drive = __fmul_rn(get(MT::kGain < 0 ? 0 : MT::kGain, k, j), drive);
-          float x, vpre;
-          sp[j] = plif_step(v[j], b, drive, th, x, vpre);
+          b[j] = brow[j];
+          th[j] = trow[j];
         }
-        const long long row = (t0 + k) * p.cols;
-        if constexpr (!PACKED && V > 1) {
-          // the V columns of a thread are contiguous: one vector store per output
-          if (valid[0]) {
-            if (p.spike) {
-              Vec<ST, V> o;
+      } else {
+        fetch(MT::kBeta, k, b);
+        fetch(MT::kVth, k, th);
+      }
+      if constexpr (MODE == MODE_AI) {
+        float gn[V];
+        fetch(MT::kGain, k, gn);
+        vmul<V>(dr, gn, dr);
+      }
+      plif_step<V>(v, b, dr, th, x, sp_);
+
+      if constexpr (VEC) {
+        IO::store_spikes(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + k * (32 * V), sp_);
+        // a thread's V columns are all valid or all invalid
+        if (o_vpost && valid[0]) IO::store(o_vpost + (size_t)k * row_elems, v);
+      } else {
 #pragma unroll
-              for (int j = 0; j < V; ++j) o.v[j] = sp[j] ? E::one() : E::zero();
-              *reinterpret_cast<Vec<ST, V>*>(static_cast<ST*>(p.spike) + row + colj[0]) = o;
-            }
-            if (p.vpost) {
-              Vec<ST, V> o;
-#pragma unroll
-              for (int j = 0; j < V; ++j) o.v[j] = E::from_f32(v[j]);
-              *reinterpret_cast<Vec<ST, V>*>(static_cast<ST*>(p.vpost) + row + colj[0]) = o;
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < V; ++j) {
-            if (valid[j]) {
-              if (p.spike) static_cast<ST*>(p.spike)[row + colj[j]] = sp[j] ? E::one() : E::zero();
-              if (p.vpost) static_cast<ST*>(p.vpost)[row + colj[j]] = E::from_f32(v[j]);
-            }
+        for (int j = 0; j < V; ++j) {
+          if (valid[j]) {
+            const size_t off = (size_t)k * row_elems + (colj[j] - colj[0]);
+            if (o_spike) o_spike[off] = sp_[j] ? E::one() : E::zero();
+            if (o_vpost) o_vpost[off] = E::from_f32(v[j]);
           }
         }
-        if constexpr (PACKED) {
+      }
+      if constexpr (PACKED) {
 #pragma unroll
-          for (int j = 0; j < V; ++j) {
-            const uint32_t w = __ballot_sync(0xffffffffu, sp[j] && valid[j]);
-            if (lane == k) words[j] = w;
-          }
+        for (int j = 0; j < V; ++j) {
+          const uint32_t w = __ballot_sync(0xffffffffu, sp_[j] && valid[j]);
+          if (lane == k) words[j] = w;
         }
       }
     }
-
     if constexpr (PACKED) {
       if (p.packed && lane < nsteps) {
 #pragma unroll
@@ -359,10 +480,46 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
         }
       }
     }
+  };
+
+  for (int i = 0; i < ntiles; ++i) {
+    t0 = (long long)i * C;
+    const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
+    if constexpr (TMA) {
+      const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 1u);
+      if (!__any_sync(0xffffffffu, ok)) {
+        failed = true;
+        break;
+      }
+      sp = reinterpret_cast<const ST*>(data_ptr + (size_t)s_idx * STAGE_BYTES) + (PACKED ? lane : V * lane);
+    }
+    if (p.ckpt) {
+      if constexpr (VEC) {
+        if (valid[0]) VecIO<float, V>::store(p.ckpt + (long long)i * row_elems + colj[0], v);
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+          if (valid[j]) p.ckpt[(long long)i * row_elems + colj[j]] = v[j];
+      }
+    }
+    if (nsteps == C)
+      tile(std::true_type{}, C);
+    else
+      tile(std::false_type{}, nsteps);
 
     if constexpr (TMA) {
+      const bool store_spikes = VEC && p.spike != nullptr;
+      if (store_spikes) proxy_async_fence();  // make this lane's shared-memory writes visible to TMA
       __syncwarp();
-      if (lane == 0 && i + stages < ntiles) issue(i + stages, s_idx);
+      if (lane == 0) {
+        if (store_spikes) {
+          tma_store_2d(&tm_spike, data0 + (uint32_t)s_idx * STAGE_BYTES + MT::kDrive * TILE_BYTES, (int)col0,
+                       i * C);
+          bulk_commit_group();
+          bulk_wait_read_all();  // the stage is refilled next
+        }
+        if (i + stages < ntiles) issue(i + stages, s_idx);
+      }
       if (++s_idx == stages) {
         s_idx = 0;
         phase ^= 1u;
@@ -371,10 +528,12 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
   }
 
   if constexpr (TMA) {
+    if (lane == 0) bulk_wait_all();
     if (failed) {
       // Give every load that may still be in flight a bounded chance to land
       // before the CTA's shared memory is released.
-      for (int s = 0; s < stages; ++s) mbar_wait_bounded(bar0 + 8u * s, (s < s_idx) ? (phase ^ 1u) : phase, nullptr, 0u);
+      for (int s = 0; s < stages; ++s)
+        mbar_wait_bounded(bar0 + 8u * s, (s < s_idx) ? (phase ^ 1u) : phase, nullptr, 0u);
       return;
     }
   }
@@ -384,6 +543,11 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
 }
 
 // ------------------------------------------------------------------ backward
+
+// 96 registers per thread keep the 21 warps per SM of the headline shape
+// (196 608 columns, 2 per thread, 148 SMs) resident in a single wave.
+constexpr int kBwdMaxRegs = 96;
+constexpr int kBwdMaxThreads = 256;
 
 struct BwdParams {
   const void* s[6];  // stream base pointers (direct path), smem order
@@ -403,36 +567,49 @@ struct BwdParams {
   uint32_t* err;
 };
 
-template <int SURR>
-__device__ __forceinline__ float surrogate_grad(float x, float alpha, float c1, float c2) {
-  if (SURR == NSB_SURR_ATAN) {
-    // (alpha/2) / (1 + (pi/2 * alpha * x)^2);  c1 = pi/2*alpha, c2 = alpha/2
-    const float z = c1 * x;
-    return __fdividef(c2, fmaf(z, z, 1.0f));
+// Surrogate derivative on the V lanes of a thread.
+//   arctangent: (alpha/2) / (1 + (pi/2*alpha*x)^2)      c1 = pi/2*alpha, c2 = alpha/2
+//   sigmoid:    alpha*sig*(1-sig) = alpha*e/(1+e)^2 with e = exp(-alpha*|x|) in (0,1]
+//               (even in x, so it cannot overflow and needs no clamp)  c1 = -alpha*log2(e)
+template <int SURR, int V>
+__device__ __forceinline__ void surrogate_grad(float (&sg)[V], const float (&x)[V], float alpha, float c1,
+                                               float c2) {
+  if constexpr (SURR == NSB_SURR_ATAN) {
+    float z[V], d[V], one[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) one[j] = 1.0f;
+    vmuls<V>(z, x, c1);
+    vfma<V>(d, z, z, one);
+#pragma unroll
+    for (int j = 0; j < V; ++j) sg[j] = __fdividef(c2, d[j]);
   } else {
-    // alpha * sig * (1 - sig) = alpha * e / (1 + e)^2 with e = exp(-alpha*|x|) in (0, 1]
-    // (even in x, so no overflow and no clamp);  c1 = -alpha*log2(e)
-    const float e = exp2f(c1 * fabsf(x));
-    const float r = __fdividef(1.0f, 1.0f + e);
-    return alpha * e * r * r;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float e = exp2f(c1 * fabsf(x[j]));
+      const float r = __fdividef(1.0f, 1.0f + e);
+      sg[j] = alpha * e * r * r;
+    }
   }
 }
 
-template <typename ST, int MODE, int SURR, int V, int C, bool TMA>
-__global__ void plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tm0,
+template <typename ST, int MODE, int SURR, int V, int C, bool TMA, bool HAS_GV>
+__global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tm0,
                                 const __grid_constant__ CUtensorMap tm1,
                                 const __grid_constant__ CUtensorMap tm2,
                                 const __grid_constant__ CUtensorMap tm3,
                                 const __grid_constant__ CUtensorMap tm4,
                                 const __grid_constant__ CUtensorMap tm5,
-                                const __grid_constant__ CUtensorMap tm_ckpt) {
+                                const __grid_constant__ CUtensorMap tmo_beta,
+                                const __grid_constant__ CUtensorMap tmo_drive,
+                                const __grid_constant__ CUtensorMap tmo_gain,
+                                const __grid_constant__ CUtensorMap tmo_vth) {
   using MT = ModeTraits<MODE>;
   using E = Elem<ST>;
+  using IO = VecIO<ST, V>;
   constexpr int NF = MT::kFwdStreams;  // forward inputs; then g_spike, then optional g_vpost
   constexpr int kGS = NF, kGV = NF + 1;
   constexpr int TILE_ELEMS = C * 32 * V;
   constexpr uint32_t TILE_BYTES = TILE_ELEMS * sizeof(ST);
-  constexpr uint32_t CKPT_BYTES = 32 * V * sizeof(float);
   extern __shared__ __align__(128) uint8_t smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -441,9 +618,9 @@ __global__ void plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUten
   const long long col0 = ((long long)blockIdx.x * wpc + warp) * (32 * V);
   if (col0 >= p.cols) return;
 
-  const int nstreams = p.nstreams;  // NF + 1 + has_gv
-  const bool has_gv = p.has_gv != 0;
-  const uint32_t stage_bytes = (uint32_t)nstreams * TILE_BYTES + CKPT_BYTES;
+  constexpr int nstreams = NF + 1 + (HAS_GV ? 1 : 0);
+  constexpr bool has_gv = HAS_GV;
+  constexpr uint32_t stage_bytes = (uint32_t)nstreams * TILE_BYTES;
 
   long long colj[V];
   bool valid[V];
@@ -489,7 +666,6 @@ __global__ void plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUten
       if (nstreams > 3) tma_load_2d(dst + 3 * TILE_BYTES, &tm3, x, y, bar);
       if (nstreams > 4) tma_load_2d(dst + 4 * TILE_BYTES, &tm4, x, y, bar);
       if (nstreams > 5) tma_load_2d(dst + 5 * TILE_BYTES, &tm5, x, y, bar);
-      tma_load_2d(dst + (uint32_t)nstreams * TILE_BYTES, &tm_ckpt, x, tile, bar);
     }
   };
 
@@ -501,28 +677,156 @@ __global__ void plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUten
     }
   }
 
-  const ST* stage_ptr = nullptr;
+  const ST* sp = nullptr;  // this thread's first element inside the current stage
   ST regs[TMA ? 1 : (NF + 2) * C * V] = {};
-  auto get = [&](int stream, int k, int j) -> float {
+  auto fetch = [&](int stream, int k, float (&out)[V]) {
     if constexpr (TMA) {
-      return E::to_f32(stage_ptr[stream * TILE_ELEMS + k * 32 * V + V * lane + j]);
+      IO::load(sp + stream * TILE_ELEMS + k * (32 * V), out);
     } else {
-      return E::to_f32(regs[(stream * C + k) * V + j]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) out[j] = E::to_f32(regs[(stream * C + k) * V + j]);
     }
   };
 
   const float alpha = p.alpha;
   const float c1 = SURR == NSB_SURR_ATAN ? 1.5707963267948966f * alpha : -alpha * 1.4426950408889634f;
   const float c2 = 0.5f * alpha;
+  const long long row_elems = p.cols;
+
+  long long t0 = 0;
+  float v[V];
+  // The checkpoint of a tile (membrane state before its first step) is read
+  // straight from global memory one tile ahead of its use.
+  float vnext[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) vnext[j] = 0.0f;
+  if constexpr (TMA) {
+    if (ntiles > 0 && valid[0]) VecIO<float, V>::load(p.ckpt + (long long)(ntiles - 1) * row_elems + colj[0], vnext);
+  }
+
+  auto tile = [&](auto full_tag, int nsteps) {
+    constexpr bool FULL = decltype(full_tag)::value;
+    // recompute the tile forward, keeping V[k-1] and x[k] = V_pre[k] - V_th[k]
+    float vprev[C][V], xs[C][V];
+#pragma unroll
+    for (int k = 0; k < C; ++k) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        vprev[k][j] = v[j];
+        xs[k][j] = 0.0f;
+      }
+      if (FULL || k < nsteps) {
+        float b[V], th[V], dr[V];
+        bool s_[V];
+        fetch(MT::kDrive, k, dr);
+        if constexpr (MODE == MODE_ROW) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            b[j] = brow[j];
+            th[j] = trow[j];
+          }
+        } else {
+          fetch(MT::kBeta, k, b);
+          fetch(MT::kVth, k, th);
+        }
+        if constexpr (MODE == MODE_AI) {
+          float gn[V];
+          fetch(MT::kGain, k, gn);
+          vmul<V>(dr, gn, dr);
+        }
+        plif_step<V>(v, b, dr, th, xs[k], s_);
+      }
+    }
+
+    // adjoint recurrence, last step of the tile first. On the TMA path each
+    // gradient of step k is written over the input it corresponds to in shared
+    // memory (grad beta over beta[k], grad drive over drive[k], ...): that slot
+    // is dead once step k has read it, and the finished tiles leave through one
+    // TMA store each, which also clips the ragged edges.
+    const size_t tile_off = (size_t)(t0 * row_elems + colj[0]);
+    ST* o_beta = (!TMA && MODE != MODE_ROW && p.g_beta) ? static_cast<ST*>(p.g_beta) + tile_off : nullptr;
+    ST* o_vth = (!TMA && MODE != MODE_ROW && p.g_vth) ? static_cast<ST*>(p.g_vth) + tile_off : nullptr;
+    ST* o_drive = (!TMA && p.g_drive) ? static_cast<ST*>(p.g_drive) + tile_off : nullptr;
+    ST* o_gain = (!TMA && MODE == MODE_AI && p.g_gain) ? static_cast<ST*>(p.g_gain) + tile_off : nullptr;
+    ST* wsp = const_cast<ST*>(sp);
+#pragma unroll
+    for (int kk = 0; kk < C; ++kk) {
+      const int k = C - 1 - kk;
+      if (FULL || k < nsteps) {
+        float sg[V], gs[V], tot[V], gssg[V], gpre[V], b[V], gb[V], gth[V], gd[V], gg[V];
+        surrogate_grad<SURR, V>(sg, xs[k], alpha, c1, c2);
+        fetch(kGS, k, gs);
+        if (has_gv) {
+          float gv[V];
+          fetch(kGV, k, gv);
+          vadd<V>(tot, acc, gv);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) tot[j] = acc[j];
+        }
+        vmul<V>(gssg, gs, sg);
+        vadd<V>(gpre, gssg, tot);
+        vmul<V>(gb, gpre, vprev[k]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) gth[j] = -gssg[j] - (xs[k][j] >= 0.0f ? tot[j] : 0.0f);
+        if constexpr (MODE == MODE_ROW) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) b[j] = brow[j];
+          vadd<V>(accb, accb, gb);
+          vadd<V>(acct, acct, gth);
+        } else {
+          fetch(MT::kBeta, k, b);
+        }
+        if constexpr (MODE == MODE_AI) {
+          float gn[V], dr[V];
+          fetch(MT::kGain, k, gn);
+          fetch(MT::kDrive, k, dr);
+          vmul<V>(gd, gpre, gn);
+          vmul<V>(gg, gpre, dr);
+        }
+        vmul<V>(acc, gpre, b);
+
+        if constexpr (TMA) {
+          if constexpr (MODE != MODE_ROW) {
+            IO::store(wsp + MT::kBeta * TILE_ELEMS + k * (32 * V), gb);
+            IO::store(wsp + MT::kVth * TILE_ELEMS + k * (32 * V), gth);
+          }
+          if constexpr (MODE == MODE_AI) {
+            IO::store(wsp + MT::kDrive * TILE_ELEMS + k * (32 * V), gd);
+            IO::store(wsp + MT::kGain * TILE_ELEMS + k * (32 * V), gg);
+          } else {
+            IO::store(wsp + MT::kDrive * TILE_ELEMS + k * (32 * V), gpre);
+          }
+        } else {
+          const size_t ro = (size_t)k * row_elems;
+          auto put = [&](ST* dst, const float (&val)[V]) {
+            if (!dst) return;
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+              if (valid[j]) dst[ro + j] = E::from_f32(val[j]);
+          };
+          if constexpr (MODE != MODE_ROW) {
+            put(o_beta, gb);
+            put(o_vth, gth);
+          }
+          if constexpr (MODE == MODE_AI) {
+            put(o_drive, gd);
+            put(o_gain, gg);
+          } else {
+            put(o_drive, gpre);
+          }
+        }
+      }
+    }
+  };
 
   int s_idx = 0;
   uint32_t phase = 0;
   bool failed = false;
   for (int n = 0; n < ntiles; ++n) {
     const int i = ntiles - 1 - n;
-    const long long t0 = (long long)i * C;
+    t0 = (long long)i * C;
     const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
-    float v[V];
     if constexpr (TMA) {
       const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 2u);
       if (!__any_sync(0xffffffffu, ok)) {
@@ -530,10 +834,10 @@ __global__ void plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUten
         break;
       }
       const uint8_t* sp8 = data_ptr + (size_t)s_idx * stage_bytes;
-      stage_ptr = reinterpret_cast<const ST*>(sp8);
-      const float* ck = reinterpret_cast<const float*>(sp8 + (size_t)nstreams * TILE_BYTES);
+      sp = reinterpret_cast<const ST*>(sp8) + V * lane;
 #pragma unroll
-      for (int j = 0; j < V; ++j) v[j] = ck[V * lane + j];
+      for (int j = 0; j < V; ++j) v[j] = vnext[j];
+      if (i > 0 && valid[0]) VecIO<float, V>::load(p.ckpt + (long long)(i - 1) * row_elems + colj[0], vnext);
     } else {
 #pragma unroll
       for (int st = 0; st < NF + 2; ++st) {
@@ -544,89 +848,31 @@ __global__ void plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUten
 #pragma unroll
           for (int j = 0; j < V; ++j)
             regs[(st * C + k) * V + j] =
-                (present && k < nsteps && valid[j]) ? g[(t0 + k) * p.cols + colj[j]] : E::zero();
+                (present && k < nsteps && valid[j]) ? g[(t0 + k) * row_elems + colj[j]] : E::zero();
       }
 #pragma unroll
-      for (int j = 0; j < V; ++j) v[j] = valid[j] ? p.ckpt[(long long)i * p.cols + colj[j]] : 0.0f;
+      for (int j = 0; j < V; ++j) v[j] = valid[j] ? p.ckpt[(long long)i * row_elems + colj[j]] : 0.0f;
     }
 
-    // recompute the tile forward, keeping V[k-1] and x[k] = V_pre[k] - V_th[k]
-    float vprev[C][V], xs[C][V];
-#pragma unroll
-    for (int k = 0; k < C; ++k) {
-#pragma unroll
-      for (int j = 0; j < V; ++j) {
-        vprev[k][j] = v[j];
-        xs[k][j] = 0.0f;
-        if (k < nsteps) {
-          const float b = MODE == MODE_ROW ? brow[j] : get(MT::kBeta < 0 ? 0 : MT::kBeta, k, j);
-          const float th = MODE == MODE_ROW ? trow[j] : get(MT::kVth < 0 ? 0 : MT::kVth, k, j);
-          float drive = get(MT::kDrive, k, j);
-          if (MODE == MODE_AI) drive = __fmul_rn(get(MT::kGain < 0 ? 0 : MT::kGain, k, j), drive);
-          float vpre;
-          plif_step(v[j], b, drive, th, xs[k][j], vpre);
-        }
-      }
-    }
-
-    // adjoint recurrence, last step of the tile first
-#pragma unroll
-    for (int kk = 0; kk < C; ++kk) {
-      const int k = C - 1 - kk;
-      if (k < nsteps) {
-        float o_beta[V], o_drive[V], o_gain[V], o_vth[V];
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const float x = xs[k][j];
-          const bool s = x >= 0.0f;
-          const float sg = surrogate_grad<SURR>(x, alpha, c1, c2);
-          const float gs = get(kGS, k, j);
-          const float tot = has_gv ? acc[j] + get(kGV, k, j) : acc[j];
-          const float gssg = gs * sg;
-          const float gpre = gssg + tot;
-          const float b = MODE == MODE_ROW ? brow[j] : get(MT::kBeta < 0 ? 0 : MT::kBeta, k, j);
-          const float gvth = s ? (-gssg - tot) : -gssg;
-          o_beta[j] = gpre * vprev[k][j];
-          o_vth[j] = gvth;
-          if (MODE == MODE_AI) {
-            o_drive[j] = gpre * get(MT::kGain < 0 ? 0 : MT::kGain, k, j);
-            o_gain[j] = gpre * get(MT::kDrive, k, j);
-          } else {
-            o_drive[j] = gpre;
-            o_gain[j] = 0.0f;
-          }
-          if (MODE == MODE_ROW) {
-            accb[j] += o_beta[j];
-            acct[j] += gvth;
-          }
-          acc[j] = gpre * b;
-        }
-        const long long off = (t0 + k) * p.cols + colj[0];
-        auto store = [&](void* dst, const float (&val)[V]) {
-          if (!dst) return;
-          if constexpr (V > 1) {
-            if (valid[0]) {
-              Vec<ST, V> o;
-#pragma unroll
-              for (int j = 0; j < V; ++j) o.v[j] = E::from_f32(val[j]);
-              *reinterpret_cast<Vec<ST, V>*>(static_cast<ST*>(dst) + off) = o;
-            }
-          } else {
-            if (valid[0]) static_cast<ST*>(dst)[off] = E::from_f32(val[0]);
-          }
-        };
-        if (MODE != MODE_ROW) {
-          store(p.g_beta, o_beta);
-          store(p.g_vth, o_vth);
-        }
-        store(p.g_drive, o_drive);
-        if (MODE == MODE_AI) store(p.g_gain, o_gain);
-      }
-    }
+    if (nsteps == C)
+      tile(std::true_type{}, C);
+    else
+      tile(std::false_type{}, nsteps);
 
     if constexpr (TMA) {
+      proxy_async_fence();  // make this lane's shared-memory writes visible to TMA
       __syncwarp();
-      if (lane == 0 && i - stages >= 0) issue(i - stages, s_idx);
+      if (lane == 0) {
+        const uint32_t src = data0 + (uint32_t)s_idx * stage_bytes;
+        const int x = (int)col0, y = i * C;
+        if (MODE != MODE_ROW && p.g_beta) tma_store_2d(&tmo_beta, src + MT::kBeta * TILE_BYTES, x, y);
+        if (MODE != MODE_ROW && p.g_vth) tma_store_2d(&tmo_vth, src + MT::kVth * TILE_BYTES, x, y);
+        if (p.g_drive) tma_store_2d(&tmo_drive, src + MT::kDrive * TILE_BYTES, x, y);
+        if (MODE == MODE_AI && p.g_gain) tma_store_2d(&tmo_gain, src + MT::kGain * TILE_BYTES, x, y);
+        bulk_commit_group();
+        bulk_wait_read_all();  // the stage is refilled next
+        if (i - stages >= 0) issue(i - stages, s_idx);
+      }
       if (++s_idx == stages) {
         s_idx = 0;
         phase ^= 1u;
@@ -635,8 +881,10 @@ __global__ void plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUten
   }
 
   if constexpr (TMA) {
+    if (lane == 0) bulk_wait_all();
     if (failed) {
-      for (int s = 0; s < stages; ++s) mbar_wait_bounded(bar0 + 8u * s, (s < s_idx) ? (phase ^ 1u) : phase, nullptr, 0u);
+      for (int s = 0; s < stages; ++s)
+        mbar_wait_bounded(bar0 + 8u * s, (s < s_idx) ? (phase ^ 1u) : phase, nullptr, 0u);
       return;
     }
   }
@@ -657,7 +905,7 @@ __global__ void plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUten
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
-int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune) {
+int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, const Plan& planned) {
   using MT = ModeTraits<MODE>;
   constexpr int NS = MT::kFwdStreams;
   auto kern = plif_fwd_kernel<ST, MODE, PACKED, V, C, TMA>;
@@ -678,7 +926,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune) 
   p.err = device_error_word_ptr();
 
   const long long nwarps = (a.cols + 32 * V - 1) / (32 * V);
-  CUtensorMap tm[4];
+  CUtensorMap tm[5];
   memset(tm, 0, sizeof tm);
   Plan plan;
   LaunchInfo& li = last_launch();
@@ -688,10 +936,11 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune) 
                                  32 * V);
       if (r != NSB_OK) return r;
     }
-    cudaFuncAttributes fa;
-    NSB_CUDA_TRY(cudaFuncGetAttributes(&fa, kern), "cudaFuncGetAttributes(fwd)");
-    const size_t stage_bytes = (size_t)NS * C * 32 * V * sizeof(ST);
-    plan = make_plan(dev, nwarps, stage_bytes, fa.numRegs, tune, std::min(4, p.ntiles));
+    if (!PACKED && a.spike) {
+      int r = make_tensor_map_2d(&tm[4], a.spike, Elem<ST>::kDtype, (uint64_t)a.T, (uint64_t)a.cols, C, 32 * V);
+      if (r != NSB_OK) return r;
+    }
+    plan = planned;
     if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;
     NSB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem),
                  "cudaFuncSetAttribute(fwd)");
@@ -702,18 +951,18 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune) 
     plan.smem = 0;
   }
   p.stages = plan.stages;
-  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3]);
+  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4]);
   NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_kernel");
   li.used_tma = TMA; li.warps_per_cta = plan.wpc; li.stages = plan.stages; li.lanes_per_thread = V;
   li.grid = plan.grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = 1;
   return NSB_OK;
 }
 
-template <typename ST, int MODE, int SURR, int V, int C, bool TMA>
-int launch_bwd_one(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune) {
+template <typename ST, int MODE, int SURR, int V, int C, bool TMA, bool HAS_GV>
+int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune, const Plan& planned) {
   using MT = ModeTraits<MODE>;
   constexpr int NF = MT::kFwdStreams;
-  auto kern = plif_bwd_kernel<ST, MODE, SURR, V, C, TMA>;
+  auto kern = plif_bwd_kernel<ST, MODE, SURR, V, C, TMA, HAS_GV>;
   BwdParams p = {};
   const void* streams[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   if (MODE == MODE_ROW) {
@@ -737,7 +986,7 @@ int launch_bwd_one(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune) 
   p.err = device_error_word_ptr();
 
   const long long nwarps = (a.cols + 32 * V - 1) / (32 * V);
-  CUtensorMap tm[7];
+  CUtensorMap tm[11];
   memset(tm, 0, sizeof tm);
   Plan plan;
   if (TMA) {
@@ -746,28 +995,37 @@ int launch_bwd_one(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune) 
                                  32 * V);
       if (r != NSB_OK) return r;
     }
-    int r = make_tensor_map_2d(&tm[6], a.ckpt, NSB_F32, (uint64_t)p.ntiles, (uint64_t)a.cols, 1, 32 * V);
-    if (r != NSB_OK) return r;
-    cudaFuncAttributes fa;
-    NSB_CUDA_TRY(cudaFuncGetAttributes(&fa, kern), "cudaFuncGetAttributes(bwd)");
-    const size_t stage_bytes = (size_t)nstreams * C * 32 * V * sizeof(ST) + 32 * V * sizeof(float);
-    plan = make_plan(dev, nwarps, stage_bytes, fa.numRegs, tune, std::min(3, p.ntiles));
+    const void* outs[4] = {a.g_beta, a.g_drive, a.g_gain, a.g_vth};
+    for (int i = 0; i < 4; ++i) {
+      if (!outs[i]) continue;
+      int r = make_tensor_map_2d(&tm[7 + i], outs[i], Elem<ST>::kDtype, (uint64_t)a.T, (uint64_t)a.cols, C,
+                                 32 * V);
+      if (r != NSB_OK) return r;
+    }
+    plan = planned;
     if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;
     NSB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem),
                  "cudaFuncSetAttribute(bwd)");
   } else {
-    plan.wpc = tune.warps_per_cta > 0 ? tune.warps_per_cta : 4;
+    plan.wpc = tune.warps_per_cta > 0 ? std::min(tune.warps_per_cta, kBwdMaxThreads / 32) : 4;
     plan.stages = 1;
     plan.grid = (int)((nwarps + plan.wpc - 1) / plan.wpc);
     plan.smem = 0;
   }
   p.stages = plan.stages;
-  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6]);
+  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[7], tm[8], tm[9],
+                                                          tm[10]);
   NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel");
   LaunchInfo& li = last_launch();
   li.used_tma = TMA; li.warps_per_cta = plan.wpc; li.stages = plan.stages; li.lanes_per_thread = V;
   li.grid = plan.grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = 1;
   return NSB_OK;
+}
+
+template <typename ST, int MODE, int SURR, int V, int C, bool TMA>
+int launch_bwd_one(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune, const Plan& planned) {
+  return a.g_vpost ? launch_bwd_impl<ST, MODE, SURR, V, C, TMA, true>(a, dev, tune, planned)
+                   : launch_bwd_impl<ST, MODE, SURR, V, C, TMA, false>(a, dev, tune, planned);
 }
 
 // The TMA path needs 16-byte aligned bases and row pitch, int32 coordinates and
@@ -792,12 +1050,20 @@ int scan_fwd_dispatch(const FwdArgs& a) {
   const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.spike, a.vpost, a.ckpt};
   for (const void* q : ptrs) tma = tma && aligned16(q);
   const bool packed = a.packed != nullptr;
-  const int V = tune.lanes_per_thread > 0 ? tune.lanes_per_thread : 2;
   const int C = a.tile;
+  Plan plan;
+  if (tma) {
+    PlanQuery q;
+    q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
+    q.nstreams = a.mode == MODE_ROW ? 1 : (a.mode == MODE_AI ? 4 : 3);
+    q.tile = C; q.backward = false; q.max_lanes = 4;
+    plan = plan_scan(dev, q, tune);
+  }
+  const int V = plan.lanes;
 
 #define NSB_FWD_CASE(MODE_, PACKED_, V_, C_)                                           \
   if (a.mode == MODE_ && packed == PACKED_ && V == V_ && C == C_)                      \
-    return launch_fwd_one<ST, MODE_, PACKED_, V_, C_, true>(a, dev, tune);
+    return launch_fwd_one<ST, MODE_, PACKED_, V_, C_, true>(a, dev, tune, plan);
 #define NSB_FWD_CASES_V(MODE_, PACKED_)                                                \
   NSB_FWD_CASE(MODE_, PACKED_, 1, 8) NSB_FWD_CASE(MODE_, PACKED_, 2, 8)                \
   NSB_FWD_CASE(MODE_, PACKED_, 4, 8) NSB_FWD_CASE(MODE_, PACKED_, 1, 16)               \
@@ -812,8 +1078,8 @@ int scan_fwd_dispatch(const FwdArgs& a) {
 #undef NSB_FWD_CASE
 #define NSB_FWD_DIRECT(MODE_, C_)                                                      \
   if (a.mode == MODE_ && C == C_)                                                      \
-    return packed ? launch_fwd_one<ST, MODE_, true, 1, C_, false>(a, dev, tune)        \
-                  : launch_fwd_one<ST, MODE_, false, 1, C_, false>(a, dev, tune);
+    return packed ? launch_fwd_one<ST, MODE_, true, 1, C_, false>(a, dev, tune, plan)  \
+                  : launch_fwd_one<ST, MODE_, false, 1, C_, false>(a, dev, tune, plan);
   NSB_FWD_DIRECT(MODE_U, 8) NSB_FWD_DIRECT(MODE_U, 16)
   NSB_FWD_DIRECT(MODE_AI, 8) NSB_FWD_DIRECT(MODE_AI, 16)
   NSB_FWD_DIRECT(MODE_ROW, 8) NSB_FWD_DIRECT(MODE_ROW, 16)
@@ -832,16 +1098,25 @@ int scan_bwd_dispatch(const BwdArgs& a) {
   const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.ckpt, a.g_spike, a.g_vpost,
                         a.g_beta, a.g_drive, a.g_gain, a.g_vth};
   for (const void* q : ptrs) tma = tma && aligned16(q);
-  const int V = tune.lanes_per_thread > 0 ? tune.lanes_per_thread : 2;
   const int C = a.tile;
+  Plan plan;
+  if (tma) {
+    PlanQuery q;
+    q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
+    q.nstreams = (a.mode == MODE_ROW ? 1 : (a.mode == MODE_AI ? 4 : 3)) + 1 + (a.g_vpost ? 1 : 0);
+    q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : 2;
+    plan = plan_scan(dev, q, tune);
+  }
+  const int V = plan.lanes;
 
 #define NSB_BWD_CASE(MODE_, SURR_, V_, C_)                                             \
   if (a.mode == MODE_ && a.surrogate == SURR_ && V == V_ && C == C_)                   \
-    return launch_bwd_one<ST, MODE_, SURR_, V_, C_, true>(a, dev, tune);
+    return launch_bwd_one<ST, MODE_, SURR_, V_, C_, true>(a, dev, tune, plan);
 #define NSB_BWD_CASES_V(MODE_, SURR_)                                                  \
   NSB_BWD_CASE(MODE_, SURR_, 1, 8) NSB_BWD_CASE(MODE_, SURR_, 2, 8)                    \
-  NSB_BWD_CASE(MODE_, SURR_, 1, 16) NSB_BWD_CASE(MODE_, SURR_, 2, 16)
-  if (tma && V <= 2) {
+  NSB_BWD_CASE(MODE_, SURR_, 4, 8) NSB_BWD_CASE(MODE_, SURR_, 1, 16)                   \
+  NSB_BWD_CASE(MODE_, SURR_, 2, 16)
+  if (tma) {
     NSB_BWD_CASES_V(MODE_U, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_U, NSB_SURR_ATAN)
     NSB_BWD_CASES_V(MODE_AI, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_AI, NSB_SURR_ATAN)
     NSB_BWD_CASES_V(MODE_ROW, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_ROW, NSB_SURR_ATAN)
@@ -851,7 +1126,7 @@ int scan_bwd_dispatch(const BwdArgs& a) {
 #undef NSB_BWD_CASE
 #define NSB_BWD_DIRECT(MODE_, SURR_, C_)                                               \
   if (a.mode == MODE_ && a.surrogate == SURR_ && C == C_)                              \
-    return launch_bwd_one<ST, MODE_, SURR_, 1, C_, false>(a, dev, tune);
+    return launch_bwd_one<ST, MODE_, SURR_, 1, C_, false>(a, dev, tune, plan);
 #define NSB_BWD_DIRECT_S(MODE_)                                                        \
   NSB_BWD_DIRECT(MODE_, NSB_SURR_SIGMOID, 8) NSB_BWD_DIRECT(MODE_, NSB_SURR_SIGMOID, 16) \
   NSB_BWD_DIRECT(MODE_, NSB_SURR_ATAN, 8) NSB_BWD_DIRECT(MODE_, NSB_SURR_ATAN, 16)

@@ -81,3 +81,25 @@ def test_stream_dtype_rule():
     assert _common_stream_dtype(b, h) == torch.float32
     assert _common_stream_dtype(torch.empty(1, dtype=torch.float64)) == torch.float32
     assert _common_stream_dtype(b, None, b) == torch.bfloat16
+
+
+def test_launch_planner(built_lib):
+    """The planner is pure host arithmetic over a B200 description."""
+    from neuronspark_b200 import _lib
+    _lib.set_tuning()
+    # headline shape: 196 608 columns, bf16, gain*cur form
+    fwd = _lib.scan_plan(False, 4, 2, 8192, 32 * 6144)
+    bwd = _lib.scan_plan(True, 5, 2, 8192, 32 * 6144)
+    for p in (fwd, bwd):
+        assert p["lanes_per_thread"] in (1, 2, 4) and 2 <= p["stages"] <= 6
+        assert p["grid"] * p["warps_per_cta"] * 32 * p["lanes_per_thread"] >= 32 * 6144
+        assert p["smem_bytes"] <= 227 * 1024
+    # wide TMA tiles (>= 2 KB per stream) are what reaches HBM bandwidth on this shape
+    assert fwd["lanes_per_thread"] * 8 * 32 * 2 >= 2048
+    # the override is honoured
+    _lib.set_tuning(warps_per_cta=3, stages=2, lanes_per_thread=2)
+    p = _lib.scan_plan(True, 5, 2, 8192, 32 * 6144)
+    assert (p["lanes_per_thread"], p["warps_per_cta"], p["stages"]) == (2, 3, 2)
+    _lib.set_tuning()
+    # a single tile never asks for a deep ring; tiny problems still get a plan
+    assert _lib.scan_plan(False, 1, 4, 5, 7)["grid"] == 1

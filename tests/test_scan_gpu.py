@@ -266,7 +266,7 @@ def test_tuning_variants_bitwise_identical(lanes, stages, wpc):
     assert torch.equal(last2, ref_last.float())
 
 
-@pytest.mark.parametrize("lanes", [1, 2])
+@pytest.mark.parametrize("lanes", [1, 2, 4])
 @pytest.mark.parametrize("surrogate", ["sigmoid", "atan"])
 def test_backward_direct_and_tma_paths_agree(lanes, surrogate):
     T, B, D = 45, 2, 192
