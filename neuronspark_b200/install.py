@@ -1,0 +1,93 @@
+"""Rebinds NeuronSpark's own modules to the B200 implementations.
+
+The reference's layers import the scan functions by name at import time
+(``from .parallel_scan import plif_rowparam_forward_recompute`` in
+``atomic_ops/snn_block.py`` and ``atomic_ops/snn_ffn.py``; ``from
+atomic_ops.fp16_codec import fp16_encode, fp16_decode`` in ``model.py``), so
+replacing the attributes of ``atomic_ops.parallel_scan`` alone is not enough:
+every already-imported module that holds one of those names has to be patched
+too. ``install()`` does both and returns what it changed; ``uninstall()`` puts
+the originals back.
+
+    import atomic_ops, model            # the reference, unmodified
+    import neuronspark_b200.install as nsb_install
+    nsb_install.install()               # snn_block / snn_ffn / model now call the CUDA kernels
+
+Functions of the reference that this package does not replace (the
+second-order RF scan, the linear recurrence, MoE combine) are left untouched.
+"""
+from __future__ import annotations
+
+import sys
+from types import ModuleType
+
+from . import fp16_codec, lateral_inhibition, parallel_scan
+
+#: reference module (by its name inside the ``atomic_ops`` package) -> replacement names
+REPLACEMENTS = {
+    "parallel_scan": (parallel_scan, (
+        "_TritonPLIFForward", "_TritonPLIFRowParamForward", "_TritonPLIFRowParamRecompute",
+        "plif_parallel_forward", "plif_rowparam_forward", "plif_rowparam_forward_alpha",
+        "plif_rowparam_forward_recompute", "plif_fixed_param_forward")),
+    "fp16_codec": (fp16_codec, (
+        "fp16_encode", "fp16_decode", "binary_residual", "binary_encode_ste", "_BinaryResidual",
+        "_BinaryEncodeSTE")),
+    "lateral_inhibition": (lateral_inhibition, ("_LateralInhibitionTriton",)),
+}
+
+_undo: list[tuple[ModuleType, str, object]] = []
+
+
+def _reference_modules(package: str) -> dict[str, ModuleType]:
+    found = {}
+    for short in REPLACEMENTS:
+        m = sys.modules.get(f"{package}.{short}")
+        if m is not None:
+            found[short] = m
+    return found
+
+
+def install(package: str = "atomic_ops", extra_modules=()) -> list[str]:
+    """Patches the imported reference modules; returns ``module.name`` strings changed.
+
+    ``package`` is the import name of the reference's operator package.
+    ``extra_modules`` are further already-imported modules to scan for
+    by-name imports (``model`` is scanned automatically when present)."""
+    refs = _reference_modules(package)
+    if not refs:
+        raise RuntimeError(f"no module of the reference package {package!r} has been imported")
+    originals: dict[int, tuple[str, object]] = {}
+    changed: list[str] = []
+    for short, ref_mod in refs.items():
+        ours, names = REPLACEMENTS[short]
+        for name in names:
+            if hasattr(ref_mod, name):
+                old = getattr(ref_mod, name)
+                originals[id(old)] = (name, getattr(ours, name))
+                _undo.append((ref_mod, name, old))
+                setattr(ref_mod, name, getattr(ours, name))
+                changed.append(f"{ref_mod.__name__}.{name}")
+    # modules that did `from .parallel_scan import name` hold their own reference
+    scan = [m for n, m in list(sys.modules.items())
+            if m is not None and (n == package or n.startswith(package + ".") or n == "model")]
+    scan += list(extra_modules)
+    for mod in scan:
+        if mod in refs.values():
+            continue
+        for attr, val in list(vars(mod).items()):
+            hit = originals.get(id(val))
+            if hit is not None and hit[0] == attr:
+                _undo.append((mod, attr, val))
+                setattr(mod, attr, hit[1])
+                changed.append(f"{mod.__name__}.{attr}")
+    return changed
+
+
+def uninstall() -> int:
+    """Restores everything ``install()`` changed; returns the number of names restored."""
+    n = 0
+    while _undo:
+        mod, name, old = _undo.pop()
+        setattr(mod, name, old)
+        n += 1
+    return n
