@@ -49,6 +49,11 @@ WORKLOADS = {
 BYTES_FWD = 4 * 2 + 2          # beta, I, alpha, V_th in; spikes out
 BYTES_BWD = 4 * 2 + 2 + 4 * 2  # the four inputs again, dL/dspike in; four gradients out
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per neuron-step measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
+# reduced-T case "c2-short" (same grid, T=512); traffic of these kernels is proportional to T, so a
+# full launch moves this many bytes per neuron-step too (profiles/plif_scan_c2short_ncu_full.md).
+NCU_TRAFFIC_FWD = (806.124e6 + 229.413e6) / (32 * 512 * 6144)
+NCU_TRAFFIC_BWD = (1057.017e6 + 765.601e6) / (32 * 512 * 6144)
 
 
 def parse_args():
@@ -433,7 +438,10 @@ def main():
             },
             "roofline": {
                 "bound": "hbm", "kernel": "plif_bwd_kernel", "achieved": bwd_ach, "peak": peak,
-                "unit": "GB/s", "frac": bwd_ach / peak, "traffic": None, "peak_source": peak_src,
+                "unit": "GB/s", "frac": bwd_ach / peak,
+                "traffic": NCU_TRAFFIC_BWD * neuron_steps if args.workload.startswith("c2") else None,
+                "traffic_source": "ncu capture of the T=512 case scaled by T (bytes per launch)",
+                "peak_source": peak_src,
                 "algorithmic_bytes_per_neuron_step": BYTES_BWD, "avg_launch_ms": bwd_ms,
                 "forward": {"kernel": "plif_fwd_kernel", "achieved": fwd_ach, "frac": fwd_ach / peak,
                             "algorithmic_bytes_per_neuron_step": BYTES_FWD, "avg_launch_ms": fwd_ms},
