@@ -202,6 +202,37 @@ int nsb_lateral_inhibition_bwd(const void* g_out, const void* x, const void* gai
                                int64_t D, float eps, int dtype, int gain_dtype,
                                void* stream);
 
+/*
+ * nsb_lateral_inhibition_bwd for callers that cannot allocate device memory.
+ * (No counterpart in the reference: its backward allocates a rows x D tensor.)
+ *
+ * Same inputs, outputs and results as nsb_lateral_inhibition_bwd, but without the
+ * `partial` argument: the per-CTA partial sums of g_gain are kept in a fixed
+ * array inside the library image instead. It is meant for hosts that own all
+ * device memory themselves or may not call the CUDA allocator where they run
+ * this (a server that pre-reserved the device for its own pool, a plugin that
+ * only receives input/output buffers, a loop in which cudaMalloc/cudaFree are
+ * ruled out because they synchronise the device). The call itself allocates
+ * nothing, neither through CUDA nor through any library.
+ *
+ * Cost and limits:
+ *  - the array is 524 288 floats (2 MiB) of device memory on every GPU that
+ *    loads the library, held until the process exits;
+ *  - D may not exceed 524 288 (NSB_ERR_TOO_LARGE otherwise); when
+ *    (CTAs the normal entry point would use) * D exceeds the array, fewer CTAs
+ *    are launched, so very wide rows run slower than with caller scratch;
+ *  - the first call on each device looks up the array's device address
+ *    (with that device current). Make that first call outside any stream
+ *    capture; later calls do no set-up;
+ *  - all calls on a device share the one array. Nothing in it has to be zeroed:
+ *    each call writes every element it later reads. But two calls that overlap
+ *    on the GPU (different streams, or one stream per thread) race on it and
+ *    corrupt each other's g_gain — serialise them.
+ */
+int nsb_lateral_inhibition_bwd_static(const void* g_out, const void* x, const void* gain,
+                                      void* g_x, float* g_gain, int64_t rows, int64_t D,
+                                      float eps, int dtype, int gain_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

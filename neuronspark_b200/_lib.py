@@ -50,6 +50,8 @@ _SIGNATURES = {
     "nsb_li_bwd_scratch_floats": (c_int64, [c_int64, c_int64]),
     "nsb_lateral_inhibition_bwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_float, c_int, c_int,
                                                             c_void_p]),
+    "nsb_lateral_inhibition_bwd_static": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_float, c_int,
+                                                                   c_int, c_void_p]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

@@ -8,6 +8,8 @@
 // CTA are summed in a fixed order into one partial row per CTA, and a second
 // small kernel sums the partial rows in a fixed order. The result is therefore
 // bit-reproducible from run to run.
+#include <mutex>
+
 #include "nsb_common.cuh"
 
 namespace nsb {
@@ -251,3 +253,95 @@ int nsb_lateral_inhibition_bwd(const void* g_out, const void* x, const void* gai
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Backward without any caller-provided or allocated scratch.
+//
+// Some hosts of this library may not allocate device memory at the point
+// where they need the normaliser's backward: an inference/training server
+// that handed the whole device to its own memory pool at start-up, a plugin
+// that is only ever given input and output buffers, or a latency-critical
+// loop in which cudaMalloc/cudaFree are banned because they synchronise the
+// device. For them the per-CTA partial sums of grad_gain live in a fixed array
+// that is part of the library image: kLiStaticFloats floats (2 MiB) of device
+// memory on every GPU that loads the library, held until the process exits.
+// ---------------------------------------------------------------------------
+namespace nsb {
+namespace {
+
+constexpr long long kLiStaticFloats = 1LL << 19;  // 524 288 floats = 2 MiB
+static __device__ __align__(256) float g_li_static_partial[kLiStaticFloats];
+
+// In host code the name of a __device__ array is only a handle, not a device
+// address; the address each device gave the array is looked up once per device.
+std::mutex g_li_static_mu;
+float* g_li_static_ptr[64] = {};
+
+int li_static_scratch(float** out) {
+  int dev = 0;
+  NSB_CUDA_TRY(cudaGetDevice(&dev), "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return NSB_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lk(g_li_static_mu);
+  if (!g_li_static_ptr[dev]) {
+    void* p = nullptr;
+    NSB_CUDA_TRY(cudaGetSymbolAddress(&p, g_li_static_partial), "cudaGetSymbolAddress(li scratch)");
+    if (!p) return NSB_ERR_CUDA;
+    g_li_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_li_static_ptr[dev];
+  return NSB_OK;
+}
+
+}  // namespace
+}  // namespace nsb
+
+extern "C" int nsb_lateral_inhibition_bwd_static(const void* g_out, const void* x, const void* gain,
+                                                 void* g_x, float* g_gain, int64_t rows, int64_t D,
+                                                 float eps, int dtype, int gain_dtype, void* stream) {
+  if (rows < 0 || D < 0 || D >= (1ll << 31) || !dtype_ok(dtype) || !dtype_ok(gain_dtype))
+    return NSB_ERR_INVALID_ARG;
+  if (D == 0) return NSB_OK;
+  if (D > kLiStaticFloats) return NSB_ERR_TOO_LARGE;  // not even one partial row fits
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!g_gain || (reinterpret_cast<uintptr_t>(g_gain) & 3u)) return NSB_ERR_INVALID_ARG;
+  if (rows == 0) {
+    NSB_CUDA_TRY(cudaMemsetAsync(g_gain, 0, sizeof(float) * D, st), "memset g_gain");
+    return NSB_OK;
+  }
+  if (!g_out || !x || !gain || !g_x) return NSB_ERR_INVALID_ARG;
+  float* partial = nullptr;
+  int r = li_static_scratch(&partial);
+  if (r != NSB_OK) return r;
+  int wpc = 0;
+  int grid = bwd_grid(rows, (int)D, &wpc);
+  if (grid == 0) return NSB_ERR_TOO_LARGE;
+  // one partial row of D floats per CTA has to fit the fixed array: use fewer CTAs if need be
+  grid = (int)std::min<long long>(grid, kLiStaticFloats / D);
+  const size_t smem = (size_t)wpc * D * sizeof(float);
+  return with_dtype(dtype, [&](auto t) {
+    using T = decltype(t);
+    return with_dtype(gain_dtype, [&](auto tg) {
+      using TG = decltype(tg);
+      if (!can_vec<T, TG>(1, D, {g_out, x, g_x}, gain)) return NSB_ERR_INVALID_ARG;
+      const T* gop = static_cast<const T*>(g_out);
+      const T* xp = static_cast<const T*>(x);
+      const TG* gp = static_cast<const TG*>(gain);
+      T* gxp = static_cast<T*>(g_x);
+#define NSB_LI_BWD_STATIC(VE_)                                                                    \
+  {                                                                                               \
+    auto k = li_bwd_kernel<T, TG, VE_>;                                                           \
+    NSB_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), \
+                 "cudaFuncSetAttribute(li_bwd)");                                                 \
+    k<<<grid, wpc * 32, smem, st>>>(gop, xp, gp, gxp, partial, rows, (int)D, eps);                \
+  }
+      if (can_vec<T, TG>(4, D, {g_out, x, g_x}, gain)) NSB_LI_BWD_STATIC(4)
+      else if (can_vec<T, TG>(2, D, {g_out, x, g_x}, gain)) NSB_LI_BWD_STATIC(2)
+      else NSB_LI_BWD_STATIC(1)
+#undef NSB_LI_BWD_STATIC
+      NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_kernel (static scratch)");
+      li_bwd_reduce_kernel<<<(int)((D + 255) / 256), 256, 0, st>>>(partial, g_gain, grid, (int)D);
+      NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_reduce_kernel (static scratch)");
+      return NSB_OK;
+    });
+  });
+}
