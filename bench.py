@@ -240,10 +240,21 @@ def cpu_sample(B, T, D, seed, slice_b=1):
     return beta, cur, gain, vth, v0, gs
 
 
+_cpu_out = {}
+
+
 def cpu_step(orc, s):
+    """Forward + backward of the CPU port into pre-allocated (already touched) outputs."""
+    import numpy as np
     beta, cur, gain, vth, v0, gs = s
-    orc.plif_selective_ai_fwd(beta, cur, gain, vth, v0, want_vpost=False)
-    orc.plif_selective_ai_bwd(beta, cur, gain, vth, v0, gs, None, ALPHA, orc.SURR_ATAN)
+    key = cur.shape
+    if key not in _cpu_out:
+        _cpu_out.clear()
+        _cpu_out[key] = ((np.zeros_like(cur), None, np.zeros_like(v0)),
+                         tuple(np.zeros_like(cur) for _ in range(4)) + (np.zeros_like(v0),))
+    fo, bo = _cpu_out[key]
+    orc.plif_selective_ai_fwd(beta, cur, gain, vth, v0, want_vpost=False, out=fo)
+    orc.plif_selective_ai_bwd(beta, cur, gain, vth, v0, gs, None, ALPHA, orc.SURR_ATAN, out=bo)
 
 
 def cpu_baseline(B, T, D, budget_s=12.0):

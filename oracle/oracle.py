@@ -92,13 +92,17 @@ def plif_selective_fwd(beta, u, vth, v_init, want_vpost=True):
     return spike, vpost, vlast
 
 
-def plif_selective_ai_fwd(beta, cur, gain, vth, v_init, want_vpost=True):
-    """Selective scan with separate write gain and current (alpha*I form)."""
+def plif_selective_ai_fwd(beta, cur, gain, vth, v_init, want_vpost=True, out=None):
+    """Selective scan with separate write gain and current (alpha*I form).
+    ``out`` = (spike, vpost-or-None, vlast) reuses caller buffers (timing loops)."""
     beta, cur, gain, vth, v_init = map(_f32, (beta, cur, gain, vth, v_init))
     T, cols = _tc(cur)
-    spike = np.empty_like(cur)
-    vpost = np.empty_like(cur) if want_vpost else None
-    vlast = np.empty_like(v_init)
+    if out is not None:
+        spike, vpost, vlast = out
+    else:
+        spike = np.empty_like(cur)
+        vpost = np.empty_like(cur) if want_vpost else None
+        vlast = np.empty_like(v_init)
     lib().orc_plif_selective_ai_fwd(_p(beta), _p(cur), _p(gain), _p(vth), _p(v_init),
                                     _p(spike), _p(vpost), _p(vlast), _i64(T), _i64(cols))
     return spike, vpost, vlast
@@ -131,14 +135,17 @@ def plif_selective_bwd(beta, u, vth, v_init, g_spike, g_vpost, alpha, kind=SURR_
 
 
 def plif_selective_ai_bwd(beta, cur, gain, vth, v_init, g_spike, g_vpost, alpha,
-                          kind=SURR_SIGMOID):
-    """(g_beta, g_cur, g_gain, g_vth, g_vinit)."""
+                          kind=SURR_SIGMOID, out=None):
+    """(g_beta, g_cur, g_gain, g_vth, g_vinit). ``out`` reuses caller buffers."""
     beta, cur, gain, vth, v_init = map(_f32, (beta, cur, gain, vth, v_init))
     g_spike = None if g_spike is None else _f32(g_spike)
     g_vpost = None if g_vpost is None else _f32(g_vpost)
     T, cols = _tc(cur)
-    gb, gc, gg, gt = (np.empty_like(cur) for _ in range(4))
-    gv = np.empty_like(v_init)
+    if out is not None:
+        gb, gc, gg, gt, gv = out
+    else:
+        gb, gc, gg, gt = (np.empty_like(cur) for _ in range(4))
+        gv = np.empty_like(v_init)
     lib().orc_plif_selective_ai_bwd(_p(beta), _p(cur), _p(gain), _p(vth), _p(v_init),
                                     _p(g_spike), _p(g_vpost), _p(gb), _p(gc), _p(gg),
                                     _p(gt), _p(gv), _i64(T), _i64(cols),

@@ -183,48 +183,60 @@ static void selective_bwd_core(const float *beta, const float *u,
                                float *g_beta, float *g_u, float *g_cur,
                                float *g_gain, float *g_vth, float *g_vinit,
                                int64_t T, int64_t cols, double a, int kind) {
-#pragma omp parallel for schedule(dynamic, 16)
-  for (int64_t c = 0; c < cols; ++c) {
-    /* forward recompute: keep V_prev[k] and x[k] for this column */
-    float *vp = (float *)__builtin_malloc(sizeof(float) * (size_t)T * 2);
-    float *xs = vp + T;
-    float v = v_init[c];
-    for (int64_t k = 0; k < T; ++k) {
-      const int64_t o = k * cols + c;
-      float uu;
-      if (u)
-        uu = u[o];
-      else
-        uu = gain[o] * cur[o];
-      float bv = beta[o] * v;
-      float vpre = bv + uu;
-      vp[k] = v;
-      xs[k] = vpre - vth[o];
-      float s = vpre >= vth[o] ? 1.0f : 0.0f;
-      float vs = vth[o] * s;
-      v = vpre - vs;
-    }
-    double acc = 0.0;
-    for (int64_t k = T - 1; k >= 0; --k) {
-      const int64_t o = k * cols + c;
-      double s = xs[k] >= 0.0f ? 1.0 : 0.0;
-      double sg = surr_grad((double)xs[k], a, kind);
-      double gs = g_spike ? (double)g_spike[o] : 0.0;
-      double tot = (g_vpost ? (double)g_vpost[o] : 0.0) + acc;
-      double gpre = gs * sg + tot;
-      if (g_beta) g_beta[o] = (float)(gpre * (double)vp[k]);
-      if (u) {
-        if (g_u) g_u[o] = (float)gpre;
-      } else {
-        if (g_cur) g_cur[o] = (float)(gpre * (double)gain[o]);
-        if (g_gain) g_gain[o] = (float)(gpre * (double)cur[o]);
+  /* Columns are processed in blocks of BWD_BLOCK so that the inner loops run
+   * over contiguous lanes; V_prev[k] and x[k] of a block are kept for the
+   * reverse pass. */
+#define BWD_BLOCK 32
+#pragma omp parallel
+  {
+    float *vp = (float *)__builtin_malloc(sizeof(float) * (size_t)(T > 0 ? T : 1) * BWD_BLOCK * 2);
+    float *xs = vp + (size_t)(T > 0 ? T : 1) * BWD_BLOCK;
+#pragma omp for schedule(dynamic, 4)
+    for (int64_t c0 = 0; c0 < cols; c0 += BWD_BLOCK) {
+      const int64_t n = cols - c0 < BWD_BLOCK ? cols - c0 : BWD_BLOCK;
+      float v[BWD_BLOCK];
+      double acc[BWD_BLOCK];
+      for (int64_t j = 0; j < n; ++j) v[j] = v_init[c0 + j];
+      for (int64_t k = 0; k < T; ++k) {
+        const int64_t o = k * cols + c0;
+        for (int64_t j = 0; j < n; ++j) {
+          float uu = u ? u[o + j] : gain[o + j] * cur[o + j];
+          float bv = beta[o + j] * v[j];
+          float vpre = bv + uu;
+          vp[k * BWD_BLOCK + j] = v[j];
+          xs[k * BWD_BLOCK + j] = vpre - vth[o + j];
+          float s = vpre >= vth[o + j] ? 1.0f : 0.0f;
+          float vs = vth[o + j] * s;
+          v[j] = vpre - vs;
+        }
       }
-      if (g_vth) g_vth[o] = (float)(-gs * sg - tot * s);
-      acc = gpre * (double)beta[o];
+      for (int64_t j = 0; j < n; ++j) acc[j] = 0.0;
+      for (int64_t k = T - 1; k >= 0; --k) {
+        const int64_t o = k * cols + c0;
+        for (int64_t j = 0; j < n; ++j) {
+          const double x = (double)xs[k * BWD_BLOCK + j];
+          const double s = x >= 0.0 ? 1.0 : 0.0;
+          const double sg = surr_grad(x, a, kind);
+          const double gs = g_spike ? (double)g_spike[o + j] : 0.0;
+          const double tot = (g_vpost ? (double)g_vpost[o + j] : 0.0) + acc[j];
+          const double gpre = gs * sg + tot;
+          if (g_beta) g_beta[o + j] = (float)(gpre * (double)vp[k * BWD_BLOCK + j]);
+          if (u) {
+            if (g_u) g_u[o + j] = (float)gpre;
+          } else {
+            if (g_cur) g_cur[o + j] = (float)(gpre * (double)gain[o + j]);
+            if (g_gain) g_gain[o + j] = (float)(gpre * (double)cur[o + j]);
+          }
+          if (g_vth) g_vth[o + j] = (float)(-gs * sg - tot * s);
+          acc[j] = gpre * (double)beta[o + j];
+        }
+      }
+      if (g_vinit)
+        for (int64_t j = 0; j < n; ++j) g_vinit[c0 + j] = (float)acc[j];
     }
-    if (g_vinit) g_vinit[c] = (float)acc;
     __builtin_free(vp);
   }
+#undef BWD_BLOCK
 }
 
 void orc_plif_selective_bwd(const float *beta, const float *u, const float *vth,
