@@ -4,10 +4,12 @@
 // T = 8192): (1) the scan is bound by HBM bandwidth, so CTAs that are resident
 // together share it and finish together; a launch may therefore run in several
 // "waves" at no cost as long as every wave keeps enough bytes in flight; (2) a
-// small last wave is latency-bound and expensive; (3) the bandwidth a pipeline
-// reaches grows with the bytes moved per TMA tile (512 B: ~0.5 of peak, 1 KB:
-// ~0.78, 2 KB: ~0.92, >= 4 KB: ~1); (4) an SM needs roughly 1000 resident columns
-// to hide the arithmetic latency of the recurrence.
+// wave can never finish faster than one warp walks its T steps (about 100+70*V
+// cycles per step forward, 1.4x that backward), which is what bounds problems
+// with few columns and makes a small last wave expensive; (3) the bandwidth a
+// pipeline reaches grows with the bytes moved per TMA tile (512 B: ~0.5 of peak,
+// 1 KB: ~0.78, 2 KB: ~0.92, >= 4 KB: ~1). The cost of a candidate is the sum over
+// its waves of max(bandwidth time, latency time, issue time) in microseconds.
 #include <algorithm>
 #include <cmath>
 
@@ -42,7 +44,7 @@ double op_size_factor(double tile_bytes) {
   if (tile_bytes >= 4096.0) return 1.0;
   if (tile_bytes <= 256.0) return 0.3;
   const double pts_x[] = {256.0, 512.0, 1024.0, 2048.0, 4096.0};
-  const double pts_y[] = {0.30, 0.52, 0.78, 0.93, 1.0};
+  const double pts_y[] = {0.30, 0.50, 0.74, 0.92, 1.0};
   for (int i = 0; i < 4; ++i) {
     if (tile_bytes <= pts_x[i + 1]) {
       const double t = (std::log2(tile_bytes) - std::log2(pts_x[i])) /
@@ -62,17 +64,29 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
   const int sms = std::max(1, d.sm_count);
   const int reserved = d.reserved_smem_per_cta > 0 ? d.reserved_smem_per_cta : 1024;
   const int ntiles = (int)((q.T + q.tile - 1) / q.tile);
-  const double inflight_needed = 5.0e6;  // bytes in flight chip-wide to cover HBM latency
+  // Calibration constants (B200): HBM bytes per microsecond, SM clock in cycles per
+  // microsecond, time from CTA start until its first tile has landed.
+  const double hbm_bytes_per_us = 6.5e6, clk_per_us = 1.9e3, t_start_us = 4.0;
+  // HBM bytes per neuron-step: the streamed inputs plus the outputs written back
+  // (dense forward: spikes; backward: one gradient per forward input).
+  const double bytes_per_ns = q.elem_size * (q.backward ? (2.0 * q.nstreams - 1.0) : (q.nstreams + 1.0));
   const int lane_opts[3] = {4, 2, 1};
   for (int lanes : lane_opts) {
     if (lanes > q.max_lanes) continue;
     if (tune.lanes_per_thread > 0 && lanes != tune.lanes_per_thread) continue;
+    // Scans of a few tiles only (per-token decoding) are dominated by CTA start-up;
+    // measured: 2 lanes per thread (twice the CTAs per SM) beat 4 by ~20 % at T = 16.
+    if (tune.lanes_per_thread <= 0 && ntiles <= 8 && lanes > 2) continue;
     const long long nwarps = (q.cols + 32LL * lanes - 1) / (32LL * lanes);
     const size_t tile_bytes = (size_t)q.tile * 32 * lanes * q.elem_size;
     const size_t stage_bytes = tile_bytes * q.nstreams;
     const int regs = regs_estimate(q.backward, lanes, q.tile);
     const int reg_warps = std::max(1, 65536 / (regs * 32));
     const double f_op = op_size_factor((double)tile_bytes);
+    // A lone warp advances one time step in about this many cycles (dependent
+    // chain + per-tile overheads), and needs about this many issue slots for it.
+    const double cyc_per_step = (q.backward ? 1.4 : 1.0) * (100.0 + 70.0 * lanes);
+    const double issue_per_step = (q.backward ? 2.0 : 1.0) * (20.0 + 15.0 * lanes);
     for (int wpc = 1; wpc <= 8; ++wpc) {
       if (tune.warps_per_cta > 0 && wpc != tune.warps_per_cta) continue;
       if (tune.warps_per_cta <= 0 && wpc > 4) continue;
@@ -87,23 +101,26 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
         if (res < 1) continue;
         const long long ctas = (nwarps + wpc - 1) / wpc;
         const long long cap = res * sms;
-        double cost = 0.0;
+        double cost = 0.0;  // microseconds
         long long remaining = ctas;
         while (remaining > 0) {
           const long long w = std::min(cap, remaining);
           const double warps = (double)w * wpc;
-          const double inflight = warps * (st - 1) * (double)stage_bytes;
-          const double f_mem = std::min(1.0, inflight / inflight_needed);
-          const double lanes_per_sm = warps * 32.0 * lanes / sms;
-          const double f_lat = std::min(1.0, 0.5 + 0.5 * lanes_per_sm / 1024.0);
-          cost += warps * lanes / (std::max(0.02, f_mem) * f_lat * f_op);
-          remaining -= w;
-          if (ctas > 64 * cap) {  // many waves: the rest behaves like this one
-            cost *= (double)ctas / (double)w;
+          const double t_bw = warps * 32.0 * lanes * (double)q.T * bytes_per_ns / (hbm_bytes_per_us * f_op);
+          const double t_lat = t_start_us + (double)q.T * cyc_per_step / clk_per_us;
+          const double warps_per_sched = std::max(1.0, warps / (sms * 4.0));
+          const double t_issue = warps_per_sched * (double)q.T * issue_per_step / clk_per_us;
+          const double t_wave = std::max(t_bw, std::max(t_lat, t_issue));
+          if (ctas > 8 * cap) {  // many waves: they all look like this one
+            cost = t_wave * (double)ctas / (double)w;
             break;
           }
+          cost += t_wave;
+          remaining -= w;
         }
-        cost *= 1.0 + 0.004 * st + 0.002 * wpc;  // prefer the smaller configuration on ties
+        // on ties prefer a 3-deep ring (measured a few per cent better than 2 when shared
+        // memory is not the limit) and small CTAs
+        cost *= 1.0 + 0.004 * std::abs(st - 3) + 0.002 * wpc;
         if (cost < best_cost) {
           best_cost = cost;
           best.lanes = lanes;
