@@ -45,6 +45,16 @@ WORKLOADS = {
     "c2-short": (32, 512, 6144),   # same grid, 1/16 of the time steps (2.8 GB): profiler captures
     "c0": (2, 1024, 768),
 }
+# Secondary (forward-only, bit-packed spikes) workloads; not the default bench line.
+#   c1      row-parameter scan, per-channel beta / V_th, B=8 on every GPU
+#   c4      selective scan, gain*cur form, B=256 split evenly across the GPUs (strong scaling)
+#   decode  per-token decoding: 64 consecutive 16-step calls at B=1024 (split across GPUs),
+#           membrane state carried from call to call
+INFERENCE_WORKLOADS = {
+    "c1": dict(kind="row", B=8, T=8192, D=768, shard=False, calls=1, bytes_per_ns=2.125),
+    "c4": dict(kind="ai", B=256, T=8192, D=6144, shard=True, calls=1, bytes_per_ns=8.125),
+    "decode": dict(kind="ai", B=1024, T=16, D=6144, shard=True, calls=64, bytes_per_ns=8.625),
+}
 # algorithmic bytes per neuron-step with 2-byte streams
 BYTES_FWD = 4 * 2 + 2          # beta, I, alpha, V_th in; spikes out
 BYTES_BWD = 4 * 2 + 2 + 4 * 2  # the four inputs again, dL/dspike in; four gradients out
@@ -62,7 +72,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(INFERENCE_WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     return ap.parse_args()
@@ -281,7 +291,7 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle import oracle as orc
-    B, T, D = WORKLOADS[args.workload]
+    B, T, D = WORKLOADS[args.workload if args.workload in WORKLOADS else "c2"]
     cores = os.cpu_count() or 1
     orc.set_threads(cores)
     s = cpu_sample(B, T, D, 99, 1)
@@ -308,6 +318,132 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------- inference workloads
+
+
+def run_inference(args):
+    """Forward-only workloads with bit-packed spikes (c1, c4, decode)."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    import neuronspark_b200 as nsb
+    from neuronspark_b200 import _lib, parallel_scan as ps, sharding
+    w = INFERENCE_WORKLOADS[args.workload]
+    B = sharding.batch_shard(w["B"], world, rank)[1] if w["shard"] else w["B"]
+    T, D, calls = w["T"], w["D"], w["calls"]
+    L = _lib.lib()
+    cols = B * D
+    words = (cols + 31) // 32
+    stream = _lib.stream_ptr(dev)
+    p = _lib.ptr
+    packed = torch.empty((T * calls, words), dtype=torch.int32, device=dev)
+    v_a = torch.zeros((B, D), dtype=torch.float32, device=dev)
+    v_b = torch.empty_like(v_a)
+    if w["kind"] == "row":
+        g = torch.Generator(device=dev).manual_seed(1234 + rank)
+        bd = torch.sigmoid(2 + 0.5 * torch.randn(D, generator=g, device=dev))
+        td = (0.5 + 0.1 * torch.randn(D, generator=g, device=dev)).clamp(min=0.05)
+        cur = torch.randn(T, B, D, generator=g, device=dev).bfloat16()
+        u = ((1 - bd) * cur.float()).bfloat16()  # formed by the caller, as the reference does
+        beta_row, vth_row = bd.expand(B, D).contiguous(), td.expand(B, D).contiguous()
+
+        def step():
+            _lib.check(L.nsb_plif_rowparam_fwd(p(beta_row), p(u), p(vth_row), p(v_a), None, p(packed), None,
+                                               None, p(v_b), T, cols, _lib.BF16, 8, stream), "rowparam_fwd")
+    else:
+        inp = make_inputs(B, T * calls, D, dev, 1234 + rank)
+        esz = 2 * cols
+
+        def step():
+            src, dst = v_a, v_b
+            src.zero_()
+            for c in range(calls):
+                off = c * T * esz
+                _lib.check(L.nsb_plif_selective_fwd(
+                    inp["beta"].data_ptr() + off, inp["cur"].data_ptr() + off, inp["gain"].data_ptr() + off,
+                    inp["vth"].data_ptr() + off, p(src), None, packed.data_ptr() + c * T * words * 4, None,
+                    None, p(dst), T, cols, _lib.BF16, 8, stream), "selective_fwd")
+                src, dst = dst, src
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    info = _lib.last_launch_info()
+    K = args.steps
+    sampler = ClockSampler(local) if rank == 0 else None
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if T * calls * cols * 2 < (512 << 20) else None
+    barrier()
+    if sampler:
+        sampler.start()
+    if flush is None:
+        start.record()
+        for _ in range(K):
+            step()
+        end.record()
+        barrier()
+        ms = start.elapsed_time(end) / K
+    else:  # small inputs: write 256 MB between timed iterations so nothing is served from L2
+        tot = 0.0
+        for _ in range(K):
+            flush.fill_(1)
+            start.record()
+            step()
+            end.record()
+            torch.cuda.synchronize()
+            tot += start.elapsed_time(end)
+        barrier()
+        ms = tot / K
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        total_b = torch.tensor([B], device=dev)
+        dist.all_reduce(total_b)
+        total_b = int(total_b[0])
+    else:
+        total_b = B
+    assert nsb.device_error_word() == 0
+    ns_local = calls * T * cols
+    value = calls * T * total_b * D / (ms * 1e-3)
+    if rank == 0:
+        peak, peak_src = hbm_peak()
+        ach = w["bytes_per_ns"] * ns_local * 1e-9 / (ms * 1e-3)
+        line = {
+            "metric": "PLIF scan neuron-steps/s (B*T*D), forward, bit-packed spikes", "value": value,
+            "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong" if w["shard"] else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['kind']} forward, packed spikes, B={total_b} global "
+                                   f"({B} on this GPU), T={T} x {calls} call(s), D={D}, bf16 streams, fp32 state",
+                       "l2": "L2 flushed between iterations" if flush is not None else "inputs larger than L2",
+                       "launch": info},
+            "roofline": {"bound": "hbm", "kernel": "plif_fwd_kernel", "achieved": ach, "peak": peak,
+                         "unit": "GB/s", "frac": ach / peak, "traffic": None, "peak_source": peak_src,
+                         "algorithmic_bytes_per_neuron_step": w["bytes_per_ns"],
+                         "note": "few columns: bounded by the serial chain over T, not by HBM"
+                         if cols < 100000 else ""},
+            "clocks": clocks, "gpu_launches": K * calls,
+            "spike_rate": float(((packed[:64].unsqueeze(-1) >> torch.arange(32, device=dev)) & 1).float().mean()),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------- main
 
 
@@ -315,6 +451,9 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload in INFERENCE_WORKLOADS:
+        run_inference(args)
         return
     import torch
     import torch.distributed as dist
