@@ -156,6 +156,41 @@ int nsb_plif_rowparam_bwd(const float* beta_row, const void* u, const float* vth
                           int surrogate, float alpha, void* stream);
 
 /*
+ * Resonate-and-fire (second-order) PLIF scan, forward. Replaces
+ * _fused_rf_plif_fwd_kernel and _fused_rf_plif_fwd_recompute_kernel
+ * (atomic_ops/parallel_scan.py:777-818, 924-956; callers :1610-1726,
+ * atomic_ops/snn_block.py:252-256):
+ *   v_pre = (beta[k]*v - omega[k]*w) + u[k];   w' = omega[k]*v + beta[k]*w
+ *   s = (v_pre >= v_th[k]);  v = v_pre - v_th[k]*s;  w = w'      (W is never reset)
+ * beta, omega, u, v_th [T, cols] in `dtype`; v_init, w_init [cols] fp32.
+ * Optional outputs: spike_dense, spike_packed, v_post, w_out ([T, cols]); the
+ * checkpoints v_ckpt and w_ckpt ([ceil(T/ckpt_interval), cols] fp32, both or
+ * neither) are what the backward needs. v_last, w_last [cols] fp32 are required.
+ */
+int nsb_plif_rf_fwd(const void* beta, const void* omega, const void* u, const void* v_th,
+                    const float* v_init, const float* w_init, void* spike_dense,
+                    uint32_t* spike_packed, void* v_post, void* w_out, float* v_ckpt,
+                    float* w_ckpt, float* v_last, float* w_last, int64_t T, int64_t cols,
+                    int dtype, int ckpt_interval, void* stream);
+
+/*
+ * Reverse pass of the resonate-and-fire scan. Replaces _fused_rf_plif_bwd_kernel and
+ * _fused_rf_plif_bwd_recompute_kernel (atomic_ops/parallel_scan.py:820-916, 958-1069)
+ * with the same coupled V/W adjoint recurrence (:835-848):
+ *   gpre = g_spike*sg + (g_vpost + acc_v);   g_u = gpre
+ *   g_beta  = gpre*V[k-1] + acc_w*W[k-1];    g_omega = acc_w*V[k-1] - gpre*W[k-1]
+ *   g_vth   = -g_spike*sg - (g_vpost + acc_v)*s
+ *   acc_v'  = gpre*beta + acc_w*omega;       acc_w'  = acc_w*beta - gpre*omega
+ * States are recomputed per tile from the checkpoints. g_vpost may be NULL; a
+ * gradient for W is not taken (the reference ignores it, :1114).
+ */
+int nsb_plif_rf_bwd(const void* beta, const void* omega, const void* u, const void* v_th,
+                    const float* v_ckpt, const float* w_ckpt, const void* g_spike,
+                    const void* g_vpost, void* g_beta, void* g_omega, void* g_u, void* g_vth,
+                    float* g_vinit, float* g_winit, int64_t T, int64_t cols, int dtype,
+                    int ckpt_interval, int surrogate, float alpha, void* stream);
+
+/*
  * FP16 boundary codec (atomic_ops/fp16_codec.py).
  *
  * nsb_fp16_encode        fp16_encode (:17-46): values [B,S,D] in dtype_in ->

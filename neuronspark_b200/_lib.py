@@ -38,6 +38,9 @@ _SIGNATURES = {
     "nsb_plif_rowparam_fwd": (c_int, [c_void_p] * 9 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_plif_rowparam_bwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_int,
                                                          c_float, c_void_p]),
+    "nsb_plif_rf_fwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_plif_rf_bwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_float,
+                                                   c_void_p]),
     "nsb_fp16_encode": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_fp16_decode_fwd": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "nsb_fp16_decode_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,

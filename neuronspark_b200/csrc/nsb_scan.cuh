@@ -28,16 +28,22 @@
 
 namespace nsb {
 
-enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2 };
+// MODE_RF is the second-order resonate-and-fire scan: it streams beta, u, omega, v_th
+// (omega in the slot the gain*cur form uses for the gain) and carries two states, V and W.
+enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3 };
 
 struct FwdArgs {
   const void* beta = nullptr;   // streams ([T, cols], stream dtype)
   const void* drive = nullptr;  // u (MODE_U / MODE_ROW) or cur (MODE_AI)
-  const void* gain = nullptr;   // MODE_AI only
+  const void* gain = nullptr;   // MODE_AI: gain; MODE_RF: omega
   const void* vth = nullptr;
   const float* beta_row = nullptr;  // MODE_ROW
   const float* vth_row = nullptr;
   const float* v_init = nullptr;
+  const float* w_init = nullptr;  // MODE_RF
+  void* w_out = nullptr;          // MODE_RF, optional dense W
+  float* ckpt_w = nullptr;        // MODE_RF
+  float* wlast = nullptr;         // MODE_RF
   void* spike = nullptr;
   uint32_t* packed = nullptr;
   void* vpost = nullptr;
@@ -57,6 +63,8 @@ struct BwdArgs {
   const float* beta_row = nullptr;
   const float* vth_row = nullptr;
   const float* ckpt = nullptr;
+  const float* ckpt_w = nullptr;  // MODE_RF
+  float* g_winit = nullptr;       // MODE_RF
   const void* g_spike = nullptr;
   const void* g_vpost = nullptr;
   void* g_beta = nullptr;   // stream dtype (selective)
@@ -267,11 +275,15 @@ struct FwdParams {
   const float* beta_row;
   const float* vth_row;
   const float* v_init;
+  const float* w_init;
   void* spike;
   uint32_t* packed;
   void* vpost;
+  void* w_out;
   float* ckpt;
+  float* ckpt_w;
   float* vlast;
+  float* wlast;
   long long T, cols, words_per_row;
   int ntiles, stages;
   uint32_t* err;
@@ -279,13 +291,13 @@ struct FwdParams {
 
 template <int MODE>
 struct ModeTraits {
-  static constexpr int kFwdStreams = MODE == MODE_ROW ? 1 : (MODE == MODE_AI ? 4 : 3);
+  static constexpr int kFwdStreams = MODE == MODE_ROW ? 1 : ((MODE == MODE_AI || MODE == MODE_RF) ? 4 : 3);
   // index of each role inside the stage / pointer table (roles that a mode
   // does not stream alias slot 0 and are never read)
   static constexpr int kBeta = 0;
   static constexpr int kDrive = MODE == MODE_ROW ? 0 : 1;
-  static constexpr int kGain = MODE == MODE_AI ? 2 : 0;
-  static constexpr int kVth = MODE == MODE_ROW ? 0 : (MODE == MODE_AI ? 3 : 2);
+  static constexpr int kGain = (MODE == MODE_AI || MODE == MODE_RF) ? 2 : 0;
+  static constexpr int kVth = MODE == MODE_ROW ? 0 : ((MODE == MODE_AI || MODE == MODE_RF) ? 3 : 2);
 };
 
 // One charge / fire / soft-reset step on the V lanes of a thread:
@@ -302,6 +314,29 @@ __device__ __forceinline__ void plif_step(float (&v)[V], const float (&beta)[V],
   for (int j = 0; j < V; ++j) {
     s[j] = vpre[j] >= vth[j];
     v[j] = s[j] ? x[j] : vpre[j];
+  }
+}
+
+// Resonate-and-fire step: v_pre = (beta*v - omega*w) + u, w' = omega*v + beta*w, every
+// product and sum rounded separately; only V is reset.
+template <int V>
+__device__ __forceinline__ void rf_step(float (&v)[V], float (&w)[V], const float (&beta)[V],
+                                        const float (&omega)[V], const float (&u)[V], const float (&vth)[V],
+                                        float (&x)[V], bool (&s)[V]) {
+  float bv[V], ow[V], d[V], vpre[V], ov[V], bw[V], wn[V];
+  vmul<V>(bv, beta, v);
+  vmul<V>(ow, omega, w);
+  vsub<V>(d, bv, ow);
+  vadd<V>(vpre, d, u);
+  vmul<V>(ov, omega, v);
+  vmul<V>(bw, beta, w);
+  vadd<V>(wn, ov, bw);
+  vsub<V>(x, vpre, vth);
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    s[j] = vpre[j] >= vth[j];
+    v[j] = s[j] ? x[j] : vpre[j];
+    w[j] = wn[j];
   }
 }
 
@@ -329,12 +364,13 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
 
   long long colj[V];
   bool valid[V];
-  float v[V], brow[V], trow[V];
+  float v[V], w[V], brow[V], trow[V];
 #pragma unroll
   for (int j = 0; j < V; ++j) {
     colj[j] = PACKED ? col0 + 32 * j + lane : col0 + V * lane + j;
     valid[j] = colj[j] < p.cols;
     v[j] = valid[j] ? p.v_init[colj[j]] : 0.0f;
+    w[j] = (MODE == MODE_RF && valid[j]) ? p.w_init[colj[j]] : 0.0f;
     brow[j] = 0.0f;
     trow[j] = 0.0f;
     if (MODE == MODE_ROW && valid[j]) {
@@ -409,6 +445,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     // ragged edges), so the step loop carries no global address arithmetic for them.
     ST* o_spike = (!VEC && p.spike) ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
     ST* o_vpost = p.vpost ? static_cast<ST*>(p.vpost) + t0 * row_elems + colj[0] : nullptr;
+    ST* o_wout = (MODE == MODE_RF && p.w_out) ? static_cast<ST*>(p.w_out) + t0 * row_elems + colj[0] : nullptr;
     uint32_t words[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) words[j] = 0u;
@@ -447,12 +484,19 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
         fetch(MT::kGain, k, gn);
         vmul<V>(dr, gn, dr);
       }
-      plif_step<V>(v, b, dr, th, x, sp_);
+      if constexpr (MODE == MODE_RF) {
+        float om[V];
+        fetch(MT::kGain, k, om);
+        rf_step<V>(v, w, b, om, dr, th, x, sp_);
+      } else {
+        plif_step<V>(v, b, dr, th, x, sp_);
+      }
 
       if constexpr (VEC) {
         IO::store_spikes(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + k * (32 * V), sp_);
         // a thread's V columns are all valid or all invalid
         if (o_vpost && valid[0]) IO::store(o_vpost + (size_t)k * row_elems, v);
+        if (MODE == MODE_RF && o_wout && valid[0]) IO::store(o_wout + (size_t)k * row_elems, w);
       } else {
 #pragma unroll
         for (int j = 0; j < V; ++j) {
@@ -460,6 +504,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
             const size_t off = (size_t)k * row_elems + (colj[j] - colj[0]);
             if (o_spike) o_spike[off] = sp_[j] ? E::one() : E::zero();
             if (o_vpost) o_vpost[off] = E::from_f32(v[j]);
+            if (MODE == MODE_RF && o_wout) o_wout[off] = E::from_f32(w[j]);
           }
         }
       }
@@ -496,10 +541,14 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     if (p.ckpt) {
       if constexpr (VEC) {
         if (valid[0]) VecIO<float, V>::store(p.ckpt + (long long)i * row_elems + colj[0], v);
+        if (MODE == MODE_RF && valid[0]) VecIO<float, V>::store(p.ckpt_w + (long long)i * row_elems + colj[0], w);
       } else {
 #pragma unroll
         for (int j = 0; j < V; ++j)
-          if (valid[j]) p.ckpt[(long long)i * row_elems + colj[j]] = v[j];
+          if (valid[j]) {
+            p.ckpt[(long long)i * row_elems + colj[j]] = v[j];
+            if (MODE == MODE_RF) p.ckpt_w[(long long)i * row_elems + colj[j]] = w[j];
+          }
       }
     }
     if (nsteps == C)
@@ -539,7 +588,10 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
   }
 #pragma unroll
   for (int j = 0; j < V; ++j)
-    if (valid[j]) p.vlast[colj[j]] = v[j];
+    if (valid[j]) {
+      p.vlast[colj[j]] = v[j];
+      if (MODE == MODE_RF) p.wlast[colj[j]] = w[j];
+    }
 }
 
 // ------------------------------------------------------------------ backward
@@ -554,6 +606,8 @@ struct BwdParams {
   const float* beta_row;
   const float* vth_row;
   const float* ckpt;
+  const float* ckpt_w;
+  float* g_winit;
   void* g_beta;
   void* g_drive;
   void* g_gain;
@@ -593,7 +647,7 @@ __device__ __forceinline__ void surrogate_grad(float (&sg)[V], const float (&x)[
 }
 
 template <typename ST, int MODE, int SURR, int V, int C, bool TMA, bool HAS_GV>
-__global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tm0,
+__global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwdMaxRegs) : 255) plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tm0,
                                 const __grid_constant__ CUtensorMap tm1,
                                 const __grid_constant__ CUtensorMap tm2,
                                 const __grid_constant__ CUtensorMap tm3,
@@ -624,12 +678,12 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
 
   long long colj[V];
   bool valid[V];
-  float brow[V], trow[V], acc[V], accb[V], acct[V];
+  float brow[V], trow[V], acc[V], accw[V], accb[V], acct[V];
 #pragma unroll
   for (int j = 0; j < V; ++j) {
     colj[j] = col0 + V * lane + j;
     valid[j] = colj[j] < p.cols;
-    acc[j] = accb[j] = acct[j] = 0.0f;
+    acc[j] = accw[j] = accb[j] = acct[j] = 0.0f;
     brow[j] = trow[j] = 0.0f;
     if (MODE == MODE_ROW && valid[j]) {
       brow[j] = p.beta_row[colj[j]];
@@ -697,22 +751,26 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
   float v[V];
   // The checkpoint of a tile (membrane state before its first step) is read
   // straight from global memory one tile ahead of its use.
-  float vnext[V];
+  float vnext[V], w[V], wnext[V];
 #pragma unroll
-  for (int j = 0; j < V; ++j) vnext[j] = 0.0f;
+  for (int j = 0; j < V; ++j) vnext[j] = w[j] = wnext[j] = 0.0f;
   if constexpr (TMA) {
-    if (ntiles > 0 && valid[0]) VecIO<float, V>::load(p.ckpt + (long long)(ntiles - 1) * row_elems + colj[0], vnext);
+    if (ntiles > 0 && valid[0]) {
+      VecIO<float, V>::load(p.ckpt + (long long)(ntiles - 1) * row_elems + colj[0], vnext);
+      if (MODE == MODE_RF) VecIO<float, V>::load(p.ckpt_w + (long long)(ntiles - 1) * row_elems + colj[0], wnext);
+    }
   }
 
   auto tile = [&](auto full_tag, int nsteps) {
     constexpr bool FULL = decltype(full_tag)::value;
     // recompute the tile forward, keeping V[k-1] and x[k] = V_pre[k] - V_th[k]
-    float vprev[C][V], xs[C][V];
+    float vprev[C][V], xs[C][V], wprev[MODE == MODE_RF ? C : 1][V];
 #pragma unroll
     for (int k = 0; k < C; ++k) {
 #pragma unroll
       for (int j = 0; j < V; ++j) {
         vprev[k][j] = v[j];
+        if (MODE == MODE_RF) wprev[MODE == MODE_RF ? k : 0][j] = w[j];
         xs[k][j] = 0.0f;
       }
       if (FULL || k < nsteps) {
@@ -734,7 +792,13 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
           fetch(MT::kGain, k, gn);
           vmul<V>(dr, gn, dr);
         }
-        plif_step<V>(v, b, dr, th, xs[k], s_);
+        if constexpr (MODE == MODE_RF) {
+          float om[V];
+          fetch(MT::kGain, k, om);
+          rf_step<V>(v, w, b, om, dr, th, xs[k], s_);
+        } else {
+          plif_step<V>(v, b, dr, th, xs[k], s_);
+        }
       }
     }
 
@@ -747,7 +811,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
     ST* o_beta = (!TMA && MODE != MODE_ROW && p.g_beta) ? static_cast<ST*>(p.g_beta) + tile_off : nullptr;
     ST* o_vth = (!TMA && MODE != MODE_ROW && p.g_vth) ? static_cast<ST*>(p.g_vth) + tile_off : nullptr;
     ST* o_drive = (!TMA && p.g_drive) ? static_cast<ST*>(p.g_drive) + tile_off : nullptr;
-    ST* o_gain = (!TMA && MODE == MODE_AI && p.g_gain) ? static_cast<ST*>(p.g_gain) + tile_off : nullptr;
+    ST* o_gain = (!TMA && MT::kFwdStreams == 4 && p.g_gain) ? static_cast<ST*>(p.g_gain) + tile_off : nullptr;
     ST* wsp = const_cast<ST*>(sp);
 #pragma unroll
     for (int kk = 0; kk < C; ++kk) {
@@ -769,12 +833,28 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
         vmul<V>(gb, gpre, vprev[k]);
 #pragma unroll
         for (int j = 0; j < V; ++j) gth[j] = -gssg[j] - (xs[k][j] >= 0.0f ? tot[j] : 0.0f);
+        if constexpr (MODE == MODE_RF) {
+          // coupled V/W adjoints: grad_beta = gpre*V[k-1] + aw*W[k-1], grad_omega = aw*V[k-1] - gpre*W[k-1],
+          // acc_v = gpre*beta + aw*omega, acc_w = aw*beta - gpre*omega  (aw = adjoint of W arriving at step k)
+          float om[V];
+          fetch(MT::kBeta, k, b);
+          fetch(MT::kGain, k, om);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const float vp_ = vprev[k][j], wp_ = wprev[MODE == MODE_RF ? k : 0][j], aw = accw[j];
+            gb[j] = fmaf(aw, wp_, gb[j]);
+            gg[j] = aw * vp_ - gpre[j] * wp_;
+            gd[j] = gpre[j];
+            acc[j] = gpre[j] * b[j] + aw * om[j];
+            accw[j] = aw * b[j] - gpre[j] * om[j];
+          }
+        }
         if constexpr (MODE == MODE_ROW) {
 #pragma unroll
           for (int j = 0; j < V; ++j) b[j] = brow[j];
           vadd<V>(accb, accb, gb);
           vadd<V>(acct, acct, gth);
-        } else {
+        } else if constexpr (MODE != MODE_RF) {
           fetch(MT::kBeta, k, b);
         }
         if constexpr (MODE == MODE_AI) {
@@ -784,14 +864,14 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
           vmul<V>(gd, gpre, gn);
           vmul<V>(gg, gpre, dr);
         }
-        vmul<V>(acc, gpre, b);
+        if constexpr (MODE != MODE_RF) vmul<V>(acc, gpre, b);
 
         if constexpr (TMA) {
           if constexpr (MODE != MODE_ROW) {
             IO::store(wsp + MT::kBeta * TILE_ELEMS + k * (32 * V), gb);
             IO::store(wsp + MT::kVth * TILE_ELEMS + k * (32 * V), gth);
           }
-          if constexpr (MODE == MODE_AI) {
+          if constexpr (MODE == MODE_AI || MODE == MODE_RF) {
             IO::store(wsp + MT::kDrive * TILE_ELEMS + k * (32 * V), gd);
             IO::store(wsp + MT::kGain * TILE_ELEMS + k * (32 * V), gg);
           } else {
@@ -809,7 +889,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
             put(o_beta, gb);
             put(o_vth, gth);
           }
-          if constexpr (MODE == MODE_AI) {
+          if constexpr (MODE == MODE_AI || MODE == MODE_RF) {
             put(o_drive, gd);
             put(o_gain, gg);
           } else {
@@ -836,8 +916,14 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
       const uint8_t* sp8 = data_ptr + (size_t)s_idx * stage_bytes;
       sp = reinterpret_cast<const ST*>(sp8) + V * lane;
 #pragma unroll
-      for (int j = 0; j < V; ++j) v[j] = vnext[j];
-      if (i > 0 && valid[0]) VecIO<float, V>::load(p.ckpt + (long long)(i - 1) * row_elems + colj[0], vnext);
+      for (int j = 0; j < V; ++j) {
+        v[j] = vnext[j];
+        w[j] = wnext[j];
+      }
+      if (i > 0 && valid[0]) {
+        VecIO<float, V>::load(p.ckpt + (long long)(i - 1) * row_elems + colj[0], vnext);
+        if (MODE == MODE_RF) VecIO<float, V>::load(p.ckpt_w + (long long)(i - 1) * row_elems + colj[0], wnext);
+      }
     } else {
 #pragma unroll
       for (int st = 0; st < NF + 2; ++st) {
@@ -851,7 +937,10 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
                 (present && k < nsteps && valid[j]) ? g[(t0 + k) * row_elems + colj[j]] : E::zero();
       }
 #pragma unroll
-      for (int j = 0; j < V; ++j) v[j] = valid[j] ? p.ckpt[(long long)i * row_elems + colj[j]] : 0.0f;
+      for (int j = 0; j < V; ++j) {
+        v[j] = valid[j] ? p.ckpt[(long long)i * row_elems + colj[j]] : 0.0f;
+        w[j] = (MODE == MODE_RF && valid[j]) ? p.ckpt_w[(long long)i * row_elems + colj[j]] : 0.0f;
+      }
     }
 
     if (nsteps == C)
@@ -868,7 +957,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
         if (MODE != MODE_ROW && p.g_beta) tma_store_2d(&tmo_beta, src + MT::kBeta * TILE_BYTES, x, y);
         if (MODE != MODE_ROW && p.g_vth) tma_store_2d(&tmo_vth, src + MT::kVth * TILE_BYTES, x, y);
         if (p.g_drive) tma_store_2d(&tmo_drive, src + MT::kDrive * TILE_BYTES, x, y);
-        if (MODE == MODE_AI && p.g_gain) tma_store_2d(&tmo_gain, src + MT::kGain * TILE_BYTES, x, y);
+        if (MT::kFwdStreams == 4 && p.g_gain) tma_store_2d(&tmo_gain, src + MT::kGain * TILE_BYTES, x, y);
         bulk_commit_group();
         bulk_wait_read_all();  // the stage is refilled next
         if (i - stages >= 0) issue(i - stages, s_idx);
@@ -892,6 +981,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? kBwdMaxRegs : 255) plif_bwd_k
   for (int j = 0; j < V; ++j) {
     if (valid[j]) {
       if (p.g_vinit) p.g_vinit[colj[j]] = acc[j];
+      if (MODE == MODE_RF && p.g_winit) p.g_winit[colj[j]] = accw[j];
       if (MODE == MODE_ROW) {
         if (p.g_beta_row) p.g_beta_row[colj[j]] = accb[j];
         if (p.g_vth_row) p.g_vth_row[colj[j]] = acct[j];
@@ -913,14 +1003,15 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   const void* streams[4] = {nullptr, nullptr, nullptr, nullptr};
   if (MODE == MODE_ROW) {
     streams[0] = a.drive;
-  } else if (MODE == MODE_AI) {
+  } else if (MODE == MODE_AI || MODE == MODE_RF) {
     streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.gain; streams[3] = a.vth;
   } else {
     streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.vth;
   }
   for (int i = 0; i < 4; ++i) p.s[i] = streams[i];
-  p.beta_row = a.beta_row; p.vth_row = a.vth_row; p.v_init = a.v_init;
-  p.spike = a.spike; p.packed = a.packed; p.vpost = a.vpost; p.ckpt = a.ckpt; p.vlast = a.vlast;
+  p.beta_row = a.beta_row; p.vth_row = a.vth_row; p.v_init = a.v_init; p.w_init = a.w_init;
+  p.spike = a.spike; p.packed = a.packed; p.vpost = a.vpost; p.w_out = a.w_out; p.ckpt = a.ckpt;
+  p.ckpt_w = a.ckpt_w; p.vlast = a.vlast; p.wlast = a.wlast;
   p.T = a.T; p.cols = a.cols; p.words_per_row = (a.cols + 31) / 32;
   p.ntiles = (int)((a.T + C - 1) / C);
   p.err = device_error_word_ptr();
@@ -967,7 +1058,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   const void* streams[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   if (MODE == MODE_ROW) {
     streams[0] = a.drive;
-  } else if (MODE == MODE_AI) {
+  } else if (MODE == MODE_AI || MODE == MODE_RF) {
     streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.gain; streams[3] = a.vth;
   } else {
     streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.vth;
@@ -977,7 +1068,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   const int has_gv = a.g_vpost != nullptr;
   const int nstreams = NF + 1 + has_gv;
   for (int i = 0; i < 6; ++i) p.s[i] = streams[i];
-  p.beta_row = a.beta_row; p.vth_row = a.vth_row; p.ckpt = a.ckpt;
+  p.beta_row = a.beta_row; p.vth_row = a.vth_row; p.ckpt = a.ckpt; p.ckpt_w = a.ckpt_w; p.g_winit = a.g_winit;
   p.g_beta = a.g_beta; p.g_drive = a.g_drive; p.g_gain = a.g_gain; p.g_vth = a.g_vth;
   p.g_beta_row = a.g_beta_row; p.g_vth_row = a.g_vth_row; p.g_vinit = a.g_vinit;
   p.T = a.T; p.cols = a.cols;
@@ -1047,7 +1138,7 @@ int scan_fwd_dispatch(const FwdArgs& a) {
   if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
   const Tuning tune = get_tuning();
   bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
-  const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.spike, a.vpost, a.ckpt};
+  const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.spike, a.vpost, a.ckpt, a.w_out, a.ckpt_w};
   for (const void* q : ptrs) tma = tma && aligned16(q);
   const bool packed = a.packed != nullptr;
   const int C = a.tile;
@@ -1055,7 +1146,7 @@ int scan_fwd_dispatch(const FwdArgs& a) {
   if (tma) {
     PlanQuery q;
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
-    q.nstreams = a.mode == MODE_ROW ? 1 : (a.mode == MODE_AI ? 4 : 3);
+    q.nstreams = a.mode == MODE_ROW ? 1 : ((a.mode == MODE_AI || a.mode == MODE_RF) ? 4 : 3);
     q.tile = C; q.backward = false; q.max_lanes = 4;
     plan = plan_scan(dev, q, tune);
   }
@@ -1072,6 +1163,7 @@ int scan_fwd_dispatch(const FwdArgs& a) {
     NSB_FWD_CASES_V(MODE_U, false) NSB_FWD_CASES_V(MODE_U, true)
     NSB_FWD_CASES_V(MODE_AI, false) NSB_FWD_CASES_V(MODE_AI, true)
     NSB_FWD_CASES_V(MODE_ROW, false) NSB_FWD_CASES_V(MODE_ROW, true)
+    NSB_FWD_CASES_V(MODE_RF, false) NSB_FWD_CASES_V(MODE_RF, true)
     return NSB_ERR_INVALID_ARG;
   }
 #undef NSB_FWD_CASES_V
@@ -1083,6 +1175,7 @@ int scan_fwd_dispatch(const FwdArgs& a) {
   NSB_FWD_DIRECT(MODE_U, 8) NSB_FWD_DIRECT(MODE_U, 16)
   NSB_FWD_DIRECT(MODE_AI, 8) NSB_FWD_DIRECT(MODE_AI, 16)
   NSB_FWD_DIRECT(MODE_ROW, 8) NSB_FWD_DIRECT(MODE_ROW, 16)
+  NSB_FWD_DIRECT(MODE_RF, 8) NSB_FWD_DIRECT(MODE_RF, 16)
 #undef NSB_FWD_DIRECT
   return NSB_ERR_INVALID_ARG;
 }
@@ -1095,7 +1188,7 @@ int scan_bwd_dispatch(const BwdArgs& a) {
   if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
   const Tuning tune = get_tuning();
   bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
-  const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.ckpt, a.g_spike, a.g_vpost,
+  const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.ckpt, a.ckpt_w, a.g_spike, a.g_vpost,
                         a.g_beta, a.g_drive, a.g_gain, a.g_vth};
   for (const void* q : ptrs) tma = tma && aligned16(q);
   const int C = a.tile;
@@ -1103,8 +1196,9 @@ int scan_bwd_dispatch(const BwdArgs& a) {
   if (tma) {
     PlanQuery q;
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
-    q.nstreams = (a.mode == MODE_ROW ? 1 : (a.mode == MODE_AI ? 4 : 3)) + 1 + (a.g_vpost ? 1 : 0);
-    q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : 2;
+    q.nstreams = (a.mode == MODE_ROW ? 1 : ((a.mode == MODE_AI || a.mode == MODE_RF) ? 4 : 3)) + 1 + (a.g_vpost ? 1 : 0);
+    // the resonate-and-fire backward keeps three per-step arrays in registers: 2 lanes at most
+    q.tile = C; q.backward = true; q.max_lanes = (C == 8 && a.mode != MODE_RF) ? 4 : 2;
     plan = plan_scan(dev, q, tune);
   }
   const int V = plan.lanes;
@@ -1116,13 +1210,18 @@ int scan_bwd_dispatch(const BwdArgs& a) {
   NSB_BWD_CASE(MODE_, SURR_, 1, 8) NSB_BWD_CASE(MODE_, SURR_, 2, 8)                    \
   NSB_BWD_CASE(MODE_, SURR_, 4, 8) NSB_BWD_CASE(MODE_, SURR_, 1, 16)                   \
   NSB_BWD_CASE(MODE_, SURR_, 2, 16)
+#define NSB_BWD_CASES_RF(SURR_)                                                         \
+  NSB_BWD_CASE(MODE_RF, SURR_, 1, 8) NSB_BWD_CASE(MODE_RF, SURR_, 2, 8)                \
+  NSB_BWD_CASE(MODE_RF, SURR_, 1, 16) NSB_BWD_CASE(MODE_RF, SURR_, 2, 16)
   if (tma) {
     NSB_BWD_CASES_V(MODE_U, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_U, NSB_SURR_ATAN)
     NSB_BWD_CASES_V(MODE_AI, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_AI, NSB_SURR_ATAN)
     NSB_BWD_CASES_V(MODE_ROW, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_ROW, NSB_SURR_ATAN)
+    NSB_BWD_CASES_RF(NSB_SURR_SIGMOID) NSB_BWD_CASES_RF(NSB_SURR_ATAN)
     return NSB_ERR_INVALID_ARG;
   }
 #undef NSB_BWD_CASES_V
+#undef NSB_BWD_CASES_RF
 #undef NSB_BWD_CASE
 #define NSB_BWD_DIRECT(MODE_, SURR_, C_)                                               \
   if (a.mode == MODE_ && a.surrogate == SURR_ && C == C_)                              \
@@ -1130,7 +1229,7 @@ int scan_bwd_dispatch(const BwdArgs& a) {
 #define NSB_BWD_DIRECT_S(MODE_)                                                        \
   NSB_BWD_DIRECT(MODE_, NSB_SURR_SIGMOID, 8) NSB_BWD_DIRECT(MODE_, NSB_SURR_SIGMOID, 16) \
   NSB_BWD_DIRECT(MODE_, NSB_SURR_ATAN, 8) NSB_BWD_DIRECT(MODE_, NSB_SURR_ATAN, 16)
-  NSB_BWD_DIRECT_S(MODE_U) NSB_BWD_DIRECT_S(MODE_AI) NSB_BWD_DIRECT_S(MODE_ROW)
+  NSB_BWD_DIRECT_S(MODE_U) NSB_BWD_DIRECT_S(MODE_AI) NSB_BWD_DIRECT_S(MODE_ROW) NSB_BWD_DIRECT_S(MODE_RF)
 #undef NSB_BWD_DIRECT_S
 #undef NSB_BWD_DIRECT
   return NSB_ERR_INVALID_ARG;

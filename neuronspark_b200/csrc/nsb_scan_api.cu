@@ -131,4 +131,59 @@ int nsb_plif_rowparam_bwd(const float* beta_row, const void* u, const float* vth
   return run_bwd(a, dtype);
 }
 
+int nsb_plif_rf_fwd(const void* beta, const void* omega, const void* u, const void* v_th,
+                    const float* v_init, const float* w_init, void* spike_dense, uint32_t* spike_packed,
+                    void* v_post, void* w_out, float* v_ckpt, float* w_ckpt, float* v_last, float* w_last,
+                    int64_t T, int64_t cols, int dtype, int ckpt_interval, void* stream) {
+  if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
+  if (cols == 0) return NSB_OK;
+  if (!v_init || !w_init || !v_last || !w_last) return NSB_ERR_INVALID_ARG;
+  if ((v_ckpt == nullptr) != (w_ckpt == nullptr)) return NSB_ERR_INVALID_ARG;
+  const void* fp[] = {v_init, w_init, v_last, w_last, v_ckpt, w_ckpt, spike_packed};
+  for (const void* p : fp)
+    if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
+  if (T > 0 && (!beta || !omega || !u || !v_th)) return NSB_ERR_INVALID_ARG;
+  const void* ep[] = {beta, omega, u, v_th, spike_dense, v_post, w_out};
+  for (const void* p : ep)
+    if (!elem_aligned(p, dtype)) return NSB_ERR_INVALID_ARG;
+  nsb::FwdArgs a;
+  a.beta = beta; a.drive = u; a.gain = omega; a.vth = v_th; a.v_init = v_init; a.w_init = w_init;
+  a.spike = spike_dense; a.packed = spike_packed; a.vpost = v_post; a.w_out = w_out;
+  a.ckpt = v_ckpt; a.ckpt_w = w_ckpt; a.vlast = v_last; a.wlast = w_last;
+  a.T = T; a.cols = cols; a.mode = nsb::MODE_RF; a.tile = ckpt_interval;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_fwd(a, dtype);
+}
+
+int nsb_plif_rf_bwd(const void* beta, const void* omega, const void* u, const void* v_th,
+                    const float* v_ckpt, const float* w_ckpt, const void* g_spike, const void* g_vpost,
+                    void* g_beta, void* g_omega, void* g_u, void* g_vth, float* g_vinit, float* g_winit,
+                    int64_t T, int64_t cols, int dtype, int ckpt_interval, int surrogate, float alpha,
+                    void* stream) {
+  if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
+  if (surrogate != NSB_SURR_SIGMOID && surrogate != NSB_SURR_ATAN) return NSB_ERR_INVALID_ARG;
+  if (cols == 0) return NSB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    float* z[] = {g_vinit, g_winit};
+    for (float* q : z)
+      if (q) NSB_CUDA_TRY(cudaMemsetAsync(q, 0, sizeof(float) * cols, st), "memset state grads");
+    return NSB_OK;
+  }
+  if (!beta || !omega || !u || !v_th || !v_ckpt || !w_ckpt || !g_spike) return NSB_ERR_INVALID_ARG;
+  const void* fp[] = {v_ckpt, w_ckpt, g_vinit, g_winit};
+  for (const void* p : fp)
+    if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
+  const void* ep[] = {beta, omega, u, v_th, g_spike, g_vpost, g_beta, g_omega, g_u, g_vth};
+  for (const void* p : ep)
+    if (!elem_aligned(p, dtype)) return NSB_ERR_INVALID_ARG;
+  nsb::BwdArgs a;
+  a.beta = beta; a.drive = u; a.gain = omega; a.vth = v_th; a.ckpt = v_ckpt; a.ckpt_w = w_ckpt;
+  a.g_spike = g_spike; a.g_vpost = g_vpost; a.g_beta = g_beta; a.g_drive = g_u; a.g_gain = g_omega;
+  a.g_vth = g_vth; a.g_vinit = g_vinit; a.g_winit = g_winit;
+  a.T = T; a.cols = cols; a.mode = nsb::MODE_RF; a.tile = ckpt_interval;
+  a.surrogate = surrogate; a.alpha = alpha; a.stream = st;
+  return run_bwd(a, dtype);
+}
+
 }  // extern "C"

@@ -13,8 +13,8 @@ the originals back.
     import neuronspark_b200.install as nsb_install
     nsb_install.install()               # snn_block / snn_ffn / model now call the CUDA kernels
 
-Functions of the reference that this package does not replace (the
-second-order RF scan, the linear recurrence, MoE combine) are left untouched.
+Functions of the reference that this package does not replace (the linear
+recurrence, MoE combine) are left untouched.
 """
 from __future__ import annotations
 
@@ -28,7 +28,9 @@ REPLACEMENTS = {
     "parallel_scan": (parallel_scan, (
         "_TritonPLIFForward", "_TritonPLIFRowParamForward", "_TritonPLIFRowParamRecompute",
         "plif_parallel_forward", "plif_rowparam_forward", "plif_rowparam_forward_alpha",
-        "plif_rowparam_forward_recompute", "plif_fixed_param_forward")),
+        "plif_rowparam_forward_recompute", "plif_fixed_param_forward",
+        "_TritonRFPLIFForward", "_TritonRFPLIFRecompute", "rf_plif_parallel_forward",
+        "rf_plif_parallel_forward_recompute")),
     "fp16_codec": (fp16_codec, (
         "fp16_encode", "fp16_decode", "binary_residual", "binary_encode_ste", "_BinaryResidual",
         "_BinaryEncodeSTE")),

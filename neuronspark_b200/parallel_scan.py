@@ -13,6 +13,9 @@ semantics as the reference):
     plif_parallel_forward, plif_rowparam_forward, plif_rowparam_forward_alpha,
     plif_rowparam_forward_recompute, plif_fixed_param_forward
         reference: :1309-1412, :1415-1453, :1456-1495, :1499-1535, :1538-1603
+    _TritonRFPLIFForward / _TritonRFPLIFRecompute .apply(beta, omega, u, v_th, v_init, w_init, alpha)
+    rf_plif_parallel_forward, rf_plif_parallel_forward_recompute
+        reference: :1071-1233, :1610-1726 (second-order resonate-and-fire scan)
 
 Differences, all deliberate:
   * CUDA only. A CPU tensor raises; nothing falls back to PyTorch ops.
@@ -327,7 +330,98 @@ class PLIFRowParamRecomputeScan(torch.autograd.Function):
         return _rowparam_backward(ctx, grad_spike, None)
 
 
+# ------------------------------------------------- resonate-and-fire (second-order) scan
+
+
+def _rf_forward(ctx, beta, omega, u, v_th, v_init, w_init, alpha, want_states):
+    out_dtype = u.dtype
+    dt = _common_stream_dtype(beta, omega, u, v_th)
+    beta_c, omega_c, u_c, vth_c = (_as_stream(t, dt) for t in (beta, omega, u, v_th))
+    shape = u.shape[1:]
+    v0, w0 = _row_f32(v_init, shape), _row_f32(w_init, shape)
+    dev = _lib.require_cuda(beta_c, omega_c, u_c, vth_c, v0, w0)
+    T, cols = u_c.shape[0], _cols(u_c)
+    needs_grad = any(ctx.needs_input_grad[:6])
+    spike = torch.empty_like(u_c)
+    vpost = torch.empty_like(u_c) if want_states else None
+    wout = torch.empty_like(u_c) if want_states else None
+    ckv = ckw = None
+    if needs_grad:
+        ckv = torch.empty((_n_tiles(T), cols), dtype=torch.float32, device=dev)
+        ckw = torch.empty_like(ckv)
+    v_last = torch.empty(shape, dtype=torch.float32, device=dev)
+    w_last = torch.empty_like(v_last)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_plif_rf_fwd(
+            _lib.ptr(beta_c), _lib.ptr(omega_c), _lib.ptr(u_c), _lib.ptr(vth_c), _lib.ptr(v0), _lib.ptr(w0),
+            _lib.ptr(spike), None, _lib.ptr(vpost), _lib.ptr(wout), _lib.ptr(ckv), _lib.ptr(ckw),
+            _lib.ptr(v_last), _lib.ptr(w_last), T, cols, _lib.dtype_code(dt), CKPT_INTERVAL,
+            _lib.stream_ptr(dev)), "nsb_plif_rf_fwd")
+    if needs_grad:
+        ctx.save_for_backward(beta_c, omega_c, u_c, vth_c, ckv, ckw)
+    ctx.alpha = float(alpha)
+    ctx.in_dtypes = tuple(t.dtype for t in (beta, omega, u, v_th, v_init, w_init))
+    ctx.state_shapes = (v_init.shape, w_init.shape)
+    cast = (lambda t: None if t is None else t.to(out_dtype)) if spike.dtype != out_dtype else (lambda t: t)
+    return cast(spike), cast(vpost), cast(wout), v_last, w_last
+
+
+def _rf_backward(ctx, grad_spike, grad_V_post):
+    beta_c, omega_c, u_c, vth_c, ckv, ckw = ctx.saved_tensors
+    dt, dev = u_c.dtype, u_c.device
+    T, cols = u_c.shape[0], _cols(u_c)
+    if grad_spike is None:
+        grad_spike = torch.zeros_like(u_c)
+    gs = _grad_stream(grad_spike, u_c, dt)
+    gv = _grad_stream(grad_V_post, u_c, dt)
+    g_beta, g_omega, g_u, g_vth = (torch.empty_like(u_c) for _ in range(4))
+    g_v0 = torch.empty(u_c.shape[1:], dtype=torch.float32, device=dev)
+    g_w0 = torch.empty_like(g_v0)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_plif_rf_bwd(
+            _lib.ptr(beta_c), _lib.ptr(omega_c), _lib.ptr(u_c), _lib.ptr(vth_c), _lib.ptr(ckv),
+            _lib.ptr(ckw), _lib.ptr(gs), _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_omega), _lib.ptr(g_u),
+            _lib.ptr(g_vth), _lib.ptr(g_v0), _lib.ptr(g_w0), T, cols, _lib.dtype_code(dt), CKPT_INTERVAL,
+            ctx_surrogate(ctx), ctx.alpha, _lib.stream_ptr(dev)), "nsb_plif_rf_bwd")
+    db, do, du, dth, dv, dw = ctx.in_dtypes
+    return (g_beta.to(db), g_omega.to(do), g_u.to(du), g_vth.to(dth),
+            g_v0.to(dv).reshape(ctx.state_shapes[0]), g_w0.to(dw).reshape(ctx.state_shapes[1]), None)
+
+
+class PLIFRFScan(torch.autograd.Function):
+    """Resonate-and-fire PLIF scan returning ``(spike, V_post, W)``; contract of the
+    reference's ``_TritonRFPLIFForward`` (atomic_ops/parallel_scan.py:1071-1148). A
+    gradient arriving for ``W`` is ignored, as in the reference (:1114)."""
+
+    @staticmethod
+    def forward(ctx, beta, omega, u, v_th, v_init, w_init, alpha):
+        spike, vpost, wout, _, _ = _rf_forward(ctx, beta, omega, u, v_th, v_init, w_init, alpha, True)
+        return spike, vpost, wout
+
+    @staticmethod
+    def backward(ctx, grad_spike, grad_V_post, _grad_W):
+        return _rf_backward(ctx, grad_spike, grad_V_post)
+
+
+class PLIFRFRecomputeScan(torch.autograd.Function):
+    """Resonate-and-fire PLIF scan returning ``(spike, V_last, W_last)``; contract of
+    the reference's ``_TritonRFPLIFRecompute`` (:1150-1233). Gradients arriving for the
+    final states are ignored (:1203); grad_u and grad_v_th are new tensors, not the
+    saved inputs overwritten in place (:1232-1233)."""
+
+    @staticmethod
+    def forward(ctx, beta, omega, u, v_th, v_init, w_init, alpha):
+        spike, _, _, v_last, w_last = _rf_forward(ctx, beta, omega, u, v_th, v_init, w_init, alpha, False)
+        return spike, v_last.to(v_init.dtype), w_last.to(w_init.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_spike, _gv, _gw):
+        return _rf_backward(ctx, grad_spike, None)
+
+
 # Names the reference's callers import (snn_block.py, snn_ffn.py, test_recompute.py ...).
+_TritonRFPLIFForward = PLIFRFScan
+_TritonRFPLIFRecompute = PLIFRFRecomputeScan
 _TritonPLIFForward = PLIFSelectiveScan
 _TritonPLIFRowParamForward = PLIFRowParamScan
 _TritonPLIFRowParamRecompute = PLIFRowParamRecomputeScan
@@ -404,6 +498,27 @@ def plif_rowparam_forward_recompute(beta_row, u, v_th_row, v_init, alpha: float)
     """Reference: atomic_ops/parallel_scan.py:1499-1535. Returns ``(spike, V_last)``."""
     beta_row, v_th_row, v_init = _rows(u, beta_row, v_th_row, v_init)
     return PLIFRowParamRecomputeScan.apply(beta_row, u, v_th_row, v_init, alpha)
+
+
+def _rf_apply(fn, beta, omega, u, v_th, v_init, w_init, surrogate_function):
+    if surrogate_function is None:
+        with torch.no_grad():
+            return fn.apply(beta, omega, u, v_th, v_init, w_init, 0.0)
+    alpha, kind = _alpha_and_kind(surrogate_function)
+    if kind != _lib.SURR_SIGMOID:
+        raise NSBError("the resonate-and-fire scan supports the Sigmoid surrogate only")
+    return fn.apply(beta, omega, u, v_th, v_init, w_init, alpha)
+
+
+def rf_plif_parallel_forward(beta, omega, u, v_th, v_init, w_init, surrogate_function=None):
+    """Reference: atomic_ops/parallel_scan.py:1610-1683. Returns ``(spike, V_post, W)``.
+    With ``surrogate_function=None`` the outputs carry no gradient."""
+    return _rf_apply(PLIFRFScan, beta, omega, u, v_th, v_init, w_init, surrogate_function)
+
+
+def rf_plif_parallel_forward_recompute(beta, omega, u, v_th, v_init, w_init, surrogate_function=None):
+    """Reference: atomic_ops/parallel_scan.py:1690-1726. Returns ``(spike, V_last, W_last)``."""
+    return _rf_apply(PLIFRFRecomputeScan, beta, omega, u, v_th, v_init, w_init, surrogate_function)
 
 
 def plif_fixed_param_forward(beta, u, v_th, v_init, max_iter: int = 3, surrogate_function=None):

@@ -168,6 +168,33 @@ def plif_rowparam_bwd(beta_row, u, vth_row, v_init, g_spike, g_vpost, alpha,
     return gb, gu, gt, gv
 
 
+def plif_rf_fwd(beta, omega, u, vth, v_init, w_init, want_states=True):
+    """Resonate-and-fire scan: (spike, V_post or None, W or None, V_last, W_last)."""
+    beta, omega, u, vth, v_init, w_init = map(_f32, (beta, omega, u, vth, v_init, w_init))
+    T, cols = _tc(u)
+    spike = np.empty_like(u)
+    vpost = np.empty_like(u) if want_states else None
+    wout = np.empty_like(u) if want_states else None
+    vlast, wlast = np.empty_like(v_init), np.empty_like(w_init)
+    lib().orc_plif_rf_fwd(_p(beta), _p(omega), _p(u), _p(vth), _p(v_init), _p(w_init), _p(spike),
+                          _p(vpost), _p(wout), _p(vlast), _p(wlast), _i64(T), _i64(cols))
+    return spike, vpost, wout, vlast, wlast
+
+
+def plif_rf_bwd(beta, omega, u, vth, v_init, w_init, g_spike, g_vpost, alpha, kind=SURR_SIGMOID):
+    """(g_beta, g_omega, g_u, g_vth, g_vinit, g_winit)."""
+    beta, omega, u, vth, v_init, w_init = map(_f32, (beta, omega, u, vth, v_init, w_init))
+    g_spike = None if g_spike is None else _f32(g_spike)
+    g_vpost = None if g_vpost is None else _f32(g_vpost)
+    T, cols = _tc(u)
+    gb, go, gu, gt = (np.empty_like(u) for _ in range(4))
+    gv, gw = np.empty_like(v_init), np.empty_like(w_init)
+    lib().orc_plif_rf_bwd(_p(beta), _p(omega), _p(u), _p(vth), _p(v_init), _p(w_init), _p(g_spike),
+                          _p(g_vpost), _p(gb), _p(go), _p(gu), _p(gt), _p(gv), _p(gw), _i64(T),
+                          _i64(cols), ctypes.c_double(alpha), ctypes.c_int(kind))
+    return gb, go, gu, gt, gv, gw
+
+
 # ---------------------------------------------------------------- codec
 
 

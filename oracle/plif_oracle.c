@@ -307,6 +307,124 @@ void orc_plif_rowparam_bwd(const float *beta_row, const float *u,
 }
 
 /* ------------------------------------------------------------------ */
+/* Resonate-and-fire (second-order) scan.                              */
+/* Forward: the reference's executable CPU loop,                       */
+/* atomic_ops/parallel_scan.py:1667-1677:                              */
+/*   v_pre = beta*v - omega*w + u     ((beta*v) - (omega*w)) + u       */
+/*   w_new = omega*v + beta*w         only V is reset, W is not        */
+/* vpost / wout / spike may be NULL.                                   */
+/* ------------------------------------------------------------------ */
+void orc_plif_rf_fwd(const float *beta, const float *omega, const float *u,
+                     const float *vth, const float *v_init, const float *w_init,
+                     float *spike, float *vpost, float *wout, float *vlast,
+                     float *wlast, int64_t T, int64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (int64_t c0 = 0; c0 < cols; c0 += COL_BLOCK) {
+    int64_t n = cols - c0 < COL_BLOCK ? cols - c0 : COL_BLOCK;
+    float v[COL_BLOCK], w[COL_BLOCK];
+    for (int64_t j = 0; j < n; ++j) {
+      v[j] = v_init[c0 + j];
+      w[j] = w_init[c0 + j];
+    }
+    for (int64_t k = 0; k < T; ++k) {
+      const int64_t off = k * cols + c0;
+      for (int64_t j = 0; j < n; ++j) {
+        float bv = beta[off + j] * v[j];
+        float ow = omega[off + j] * w[j];
+        float d = bv - ow;
+        float vpre = d + u[off + j];
+        float ov = omega[off + j] * v[j];
+        float bw = beta[off + j] * w[j];
+        float wn = ov + bw;
+        float s = vpre >= vth[off + j] ? 1.0f : 0.0f;
+        float vs = vth[off + j] * s;
+        v[j] = vpre - vs;
+        w[j] = wn;
+        if (spike) spike[off + j] = s;
+        if (vpost) vpost[off + j] = v[j];
+        if (wout) wout[off + j] = w[j];
+      }
+    }
+    for (int64_t j = 0; j < n; ++j) {
+      if (vlast) vlast[c0 + j] = v[j];
+      if (wlast) wlast[c0 + j] = w[j];
+    }
+  }
+}
+
+/* Reverse pass of the resonate-and-fire scan with the two coupled adjoint   */
+/* accumulators of atomic_ops/parallel_scan.py:835-848 (hard spike constant  */
+/* in the reset path; a gradient arriving for W is ignored, as :1114 does).  */
+void orc_plif_rf_bwd(const float *beta, const float *omega, const float *u,
+                     const float *vth, const float *v_init, const float *w_init,
+                     const float *g_spike, const float *g_vpost, float *g_beta,
+                     float *g_omega, float *g_u, float *g_vth, float *g_vinit,
+                     float *g_winit, int64_t T, int64_t cols, double a, int kind) {
+#define RF_BLOCK 32
+#pragma omp parallel
+  {
+    const size_t tt = (size_t)(T > 0 ? T : 1) * RF_BLOCK;
+    float *vp = (float *)__builtin_malloc(sizeof(float) * tt * 3);
+    float *wp = vp + tt, *xs = wp + tt;
+#pragma omp for schedule(dynamic, 4)
+    for (int64_t c0 = 0; c0 < cols; c0 += RF_BLOCK) {
+      const int64_t n = cols - c0 < RF_BLOCK ? cols - c0 : RF_BLOCK;
+      float v[RF_BLOCK], w[RF_BLOCK];
+      double av[RF_BLOCK], aw[RF_BLOCK];
+      for (int64_t j = 0; j < n; ++j) {
+        v[j] = v_init[c0 + j];
+        w[j] = w_init[c0 + j];
+      }
+      for (int64_t k = 0; k < T; ++k) {
+        const int64_t o = k * cols + c0;
+        for (int64_t j = 0; j < n; ++j) {
+          float bv = beta[o + j] * v[j];
+          float ow = omega[o + j] * w[j];
+          float d = bv - ow;
+          float vpre = d + u[o + j];
+          float ov = omega[o + j] * v[j];
+          float bw = beta[o + j] * w[j];
+          vp[k * RF_BLOCK + j] = v[j];
+          wp[k * RF_BLOCK + j] = w[j];
+          xs[k * RF_BLOCK + j] = vpre - vth[o + j];
+          float s = vpre >= vth[o + j] ? 1.0f : 0.0f;
+          float vs = vth[o + j] * s;
+          v[j] = vpre - vs;
+          w[j] = ov + bw;
+        }
+      }
+      for (int64_t j = 0; j < n; ++j) av[j] = aw[j] = 0.0;
+      for (int64_t k = T - 1; k >= 0; --k) {
+        const int64_t o = k * cols + c0;
+        for (int64_t j = 0; j < n; ++j) {
+          const double x = (double)xs[k * RF_BLOCK + j];
+          const double s = x >= 0.0 ? 1.0 : 0.0;
+          const double sg = surr_grad(x, a, kind);
+          const double gs = g_spike ? (double)g_spike[o + j] : 0.0;
+          const double tv = (g_vpost ? (double)g_vpost[o + j] : 0.0) + av[j];
+          const double tw = aw[j];
+          const double gpre = gs * sg + tv;
+          const double vpr = (double)vp[k * RF_BLOCK + j], wpr = (double)wp[k * RF_BLOCK + j];
+          const double b = (double)beta[o + j], om = (double)omega[o + j];
+          if (g_beta) g_beta[o + j] = (float)(gpre * vpr + tw * wpr);
+          if (g_omega) g_omega[o + j] = (float)(tw * vpr - gpre * wpr);
+          if (g_u) g_u[o + j] = (float)gpre;
+          if (g_vth) g_vth[o + j] = (float)(-gs * sg - tv * s);
+          av[j] = gpre * b + tw * om;
+          aw[j] = tw * b - gpre * om;
+        }
+      }
+      for (int64_t j = 0; j < n; ++j) {
+        if (g_vinit) g_vinit[c0 + j] = (float)av[j];
+        if (g_winit) g_winit[c0 + j] = (float)aw[j];
+      }
+    }
+    __builtin_free(vp);
+  }
+#undef RF_BLOCK
+}
+
+/* ------------------------------------------------------------------ */
 /* FP16 boundary codec.                                                */
 /* ------------------------------------------------------------------ */
 

@@ -189,6 +189,39 @@ def main():
         alpha=np.float64(4.0), spike=S, vpost=V, g_beta_row=beta_row.grad, g_u=u.grad,
         g_vth_row=vth_row.grad, g_vinit=v0.grad)
 
+    # ---- resonate-and-fire scan: forward from the reference's CPU loop
+    # (rf_plif_parallel_forward, surrogate None); backward from autograd through the
+    # same recurrence with the hard spike detached in the reset, which is what the
+    # reference's fused kernel computes (atomic_ops/parallel_scan.py:835-848).
+    # Inputs as test_recompute.py:87-94 draws them, smaller (seed 42).
+    torch.manual_seed(42)
+    T, B, D = 48, 2, 40
+    beta = torch.sigmoid(torch.randn(T, B, D))
+    omega = torch.abs(torch.randn(T, B, D)) * 0.3
+    u = torch.randn(T, B, D)
+    vth = torch.abs(torch.randn(T, B, D)) + 0.1
+    v0, w0 = torch.randn(B, D), torch.randn(B, D) * 0.1
+    s, V, W = ps.rf_plif_parallel_forward(beta, omega, u, vth, v0, w0, None)
+    leaves = [t.clone().requires_grad_() for t in (beta, omega, u, vth, v0, w0)]
+    b_, o_, u_, t_, v, w = leaves
+    S_l, V_l = [], []
+    for k in range(T):
+        v_pre = b_[k] * v - o_[k] * w + u_[k]
+        w_new = o_[k] * v + b_[k] * w
+        sp = (v_pre.detach() >= t_[k].detach()).to(v_pre.dtype)
+        S_l.append(SigmoidSurrogate.apply(v_pre - t_[k], 4.0))
+        v = v_pre - t_[k] * sp
+        w = w_new
+        V_l.append(v)
+    S2, V2 = torch.stack(S_l), torch.stack(V_l)
+    assert torch.equal(S2.detach(), s) and torch.equal(V2.detach(), V)
+    gS = torch.randn(T, B, D)
+    gV = torch.randn(T, B, D) * 0.3
+    ((S2 * gS).sum() + (V2 * gV).sum()).backward()
+    npz("rf_a", beta=beta, omega=omega, u=u, vth=vth, v_init=v0, w_init=w0, spike=s, vpost=V, w=W,
+        g_spike=gS, g_vpost=gV, alpha=np.float64(4.0),
+        **{f"g_{n}": t.grad for n, t in zip(("beta", "omega", "u", "vth", "vinit", "winit"), leaves)})
+
     # ---- codec: the inputs of test_binary_residual.py (seed 42) + edge values
     torch.manual_seed(42)
     B, S_, D = 2, 4, 8

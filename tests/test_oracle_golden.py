@@ -120,3 +120,19 @@ def test_lateral_inhibition(golden):
     gx, gg = orc.li_bwd(g["g_out"], g["x"], g["gain"], float(g["eps"]))
     assert rel_err(gx, g["g_x"]) < TOL
     assert rel_err(gg, g["g_gain"]) < TOL
+
+
+def test_rf_scan(golden):
+    g = golden("rf_a")
+    s, v, w, vl, wl = orc.plif_rf_fwd(g["beta"], g["omega"], g["u"], g["vth"], g["v_init"], g["w_init"])
+    assert np.array_equal(s, g["spike"]) and np.array_equal(v, g["vpost"]) and np.array_equal(w, g["w"])
+    assert np.array_equal(vl, g["vpost"][-1]) and np.array_equal(wl, g["w"][-1])
+    out = orc.plif_rf_bwd(g["beta"], g["omega"], g["u"], g["vth"], g["v_init"], g["w_init"],
+                          g["g_spike"], g["g_vpost"], float(g["alpha"]))
+    for mine, ref in zip(out, ("g_beta", "g_omega", "g_u", "g_vth", "g_vinit", "g_winit")):
+        assert rel_err(mine, g[ref]) < TOL, ref
+    # omega = 0, w_init = 0 is the first-order scan
+    z = np.zeros_like(g["u"])
+    s1, v1, _, _, _ = orc.plif_rf_fwd(g["beta"], z, g["u"], g["vth"], g["v_init"], z[0])
+    s2, v2, _ = orc.plif_selective_fwd(g["beta"], g["u"], g["vth"], g["v_init"])
+    assert np.array_equal(s1, s2) and np.array_equal(v1, v2)
