@@ -44,6 +44,9 @@ WORKLOADS = {
     "c2": (32, 8192, 6144),
     "c2-short": (32, 512, 6144),   # same grid, 1/16 of the time steps (2.8 GB): profiler captures
     "c0": (2, 1024, 768),
+    # the second-order resonate-and-fire scan of the hidden neurons at the headline shape
+    # (sigmoid surrogate alpha=4, u-form with an omega stream): same byte counts as c2
+    "rf": (32, 8192, 6144),
 }
 # Secondary (forward-only, bit-packed spikes) workloads; not the default bench line.
 #   c1      row-parameter scan, per-channel beta / V_th, B=8 on every GPU
@@ -125,9 +128,10 @@ def make_inputs(B, T, D, device, seed):
 class ScanStep:
     """Pre-allocated forward+backward through the C ABI (device-resident buffers)."""
 
-    def __init__(self, inp, B, T, D):
+    def __init__(self, inp, B, T, D, rf=False):
         import torch
         from neuronspark_b200 import _lib, parallel_scan as ps
+        self.rf = rf
         self._lib = _lib
         self.L = _lib.lib()
         self.inp = inp
@@ -141,11 +145,23 @@ class ScanStep:
         self.v_last = torch.empty((B, D), dtype=torch.float32, device=dev)
         self.g_beta, self.g_cur, self.g_gain, self.g_vth = (torch.empty((T, B, D), **bf) for _ in range(4))
         self.g_v0 = torch.empty((B, D), dtype=torch.float32, device=dev)
+        if rf:
+            self.ckpt_w = torch.empty_like(self.ckpt)
+            self.w_last, self.g_w0, self.w0 = (torch.zeros((B, D), dtype=torch.float32, device=dev)
+                                               for _ in range(3))
         self.stream = _lib.stream_ptr(dev)
         self.launch_fwd = self.launch_bwd = None
 
     def fwd(self):
         i, p = self.inp, self._lib.ptr
+        if self.rf:  # "gain" doubles as omega (scaled into the stable range by make_inputs' caller)
+            self._lib.check(self.L.nsb_plif_rf_fwd(
+                p(i["beta"]), p(i["gain"]), p(i["cur"]), p(i["vth"]), p(i["v0"]), p(self.w0), p(self.spike),
+                None, None, None, p(self.ckpt), p(self.ckpt_w), p(self.v_last), p(self.w_last), self.T,
+                self.cols, self._lib.BF16, self.C, self.stream), "nsb_plif_rf_fwd")
+            if self.launch_fwd is None:
+                self.launch_fwd = self._lib.last_launch_info()
+            return
         self._lib.check(self.L.nsb_plif_selective_fwd(
             p(i["beta"]), p(i["cur"]), p(i["gain"]), p(i["vth"]), p(i["v0"]), p(self.spike), None, None,
             p(self.ckpt), p(self.v_last), self.T, self.cols, self._lib.BF16, self.C, self.stream),
@@ -155,6 +171,15 @@ class ScanStep:
 
     def bwd(self):
         i, p = self.inp, self._lib.ptr
+        if self.rf:
+            self._lib.check(self.L.nsb_plif_rf_bwd(
+                p(i["beta"]), p(i["gain"]), p(i["cur"]), p(i["vth"]), p(self.ckpt), p(self.ckpt_w),
+                p(i["g_spike"]), None, p(self.g_beta), p(self.g_gain), p(self.g_cur), p(self.g_vth),
+                p(self.g_v0), p(self.g_w0), self.T, self.cols, self._lib.BF16, self.C,
+                self._lib.SURR_SIGMOID, 4.0, self.stream), "nsb_plif_rf_bwd")
+            if self.launch_bwd is None:
+                self.launch_bwd = self._lib.last_launch_info()
+            return
         self._lib.check(self.L.nsb_plif_selective_bwd(
             p(i["beta"]), p(i["cur"]), p(i["gain"]), p(i["vth"]), p(self.ckpt), p(i["g_spike"]), None,
             p(self.g_beta), p(self.g_cur), p(self.g_gain), p(self.g_vth), p(self.g_v0), self.T,
@@ -474,7 +499,19 @@ def main():
 
     B, T, D = WORKLOADS[args.workload]
     inp = make_inputs(B, T, D, dev, 1234 + rank)
-    step = ScanStep(inp, B, T, D)
+    is_rf = args.workload == "rf"
+    if is_rf:
+        # omega = 0.3*|gain|, then the reference's stability rescale sqrt(beta^2+omega^2) <= 0.999
+        # (test_recompute.py:91-96); done in slices to bound temporaries
+        for t0 in range(0, T, max(1, T // 16)):
+            sl = slice(t0, t0 + max(1, T // 16))
+            b, o = inp["beta"][sl].float(), 0.3 * inp["gain"][sl].float().abs()
+            r_sq = b * b + o * o
+            sc = torch.where(r_sq > 0.999 ** 2, 0.999 * torch.rsqrt(r_sq.clamp(min=1e-12)), torch.ones_like(r_sq))
+            inp["beta"][sl] = (b * sc).bfloat16()
+            inp["gain"][sl] = (o * sc).bfloat16()
+        args.no_e2e = True
+    step = ScanStep(inp, B, T, D, rf=is_rf)
     neuron_steps = B * T * D
 
     def barrier():
@@ -578,9 +615,12 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
-                "workload": f"{args.workload}: selective PLIF forward+backward, B={B} per GPU "
-                            f"(global {B * world}), T={T}, D={D}, bf16 streams, fp32 state, atan "
-                            f"surrogate alpha={ALPHA}, grads for I/beta/alpha/V_th/V0",
+                "workload": (f"{args.workload}: selective PLIF forward+backward, B={B} per GPU "
+                             f"(global {B * world}), T={T}, D={D}, bf16 streams, fp32 state, atan "
+                             f"surrogate alpha={ALPHA}, grads for I/beta/alpha/V_th/V0") if not is_rf else
+                            (f"rf: resonate-and-fire PLIF forward+backward, B={B} per GPU, T={T}, D={D}, "
+                             "bf16 streams, fp32 V/W state, sigmoid surrogate alpha=4, grads for "
+                             "beta/omega/u/V_th/V0/W0"),
                 "parallelism": f"batch-sharded x{world}, no collective in the timed region",
                 "l2": "inputs (16 GB per GPU) are far larger than L2; no flush needed",
                 "storage_dtype": "bf16", "ckpt_interval": ps.CKPT_INTERVAL,
@@ -606,7 +646,7 @@ def main():
         }
         if e2e is not None:
             line["e2e"] = e2e
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and not is_rf:
             line["cpu_baseline"] = cpu_baseline(B, T, D)
         print(json.dumps(line), flush=True)
     if world > 1:
