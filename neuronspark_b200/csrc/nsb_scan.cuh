@@ -317,6 +317,24 @@ __device__ __forceinline__ void plif_step(float (&v)[V], const float (&beta)[V],
   }
 }
 
+// Moves bit m of the low 32/V bits of x to bit V*m (V = 1, 2 or 4).
+template <int V>
+__device__ __forceinline__ uint32_t spread_bits(uint32_t x) {
+  if constexpr (V == 2) {
+    x &= 0xFFFFu;
+    x = (x | (x << 8)) & 0x00FF00FFu;
+    x = (x | (x << 4)) & 0x0F0F0F0Fu;
+    x = (x | (x << 2)) & 0x33333333u;
+    x = (x | (x << 1)) & 0x55555555u;
+  } else if constexpr (V == 4) {
+    x &= 0xFFu;
+    x = (x | (x << 12)) & 0x000F000Fu;
+    x = (x | (x << 6)) & 0x03030303u;
+    x = (x | (x << 3)) & 0x11111111u;
+  }
+  return x;
+}
+
 // Resonate-and-fire step: v_pre = (beta*v - omega*w) + u, w' = omega*v + beta*w, every
 // product and sum rounded separately; only V is reset.
 template <int V>
@@ -353,7 +371,13 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
   constexpr int TILE_ELEMS = C * 32 * V;
   constexpr uint32_t TILE_BYTES = TILE_ELEMS * sizeof(ST);
   constexpr uint32_t STAGE_BYTES = NS * TILE_BYTES;
-  constexpr bool VEC = !PACKED && TMA;  // a thread's V columns are contiguous and aligned
+  constexpr bool VEC = TMA;  // a thread's V columns are contiguous and aligned
+  // Dense spikes leave through shared memory + TMA only in the kernels built for them; a
+  // bit-packing kernel that is also asked for dense spikes writes them from registers.
+  constexpr bool DENSE_TMA = VEC && !PACKED;
+  // Bit packing: a 32-column word belongs to the 32/V lanes that own those columns.
+  constexpr int G = 32 / V;
+  constexpr int NSLOT = (C + G - 1) / G;
   extern __shared__ __align__(128) uint8_t smem_raw[];
 
   const int lane = threadIdx.x & 31;
@@ -367,7 +391,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
   float v[V], w[V], brow[V], trow[V];
 #pragma unroll
   for (int j = 0; j < V; ++j) {
-    colj[j] = PACKED ? col0 + 32 * j + lane : col0 + V * lane + j;
+    colj[j] = col0 + V * lane + j;
     valid[j] = colj[j] < p.cols;
     v[j] = valid[j] ? p.v_init[colj[j]] : 0.0f;
     w[j] = (MODE == MODE_RF && valid[j]) ? p.w_init[colj[j]] : 0.0f;
@@ -423,9 +447,6 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
   auto fetch = [&](int stream, int k, float (&out)[V]) {
     if constexpr (VEC) {
       IO::load(sp + stream * TILE_ELEMS + k * (32 * V), out);
-    } else if constexpr (TMA) {
-#pragma unroll
-      for (int j = 0; j < V; ++j) out[j] = E::to_f32(sp[stream * TILE_ELEMS + k * (32 * V) + 32 * j]);
     } else {
 #pragma unroll
       for (int j = 0; j < V; ++j) out[j] = E::to_f32(regs[(stream * KB + (k % KB)) * V + j]);
@@ -443,12 +464,14 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     // On the vector path dense spikes are written over the consumed drive tile in
     // shared memory and leave through one TMA store per tile (which also clips the
     // ragged edges), so the step loop carries no global address arithmetic for them.
-    ST* o_spike = (!VEC && p.spike) ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
+    ST* o_spike = (!DENSE_TMA && p.spike) ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
     ST* o_vpost = p.vpost ? static_cast<ST*>(p.vpost) + t0 * row_elems + colj[0] : nullptr;
     ST* o_wout = (MODE == MODE_RF && p.w_out) ? static_cast<ST*>(p.w_out) + t0 * row_elems + colj[0] : nullptr;
-    uint32_t words[V];
+    uint32_t keep[NSLOT][V];  // raw ballots of the step(s) this lane is responsible for
 #pragma unroll
-    for (int j = 0; j < V; ++j) words[j] = 0u;
+    for (int q = 0; q < NSLOT; ++q)
+#pragma unroll
+      for (int j = 0; j < V; ++j) keep[q][j] = 0u;
 #pragma unroll
     for (int k = 0; k < C; ++k) {
       if (!FULL && k >= nsteps) break;
@@ -493,8 +516,9 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
       }
 
       if constexpr (VEC) {
-        IO::store_spikes(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + k * (32 * V), sp_);
+        if constexpr (DENSE_TMA) IO::store_spikes(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + k * (32 * V), sp_);
         // a thread's V columns are all valid or all invalid
+        if (!DENSE_TMA && o_spike && valid[0]) IO::store_spikes(o_spike + (size_t)k * row_elems, sp_);
         if (o_vpost && valid[0]) IO::store(o_vpost + (size_t)k * row_elems, v);
         if (MODE == MODE_RF && o_wout && valid[0]) IO::store(o_wout + (size_t)k * row_elems, w);
       } else {
@@ -509,19 +533,28 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
         }
       }
       if constexpr (PACKED) {
+        // one ballot per lane slot j: bit l = spike of column col0 + V*l + j. Lane (k mod G) of
+        // every group of G lanes keeps the V ballots of step k and interleaves them into the
+        // word it stores once the tile is done.
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const uint32_t w = __ballot_sync(0xffffffffu, sp_[j] && valid[j]);
-          if (lane == k) words[j] = w;
+          const uint32_t b = __ballot_sync(0xffffffffu, sp_[j] && valid[j]);
+          if ((lane % G) == (k % G)) keep[k / G][j] = b;
         }
       }
     }
     if constexpr (PACKED) {
-      if (p.packed && lane < nsteps) {
+      if (p.packed) {
+        const long long widx = col0 / 32 + lane / G;
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const long long widx = col0 / 32 + j;
-          if (widx < p.words_per_row) p.packed[(t0 + lane) * p.words_per_row + widx] = words[j];
+        for (int q = 0; q < NSLOT; ++q) {
+          const int kk = q * G + (lane % G);
+          // columns 32*w .. 32*w+31 (w = lane / G) are lanes G*w .. G*w+G-1: bit (V*m + j) of the
+          // word is bit (G*w + m) of ballot j
+          uint32_t word = 0u;
+#pragma unroll
+          for (int j = 0; j < V; ++j) word |= spread_bits<V>(keep[q][j] >> (G * (lane / G) % 32)) << j;
+          if (kk < nsteps && widx < p.words_per_row) p.packed[(t0 + kk) * p.words_per_row + widx] = word;
         }
       }
     }
@@ -536,7 +569,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
         failed = true;
         break;
       }
-      sp = reinterpret_cast<const ST*>(data_ptr + (size_t)s_idx * STAGE_BYTES) + (PACKED ? lane : V * lane);
+      sp = reinterpret_cast<const ST*>(data_ptr + (size_t)s_idx * STAGE_BYTES) + V * lane;
     }
     if (p.ckpt) {
       if constexpr (VEC) {
@@ -557,7 +590,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
       tile(std::false_type{}, nsteps);
 
     if constexpr (TMA) {
-      const bool store_spikes = VEC && p.spike != nullptr;
+      const bool store_spikes = DENSE_TMA && p.spike != nullptr;
       if (store_spikes) proxy_async_fence();  // make this lane's shared-memory writes visible to TMA
       __syncwarp();
       if (lane == 0) {
