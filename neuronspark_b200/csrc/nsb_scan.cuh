@@ -1230,8 +1230,7 @@ int scan_bwd_dispatch(const BwdArgs& a) {
     PlanQuery q;
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
     q.nstreams = (a.mode == MODE_ROW ? 1 : ((a.mode == MODE_AI || a.mode == MODE_RF) ? 4 : 3)) + 1 + (a.g_vpost ? 1 : 0);
-    // the resonate-and-fire backward keeps three per-step arrays in registers: 2 lanes at most
-    q.tile = C; q.backward = true; q.max_lanes = (C == 8 && a.mode != MODE_RF) ? 4 : 2;
+    q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : 2;
     plan = plan_scan(dev, q, tune);
   }
   const int V = plan.lanes;
@@ -1245,7 +1244,8 @@ int scan_bwd_dispatch(const BwdArgs& a) {
   NSB_BWD_CASE(MODE_, SURR_, 2, 16)
 #define NSB_BWD_CASES_RF(SURR_)                                                         \
   NSB_BWD_CASE(MODE_RF, SURR_, 1, 8) NSB_BWD_CASE(MODE_RF, SURR_, 2, 8)                \
-  NSB_BWD_CASE(MODE_RF, SURR_, 1, 16) NSB_BWD_CASE(MODE_RF, SURR_, 2, 16)
+  NSB_BWD_CASE(MODE_RF, SURR_, 4, 8) NSB_BWD_CASE(MODE_RF, SURR_, 1, 16)               \
+  NSB_BWD_CASE(MODE_RF, SURR_, 2, 16)
   if (tma) {
     NSB_BWD_CASES_V(MODE_U, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_U, NSB_SURR_ATAN)
     NSB_BWD_CASES_V(MODE_AI, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_AI, NSB_SURR_ATAN)

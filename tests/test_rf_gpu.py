@@ -118,6 +118,18 @@ def test_rf_paths_agree(lanes, stages, wpc):
     assert nsb.last_launch_info()["used_tma"] == 1
     for a, b in zip(ref, got):
         assert torch.equal(a, b)
+    # backward: the TMA path at this lane count against the direct path
+    gS = torch.randn(70, 2, 384, device=DEV).bfloat16()
+    grads = []
+    for direct in (True, False):
+        nsb.set_tuning(warps_per_cta=wpc, stages=stages, lanes_per_thread=lanes, force_direct=direct)
+        ins = [t.clone().requires_grad_() for t in (beta, omega, u, vth, v0, w0)]
+        s_, _, _ = ps.rf_plif_parallel_forward_recompute(*ins, _Sigmoid(4.0))
+        s_.backward(gS)
+        assert nsb.last_launch_info()["used_tma"] == (0 if direct else 1)
+        grads.append([t.grad for t in ins])
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)
 
 
 def test_rf_with_zero_omega_is_the_first_order_scan():
