@@ -3,7 +3,7 @@
 //
 // Frames are [S*16, B, D] (frame s*16+k = bit 15-k of the IEEE half pattern of
 // token s: sign, E4..E0, M9..M0), values are [B, S, D]. One thread owns VE
-// consecutive channels of one (b, s) token; a warp therefore touches 32*VE
+// consecutive channels of one (b, s) token (VE up to 16 bytes' worth); a warp therefore touches 32*VE
 // consecutive elements of each of the 16 frame rows, so every access is a full
 // coalesced line. The kernels are pure streaming: the 16 frame reads (or
 // writes) of a thread are independent and all in flight together.
@@ -256,6 +256,15 @@ bool vec_ok(long long D, int ve, size_t elem, std::initializer_list<const void*>
 
 bool dtype_ok(int d) { return d == NSB_F32 || d == NSB_BF16 || d == NSB_F16; }
 
+// Widest vector (in elements) that D and every pointer allow, at most 16 bytes
+// (MAXB = largest vector in bytes the kernel's register budget takes).
+template <typename T>
+int pick_ve(long long D, std::initializer_list<const void*> ptrs, int maxb) {
+  for (int ve = maxb / (int)sizeof(T); ve > 1; ve >>= 1)
+    if (vec_ok(D, ve, sizeof(T), ptrs)) return ve;
+  return 1;
+}
+
 // Calls f.template operator()<T>() with the element type of `dtype`.
 template <typename F>
 int with_dtype(int dtype, F&& f) {
@@ -288,35 +297,46 @@ int nsb_fp16_encode(const void* values, void* frames, int64_t B, int64_t S, int6
       using TO = decltype(to);
       if (reinterpret_cast<uintptr_t>(values) % sizeof(TI) || reinterpret_cast<uintptr_t>(frames) % sizeof(TO))
         return NSB_ERR_INVALID_ARG;
-      const bool v2 = D % 2 == 0 && reinterpret_cast<uintptr_t>(values) % (2 * sizeof(TI)) == 0 &&
-                      reinterpret_cast<uintptr_t>(frames) % (2 * sizeof(TO)) == 0;
-      const long long items = (long long)B * S * (v2 ? D / 2 : D);
+      int ve = 1;
+      for (int c = 8; c > 1; c >>= 1) {
+        if (c * sizeof(TI) > 16 || c * sizeof(TO) > 16) continue;
+        if (D % c == 0 && reinterpret_cast<uintptr_t>(values) % (c * sizeof(TI)) == 0 &&
+            reinterpret_cast<uintptr_t>(frames) % (c * sizeof(TO)) == 0) {
+          ve = c;
+          break;
+        }
+      }
+      const long long items = (long long)B * S * (D / ve);
       const int grid = grid_for(items, kThreads);
       if (grid == 0) return NSB_ERR_CUDA;
-      if (v2)
-        encode_kernel<TI, TO, 2><<<grid, kThreads, 0, st>>>(static_cast<const TI*>(values),
-                                                            static_cast<TO*>(frames), B, S, D);
-      else
-        encode_kernel<TI, TO, 1><<<grid, kThreads, 0, st>>>(static_cast<const TI*>(values),
-                                                            static_cast<TO*>(frames), B, S, D);
+      const TI* vp = static_cast<const TI*>(values);
+      TO* fp = static_cast<TO*>(frames);
+      switch (ve) {
+        case 8: encode_kernel<TI, TO, (sizeof(TI) == 2 && sizeof(TO) == 2) ? 8 : 1><<<grid, kThreads, 0, st>>>(vp, fp, B, S, D); break;
+        case 4: encode_kernel<TI, TO, 4><<<grid, kThreads, 0, st>>>(vp, fp, B, S, D); break;
+        case 2: encode_kernel<TI, TO, 2><<<grid, kThreads, 0, st>>>(vp, fp, B, S, D); break;
+        default: encode_kernel<TI, TO, 1><<<grid, kThreads, 0, st>>>(vp, fp, B, S, D); break;
+      }
       NSB_CUDA_TRY(cudaGetLastError(), "launch encode_kernel");
       return NSB_OK;
     });
   });
 }
 
-#define NSB_CODEC_LAUNCH(KERNEL, WHERE, PTRS, ...)                                         \
+#define NSB_CODEC_LAUNCH(KERNEL, WHERE, MAXB, PTRS, ...)                                   \
   return with_dtype(dtype, [&](auto t) {                                                   \
     using T = decltype(t);                                                                 \
     if (!vec_ok(D, 1, sizeof(T), PTRS)) return NSB_ERR_INVALID_ARG;                        \
-    const bool v2 = vec_ok(D, 2, sizeof(T), PTRS);                                         \
-    const long long items = (long long)B * S * (v2 ? D / 2 : D);                           \
+    const int ve = pick_ve<T>(D, PTRS, MAXB);                                              \
+    const long long items = (long long)B * S * (D / ve);                                   \
     const int grid = grid_for(items, kThreads);                                            \
     if (grid == 0) return NSB_ERR_CUDA;                                                    \
-    if (v2)                                                                                \
-      KERNEL<T, 2><<<grid, kThreads, 0, st>>>(__VA_ARGS__, B, S, D);                       \
-    else                                                                                   \
-      KERNEL<T, 1><<<grid, kThreads, 0, st>>>(__VA_ARGS__, B, S, D);                       \
+    switch (ve) {                                                                          \
+      case 8: KERNEL<T, (sizeof(T) == 2 ? 8 : 1)><<<grid, kThreads, 0, st>>>(__VA_ARGS__, B, S, D); break; \
+      case 4: KERNEL<T, 4><<<grid, kThreads, 0, st>>>(__VA_ARGS__, B, S, D); break;        \
+      case 2: KERNEL<T, 2><<<grid, kThreads, 0, st>>>(__VA_ARGS__, B, S, D); break;        \
+      default: KERNEL<T, 1><<<grid, kThreads, 0, st>>>(__VA_ARGS__, B, S, D); break;       \
+    }                                                                                      \
     NSB_CUDA_TRY(cudaGetLastError(), WHERE);                                               \
     return NSB_OK;                                                                         \
   })
@@ -329,7 +349,7 @@ int nsb_fp16_decode_fwd(const void* frames, void* values, int64_t B, int64_t S, 
   if (B * S * D == 0) return NSB_OK;
   if (!frames || !values) return NSB_ERR_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  NSB_CODEC_LAUNCH(decode_fwd_kernel, "launch decode_fwd_kernel", NSB_PTRS(frames, values),
+  NSB_CODEC_LAUNCH(decode_fwd_kernel, "launch decode_fwd_kernel", 16, NSB_PTRS(frames, values),
                    static_cast<const T*>(frames), static_cast<T*>(values));
 }
 
@@ -339,7 +359,7 @@ int nsb_fp16_decode_bwd(const void* frames, const void* g_values, void* g_frames
   if (B * S * D == 0) return NSB_OK;
   if (!frames || !g_values || !g_frames) return NSB_ERR_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  NSB_CODEC_LAUNCH(decode_bwd_kernel, "launch decode_bwd_kernel", NSB_PTRS(frames, g_values, g_frames),
+  NSB_CODEC_LAUNCH(decode_bwd_kernel, "launch decode_bwd_kernel", 8, NSB_PTRS(frames, g_values, g_frames),
                    static_cast<const T*>(frames), static_cast<const T*>(g_values),
                    static_cast<T*>(g_frames));
 }
@@ -350,7 +370,7 @@ int nsb_binary_residual(const void* frames_a, const void* frames_b, void* frames
   if (B * S * D == 0) return NSB_OK;
   if (!frames_a || !frames_b || !frames_out) return NSB_ERR_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  NSB_CODEC_LAUNCH(residual_kernel, "launch residual_kernel", NSB_PTRS(frames_a, frames_b, frames_out),
+  NSB_CODEC_LAUNCH(residual_kernel, "launch residual_kernel", 8, NSB_PTRS(frames_a, frames_b, frames_out),
                    static_cast<const T*>(frames_a), static_cast<const T*>(frames_b),
                    static_cast<T*>(frames_out));
 }
@@ -361,7 +381,7 @@ int nsb_encode_ste_bwd(const void* g_frames, void* g_values, int64_t B, int64_t 
   if (B * S * D == 0) return NSB_OK;
   if (!g_frames || !g_values) return NSB_ERR_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  NSB_CODEC_LAUNCH(ste_bwd_kernel, "launch ste_bwd_kernel", NSB_PTRS(g_frames, g_values),
+  NSB_CODEC_LAUNCH(ste_bwd_kernel, "launch ste_bwd_kernel", 16, NSB_PTRS(g_frames, g_values),
                    static_cast<const T*>(g_frames), static_cast<T*>(g_values));
 }
 

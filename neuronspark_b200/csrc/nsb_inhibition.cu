@@ -117,6 +117,128 @@ __global__ void li_bwd_kernel(const T* __restrict__ g_out, const T* __restrict__
   }
 }
 
+// Register-resident variants for rows of at most 32*VE*NV elements: a lane keeps
+// its NV vectors of the row (and of g_out in the backward) in registers, so the
+// row is read from memory exactly once instead of once per pass.
+template <typename T, typename TG, int VE, int NV>
+__global__ void li_fwd_cached_kernel(const T* __restrict__ x, const TG* __restrict__ gain,
+                                     T* __restrict__ out, long long rows, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const float inv_d = 1.0f / (float)D;
+  for (long long r = warp; r < rows; r += nwarps) {
+    const T* xr = x + r * D;
+    Vec<T, VE> xv[NV];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = (lane + 32 * i) * VE;
+      if (d < D) {
+        xv[i] = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+          const float f = Elem<T>::to_f32(xv[i].v[j]);
+          ss += f * f;
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    const float rrms = 1.0f / sqrtf(ss * inv_d + eps);
+    T* orow = out + r * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = (lane + 32 * i) * VE;
+      if (d < D) {
+        const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);  // stays in L1
+        Vec<T, VE> o;
+#pragma unroll
+        for (int j = 0; j < VE; ++j)
+          o.v[j] = Elem<T>::from_f32(Elem<T>::to_f32(xv[i].v[j]) * rrms * Elem<TG>::to_f32(g.v[j]));
+        *reinterpret_cast<Vec<T, VE>*>(orow + d) = o;
+      }
+    }
+  }
+}
+
+template <typename T, typename TG, int VE, int NV>
+__global__ void li_bwd_cached_kernel(const T* __restrict__ g_out, const T* __restrict__ x,
+                                     const TG* __restrict__ gain, T* __restrict__ g_x,
+                                     float* __restrict__ partial, long long rows, int D, float eps) {
+  extern __shared__ float acc_smem[];  // [warps][D], summed over the CTA's warps at the end
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int wpc = blockDim.x >> 5;
+  const long long warp = (long long)blockIdx.x * wpc + wib;
+  const long long nwarps = (long long)gridDim.x * wpc;
+  const float inv_d = 1.0f / (float)D;
+  float acc[NV][VE];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < VE; ++j) acc[i][j] = 0.0f;
+  for (long long r = warp; r < rows; r += nwarps) {
+    const T* xr = x + r * D;
+    const T* gr = g_out + r * D;
+    Vec<T, VE> xv[NV], gv[NV];
+    float ss = 0.0f, dot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = (lane + 32 * i) * VE;
+      if (d < D) {
+        xv[i] = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+        gv[i] = *reinterpret_cast<const Vec<T, VE>*>(gr + d);
+        const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);  // stays in L1
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+          const float f = Elem<T>::to_f32(xv[i].v[j]);
+          ss += f * f;
+          dot += Elem<T>::to_f32(gv[i].v[j]) * Elem<TG>::to_f32(g.v[j]) * f;
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float rrms = 1.0f / sqrtf(ss * inv_d + eps);
+    const float mean_dot = dot * rrms * inv_d;
+    T* dxr = g_x + r * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = (lane + 32 * i) * VE;
+      if (d < D) {
+        const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);
+        Vec<T, VE> o;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+          const float xh = Elem<T>::to_f32(xv[i].v[j]) * rrms;
+          const float dout = Elem<T>::to_f32(gv[i].v[j]);
+          o.v[j] = Elem<T>::from_f32((dout * Elem<TG>::to_f32(g.v[j]) - xh * mean_dot) * rrms);
+          acc[i][j] += dout * xh;
+        }
+        *reinterpret_cast<Vec<T, VE>*>(dxr + d) = o;
+      }
+    }
+  }
+  float* mine = acc_smem + (size_t)wib * D;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int d = (lane + 32 * i) * VE;
+    if (d < D) {
+#pragma unroll
+      for (int j = 0; j < VE; ++j) mine[d + j] = acc[i][j];
+    }
+  }
+  __syncthreads();
+  float* prow = partial + (size_t)blockIdx.x * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float s = 0.0f;
+    for (int w = 0; w < wpc; ++w) s += acc_smem[(size_t)w * D + d];
+    prow[d] = s;
+  }
+}
+
+constexpr int kCacheVecs = 8;  // vectors of 16 bytes a lane keeps per row in the cached kernels
+
 // Backward, stage 2: g_gain[d] = sum over partial rows, fixed order.
 __global__ void li_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ g_gain,
                                      int nparts, int D) {
@@ -161,6 +283,49 @@ bool can_vec(int ve, long long D, std::initializer_list<const void*> tp, const v
   return reinterpret_cast<uintptr_t>(gp) % (sizeof(TG) * ve) == 0;
 }
 
+
+// Launches both backward stages with the given partial-sum buffer and grid; shared by the
+// entry point that takes scratch from the caller and the one with library-resident scratch,
+// so that both run the same kernels and give bit-identical results for an equal grid.
+template <typename T, typename TG>
+int li_bwd_launch(const void* g_out, const void* x, const void* gain, void* g_x, float* g_gain,
+                  float* partial, long long rows, long long D, float eps, int grid, int wpc,
+                  cudaStream_t st) {
+  if (!can_vec<T, TG>(1, D, {g_out, x, g_x}, gain)) return NSB_ERR_INVALID_ARG;
+  const size_t smem = (size_t)wpc * D * sizeof(float);
+  const T* gop = static_cast<const T*>(g_out);
+  const T* xp = static_cast<const T*>(x);
+  const TG* gp = static_cast<const TG*>(gain);
+  T* gxp = static_cast<T*>(g_x);
+#define NSB_LI_BWD(KERNEL_)                                                                       \
+  {                                                                                               \
+    auto k = KERNEL_;                                                                             \
+    NSB_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), \
+                 "cudaFuncSetAttribute(li_bwd)");                                                 \
+    k<<<grid, wpc * 32, smem, st>>>(gop, xp, gp, gxp, partial, rows, (int)D, eps);                \
+  }
+  constexpr int VMAX = 16 / (int)sizeof(T);  // elements in a 16-byte vector
+  if (can_vec<T, TG>(VMAX, D, {g_out, x, g_x}, gain) && sizeof(TG) * VMAX <= 32 &&
+      D <= 32 * VMAX * kCacheVecs) {
+    if (D <= 32 * VMAX * 2)
+      NSB_LI_BWD((li_bwd_cached_kernel<T, TG, VMAX, 2>))
+    else if (D <= 32 * VMAX * 4)
+      NSB_LI_BWD((li_bwd_cached_kernel<T, TG, VMAX, 4>))
+    else
+      NSB_LI_BWD((li_bwd_cached_kernel<T, TG, VMAX, kCacheVecs>))
+  } else if (can_vec<T, TG>(4, D, {g_out, x, g_x}, gain))
+    NSB_LI_BWD((li_bwd_kernel<T, TG, 4>))
+  else if (can_vec<T, TG>(2, D, {g_out, x, g_x}, gain))
+    NSB_LI_BWD((li_bwd_kernel<T, TG, 2>))
+  else
+    NSB_LI_BWD((li_bwd_kernel<T, TG, 1>))
+#undef NSB_LI_BWD
+  NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_kernel");
+  li_bwd_reduce_kernel<<<(int)((D + 255) / 256), 256, 0, st>>>(partial, g_gain, grid, (int)D);
+  NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_reduce_kernel");
+  return NSB_OK;
+}
+
 }  // namespace
 }  // namespace nsb
 
@@ -188,7 +353,16 @@ int nsb_lateral_inhibition_fwd(const void* x, const void* gain, void* out, int64
       const T* xp = static_cast<const T*>(x);
       const TG* gp = static_cast<const TG*>(gain);
       T* op = static_cast<T*>(out);
-      if (can_vec<T, TG>(4, D, {x, out}, gain))
+      constexpr int VMAX = 16 / (int)sizeof(T);  // elements in a 16-byte vector
+      if (can_vec<T, TG>(VMAX, D, {x, out}, gain) && sizeof(TG) * VMAX <= 32 && D <= 32 * VMAX * kCacheVecs) {
+        const int g = (int)grid, th = kWarpsPerCta * 32;
+        if (D <= 32 * VMAX * 2)
+          li_fwd_cached_kernel<T, TG, VMAX, 2><<<g, th, 0, st>>>(xp, gp, op, rows, (int)D, eps);
+        else if (D <= 32 * VMAX * 4)
+          li_fwd_cached_kernel<T, TG, VMAX, 4><<<g, th, 0, st>>>(xp, gp, op, rows, (int)D, eps);
+        else
+          li_fwd_cached_kernel<T, TG, VMAX, kCacheVecs><<<g, th, 0, st>>>(xp, gp, op, rows, (int)D, eps);
+      } else if (can_vec<T, TG>(4, D, {x, out}, gain))
         li_fwd_kernel<T, TG, 4><<<(int)grid, kWarpsPerCta * 32, 0, st>>>(xp, gp, op, rows, (int)D, eps);
       else if (can_vec<T, TG>(2, D, {x, out}, gain))
         li_fwd_kernel<T, TG, 2><<<(int)grid, kWarpsPerCta * 32, 0, st>>>(xp, gp, op, rows, (int)D, eps);
@@ -223,31 +397,11 @@ int nsb_lateral_inhibition_bwd(const void* g_out, const void* x, const void* gai
   int wpc = 0;
   const int grid = bwd_grid(rows, (int)D, &wpc);
   if (grid == 0) return NSB_ERR_TOO_LARGE;
-  const size_t smem = (size_t)wpc * D * sizeof(float);
   return with_dtype(dtype, [&](auto t) {
     using T = decltype(t);
     return with_dtype(gain_dtype, [&](auto tg) {
       using TG = decltype(tg);
-      if (!can_vec<T, TG>(1, D, {g_out, x, g_x}, gain)) return NSB_ERR_INVALID_ARG;
-      const T* gop = static_cast<const T*>(g_out);
-      const T* xp = static_cast<const T*>(x);
-      const TG* gp = static_cast<const TG*>(gain);
-      T* gxp = static_cast<T*>(g_x);
-#define NSB_LI_BWD(VE_)                                                                          \
-  {                                                                                              \
-    auto k = li_bwd_kernel<T, TG, VE_>;                                                          \
-    NSB_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), \
-                 "cudaFuncSetAttribute(li_bwd)");                                                \
-    k<<<grid, wpc * 32, smem, st>>>(gop, xp, gp, gxp, partial, rows, (int)D, eps);               \
-  }
-      if (can_vec<T, TG>(4, D, {g_out, x, g_x}, gain)) NSB_LI_BWD(4)
-      else if (can_vec<T, TG>(2, D, {g_out, x, g_x}, gain)) NSB_LI_BWD(2)
-      else NSB_LI_BWD(1)
-#undef NSB_LI_BWD
-      NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_kernel");
-      li_bwd_reduce_kernel<<<(int)((D + 255) / 256), 256, 0, st>>>(partial, g_gain, grid, (int)D);
-      NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_reduce_kernel");
-      return NSB_OK;
+      return li_bwd_launch<T, TG>(g_out, x, gain, g_x, g_gain, partial, rows, D, eps, grid, wpc, st);
     });
   });
 }
@@ -317,31 +471,11 @@ extern "C" int nsb_lateral_inhibition_bwd_static(const void* g_out, const void* 
   if (grid == 0) return NSB_ERR_TOO_LARGE;
   // one partial row of D floats per CTA has to fit the fixed array: use fewer CTAs if need be
   grid = (int)std::min<long long>(grid, kLiStaticFloats / D);
-  const size_t smem = (size_t)wpc * D * sizeof(float);
   return with_dtype(dtype, [&](auto t) {
     using T = decltype(t);
     return with_dtype(gain_dtype, [&](auto tg) {
       using TG = decltype(tg);
-      if (!can_vec<T, TG>(1, D, {g_out, x, g_x}, gain)) return NSB_ERR_INVALID_ARG;
-      const T* gop = static_cast<const T*>(g_out);
-      const T* xp = static_cast<const T*>(x);
-      const TG* gp = static_cast<const TG*>(gain);
-      T* gxp = static_cast<T*>(g_x);
-#define NSB_LI_BWD_STATIC(VE_)                                                                    \
-  {                                                                                               \
-    auto k = li_bwd_kernel<T, TG, VE_>;                                                           \
-    NSB_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), \
-                 "cudaFuncSetAttribute(li_bwd)");                                                 \
-    k<<<grid, wpc * 32, smem, st>>>(gop, xp, gp, gxp, partial, rows, (int)D, eps);                \
-  }
-      if (can_vec<T, TG>(4, D, {g_out, x, g_x}, gain)) NSB_LI_BWD_STATIC(4)
-      else if (can_vec<T, TG>(2, D, {g_out, x, g_x}, gain)) NSB_LI_BWD_STATIC(2)
-      else NSB_LI_BWD_STATIC(1)
-#undef NSB_LI_BWD_STATIC
-      NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_kernel (static scratch)");
-      li_bwd_reduce_kernel<<<(int)((D + 255) / 256), 256, 0, st>>>(partial, g_gain, grid, (int)D);
-      NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_reduce_kernel (static scratch)");
-      return NSB_OK;
+      return li_bwd_launch<T, TG>(g_out, x, gain, g_x, g_gain, partial, rows, D, eps, grid, wpc, st);
     });
   });
 }
