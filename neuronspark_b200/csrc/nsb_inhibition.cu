@@ -239,14 +239,25 @@ __global__ void li_bwd_cached_kernel(const T* __restrict__ g_out, const T* __res
 
 constexpr int kCacheVecs = 8;  // vectors of 16 bytes a lane keeps per row in the cached kernels
 
-// Backward, stage 2: g_gain[d] = sum over partial rows, fixed order.
+// Backward, stage 2: g_gain[d] = sum over the partial rows. A block covers 32 channels with
+// 8 groups of threads; group g adds rows g, g+8, g+16, ... and the 8 group sums are then
+// added in a fixed order, so the result does not depend on scheduling.
 __global__ void li_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ g_gain,
                                      int nparts, int D) {
-  const int d = blockIdx.x * blockDim.x + threadIdx.x;
-  if (d >= D) return;
+  __shared__ float part[8][33];
+  const int c = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int d = blockIdx.x * 32 + c;
   float s = 0.0f;
-  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * D + d];
-  g_gain[d] = s;
+  if (d < D)
+    for (int p = g; p < nparts; p += 8) s += partial[(size_t)p * D + d];
+  part[g][c] = s;
+  __syncthreads();
+  if (g == 0 && d < D) {
+    float t = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) t += part[q][c];
+    g_gain[d] = t;
+  }
 }
 
 int bwd_grid(long long rows, int D, int* wpc_out) {
@@ -321,7 +332,7 @@ int li_bwd_launch(const void* g_out, const void* x, const void* gain, void* g_x,
     NSB_LI_BWD((li_bwd_kernel<T, TG, 1>))
 #undef NSB_LI_BWD
   NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_kernel");
-  li_bwd_reduce_kernel<<<(int)((D + 255) / 256), 256, 0, st>>>(partial, g_gain, grid, (int)D);
+  li_bwd_reduce_kernel<<<(int)((D + 31) / 32), 256, 0, st>>>(partial, g_gain, grid, (int)D);
   NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_reduce_kernel");
   return NSB_OK;
 }

@@ -1,0 +1,95 @@
+"""Timing of the boundary kernels (FP16 codec, lateral inhibition) on one GPU.
+
+    python -m neuronspark_b200.microbench [--dtype bf16|f32] [--iters N]
+
+Prints one JSON line per kernel and shape: microseconds per call (CUDA events,
+best of N, 256 MB written between calls so that nothing is served from L2),
+algorithmic bytes and the bandwidth they imply. Shapes are those of the
+reference's 768-wide model: token blocks of (batch 8 or 32, 512 tokens, D 768)
+for the codec, (rows, 768) for the normaliser, plus a wide case."""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import fp16_codec as codec
+from . import lateral_inhibition as li
+
+
+def _time(fn, iters, flush):
+    fn()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(iters):
+        flush.fill_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b))
+    return best * 1e3  # us
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--only", default="", help="substring filter on the kernel name")
+    args = ap.parse_args()
+    dt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    es = 2 if dt == torch.bfloat16 else 4
+    dev = torch.device("cuda", 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def report(name, shape, us, nbytes):
+        print(json.dumps({"kernel": name, "shape": list(shape), "dtype": args.dtype, "us": round(us, 2),
+                          "algorithmic_bytes": int(nbytes), "GB_per_s": round(nbytes / us / 1e3, 1)}),
+              flush=True)
+
+    for shape in [(8, 512, 768), (32, 512, 768), (8, 512, 6144)]:
+        B, S, D = shape
+        n = B * S * D
+        x = torch.randn(B, S, D, device=dev).to(dt)
+        fa, fb = codec.fp16_encode(x), codec.fp16_encode(-0.5 * x)
+        gv = torch.randn(B, S, D, device=dev).to(dt)
+        gf = torch.randn(S * 16, B, D, device=dev).to(dt)
+        cases = {
+            "fp16_encode": (lambda: codec.fp16_encode(x), n * 17 * es),
+            "fp16_decode_fwd": (lambda: codec.fp16_decode(fa, S), n * 17 * es),
+            "binary_residual": (lambda: codec.binary_residual(fa, fb), n * 48 * es),
+            "fp16_decode_bwd": (lambda: codec._FP16Decode.backward(_Ctx((fa,)), gv), n * 33 * es),
+            "encode_ste_bwd": (lambda: codec._BinaryEncodeSTE.backward(_Ctx((), dt), gf), n * 17 * es),
+        }
+        for name, (fn, nbytes) in cases.items():
+            if args.only in name:
+                report(name, shape, _time(fn, args.iters, flush), nbytes)
+
+    for rows, D in [(4096, 768), (65536, 768), (8192, 6144)]:
+        x = torch.randn(rows, D, device=dev).to(dt)
+        gain = 1 + 0.1 * torch.randn(D, device=dev)
+        go = torch.randn(rows, D, device=dev).to(dt)
+        fn = li.LateralInhibitionFunction
+        if args.only in "lateral_inhibition_fwd":
+            report("lateral_inhibition_fwd", (rows, D),
+                   _time(lambda: fn.apply(x, gain, 1e-6), args.iters, flush), rows * D * 2 * es)
+        if args.only in "lateral_inhibition_bwd":
+            ctx = _Ctx((x, gain))
+            ctx.eps, ctx.orig_shape, ctx.gain_dtype, ctx.gain_shape = 1e-6, x.shape, gain.dtype, gain.shape
+            report("lateral_inhibition_bwd", (rows, D),
+                   _time(lambda: fn.backward(ctx, go), args.iters, flush), rows * D * 4 * es)
+
+
+class _Ctx:
+    """Just enough of an autograd context to call a Function's backward directly."""
+
+    def __init__(self, saved, in_dtype=None):
+        self.saved_tensors = saved
+        self.in_dtype = in_dtype
+        self.needs_input_grad = (True,)
+
+
+if __name__ == "__main__":
+    main()
