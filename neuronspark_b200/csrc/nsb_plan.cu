@@ -36,7 +36,7 @@ namespace {
 int regs_estimate(bool backward, int lanes, int tile) {
   if (!backward) return lanes == 4 ? 72 : (lanes == 2 ? 56 : 48);
   if (tile * lanes <= 16) return 96;
-  return lanes == 4 ? 200 : 240;
+  return lanes == 4 ? 232 : 240;
 }
 
 double op_size_factor(double tile_bytes) {
@@ -81,15 +81,15 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
     const size_t tile_bytes = (size_t)q.tile * 32 * lanes * q.elem_size;
     const size_t stage_bytes = tile_bytes * q.nstreams;
     const int regs = regs_estimate(q.backward, lanes, q.tile);
-    const int reg_warps = std::max(1, 65536 / (regs * 32));
+    // each of the 4 SM sub-partitions has its own 16 K registers and takes every 4th warp
+    const int reg_warps = std::max(1, 4 * (16384 / (regs * 32)));
     const double f_op = op_size_factor((double)tile_bytes);
     // A lone warp advances one time step in about this many cycles (dependent
     // chain + per-tile overheads), and needs about this many issue slots for it.
     const double cyc_per_step = (q.backward ? 1.4 : 1.0) * (100.0 + 70.0 * lanes);
     const double issue_per_step = (q.backward ? 2.0 : 1.0) * (20.0 + 15.0 * lanes);
-    for (int wpc = 1; wpc <= 8; ++wpc) {
+    for (int wpc = 1; wpc <= 16; ++wpc) {
       if (tune.warps_per_cta > 0 && wpc != tune.warps_per_cta) continue;
-      if (tune.warps_per_cta <= 0 && wpc > 4) continue;
       for (int st = 2; st <= 6; ++st) {
         if (tune.stages > 0 && st != tune.stages) continue;
         if (tune.stages <= 0 && (st > 4 || st > std::max(2, ntiles))) continue;

@@ -632,6 +632,11 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
 // 96 registers per thread keep the 21 warps per SM of the headline shape
 // (196 608 columns, 2 per thread, 148 SMs) resident in a single wave.
 constexpr int kBwdMaxRegs = 96;
+// The 4-lane backward is left uncapped (~230 registers, 8 warps per SM). Capping it so that
+// 11-12 warps fit an SM (the headline shape would then run in one wave) was measured: at 184
+// registers an 11-warp CTA does not launch (3 warps land on one 16 K-register sub-partition), at
+// 168 the spills cost 15-40 %.
+constexpr int kBwdMaxRegsV4 = 255;
 constexpr int kBwdMaxThreads = 256;
 
 struct BwdParams {
@@ -680,7 +685,7 @@ __device__ __forceinline__ void surrogate_grad(float (&sg)[V], const float (&x)[
 }
 
 template <typename ST, int MODE, int SURR, int V, int C, bool TMA, bool HAS_GV>
-__global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwdMaxRegs) : 255) plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tm0,
+__global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwdMaxRegs) : ((TMA && C * V == 32 && MODE != MODE_RF) ? kBwdMaxRegsV4 : 255)) plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tm0,
                                 const __grid_constant__ CUtensorMap tm1,
                                 const __grid_constant__ CUtensorMap tm2,
                                 const __grid_constant__ CUtensorMap tm3,
