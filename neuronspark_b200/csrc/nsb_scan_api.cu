@@ -38,7 +38,12 @@ int nsb_plif_selective_fwd(const void* beta, const void* u_or_cur, const void* g
   if (!v_init || !v_last || !f32_aligned(v_init) || !f32_aligned(v_last) || !f32_aligned(v_ckpt) ||
       !f32_aligned(spike_packed))
     return NSB_ERR_INVALID_ARG;
-  if (T > 0 && (!beta || !u_or_cur || !v_th)) return NSB_ERR_INVALID_ARG;
+  if (T == 0) {  // nothing to scan: the final state is the initial state
+    NSB_CUDA_TRY(cudaMemcpyAsync(v_last, v_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice,
+                                 static_cast<cudaStream_t>(stream)), "copy v_init");
+    return NSB_OK;
+  }
+  if (!beta || !u_or_cur || !v_th) return NSB_ERR_INVALID_ARG;
   const void* ep[] = {beta, u_or_cur, gain, v_th, spike_dense, v_post};
   for (const void* p : ep)
     if (!elem_aligned(p, dtype)) return NSB_ERR_INVALID_ARG;
@@ -60,7 +65,12 @@ int nsb_plif_rowparam_fwd(const float* beta_row, const void* u, const float* vth
   const void* fp[] = {beta_row, vth_row, v_init, v_last, v_ckpt, spike_packed};
   for (const void* p : fp)
     if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
-  if (T > 0 && !u) return NSB_ERR_INVALID_ARG;
+  if (T == 0) {
+    NSB_CUDA_TRY(cudaMemcpyAsync(v_last, v_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice,
+                                 static_cast<cudaStream_t>(stream)), "copy v_init");
+    return NSB_OK;
+  }
+  if (!u) return NSB_ERR_INVALID_ARG;
   const void* ep[] = {u, spike_dense, v_post};
   for (const void* p : ep)
     if (!elem_aligned(p, dtype)) return NSB_ERR_INVALID_ARG;
@@ -142,7 +152,15 @@ int nsb_plif_rf_fwd(const void* beta, const void* omega, const void* u, const vo
   const void* fp[] = {v_init, w_init, v_last, w_last, v_ckpt, w_ckpt, spike_packed};
   for (const void* p : fp)
     if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
-  if (T > 0 && (!beta || !omega || !u || !v_th)) return NSB_ERR_INVALID_ARG;
+  if (T == 0) {
+    cudaStream_t st0 = static_cast<cudaStream_t>(stream);
+    NSB_CUDA_TRY(cudaMemcpyAsync(v_last, v_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice, st0),
+                 "copy v_init");
+    NSB_CUDA_TRY(cudaMemcpyAsync(w_last, w_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice, st0),
+                 "copy w_init");
+    return NSB_OK;
+  }
+  if (!beta || !omega || !u || !v_th) return NSB_ERR_INVALID_ARG;
   const void* ep[] = {beta, omega, u, v_th, spike_dense, v_post, w_out};
   for (const void* p : ep)
     if (!elem_aligned(p, dtype)) return NSB_ERR_INVALID_ARG;

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import neuronspark_b200 as nsb
+import neuronspark_b200._lib  # noqa: F401  (nsb._lib)
 from neuronspark_b200 import parallel_scan as ps
 from oracle import oracle as orc
 from util import (REL_TOL, assert_close, assert_close_lowp, assert_spikes_match, f32,
@@ -366,3 +367,42 @@ def test_cpu_tensor_is_rejected():
     with pytest.raises(nsb.NSBError):
         ps.plif_parallel_forward(torch.ones(2, 1, 4), torch.ones(2, 1, 4), torch.ones(2, 1, 4),
                                  torch.zeros(1, 4))
+
+
+def test_empty_time_axis_and_empty_columns():
+    """T = 0: nothing to scan, the final state is the initial state and the gradient of the
+    initial state is zero; zero columns: a no-op."""
+    B, D = 2, 64
+    v0 = torch.randn(B, D, device=DEV)
+    e = torch.empty(0, B, D, device=DEV)
+    packed, v_last = ps.plif_selective_forward_packed(e, e, e, v0)
+    assert packed.shape == (0, B * D // 32) and torch.equal(v_last, v0)
+    spike, v_l = ps.plif_rowparam_forward_recompute(torch.rand(B, D, device=DEV), e, torch.rand(B, D, device=DEV),
+                                                    v0, 4.0)
+    assert spike.shape == (0, B, D) and torch.equal(v_l, v0)
+    z = torch.empty(4, 0, 8, device=DEV)
+    s, v, _ = ps.plif_parallel_forward(z, z, z, torch.empty(0, 8, device=DEV))
+    assert s.shape == (4, 0, 8) and v.shape == (4, 0, 8)
+    L = nsb._lib.lib()
+    g = torch.full((B, D), 7.0, device=DEV)
+    dummy = torch.zeros(8, device=DEV)
+    st = L.nsb_plif_selective_bwd(nsb._lib.ptr(dummy), nsb._lib.ptr(dummy), None, nsb._lib.ptr(dummy),
+                                  nsb._lib.ptr(dummy), nsb._lib.ptr(dummy), None, None, None, None, None,
+                                  nsb._lib.ptr(g), 0, B * D, 0, 8, 0, 4.0, nsb._lib.stream_ptr(torch.device(DEV)))
+    assert st == 0 and float(g.abs().max()) == 0.0
+
+
+def test_unaligned_views_take_the_direct_path_and_stay_exact():
+    """A tensor view that starts 2 bytes into an allocation cannot be a TMA source."""
+    T, B, D = 24, 2, 64
+    beta, cur, gain, vth, v0 = selective_inputs(T, B, D, torch.bfloat16, DEV, seed=12)
+    u = (gain.float() * cur.float()).bfloat16()
+    flat = torch.empty(T * B * D + 1, dtype=torch.bfloat16, device=DEV)
+    u_off = flat[1:].view(T, B, D)
+    u_off.copy_(u)
+    assert u_off.data_ptr() % 16 != 0 and u_off.is_contiguous()
+    s_ref, v_ref, _ = ps.plif_parallel_forward(beta, u, vth, v0)
+    assert nsb.last_launch_info()["used_tma"] == 1
+    s, v, _ = ps.plif_parallel_forward(beta, u_off, vth, v0)
+    assert nsb.last_launch_info()["used_tma"] == 0
+    assert torch.equal(s, s_ref) and torch.equal(v, v_ref)
