@@ -102,7 +102,9 @@ int nsb_scan_plan_query(int backward, int nstreams, int elem_size, int64_t T, in
  *                              the membrane state BEFORE step j*ckpt_interval
  *                              (row 0 = v_init). Needed by the backward.
  * v_last                     : [cols] fp32, state after the last step
- * ckpt_interval              : 8 or 16 (also the time-tile of the pipeline)
+ * ckpt_interval              : 8, 16 or 32 (also the time-tile of the pipeline; longer
+ *                              tiles amortise per-tile overhead when there are few
+ *                              columns, 8 gives the widest kernels for many columns)
  */
 int nsb_plif_selective_fwd(const void* beta, const void* u_or_cur, const void* gain,
                            const void* v_th, const float* v_init, void* spike_dense,

@@ -36,6 +36,7 @@ namespace {
 int regs_estimate(bool backward, int lanes, int tile) {
   if (!backward) return lanes == 4 ? 72 : (lanes == 2 ? 56 : 48);
   if (tile * lanes <= 16) return 96;
+  if (lanes == 1) return tile == 16 ? 128 : 200;
   return lanes == 4 ? 232 : 240;
 }
 
@@ -144,7 +145,7 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
 extern "C" int nsb_scan_plan_query(int backward, int nstreams, int elem_size, int64_t T, int64_t cols,
                                    int tile, int32_t out[5]) {
   if (!out || T < 0 || cols <= 0 || nstreams < 1 || nstreams > 6 || (elem_size != 2 && elem_size != 4) ||
-      (tile != 8 && tile != 16))
+      (tile != 8 && tile != 16 && tile != 32))
     return NSB_ERR_INVALID_ARG;
   nsb::PlanQuery q;
   q.T = T;
@@ -153,7 +154,7 @@ extern "C" int nsb_scan_plan_query(int backward, int nstreams, int elem_size, in
   q.nstreams = nstreams;
   q.tile = tile;
   q.backward = backward != 0;
-  q.max_lanes = (backward && tile == 16) ? 2 : 4;
+  q.max_lanes = tile == 32 ? 1 : ((backward && tile == 16) ? 2 : 4);
   const nsb::Plan p = nsb::plan_scan(nsb::b200_device_info(), q, nsb::get_tuning());
   if (p.grid == 0) return NSB_ERR_UNSUPPORTED;
   out[0] = p.lanes;

@@ -1185,7 +1185,7 @@ int scan_fwd_dispatch(const FwdArgs& a) {
     PlanQuery q;
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
     q.nstreams = a.mode == MODE_ROW ? 1 : ((a.mode == MODE_AI || a.mode == MODE_RF) ? 4 : 3);
-    q.tile = C; q.backward = false; q.max_lanes = 4;
+    q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;  // 32-step tiles: 1 lane per thread only
     plan = plan_scan(dev, q, tune);
   }
   const int V = plan.lanes;
@@ -1196,7 +1196,8 @@ int scan_fwd_dispatch(const FwdArgs& a) {
 #define NSB_FWD_CASES_V(MODE_, PACKED_)                                                \
   NSB_FWD_CASE(MODE_, PACKED_, 1, 8) NSB_FWD_CASE(MODE_, PACKED_, 2, 8)                \
   NSB_FWD_CASE(MODE_, PACKED_, 4, 8) NSB_FWD_CASE(MODE_, PACKED_, 1, 16)               \
-  NSB_FWD_CASE(MODE_, PACKED_, 2, 16) NSB_FWD_CASE(MODE_, PACKED_, 4, 16)
+  NSB_FWD_CASE(MODE_, PACKED_, 2, 16) NSB_FWD_CASE(MODE_, PACKED_, 4, 16)              \
+  NSB_FWD_CASE(MODE_, PACKED_, 1, 32)
   if (tma) {
     NSB_FWD_CASES_V(MODE_U, false) NSB_FWD_CASES_V(MODE_U, true)
     NSB_FWD_CASES_V(MODE_AI, false) NSB_FWD_CASES_V(MODE_AI, true)
@@ -1214,6 +1215,7 @@ int scan_fwd_dispatch(const FwdArgs& a) {
   NSB_FWD_DIRECT(MODE_AI, 8) NSB_FWD_DIRECT(MODE_AI, 16)
   NSB_FWD_DIRECT(MODE_ROW, 8) NSB_FWD_DIRECT(MODE_ROW, 16)
   NSB_FWD_DIRECT(MODE_RF, 8) NSB_FWD_DIRECT(MODE_RF, 16)
+  NSB_FWD_DIRECT(MODE_U, 32) NSB_FWD_DIRECT(MODE_AI, 32) NSB_FWD_DIRECT(MODE_ROW, 32) NSB_FWD_DIRECT(MODE_RF, 32)
 #undef NSB_FWD_DIRECT
   return NSB_ERR_INVALID_ARG;
 }
@@ -1235,7 +1237,7 @@ int scan_bwd_dispatch(const BwdArgs& a) {
     PlanQuery q;
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
     q.nstreams = (a.mode == MODE_ROW ? 1 : ((a.mode == MODE_AI || a.mode == MODE_RF) ? 4 : 3)) + 1 + (a.g_vpost ? 1 : 0);
-    q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : 2;
+    q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : (C == 16 ? 2 : 1);
     plan = plan_scan(dev, q, tune);
   }
   const int V = plan.lanes;
@@ -1246,11 +1248,11 @@ int scan_bwd_dispatch(const BwdArgs& a) {
 #define NSB_BWD_CASES_V(MODE_, SURR_)                                                  \
   NSB_BWD_CASE(MODE_, SURR_, 1, 8) NSB_BWD_CASE(MODE_, SURR_, 2, 8)                    \
   NSB_BWD_CASE(MODE_, SURR_, 4, 8) NSB_BWD_CASE(MODE_, SURR_, 1, 16)                   \
-  NSB_BWD_CASE(MODE_, SURR_, 2, 16)
+  NSB_BWD_CASE(MODE_, SURR_, 2, 16) NSB_BWD_CASE(MODE_, SURR_, 1, 32)
 #define NSB_BWD_CASES_RF(SURR_)                                                         \
   NSB_BWD_CASE(MODE_RF, SURR_, 1, 8) NSB_BWD_CASE(MODE_RF, SURR_, 2, 8)                \
   NSB_BWD_CASE(MODE_RF, SURR_, 4, 8) NSB_BWD_CASE(MODE_RF, SURR_, 1, 16)               \
-  NSB_BWD_CASE(MODE_RF, SURR_, 2, 16)
+  NSB_BWD_CASE(MODE_RF, SURR_, 2, 16) NSB_BWD_CASE(MODE_RF, SURR_, 1, 32)
   if (tma) {
     NSB_BWD_CASES_V(MODE_U, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_U, NSB_SURR_ATAN)
     NSB_BWD_CASES_V(MODE_AI, NSB_SURR_SIGMOID) NSB_BWD_CASES_V(MODE_AI, NSB_SURR_ATAN)
@@ -1266,7 +1268,8 @@ int scan_bwd_dispatch(const BwdArgs& a) {
     return launch_bwd_one<ST, MODE_, SURR_, 1, C_, false>(a, dev, tune, plan);
 #define NSB_BWD_DIRECT_S(MODE_)                                                        \
   NSB_BWD_DIRECT(MODE_, NSB_SURR_SIGMOID, 8) NSB_BWD_DIRECT(MODE_, NSB_SURR_SIGMOID, 16) \
-  NSB_BWD_DIRECT(MODE_, NSB_SURR_ATAN, 8) NSB_BWD_DIRECT(MODE_, NSB_SURR_ATAN, 16)
+  NSB_BWD_DIRECT(MODE_, NSB_SURR_ATAN, 8) NSB_BWD_DIRECT(MODE_, NSB_SURR_ATAN, 16)       \
+  NSB_BWD_DIRECT(MODE_, NSB_SURR_SIGMOID, 32) NSB_BWD_DIRECT(MODE_, NSB_SURR_ATAN, 32)
   NSB_BWD_DIRECT_S(MODE_U) NSB_BWD_DIRECT_S(MODE_AI) NSB_BWD_DIRECT_S(MODE_ROW) NSB_BWD_DIRECT_S(MODE_RF)
 #undef NSB_BWD_DIRECT_S
 #undef NSB_BWD_DIRECT

@@ -3,7 +3,7 @@
 
 namespace {
 
-bool tile_ok(int c) { return c == 8 || c == 16; }
+bool tile_ok(int c) { return c == 8 || c == 16 || c == 32; }
 bool dtype_ok(int d) { return d == NSB_F32 || d == NSB_BF16 || d == NSB_F16; }
 bool elem_aligned(const void* p, int dtype) {
   return (reinterpret_cast<uintptr_t>(p) % nsb::dtype_size(dtype)) == 0;

@@ -38,8 +38,22 @@ import torch
 from . import _lib
 from ._lib import NSBError
 
-#: Steps per time tile = spacing of the fp32 state checkpoints kept for backward.
-CKPT_INTERVAL = 8
+#: Steps per time tile = spacing of the fp32 state checkpoints kept for backward
+#: (8, 16 or 32). None = chosen per call from the number of columns: problems with few
+#: columns are bound by per-tile latency and run faster with long tiles, problems with
+#: many columns are bound by HBM bandwidth and want the widest (8-step) kernels.
+CKPT_INTERVAL = None
+
+
+def _interval(cols: int, row_param: bool = False) -> int:
+    """Tile length for a problem with ``cols`` columns. Thresholds from forward+backward
+    timings on B200 (bf16, T=8192): 32-step tiles win up to ~32 K columns for the selective
+    scans and ~64 K for the row-parameter scan (one streamed input), 8-step tiles beyond."""
+    if CKPT_INTERVAL is not None:
+        return int(CKPT_INTERVAL)
+    if row_param:
+        return 32 if cols <= 65536 else (16 if cols <= 131072 else 8)
+    return 32 if cols <= 32768 else 8
 
 _SURROGATES = {"sigmoid": _lib.SURR_SIGMOID, "atan": _lib.SURR_ATAN}
 
@@ -90,8 +104,8 @@ def _surrogate_kind(surrogate) -> int:
         raise NSBError(f"unknown surrogate {surrogate!r}; expected 'sigmoid' or 'atan'") from None
 
 
-def _n_tiles(T: int) -> int:
-    return (T + CKPT_INTERVAL - 1) // CKPT_INTERVAL
+def _n_tiles(T: int, interval: int) -> int:
+    return (T + interval - 1) // interval
 
 
 def _launch_selective_fwd(beta, drive, gain, v_th, v_init32, *, want_spike, want_packed, want_vpost,
@@ -104,15 +118,16 @@ def _launch_selective_fwd(beta, drive, gain, v_th, v_init32, *, want_spike, want
     packed = (torch.empty((T, (cols + 31) // 32), dtype=torch.int32, device=dev)
               if want_packed else None)
     vpost = torch.empty_like(drive) if want_vpost else None
-    ckpt = (torch.empty((_n_tiles(T), cols), dtype=torch.float32, device=dev) if want_ckpt else None)
+    C = _interval(cols)
+    ckpt = (torch.empty((_n_tiles(T, C), cols), dtype=torch.float32, device=dev) if want_ckpt else None)
     v_last = torch.empty(drive.shape[1:], dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().nsb_plif_selective_fwd(
             _lib.ptr(beta), _lib.ptr(drive), _lib.ptr(gain), _lib.ptr(v_th), _lib.ptr(v_init32),
             _lib.ptr(spike), _lib.ptr(packed), _lib.ptr(vpost), _lib.ptr(ckpt), _lib.ptr(v_last),
-            T, cols, _lib.dtype_code(dt), CKPT_INTERVAL, _lib.stream_ptr(dev)),
+            T, cols, _lib.dtype_code(dt), C, _lib.stream_ptr(dev)),
             "nsb_plif_selective_fwd")
-    return spike, packed, vpost, ckpt, v_last
+    return spike, packed, vpost, ckpt, v_last, C
 
 
 def _launch_rowparam_fwd(beta_row32, u, vth_row32, v_init32, *, want_spike, want_packed, want_vpost,
@@ -123,15 +138,16 @@ def _launch_rowparam_fwd(beta_row32, u, vth_row32, v_init32, *, want_spike, want
     packed = (torch.empty((T, (cols + 31) // 32), dtype=torch.int32, device=dev)
               if want_packed else None)
     vpost = torch.empty_like(u) if want_vpost else None
-    ckpt = (torch.empty((_n_tiles(T), cols), dtype=torch.float32, device=dev) if want_ckpt else None)
+    C = _interval(cols, row_param=True)
+    ckpt = (torch.empty((_n_tiles(T, C), cols), dtype=torch.float32, device=dev) if want_ckpt else None)
     v_last = torch.empty(u.shape[1:], dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().nsb_plif_rowparam_fwd(
             _lib.ptr(beta_row32), _lib.ptr(u), _lib.ptr(vth_row32), _lib.ptr(v_init32),
             _lib.ptr(spike), _lib.ptr(packed), _lib.ptr(vpost), _lib.ptr(ckpt), _lib.ptr(v_last),
-            T, cols, _lib.dtype_code(u.dtype), CKPT_INTERVAL, _lib.stream_ptr(dev)),
+            T, cols, _lib.dtype_code(u.dtype), C, _lib.stream_ptr(dev)),
             "nsb_plif_rowparam_fwd")
-    return spike, packed, vpost, ckpt, v_last
+    return spike, packed, vpost, ckpt, v_last, C
 
 
 def _grad_stream(g, like, dt):
@@ -164,7 +180,7 @@ class PLIFSelectiveScan(torch.autograd.Function):
         beta_c, u_c, vth_c = (_as_stream(t, dt) for t in (beta, u, v_th))
         v0 = _row_f32(v_init, u.shape[1:])
         needs_grad = any(ctx.needs_input_grad[:4])
-        spike, _, vpost, ckpt, _ = _launch_selective_fwd(
+        spike, _, vpost, ckpt, _, ctx.interval = _launch_selective_fwd(
             beta_c, u_c, None, vth_c, v0, want_spike=True, want_packed=False, want_vpost=True,
             want_ckpt=needs_grad)
         if needs_grad:
@@ -192,7 +208,7 @@ class PLIFSelectiveScan(torch.autograd.Function):
             _lib.check(_lib.lib().nsb_plif_selective_bwd(
                 _lib.ptr(beta_c), _lib.ptr(u_c), None, _lib.ptr(vth_c), _lib.ptr(ckpt), _lib.ptr(gs),
                 _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), None, _lib.ptr(g_vth), _lib.ptr(g_v0),
-                T, cols, _lib.dtype_code(dt), CKPT_INTERVAL, ctx_surrogate(ctx), ctx.alpha,
+                T, cols, _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), ctx.alpha,
                 _lib.stream_ptr(dev)), "nsb_plif_selective_bwd")
         db, du, dth, dv = ctx.in_dtypes
         return (g_beta.to(db), g_u.to(du), g_vth.to(dth),
@@ -216,7 +232,7 @@ class PLIFSelectiveScanAI(torch.autograd.Function):
         beta_c, cur_c, gain_c, vth_c = (_as_stream(t, dt) for t in (beta, cur, gain, v_th))
         v0 = _row_f32(v_init, cur.shape[1:])
         needs_grad = any(ctx.needs_input_grad[:5])
-        spike, _, _, ckpt, v_last = _launch_selective_fwd(
+        spike, _, _, ckpt, v_last, ctx.interval = _launch_selective_fwd(
             beta_c, cur_c, gain_c, vth_c, v0, want_spike=True, want_packed=False, want_vpost=False,
             want_ckpt=needs_grad)
         if needs_grad:
@@ -245,7 +261,7 @@ class PLIFSelectiveScanAI(torch.autograd.Function):
             _lib.check(_lib.lib().nsb_plif_selective_bwd(
                 _lib.ptr(beta_c), _lib.ptr(cur_c), _lib.ptr(gain_c), _lib.ptr(vth_c), _lib.ptr(ckpt),
                 _lib.ptr(gs), None, _lib.ptr(g_beta), _lib.ptr(g_cur), _lib.ptr(g_gain),
-                _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols, _lib.dtype_code(dt), CKPT_INTERVAL,
+                _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols, _lib.dtype_code(dt), ctx.interval,
                 ctx.surrogate, ctx.alpha, _lib.stream_ptr(dev)), "nsb_plif_selective_bwd")
         db, dc, dg, dth, dv = ctx.in_dtypes
         return (g_beta.to(db), g_cur.to(dc), g_gain.to(dg), g_vth.to(dth),
@@ -271,7 +287,7 @@ def _rowparam_backward(ctx, grad_spike, grad_V_post):
         _lib.check(_lib.lib().nsb_plif_rowparam_bwd(
             _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(ckpt), _lib.ptr(gs),
             _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols,
-            _lib.dtype_code(dt), CKPT_INTERVAL, ctx_surrogate(ctx), ctx.alpha,
+            _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), ctx.alpha,
             _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd")
     db, du, dth, dv = ctx.in_dtypes
     return (g_beta.to(db).reshape(ctx.row_shapes[0]), g_u.to(du),
@@ -287,7 +303,7 @@ def _rowparam_forward(ctx, beta_row, u, v_th_row, v_init, alpha, want_vpost):
     u_c = _as_stream(u, dt)
     beta32, vth32, v0 = (_row_f32(t, shape) for t in (beta_row, v_th_row, v_init))
     needs_grad = any(ctx.needs_input_grad[:4])
-    spike, _, vpost, ckpt, v_last = _launch_rowparam_fwd(
+    spike, _, vpost, ckpt, v_last, ctx.interval = _launch_rowparam_fwd(
         beta32, u_c, vth32, v0, want_spike=True, want_packed=False, want_vpost=want_vpost,
         want_ckpt=needs_grad)
     if needs_grad:
@@ -346,8 +362,9 @@ def _rf_forward(ctx, beta, omega, u, v_th, v_init, w_init, alpha, want_states):
     vpost = torch.empty_like(u_c) if want_states else None
     wout = torch.empty_like(u_c) if want_states else None
     ckv = ckw = None
+    C = ctx.interval = _interval(cols)
     if needs_grad:
-        ckv = torch.empty((_n_tiles(T), cols), dtype=torch.float32, device=dev)
+        ckv = torch.empty((_n_tiles(T, C), cols), dtype=torch.float32, device=dev)
         ckw = torch.empty_like(ckv)
     v_last = torch.empty(shape, dtype=torch.float32, device=dev)
     w_last = torch.empty_like(v_last)
@@ -355,7 +372,7 @@ def _rf_forward(ctx, beta, omega, u, v_th, v_init, w_init, alpha, want_states):
         _lib.check(_lib.lib().nsb_plif_rf_fwd(
             _lib.ptr(beta_c), _lib.ptr(omega_c), _lib.ptr(u_c), _lib.ptr(vth_c), _lib.ptr(v0), _lib.ptr(w0),
             _lib.ptr(spike), None, _lib.ptr(vpost), _lib.ptr(wout), _lib.ptr(ckv), _lib.ptr(ckw),
-            _lib.ptr(v_last), _lib.ptr(w_last), T, cols, _lib.dtype_code(dt), CKPT_INTERVAL,
+            _lib.ptr(v_last), _lib.ptr(w_last), T, cols, _lib.dtype_code(dt), C,
             _lib.stream_ptr(dev)), "nsb_plif_rf_fwd")
     if needs_grad:
         ctx.save_for_backward(beta_c, omega_c, u_c, vth_c, ckv, ckw)
@@ -381,7 +398,7 @@ def _rf_backward(ctx, grad_spike, grad_V_post):
         _lib.check(_lib.lib().nsb_plif_rf_bwd(
             _lib.ptr(beta_c), _lib.ptr(omega_c), _lib.ptr(u_c), _lib.ptr(vth_c), _lib.ptr(ckv),
             _lib.ptr(ckw), _lib.ptr(gs), _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_omega), _lib.ptr(g_u),
-            _lib.ptr(g_vth), _lib.ptr(g_v0), _lib.ptr(g_w0), T, cols, _lib.dtype_code(dt), CKPT_INTERVAL,
+            _lib.ptr(g_vth), _lib.ptr(g_v0), _lib.ptr(g_w0), T, cols, _lib.dtype_code(dt), ctx.interval,
             ctx_surrogate(ctx), ctx.alpha, _lib.stream_ptr(dev)), "nsb_plif_rf_bwd")
     db, do, du, dth, dv, dw = ctx.in_dtypes
     return (g_beta.to(db), g_omega.to(do), g_u.to(du), g_vth.to(dth),
@@ -568,7 +585,7 @@ def plif_selective_forward_packed(beta, drive, v_th, v_init, gain=None):
     dt = _common_stream_dtype(beta, drive, v_th, gain)
     beta_c, drive_c, vth_c, gain_c = (_as_stream(t, dt) for t in (beta, drive, v_th, gain))
     v0 = _row_f32(v_init, drive.shape[1:])
-    _, packed, _, _, v_last = _launch_selective_fwd(
+    _, packed, _, _, v_last, _ = _launch_selective_fwd(
         beta_c, drive_c, gain_c, vth_c, v0, want_spike=False, want_packed=True, want_vpost=False,
         want_ckpt=False)
     return packed, v_last
@@ -581,7 +598,7 @@ def plif_rowparam_forward_packed(beta_row, u, v_th_row, v_init):
     shape = u.shape[1:]
     u_c = _as_stream(u, _common_stream_dtype(u))
     beta32, vth32, v0 = (_row_f32(t, shape) for t in (beta_row, v_th_row, v_init))
-    _, packed, _, _, v_last = _launch_rowparam_fwd(
+    _, packed, _, _, v_last, _ = _launch_rowparam_fwd(
         beta32, u_c, vth32, v0, want_spike=False, want_packed=True, want_vpost=False,
         want_ckpt=False)
     return packed, v_last

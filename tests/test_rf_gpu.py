@@ -24,8 +24,10 @@ _Sigmoid.__name__ = "Sigmoid"
 @pytest.fixture(autouse=True)
 def _reset():
     nsb.set_tuning()
+    ps.CKPT_INTERVAL = None
     yield
     nsb.set_tuning()
+    ps.CKPT_INTERVAL = None
     assert nsb.device_error_word() == 0
 
 
@@ -109,6 +111,7 @@ def test_rf_vs_oracle(shape, dtype):
 
 @pytest.mark.parametrize("lanes,stages,wpc", [(1, 2, 1), (2, 3, 2), (4, 2, 1)])
 def test_rf_paths_agree(lanes, stages, wpc):
+    ps.CKPT_INTERVAL = 8
     beta, omega, u, vth, v0, w0 = rf_inputs(70, 2, 384, torch.bfloat16, 9)
     nsb.set_tuning(force_direct=True)
     ref = ps.rf_plif_parallel_forward(beta, omega, u, vth, v0, w0)

@@ -20,8 +20,10 @@ DEV = "cuda:0"
 @pytest.fixture(autouse=True)
 def _reset_tuning():
     nsb.set_tuning()
+    ps.CKPT_INTERVAL = None
     yield
     nsb.set_tuning()
+    ps.CKPT_INTERVAL = None
     assert nsb.device_error_word() == 0
 
 
@@ -252,6 +254,7 @@ def test_rowparam_backward_vs_oracle(shape, dtype, surrogate):
 
 @pytest.mark.parametrize("lanes,stages,wpc", [(1, 2, 1), (2, 3, 3), (4, 2, 2), (2, 4, 8), (1, 6, 4)])
 def test_tuning_variants_bitwise_identical(lanes, stages, wpc):
+    ps.CKPT_INTERVAL = 8  # the lane count is forced below; 8-step tiles exist for every lane count
     T, B, D = 70, 2, 384
     beta, cur, gain, vth, v0 = selective_inputs(T, B, D, torch.bfloat16, DEV, seed=3)
     nsb.set_tuning(force_direct=True)
@@ -270,6 +273,7 @@ def test_tuning_variants_bitwise_identical(lanes, stages, wpc):
 @pytest.mark.parametrize("lanes", [1, 2, 4])
 @pytest.mark.parametrize("surrogate", ["sigmoid", "atan"])
 def test_backward_direct_and_tma_paths_agree(lanes, surrogate):
+    ps.CKPT_INTERVAL = 8
     T, B, D = 45, 2, 192
     base = selective_inputs(T, B, D, torch.float32, DEV, seed=11, zero_init=False)
     gS = 0.1 * torch.randn(T, B, D, device=DEV)
@@ -406,3 +410,29 @@ def test_unaligned_views_take_the_direct_path_and_stay_exact():
     s, v, _ = ps.plif_parallel_forward(beta, u_off, vth, v0)
     assert nsb.last_launch_info()["used_tma"] == 0
     assert torch.equal(s, s_ref) and torch.equal(v, v_ref)
+
+
+@pytest.mark.parametrize("interval", [8, 16, 32])
+@pytest.mark.parametrize("shape", [(5, 1, 31), (33, 2, 64), (100, 2, 200), (257, 1, 512)])
+def test_every_tile_length_vs_oracle(interval, shape):
+    """The checkpoint spacing / tile length (8, 16, 32 steps) never changes a result bit."""
+    ps.CKPT_INTERVAL = interval
+    T, B, D = shape
+    beta, cur, gain, vth, v0 = selective_inputs(T, B, D, torch.float32, DEV, seed=T + interval, zero_init=False)
+    rs, _, rl = oracle_selective(beta, cur, gain, vth, v0)
+    ins = [t.requires_grad_() for t in (beta, cur, gain, vth, v0)]
+    spike, v_last = ps.plif_selective_scan_ai(*ins, alpha=4.0, surrogate="sigmoid")
+    assert nsb.last_launch_info()["tile_steps"] == interval
+    assert np.array_equal(f32(spike), rs) and np.array_equal(f32(v_last), rl)
+    gS = torch.randn(T, B, D, device=DEV)
+    (spike * gS).sum().backward()
+    ref = orc.plif_selective_ai_bwd(*(f32(t) for t in ins), f32(gS), None, 4.0)
+    for t, e, n in zip(ins, ref, ("g_beta", "g_cur", "g_gain", "g_vth", "g_vinit")):
+        assert_close(f32(t.grad), e, what=n)
+    packed, _ = ps.plif_selective_forward_packed(beta.detach(), cur.detach(), vth.detach(), v0.detach(),
+                                                 gain=gain.detach())
+    assert np.array_equal(f32(ps.unpack_spikes(packed, (B, D))), rs)
+    br, u, tr, v0r = rowparam_inputs(T, B, D, torch.bfloat16, DEV, seed=3)
+    s2, vl2 = ps.plif_rowparam_forward_recompute(br, u, tr, v0r, 4.0)
+    r2 = orc.plif_rowparam_fwd(f32(br), f32(u), f32(tr), f32(v0r), want_vpost=False)
+    assert np.array_equal(f32(s2), r2[0]) and np.array_equal(f32(vl2), r2[2])
