@@ -368,6 +368,7 @@ def run_inference(args):
     words = (cols + 31) // 32
     stream = _lib.stream_ptr(dev)
     p = _lib.ptr
+    tile_steps = ps._interval(cols, w["kind"] == "row")  # the tile length the public API would pick
     packed = torch.empty((T * calls, words), dtype=torch.int32, device=dev)
     v_a = torch.zeros((B, D), dtype=torch.float32, device=dev)
     v_b = torch.empty_like(v_a)
@@ -381,7 +382,7 @@ def run_inference(args):
 
         def step():
             _lib.check(L.nsb_plif_rowparam_fwd(p(beta_row), p(u), p(vth_row), p(v_a), None, p(packed), None,
-                                               None, p(v_b), T, cols, _lib.BF16, 8, stream), "rowparam_fwd")
+                                               None, p(v_b), T, cols, _lib.BF16, tile_steps, stream), "rowparam_fwd")
     else:
         inp = make_inputs(B, T * calls, D, dev, 1234 + rank)
         esz = 2 * cols
@@ -394,7 +395,7 @@ def run_inference(args):
                 _lib.check(L.nsb_plif_selective_fwd(
                     inp["beta"].data_ptr() + off, inp["cur"].data_ptr() + off, inp["gain"].data_ptr() + off,
                     inp["vth"].data_ptr() + off, p(src), None, packed.data_ptr() + c * T * words * 4, None,
-                    None, p(dst), T, cols, _lib.BF16, 8, stream), "selective_fwd")
+                    None, p(dst), T, cols, _lib.BF16, tile_steps, stream), "selective_fwd")
                 src, dst = dst, src
 
     def barrier():

@@ -65,7 +65,9 @@ int nsb_device_error_word(uint32_t* out);
  * <= 0 keeps the built-in heuristic. warps_per_cta: warps of one CTA (each
  * warp owns 32*lanes_per_thread columns and its own TMA pipeline); stages:
  * depth of each warp's shared-memory ring; lanes_per_thread: 1, 2 or 4;
- * force_direct: 1 = never use the TMA path. Process-global. */
+ * force_direct: 0 = automatic, 1 = never use the TMA path, 2 / 3 = TMA path with
+ * the ring refilled one tile late always / never (automatic: late when the
+ * launch has few warps per SM). Process-global. */
 int nsb_set_tuning(int warps_per_cta, int stages, int lanes_per_thread, int force_direct);
 
 /* How the last scan launch on this thread was configured (for benchmarks):

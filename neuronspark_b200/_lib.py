@@ -125,8 +125,11 @@ def require_cuda(*tensors) -> torch.device:
 
 
 def set_tuning(warps_per_cta: int = 0, stages: int = 0, lanes_per_thread: int = 0,
-               force_direct: bool = False) -> None:
-    """Overrides the scan launch heuristics (0 = automatic). Process-global."""
+               force_direct: int = 0) -> None:
+    """Overrides the scan launch heuristics (0 = automatic). Process-global.
+
+    ``force_direct``: 1 (or True) = no TMA; 2 / 3 = TMA with the ring refilled one
+    tile late always / never."""
     check(lib().nsb_set_tuning(warps_per_cta, stages, lanes_per_thread, int(force_direct)),
           "nsb_set_tuning")
 

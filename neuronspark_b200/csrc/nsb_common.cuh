@@ -175,6 +175,10 @@ __device__ __forceinline__ void bulk_commit_group() {
 __device__ __forceinline__ void bulk_wait_read_all() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// Same, but the most recently committed group may still be reading.
+__device__ __forceinline__ void bulk_wait_read_keep1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 // Waits until every committed bulk store of this thread has completed.
 __device__ __forceinline__ void bulk_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");

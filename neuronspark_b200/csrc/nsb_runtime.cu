@@ -157,7 +157,7 @@ int nsb_device_error_word(uint32_t* out) {
 }
 
 int nsb_set_tuning(int warps_per_cta, int stages, int lanes_per_thread, int force_direct) {
-  if (warps_per_cta > 16 || stages > 16 ||
+  if (warps_per_cta > 16 || stages > 16 || force_direct < 0 || force_direct > 3 ||
       !(lanes_per_thread <= 0 || lanes_per_thread == 1 || lanes_per_thread == 2 ||
         lanes_per_thread == 4))
     return NSB_ERR_INVALID_ARG;

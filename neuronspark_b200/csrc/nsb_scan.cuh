@@ -286,6 +286,7 @@ struct FwdParams {
   float* wlast;
   long long T, cols, words_per_row;
   int ntiles, stages;
+  int defer;  // 1: a stage is refilled one tile after its outputs were handed to TMA
   uint32_t* err;
 };
 
@@ -459,14 +460,22 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
   uint32_t phase = 0;
   bool failed = false;
 
-  auto tile = [&](auto full_tag, int nsteps) {
+  // Outputs that leave through per-step global stores (V_post, W, and dense spikes of a
+  // bit-packing kernel). When a call asks for none of them the step loop is compiled
+  // without their address arithmetic and predicated stores (they were ~40 % of the
+  // instructions of a step, which is what bounds a launch with one warp per SM).
+  const bool any_direct = p.vpost != nullptr || (MODE == MODE_RF && p.w_out != nullptr) ||
+                          (!DENSE_TMA && p.spike != nullptr);
+
+  auto tile = [&](auto full_tag, auto direct_tag, int nsteps) {
     constexpr bool FULL = decltype(full_tag)::value;
+    constexpr bool DIRECT = decltype(direct_tag)::value;
     // On the vector path dense spikes are written over the consumed drive tile in
     // shared memory and leave through one TMA store per tile (which also clips the
     // ragged edges), so the step loop carries no global address arithmetic for them.
-    ST* o_spike = (!DENSE_TMA && p.spike) ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
-    ST* o_vpost = p.vpost ? static_cast<ST*>(p.vpost) + t0 * row_elems + colj[0] : nullptr;
-    ST* o_wout = (MODE == MODE_RF && p.w_out) ? static_cast<ST*>(p.w_out) + t0 * row_elems + colj[0] : nullptr;
+    ST* o_spike = (DIRECT && !DENSE_TMA && p.spike) ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
+    ST* o_vpost = (DIRECT && p.vpost) ? static_cast<ST*>(p.vpost) + t0 * row_elems + colj[0] : nullptr;
+    ST* o_wout = (DIRECT && MODE == MODE_RF && p.w_out) ? static_cast<ST*>(p.w_out) + t0 * row_elems + colj[0] : nullptr;
     uint32_t keep[NSLOT][V];  // raw ballots of the step(s) this lane is responsible for
 #pragma unroll
     for (int q = 0; q < NSLOT; ++q)
@@ -517,14 +526,16 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
 
       if constexpr (VEC) {
         if constexpr (DENSE_TMA) IO::store_spikes(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + k * (32 * V), sp_);
-        // a thread's V columns are all valid or all invalid
-        if (!DENSE_TMA && o_spike && valid[0]) IO::store_spikes(o_spike + (size_t)k * row_elems, sp_);
-        if (o_vpost && valid[0]) IO::store(o_vpost + (size_t)k * row_elems, v);
-        if (MODE == MODE_RF && o_wout && valid[0]) IO::store(o_wout + (size_t)k * row_elems, w);
+        if constexpr (DIRECT) {
+          // a thread's V columns are all valid or all invalid
+          if (!DENSE_TMA && o_spike && valid[0]) IO::store_spikes(o_spike + (size_t)k * row_elems, sp_);
+          if (o_vpost && valid[0]) IO::store(o_vpost + (size_t)k * row_elems, v);
+          if (MODE == MODE_RF && o_wout && valid[0]) IO::store(o_wout + (size_t)k * row_elems, w);
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          if (valid[j]) {
+          if (DIRECT && valid[j]) {
             const size_t off = (size_t)k * row_elems + (colj[j] - colj[0]);
             if (o_spike) o_spike[off] = sp_[j] ? E::one() : E::zero();
             if (o_vpost) o_vpost[off] = E::from_f32(v[j]);
@@ -584,10 +595,14 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
           }
       }
     }
-    if (nsteps == C)
-      tile(std::true_type{}, C);
-    else
-      tile(std::false_type{}, nsteps);
+    if (nsteps == C) {
+      if (any_direct)
+        tile(std::true_type{}, std::true_type{}, C);
+      else
+        tile(std::true_type{}, std::false_type{}, C);
+    } else {
+      tile(std::false_type{}, std::true_type{}, nsteps);
+    }
 
     if constexpr (TMA) {
       const bool store_spikes = DENSE_TMA && p.spike != nullptr;
@@ -598,9 +613,18 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
           tma_store_2d(&tm_spike, data0 + (uint32_t)s_idx * STAGE_BYTES + MT::kDrive * TILE_BYTES, (int)col0,
                        i * C);
           bulk_commit_group();
-          bulk_wait_read_all();  // the stage is refilled next
         }
-        if (i + stages < ntiles) issue(i + stages, s_idx);
+        if (store_spikes && p.defer) {
+          // Refill the stage of the PREVIOUS tile: its store has had a whole tile of
+          // compute to read shared memory, so this wait returns at once and the warp
+          // never stands still behind its own store.
+          bulk_wait_read_keep1();
+          const int sp_idx = s_idx == 0 ? stages - 1 : s_idx - 1;
+          if (i >= 1 && i - 1 + stages < ntiles) issue(i - 1 + stages, sp_idx);
+        } else {
+          if (store_spikes) bulk_wait_read_all();  // the stage is refilled next
+          if (i + stages < ntiles) issue(i + stages, s_idx);
+        }
       }
       if (++s_idx == stages) {
         s_idx = 0;
@@ -655,6 +679,7 @@ struct BwdParams {
   float* g_vinit;
   long long T, cols;
   int ntiles, stages, has_gv, nstreams;
+  int defer;  // 1: a stage is refilled one tile after its outputs were handed to TMA
   float alpha;
   uint32_t* err;
 };
@@ -677,9 +702,12 @@ __device__ __forceinline__ void surrogate_grad(float (&sg)[V], const float (&x)[
   } else {
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-      const float e = exp2f(c1 * fabsf(x[j]));
-      const float r = __fdividef(1.0f, 1.0f + e);
-      sg[j] = alpha * e * r * r;
+      // the argument is <= 0, so the result is in [0, 1]: the hardware exponential
+      // (relative error 2^-22, tiny results flushed to zero) needs no range handling
+      float e, r;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(c1 * fabsf(x[j])));
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+      sg[j] = (alpha * e) * (r * r);
     }
   }
 }
@@ -869,8 +897,9 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
         vmul<V>(gssg, gs, sg);
         vadd<V>(gpre, gssg, tot);
         vmul<V>(gb, gpre, vprev[k]);
+        // grad v_th = -gS*sg - tot*spike = -(spike ? gpre : gS*sg)
 #pragma unroll
-        for (int j = 0; j < V; ++j) gth[j] = -gssg[j] - (xs[k][j] >= 0.0f ? tot[j] : 0.0f);
+        for (int j = 0; j < V; ++j) gth[j] = -(xs[k][j] >= 0.0f ? gpre[j] : gssg[j]);
         if constexpr (MODE == MODE_RF) {
           // coupled V/W adjoints: grad_beta = gpre*V[k-1] + aw*W[k-1], grad_omega = aw*V[k-1] - gpre*W[k-1],
           // acc_v = gpre*beta + aw*omega, acc_w = aw*beta - gpre*omega  (aw = adjoint of W arriving at step k)
@@ -997,8 +1026,15 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
         if (p.g_drive) tma_store_2d(&tmo_drive, src + MT::kDrive * TILE_BYTES, x, y);
         if (MT::kFwdStreams == 4 && p.g_gain) tma_store_2d(&tmo_gain, src + MT::kGain * TILE_BYTES, x, y);
         bulk_commit_group();
-        bulk_wait_read_all();  // the stage is refilled next
-        if (i - stages >= 0) issue(i - stages, s_idx);
+        if (p.defer) {
+          // see the forward kernel: refill the stage of the previous tile
+          bulk_wait_read_keep1();
+          const int sp_idx = s_idx == 0 ? stages - 1 : s_idx - 1;
+          if (i + 1 <= ntiles - 1 && i + 1 - stages >= 0) issue(i + 1 - stages, sp_idx);
+        } else {
+          bulk_wait_read_all();  // the stage is refilled next
+          if (i - stages >= 0) issue(i - stages, s_idx);
+        }
       }
       if (++s_idx == stages) {
         s_idx = 0;
@@ -1031,6 +1067,17 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
 // -------------------------------------------------------------- host launchers
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Whether a ring stage is refilled one tile late (so that the producer lane never
+// waits for its own TMA store to finish reading shared memory). It costs one stage
+// of prefetch depth, so it is for launches with few warps per SM, where that wait
+// is exposed; with many resident warps the other warps cover it.
+inline int defer_refill(const Tuning& tune, const Plan& plan, const DeviceInfo& dev) {
+  if (plan.stages < 3) return 0;
+  if (tune.force_direct == 2) return 1;
+  if (tune.force_direct == 3) return 0;
+  return (long long)plan.grid * plan.wpc <= 8LL * std::max(1, dev.sm_count);
+}
 
 template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
 int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, const Plan& planned) {
@@ -1080,6 +1127,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
     plan.smem = 0;
   }
   p.stages = plan.stages;
+  p.defer = defer_refill(tune, plan, dev);
   kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4]);
   NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_kernel");
   li.used_tma = TMA; li.warps_per_cta = plan.wpc; li.stages = plan.stages; li.lanes_per_thread = V;
@@ -1142,6 +1190,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
     plan.smem = 0;
   }
   p.stages = plan.stages;
+  p.defer = defer_refill(tune, plan, dev);
   kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[7], tm[8], tm[9],
                                                           tm[10]);
   NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel");
@@ -1161,7 +1210,7 @@ int launch_bwd_one(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
 // an sm_100 device; anything else takes the direct-load kernel.
 template <typename ST>
 inline bool tma_ok_common(const DeviceInfo& dev, long long T, long long cols, const Tuning& tune) {
-  if (tune.force_direct) return false;
+  if (tune.force_direct == 1) return false;
   if (dev.cc_major != 10) return false;
   if ((cols * (long long)sizeof(ST)) % 16 != 0) return false;
   if (cols >= (1ll << 31) || T >= (1ll << 31)) return false;
