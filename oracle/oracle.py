@@ -198,6 +198,93 @@ def plif_rf_bwd(beta, omega, u, vth, v_init, w_init, g_spike, g_vpost, alpha, ki
 # ---------------------------------------------------------------- codec
 
 
+# ----------------------------------------------------------- modulation
+
+MOD_ROUND = {None: 0, "f32": 0, "bf16": 1, "f16": 2}
+
+
+def modulation_fwd(raw_beta, raw_alpha, raw_th, cur, b_beta, b_alpha, b_th, v_th_min,
+                   raw_omega=None, b_omega=None, mod_round=None):
+    """(beta, u, v_th[, omega]) from raw projections ``[..., ch]`` and biases ``[ch]``
+    (atomic_ops/snn_block.py:52-76; first-order form without ``raw_omega``)."""
+    raw_beta, raw_alpha, raw_th, cur = map(_f32, (raw_beta, raw_alpha, raw_th, cur))
+    b_beta, b_alpha, b_th = map(_f32, (b_beta, b_alpha, b_th))
+    rf = raw_omega is not None
+    raw_omega = _f32(raw_omega) if rf else None
+    b_omega = _f32(b_omega) if rf else None
+    ch = b_beta.size
+    rows = cur.size // ch
+    beta, u, vth = np.empty_like(cur), np.empty_like(cur), np.empty_like(cur)
+    omega = np.empty_like(cur) if rf else None
+    lib().orc_modulation_fwd(_p(raw_beta), _p(raw_alpha), _p(raw_th), _p(raw_omega), _p(cur),
+                             _p(b_beta), _p(b_alpha), _p(b_th), _p(b_omega),
+                             ctypes.c_float(v_th_min), _i64(rows), _i64(ch),
+                             ctypes.c_int(MOD_ROUND[mod_round]), _p(beta), _p(u), _p(vth), _p(omega))
+    return (beta, u, vth, omega) if rf else (beta, u, vth)
+
+
+def modulation_bwd(raw_beta, raw_alpha, raw_th, cur, b_beta, b_alpha, b_th, g_beta, g_u, g_vth,
+                   raw_omega=None, b_omega=None, g_omega=None):
+    """Gradients of the raw projections, of I and of the biases given the gradients of the
+    modulated values. Returns a dict (bias gradients as float64 ``[ch]``)."""
+    raw_beta, raw_alpha, raw_th, cur = map(_f32, (raw_beta, raw_alpha, raw_th, cur))
+    b_beta, b_alpha, b_th = map(_f32, (b_beta, b_alpha, b_th))
+    g_beta, g_u, g_vth = map(_f32, (g_beta, g_u, g_vth))
+    rf = raw_omega is not None
+    raw_omega = _f32(raw_omega) if rf else None
+    b_omega = _f32(b_omega) if rf else None
+    g_omega = _f32(g_omega) if rf else None
+    ch = b_beta.size
+    rows = cur.size // ch
+    out = {k: np.empty_like(cur) for k in ("raw_beta", "raw_alpha", "raw_th", "cur")}
+    out["raw_omega"] = np.empty_like(cur) if rf else None
+    for k in ("b_beta", "b_alpha", "b_th"):
+        out[k] = np.zeros(ch, dtype=np.float64)
+    out["b_omega"] = np.zeros(ch, dtype=np.float64) if rf else None
+    lib().orc_modulation_bwd(_p(raw_beta), _p(raw_alpha), _p(raw_th), _p(raw_omega), _p(cur),
+                             _p(b_beta), _p(b_alpha), _p(b_th), _p(b_omega), _i64(rows), _i64(ch),
+                             _p(g_beta), _p(g_u), _p(g_vth), _p(g_omega), _p(out["raw_beta"]),
+                             _p(out["raw_alpha"]), _p(out["raw_th"]), _p(out["raw_omega"]),
+                             _p(out["cur"]), _p(out["b_beta"]), _p(out["b_alpha"]), _p(out["b_th"]),
+                             _p(out["b_omega"]))
+    return out
+
+
+def modulated_scan_fwd(raw_beta, raw_alpha, raw_th, cur, b_beta, b_alpha, b_th, v_th_min, v_init,
+                       raw_omega=None, b_omega=None, w_init=None, mod_round=None):
+    """Modulation followed by the selective scan (u-form) or the resonate-and-fire scan:
+    what ``SNNBlock.forward_parallel`` computes between its projections and ``W_out``
+    (atomic_ops/snn_block.py:237-256). Returns the scan's outputs and the modulated values."""
+    mod = modulation_fwd(raw_beta, raw_alpha, raw_th, cur, b_beta, b_alpha, b_th, v_th_min,
+                         raw_omega, b_omega, mod_round)
+    if raw_omega is None:
+        beta, u, vth = mod
+        return plif_selective_fwd(beta, u, vth, v_init), mod
+    beta, u, vth, omega = mod
+    return plif_rf_fwd(beta, omega, u, vth, v_init, w_init), mod
+
+
+def modulated_scan_bwd(raw_beta, raw_alpha, raw_th, cur, b_beta, b_alpha, b_th, v_th_min, v_init,
+                       g_spike, alpha, raw_omega=None, b_omega=None, w_init=None, kind=SURR_SIGMOID,
+                       mod_round=None):
+    """Adjoint of ``modulated_scan_fwd`` for a gradient arriving on the spikes. Returns the
+    dict of ``modulation_bwd`` plus ``v_init`` (and ``w_init``)."""
+    mod = modulation_fwd(raw_beta, raw_alpha, raw_th, cur, b_beta, b_alpha, b_th, v_th_min,
+                         raw_omega, b_omega, mod_round)
+    if raw_omega is None:
+        beta, u, vth = mod
+        gb, gu, gt, gv = plif_selective_bwd(beta, u, vth, v_init, g_spike, None, alpha, kind)
+        out = modulation_bwd(raw_beta, raw_alpha, raw_th, cur, b_beta, b_alpha, b_th, gb, gu, gt)
+        out["v_init"] = gv
+        return out
+    beta, u, vth, omega = mod
+    gb, go, gu, gt, gv, gw = plif_rf_bwd(beta, omega, u, vth, v_init, w_init, g_spike, None, alpha, kind)
+    out = modulation_bwd(raw_beta, raw_alpha, raw_th, cur, b_beta, b_alpha, b_th, gb, gu, gt,
+                         raw_omega, b_omega, go)
+    out["v_init"], out["w_init"] = gv, gw
+    return out
+
+
 def fp16_encode(emb):
     """[B,S,D] values -> [S*16,B,D] frames in {0,1}."""
     emb = _f32(emb)

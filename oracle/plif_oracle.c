@@ -670,3 +670,165 @@ void orc_li_bwd(const float *g_out, const float *x, const float *gain,
     }
   }
 }
+
+/* ------------------------------------------------------------------ */
+/* Modulation: raw projections + per-channel biases -> scan inputs.    */
+/* Follows atomic_ops/snn_block.py:52-76 (_fused_modulation_rf) and    */
+/* archive/atomic_ops_v75_pre/snn_block.py:41-47 (_fused_modulation):  */
+/*   beta  = sigmoid(raw_beta + b_beta)                                */
+/*   alpha = softplus(raw_alpha + b_alpha)      (threshold 20)         */
+/*   v_th  = v_th_min + |raw_th + b_th|                                */
+/*   omega = softplus(raw_omega + b_omega)                 (RF only)   */
+/*   r2 = beta*beta + omega*omega;                         (RF only)   */
+/*   scale = r2 > 0.999^2 ? 0.999 * rsqrt(max(r2, 1e-12)) : 1          */
+/*   beta *= scale; omega *= scale                                     */
+/*   u = alpha * I                                                     */
+/* Every +, * is one rounded fp32 operation in the order written; the  */
+/* transcendental functions are evaluated in double and rounded once   */
+/* (the reference's eager CPU evaluation agrees with that to 1-2 ulp,  */
+/* which is what the golden-vector test allows).                       */
+/* rows = T*batch, ch = channels; biases are [ch]. raw_omega == NULL   */
+/* selects the first-order form. mod_round: 0 = keep fp32, 1 = round   */
+/* beta/u/v_th/omega to bf16, 2 = to fp16 (a reference run with bf16   */
+/* parameters materialises them in that dtype).                        */
+/* ------------------------------------------------------------------ */
+static inline float orc_sigmoidf(float z) { return (float)(1.0 / (1.0 + exp(-(double)z))); }
+static inline float orc_softplusf(float z) {
+  return z > 20.0f ? z : (float)log1p(exp((double)z));
+}
+static inline float round_f16(float f);
+static inline float orc_mod_round(float f, int mode);
+
+void orc_modulation_fwd(const float *raw_beta, const float *raw_alpha,
+                        const float *raw_th, const float *raw_omega,
+                        const float *cur, const float *b_beta,
+                        const float *b_alpha, const float *b_th,
+                        const float *b_omega, float v_th_min, int64_t rows,
+                        int64_t ch, int mod_round, float *beta, float *u,
+                        float *vth, float *omega) {
+  const float rmax = 0.999f;
+  const float rmax_sq = (float)(0.999 * 0.999);
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    for (int64_t c = 0; c < ch; ++c) {
+      const int64_t i = r * ch + c;
+      float b = orc_sigmoidf(raw_beta[i] + b_beta[c]);
+      const float a = orc_softplusf(raw_alpha[i] + b_alpha[c]);
+      const float th = v_th_min + fabsf(raw_th[i] + b_th[c]);
+      if (raw_omega) {
+        float o = orc_softplusf(raw_omega[i] + b_omega[c]);
+        const float bb = b * b, oo = o * o;
+        const float r2 = bb + oo;
+        float scale = 1.0f;
+        if (r2 > rmax_sq) {
+          const float cl = r2 < 1e-12f ? 1e-12f : r2;
+          const float rs = (float)(1.0 / sqrt((double)cl));
+          scale = rmax * rs;
+        }
+        b = b * scale;
+        o = o * scale;
+        omega[i] = orc_mod_round(o, mod_round);
+      }
+      beta[i] = orc_mod_round(b, mod_round);
+      u[i] = orc_mod_round(a * cur[i], mod_round);
+      vth[i] = orc_mod_round(th, mod_round);
+    }
+  }
+}
+
+/* Adjoint of the above in double. Upstream gradients g_beta, g_u, g_vth,    */
+/* g_omega (NULL with the first-order form) are those of the modulated      */
+/* values; outputs are the gradients of the raw projections and of I, and   */
+/* the bias gradients summed over rows ([ch], double accumulation).         */
+/*   d sigmoid = s(1-s);  d softplus(z) = sigmoid(z);  d|z| = sign(z)        */
+/*   scale active: beta = c*b0/r, omega = c*o0/r with r = sqrt(b0^2+o0^2):   */
+/*     g_b0 = scale*(g_beta - (g_beta*b0 + g_omega*o0)*b0/r2), same for o0   */
+void orc_modulation_bwd(const float *raw_beta, const float *raw_alpha,
+                        const float *raw_th, const float *raw_omega,
+                        const float *cur, const float *b_beta,
+                        const float *b_alpha, const float *b_th,
+                        const float *b_omega, int64_t rows, int64_t ch,
+                        const float *g_beta, const float *g_u,
+                        const float *g_vth, const float *g_omega,
+                        float *g_raw_beta, float *g_raw_alpha, float *g_raw_th,
+                        float *g_raw_omega, float *g_cur, double *gb_beta,
+                        double *gb_alpha, double *gb_th, double *gb_omega) {
+  const double rmax = (double)0.999f;
+  const float rmax_sq = (float)(0.999 * 0.999);
+  for (int64_t c = 0; c < ch; ++c) {
+    gb_beta[c] = gb_alpha[c] = gb_th[c] = 0.0;
+    if (raw_omega) gb_omega[c] = 0.0;
+  }
+#pragma omp parallel for schedule(static)
+  for (int64_t c = 0; c < ch; ++c) {
+    double sb = 0.0, sa = 0.0, st = 0.0, so = 0.0;
+    for (int64_t r = 0; r < rows; ++r) {
+      const int64_t i = r * ch + c;
+      const float zb = raw_beta[i] + b_beta[c];
+      const float za = raw_alpha[i] + b_alpha[c];
+      const float zt = raw_th[i] + b_th[c];
+      const double b0 = 1.0 / (1.0 + exp(-(double)zb));
+      const double alpha = za > 20.0f ? (double)za : log1p(exp((double)za));
+      double gb0 = g_beta[i];
+      if (raw_omega) {
+        const float zo = raw_omega[i] + b_omega[c];
+        const double o0 = zo > 20.0f ? (double)zo : log1p(exp((double)zo));
+        /* the branch is taken on the fp32 value the forward compares */
+        const float b0f = (float)b0, o0f = (float)o0;
+        const float r2f = b0f * b0f + o0f * o0f;
+        double go0 = g_omega[i];
+        if (r2f > rmax_sq) {
+          const double r2 = b0 * b0 + o0 * o0;
+          const double scale = rmax / sqrt(r2);
+          const double dot = (gb0 * b0 + go0 * o0) / r2;
+          const double nb = scale * (gb0 - dot * b0);
+          const double no = scale * (go0 - dot * o0);
+          gb0 = nb;
+          go0 = no;
+        }
+        const double dsp = zo > 20.0f ? 1.0 : 1.0 / (1.0 + exp(-(double)zo));
+        const double gzo = go0 * dsp;
+        g_raw_omega[i] = (float)gzo;
+        so += gzo;
+      }
+      const double gzb = gb0 * b0 * (1.0 - b0);
+      const double dsa = za > 20.0f ? 1.0 : 1.0 / (1.0 + exp(-(double)za));
+      const double gza = (double)g_u[i] * (double)cur[i] * dsa;
+      const double sgn = zt > 0.0f ? 1.0 : (zt < 0.0f ? -1.0 : 0.0);
+      const double gzt = (double)g_vth[i] * sgn;
+      g_raw_beta[i] = (float)gzb;
+      g_raw_alpha[i] = (float)gza;
+      g_raw_th[i] = (float)gzt;
+      g_cur[i] = (float)((double)g_u[i] * alpha);
+      sb += gzb;
+      sa += gza;
+      st += gzt;
+    }
+    gb_beta[c] = sb;
+    gb_alpha[c] = sa;
+    gb_th[c] = st;
+    if (raw_omega) gb_omega[c] = so;
+  }
+}
+
+static inline float round_f16(float f) {
+  const uint16_t h = f32_to_f16_bits(f);
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  const uint32_t e = (h >> 10) & 0x1Fu, m = h & 0x3FFu;
+  float out;
+  if (e == 0) {
+    out = ldexpf((float)m, -24);
+  } else if (e == 31) {
+    out = m ? NAN : INFINITY;
+  } else {
+    out = ldexpf((float)(m | 0x400u), (int)e - 25);
+  }
+  uint32_t bits;
+  memcpy(&bits, &out, 4);
+  bits |= sign;
+  memcpy(&out, &bits, 4);
+  return out;
+}
+static inline float orc_mod_round(float f, int mode) {
+  return mode == 1 ? round_bf16(f) : (mode == 2 ? round_f16(f) : f);
+}

@@ -26,6 +26,11 @@ What each fixture is produced by:
   codec_*         fp16_encode, fp16_decode (+ autograd), _binary_residual_fwd,
                   _binary_residual_naive, _BinaryEncodeSTE from
                   atomic_ops/fp16_codec.py, in fp32 and bf16.
+  modulation_*    _fused_modulation_rf (atomic_ops/snn_block.py:52-76) and
+                  _fused_modulation (archive/atomic_ops_v75_pre/snn_block.py:41-47),
+                  taken out of their files by name with ``ast`` (the modules need
+                  SpikingJelly to import) and run eagerly, without their
+                  torch.compile decorator, + autograd.
   li_*            the PyTorch fallback of LateralInhibition.forward
                   (atomic_ops/lateral_inhibition.py:208-212) + autograd.
 """
@@ -79,6 +84,21 @@ def seq_loop(beta, u, vth, v_init, alpha, rowparam=False, gain=None, cur=None):
         S.append(SigmoidSurrogate.apply(v_pre - th, alpha))
         V.append(v)
     return torch.stack(S), torch.stack(V)
+
+
+def function_from_source(rel, name):
+    """Compiles one top-level function of a reference file, without its decorators, in a
+    namespace that has only torch and torch.nn.functional."""
+    import ast
+    tree = ast.parse((REF / rel).read_text())
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name == name:
+            node.decorator_list = []
+            mod = ast.Module(body=[node], type_ignores=[])
+            ns = {"torch": torch, "F": torch.nn.functional}
+            exec(compile(ast.fix_missing_locations(mod), str(REF / rel), "exec"), ns)
+            return ns[name]
+    raise KeyError(f"{name} not found in {rel}")
 
 
 def npz(name, **arrs):
@@ -262,6 +282,43 @@ def main():
         residual=codec._binary_residual_fwd(fab, fbb),
         frames_e=fe.bfloat16(), decoded_e=codec.fp16_decode(fe.bfloat16(), 4, 16),
         residual_e=codec._binary_residual_fwd(fe.bfloat16(), fe2.bfloat16()))
+
+    # ---- modulation: raw projections + biases -> beta, u, v_th (, omega)
+    mod_rf = function_from_source("atomic_ops/snn_block.py", "_fused_modulation_rf")
+    mod_1 = function_from_source("archive/atomic_ops_v75_pre/snn_block.py", "_fused_modulation")
+    torch.manual_seed(77)
+    rows, ch = 96, 40
+    names = ("raw_beta", "raw_alpha", "raw_th", "raw_omega", "cur")
+    raw = {n: torch.randn(rows, ch) * 1.5 for n in names}
+    # softplus threshold (z > 20), saturated sigmoid, |z| at exactly 0, stability rescale on and off
+    raw["raw_alpha"][0, :8] = torch.tensor([19.9, 20.0, 20.1, 25.0, -25.0, -90.0, 0.0, 60.0])
+    raw["raw_beta"][1, :8] = torch.tensor([30.0, -30.0, 88.0, -88.0, -104.0, 0.0, 5.0, 9.0])
+    raw["raw_omega"][2, :8] = torch.tensor([-30.0, 21.0, 0.0, -5.0, 3.0, -2.0, 0.5, -0.5])
+    raw["raw_th"][3, :4] = torch.tensor([0.0, -0.0, 1e-8, -1e-8])
+    bias = {"b_beta": 2.0 + 0.5 * torch.randn(ch), "b_alpha": 0.3 * torch.randn(ch),
+            "b_th": 0.3 * torch.randn(ch), "b_omega": -1.0 + 0.5 * torch.randn(ch)}
+    bias["b_alpha"][:8] = 0.0
+    bias["b_beta"][:8] = 0.0
+    bias["b_omega"][:8] = 0.0
+    bias["b_th"][:4] = 0.0
+    v_th_min = 0.1
+    leaves = {k: v.clone().requires_grad_() for k, v in {**raw, **bias}.items()}
+    beta, u, vth, omega = mod_rf(leaves["raw_beta"], leaves["b_beta"], leaves["raw_alpha"], leaves["b_alpha"],
+                                 leaves["raw_th"], leaves["b_th"], v_th_min, leaves["cur"],
+                                 leaves["raw_omega"], leaves["b_omega"])
+    ups = {n: torch.randn(rows, ch) for n in ("g_beta", "g_u", "g_vth", "g_omega")}
+    ((beta * ups["g_beta"]).sum() + (u * ups["g_u"]).sum() + (vth * ups["g_vth"]).sum()
+     + (omega * ups["g_omega"]).sum()).backward()
+    npz("modulation_rf", **raw, **bias, v_th_min=np.float64(v_th_min), beta=beta, u=u, vth=vth, omega=omega,
+        **ups, **{f"grad_{k}": v.grad for k, v in leaves.items()})
+    leaves = {k: v.clone().requires_grad_() for k, v in {**raw, **bias}.items() if "omega" not in k}
+    beta, u, vth = mod_1(leaves["raw_beta"], leaves["b_beta"], leaves["raw_alpha"], leaves["b_alpha"],
+                         leaves["raw_th"], leaves["b_th"], v_th_min, leaves["cur"])
+    ((beta * ups["g_beta"]).sum() + (u * ups["g_u"]).sum() + (vth * ups["g_vth"]).sum()).backward()
+    npz("modulation_first_order", **{k: v for k, v in raw.items() if "omega" not in k},
+        **{k: v for k, v in bias.items() if "omega" not in k}, v_th_min=np.float64(v_th_min),
+        beta=beta, u=u, vth=vth, **{k: v for k, v in ups.items() if "omega" not in k},
+        **{f"grad_{k}": v.grad for k, v in leaves.items()})
 
     # ---- lateral inhibition fallback (atomic_ops/lateral_inhibition.py:208-212)
     torch.manual_seed(42)

@@ -136,3 +136,46 @@ def test_rf_scan(golden):
     s1, v1, _, _, _ = orc.plif_rf_fwd(g["beta"], z, g["u"], g["vth"], g["v_init"], z[0])
     s2, v2, _ = orc.plif_selective_fwd(g["beta"], g["u"], g["vth"], g["v_init"])
     assert np.array_equal(s1, s2) and np.array_equal(v1, v2)
+
+
+def _ulp_distance(a, b):
+    ai = np.asarray(a, np.float32).view(np.int32).astype(np.int64)
+    bi = np.asarray(b, np.float32).view(np.int32).astype(np.int64)
+    return np.abs(ai - bi)
+
+
+@pytest.mark.parametrize("name", ["modulation_rf", "modulation_first_order"])
+def test_modulation(golden, name):
+    """The reference evaluates sigmoid / softplus / rsqrt with PyTorch's vectorised CPU
+    routines (1-2 ulp each); the oracle rounds a double evaluation once. Allowed distance:
+    4 ulp on the modulated values, |z| + v_th_min exact; gradients 1e-6 of the largest."""
+    g = golden(name)
+    rf = "raw_omega" in g
+    extra = dict(raw_omega=g["raw_omega"], b_omega=g["b_omega"]) if rf else {}
+    out = orc.modulation_fwd(g["raw_beta"], g["raw_alpha"], g["raw_th"], g["cur"], g["b_beta"], g["b_alpha"],
+                             g["b_th"], float(g["v_th_min"]), **extra)
+    for mine, ref in zip(out, ("beta", "u", "vth", "omega")):
+        assert _ulp_distance(mine, g[ref]).max() <= 4, ref
+    assert np.array_equal(out[2], g["vth"])
+    if rf:
+        extra["g_omega"] = g["g_omega"]
+        # the stability rescale is exercised on both sides of its threshold
+        r2 = g["beta"].astype(np.float64) ** 2 + g["omega"].astype(np.float64) ** 2
+        assert (r2 > 0.9979).any() and (r2 < 0.99).any()
+    grads = orc.modulation_bwd(g["raw_beta"], g["raw_alpha"], g["raw_th"], g["cur"], g["b_beta"], g["b_alpha"],
+                               g["b_th"], g["g_beta"], g["g_u"], g["g_vth"], **extra)
+    for k, v in grads.items():
+        if v is not None:
+            assert rel_err(v, g["grad_" + k]) < 1e-6, k
+    # rounding the modulated values to bf16 is the fp32 result rounded once
+    import torch
+    outb = orc.modulation_fwd(g["raw_beta"], g["raw_alpha"], g["raw_th"], g["cur"], g["b_beta"], g["b_alpha"],
+                              g["b_th"], float(g["v_th_min"]), mod_round="bf16",
+                              **{k: v for k, v in extra.items() if k != "g_omega"})
+    for a, b in zip(out, outb):
+        assert np.array_equal(torch.from_numpy(a).bfloat16().float().numpy(), b)
+    outh = orc.modulation_fwd(g["raw_beta"], g["raw_alpha"], g["raw_th"], g["cur"], g["b_beta"], g["b_alpha"],
+                              g["b_th"], float(g["v_th_min"]), mod_round="f16",
+                              **{k: v for k, v in extra.items() if k != "g_omega"})
+    for a, b in zip(out, outh):
+        assert np.array_equal(torch.from_numpy(a).half().float().numpy(), b)
