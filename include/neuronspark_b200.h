@@ -272,6 +272,73 @@ int nsb_lateral_inhibition_bwd_static(const void* g_out, const void* x, const vo
                                       void* g_x, float* g_gain, int64_t rows, int64_t D,
                                       float eps, int dtype, int gain_dtype, void* stream);
 
+/*
+ * Modulation + scan in one pass. Replaces the pair the reference runs between
+ * its input projections and W_out in SNNBlock.forward_parallel: the inductor
+ * kernel of _fused_modulation_rf (atomic_ops/snn_block.py:52-76, called at
+ * :237-241) followed by rf_plif_parallel_forward_recompute (:252-256); with
+ * raw_omega == NULL, the first-order pair _fused_modulation + plif_parallel_forward
+ * (archive/atomic_ops_v75_pre/snn_block.py:41-47, 186-199).
+ *   beta  = sigmoid(raw_beta + b_beta)       alpha = softplus(raw_alpha + b_alpha)
+ *   v_th  = v_th_min + |raw_th + b_th|       omega = softplus(raw_omega + b_omega)
+ *   r2 = beta^2 + omega^2; if r2 > 0.999^2: (beta, omega) *= 0.999 * rsqrt(r2)
+ *   u = alpha * I
+ * and then the selective scan (u-form) or the resonate-and-fire scan on those
+ * values, which stay in registers: beta, u, v_th, omega are never written to
+ * memory (the reference writes and re-reads these four [T, cols] tensors, the
+ * largest of a layer, and their gradients).
+ * raw_* and cur are [T, cols] in `dtype`; the biases are fp32 [channels] with
+ * cols = batch * channels (column c uses bias c % channels); v_init / w_init
+ * [cols] fp32. Outputs as nsb_plif_rf_fwd, without v_post / w_out.
+ * ckpt_interval is 8 or 32.
+ * Numerics: all arithmetic in fp32; sigmoid, softplus and rsqrt use the
+ * hardware approximations, relative error < 1e-6 against correct rounding;
+ * the modulated values are not rounded to `dtype` (the reference rounds them
+ * when its parameters are bf16).
+ */
+int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
+                           const void* raw_omega, const void* cur, const float* b_beta,
+                           const float* b_alpha, const float* b_th, const float* b_omega,
+                           float v_th_min, int64_t channels, const float* v_init,
+                           const float* w_init, void* spike_dense, uint32_t* spike_packed,
+                           float* v_ckpt, float* w_ckpt, float* v_last, float* w_last, int64_t T,
+                           int64_t cols, int dtype, int ckpt_interval, void* stream);
+
+/* Floats of scratch nsb_plif_modulated_bwd needs when any bias gradient is asked for. */
+int64_t nsb_plif_modulated_bwd_scratch_floats(int64_t cols);
+
+/*
+ * Reverse pass of nsb_plif_modulated_fwd for a gradient arriving on the spikes:
+ * recomputes modulation and membrane state tile by tile from the checkpoints,
+ * runs the scan's adjoint and pushes it through the modulation in registers.
+ * Outputs (each optional): gradients of the raw projections and of I
+ * ([T, cols], `dtype`), of the biases (fp32 [channels], summed over time and
+ * batch in a fixed order; needs `scratch`), of v_init / w_init (fp32 [cols]).
+ * Replaces the autograd backward of the two reference functions named above.
+ */
+int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
+                           const void* raw_omega, const void* cur, const float* b_beta,
+                           const float* b_alpha, const float* b_th, const float* b_omega,
+                           float v_th_min, int64_t channels, const float* v_ckpt,
+                           const float* w_ckpt, const void* g_spike, void* g_raw_beta,
+                           void* g_raw_alpha, void* g_raw_th, void* g_raw_omega, void* g_cur,
+                           float* g_b_beta, float* g_b_alpha, float* g_b_th, float* g_b_omega,
+                           float* scratch, float* g_vinit, float* g_winit, int64_t T, int64_t cols,
+                           int dtype, int ckpt_interval, int surrogate, float alpha, void* stream);
+
+/*
+ * The modulation alone, written out: beta, u, v_th (and omega when raw_omega is
+ * given) as [rows, channels] tensors in dtype_out (NSB_F32, or dtype_in). A
+ * drop-in for the reference's _fused_modulation(_rf) functions in code that
+ * keeps the unfused scan; it evaluates exactly what the fused scan evaluates
+ * in registers.
+ */
+int nsb_modulation_fwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
+                       const void* raw_omega, const void* cur, const float* b_beta,
+                       const float* b_alpha, const float* b_th, const float* b_omega,
+                       float v_th_min, int64_t rows, int64_t channels, void* beta, void* u,
+                       void* v_th, void* omega, int dtype_in, int dtype_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -25,18 +25,26 @@
 #include <type_traits>
 
 #include "nsb_common.cuh"
+#include "nsb_modulation.cuh"
 
 namespace nsb {
 
+// MODE_MOD / MODE_RFMOD are MODE_AI / MODE_RF with the modulation fused into the load path: they
+// stream the RAW projections (raw_beta, I, raw_alpha, raw_th [, raw_omega]) and form beta, u = alpha*I,
+// v_th (, omega) per element in registers (nsb_modulation.cuh).
 // MODE_RF is the second-order resonate-and-fire scan: it streams beta, u, omega, v_th
 // (omega in the slot the gain*cur form uses for the gain) and carries two states, V and W.
-enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3 };
+enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3, MODE_MOD = 4, MODE_RFMOD = 5 };
 
 struct FwdArgs {
   const void* beta = nullptr;   // streams ([T, cols], stream dtype)
   const void* drive = nullptr;  // u (MODE_U / MODE_ROW) or cur (MODE_AI)
-  const void* gain = nullptr;   // MODE_AI: gain; MODE_RF: omega
+  const void* gain = nullptr;   // MODE_AI: gain; MODE_RF: omega; modulated modes: raw_alpha
   const void* vth = nullptr;
+  const void* extra = nullptr;  // MODE_RFMOD: raw_omega
+  const float* bias[4] = {nullptr, nullptr, nullptr, nullptr};  // modulated modes: b_beta, b_alpha, b_th, b_omega ([channels])
+  long long channels = 0;                                         // cols is a multiple of it
+  float v_th_min = 0.0f;
   const float* beta_row = nullptr;  // MODE_ROW
   const float* vth_row = nullptr;
   const float* v_init = nullptr;
@@ -60,6 +68,12 @@ struct BwdArgs {
   const void* drive = nullptr;
   const void* gain = nullptr;
   const void* vth = nullptr;
+  const void* extra = nullptr;  // MODE_RFMOD: raw_omega
+  const float* bias[4] = {nullptr, nullptr, nullptr, nullptr};
+  long long channels = 0;
+  float v_th_min = 0.0f;
+  void* g_extra = nullptr;                                 // MODE_RFMOD: grad raw_omega
+  float* g_bias[4] = {nullptr, nullptr, nullptr, nullptr};  // modulated modes: per-column sums over time ([cols])
   const float* beta_row = nullptr;
   const float* vth_row = nullptr;
   const float* ckpt = nullptr;
@@ -89,6 +103,13 @@ int scan_fwd_f16(const FwdArgs& a);
 int scan_bwd_f32(const BwdArgs& a);
 int scan_bwd_bf16(const BwdArgs& a);
 int scan_bwd_f16(const BwdArgs& a);
+// The modulated modes (MODE_MOD, MODE_RFMOD) are instantiated in their own translation units.
+int scan_mod_fwd_f32(const FwdArgs& a);
+int scan_mod_fwd_bf16(const FwdArgs& a);
+int scan_mod_fwd_f16(const FwdArgs& a);
+int scan_mod_bwd_f32(const BwdArgs& a);
+int scan_mod_bwd_bf16(const BwdArgs& a);
+int scan_mod_bwd_f16(const BwdArgs& a);
 
 // ----------------------------------------------------------------- launch plan
 
@@ -271,7 +292,10 @@ __device__ __forceinline__ void vfma(float (&r)[V], const float (&a)[V], const f
 // ------------------------------------------------------------------- forward
 
 struct FwdParams {
-  const void* s[4];  // stream base pointers (direct path), order as in smem
+  const void* s[5];  // stream base pointers (direct path), order as in smem
+  const float* bias[4];  // modulated modes: b_beta, b_alpha, b_th, b_omega
+  long long channels;
+  float v_th_min;
   const float* beta_row;
   const float* vth_row;
   const float* v_init;
@@ -292,13 +316,17 @@ struct FwdParams {
 
 template <int MODE>
 struct ModeTraits {
-  static constexpr int kFwdStreams = MODE == MODE_ROW ? 1 : ((MODE == MODE_AI || MODE == MODE_RF) ? 4 : 3);
+  static constexpr bool kSecond = MODE == MODE_RF || MODE == MODE_RFMOD;  // carries the second state W
+  static constexpr bool kMod = MODE == MODE_MOD || MODE == MODE_RFMOD;    // modulation fused into the loads
+  static constexpr int kFwdStreams =
+      MODE == MODE_ROW ? 1 : (MODE == MODE_RFMOD ? 5 : ((MODE == MODE_AI || MODE == MODE_RF || MODE == MODE_MOD) ? 4 : 3));
   // index of each role inside the stage / pointer table (roles that a mode
   // does not stream alias slot 0 and are never read)
   static constexpr int kBeta = 0;
   static constexpr int kDrive = MODE == MODE_ROW ? 0 : 1;
-  static constexpr int kGain = (MODE == MODE_AI || MODE == MODE_RF) ? 2 : 0;
-  static constexpr int kVth = MODE == MODE_ROW ? 0 : ((MODE == MODE_AI || MODE == MODE_RF) ? 3 : 2);
+  static constexpr int kGain = kFwdStreams >= 4 ? 2 : 0;
+  static constexpr int kVth = MODE == MODE_ROW ? 0 : (kFwdStreams >= 4 ? 3 : 2);
+  static constexpr int kOmega = MODE == MODE_RFMOD ? 4 : (MODE == MODE_RF ? 2 : 0);
 };
 
 // One charge / fire / soft-reset step on the V lanes of a thread:
@@ -364,6 +392,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
                                 const __grid_constant__ CUtensorMap tm1,
                                 const __grid_constant__ CUtensorMap tm2,
                                 const __grid_constant__ CUtensorMap tm3,
+                                const __grid_constant__ CUtensorMap tm4,
                                 const __grid_constant__ CUtensorMap tm_spike) {
   using MT = ModeTraits<MODE>;
   using E = Elem<ST>;
@@ -395,12 +424,25 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     colj[j] = col0 + V * lane + j;
     valid[j] = colj[j] < p.cols;
     v[j] = valid[j] ? p.v_init[colj[j]] : 0.0f;
-    w[j] = (MODE == MODE_RF && valid[j]) ? p.w_init[colj[j]] : 0.0f;
+    w[j] = (MT::kSecond && valid[j]) ? p.w_init[colj[j]] : 0.0f;
     brow[j] = 0.0f;
     trow[j] = 0.0f;
     if (MODE == MODE_ROW && valid[j]) {
       brow[j] = p.beta_row[colj[j]];
       trow[j] = p.vth_row[colj[j]];
+    }
+  }
+  mod::Bias<V> bias = {};
+  if constexpr (MT::kMod) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      if (valid[j]) {
+        const long long ch = colj[j] % p.channels;
+        bias.beta[j] = p.bias[0][ch];
+        bias.alpha[j] = p.bias[1][ch];
+        bias.th[j] = p.bias[2][ch];
+        if (MT::kSecond) bias.omega[j] = p.bias[3][ch];
+      }
     }
   }
 
@@ -430,6 +472,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
       if (NS > 1) tma_load_2d(dst + TILE_BYTES, &tm1, (int)col0, tile * C, bar);
       if (NS > 2) tma_load_2d(dst + 2 * TILE_BYTES, &tm2, (int)col0, tile * C, bar);
       if (NS > 3) tma_load_2d(dst + 3 * TILE_BYTES, &tm3, (int)col0, tile * C, bar);
+      if (NS > 4) tma_load_2d(dst + 4 * TILE_BYTES, &tm4, (int)col0, tile * C, bar);
     }
   };
 
@@ -464,7 +507,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
   // bit-packing kernel). When a call asks for none of them the step loop is compiled
   // without their address arithmetic and predicated stores (they were ~40 % of the
   // instructions of a step, which is what bounds a launch with one warp per SM).
-  const bool any_direct = p.vpost != nullptr || (MODE == MODE_RF && p.w_out != nullptr) ||
+  const bool any_direct = p.vpost != nullptr || (MT::kSecond && p.w_out != nullptr) ||
                           (!DENSE_TMA && p.spike != nullptr);
 
   auto tile = [&](auto full_tag, auto direct_tag, int nsteps) {
@@ -475,7 +518,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     // ragged edges), so the step loop carries no global address arithmetic for them.
     ST* o_spike = (DIRECT && !DENSE_TMA && p.spike) ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
     ST* o_vpost = (DIRECT && p.vpost) ? static_cast<ST*>(p.vpost) + t0 * row_elems + colj[0] : nullptr;
-    ST* o_wout = (DIRECT && MODE == MODE_RF && p.w_out) ? static_cast<ST*>(p.w_out) + t0 * row_elems + colj[0] : nullptr;
+    ST* o_wout = (DIRECT && MT::kSecond && p.w_out) ? static_cast<ST*>(p.w_out) + t0 * row_elems + colj[0] : nullptr;
     uint32_t keep[NSLOT][V];  // raw ballots of the step(s) this lane is responsible for
 #pragma unroll
     for (int q = 0; q < NSLOT; ++q)
@@ -498,7 +541,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
           }
         }
       }
-      float b[V], th[V], dr[V], x[V];
+      float b[V], th[V], dr[V], om[V], x[V];
       bool sp_[V];
       fetch(MT::kDrive, k, dr);
       if constexpr (MODE == MODE_ROW) {
@@ -516,9 +559,18 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
         fetch(MT::kGain, k, gn);
         vmul<V>(dr, gn, dr);
       }
-      if constexpr (MODE == MODE_RF) {
-        float om[V];
-        fetch(MT::kGain, k, om);
+      if constexpr (MODE == MODE_RF || MODE == MODE_RFMOD) fetch(MT::kOmega, k, om);
+      if constexpr (MT::kMod) {
+        // b, th, om, dr hold the raw projections and I: turn them into beta, v_th, omega, u
+        float ra[V];
+        fetch(MT::kGain, k, ra);
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+          mod::forward<MT::kSecond>(b[j], ra[j], th[j], MT::kSecond ? om[j] : 0.0f, dr[j], bias.beta[j],
+                                    bias.alpha[j], bias.th[j], bias.omega[j], p.v_th_min, b[j], dr[j], th[j],
+                                    om[j]);
+      }
+      if constexpr (MT::kSecond) {
         rf_step<V>(v, w, b, om, dr, th, x, sp_);
       } else {
         plif_step<V>(v, b, dr, th, x, sp_);
@@ -530,7 +582,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
           // a thread's V columns are all valid or all invalid
           if (!DENSE_TMA && o_spike && valid[0]) IO::store_spikes(o_spike + (size_t)k * row_elems, sp_);
           if (o_vpost && valid[0]) IO::store(o_vpost + (size_t)k * row_elems, v);
-          if (MODE == MODE_RF && o_wout && valid[0]) IO::store(o_wout + (size_t)k * row_elems, w);
+          if (MT::kSecond && o_wout && valid[0]) IO::store(o_wout + (size_t)k * row_elems, w);
         }
       } else {
 #pragma unroll
@@ -539,7 +591,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
             const size_t off = (size_t)k * row_elems + (colj[j] - colj[0]);
             if (o_spike) o_spike[off] = sp_[j] ? E::one() : E::zero();
             if (o_vpost) o_vpost[off] = E::from_f32(v[j]);
-            if (MODE == MODE_RF && o_wout) o_wout[off] = E::from_f32(w[j]);
+            if (MT::kSecond && o_wout) o_wout[off] = E::from_f32(w[j]);
           }
         }
       }
@@ -585,13 +637,13 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     if (p.ckpt) {
       if constexpr (VEC) {
         if (valid[0]) VecIO<float, V>::store(p.ckpt + (long long)i * row_elems + colj[0], v);
-        if (MODE == MODE_RF && valid[0]) VecIO<float, V>::store(p.ckpt_w + (long long)i * row_elems + colj[0], w);
+        if (MT::kSecond && valid[0]) VecIO<float, V>::store(p.ckpt_w + (long long)i * row_elems + colj[0], w);
       } else {
 #pragma unroll
         for (int j = 0; j < V; ++j)
           if (valid[j]) {
             p.ckpt[(long long)i * row_elems + colj[j]] = v[j];
-            if (MODE == MODE_RF) p.ckpt_w[(long long)i * row_elems + colj[j]] = w[j];
+            if (MT::kSecond) p.ckpt_w[(long long)i * row_elems + colj[j]] = w[j];
           }
       }
     }
@@ -647,7 +699,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
   for (int j = 0; j < V; ++j)
     if (valid[j]) {
       p.vlast[colj[j]] = v[j];
-      if (MODE == MODE_RF) p.wlast[colj[j]] = w[j];
+      if (MT::kSecond) p.wlast[colj[j]] = w[j];
     }
 }
 
@@ -664,7 +716,12 @@ constexpr int kBwdMaxRegsV4 = 255;
 constexpr int kBwdMaxThreads = 256;
 
 struct BwdParams {
-  const void* s[6];  // stream base pointers (direct path), smem order
+  const void* s[7];  // stream base pointers (direct path), smem order
+  const float* bias[4];  // modulated modes: b_beta, b_alpha, b_th, b_omega
+  long long channels;
+  float v_th_min;
+  void* g_extra;     // MODE_RFMOD: grad raw_omega
+  float* g_bias[4];  // modulated modes: per-column sums over time of the raw gradients
   const float* beta_row;
   const float* vth_row;
   const float* ckpt;
@@ -713,16 +770,18 @@ __device__ __forceinline__ void surrogate_grad(float (&sg)[V], const float (&x)[
 }
 
 template <typename ST, int MODE, int SURR, int V, int C, bool TMA, bool HAS_GV>
-__global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwdMaxRegs) : ((TMA && C * V == 32 && MODE != MODE_RF) ? kBwdMaxRegsV4 : 255)) plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tm0,
+__global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == MODE_MOD) ? 128 : (MODE == MODE_RFMOD ? 168 : kBwdMaxRegs)) : ((TMA && C * V == 32 && MODE != MODE_RF && MODE != MODE_RFMOD) ? kBwdMaxRegsV4 : 255)) plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tm0,
                                 const __grid_constant__ CUtensorMap tm1,
                                 const __grid_constant__ CUtensorMap tm2,
                                 const __grid_constant__ CUtensorMap tm3,
                                 const __grid_constant__ CUtensorMap tm4,
                                 const __grid_constant__ CUtensorMap tm5,
+                                const __grid_constant__ CUtensorMap tm6,
                                 const __grid_constant__ CUtensorMap tmo_beta,
                                 const __grid_constant__ CUtensorMap tmo_drive,
                                 const __grid_constant__ CUtensorMap tmo_gain,
-                                const __grid_constant__ CUtensorMap tmo_vth) {
+                                const __grid_constant__ CUtensorMap tmo_vth,
+                                const __grid_constant__ CUtensorMap tmo_omega) {
   using MT = ModeTraits<MODE>;
   using E = Elem<ST>;
   using IO = VecIO<ST, V>;
@@ -756,6 +815,24 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
       trow[j] = p.vth_row[colj[j]];
     }
   }
+  // modulated modes: biases of this thread's channels, and the sums over time of the raw
+  // gradients (= bias gradients per column; accb / acct take those of beta and v_th)
+  mod::Bias<V> bias = {};
+  float acca[V], acco[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acca[j] = acco[j] = 0.0f;
+  if constexpr (MT::kMod) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      if (valid[j]) {
+        const long long ch = colj[j] % p.channels;
+        bias.beta[j] = p.bias[0][ch];
+        bias.alpha[j] = p.bias[1][ch];
+        bias.th[j] = p.bias[2][ch];
+        if (MT::kSecond) bias.omega[j] = p.bias[3][ch];
+      }
+    }
+  }
 
   const int stages = p.stages;
   uint32_t bar0 = 0, data0 = 0;
@@ -786,6 +863,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
       if (nstreams > 3) tma_load_2d(dst + 3 * TILE_BYTES, &tm3, x, y, bar);
       if (nstreams > 4) tma_load_2d(dst + 4 * TILE_BYTES, &tm4, x, y, bar);
       if (nstreams > 5) tma_load_2d(dst + 5 * TILE_BYTES, &tm5, x, y, bar);
+      if (nstreams > 6) tma_load_2d(dst + 6 * TILE_BYTES, &tm6, x, y, bar);
     }
   };
 
@@ -823,24 +901,24 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
   if constexpr (TMA) {
     if (ntiles > 0 && valid[0]) {
       VecIO<float, V>::load(p.ckpt + (long long)(ntiles - 1) * row_elems + colj[0], vnext);
-      if (MODE == MODE_RF) VecIO<float, V>::load(p.ckpt_w + (long long)(ntiles - 1) * row_elems + colj[0], wnext);
+      if (MT::kSecond) VecIO<float, V>::load(p.ckpt_w + (long long)(ntiles - 1) * row_elems + colj[0], wnext);
     }
   }
 
   auto tile = [&](auto full_tag, int nsteps) {
     constexpr bool FULL = decltype(full_tag)::value;
     // recompute the tile forward, keeping V[k-1] and x[k] = V_pre[k] - V_th[k]
-    float vprev[C][V], xs[C][V], wprev[MODE == MODE_RF ? C : 1][V];
+    float vprev[C][V], xs[C][V], wprev[MT::kSecond ? C : 1][V];
 #pragma unroll
     for (int k = 0; k < C; ++k) {
 #pragma unroll
       for (int j = 0; j < V; ++j) {
         vprev[k][j] = v[j];
-        if (MODE == MODE_RF) wprev[MODE == MODE_RF ? k : 0][j] = w[j];
+        if (MT::kSecond) wprev[MT::kSecond ? k : 0][j] = w[j];
         xs[k][j] = 0.0f;
       }
       if (FULL || k < nsteps) {
-        float b[V], th[V], dr[V];
+        float b[V], th[V], dr[V], om[V];
         bool s_[V];
         fetch(MT::kDrive, k, dr);
         if constexpr (MODE == MODE_ROW) {
@@ -858,9 +936,17 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
           fetch(MT::kGain, k, gn);
           vmul<V>(dr, gn, dr);
         }
-        if constexpr (MODE == MODE_RF) {
-          float om[V];
-          fetch(MT::kGain, k, om);
+        if constexpr (MT::kSecond) fetch(MT::kOmega, k, om);
+        if constexpr (MT::kMod) {
+          float ra[V];
+          fetch(MT::kGain, k, ra);
+#pragma unroll
+          for (int j = 0; j < V; ++j)
+            mod::forward<MT::kSecond>(b[j], ra[j], th[j], MT::kSecond ? om[j] : 0.0f, dr[j], bias.beta[j],
+                                      bias.alpha[j], bias.th[j], bias.omega[j], p.v_th_min, b[j], dr[j], th[j],
+                                      om[j]);
+        }
+        if constexpr (MT::kSecond) {
           rf_step<V>(v, w, b, om, dr, th, xs[k], s_);
         } else {
           plif_step<V>(v, b, dr, th, xs[k], s_);
@@ -877,13 +963,14 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
     ST* o_beta = (!TMA && MODE != MODE_ROW && p.g_beta) ? static_cast<ST*>(p.g_beta) + tile_off : nullptr;
     ST* o_vth = (!TMA && MODE != MODE_ROW && p.g_vth) ? static_cast<ST*>(p.g_vth) + tile_off : nullptr;
     ST* o_drive = (!TMA && p.g_drive) ? static_cast<ST*>(p.g_drive) + tile_off : nullptr;
-    ST* o_gain = (!TMA && MT::kFwdStreams == 4 && p.g_gain) ? static_cast<ST*>(p.g_gain) + tile_off : nullptr;
+    ST* o_gain = (!TMA && MT::kFwdStreams >= 4 && p.g_gain) ? static_cast<ST*>(p.g_gain) + tile_off : nullptr;
+    ST* o_omega = (!TMA && MODE == MODE_RFMOD && p.g_extra) ? static_cast<ST*>(p.g_extra) + tile_off : nullptr;
     ST* wsp = const_cast<ST*>(sp);
 #pragma unroll
     for (int kk = 0; kk < C; ++kk) {
       const int k = C - 1 - kk;
       if (FULL || k < nsteps) {
-        float sg[V], gs[V], tot[V], gssg[V], gpre[V], b[V], gb[V], gth[V], gd[V], gg[V];
+        float sg[V], gs[V], tot[V], gssg[V], gpre[V], b[V], gb[V], gth[V], gd[V], gg[V], go[V];
         surrogate_grad<SURR, V>(sg, xs[k], alpha, c1, c2);
         fetch(kGS, k, gs);
         if (has_gv) {
@@ -905,10 +992,10 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
           // acc_v = gpre*beta + aw*omega, acc_w = aw*beta - gpre*omega  (aw = adjoint of W arriving at step k)
           float om[V];
           fetch(MT::kBeta, k, b);
-          fetch(MT::kGain, k, om);
+          fetch(MT::kOmega, k, om);
 #pragma unroll
           for (int j = 0; j < V; ++j) {
-            const float vp_ = vprev[k][j], wp_ = wprev[MODE == MODE_RF ? k : 0][j], aw = accw[j];
+            const float vp_ = vprev[k][j], wp_ = wprev[MT::kSecond ? k : 0][j], aw = accw[j];
             gb[j] = fmaf(aw, wp_, gb[j]);
             gg[j] = aw * vp_ - gpre[j] * wp_;
             gd[j] = gpre[j];
@@ -916,7 +1003,60 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
             accw[j] = aw * b[j] - gpre[j] * om[j];
           }
         }
-        if constexpr (MODE == MODE_ROW) {
+        if constexpr (MT::kMod) {
+          // Modulated modes: recompute the modulation of step k together with its derivative
+          // factors, push the scan's adjoints (w.r.t. beta, omega, u, v_th) through it and leave
+          // the gradients of the raw projections and of I in gb / go / gg / gth / gd.
+          //   d sigmoid = s(1-s); d softplus(z) = sigmoid(z); d|z| = sign(z);
+          //   rescale active (beta, omega) = scale*(b0, o0), scale = 0.999/r:
+          //     G_b0 = scale*(G_beta - dot*b0), G_o0 = scale*(G_omega - dot*o0), dot = (G_beta*b0 + G_omega*o0)/r2
+          float rb[V], ra[V], rt[V], ro[V], ci[V];
+          fetch(MT::kBeta, k, rb);
+          fetch(MT::kGain, k, ra);
+          fetch(MT::kVth, k, rt);
+          fetch(MT::kDrive, k, ci);
+          if constexpr (MT::kSecond) fetch(MT::kOmega, k, ro);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const float zb = __fadd_rn(rb[j], bias.beta[j]);
+            const float b0 = mod::sigmoid(zb);
+            const float za = __fadd_rn(ra[j], bias.alpha[j]);
+            const float ta = mod::exp_neg_abs(za);
+            const float al = mod::softplus_from_t(za, ta);
+            const float sa = mod::sigmoid_from_t(za, ta);
+            const float zt = __fadd_rn(rt[j], bias.th[j]);
+            float Gb = gb[j];
+            if constexpr (MT::kSecond) {
+              const float zo = __fadd_rn(ro[j], bias.omega[j]);
+              const float to = mod::exp_neg_abs(zo);
+              const float o0 = mod::softplus_from_t(zo, to);
+              const float so = mod::sigmoid_from_t(zo, to);
+              float be = b0, om_ = o0, r2;
+              const float scale = mod::rf_rescale(be, om_, r2);
+              const float vp_ = vprev[k][j], wp_ = wprev[MT::kSecond ? k : 0][j], aw = accw[j];
+              Gb = fmaf(aw, wp_, Gb);
+              float Go = aw * vp_ - gpre[j] * wp_;
+              acc[j] = gpre[j] * be + aw * om_;
+              accw[j] = aw * be - gpre[j] * om_;
+              if (r2 > mod::kRmaxSq) {
+                const float dot = (Gb * b0 + Go * o0) * mod::rcp_approx(r2);
+                Gb = scale * (Gb - dot * b0);
+                Go = scale * (Go - dot * o0);
+              }
+              go[j] = Go * so;
+              acco[j] += go[j];
+            } else {
+              acc[j] = gpre[j] * b0;
+            }
+            gb[j] = Gb * (b0 * (1.0f - b0));
+            gg[j] = gpre[j] * ci[j] * sa;
+            gd[j] = gpre[j] * al;
+            gth[j] = zt > 0.0f ? gth[j] : (zt < 0.0f ? -gth[j] : 0.0f);
+            accb[j] += gb[j];
+            acca[j] += gg[j];
+            acct[j] += gth[j];
+          }
+        } else if constexpr (MODE == MODE_ROW) {
 #pragma unroll
           for (int j = 0; j < V; ++j) b[j] = brow[j];
           vadd<V>(accb, accb, gb);
@@ -931,14 +1071,15 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
           vmul<V>(gd, gpre, gn);
           vmul<V>(gg, gpre, dr);
         }
-        if constexpr (MODE != MODE_RF) vmul<V>(acc, gpre, b);
+        if constexpr (MODE != MODE_RF && !MT::kMod) vmul<V>(acc, gpre, b);
 
         if constexpr (TMA) {
           if constexpr (MODE != MODE_ROW) {
             IO::store(wsp + MT::kBeta * TILE_ELEMS + k * (32 * V), gb);
             IO::store(wsp + MT::kVth * TILE_ELEMS + k * (32 * V), gth);
           }
-          if constexpr (MODE == MODE_AI || MODE == MODE_RF) {
+          if constexpr (MODE == MODE_RFMOD) IO::store(wsp + MT::kOmega * TILE_ELEMS + k * (32 * V), go);
+          if constexpr (MT::kFwdStreams >= 4) {
             IO::store(wsp + MT::kDrive * TILE_ELEMS + k * (32 * V), gd);
             IO::store(wsp + MT::kGain * TILE_ELEMS + k * (32 * V), gg);
           } else {
@@ -956,7 +1097,8 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
             put(o_beta, gb);
             put(o_vth, gth);
           }
-          if constexpr (MODE == MODE_AI || MODE == MODE_RF) {
+          if constexpr (MODE == MODE_RFMOD) put(o_omega, go);
+          if constexpr (MT::kFwdStreams >= 4) {
             put(o_drive, gd);
             put(o_gain, gg);
           } else {
@@ -989,7 +1131,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
       }
       if (i > 0 && valid[0]) {
         VecIO<float, V>::load(p.ckpt + (long long)(i - 1) * row_elems + colj[0], vnext);
-        if (MODE == MODE_RF) VecIO<float, V>::load(p.ckpt_w + (long long)(i - 1) * row_elems + colj[0], wnext);
+        if (MT::kSecond) VecIO<float, V>::load(p.ckpt_w + (long long)(i - 1) * row_elems + colj[0], wnext);
       }
     } else {
 #pragma unroll
@@ -1006,7 +1148,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
 #pragma unroll
       for (int j = 0; j < V; ++j) {
         v[j] = valid[j] ? p.ckpt[(long long)i * row_elems + colj[j]] : 0.0f;
-        w[j] = (MODE == MODE_RF && valid[j]) ? p.ckpt_w[(long long)i * row_elems + colj[j]] : 0.0f;
+        w[j] = (MT::kSecond && valid[j]) ? p.ckpt_w[(long long)i * row_elems + colj[j]] : 0.0f;
       }
     }
 
@@ -1024,7 +1166,8 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
         if (MODE != MODE_ROW && p.g_beta) tma_store_2d(&tmo_beta, src + MT::kBeta * TILE_BYTES, x, y);
         if (MODE != MODE_ROW && p.g_vth) tma_store_2d(&tmo_vth, src + MT::kVth * TILE_BYTES, x, y);
         if (p.g_drive) tma_store_2d(&tmo_drive, src + MT::kDrive * TILE_BYTES, x, y);
-        if (MT::kFwdStreams == 4 && p.g_gain) tma_store_2d(&tmo_gain, src + MT::kGain * TILE_BYTES, x, y);
+        if (MT::kFwdStreams >= 4 && p.g_gain) tma_store_2d(&tmo_gain, src + MT::kGain * TILE_BYTES, x, y);
+        if (MODE == MODE_RFMOD && p.g_extra) tma_store_2d(&tmo_omega, src + MT::kOmega * TILE_BYTES, x, y);
         bulk_commit_group();
         if (p.defer) {
           // see the forward kernel: refill the stage of the previous tile
@@ -1055,7 +1198,13 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? (MODE == MODE_RF ? 128 : kBwd
   for (int j = 0; j < V; ++j) {
     if (valid[j]) {
       if (p.g_vinit) p.g_vinit[colj[j]] = acc[j];
-      if (MODE == MODE_RF && p.g_winit) p.g_winit[colj[j]] = accw[j];
+      if (MT::kSecond && p.g_winit) p.g_winit[colj[j]] = accw[j];
+      if (MT::kMod) {
+        if (p.g_bias[0]) p.g_bias[0][colj[j]] = accb[j];
+        if (p.g_bias[1]) p.g_bias[1][colj[j]] = acca[j];
+        if (p.g_bias[2]) p.g_bias[2][colj[j]] = acct[j];
+        if (MT::kSecond && p.g_bias[3]) p.g_bias[3][colj[j]] = acco[j];
+      }
       if (MODE == MODE_ROW) {
         if (p.g_beta_row) p.g_beta_row[colj[j]] = accb[j];
         if (p.g_vth_row) p.g_vth_row[colj[j]] = acct[j];
@@ -1085,15 +1234,17 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   constexpr int NS = MT::kFwdStreams;
   auto kern = plif_fwd_kernel<ST, MODE, PACKED, V, C, TMA>;
   FwdParams p = {};
-  const void* streams[4] = {nullptr, nullptr, nullptr, nullptr};
+  const void* streams[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
   if (MODE == MODE_ROW) {
     streams[0] = a.drive;
-  } else if (MODE == MODE_AI || MODE == MODE_RF) {
-    streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.gain; streams[3] = a.vth;
+  } else if (NS >= 4) {
+    streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.gain; streams[3] = a.vth; streams[4] = a.extra;
   } else {
     streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.vth;
   }
-  for (int i = 0; i < 4; ++i) p.s[i] = streams[i];
+  for (int i = 0; i < 5; ++i) p.s[i] = streams[i];
+  for (int i = 0; i < 4; ++i) p.bias[i] = a.bias[i];
+  p.channels = a.channels > 0 ? a.channels : 1; p.v_th_min = a.v_th_min;
   p.beta_row = a.beta_row; p.vth_row = a.vth_row; p.v_init = a.v_init; p.w_init = a.w_init;
   p.spike = a.spike; p.packed = a.packed; p.vpost = a.vpost; p.w_out = a.w_out; p.ckpt = a.ckpt;
   p.ckpt_w = a.ckpt_w; p.vlast = a.vlast; p.wlast = a.wlast;
@@ -1102,7 +1253,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   p.err = device_error_word_ptr();
 
   const long long nwarps = (a.cols + 32 * V - 1) / (32 * V);
-  CUtensorMap tm[5];
+  CUtensorMap tm[6];
   memset(tm, 0, sizeof tm);
   Plan plan;
   LaunchInfo& li = last_launch();
@@ -1113,7 +1264,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
       if (r != NSB_OK) return r;
     }
     if (!PACKED && a.spike) {
-      int r = make_tensor_map_2d(&tm[4], a.spike, Elem<ST>::kDtype, (uint64_t)a.T, (uint64_t)a.cols, C, 32 * V);
+      int r = make_tensor_map_2d(&tm[5], a.spike, Elem<ST>::kDtype, (uint64_t)a.T, (uint64_t)a.cols, C, 32 * V);
       if (r != NSB_OK) return r;
     }
     plan = planned;
@@ -1128,7 +1279,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   }
   p.stages = plan.stages;
   p.defer = defer_refill(tune, plan, dev);
-  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4]);
+  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
   NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_kernel");
   li.used_tma = TMA; li.warps_per_cta = plan.wpc; li.stages = plan.stages; li.lanes_per_thread = V;
   li.grid = plan.grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = 1;
@@ -1141,11 +1292,11 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   constexpr int NF = MT::kFwdStreams;
   auto kern = plif_bwd_kernel<ST, MODE, SURR, V, C, TMA, HAS_GV>;
   BwdParams p = {};
-  const void* streams[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  const void* streams[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   if (MODE == MODE_ROW) {
     streams[0] = a.drive;
-  } else if (MODE == MODE_AI || MODE == MODE_RF) {
-    streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.gain; streams[3] = a.vth;
+  } else if (NF >= 4) {
+    streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.gain; streams[3] = a.vth; streams[4] = a.extra;
   } else {
     streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.vth;
   }
@@ -1153,7 +1304,12 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   streams[NF + 1] = a.g_vpost;
   const int has_gv = a.g_vpost != nullptr;
   const int nstreams = NF + 1 + has_gv;
-  for (int i = 0; i < 6; ++i) p.s[i] = streams[i];
+  for (int i = 0; i < 7; ++i) p.s[i] = streams[i];
+  for (int i = 0; i < 4; ++i) {
+    p.bias[i] = a.bias[i];
+    p.g_bias[i] = a.g_bias[i];
+  }
+  p.channels = a.channels > 0 ? a.channels : 1; p.v_th_min = a.v_th_min; p.g_extra = a.g_extra;
   p.beta_row = a.beta_row; p.vth_row = a.vth_row; p.ckpt = a.ckpt; p.ckpt_w = a.ckpt_w; p.g_winit = a.g_winit;
   p.g_beta = a.g_beta; p.g_drive = a.g_drive; p.g_gain = a.g_gain; p.g_vth = a.g_vth;
   p.g_beta_row = a.g_beta_row; p.g_vth_row = a.g_vth_row; p.g_vinit = a.g_vinit;
@@ -1163,7 +1319,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   p.err = device_error_word_ptr();
 
   const long long nwarps = (a.cols + 32 * V - 1) / (32 * V);
-  CUtensorMap tm[11];
+  CUtensorMap tm[12];
   memset(tm, 0, sizeof tm);
   Plan plan;
   if (TMA) {
@@ -1172,8 +1328,8 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
                                  32 * V);
       if (r != NSB_OK) return r;
     }
-    const void* outs[4] = {a.g_beta, a.g_drive, a.g_gain, a.g_vth};
-    for (int i = 0; i < 4; ++i) {
+    const void* outs[5] = {a.g_beta, a.g_drive, a.g_gain, a.g_vth, a.g_extra};
+    for (int i = 0; i < 5; ++i) {
       if (!outs[i]) continue;
       int r = make_tensor_map_2d(&tm[7 + i], outs[i], Elem<ST>::kDtype, (uint64_t)a.T, (uint64_t)a.cols, C,
                                  32 * V);
@@ -1191,8 +1347,8 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   }
   p.stages = plan.stages;
   p.defer = defer_refill(tune, plan, dev);
-  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[7], tm[8], tm[9],
-                                                          tm[10]);
+  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8],
+                                                          tm[9], tm[10], tm[11]);
   NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel");
   LaunchInfo& li = last_launch();
   li.used_tma = TMA; li.warps_per_cta = plan.wpc; li.stages = plan.stages; li.lanes_per_thread = V;
@@ -1322,6 +1478,98 @@ int scan_bwd_dispatch(const BwdArgs& a) {
   NSB_BWD_DIRECT_S(MODE_U) NSB_BWD_DIRECT_S(MODE_AI) NSB_BWD_DIRECT_S(MODE_ROW) NSB_BWD_DIRECT_S(MODE_RF)
 #undef NSB_BWD_DIRECT_S
 #undef NSB_BWD_DIRECT
+  return NSB_ERR_INVALID_ARG;
+}
+
+// Modulated modes: tiles of 8 steps (1, 2 or 4 lanes per thread) or 32 steps (1 lane); the
+// fused scan returns spikes only, so there is no V_post gradient stream.
+template <typename ST>
+int scan_mod_fwd_dispatch(const FwdArgs& a) {
+  DeviceInfo dev;
+  int r = get_device_info(&dev);
+  if (r != NSB_OK) return r;
+  if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
+  const Tuning tune = get_tuning();
+  bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
+  const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.extra, a.spike, a.ckpt, a.ckpt_w};
+  for (const void* q : ptrs) tma = tma && aligned16(q);
+  const bool packed = a.packed != nullptr;
+  const int C = a.tile;
+  Plan plan;
+  if (tma) {
+    PlanQuery q;
+    q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
+    q.nstreams = a.mode == MODE_RFMOD ? 5 : 4;
+    q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;
+    plan = plan_scan(dev, q, tune);
+  }
+  const int V = plan.lanes;
+#define NSB_MFWD_CASE(MODE_, PACKED_, V_, C_)                                          \
+  if (a.mode == MODE_ && packed == PACKED_ && V == V_ && C == C_)                      \
+    return launch_fwd_one<ST, MODE_, PACKED_, V_, C_, true>(a, dev, tune, plan);
+#define NSB_MFWD_CASES(MODE_, PACKED_)                                                 \
+  NSB_MFWD_CASE(MODE_, PACKED_, 1, 8) NSB_MFWD_CASE(MODE_, PACKED_, 2, 8)              \
+  NSB_MFWD_CASE(MODE_, PACKED_, 4, 8) NSB_MFWD_CASE(MODE_, PACKED_, 1, 32)
+  if (tma) {
+    NSB_MFWD_CASES(MODE_MOD, false) NSB_MFWD_CASES(MODE_MOD, true)
+    NSB_MFWD_CASES(MODE_RFMOD, false) NSB_MFWD_CASES(MODE_RFMOD, true)
+    return NSB_ERR_INVALID_ARG;
+  }
+#undef NSB_MFWD_CASES
+#undef NSB_MFWD_CASE
+#define NSB_MFWD_DIRECT(MODE_, C_)                                                     \
+  if (a.mode == MODE_ && C == C_)                                                      \
+    return packed ? launch_fwd_one<ST, MODE_, true, 1, C_, false>(a, dev, tune, plan)  \
+                  : launch_fwd_one<ST, MODE_, false, 1, C_, false>(a, dev, tune, plan);
+  NSB_MFWD_DIRECT(MODE_MOD, 8) NSB_MFWD_DIRECT(MODE_MOD, 32)
+  NSB_MFWD_DIRECT(MODE_RFMOD, 8) NSB_MFWD_DIRECT(MODE_RFMOD, 32)
+#undef NSB_MFWD_DIRECT
+  return NSB_ERR_INVALID_ARG;
+}
+
+template <typename ST>
+int scan_mod_bwd_dispatch(const BwdArgs& a) {
+  DeviceInfo dev;
+  int r = get_device_info(&dev);
+  if (r != NSB_OK) return r;
+  if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
+  if (a.g_vpost) return NSB_ERR_INVALID_ARG;
+  const Tuning tune = get_tuning();
+  bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
+  const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.extra, a.ckpt, a.ckpt_w, a.g_spike,
+                        a.g_beta, a.g_drive, a.g_gain, a.g_vth, a.g_extra};
+  for (const void* q : ptrs) tma = tma && aligned16(q);
+  const int C = a.tile;
+  Plan plan;
+  if (tma) {
+    PlanQuery q;
+    q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
+    q.nstreams = (a.mode == MODE_RFMOD ? 5 : 4) + 1;
+    q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : 1;
+    plan = plan_scan(dev, q, tune);
+  }
+  const int V = plan.lanes;
+#define NSB_MBWD_CASE(MODE_, SURR_, V_, C_)                                            \
+  if (a.mode == MODE_ && a.surrogate == SURR_ && V == V_ && C == C_)                   \
+    return launch_bwd_impl<ST, MODE_, SURR_, V_, C_, true, false>(a, dev, tune, plan);
+#define NSB_MBWD_CASES(MODE_, SURR_)                                                   \
+  NSB_MBWD_CASE(MODE_, SURR_, 1, 8) NSB_MBWD_CASE(MODE_, SURR_, 2, 8)                  \
+  NSB_MBWD_CASE(MODE_, SURR_, 4, 8) NSB_MBWD_CASE(MODE_, SURR_, 1, 32)
+  if (tma) {
+    NSB_MBWD_CASES(MODE_MOD, NSB_SURR_SIGMOID) NSB_MBWD_CASES(MODE_MOD, NSB_SURR_ATAN)
+    NSB_MBWD_CASES(MODE_RFMOD, NSB_SURR_SIGMOID) NSB_MBWD_CASES(MODE_RFMOD, NSB_SURR_ATAN)
+    return NSB_ERR_INVALID_ARG;
+  }
+#undef NSB_MBWD_CASES
+#undef NSB_MBWD_CASE
+#define NSB_MBWD_DIRECT(MODE_, SURR_, C_)                                              \
+  if (a.mode == MODE_ && a.surrogate == SURR_ && C == C_)                              \
+    return launch_bwd_impl<ST, MODE_, SURR_, 1, C_, false, false>(a, dev, tune, plan);
+  NSB_MBWD_DIRECT(MODE_MOD, NSB_SURR_SIGMOID, 8) NSB_MBWD_DIRECT(MODE_MOD, NSB_SURR_ATAN, 8)
+  NSB_MBWD_DIRECT(MODE_MOD, NSB_SURR_SIGMOID, 32) NSB_MBWD_DIRECT(MODE_MOD, NSB_SURR_ATAN, 32)
+  NSB_MBWD_DIRECT(MODE_RFMOD, NSB_SURR_SIGMOID, 8) NSB_MBWD_DIRECT(MODE_RFMOD, NSB_SURR_ATAN, 8)
+  NSB_MBWD_DIRECT(MODE_RFMOD, NSB_SURR_SIGMOID, 32) NSB_MBWD_DIRECT(MODE_RFMOD, NSB_SURR_ATAN, 32)
+#undef NSB_MBWD_DIRECT
   return NSB_ERR_INVALID_ARG;
 }
 

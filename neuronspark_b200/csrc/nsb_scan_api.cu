@@ -25,6 +25,36 @@ int run_bwd(const nsb::BwdArgs& a, int dtype) {
   }
 }
 
+int run_mod_fwd(const nsb::FwdArgs& a, int dtype) {
+  switch (dtype) {
+    case NSB_F32: return nsb::scan_mod_fwd_f32(a);
+    case NSB_BF16: return nsb::scan_mod_fwd_bf16(a);
+    default: return nsb::scan_mod_fwd_f16(a);
+  }
+}
+int run_mod_bwd(const nsb::BwdArgs& a, int dtype) {
+  switch (dtype) {
+    case NSB_F32: return nsb::scan_mod_bwd_f32(a);
+    case NSB_BF16: return nsb::scan_mod_bwd_bf16(a);
+    default: return nsb::scan_mod_bwd_f16(a);
+  }
+}
+
+// out[n][c] = sum over b of in[n][b*ch + c], b ascending (deterministic).
+__global__ void sum_over_batch_kernel(const float* __restrict__ in, float* __restrict__ out0,
+                                      float* __restrict__ out1, float* __restrict__ out2,
+                                      float* __restrict__ out3, long long batch, long long ch, int n) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * ch) return;
+  const int which = (int)(idx / ch);
+  const long long c = idx % ch;
+  const float* src = in + (long long)which * batch * ch + c;
+  float acc = 0.0f;
+  for (long long b = 0; b < batch; ++b) acc += src[b * ch];
+  float* out = which == 0 ? out0 : (which == 1 ? out1 : (which == 2 ? out2 : out3));
+  if (out) out[c] = acc;
+}
+
 }  // namespace
 
 extern "C" {
@@ -202,6 +232,108 @@ int nsb_plif_rf_bwd(const void* beta, const void* omega, const void* u, const vo
   a.T = T; a.cols = cols; a.mode = nsb::MODE_RF; a.tile = ckpt_interval;
   a.surrogate = surrogate; a.alpha = alpha; a.stream = st;
   return run_bwd(a, dtype);
+}
+
+int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
+                           const void* raw_omega, const void* cur, const float* b_beta,
+                           const float* b_alpha, const float* b_th, const float* b_omega, float v_th_min,
+                           int64_t channels, const float* v_init, const float* w_init, void* spike_dense,
+                           uint32_t* spike_packed, float* v_ckpt, float* w_ckpt, float* v_last,
+                           float* w_last, int64_t T, int64_t cols, int dtype, int ckpt_interval,
+                           void* stream) {
+  if (T < 0 || cols < 0 || !dtype_ok(dtype) || (ckpt_interval != 8 && ckpt_interval != 32))
+    return NSB_ERR_INVALID_ARG;
+  if (cols == 0) return NSB_OK;
+  if (channels <= 0 || cols % channels != 0) return NSB_ERR_INVALID_ARG;
+  const bool rf = raw_omega != nullptr || b_omega != nullptr;  // (an empty raw_omega may be NULL)
+  if (!v_init || !v_last || !b_beta || !b_alpha || !b_th) return NSB_ERR_INVALID_ARG;
+  if (rf && (!b_omega || !w_init || !w_last)) return NSB_ERR_INVALID_ARG;
+  if (rf && (v_ckpt == nullptr) != (w_ckpt == nullptr)) return NSB_ERR_INVALID_ARG;
+  const void* fp[] = {v_init, w_init, v_last, w_last, v_ckpt, w_ckpt, spike_packed, b_beta, b_alpha, b_th, b_omega};
+  for (const void* p : fp)
+    if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    NSB_CUDA_TRY(cudaMemcpyAsync(v_last, v_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice, st), "copy v_init");
+    if (rf)
+      NSB_CUDA_TRY(cudaMemcpyAsync(w_last, w_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice, st),
+                   "copy w_init");
+    return NSB_OK;
+  }
+  if (!raw_beta || !raw_alpha || !raw_th || !cur || (rf && !raw_omega)) return NSB_ERR_INVALID_ARG;
+  const void* ep[] = {raw_beta, raw_alpha, raw_th, raw_omega, cur, spike_dense};
+  for (const void* p : ep)
+    if (!elem_aligned(p, dtype)) return NSB_ERR_INVALID_ARG;
+  nsb::FwdArgs a;
+  a.beta = raw_beta; a.drive = cur; a.gain = raw_alpha; a.vth = raw_th; a.extra = raw_omega;
+  a.bias[0] = b_beta; a.bias[1] = b_alpha; a.bias[2] = b_th; a.bias[3] = b_omega;
+  a.channels = channels; a.v_th_min = v_th_min;
+  a.v_init = v_init; a.w_init = w_init; a.spike = spike_dense; a.packed = spike_packed;
+  a.ckpt = v_ckpt; a.ckpt_w = w_ckpt; a.vlast = v_last; a.wlast = w_last;
+  a.T = T; a.cols = cols; a.mode = rf ? nsb::MODE_RFMOD : nsb::MODE_MOD; a.tile = ckpt_interval;
+  a.stream = st;
+  return run_mod_fwd(a, dtype);
+}
+
+int64_t nsb_plif_modulated_bwd_scratch_floats(int64_t cols) { return cols > 0 ? 4 * cols : 0; }
+
+int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
+                           const void* raw_omega, const void* cur, const float* b_beta,
+                           const float* b_alpha, const float* b_th, const float* b_omega, float v_th_min,
+                           int64_t channels, const float* v_ckpt, const float* w_ckpt, const void* g_spike,
+                           void* g_raw_beta, void* g_raw_alpha, void* g_raw_th, void* g_raw_omega,
+                           void* g_cur, float* g_b_beta, float* g_b_alpha, float* g_b_th, float* g_b_omega,
+                           float* scratch, float* g_vinit, float* g_winit, int64_t T, int64_t cols,
+                           int dtype, int ckpt_interval, int surrogate, float alpha, void* stream) {
+  if (T < 0 || cols < 0 || !dtype_ok(dtype) || (ckpt_interval != 8 && ckpt_interval != 32))
+    return NSB_ERR_INVALID_ARG;
+  if (surrogate != NSB_SURR_SIGMOID && surrogate != NSB_SURR_ATAN) return NSB_ERR_INVALID_ARG;
+  if (cols == 0) return NSB_OK;
+  if (channels <= 0 || cols % channels != 0) return NSB_ERR_INVALID_ARG;
+  const bool rf = raw_omega != nullptr || b_omega != nullptr;  // (an empty raw_omega may be NULL)
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const void* fp[] = {v_ckpt, w_ckpt, g_vinit, g_winit, b_beta, b_alpha, b_th, b_omega,
+                      g_b_beta, g_b_alpha, g_b_th, g_b_omega, scratch};
+  for (const void* p : fp)
+    if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
+  if (T == 0) {
+    float* zc[] = {g_vinit, rf ? g_winit : nullptr};
+    for (float* q : zc)
+      if (q) NSB_CUDA_TRY(cudaMemsetAsync(q, 0, sizeof(float) * cols, st), "memset state grads");
+    float* zb[] = {g_b_beta, g_b_alpha, g_b_th, rf ? g_b_omega : nullptr};
+    for (float* q : zb)
+      if (q) NSB_CUDA_TRY(cudaMemsetAsync(q, 0, sizeof(float) * channels, st), "memset bias grads");
+    return NSB_OK;
+  }
+  if (!raw_beta || !raw_alpha || !raw_th || !cur || !b_beta || !b_alpha || !b_th || !v_ckpt || !g_spike)
+    return NSB_ERR_INVALID_ARG;
+  if (rf && (!raw_omega || !b_omega || !w_ckpt)) return NSB_ERR_INVALID_ARG;
+  const bool want_bias = g_b_beta || g_b_alpha || g_b_th || (rf && g_b_omega);
+  if (want_bias && !scratch) return NSB_ERR_INVALID_ARG;
+  const void* ep[] = {raw_beta, raw_alpha, raw_th, raw_omega, cur, g_spike,
+                      g_raw_beta, g_raw_alpha, g_raw_th, g_raw_omega, g_cur};
+  for (const void* p : ep)
+    if (!elem_aligned(p, dtype)) return NSB_ERR_INVALID_ARG;
+  nsb::BwdArgs a;
+  a.beta = raw_beta; a.drive = cur; a.gain = raw_alpha; a.vth = raw_th; a.extra = raw_omega;
+  a.bias[0] = b_beta; a.bias[1] = b_alpha; a.bias[2] = b_th; a.bias[3] = b_omega;
+  a.channels = channels; a.v_th_min = v_th_min;
+  a.ckpt = v_ckpt; a.ckpt_w = w_ckpt; a.g_spike = g_spike;
+  a.g_beta = g_raw_beta; a.g_drive = g_cur; a.g_gain = g_raw_alpha; a.g_vth = g_raw_th; a.g_extra = g_raw_omega;
+  const int nb = rf ? 4 : 3;
+  if (want_bias)
+    for (int i = 0; i < nb; ++i) a.g_bias[i] = scratch + (long long)i * cols;
+  a.g_vinit = g_vinit; a.g_winit = g_winit;
+  a.T = T; a.cols = cols; a.mode = rf ? nsb::MODE_RFMOD : nsb::MODE_MOD; a.tile = ckpt_interval;
+  a.surrogate = surrogate; a.alpha = alpha; a.stream = st;
+  int r = run_mod_bwd(a, dtype);
+  if (r != NSB_OK || !want_bias) return r;
+  const long long items = (long long)nb * channels;
+  const int threads = 128;
+  sum_over_batch_kernel<<<(int)((items + threads - 1) / threads), threads, 0, st>>>(
+      scratch, g_b_beta, g_b_alpha, g_b_th, rf ? g_b_omega : nullptr, cols / channels, channels, nb);
+  NSB_CUDA_TRY(cudaGetLastError(), "launch sum_over_batch_kernel");
+  return NSB_OK;
 }
 
 }  // extern "C"

@@ -1,0 +1,8 @@
+// Forward PLIF scan kernels with the modulation fused into the loads, bf16 stream dtype.
+#include <cstring>
+
+#include "nsb_scan.cuh"
+
+namespace nsb {
+int scan_mod_fwd_bf16(const FwdArgs& a) { return scan_mod_fwd_dispatch<__nv_bfloat16>(a); }
+}  // namespace nsb

@@ -1,0 +1,8 @@
+// Forward PLIF scan kernels with the modulation fused into the loads, f16 stream dtype.
+#include <cstring>
+
+#include "nsb_scan.cuh"
+
+namespace nsb {
+int scan_mod_fwd_f16(const FwdArgs& a) { return scan_mod_fwd_dispatch<__half>(a); }
+}  // namespace nsb

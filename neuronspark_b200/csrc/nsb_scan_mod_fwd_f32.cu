@@ -1,0 +1,8 @@
+// Forward PLIF scan kernels with the modulation fused into the loads, f32 stream dtype.
+#include <cstring>
+
+#include "nsb_scan.cuh"
+
+namespace nsb {
+int scan_mod_fwd_f32(const FwdArgs& a) { return scan_mod_fwd_dispatch<float>(a); }
+}  // namespace nsb

@@ -76,9 +76,9 @@ def assert_close_lowp(actual, expected, dtype, what="", scale=None):
                            f"{dtype} ulp; worst {np.abs(a - e).max():.3e}")
 
 
-def assert_spikes_match(spike, ref_spike, ref_vpost, vth, what=""):
+def assert_spikes_match(spike, ref_spike, ref_vpost, vth, what="", margin=1e-5):
     """Spikes must be bit-exact, except that a lane may diverge from the first
-    step at which |V_pre - V_th| < 1e-5*|V_th| in the oracle (a legitimately
+    step at which |V_pre - V_th| < margin*|V_th| in the oracle (a legitimately
     ambiguous threshold crossing changes that lane's future)."""
     s = np.asarray(spike, np.float32).reshape(ref_spike.shape[0], -1)
     r = np.asarray(ref_spike, np.float32).reshape(s.shape)
@@ -87,7 +87,7 @@ def assert_spikes_match(spike, ref_spike, ref_vpost, vth, what=""):
     vp = np.asarray(ref_vpost, np.float32).reshape(s.shape)
     th = np.broadcast_to(np.asarray(vth, np.float32), ref_spike.shape).reshape(s.shape)
     x = vp - th * (1.0 - r)  # V_pre - V_th
-    near = np.abs(x) < 1e-5 * np.abs(th)
+    near = np.abs(x) < margin * np.abs(th)
     ambiguous_from = np.where(near.any(0), near.argmax(0), s.shape[0])
     mism = s != r
     first_bad = np.where(mism.any(0), mism.argmax(0), s.shape[0])
