@@ -33,16 +33,27 @@ __global__ void modulation_fwd_kernel(const TI* __restrict__ raw_beta, const TI*
     Vec<TI, VE> ro;
     if constexpr (RF) ro = *reinterpret_cast<const Vec<TI, VE>*>(raw_omega + off);
     Vec<TO, VE> ob, ou, ot, oo;
+    float b[VE], a[VE], th[VE], om[VE], dr[VE], q0[VE], q1[VE], q2[VE], q3[VE], q4[VE];
+    mod::Bias<VE> bias;
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
-      float b, uu, th, om;
-      mod::forward<RF>(Elem<TI>::to_f32(rb.v[j]), Elem<TI>::to_f32(ra.v[j]), Elem<TI>::to_f32(rt.v[j]),
-                       RF ? Elem<TI>::to_f32(ro.v[j]) : 0.0f, Elem<TI>::to_f32(ci.v[j]), b_beta[c + j],
-                       b_alpha[c + j], b_th[c + j], RF ? b_omega[c + j] : 0.0f, v_th_min, b, uu, th, om);
-      ob.v[j] = Elem<TO>::from_f32(b);
-      ou.v[j] = Elem<TO>::from_f32(uu);
-      ot.v[j] = Elem<TO>::from_f32(th);
-      if constexpr (RF) oo.v[j] = Elem<TO>::from_f32(om);
+      b[j] = Elem<TI>::to_f32(rb.v[j]);
+      a[j] = Elem<TI>::to_f32(ra.v[j]);
+      th[j] = Elem<TI>::to_f32(rt.v[j]);
+      om[j] = RF ? Elem<TI>::to_f32(ro.v[j]) : 0.0f;
+      dr[j] = Elem<TI>::to_f32(ci.v[j]);
+      bias.beta[j] = b_beta[c + j];
+      bias.alpha[j] = b_alpha[c + j];
+      bias.th[j] = b_th[c + j];
+      bias.omega[j] = RF ? b_omega[c + j] : 0.0f;
+    }
+    mod::forward_lanes<RF, VE>(b, a, th, om, dr, bias, v_th_min, q0, q1, q2, q3, q4);
+#pragma unroll
+    for (int j = 0; j < VE; ++j) {
+      ob.v[j] = Elem<TO>::from_f32(b[j]);
+      ou.v[j] = Elem<TO>::from_f32(dr[j]);
+      ot.v[j] = Elem<TO>::from_f32(th[j]);
+      if constexpr (RF) oo.v[j] = Elem<TO>::from_f32(om[j]);
     }
     *reinterpret_cast<Vec<TO, VE>*>(beta + off) = ob;
     *reinterpret_cast<Vec<TO, VE>*>(u + off) = ou;

@@ -10,8 +10,8 @@
 //
 // These device functions are shared by the fused scan kernels and by the stand-alone
 // modulation kernel, and are written with explicit rounded operations only (no expression
-// the compiler may contract or reassociate), so that both produce the same bits from the
-// same inputs. The transcendental parts use the hardware approximations (ex2, rcp, rsqrt)
+// the compiler may contract or reassociate), so that every kernel variant produces the same
+// bits from the same inputs. The transcendental parts use the hardware approximations (ex2, rcp, rsqrt)
 // on arguments whose range makes them safe; relative error of beta, alpha, omega against a
 // correctly rounded evaluation stays below 1e-6 (the exponential's argument rounding
 // dominates), v_th is exact.
@@ -42,46 +42,120 @@ __device__ __forceinline__ float rsqrt_approx(float x) {
   return y;
 }
 
-// t = exp(-|z|) in (0, 1]
-__device__ __forceinline__ float exp_neg_abs(float z) { return ex2_approx(__fmul_rn(-fabsf(z), kLog2e)); }
+// ---------------------------------------------------------------------------------------
+// Lane packs. The modulation is issue-bound, so where a thread owns an even number of
+// columns the additions, multiplications and fused multiply-adds run two lanes at a time on
+// the packed fp32x2 instructions of sm_100 (half the issue slots); the exponentials,
+// reciprocals, comparisons and selects stay per lane. Pack<1> is the same arithmetic on
+// one lane. For both to give the same bits from the same inputs the formulas obey one
+// rule: NO ADDITION TAKES THE RESULT OF A MULTIPLICATION AS AN OPERAND unless it is written
+// as a fused multiply-add - the assembler contracts a packed multiply followed by a packed
+// add into a packed FMA even when both carry .rn (measured), and never contracts the scalar
+// forms, so any other shape would round differently in the two packs.
+// ---------------------------------------------------------------------------------------
+template <int N>
+struct Pack;
+
+template <>
+struct Pack<1> {
+  float v;
+  __device__ __forceinline__ static Pack load(const float* p) { return {p[0]}; }
+  __device__ __forceinline__ void store(float* p) const { p[0] = v; }
+  __device__ __forceinline__ static Pack splat(float c) { return {c}; }
+  __device__ __forceinline__ friend Pack add(Pack a, Pack b) { return {__fadd_rn(a.v, b.v)}; }
+  __device__ __forceinline__ friend Pack mul(Pack a, Pack b) { return {__fmul_rn(a.v, b.v)}; }
+  __device__ __forceinline__ friend Pack fma(Pack a, Pack b, Pack c) { return {__fmaf_rn(a.v, b.v, c.v)}; }
+  template <typename F>
+  __device__ __forceinline__ Pack map(F f) const { return {f(v)}; }
+  template <typename F>
+  __device__ __forceinline__ friend Pack zip(Pack a, Pack b, Pack c, F f) { return {f(a.v, b.v, c.v)}; }
+};
+
+template <>
+struct Pack<2> {
+  unsigned long long v;
+  __device__ __forceinline__ static Pack make(float lo, float hi) {
+    Pack r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(lo), "f"(hi));
+    return r;
+  }
+  __device__ __forceinline__ void get(float& lo, float& hi) const { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+  __device__ __forceinline__ static Pack load(const float* p) { return make(p[0], p[1]); }
+  __device__ __forceinline__ void store(float* p) const { get(p[0], p[1]); }
+  __device__ __forceinline__ static Pack splat(float c) { return make(c, c); }
+  __device__ __forceinline__ friend Pack add(Pack a, Pack b) {
+    Pack r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+    return r;
+  }
+  __device__ __forceinline__ friend Pack mul(Pack a, Pack b) {
+    Pack r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+    return r;
+  }
+  __device__ __forceinline__ friend Pack fma(Pack a, Pack b, Pack c) {
+    Pack r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v));
+    return r;
+  }
+  template <typename F>
+  __device__ __forceinline__ Pack map(F f) const {
+    float lo, hi;
+    get(lo, hi);
+    return make(f(lo), f(hi));
+  }
+  template <typename F>
+  __device__ __forceinline__ friend Pack zip(Pack a, Pack b, Pack c, F f) {
+    float a0, a1, b0, b1, c0, c1;
+    a.get(a0, a1);
+    b.get(b0, b1);
+    c.get(c0, c1);
+    return make(f(a0, b0, c0), f(a1, b1, c1));
+  }
+};
+
+// t = exp(-|z|) in (0, 1]   (the product feeds the exponential only)
+template <class P>
+__device__ __forceinline__ P exp_neg_abs(P z) {
+  return z.map([](float x) { return ex2_approx(__fmul_rn(-fabsf(x), kLog2e)); });
+}
 
 // sigmoid(z) = z >= 0 ? 1/(1+t) : t/(1+t), t = exp(-|z|): never overflows.
-__device__ __forceinline__ float sigmoid_from_t(float z, float t) {
-  const float r = rcp_approx(__fadd_rn(1.0f, t));
-  return z >= 0.0f ? r : __fmul_rn(t, r);
+template <class P>
+__device__ __forceinline__ P sigmoid_from_t(P z, P t) {
+  const P r = add(P::splat(1.0f), t).map([](float x) { return rcp_approx(x); });
+  return zip(z, r, mul(t, r), [](float zz, float rr, float tr) { return zz >= 0.0f ? rr : tr; });
 }
-__device__ __forceinline__ float sigmoid(float z) { return sigmoid_from_t(z, exp_neg_abs(z)); }
-
-// log1p(t) for t in [0, 1]: 2*atanh(s) with s = t/(2+t) <= 1/3, odd series to s^13
-// (truncation 1.4e-8 relative).
-__device__ __forceinline__ float log1p_unit(float t) {
-  const float s = __fmul_rn(t, rcp_approx(__fadd_rn(2.0f, t)));
-  const float s2 = __fmul_rn(s, s);
-  float p = 2.0f / 13.0f;
-  p = __fmaf_rn(p, s2, 2.0f / 11.0f);
-  p = __fmaf_rn(p, s2, 2.0f / 9.0f);
-  p = __fmaf_rn(p, s2, 2.0f / 7.0f);
-  p = __fmaf_rn(p, s2, 2.0f / 5.0f);
-  p = __fmaf_rn(p, s2, 2.0f / 3.0f);
-  p = __fmaf_rn(p, s2, 2.0f);
-  return __fmul_rn(s, p);
+template <class P>
+__device__ __forceinline__ P sigmoid(P z) {
+  return sigmoid_from_t(z, exp_neg_abs(z));
 }
 
-// softplus(z) = max(z, 0) + log1p(exp(-|z|)); equals z for z > 20 in fp32, which is the
-// reference's threshold form. `t` is exp(-|z|), for the caller that also wants sigmoid(z).
-__device__ __forceinline__ float softplus_from_t(float z, float t) {
-  return __fadd_rn(fmaxf(z, 0.0f), log1p_unit(t));
+// softplus(z) = max(z, 0) + log1p(t), t = exp(-|z|) in (0, 1]; log1p(t) = 2*atanh(s) with
+// s = t/(2+t) <= 1/3, odd series to s^13 (truncation 1.4e-8 relative), and the last step
+// s*p + max(z, 0) is one FMA. Equals z for z > 20 in fp32: the reference's threshold form.
+template <class P>
+__device__ __forceinline__ P softplus_from_t(P z, P t) {
+  const P s = mul(t, add(P::splat(2.0f), t).map([](float x) { return rcp_approx(x); }));
+  const P s2 = mul(s, s);
+  P p = P::splat(2.0f / 13.0f);
+  p = fma(p, s2, P::splat(2.0f / 11.0f));
+  p = fma(p, s2, P::splat(2.0f / 9.0f));
+  p = fma(p, s2, P::splat(2.0f / 7.0f));
+  p = fma(p, s2, P::splat(2.0f / 5.0f));
+  p = fma(p, s2, P::splat(2.0f / 3.0f));
+  p = fma(p, s2, P::splat(2.0f));
+  return fma(s, p, z.map([](float x) { return fmaxf(x, 0.0f); }));
 }
-__device__ __forceinline__ float softplus(float z) { return softplus_from_t(z, exp_neg_abs(z)); }
 
 // Stability rescale of (beta, omega): radius sqrt(beta^2 + omega^2) capped at 0.999.
-// Returns the scale applied (1 when inactive) and r2 of the unscaled pair.
-__device__ __forceinline__ float rf_rescale(float& beta, float& omega, float& r2) {
-  r2 = __fadd_rn(__fmul_rn(beta, beta), __fmul_rn(omega, omega));
-  float scale = 1.0f;
-  if (r2 > kRmaxSq) scale = __fmul_rn(kRmax, rsqrt_approx(r2));
-  beta = __fmul_rn(beta, scale);
-  omega = __fmul_rn(omega, scale);
+// r2 = fma(beta, beta, omega*omega). Returns the scale applied (1 when inactive).
+template <class P>
+__device__ __forceinline__ P rf_rescale(P& beta, P& omega, P& r2) {
+  r2 = fma(beta, beta, mul(omega, omega));
+  const P scale = r2.map([](float x) { return x > kRmaxSq ? __fmul_rn(kRmax, rsqrt_approx(x)) : 1.0f; });
+  beta = mul(beta, scale);
+  omega = mul(omega, scale);
   return scale;
 }
 
@@ -91,22 +165,55 @@ struct Bias {
   float beta[V], alpha[V], th[V], omega[V];
 };
 
-// Forward modulation of one element. RF selects the second-order form.
-template <bool RF>
-__device__ __forceinline__ void forward(float raw_beta, float raw_alpha, float raw_th, float raw_omega, float cur,
-                                        float bb, float ba, float bt, float bo, float v_th_min, float& beta,
-                                        float& u, float& vth, float& omega) {
-  beta = sigmoid(__fadd_rn(raw_beta, bb));
-  const float alpha = softplus(__fadd_rn(raw_alpha, ba));
-  vth = __fadd_rn(v_th_min, fabsf(__fadd_rn(raw_th, bt)));
+// Forward modulation of N = 1 or 2 lanes with the intermediates its adjoint needs:
+// b0 = unscaled beta, alpha, sa = sigmoid(z_alpha) = d softplus, o0 = unscaled omega,
+// so = sigmoid(z_omega). RF selects the second-order form. u = alpha * I is a per-lane
+// multiply (it feeds the scan's rounded add, which must never be contracted with it).
+template <bool RF, int N>
+__device__ __forceinline__ void forward_full(const float* raw_beta, const float* raw_alpha, const float* raw_th,
+                                             const float* raw_omega, const float* cur, const float* bb,
+                                             const float* ba, const float* bt, const float* bo, float v_th_min,
+                                             float* beta, float* u, float* vth, float* omega, float* b0,
+                                             float* alpha, float* sa, float* o0, float* so) {
+  using P = Pack<N>;
+  P be = sigmoid(add(P::load(raw_beta), P::load(bb)));
+  be.store(b0);
+  const P za = add(P::load(raw_alpha), P::load(ba));
+  const P ta = exp_neg_abs(za);
+  const P al = softplus_from_t(za, ta);
+  al.store(alpha);
+  sigmoid_from_t(za, ta).store(sa);
+  add(P::splat(v_th_min), add(P::load(raw_th), P::load(bt)).map([](float x) { return fabsf(x); })).store(vth);
   if constexpr (RF) {
-    omega = softplus(__fadd_rn(raw_omega, bo));
-    float r2;
-    rf_rescale(beta, omega, r2);
+    const P zo = add(P::load(raw_omega), P::load(bo));
+    const P to = exp_neg_abs(zo);
+    P om = softplus_from_t(zo, to);
+    om.store(o0);
+    sigmoid_from_t(zo, to).store(so);
+    P r2;
+    rf_rescale(be, om, r2);
+    om.store(omega);
   } else {
-    omega = 0.0f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) omega[i] = o0[i] = so[i] = 0.0f;
   }
-  u = __fmul_rn(alpha, cur);
+  be.store(beta);
+#pragma unroll
+  for (int i = 0; i < N; ++i) u[i] = __fmul_rn(alpha[i], cur[i]);
+}
+
+// The same for the V lanes of a thread (pairs where V is even). Inputs and outputs may alias
+// lane by lane (raw_beta with beta, cur with u, raw_th with vth, raw_omega with omega).
+template <bool RF, int V>
+__device__ __forceinline__ void forward_lanes(float (&b)[V], const float (&ra)[V], float (&th)[V], float (&om)[V],
+                                              float (&dr)[V], const Bias<V>& bias, float v_th_min, float (&b0)[V],
+                                              float (&al)[V], float (&sa)[V], float (&o0)[V], float (&so)[V]) {
+  constexpr int N = V % 2 == 0 ? 2 : 1;
+#pragma unroll
+  for (int j = 0; j < V; j += N)
+    forward_full<RF, N>(&b[j], &ra[j], &th[j], &om[j], &dr[j], &bias.beta[j], &bias.alpha[j], &bias.th[j],
+                        &bias.omega[j], v_th_min, &b[j], &dr[j], &th[j], &om[j], &b0[j], &al[j], &sa[j], &o0[j],
+                        &so[j]);
 }
 
 }  // namespace mod

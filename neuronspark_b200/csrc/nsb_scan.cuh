@@ -121,6 +121,7 @@ struct PlanQuery {
   int tile = 8;        // steps per tile (C)
   bool backward = false;
   int max_lanes = 4;   // largest lanes-per-thread the kernel family is built for
+  int stash = 0;       // fp32 values per element of a tile that each warp keeps in shared memory
 };
 
 struct Plan {
@@ -562,13 +563,9 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
       if constexpr (MODE == MODE_RF || MODE == MODE_RFMOD) fetch(MT::kOmega, k, om);
       if constexpr (MT::kMod) {
         // b, th, om, dr hold the raw projections and I: turn them into beta, v_th, omega, u
-        float ra[V];
+        float ra[V], q0[V], q1[V], q2[V], q3[V], q4[V];
         fetch(MT::kGain, k, ra);
-#pragma unroll
-        for (int j = 0; j < V; ++j)
-          mod::forward<MT::kSecond>(b[j], ra[j], th[j], MT::kSecond ? om[j] : 0.0f, dr[j], bias.beta[j],
-                                    bias.alpha[j], bias.th[j], bias.omega[j], p.v_th_min, b[j], dr[j], th[j],
-                                    om[j]);
+        mod::forward_lanes<MT::kSecond, V>(b, ra, th, om, dr, bias, p.v_th_min, q0, q1, q2, q3, q4);
       }
       if constexpr (MT::kSecond) {
         rf_step<V>(v, w, b, om, dr, th, x, sp_);
@@ -800,6 +797,11 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   constexpr int nstreams = NF + 1 + (HAS_GV ? 1 : 0);
   constexpr bool has_gv = HAS_GV;
   constexpr uint32_t stage_bytes = (uint32_t)nstreams * TILE_BYTES;
+  // Modulated modes: the recompute pass leaves what the adjoint pass needs of the modulation
+  // (unscaled beta, alpha, sigmoid(z_alpha) [, unscaled omega, sigmoid(z_omega)]) in a private
+  // fp32 region of shared memory, so that the transcendental work is done once per element.
+  constexpr int NQ = ModeTraits<MODE>::kMod ? (ModeTraits<MODE>::kSecond ? 5 : 3) : 0;
+  constexpr bool STASH = TMA && NQ > 0;
 
   long long colj[V];
   bool valid[V];
@@ -837,12 +839,16 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   const int stages = p.stages;
   uint32_t bar0 = 0, data0 = 0;
   const uint8_t* data_ptr = nullptr;
+  float* stash = nullptr;
   if constexpr (TMA) {
     const uint32_t base = smem_u32(smem_raw);
     bar0 = base + (uint32_t)(warp * stages) * 8u;
     const uint32_t data_base = (base + (uint32_t)(wpc * stages) * 8u + 127u) & ~127u;
     data0 = data_base + (uint32_t)(warp * stages) * stage_bytes;
     data_ptr = smem_raw + (data0 - base);
+    if constexpr (STASH)
+      stash = reinterpret_cast<float*>(smem_raw + (data_base - base) + (size_t)(wpc * stages) * stage_bytes) +
+              (size_t)warp * (NQ * TILE_ELEMS) + V * lane;
     if (lane == 0) {
       for (int s = 0; s < stages; ++s) mbar_init(bar0 + 8u * s, 1);
       mbar_init_fence();
@@ -938,13 +944,18 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
         }
         if constexpr (MT::kSecond) fetch(MT::kOmega, k, om);
         if constexpr (MT::kMod) {
-          float ra[V];
+          float ra[V], q0[V], q1[V], q2[V], q3[V], q4[V];
           fetch(MT::kGain, k, ra);
-#pragma unroll
-          for (int j = 0; j < V; ++j)
-            mod::forward<MT::kSecond>(b[j], ra[j], th[j], MT::kSecond ? om[j] : 0.0f, dr[j], bias.beta[j],
-                                      bias.alpha[j], bias.th[j], bias.omega[j], p.v_th_min, b[j], dr[j], th[j],
-                                      om[j]);
+          mod::forward_lanes<MT::kSecond, V>(b, ra, th, om, dr, bias, p.v_th_min, q0, q1, q2, q3, q4);
+          if constexpr (STASH) {
+            VecIO<float, V>::store(stash + (0 * C + k) * (32 * V), q0);
+            VecIO<float, V>::store(stash + (1 * C + k) * (32 * V), q1);
+            VecIO<float, V>::store(stash + (2 * C + k) * (32 * V), q2);
+            if constexpr (MT::kSecond) {
+              VecIO<float, V>::store(stash + (3 * C + k) * (32 * V), q3);
+              VecIO<float, V>::store(stash + (4 * C + k) * (32 * V), q4);
+            }
+          }
         }
         if constexpr (MT::kSecond) {
           rf_step<V>(v, w, b, om, dr, th, xs[k], s_);
@@ -1010,29 +1021,39 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
           //   d sigmoid = s(1-s); d softplus(z) = sigmoid(z); d|z| = sign(z);
           //   rescale active (beta, omega) = scale*(b0, o0), scale = 0.999/r:
           //     G_b0 = scale*(G_beta - dot*b0), G_o0 = scale*(G_omega - dot*o0), dot = (G_beta*b0 + G_omega*o0)/r2
-          float rb[V], ra[V], rt[V], ro[V], ci[V];
-          fetch(MT::kBeta, k, rb);
-          fetch(MT::kGain, k, ra);
+          float rt[V], ci[V], b0v[V], alv[V], sav[V], o0v[V], sov[V];
           fetch(MT::kVth, k, rt);
           fetch(MT::kDrive, k, ci);
-          if constexpr (MT::kSecond) fetch(MT::kOmega, k, ro);
+          if constexpr (STASH) {
+            VecIO<float, V>::load(stash + (0 * C + k) * (32 * V), b0v);
+            VecIO<float, V>::load(stash + (1 * C + k) * (32 * V), alv);
+            VecIO<float, V>::load(stash + (2 * C + k) * (32 * V), sav);
+            if constexpr (MT::kSecond) {
+              VecIO<float, V>::load(stash + (3 * C + k) * (32 * V), o0v);
+              VecIO<float, V>::load(stash + (4 * C + k) * (32 * V), sov);
+            }
+          } else {
+            float rb[V], ra[V], ro[V], th_[V], u_[V];
+            fetch(MT::kBeta, k, rb);
+            fetch(MT::kGain, k, ra);
+            if constexpr (MT::kSecond) fetch(MT::kOmega, k, ro);
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+              th_[j] = rt[j];
+              u_[j] = ci[j];
+            }
+            mod::forward_lanes<MT::kSecond, V>(rb, ra, th_, ro, u_, bias, p.v_th_min, b0v, alv, sav, o0v, sov);
+          }
 #pragma unroll
           for (int j = 0; j < V; ++j) {
-            const float zb = __fadd_rn(rb[j], bias.beta[j]);
-            const float b0 = mod::sigmoid(zb);
-            const float za = __fadd_rn(ra[j], bias.alpha[j]);
-            const float ta = mod::exp_neg_abs(za);
-            const float al = mod::softplus_from_t(za, ta);
-            const float sa = mod::sigmoid_from_t(za, ta);
+            const float b0 = b0v[j], al = alv[j], sa = sav[j];
             const float zt = __fadd_rn(rt[j], bias.th[j]);
             float Gb = gb[j];
             if constexpr (MT::kSecond) {
-              const float zo = __fadd_rn(ro[j], bias.omega[j]);
-              const float to = mod::exp_neg_abs(zo);
-              const float o0 = mod::softplus_from_t(zo, to);
-              const float so = mod::sigmoid_from_t(zo, to);
-              float be = b0, om_ = o0, r2;
-              const float scale = mod::rf_rescale(be, om_, r2);
+              const float o0 = o0v[j], so = sov[j];
+              mod::Pack<1> bep{b0}, omp{o0}, r2p;
+              const float scale = mod::rf_rescale(bep, omp, r2p).v;
+              const float be = bep.v, om_ = omp.v, r2 = r2p.v;
               const float vp_ = vprev[k][j], wp_ = wprev[MT::kSecond ? k : 0][j], aw = accw[j];
               Gb = fmaf(aw, wp_, Gb);
               float Go = aw * vp_ - gpre[j] * wp_;
@@ -1051,7 +1072,9 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
             gb[j] = Gb * (b0 * (1.0f - b0));
             gg[j] = gpre[j] * ci[j] * sa;
             gd[j] = gpre[j] * al;
-            gth[j] = zt > 0.0f ? gth[j] : (zt < 0.0f ? -gth[j] : 0.0f);
+            // grad raw_th = grad v_th * sign(z_th) (0 at z_th = 0): flip the sign bit, no branch
+            gth[j] = zt == 0.0f ? 0.0f
+                                : __uint_as_float(__float_as_uint(gth[j]) ^ (__float_as_uint(zt) & 0x80000000u));
             accb[j] += gb[j];
             acca[j] += gg[j];
             acct[j] += gth[j];
@@ -1534,7 +1557,9 @@ int scan_mod_bwd_dispatch(const BwdArgs& a) {
   if (r != NSB_OK) return r;
   if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
   if (a.g_vpost) return NSB_ERR_INVALID_ARG;
-  const Tuning tune = get_tuning();
+  Tuning tune = get_tuning();
+  // built for at most 2 lanes per thread (8-step tiles) / 1 lane (32-step tiles)
+  tune.lanes_per_thread = std::min(tune.lanes_per_thread, a.tile == 8 ? 2 : 1);
   bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
   const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.extra, a.ckpt, a.ckpt_w, a.g_spike,
                         a.g_beta, a.g_drive, a.g_gain, a.g_vth, a.g_extra};
@@ -1545,7 +1570,9 @@ int scan_mod_bwd_dispatch(const BwdArgs& a) {
     PlanQuery q;
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
     q.nstreams = (a.mode == MODE_RFMOD ? 5 : 4) + 1;
-    q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : 1;
+    q.stash = a.mode == MODE_RFMOD ? 5 : 3;
+    // 4 lanes per thread spill heavily with the modulation's extra live values (measured 3x slower)
+    q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 2 : 1;
     plan = plan_scan(dev, q, tune);
   }
   const int V = plan.lanes;
@@ -1554,7 +1581,7 @@ int scan_mod_bwd_dispatch(const BwdArgs& a) {
     return launch_bwd_impl<ST, MODE_, SURR_, V_, C_, true, false>(a, dev, tune, plan);
 #define NSB_MBWD_CASES(MODE_, SURR_)                                                   \
   NSB_MBWD_CASE(MODE_, SURR_, 1, 8) NSB_MBWD_CASE(MODE_, SURR_, 2, 8)                  \
-  NSB_MBWD_CASE(MODE_, SURR_, 4, 8) NSB_MBWD_CASE(MODE_, SURR_, 1, 32)
+  NSB_MBWD_CASE(MODE_, SURR_, 1, 32)
   if (tma) {
     NSB_MBWD_CASES(MODE_MOD, NSB_SURR_SIGMOID) NSB_MBWD_CASES(MODE_MOD, NSB_SURR_ATAN)
     NSB_MBWD_CASES(MODE_RFMOD, NSB_SURR_SIGMOID) NSB_MBWD_CASES(MODE_RFMOD, NSB_SURR_ATAN)
