@@ -53,6 +53,15 @@ WORKLOADS = {
 #   c4      selective scan, gain*cur form, B=256 split evenly across the GPUs (strong scaling)
 #   decode  per-token decoding: 64 consecutive 16-step calls at B=1024 (split across GPUs),
 #           membrane state carried from call to call
+# Modulation fused into the scan (raw projections + biases in, spikes out; forward+backward):
+#   mod     first-order block: raw_beta, raw_alpha, raw_th, I            (4 streams)
+#   rfmod   resonate-and-fire block: + raw_omega and the stability rescale (5 streams)
+MODULATED_WORKLOADS = {
+    "mod": dict(rf=False, B=32, T=8192, D=6144),
+    "rfmod": dict(rf=True, B=32, T=8192, D=6144),
+    "mod-short": dict(rf=False, B=32, T=512, D=6144),     # 1/16 of the time steps: profiler captures
+    "rfmod-short": dict(rf=True, B=32, T=512, D=6144),
+}
 INFERENCE_WORKLOADS = {
     "c1": dict(kind="row", B=8, T=8192, D=768, shard=False, calls=1, bytes_per_ns=2.125),
     "c4": dict(kind="ai", B=256, T=8192, D=6144, shard=True, calls=1, bytes_per_ns=8.125),
@@ -75,7 +84,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(INFERENCE_WORKLOADS))
+    ap.add_argument("--workload", default="c2",
+                    choices=sorted(WORKLOADS) + sorted(INFERENCE_WORKLOADS) + sorted(MODULATED_WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     return ap.parse_args()
@@ -346,6 +356,168 @@ def run_reference(args):
 # ------------------------------------------------------- inference workloads
 
 
+def run_modulated(args):
+    """Forward+backward of the scan with the modulation fused in, through the C ABI."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    import neuronspark_b200 as nsb
+    from neuronspark_b200 import _lib, parallel_scan as ps, snn_block as sb
+    w = MODULATED_WORKLOADS[args.workload]
+    rf, B, T, D = w["rf"], w["B"], w["T"], w["D"]
+    L, p = _lib.lib(), _lib.ptr
+    cols = B * D
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+
+    def rn(*shape):  # generated in slices of time to bound the fp32 temporaries
+        out = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+        step_t = max(1, shape[0] // 16)
+        for t0 in range(0, shape[0], step_t):
+            out[t0:t0 + step_t] = torch.randn(out[t0:t0 + step_t].shape, generator=g, device=dev).bfloat16()
+        return out
+
+    raw_beta, raw_alpha, raw_th, cur = rn(T, B, D), rn(T, B, D), rn(T, B, D), rn(T, B, D)
+    raw_th.mul_(0.5)
+    raw_omega = rn(T, B, D).sub_(1.0) if rf else None
+    g_spike = rn(T, B, D).mul_(0.1)
+    bias = [2.0 + 0.5 * torch.randn(D, generator=g, device=dev), 0.3 * torch.randn(D, generator=g, device=dev),
+            0.3 * torch.randn(D, generator=g, device=dev),
+            (-1.0 + 0.5 * torch.randn(D, generator=g, device=dev)) if rf else None]
+    v0 = torch.zeros(B, D, device=dev)
+    w0 = torch.zeros(B, D, device=dev) if rf else None
+    C = 32 if ps._interval(cols) == 32 else 8
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    spike = torch.empty((T, B, D), **bf)
+    ckv = torch.empty(((T + C - 1) // C, cols), dtype=torch.float32, device=dev)
+    ckw = torch.empty_like(ckv) if rf else None
+    v_last = torch.empty((B, D), dtype=torch.float32, device=dev)
+    w_last = torch.empty_like(v_last) if rf else None
+    grads = [torch.empty((T, B, D), **bf) for _ in range(5 if rf else 4)]  # raw_beta, raw_alpha, raw_th, I, raw_omega
+    g_bias = [torch.empty(D, dtype=torch.float32, device=dev) for _ in range(4 if rf else 3)]
+    scratch = torch.empty(int(L.nsb_plif_modulated_bwd_scratch_floats(cols)), dtype=torch.float32, device=dev)
+    g_v0 = torch.empty_like(v_last)
+    g_w0 = torch.empty_like(v_last) if rf else None
+    stream = _lib.stream_ptr(dev)
+    info = {}
+
+    def fwd():
+        _lib.check(L.nsb_plif_modulated_fwd(
+            p(raw_beta), p(raw_alpha), p(raw_th), p(raw_omega), p(cur), p(bias[0]), p(bias[1]), p(bias[2]),
+            p(bias[3]), 0.1, D, p(v0), p(w0), p(spike), None, p(ckv), p(ckw), p(v_last), p(w_last), T, cols,
+            _lib.BF16, C, stream), "nsb_plif_modulated_fwd")
+        info.setdefault("fwd", _lib.last_launch_info())
+
+    def bwd():
+        _lib.check(L.nsb_plif_modulated_bwd(
+            p(raw_beta), p(raw_alpha), p(raw_th), p(raw_omega), p(cur), p(bias[0]), p(bias[1]), p(bias[2]),
+            p(bias[3]), 0.1, D, p(ckv), p(ckw), p(g_spike), p(grads[0]), p(grads[1]), p(grads[2]),
+            p(grads[4]) if rf else None, p(grads[3]), p(g_bias[0]), p(g_bias[1]), p(g_bias[2]),
+            p(g_bias[3]) if rf else None, p(scratch), p(g_v0), p(g_w0), T, cols, _lib.BF16, C,
+            _lib.SURR_SIGMOID, 4.0, stream), "nsb_plif_modulated_bwd")
+        info.setdefault("bwd", _lib.last_launch_info())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        fwd()
+        bwd()
+    barrier()
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    sampler = ClockSampler(local) if rank == 0 else None
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    if sampler:
+        sampler.start()
+    start.record()
+    for k in range(K):
+        ev[k][0].record()
+        fwd()
+        ev[k][1].record()
+        bwd()
+        ev[k][2].record()
+    end.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    ms_step = start.elapsed_time(end) / K
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+    if world > 1:
+        t = torch.tensor([ms_step, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, fwd_ms, bwd_ms = (float(x) for x in t)
+    assert nsb.device_error_word() == 0, "a device-side wait timed out"
+
+    # context: the unfused forward (modulation written out in bf16, then the plain scan) on this GPU
+    unfused_ms = None
+    if rank == 0 and T * cols * 2 * 12 < 120e9:
+        with torch.no_grad():
+            def unfused():
+                if rf:
+                    be, u, th, om = sb._fused_modulation_rf(raw_beta, bias[0], raw_alpha, bias[1], raw_th, bias[2],
+                                                            0.1, cur, raw_omega, bias[3], out_dtype=torch.bfloat16)
+                    ps.rf_plif_parallel_forward_recompute(be, om, u, th, v0, w0)
+                else:
+                    be, u, th = sb._fused_modulation(raw_beta, bias[0], raw_alpha, bias[1], raw_th, bias[2], 0.1,
+                                                     cur, out_dtype=torch.bfloat16)
+                    ps.plif_parallel_forward(be, u, th, v0)
+            unfused()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(3):
+                unfused()
+            b.record()
+            torch.cuda.synchronize()
+            unfused_ms = a.elapsed_time(b) / 3
+    ns = T * cols
+    value = world * ns / (ms_step * 1e-3)
+    if rank == 0:
+        peak, peak_src = hbm_peak()
+        nin = 5 if rf else 4
+        bytes_fwd, bytes_bwd = 2 * (nin + 1), 2 * (2 * nin + 1)
+        ach = lambda by, ms: by * ns * 1e-9 / (ms * 1e-3)
+        line = {
+            "metric": "PLIF scan neuron-steps/s (B*T*D), modulation fused into the scan, forward+backward",
+            "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {'resonate-and-fire' if rf else 'first-order'} block, raw "
+                                   f"projections + biases -> spikes, B={B} per GPU, T={T}, D={D}, bf16 streams, fp32 "
+                                   "state, sigmoid surrogate alpha=4, grads for the raw projections, I, biases and "
+                                   "initial states",
+                       "l2": "inputs are far larger than L2" if T * cols * 2 > (512 << 20) else "L2 not flushed",
+                       "ckpt_interval": C, "launch_fwd": info.get("fwd"), "launch_bwd": info.get("bwd")},
+            "roofline": {"bound": "hbm", "kernel": "plif_bwd_kernel (modulated)", "achieved": ach(bytes_bwd, bwd_ms),
+                         "peak": peak, "unit": "GB/s", "frac": ach(bytes_bwd, bwd_ms) / peak, "traffic": None,
+                         "peak_source": peak_src, "algorithmic_bytes_per_neuron_step": bytes_bwd,
+                         "avg_launch_ms": bwd_ms,
+                         "forward": {"kernel": "plif_fwd_kernel (modulated)", "achieved": ach(bytes_fwd, fwd_ms),
+                                     "frac": ach(bytes_fwd, fwd_ms) / peak,
+                                     "algorithmic_bytes_per_neuron_step": bytes_fwd, "avg_launch_ms": fwd_ms},
+                         "note": "these kernels are bound by instruction issue and latency (transcendental "
+                                 "modulation per element), not by HBM"},
+            "unfused_forward_ms": unfused_ms,
+            "clocks": clocks, "gpu_launches": 3 * K,
+            "validation": {"finite": bool(torch.isfinite(g_v0).all() and torch.isfinite(g_bias[0]).all()),
+                           "spike_rate": float(spike[:64].float().mean())},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_inference(args):
     """Forward-only workloads with bit-packed spikes (c1, c4, decode)."""
     import torch
@@ -477,6 +649,9 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload in MODULATED_WORKLOADS:
+        run_modulated(args)
         return
     if args.workload in INFERENCE_WORKLOADS:
         run_inference(args)

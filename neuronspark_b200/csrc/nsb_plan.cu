@@ -33,7 +33,17 @@ namespace {
 
 // Registers per thread of the kernel family (upper estimates from ptxas -v; they
 // only bound how many warps fit an SM).
-int regs_estimate(bool backward, int lanes, int tile) {
+int regs_estimate(bool backward, int lanes, int tile, int modulated) {
+  if (modulated) {  // scans with the modulation fused in: 1 = first order, 2 = resonate-and-fire
+    const bool rf = modulated == 2;
+    if (!backward) {
+      if (lanes == 4) return rf ? 160 : 152;  // (the bit-packing variants need ~24 more; the launcher shrinks the CTA if so)
+      if (lanes == 2) return rf ? 160 : 128;
+      return tile == 32 ? (rf ? 168 : 96) : (rf ? 80 : 56);
+    }
+    if (lanes >= 2) return rf ? 136 : 104;
+    return tile == 32 ? (rf ? 168 : 152) : (rf ? 80 : 64);
+  }
   if (!backward) return lanes == 4 ? 72 : (lanes == 2 ? 56 : 48);
   if (tile * lanes <= 16) return 96;
   if (lanes == 1) return tile == 16 ? 128 : 200;
@@ -81,7 +91,7 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
     const long long nwarps = (q.cols + 32LL * lanes - 1) / (32LL * lanes);
     const size_t tile_bytes = (size_t)q.tile * 32 * lanes * q.elem_size;
     const size_t stage_bytes = tile_bytes * q.nstreams;
-    const int regs = regs_estimate(q.backward, lanes, q.tile);
+    const int regs = regs_estimate(q.backward, lanes, q.tile, q.modulated);
     // each of the 4 SM sub-partitions has its own 16 K registers and takes every 4th warp
     const int reg_warps = std::max(1, 4 * (16384 / (regs * 32)));
     const double f_op = op_size_factor((double)tile_bytes);

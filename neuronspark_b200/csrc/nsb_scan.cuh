@@ -122,6 +122,7 @@ struct PlanQuery {
   bool backward = false;
   int max_lanes = 4;   // largest lanes-per-thread the kernel family is built for
   int stash = 0;       // fp32 values per element of a tile that each warp keeps in shared memory
+  int modulated = 0;   // 0 plain scan, 1 first-order modulation fused in, 2 resonate-and-fire modulation
 };
 
 struct Plan {
@@ -521,6 +522,9 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     ST* o_vpost = (DIRECT && p.vpost) ? static_cast<ST*>(p.vpost) + t0 * row_elems + colj[0] : nullptr;
     ST* o_wout = (DIRECT && MT::kSecond && p.w_out) ? static_cast<ST*>(p.w_out) + t0 * row_elems + colj[0] : nullptr;
     uint32_t keep[NSLOT][V];  // raw ballots of the step(s) this lane is responsible for
+    // modulated modes: steps whose modulation is evaluated together, and its results
+    constexpr int CH = (MT::kMod && TMA) ? ((16 / V) < C ? (16 / V) : C) : 1;
+    float mb[CH][V], mu[CH][V], mth[CH][V], mom[CH][V];
 #pragma unroll
     for (int q = 0; q < NSLOT; ++q)
 #pragma unroll
@@ -562,10 +566,33 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
       }
       if constexpr (MODE == MODE_RF || MODE == MODE_RFMOD) fetch(MT::kOmega, k, om);
       if constexpr (MT::kMod) {
-        // b, th, om, dr hold the raw projections and I: turn them into beta, v_th, omega, u
-        float ra[V], q0[V], q1[V], q2[V], q3[V], q4[V];
-        fetch(MT::kGain, k, ra);
-        mod::forward_lanes<MT::kSecond, V>(b, ra, th, om, dr, bias, p.v_th_min, q0, q1, q2, q3, q4);
+        // Modulated modes: the raw projections of CH steps are turned into beta, u, v_th, omega
+        // together, ahead of the steps that use them. The modulation is long chains of dependent
+        // arithmetic with no dependence between steps; evaluated step by step, in between the
+        // serial scan, a warp stalls on every link (measured: 1.6 wait + 1.1 scoreboard cycles
+        // per instruction). CH steps at once give the scheduler CH*V independent chains.
+        if (k % CH == 0) {
+#pragma unroll
+          for (int kk = 0; kk < CH; ++kk) {
+            if (k + kk < C && (FULL || k + kk < nsteps)) {
+              float ra[V], q0[V], q1[V], q2[V], q3[V], q4[V];
+              fetch(MT::kBeta, k + kk, mb[kk]);
+              fetch(MT::kVth, k + kk, mth[kk]);
+              fetch(MT::kDrive, k + kk, mu[kk]);
+              fetch(MT::kGain, k + kk, ra);
+              if constexpr (MT::kSecond) fetch(MT::kOmega, k + kk, mom[kk]);
+              mod::forward_lanes<MT::kSecond, V>(mb[kk], ra, mth[kk], mom[kk], mu[kk], bias, p.v_th_min, q0, q1,
+                                                 q2, q3, q4);
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          b[j] = mb[k % CH][j];
+          th[j] = mth[k % CH][j];
+          dr[j] = mu[k % CH][j];
+          om[j] = mom[k % CH][j];
+        }
       }
       if constexpr (MT::kSecond) {
         rf_step<V>(v, w, b, om, dr, th, x, sp_);
@@ -915,6 +942,11 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     constexpr bool FULL = decltype(full_tag)::value;
     // recompute the tile forward, keeping V[k-1] and x[k] = V_pre[k] - V_th[k]
     float vprev[C][V], xs[C][V], wprev[MT::kSecond ? C : 1][V];
+    // Modulated modes: steps whose modulation is evaluated together. 1 here: evaluating several
+    // steps ahead, which pays in the forward kernel, costs the backward more in registers (and so
+    // in resident warps) than it gains (measured: 6.3 -> 6.5 ms first order, 10.3 -> 11.3 ms RF).
+    constexpr int CH = 1;
+    float mb[CH][V], mu[CH][V], mth[CH][V], mom[CH][V];
 #pragma unroll
     for (int k = 0; k < C; ++k) {
 #pragma unroll
@@ -944,17 +976,36 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
         }
         if constexpr (MT::kSecond) fetch(MT::kOmega, k, om);
         if constexpr (MT::kMod) {
-          float ra[V], q0[V], q1[V], q2[V], q3[V], q4[V];
-          fetch(MT::kGain, k, ra);
-          mod::forward_lanes<MT::kSecond, V>(b, ra, th, om, dr, bias, p.v_th_min, q0, q1, q2, q3, q4);
-          if constexpr (STASH) {
-            VecIO<float, V>::store(stash + (0 * C + k) * (32 * V), q0);
-            VecIO<float, V>::store(stash + (1 * C + k) * (32 * V), q1);
-            VecIO<float, V>::store(stash + (2 * C + k) * (32 * V), q2);
-            if constexpr (MT::kSecond) {
-              VecIO<float, V>::store(stash + (3 * C + k) * (32 * V), q3);
-              VecIO<float, V>::store(stash + (4 * C + k) * (32 * V), q4);
+          if (k % CH == 0) {
+#pragma unroll
+            for (int kk = 0; kk < CH; ++kk) {
+              if (k + kk < C && (FULL || k + kk < nsteps)) {
+                float ra[V], q0[V], q1[V], q2[V], q3[V], q4[V];
+                fetch(MT::kBeta, k + kk, mb[kk]);
+                fetch(MT::kVth, k + kk, mth[kk]);
+                fetch(MT::kDrive, k + kk, mu[kk]);
+                fetch(MT::kGain, k + kk, ra);
+                if constexpr (MT::kSecond) fetch(MT::kOmega, k + kk, mom[kk]);
+                mod::forward_lanes<MT::kSecond, V>(mb[kk], ra, mth[kk], mom[kk], mu[kk], bias, p.v_th_min, q0, q1,
+                                                   q2, q3, q4);
+                if constexpr (STASH) {
+                  VecIO<float, V>::store(stash + (0 * C + k + kk) * (32 * V), q0);
+                  VecIO<float, V>::store(stash + (1 * C + k + kk) * (32 * V), q1);
+                  VecIO<float, V>::store(stash + (2 * C + k + kk) * (32 * V), q2);
+                  if constexpr (MT::kSecond) {
+                    VecIO<float, V>::store(stash + (3 * C + k + kk) * (32 * V), q3);
+                    VecIO<float, V>::store(stash + (4 * C + k + kk) * (32 * V), q4);
+                  }
+                }
+              }
             }
+          }
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            b[j] = mb[k % CH][j];
+            th[j] = mth[k % CH][j];
+            dr[j] = mu[k % CH][j];
+            om[j] = mom[k % CH][j];
           }
         }
         if constexpr (MT::kSecond) {
@@ -1044,40 +1095,53 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
             }
             mod::forward_lanes<MT::kSecond, V>(rb, ra, th_, ro, u_, bias, p.v_th_min, b0v, alv, sav, o0v, sov);
           }
+          // pairs of lanes on the packed fp32x2 instructions where V is even (no rounding
+          // contract here: gradients are compared to a tolerance)
+          constexpr int N = V % 2 == 0 ? 2 : 1;
+          using P = mod::Pack<N>;
+          const P minus1 = P::splat(-1.0f);
 #pragma unroll
-          for (int j = 0; j < V; ++j) {
-            const float b0 = b0v[j], al = alv[j], sa = sav[j];
-            const float zt = __fadd_rn(rt[j], bias.th[j]);
-            float Gb = gb[j];
+          for (int j = 0; j < V; j += N) {
+            const P B0 = P::load(&b0v[j]), Gpre = P::load(&gpre[j]);
+            P Gb = P::load(&gb[j]);
             if constexpr (MT::kSecond) {
-              const float o0 = o0v[j], so = sov[j];
-              mod::Pack<1> bep{b0}, omp{o0}, r2p;
-              const float scale = mod::rf_rescale(bep, omp, r2p).v;
-              const float be = bep.v, om_ = omp.v, r2 = r2p.v;
-              const float vp_ = vprev[k][j], wp_ = wprev[MT::kSecond ? k : 0][j], aw = accw[j];
-              Gb = fmaf(aw, wp_, Gb);
-              float Go = aw * vp_ - gpre[j] * wp_;
-              acc[j] = gpre[j] * be + aw * om_;
-              accw[j] = aw * be - gpre[j] * om_;
-              if (r2 > mod::kRmaxSq) {
-                const float dot = (Gb * b0 + Go * o0) * mod::rcp_approx(r2);
-                Gb = scale * (Gb - dot * b0);
-                Go = scale * (Go - dot * o0);
-              }
-              go[j] = Go * so;
-              acco[j] += go[j];
+              const P O0 = P::load(&o0v[j]);
+              P be = B0, om_ = O0, r2;
+              const P scale = mod::rf_rescale(be, om_, r2);
+              const P VP = P::load(&vprev[k][j]), WP = P::load(&wprev[MT::kSecond ? k : 0][j]);
+              const P AW = P::load(&accw[j]), NG = mul(Gpre, minus1);
+              Gb = fma(AW, WP, Gb);
+              P Go = fma(NG, WP, mul(AW, VP));
+              fma(Gpre, be, mul(AW, om_)).store(&acc[j]);
+              fma(NG, om_, mul(AW, be)).store(&accw[j]);
+              // through the rescale where it is active (computed for every lane, selected per lane)
+              const P ndot = mul(mul(fma(Gb, B0, mul(Go, O0)), r2.map([](float x) { return mod::rcp_approx(x); })),
+                                 minus1);
+              const P Gb2 = mul(scale, fma(ndot, B0, Gb)), Go2 = mul(scale, fma(ndot, O0, Go));
+              Gb = zip(r2, Gb2, Gb, [](float rr, float a, float b_) { return rr > mod::kRmaxSq ? a : b_; });
+              Go = zip(r2, Go2, Go, [](float rr, float a, float b_) { return rr > mod::kRmaxSq ? a : b_; });
+              const P g = mul(Go, P::load(&sov[j]));
+              g.store(&go[j]);
+              add(P::load(&acco[j]), g).store(&acco[j]);
             } else {
-              acc[j] = gpre[j] * b0;
+              mul(Gpre, B0).store(&acc[j]);
             }
-            gb[j] = Gb * (b0 * (1.0f - b0));
-            gg[j] = gpre[j] * ci[j] * sa;
-            gd[j] = gpre[j] * al;
+            const P gB = mul(Gb, mul(B0, fma(B0, minus1, P::splat(1.0f))));
+            const P gA = mul(mul(Gpre, P::load(&ci[j])), P::load(&sav[j]));
+            gB.store(&gb[j]);
+            gA.store(&gg[j]);
+            mul(Gpre, P::load(&alv[j])).store(&gd[j]);
             // grad raw_th = grad v_th * sign(z_th) (0 at z_th = 0): flip the sign bit, no branch
-            gth[j] = zt == 0.0f ? 0.0f
-                                : __uint_as_float(__float_as_uint(gth[j]) ^ (__float_as_uint(zt) & 0x80000000u));
-            accb[j] += gb[j];
-            acca[j] += gg[j];
-            acct[j] += gth[j];
+            const P gT = zip(add(P::load(&rt[j]), P::load(&bias.th[j])), P::load(&gth[j]), P::splat(0.0f),
+                             [](float zt, float g_, float) {
+                               return zt == 0.0f ? 0.0f
+                                                 : __uint_as_float(__float_as_uint(g_) ^
+                                                                   (__float_as_uint(zt) & 0x80000000u));
+                             });
+            gT.store(&gth[j]);
+            add(P::load(&accb[j]), gB).store(&accb[j]);
+            add(P::load(&acca[j]), gA).store(&acca[j]);
+            add(P::load(&acct[j]), gT).store(&acct[j]);
           }
         } else if constexpr (MODE == MODE_ROW) {
 #pragma unroll
@@ -1251,6 +1315,24 @@ inline int defer_refill(const Tuning& tune, const Plan& plan, const DeviceInfo& 
   return (long long)plan.grid * plan.wpc <= 8LL * std::max(1, dev.sm_count);
 }
 
+// The planner works from register estimates. If the CTA it chose does not fit an SM with the
+// registers the kernel really has, halve the warps per CTA (shared memory is per warp, so it
+// shrinks in proportion) until it does.
+template <typename K>
+int shrink_to_fit(K kern, Plan& plan, long long nwarps) {
+  for (;;) {
+    int blocks = 0;
+    NSB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kern, plan.wpc * 32, plan.smem),
+                 "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+    if (blocks > 0) return NSB_OK;
+    if (plan.wpc == 1) return NSB_ERR_UNSUPPORTED;
+    const size_t per_warp = (plan.smem - 256) / plan.wpc;
+    plan.wpc = (plan.wpc + 1) / 2;
+    plan.smem = per_warp * plan.wpc + 256;
+    plan.grid = (int)((nwarps + plan.wpc - 1) / plan.wpc);
+  }
+}
+
 template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
 int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, const Plan& planned) {
   using MT = ModeTraits<MODE>;
@@ -1294,6 +1376,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
     if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;
     NSB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem),
                  "cudaFuncSetAttribute(fwd)");
+    if (int r = shrink_to_fit(kern, plan, nwarps); r != NSB_OK) return r;
   } else {
     plan.wpc = tune.warps_per_cta > 0 ? tune.warps_per_cta : 4;
     plan.stages = 1;
@@ -1362,6 +1445,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
     if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;
     NSB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem),
                  "cudaFuncSetAttribute(bwd)");
+    if (int r = shrink_to_fit(kern, plan, nwarps); r != NSB_OK) return r;
   } else {
     plan.wpc = tune.warps_per_cta > 0 ? std::min(tune.warps_per_cta, kBwdMaxThreads / 32) : 4;
     plan.stages = 1;
@@ -1523,6 +1607,7 @@ int scan_mod_fwd_dispatch(const FwdArgs& a) {
     PlanQuery q;
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
     q.nstreams = a.mode == MODE_RFMOD ? 5 : 4;
+    q.modulated = a.mode == MODE_RFMOD ? 2 : 1;
     q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;
     plan = plan_scan(dev, q, tune);
   }
@@ -1571,6 +1656,7 @@ int scan_mod_bwd_dispatch(const BwdArgs& a) {
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
     q.nstreams = (a.mode == MODE_RFMOD ? 5 : 4) + 1;
     q.stash = a.mode == MODE_RFMOD ? 5 : 3;
+    q.modulated = a.mode == MODE_RFMOD ? 2 : 1;
     // 4 lanes per thread spill heavily with the modulation's extra live values (measured 3x slower)
     q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 2 : 1;
     plan = plan_scan(dev, q, tune);
