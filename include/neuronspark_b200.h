@@ -327,6 +327,26 @@ int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const vo
                            int dtype, int ckpt_interval, int surrogate, float alpha, void* stream);
 
 /*
+ * Row-parameter scan followed by the binary residual, in one pass. Replaces the
+ * pair that ends SNNBlock.forward_parallel and SNNFFN.forward_parallel
+ * (atomic_ops/snn_block.py:281-285, atomic_ops/snn_ffn.py:188-195):
+ *   spike_out, V_last = plif_rowparam_forward_recompute(beta_row, u, v_th_row, v_init, alpha)
+ *   return binary_residual(spike_out, spike_in_seq)          (atomic_ops/fp16_codec.py:115-197)
+ * Every 16 steps of a column are one IEEE half bit pattern (frame 0 = sign):
+ * frames_out = encode(decode(spikes) + decode(frames_in)), with the reference's
+ * roundings for frames stored in `dtype`. The spikes themselves are never
+ * written. u, frames_in, frames_out are [T, cols] in `dtype`, T a multiple of
+ * 16; ckpt_interval is 16 or 32; v_ckpt ([T/ckpt_interval, cols] fp32) is what
+ * nsb_plif_rowparam_bwd needs - the residual's backward is the identity on both
+ * inputs (straight-through, :171-173), so the gradient arriving for frames_out is
+ * at once the gradient of frames_in and the g_spike of that call.
+ */
+int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const float* vth_row,
+                                   const float* v_init, const void* frames_in, void* frames_out,
+                                   float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
+                                   int ckpt_interval, void* stream);
+
+/*
  * The modulation alone, written out: beta, u, v_th (and omega when raw_omega is
  * given) as [rows, channels] tensors in dtype_out (NSB_F32, or dtype_in). A
  * drop-in for the reference's _fused_modulation(_rf) functions in code that

@@ -8,56 +8,15 @@
 // coalesced line. The kernels are pure streaming: the 16 frame reads (or
 // writes) of a thread are independent and all in flight together.
 #include "nsb_common.cuh"
+#include "nsb_codec.cuh"
 
 namespace nsb {
 namespace {
 
-// fp32 -> half bit pattern as the reference does it: clamp to +-65504, round
-// to nearest even. NaN maps to a quiet NaN with the input's sign.
-__device__ __forceinline__ uint32_t half_bits_clamped(float f) {
-  if (f != f) return ((__float_as_uint(f) >> 16) & 0x8000u) | 0x7e00u;
-  f = fminf(fmaxf(f, -65504.0f), 65504.0f);
-  return (uint32_t)__half_as_ushort(__float2half_rn(f));
-}
-
-__device__ __forceinline__ float round_through_bf16(float f) {
-  return __bfloat162float(__float2bfloat16_rn(f));
-}
-
-// Decode 16 frame values (any reals, normally {0,1}) to a number with the
-// reference's formula. EMU_BF16: round the mantissa sum, 1+m and the products
-// to bf16 where the reference's bf16 arithmetic does.
-template <bool EMU_BF16>
-__device__ __forceinline__ float decode16(const float (&bit)[16]) {
-  float sign = 1.0f - 2.0f * bit[0];
-  float e = 16.0f * bit[1] + 8.0f * bit[2] + 4.0f * bit[3] + 2.0f * bit[4] + bit[5];
-  float m = 0.0f;
-  float w = 0.5f;
-#pragma unroll
-  for (int i = 0; i < 10; ++i) {
-    m += bit[6 + i] * w;
-    w *= 0.5f;
-  }
-  if (EMU_BF16) {
-    sign = round_through_bf16(sign);
-    e = round_through_bf16(e);
-    m = round_through_bf16(m);
-  }
-  float val;
-  if (e > 0.0f) {
-    float opm = 1.0f + m;
-    float p = sign * exp2f(e - 15.0f);
-    if (EMU_BF16) {
-      opm = round_through_bf16(opm);
-      p = round_through_bf16(p);
-    }
-    val = p * opm;
-  } else {
-    val = (sign * 6.103515625e-05f) * m;
-  }
-  if (EMU_BF16) val = round_through_bf16(val);
-  return val;
-}
+using codec::decode16;
+using codec::half_bits_clamped;
+using codec::round_through_bf16;
+using codec::residual_half_bits;
 
 template <typename TI, typename TO, int VE>
 __global__ void encode_kernel(const TI* __restrict__ values, TO* __restrict__ frames, long long B,
@@ -195,10 +154,7 @@ __global__ void residual_kernel(const T* __restrict__ fa, const T* __restrict__ 
         ba[k] = Elem<T>::to_f32(a[k].v[j]);
         bb[k] = Elem<T>::to_f32(c[k].v[j]);
       }
-      float sum = decode16<EMU>(ba) + decode16<EMU>(bb);
-      if (EMU) sum = round_through_bf16(sum);
-      if (Elem<T>::kDtype == NSB_F16) sum = __half2float(__float2half_rn(sum));
-      h[j] = half_bits_clamped(sum);
+      h[j] = residual_half_bits<Elem<T>::kDtype>(ba, bb);
     }
 #pragma unroll
     for (int k = 0; k < 16; ++k) {

@@ -1,0 +1,73 @@
+// Device functions of the FP16 bit-plane codec shared by the codec kernels and by the scan
+// kernel that applies the binary residual to its own spikes.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/neuronspark_b200.h"
+
+namespace nsb {
+namespace codec {
+
+// fp32 -> half bit pattern as the reference does it: clamp to +-65504, round
+// to nearest even. NaN maps to a quiet NaN with the input's sign.
+__device__ __forceinline__ uint32_t half_bits_clamped(float f) {
+  if (f != f) return ((__float_as_uint(f) >> 16) & 0x8000u) | 0x7e00u;
+  f = fminf(fmaxf(f, -65504.0f), 65504.0f);
+  return (uint32_t)__half_as_ushort(__float2half_rn(f));
+}
+
+__device__ __forceinline__ float round_through_bf16(float f) {
+  return __bfloat162float(__float2bfloat16_rn(f));
+}
+
+// Decode 16 frame values (any reals, normally {0,1}) to a number with the
+// reference's formula. EMU_BF16: round the mantissa sum, 1+m and the products
+// to bf16 where the reference's bf16 arithmetic does.
+template <bool EMU_BF16>
+__device__ __forceinline__ float decode16(const float (&bit)[16]) {
+  float sign = 1.0f - 2.0f * bit[0];
+  float e = 16.0f * bit[1] + 8.0f * bit[2] + 4.0f * bit[3] + 2.0f * bit[4] + bit[5];
+  float m = 0.0f;
+  float w = 0.5f;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    m += bit[6 + i] * w;
+    w *= 0.5f;
+  }
+  if (EMU_BF16) {
+    sign = round_through_bf16(sign);
+    e = round_through_bf16(e);
+    m = round_through_bf16(m);
+  }
+  float val;
+  if (e > 0.0f) {
+    float opm = 1.0f + m;
+    float p = sign * exp2f(e - 15.0f);
+    if (EMU_BF16) {
+      opm = round_through_bf16(opm);
+      p = round_through_bf16(p);
+    }
+    val = p * opm;
+  } else {
+    val = (sign * 6.103515625e-05f) * m;
+  }
+  if (EMU_BF16) val = round_through_bf16(val);
+  return val;
+}
+
+// Half bit pattern of decode(a) + decode(b) for frames stored in DTYPE, with the roundings
+// the reference's arithmetic in that dtype performs (atomic_ops/fp16_codec.py:115-164).
+template <int DTYPE>
+__device__ __forceinline__ uint32_t residual_half_bits(const float (&a)[16], const float (&b)[16]) {
+  constexpr bool EMU = DTYPE == NSB_BF16;
+  float sum = decode16<EMU>(a) + decode16<EMU>(b);
+  if (EMU) sum = round_through_bf16(sum);
+  if (DTYPE == NSB_F16) sum = __half2float(__float2half_rn(sum));
+  return half_bits_clamped(sum);
+}
+
+}  // namespace codec
+}  // namespace nsb

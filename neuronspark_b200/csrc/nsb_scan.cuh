@@ -24,6 +24,7 @@
 #include <algorithm>
 #include <type_traits>
 
+#include "nsb_codec.cuh"
 #include "nsb_common.cuh"
 #include "nsb_modulation.cuh"
 
@@ -32,9 +33,12 @@ namespace nsb {
 // MODE_MOD / MODE_RFMOD are MODE_AI / MODE_RF with the modulation fused into the load path: they
 // stream the RAW projections (raw_beta, I, raw_alpha, raw_th [, raw_omega]) and form beta, u = alpha*I,
 // v_th (, omega) per element in registers (nsb_modulation.cuh).
+// MODE_ROWRES (forward only) is MODE_ROW followed by the binary residual of the FP16 codec: every 16
+// steps the column's spikes are one half bit pattern; it is decoded, added to the value decoded from
+// the 16 frames of a second input stream, re-encoded, and those frames are the output.
 // MODE_RF is the second-order resonate-and-fire scan: it streams beta, u, omega, v_th
 // (omega in the slot the gain*cur form uses for the gain) and carries two states, V and W.
-enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3, MODE_MOD = 4, MODE_RFMOD = 5 };
+enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3, MODE_MOD = 4, MODE_RFMOD = 5, MODE_ROWRES = 6 };
 
 struct FwdArgs {
   const void* beta = nullptr;   // streams ([T, cols], stream dtype)
@@ -107,6 +111,9 @@ int scan_bwd_f16(const BwdArgs& a);
 int scan_mod_fwd_f32(const FwdArgs& a);
 int scan_mod_fwd_bf16(const FwdArgs& a);
 int scan_mod_fwd_f16(const FwdArgs& a);
+int scan_res_fwd_f32(const FwdArgs& a);  // MODE_ROWRES, same translation units
+int scan_res_fwd_bf16(const FwdArgs& a);
+int scan_res_fwd_f16(const FwdArgs& a);
 int scan_mod_bwd_f32(const BwdArgs& a);
 int scan_mod_bwd_bf16(const BwdArgs& a);
 int scan_mod_bwd_f16(const BwdArgs& a);
@@ -320,14 +327,16 @@ template <int MODE>
 struct ModeTraits {
   static constexpr bool kSecond = MODE == MODE_RF || MODE == MODE_RFMOD;  // carries the second state W
   static constexpr bool kMod = MODE == MODE_MOD || MODE == MODE_RFMOD;    // modulation fused into the loads
+  static constexpr bool kRow = MODE == MODE_ROW || MODE == MODE_ROWRES;  // per-column beta / v_th
   static constexpr int kFwdStreams =
-      MODE == MODE_ROW ? 1 : (MODE == MODE_RFMOD ? 5 : ((MODE == MODE_AI || MODE == MODE_RF || MODE == MODE_MOD) ? 4 : 3));
+      MODE == MODE_ROW ? 1 : (MODE == MODE_ROWRES ? 2 : (MODE == MODE_RFMOD ? 5 : ((MODE == MODE_AI || MODE == MODE_RF || MODE == MODE_MOD) ? 4 : 3)));
   // index of each role inside the stage / pointer table (roles that a mode
   // does not stream alias slot 0 and are never read)
   static constexpr int kBeta = 0;
-  static constexpr int kDrive = MODE == MODE_ROW ? 0 : 1;
+  static constexpr int kDrive = kRow ? 0 : 1;
+  static constexpr int kRes = 1;  // MODE_ROWRES: the frames added to the scan's spikes
   static constexpr int kGain = kFwdStreams >= 4 ? 2 : 0;
-  static constexpr int kVth = MODE == MODE_ROW ? 0 : (kFwdStreams >= 4 ? 3 : 2);
+  static constexpr int kVth = kRow ? 0 : (kFwdStreams >= 4 ? 3 : 2);
   static constexpr int kOmega = MODE == MODE_RFMOD ? 4 : (MODE == MODE_RF ? 2 : 0);
 };
 
@@ -429,7 +438,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     w[j] = (MT::kSecond && valid[j]) ? p.w_init[colj[j]] : 0.0f;
     brow[j] = 0.0f;
     trow[j] = 0.0f;
-    if (MODE == MODE_ROW && valid[j]) {
+    if (MT::kRow && valid[j]) {
       brow[j] = p.beta_row[colj[j]];
       trow[j] = p.vth_row[colj[j]];
     }
@@ -518,7 +527,11 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
     // On the vector path dense spikes are written over the consumed drive tile in
     // shared memory and leave through one TMA store per tile (which also clips the
     // ragged edges), so the step loop carries no global address arithmetic for them.
-    ST* o_spike = (DIRECT && !DENSE_TMA && p.spike) ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
+    ST* o_spike = (DIRECT && !DENSE_TMA && MODE != MODE_ROWRES && p.spike)
+                      ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
+    uint32_t hb[V];  // MODE_ROWRES: the spikes of the current token as a half bit pattern
+#pragma unroll
+    for (int j = 0; j < V; ++j) hb[j] = 0u;
     ST* o_vpost = (DIRECT && p.vpost) ? static_cast<ST*>(p.vpost) + t0 * row_elems + colj[0] : nullptr;
     ST* o_wout = (DIRECT && MT::kSecond && p.w_out) ? static_cast<ST*>(p.w_out) + t0 * row_elems + colj[0] : nullptr;
     uint32_t keep[NSLOT][V];  // raw ballots of the step(s) this lane is responsible for
@@ -549,7 +562,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
       float b[V], th[V], dr[V], om[V], x[V];
       bool sp_[V];
       fetch(MT::kDrive, k, dr);
-      if constexpr (MODE == MODE_ROW) {
+      if constexpr (MT::kRow) {
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           b[j] = brow[j];
@@ -600,7 +613,53 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
         plif_step<V>(v, b, dr, th, x, sp_);
       }
 
-      if constexpr (VEC) {
+      if constexpr (MODE == MODE_ROWRES) {
+        // Step k is bit 15 - (k mod 16) of the token's half pattern (frame 0 = sign). After the
+        // token's last step: decode it, add the value decoded from the 16 input frames, re-encode,
+        // and write the 16 output frames over the token's (consumed) drive rows / to global memory.
+#pragma unroll
+        for (int j = 0; j < V; ++j) hb[j] = (k % 16 == 0 ? 0u : hb[j]) | (sp_[j] ? (1u << (15 - k % 16)) : 0u);
+        if (k % 16 == 15) {
+          const int k0 = k - 15;
+          float fb[16][V];
+          const ST* g_res = static_cast<const ST*>(p.s[MT::kRes]);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if constexpr (VEC) {
+              IO::load(sp + MT::kRes * TILE_ELEMS + (k0 + i) * (32 * V), fb[i]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < V; ++j)
+                fb[i][j] = valid[j] ? E::to_f32(g_res[(t0 + k0 + i) * row_elems + colj[j]]) : 0.0f;
+            }
+          }
+          uint32_t h[V];
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            float a_[16], b_[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              a_[i] = ((hb[j] >> (15 - i)) & 1u) ? 1.0f : 0.0f;
+              b_[i] = fb[i][j];
+            }
+            h[j] = codec::residual_half_bits<E::kDtype>(a_, b_);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            bool ob[V];
+#pragma unroll
+            for (int j = 0; j < V; ++j) ob[j] = (h[j] >> (15 - i)) & 1u;
+            if constexpr (VEC) {
+              IO::store_spikes(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + (k0 + i) * (32 * V), ob);
+            } else {
+              ST* g_out = static_cast<ST*>(p.spike);
+#pragma unroll
+              for (int j = 0; j < V; ++j)
+                if (valid[j]) g_out[(t0 + k0 + i) * row_elems + colj[j]] = ob[j] ? E::one() : E::zero();
+            }
+          }
+        }
+      } else if constexpr (VEC) {
         if constexpr (DENSE_TMA) IO::store_spikes(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + k * (32 * V), sp_);
         if constexpr (DIRECT) {
           // a thread's V columns are all valid or all invalid
@@ -1340,8 +1399,8 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   auto kern = plif_fwd_kernel<ST, MODE, PACKED, V, C, TMA>;
   FwdParams p = {};
   const void* streams[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
-  if (MODE == MODE_ROW) {
-    streams[0] = a.drive;
+  if (MT::kRow) {
+    streams[0] = a.drive; streams[1] = a.extra;  // MODE_ROWRES: the frames to add
   } else if (NS >= 4) {
     streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.gain; streams[3] = a.vth; streams[4] = a.extra;
   } else {
@@ -1632,6 +1691,40 @@ int scan_mod_fwd_dispatch(const FwdArgs& a) {
   NSB_MFWD_DIRECT(MODE_MOD, 8) NSB_MFWD_DIRECT(MODE_MOD, 32)
   NSB_MFWD_DIRECT(MODE_RFMOD, 8) NSB_MFWD_DIRECT(MODE_RFMOD, 32)
 #undef NSB_MFWD_DIRECT
+  return NSB_ERR_INVALID_ARG;
+}
+
+// Row-parameter scan + binary residual (MODE_ROWRES): tiles of 16 steps (one token; 1, 2 or 4
+// lanes per thread) or 32 steps (1 lane).
+template <typename ST>
+int scan_res_fwd_dispatch(const FwdArgs& a) {
+  DeviceInfo dev;
+  int r = get_device_info(&dev);
+  if (r != NSB_OK) return r;
+  if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
+  const Tuning tune = get_tuning();
+  bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
+  const void* ptrs[] = {a.drive, a.extra, a.spike, a.ckpt};
+  for (const void* q : ptrs) tma = tma && aligned16(q);
+  const int C = a.tile;
+  Plan plan;
+  if (tma) {
+    PlanQuery q;
+    q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
+    q.nstreams = 2;
+    q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;
+    plan = plan_scan(dev, q, tune);
+  }
+  const int V = plan.lanes;
+#define NSB_RFWD_CASE(V_, C_)                                                          \
+  if (V == V_ && C == C_) return launch_fwd_one<ST, MODE_ROWRES, false, V_, C_, true>(a, dev, tune, plan);
+  if (tma) {
+    NSB_RFWD_CASE(1, 16) NSB_RFWD_CASE(2, 16) NSB_RFWD_CASE(4, 16) NSB_RFWD_CASE(1, 32)
+    return NSB_ERR_INVALID_ARG;
+  }
+#undef NSB_RFWD_CASE
+  if (C == 16) return launch_fwd_one<ST, MODE_ROWRES, false, 1, 16, false>(a, dev, tune, plan);
+  if (C == 32) return launch_fwd_one<ST, MODE_ROWRES, false, 1, 32, false>(a, dev, tune, plan);
   return NSB_ERR_INVALID_ARG;
 }
 

@@ -32,6 +32,13 @@ int run_mod_fwd(const nsb::FwdArgs& a, int dtype) {
     default: return nsb::scan_mod_fwd_f16(a);
   }
 }
+int run_res_fwd(const nsb::FwdArgs& a, int dtype) {
+  switch (dtype) {
+    case NSB_F32: return nsb::scan_res_fwd_f32(a);
+    case NSB_BF16: return nsb::scan_res_fwd_bf16(a);
+    default: return nsb::scan_res_fwd_f16(a);
+  }
+}
 int run_mod_bwd(const nsb::BwdArgs& a, int dtype) {
   switch (dtype) {
     case NSB_F32: return nsb::scan_mod_bwd_f32(a);
@@ -334,6 +341,33 @@ int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const vo
       scratch, g_b_beta, g_b_alpha, g_b_th, rf ? g_b_omega : nullptr, cols / channels, channels, nb);
   NSB_CUDA_TRY(cudaGetLastError(), "launch sum_over_batch_kernel");
   return NSB_OK;
+}
+
+int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const float* vth_row,
+                                   const float* v_init, const void* frames_in, void* frames_out,
+                                   float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
+                                   int ckpt_interval, void* stream) {
+  if (T < 0 || cols < 0 || T % 16 != 0 || !dtype_ok(dtype) || (ckpt_interval != 16 && ckpt_interval != 32))
+    return NSB_ERR_INVALID_ARG;
+  if (cols == 0) return NSB_OK;
+  if (!beta_row || !vth_row || !v_init || !v_last) return NSB_ERR_INVALID_ARG;
+  const void* fp[] = {beta_row, vth_row, v_init, v_last, v_ckpt};
+  for (const void* p : fp)
+    if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
+  if (T == 0) {
+    NSB_CUDA_TRY(cudaMemcpyAsync(v_last, v_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice,
+                                 static_cast<cudaStream_t>(stream)), "copy v_init");
+    return NSB_OK;
+  }
+  if (!u || !frames_in || !frames_out) return NSB_ERR_INVALID_ARG;
+  if (!elem_aligned(u, dtype) || !elem_aligned(frames_in, dtype) || !elem_aligned(frames_out, dtype))
+    return NSB_ERR_INVALID_ARG;
+  nsb::FwdArgs a;
+  a.drive = u; a.extra = frames_in; a.beta_row = beta_row; a.vth_row = vth_row; a.v_init = v_init;
+  a.spike = frames_out; a.ckpt = v_ckpt; a.vlast = v_last;
+  a.T = T; a.cols = cols; a.mode = nsb::MODE_ROWRES; a.tile = ckpt_interval;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_res_fwd(a, dtype);
 }
 
 }  // extern "C"

@@ -1,8 +1,10 @@
-// Forward PLIF scan kernels with the modulation fused into the loads, bf16 stream dtype.
+// Forward PLIF scan kernels with the modulation fused into the loads, and the row-parameter
+// scan with the binary residual applied to its spikes, bf16 stream dtype.
 #include <cstring>
 
 #include "nsb_scan.cuh"
 
 namespace nsb {
 int scan_mod_fwd_bf16(const FwdArgs& a) { return scan_mod_fwd_dispatch<__nv_bfloat16>(a); }
+int scan_res_fwd_bf16(const FwdArgs& a) { return scan_res_fwd_dispatch<__nv_bfloat16>(a); }
 }  // namespace nsb

@@ -517,6 +517,62 @@ def plif_rowparam_forward_recompute(beta_row, u, v_th_row, v_init, alpha: float)
     return PLIFRowParamRecomputeScan.apply(beta_row, u, v_th_row, v_init, alpha)
 
 
+class PLIFRowParamResidualScan(torch.autograd.Function):
+    """Row-parameter scan + binary residual in one kernel: what the reference computes as
+    ``binary_residual(plif_rowparam_forward_recompute(...)[0], spike_in)`` at the end of
+    ``SNNBlock.forward_parallel`` and ``SNNFFN.forward_parallel`` (atomic_ops/snn_block.py:281-285,
+    atomic_ops/snn_ffn.py:188-195). Returns ``(frames_out, V_last)``. The residual's backward is
+    the identity on both of its inputs (atomic_ops/fp16_codec.py:171-173): the gradient arriving
+    for ``frames_out`` is returned for ``spike_in`` and drives the scan's backward."""
+
+    @staticmethod
+    def forward(ctx, beta_row, u, v_th_row, v_init, spike_in, alpha):
+        shape = u.shape[1:]
+        if spike_in.shape != u.shape or u.shape[0] % 16:
+            raise NSBError("spike_in must have u's shape (T*16, ...)")
+        dt = u.dtype if u.dtype in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+        u_c = _as_stream(u, dt)
+        fin = _as_stream(spike_in, dt)
+        beta32, vth32, v0 = (_row_f32(t, shape) for t in (beta_row, v_th_row, v_init))
+        dev = _lib.require_cuda(u_c, fin, beta32, vth32, v0)
+        T, cols = u_c.shape[0], _cols(u_c)
+        needs_grad = any(ctx.needs_input_grad[:4])
+        C = ctx.interval = 32 if _interval(cols, row_param=True) == 32 else 16
+        out = torch.empty_like(u_c)
+        ckpt = torch.empty((_n_tiles(T, C), cols), dtype=torch.float32, device=dev) if needs_grad else None
+        v_last = torch.empty(shape, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().nsb_plif_rowparam_residual_fwd(
+                _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(v0), _lib.ptr(fin), _lib.ptr(out),
+                _lib.ptr(ckpt), _lib.ptr(v_last), T, cols, _lib.dtype_code(dt), C, _lib.stream_ptr(dev)),
+                "nsb_plif_rowparam_residual_fwd")
+        if needs_grad:
+            ctx.save_for_backward(beta32, vth32, u_c, ckpt)
+        ctx.alpha = float(alpha)
+        ctx.in_dtypes = (beta_row.dtype, u.dtype, v_th_row.dtype, v_init.dtype)
+        ctx.row_shapes = (beta_row.shape, v_th_row.shape, v_init.shape)
+        ctx.spike_in_dtype = spike_in.dtype
+        v_last = v_last.to(v_init.dtype)
+        ctx.mark_non_differentiable(v_last)
+        return (out if out.dtype == u.dtype else out.to(u.dtype)), v_last
+
+    @staticmethod
+    def backward(ctx, grad_out, _grad_v_last):
+        g_spike_in = None
+        if ctx.needs_input_grad[4] and grad_out is not None:
+            g_spike_in = grad_out.to(ctx.spike_in_dtype)
+        if not any(ctx.needs_input_grad[:4]):
+            return None, None, None, None, g_spike_in, None
+        return _rowparam_backward(ctx, grad_out, None)[:4] + (g_spike_in, None)
+
+
+def plif_rowparam_residual_forward(beta_row, u, v_th_row, v_init, spike_in, alpha: float):
+    """``(binary_residual(spike, spike_in), V_last)`` with ``spike`` the output of the row-parameter
+    scan, in one kernel; arguments of ``plif_rowparam_forward_recompute`` plus ``spike_in``."""
+    beta_row, v_th_row, v_init = _rows(u, beta_row, v_th_row, v_init)
+    return PLIFRowParamResidualScan.apply(beta_row, u, v_th_row, v_init, spike_in, alpha)
+
+
 def _rf_apply(fn, beta, omega, u, v_th, v_init, w_init, surrogate_function):
     if surrogate_function is None:
         with torch.no_grad():
