@@ -66,6 +66,8 @@ INFERENCE_WORKLOADS = {
     "c1": dict(kind="row", B=8, T=8192, D=768, shard=False, calls=1, bytes_per_ns=2.125),
     "c4": dict(kind="ai", B=256, T=8192, D=6144, shard=True, calls=1, bytes_per_ns=8.125),
     "decode": dict(kind="ai", B=1024, T=16, D=6144, shard=True, calls=64, bytes_per_ns=8.625),
+    # output neuron of a block: row-parameter scan + binary residual in one kernel (dense frames out)
+    "res": dict(kind="rowres", B=32, T=8192, D=768, shard=False, calls=1, bytes_per_ns=6.0),
 }
 # algorithmic bytes per neuron-step with 2-byte streams
 BYTES_FWD = 4 * 2 + 2          # beta, I, alpha, V_th in; spikes out
@@ -544,7 +546,29 @@ def run_inference(args):
     packed = torch.empty((T * calls, words), dtype=torch.int32, device=dev)
     v_a = torch.zeros((B, D), dtype=torch.float32, device=dev)
     v_b = torch.empty_like(v_a)
-    if w["kind"] == "row":
+    unfused = None
+    if w["kind"] == "rowres":
+        from neuronspark_b200 import fp16_codec as codec
+        g = torch.Generator(device=dev).manual_seed(1234 + rank)
+        bd = torch.sigmoid(2 + 0.5 * torch.randn(D, generator=g, device=dev))
+        td = (0.5 + 0.1 * torch.randn(D, generator=g, device=dev)).clamp(min=0.05)
+        u = (3.0 * (1 - bd) * torch.randn(T, B, D, generator=g, device=dev)).bfloat16()
+        frames_in = codec.fp16_encode(torch.randn(B, T // 16, D, generator=g, device=dev).bfloat16())
+        frames_out = torch.empty_like(u)
+        beta_row, vth_row = bd.expand(B, D).contiguous(), td.expand(B, D).contiguous()
+        tile_steps = 32 if tile_steps == 32 else 16
+
+        def step():
+            _lib.check(L.nsb_plif_rowparam_residual_fwd(p(beta_row), p(u), p(vth_row), p(v_a), p(frames_in),
+                                                        p(frames_out), None, p(v_b), T, cols, _lib.BF16,
+                                                        tile_steps, stream), "rowparam_residual_fwd")
+
+        def unfused():
+            with torch.no_grad():
+                s_, _ = ps.plif_rowparam_forward_recompute(beta_row, u, vth_row, v_a, 4.0)
+                return codec.binary_residual(s_, frames_in)
+        packed = frames_out  # (for the spike-rate line below)
+    elif w["kind"] == "row":
         g = torch.Generator(device=dev).manual_seed(1234 + rank)
         bd = torch.sigmoid(2 + 0.5 * torch.randn(D, generator=g, device=dev))
         td = (0.5 + 0.1 * torch.randn(D, generator=g, device=dev)).clamp(min=0.05)
@@ -624,7 +648,7 @@ def run_inference(args):
             "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong" if w["shard"] else "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {w['kind']} forward, packed spikes, B={total_b} global "
+            "config": {"workload": f"{args.workload}: {w['kind']} forward, {'residual frames out' if w['kind'] == 'rowres' else 'packed spikes'}, B={total_b} global "
                                    f"({B} on this GPU), T={T} x {calls} call(s), D={D}, bf16 streams, fp32 state",
                        "l2": "L2 flushed between iterations" if flush is not None else "inputs larger than L2",
                        "launch": info},
@@ -634,8 +658,21 @@ def run_inference(args):
                          "note": "few columns: bounded by the serial chain over T, not by HBM"
                          if cols < 100000 else ""},
             "clocks": clocks, "gpu_launches": K * calls,
-            "spike_rate": float(((packed[:64].unsqueeze(-1) >> torch.arange(32, device=dev)) & 1).float().mean()),
         }
+        if unfused is not None:  # the two-kernel form on the same inputs, for scale (and a last parity check)
+            ref = unfused()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(5):
+                unfused()
+            b.record()
+            torch.cuda.synchronize()
+            line["metric"] = "PLIF scan neuron-steps/s (B*T*D), row-parameter forward + binary residual, one kernel"
+            line["unfused_ms"] = a.elapsed_time(b) / 5
+            line["matches_unfused"] = bool(torch.equal(ref, frames_out))
+        else:
+            line["spike_rate"] = float(((packed[:64].unsqueeze(-1) >> torch.arange(32, device=dev)) & 1).float().mean())
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
