@@ -327,6 +327,32 @@ int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const vo
                            int dtype, int ckpt_interval, int surrogate, float alpha, void* stream);
 
 /*
+ * Adaptive surrogate slope without a host round trip. Replaces the
+ * `u.std().item()` of PLIFNode.get_surrogate (atomic_ops/plif_node.py:78-101):
+ *   *alpha_out = clamp(alpha0 * sigma0 / max(std(u), 1e-6), 1, 20)
+ * with std the unbiased standard deviation of the n elements of u, rounded to
+ * `dtype` as torch's `u.std()` of such a tensor is. alpha_out is device memory
+ * (one float); scratch holds nsb_surrogate_alpha_scratch_doubles() doubles.
+ * Deterministic (fixed launch shape and summation order). n < 2 gives 20.
+ * The *_dalpha backward entry points below take that device float in place of
+ * the `alpha` argument and are otherwise identical to their namesakes.
+ */
+int64_t nsb_surrogate_alpha_scratch_doubles(void);
+int nsb_surrogate_alpha(const void* u, int64_t n, int dtype, float alpha0, float sigma0,
+                        double* scratch, float* alpha_out, void* stream);
+int nsb_plif_rowparam_bwd_dalpha(const float* beta_row, const void* u, const float* vth_row,
+                                 const float* v_ckpt, const void* g_spike, const void* g_vpost,
+                                 float* g_beta_row, void* g_u, float* g_vth_row, float* g_vinit,
+                                 int64_t T, int64_t cols, int dtype, int ckpt_interval,
+                                 int surrogate, const float* alpha_dev, void* stream);
+int nsb_plif_rf_bwd_dalpha(const void* beta, const void* omega, const void* u, const void* v_th,
+                           const float* v_ckpt, const float* w_ckpt, const void* g_spike,
+                           const void* g_vpost, void* g_beta, void* g_omega, void* g_u,
+                           void* g_vth, float* g_vinit, float* g_winit, int64_t T, int64_t cols,
+                           int dtype, int ckpt_interval, int surrogate, const float* alpha_dev,
+                           void* stream);
+
+/*
  * Row-parameter scan followed by the binary residual, in one pass. Replaces the
  * pair that ends SNNBlock.forward_parallel and SNNFFN.forward_parallel
  * (atomic_ops/snn_block.py:281-285, atomic_ops/snn_ffn.py:188-195):

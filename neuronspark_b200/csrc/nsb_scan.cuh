@@ -97,6 +97,7 @@ struct BwdArgs {
   int tile = 8;
   int surrogate = NSB_SURR_SIGMOID;
   float alpha = 4.0f;
+  const float* alpha_dev = nullptr;  // when set, the surrogate slope is read from device memory
   cudaStream_t stream = nullptr;
 };
 
@@ -821,6 +822,7 @@ struct BwdParams {
   int ntiles, stages, has_gv, nstreams;
   int defer;  // 1: a stage is refilled one tile after its outputs were handed to TMA
   float alpha;
+  const float* alpha_dev;
   uint32_t* err;
 };
 
@@ -978,7 +980,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     }
   };
 
-  const float alpha = p.alpha;
+  const float alpha = p.alpha_dev ? __ldg(p.alpha_dev) : p.alpha;
   const float c1 = SURR == NSB_SURR_ATAN ? 1.5707963267948966f * alpha : -alpha * 1.4426950408889634f;
   const float c2 = 0.5f * alpha;
   const long long row_elems = p.cols;
@@ -1480,7 +1482,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   p.g_beta_row = a.g_beta_row; p.g_vth_row = a.g_vth_row; p.g_vinit = a.g_vinit;
   p.T = a.T; p.cols = a.cols;
   p.ntiles = (int)((a.T + C - 1) / C);
-  p.has_gv = has_gv; p.nstreams = nstreams; p.alpha = a.alpha;
+  p.has_gv = has_gv; p.nstreams = nstreams; p.alpha = a.alpha; p.alpha_dev = a.alpha_dev;
   p.err = device_error_word_ptr();
 
   const long long nwarps = (a.cols + 32 * V - 1) / (32 * V);

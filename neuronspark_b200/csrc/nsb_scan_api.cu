@@ -148,10 +148,11 @@ int nsb_plif_selective_bwd(const void* beta, const void* u_or_cur, const void* g
   return run_bwd(a, dtype);
 }
 
-int nsb_plif_rowparam_bwd(const float* beta_row, const void* u, const float* vth_row, const float* v_ckpt,
-                          const void* g_spike, const void* g_vpost, float* g_beta_row, void* g_u,
-                          float* g_vth_row, float* g_vinit, int64_t T, int64_t cols, int dtype,
-                          int ckpt_interval, int surrogate, float alpha, void* stream) {
+static int rowparam_bwd_impl(const float* beta_row, const void* u, const float* vth_row, const float* v_ckpt,
+                             const void* g_spike, const void* g_vpost, float* g_beta_row, void* g_u,
+                             float* g_vth_row, float* g_vinit, int64_t T, int64_t cols, int dtype,
+                             int ckpt_interval, int surrogate, float alpha, const float* alpha_dev,
+                             void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
   if (surrogate != NSB_SURR_SIGMOID && surrogate != NSB_SURR_ATAN) return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
@@ -174,8 +175,26 @@ int nsb_plif_rowparam_bwd(const float* beta_row, const void* u, const float* vth
   a.g_spike = g_spike; a.g_vpost = g_vpost; a.g_drive = g_u;
   a.g_beta_row = g_beta_row; a.g_vth_row = g_vth_row; a.g_vinit = g_vinit;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_ROW; a.tile = ckpt_interval;
-  a.surrogate = surrogate; a.alpha = alpha; a.stream = st;
+  a.surrogate = surrogate; a.alpha = alpha; a.alpha_dev = alpha_dev; a.stream = st;
   return run_bwd(a, dtype);
+}
+
+int nsb_plif_rowparam_bwd(const float* beta_row, const void* u, const float* vth_row, const float* v_ckpt,
+                          const void* g_spike, const void* g_vpost, float* g_beta_row, void* g_u,
+                          float* g_vth_row, float* g_vinit, int64_t T, int64_t cols, int dtype,
+                          int ckpt_interval, int surrogate, float alpha, void* stream) {
+  return rowparam_bwd_impl(beta_row, u, vth_row, v_ckpt, g_spike, g_vpost, g_beta_row, g_u, g_vth_row, g_vinit,
+                           T, cols, dtype, ckpt_interval, surrogate, alpha, nullptr, stream);
+}
+
+int nsb_plif_rowparam_bwd_dalpha(const float* beta_row, const void* u, const float* vth_row,
+                                 const float* v_ckpt, const void* g_spike, const void* g_vpost,
+                                 float* g_beta_row, void* g_u, float* g_vth_row, float* g_vinit, int64_t T,
+                                 int64_t cols, int dtype, int ckpt_interval, int surrogate,
+                                 const float* alpha_dev, void* stream) {
+  if (!alpha_dev || !f32_aligned(alpha_dev)) return NSB_ERR_INVALID_ARG;
+  return rowparam_bwd_impl(beta_row, u, vth_row, v_ckpt, g_spike, g_vpost, g_beta_row, g_u, g_vth_row, g_vinit,
+                           T, cols, dtype, ckpt_interval, surrogate, 0.0f, alpha_dev, stream);
 }
 
 int nsb_plif_rf_fwd(const void* beta, const void* omega, const void* u, const void* v_th,
@@ -210,11 +229,11 @@ int nsb_plif_rf_fwd(const void* beta, const void* omega, const void* u, const vo
   return run_fwd(a, dtype);
 }
 
-int nsb_plif_rf_bwd(const void* beta, const void* omega, const void* u, const void* v_th,
-                    const float* v_ckpt, const float* w_ckpt, const void* g_spike, const void* g_vpost,
-                    void* g_beta, void* g_omega, void* g_u, void* g_vth, float* g_vinit, float* g_winit,
-                    int64_t T, int64_t cols, int dtype, int ckpt_interval, int surrogate, float alpha,
-                    void* stream) {
+static int rf_bwd_impl(const void* beta, const void* omega, const void* u, const void* v_th,
+                       const float* v_ckpt, const float* w_ckpt, const void* g_spike, const void* g_vpost,
+                       void* g_beta, void* g_omega, void* g_u, void* g_vth, float* g_vinit, float* g_winit,
+                       int64_t T, int64_t cols, int dtype, int ckpt_interval, int surrogate, float alpha,
+                       const float* alpha_dev, void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
   if (surrogate != NSB_SURR_SIGMOID && surrogate != NSB_SURR_ATAN) return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
@@ -237,8 +256,27 @@ int nsb_plif_rf_bwd(const void* beta, const void* omega, const void* u, const vo
   a.g_spike = g_spike; a.g_vpost = g_vpost; a.g_beta = g_beta; a.g_drive = g_u; a.g_gain = g_omega;
   a.g_vth = g_vth; a.g_vinit = g_vinit; a.g_winit = g_winit;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_RF; a.tile = ckpt_interval;
-  a.surrogate = surrogate; a.alpha = alpha; a.stream = st;
+  a.surrogate = surrogate; a.alpha = alpha; a.alpha_dev = alpha_dev; a.stream = st;
   return run_bwd(a, dtype);
+}
+
+int nsb_plif_rf_bwd(const void* beta, const void* omega, const void* u, const void* v_th,
+                    const float* v_ckpt, const float* w_ckpt, const void* g_spike, const void* g_vpost,
+                    void* g_beta, void* g_omega, void* g_u, void* g_vth, float* g_vinit, float* g_winit,
+                    int64_t T, int64_t cols, int dtype, int ckpt_interval, int surrogate, float alpha,
+                    void* stream) {
+  return rf_bwd_impl(beta, omega, u, v_th, v_ckpt, w_ckpt, g_spike, g_vpost, g_beta, g_omega, g_u, g_vth,
+                     g_vinit, g_winit, T, cols, dtype, ckpt_interval, surrogate, alpha, nullptr, stream);
+}
+
+int nsb_plif_rf_bwd_dalpha(const void* beta, const void* omega, const void* u, const void* v_th,
+                           const float* v_ckpt, const float* w_ckpt, const void* g_spike,
+                           const void* g_vpost, void* g_beta, void* g_omega, void* g_u, void* g_vth,
+                           float* g_vinit, float* g_winit, int64_t T, int64_t cols, int dtype,
+                           int ckpt_interval, int surrogate, const float* alpha_dev, void* stream) {
+  if (!alpha_dev || !f32_aligned(alpha_dev)) return NSB_ERR_INVALID_ARG;
+  return rf_bwd_impl(beta, omega, u, v_th, v_ckpt, w_ckpt, g_spike, g_vpost, g_beta, g_omega, g_u, g_vth,
+                     g_vinit, g_winit, T, cols, dtype, ckpt_interval, surrogate, 0.0f, alpha_dev, stream);
 }
 
 int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,

@@ -1,4 +1,4 @@
-"""Timing of the boundary kernels (FP16 codec, lateral inhibition) on one GPU.
+"""Timing of the boundary kernels (FP16 codec, lateral inhibition, adaptive surrogate slope) on one GPU.
 
     python -m neuronspark_b200.microbench [--dtype bf16|f32] [--iters N]
 
@@ -80,6 +80,15 @@ def main():
             ctx.eps, ctx.orig_shape, ctx.gain_dtype, ctx.gain_shape = 1e-6, x.shape, gain.dtype, gain.shape
             report("lateral_inhibition_bwd", (rows, D),
                    _time(lambda: fn.backward(ctx, go), args.iters, flush), rows * D * 4 * es)
+
+    # adaptive surrogate slope: one read of u (the reference pays the same pass plus a host sync)
+    from . import parallel_scan as ps
+    for shape in [(8192, 8, 768), (8192, 32, 6144)]:
+        if args.only in "surrogate_alpha":
+            u = torch.empty(shape, dtype=dt, device=dev).normal_()
+            report("surrogate_alpha", shape, _time(lambda: ps.adaptive_alpha(u, 4.0, 0.4), args.iters, flush),
+                   u.numel() * es)
+            del u
 
 
 class _Ctx:

@@ -104,6 +104,36 @@ def _surrogate_kind(surrogate) -> int:
         raise NSBError(f"unknown surrogate {surrogate!r}; expected 'sigmoid' or 'atan'") from None
 
 
+def adaptive_alpha(u: torch.Tensor, alpha0: float = 4.0, sigma0: float = 0.4) -> torch.Tensor:
+    """Adaptive surrogate slope ``clamp(alpha0 * sigma0 / max(u.std(), 1e-6), 1, 20)`` of
+    ``PLIFNode.get_surrogate`` (atomic_ops/plif_node.py:78-101) as a 0-dim float32 CUDA tensor,
+    computed without the ``.item()`` the reference pays per scan call. Pass the tensor as
+    ``alpha`` to the row-parameter scans, or as the ``.alpha`` of the surrogate object given to
+    the resonate-and-fire scans: their backward then reads the slope on the device."""
+    dev = _lib.require_cuda(u)
+    dt = u.dtype if u.dtype in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+    u_c = _as_stream(u.detach(), dt)
+    L = _lib.lib()
+    scratch = torch.empty(int(L.nsb_surrogate_alpha_scratch_doubles()), dtype=torch.float64, device=dev)
+    out = torch.empty((), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(L.nsb_surrogate_alpha(_lib.ptr(u_c), u_c.numel(), _lib.dtype_code(dt), float(alpha0),
+                                         float(sigma0), _lib.ptr(scratch), _lib.ptr(out),
+                                         _lib.stream_ptr(dev)), "nsb_surrogate_alpha")
+    return out
+
+
+def _split_alpha(alpha):
+    """(float, None) for a host number, (0.0, tensor) for a device-resident slope."""
+    if isinstance(alpha, torch.Tensor):
+        if alpha.numel() != 1:
+            raise NSBError("a tensor alpha must have one element")
+        if not alpha.is_cuda:
+            return float(alpha), None
+        return 0.0, alpha.detach().reshape(()).to(torch.float32)
+    return float(alpha), None
+
+
 def _n_tiles(T: int, interval: int) -> int:
     return (T + interval - 1) // interval
 
@@ -283,12 +313,20 @@ def _rowparam_backward(ctx, grad_spike, grad_V_post):
     g_u = torch.empty_like(u_c)
     g_beta, g_vth, g_v0 = (torch.empty(u_c.shape[1:], dtype=torch.float32, device=dev)
                            for _ in range(3))
+    alpha_t = getattr(ctx, "alpha_t", None)
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().nsb_plif_rowparam_bwd(
-            _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(ckpt), _lib.ptr(gs),
-            _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols,
-            _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), ctx.alpha,
-            _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd")
+        if alpha_t is not None:
+            _lib.check(_lib.lib().nsb_plif_rowparam_bwd_dalpha(
+                _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(ckpt), _lib.ptr(gs),
+                _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols,
+                _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), _lib.ptr(alpha_t),
+                _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd_dalpha")
+        else:
+            _lib.check(_lib.lib().nsb_plif_rowparam_bwd(
+                _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(ckpt), _lib.ptr(gs),
+                _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols,
+                _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), ctx.alpha,
+                _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd")
     db, du, dth, dv = ctx.in_dtypes
     return (g_beta.to(db).reshape(ctx.row_shapes[0]), g_u.to(du),
             g_vth.to(dth).reshape(ctx.row_shapes[1]), g_v0.to(dv).reshape(ctx.row_shapes[2]), None)
@@ -308,7 +346,7 @@ def _rowparam_forward(ctx, beta_row, u, v_th_row, v_init, alpha, want_vpost):
         want_ckpt=needs_grad)
     if needs_grad:
         ctx.save_for_backward(beta32, vth32, u_c, ckpt)
-    ctx.alpha = float(alpha)
+    ctx.alpha, ctx.alpha_t = _split_alpha(alpha)
     ctx.in_dtypes = (beta_row.dtype, u.dtype, v_th_row.dtype, v_init.dtype)
     ctx.row_shapes = (beta_row.shape, v_th_row.shape, v_init.shape)
     if spike.dtype != u.dtype:
@@ -376,7 +414,7 @@ def _rf_forward(ctx, beta, omega, u, v_th, v_init, w_init, alpha, want_states):
             _lib.stream_ptr(dev)), "nsb_plif_rf_fwd")
     if needs_grad:
         ctx.save_for_backward(beta_c, omega_c, u_c, vth_c, ckv, ckw)
-    ctx.alpha = float(alpha)
+    ctx.alpha, ctx.alpha_t = _split_alpha(alpha)
     ctx.in_dtypes = tuple(t.dtype for t in (beta, omega, u, v_th, v_init, w_init))
     ctx.state_shapes = (v_init.shape, w_init.shape)
     cast = (lambda t: None if t is None else t.to(out_dtype)) if spike.dtype != out_dtype else (lambda t: t)
@@ -394,12 +432,15 @@ def _rf_backward(ctx, grad_spike, grad_V_post):
     g_beta, g_omega, g_u, g_vth = (torch.empty_like(u_c) for _ in range(4))
     g_v0 = torch.empty(u_c.shape[1:], dtype=torch.float32, device=dev)
     g_w0 = torch.empty_like(g_v0)
+    alpha_t = getattr(ctx, "alpha_t", None)
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().nsb_plif_rf_bwd(
+        fn = _lib.lib().nsb_plif_rf_bwd if alpha_t is None else _lib.lib().nsb_plif_rf_bwd_dalpha
+        _lib.check(fn(
             _lib.ptr(beta_c), _lib.ptr(omega_c), _lib.ptr(u_c), _lib.ptr(vth_c), _lib.ptr(ckv),
             _lib.ptr(ckw), _lib.ptr(gs), _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_omega), _lib.ptr(g_u),
             _lib.ptr(g_vth), _lib.ptr(g_v0), _lib.ptr(g_w0), T, cols, _lib.dtype_code(dt), ctx.interval,
-            ctx_surrogate(ctx), ctx.alpha, _lib.stream_ptr(dev)), "nsb_plif_rf_bwd")
+            ctx_surrogate(ctx), ctx.alpha if alpha_t is None else _lib.ptr(alpha_t), _lib.stream_ptr(dev)),
+            "nsb_plif_rf_bwd")
     db, do, du, dth, dv, dw = ctx.in_dtypes
     return (g_beta.to(db), g_omega.to(do), g_u.to(du), g_vth.to(dth),
             g_v0.to(dv).reshape(ctx.state_shapes[0]), g_w0.to(dw).reshape(ctx.state_shapes[1]), None)
@@ -454,10 +495,13 @@ def _alpha_and_kind(surrogate_function):
     name = type(surrogate_function).__name__
     if not hasattr(surrogate_function, "alpha"):
         raise NSBError(f"surrogate {name} has no .alpha")
+    a = surrogate_function.alpha
+    if not (isinstance(a, torch.Tensor) and a.is_cuda):  # a device-resident slope stays on the device
+        a = float(a)
     if name == "Sigmoid":
-        return float(surrogate_function.alpha), _lib.SURR_SIGMOID
+        return a, _lib.SURR_SIGMOID
     if name == "ATan":
-        return float(surrogate_function.alpha), _lib.SURR_ATAN
+        return a, _lib.SURR_ATAN
     raise NSBError(f"surrogate {name} is not supported (Sigmoid or ATan)")
 
 
@@ -548,7 +592,7 @@ class PLIFRowParamResidualScan(torch.autograd.Function):
                 "nsb_plif_rowparam_residual_fwd")
         if needs_grad:
             ctx.save_for_backward(beta32, vth32, u_c, ckpt)
-        ctx.alpha = float(alpha)
+        ctx.alpha, ctx.alpha_t = _split_alpha(alpha)
         ctx.in_dtypes = (beta_row.dtype, u.dtype, v_th_row.dtype, v_init.dtype)
         ctx.row_shapes = (beta_row.shape, v_th_row.shape, v_init.shape)
         ctx.spike_in_dtype = spike_in.dtype

@@ -195,6 +195,22 @@ def plif_rf_bwd(beta, omega, u, vth, v_init, w_init, g_spike, g_vpost, alpha, ki
     return gb, go, gu, gt, gv, gw
 
 
+# ------------------------------------------------------- adaptive surrogate slope
+
+
+def surrogate_alpha(u, alpha0, sigma0, storage="f32"):
+    """``clamp(alpha0 * sigma0 / max(std(u), 1e-6), 1, 20)`` as PLIFNode.get_surrogate computes it
+    (atomic_ops/plif_node.py:93-100): unbiased std; ``u.std()`` of a bf16 / fp16 tensor is itself a
+    bf16 / fp16 number, and so is the 1e-6 floor."""
+    import torch
+    dt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[storage]
+    x = np.asarray(u, dtype=np.float64).ravel()
+    sd = float(np.std(x, ddof=1)) if x.size > 1 else 0.0
+    rnd = lambda v: float(torch.tensor(v, dtype=torch.float64).to(torch.float32).to(dt).double())
+    sd = max(rnd(sd), rnd(1e-6))
+    return float(np.float32(min(max(alpha0 * sigma0 / sd, 1.0), 20.0)))
+
+
 # ---------------------------------------------------------------- codec
 
 

@@ -31,6 +31,9 @@ What each fixture is produced by:
                   taken out of their files by name with ``ast`` (the modules need
                   SpikingJelly to import) and run eagerly, without their
                   torch.compile decorator, + autograd.
+  surrogate_alpha the four lines of PLIFNode.get_surrogate that derive the slope from
+                  u.std() (atomic_ops/plif_node.py:93-100; the method itself needs
+                  SpikingJelly), on fp32, bf16 and fp16 tensors.
   li_*            the PyTorch fallback of LateralInhibition.forward
                   (atomic_ops/lateral_inhibition.py:208-212) + autograd.
 """
@@ -319,6 +322,22 @@ def main():
         **{k: v for k, v in bias.items() if "omega" not in k}, v_th_min=np.float64(v_th_min),
         beta=beta, u=u, vth=vth, **{k: v for k, v in ups.items() if "omega" not in k},
         **{f"grad_{k}": v.grad for k, v in leaves.items()})
+
+    # ---- adaptive surrogate slope (atomic_ops/plif_node.py:93-100)
+    torch.manual_seed(5)
+    cases = {}
+    for i, (scale, dt) in enumerate([(0.05, torch.float32), (0.4, torch.float32), (3.0, torch.float32),
+                                     (0.13, torch.bfloat16), (0.77, torch.bfloat16), (1e-9, torch.bfloat16),
+                                     (0.31, torch.float16)]):
+        u = (torch.randn(40, 3, 50) * scale + 0.01).to(dt)
+        alpha_0, sigma_0 = 4.0, 0.4
+        sigma_V = u.std().clamp(min=1e-6)
+        alpha_adaptive = alpha_0 * sigma_0 / sigma_V.item()
+        alpha_adaptive = max(1.0, min(alpha_adaptive, 20.0))
+        cases[f"u{i}"] = u
+        cases[f"alpha{i}"] = np.float64(alpha_adaptive)
+        cases[f"dtype{i}"] = np.array({torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[dt])
+    npz("surrogate_alpha", n=np.array(7), alpha_0=np.float64(4.0), sigma_0=np.float64(0.4), **cases)
 
     # ---- lateral inhibition fallback (atomic_ops/lateral_inhibition.py:208-212)
     torch.manual_seed(42)

@@ -179,3 +179,11 @@ def test_modulation(golden, name):
                               **{k: v for k, v in extra.items() if k != "g_omega"})
     for a, b in zip(out, outh):
         assert np.array_equal(torch.from_numpy(a).half().float().numpy(), b)
+
+
+def test_surrogate_alpha(golden):
+    g = golden("surrogate_alpha")
+    for i in range(int(g["n"])):
+        storage = ("f32", "bf16", "f16")[int(g[f"dtype{i}"])]
+        mine = orc.surrogate_alpha(g[f"u{i}"], float(g["alpha_0"]), float(g["sigma_0"]), storage)
+        assert abs(mine - float(g[f"alpha{i}"])) <= 2e-6 * float(g[f"alpha{i}"]), (i, mine, float(g[f"alpha{i}"]))
