@@ -28,17 +28,29 @@ __global__ void moments_kernel(const T* __restrict__ u, long long n, double* __r
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   const bool vec = (reinterpret_cast<uintptr_t>(u) & 15u) == 0;
   const long long nvec = vec ? n / VE : 0;
-  for (long long i = tid; i < nvec; i += nthreads) {
-    const Vec<T, VE> x = *reinterpret_cast<const Vec<T, VE>*>(u + i * VE);
-    float s = 0.0f, q = 0.0f;
+  // four independent 16-byte loads per thread and iteration keep ~64 KB per SM in flight
+  constexpr int UN = 4;
+  for (long long i0 = tid; i0 < nvec; i0 += nthreads * UN) {
+    Vec<T, VE> x[UN];
 #pragma unroll
-    for (int j = 0; j < VE; ++j) {
-      const float f = Elem<T>::to_f32(x.v[j]);
-      s += f;
-      q = fmaf(f, f, q);
+    for (int r = 0; r < UN; ++r) {
+      const long long i = i0 + r * nthreads;
+      if (i < nvec) x[r] = *reinterpret_cast<const Vec<T, VE>*>(u + i * VE);
     }
-    ds += (double)s;
-    dq += (double)q;
+#pragma unroll
+    for (int r = 0; r < UN; ++r) {
+      if (i0 + r * nthreads < nvec) {
+        float s = 0.0f, q = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+          const float f = Elem<T>::to_f32(x[r].v[j]);
+          s += f;
+          q = fmaf(f, f, q);
+        }
+        ds += (double)s;
+        dq += (double)q;
+      }
+    }
   }
   for (long long i = nvec * VE + tid; i < n; i += nthreads) {  // tail, or everything when unaligned
     const double f = (double)Elem<T>::to_f32(u[i]);
