@@ -373,6 +373,41 @@ int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const f
                                    int ckpt_interval, void* stream);
 
 /*
+ * Linear recurrence V[k] = beta[k]*V[k-1] + u[k], V[-1] = v_init. Replaces
+ * _fwd_recurrence_kernel / _bwd_recurrence_kernel / _TritonLinearRecurrence and
+ * the CUDA branch of linear_recurrence (atomic_ops/parallel_scan.py:65-190,
+ * 1282-1302). beta, u, v_out [T, cols] in `dtype` (state in fp32, each step one
+ * rounded multiply and one rounded add); v_init, v_last [cols] fp32. The
+ * backward recomputes V tile by tile from v_ckpt ([ceil(T/ckpt_interval), cols]
+ * fp32, written by the forward when given) instead of reading a saved V:
+ *   g += dV[k]; grad_u[k] = g; grad_beta[k] = g * V[k-1]; g *= beta[k]   (:110-141)
+ * ckpt_interval is 8 or 32.
+ */
+int nsb_linear_recurrence_fwd(const void* beta, const void* u, const float* v_init, void* v_out,
+                              float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
+                              int ckpt_interval, void* stream);
+int nsb_linear_recurrence_bwd(const void* beta, const void* u, const float* v_ckpt, const void* g_v,
+                              void* g_beta, void* g_u, float* g_vinit, int64_t T, int64_t cols,
+                              int dtype, int ckpt_interval, void* stream);
+
+/*
+ * Mixture-of-experts output combine and its backward. Replaces
+ * _moe_combine_fwd_kernel, _moe_combine_bwd_expert_kernel,
+ * _moe_combine_bwd_weights_kernel and MoECombine (atomic_ops/moe_kernels.py:35-224):
+ *   out[n, d] = shared[n, d] + sum_e experts[e, n, d] * weights[n, e]
+ *   g_experts[e, n, d] = g_out[n, d] * weights[n, e]
+ *   g_weights[n, e]    = sum_d g_out[n, d] * experts[e, n, d]
+ * (grad of shared is g_out itself). shared / out / g_out [N, D], experts /
+ * g_experts [E, N, D] contiguous in `dtype`; weights / g_weights [N, E] fp32.
+ * fp32 accumulation. g_experts or g_weights may be NULL.
+ */
+int nsb_moe_combine_fwd(const void* shared, const void* experts, const float* weights, void* out,
+                        int64_t N, int64_t D, int E, int dtype, void* stream);
+int nsb_moe_combine_bwd(const void* g_out, const void* experts, const float* weights,
+                        void* g_experts, float* g_weights, int64_t N, int64_t D, int E, int dtype,
+                        void* stream);
+
+/*
  * The modulation alone, written out: beta, u, v_th (and omega when raw_omega is
  * given) as [rows, channels] tensors in dtype_out (NSB_F32, or dtype_in). A
  * drop-in for the reference's _fused_modulation(_rf) functions in code that

@@ -53,6 +53,10 @@ _SIGNATURES = {
     "nsb_plif_rf_bwd_dalpha": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
                                                           c_void_p]),
     "nsb_plif_rowparam_residual_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_linear_recurrence_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_linear_recurrence_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_moe_combine_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_moe_combine_bwd": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_modulation_fwd": (c_int, [c_void_p] * 9 + [c_float, c_int64, c_int64] + [c_void_p] * 4 +
                            [c_int, c_int, c_void_p]),
     "nsb_fp16_encode": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),

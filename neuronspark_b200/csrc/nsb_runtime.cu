@@ -116,6 +116,14 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, int dtype, uint64_t r
   CUresult r = fn(out, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // A thread that has made no CUDA runtime call yet (seen: PyTorch's autograd thread when a
+    // backward is the first thing it runs) has no context bound for driver entry points; a
+    // runtime call binds the device's primary context, then the encode succeeds.
+    cudaFree(nullptr);
+    r = fn(out, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) {
     set_driver_error(static_cast<int>(r), "cuTensorMapEncodeTiled");
     return NSB_ERR_CUDA;

@@ -33,12 +33,15 @@ namespace nsb {
 // MODE_MOD / MODE_RFMOD are MODE_AI / MODE_RF with the modulation fused into the load path: they
 // stream the RAW projections (raw_beta, I, raw_alpha, raw_th [, raw_omega]) and form beta, u = alpha*I,
 // v_th (, omega) per element in registers (nsb_modulation.cuh).
+// MODE_LIN is the linear recurrence V[k] = beta[k]*V[k-1] + u[k] (no threshold, no reset): the u-form
+// scan with an infinite threshold whose dense output is V instead of the spikes and whose incoming
+// gradient is that of V.
 // MODE_ROWRES (forward only) is MODE_ROW followed by the binary residual of the FP16 codec: every 16
 // steps the column's spikes are one half bit pattern; it is decoded, added to the value decoded from
 // the 16 frames of a second input stream, re-encoded, and those frames are the output.
 // MODE_RF is the second-order resonate-and-fire scan: it streams beta, u, omega, v_th
 // (omega in the slot the gain*cur form uses for the gain) and carries two states, V and W.
-enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3, MODE_MOD = 4, MODE_RFMOD = 5, MODE_ROWRES = 6 };
+enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3, MODE_MOD = 4, MODE_RFMOD = 5, MODE_ROWRES = 6, MODE_LIN = 7 };
 
 struct FwdArgs {
   const void* beta = nullptr;   // streams ([T, cols], stream dtype)
@@ -115,6 +118,12 @@ int scan_mod_fwd_f16(const FwdArgs& a);
 int scan_res_fwd_f32(const FwdArgs& a);  // MODE_ROWRES, same translation units
 int scan_res_fwd_bf16(const FwdArgs& a);
 int scan_res_fwd_f16(const FwdArgs& a);
+int scan_lin_fwd_f32(const FwdArgs& a);  // MODE_LIN, same translation units as the modulated modes
+int scan_lin_fwd_bf16(const FwdArgs& a);
+int scan_lin_fwd_f16(const FwdArgs& a);
+int scan_lin_bwd_f32(const BwdArgs& a);
+int scan_lin_bwd_bf16(const BwdArgs& a);
+int scan_lin_bwd_f16(const BwdArgs& a);
 int scan_mod_bwd_f32(const BwdArgs& a);
 int scan_mod_bwd_bf16(const BwdArgs& a);
 int scan_mod_bwd_f16(const BwdArgs& a);
@@ -330,14 +339,14 @@ struct ModeTraits {
   static constexpr bool kMod = MODE == MODE_MOD || MODE == MODE_RFMOD;    // modulation fused into the loads
   static constexpr bool kRow = MODE == MODE_ROW || MODE == MODE_ROWRES;  // per-column beta / v_th
   static constexpr int kFwdStreams =
-      MODE == MODE_ROW ? 1 : (MODE == MODE_ROWRES ? 2 : (MODE == MODE_RFMOD ? 5 : ((MODE == MODE_AI || MODE == MODE_RF || MODE == MODE_MOD) ? 4 : 3)));
+      MODE == MODE_ROW ? 1 : ((MODE == MODE_ROWRES || MODE == MODE_LIN) ? 2 : (MODE == MODE_RFMOD ? 5 : ((MODE == MODE_AI || MODE == MODE_RF || MODE == MODE_MOD) ? 4 : 3)));
   // index of each role inside the stage / pointer table (roles that a mode
   // does not stream alias slot 0 and are never read)
   static constexpr int kBeta = 0;
   static constexpr int kDrive = kRow ? 0 : 1;
   static constexpr int kRes = 1;  // MODE_ROWRES: the frames added to the scan's spikes
   static constexpr int kGain = kFwdStreams >= 4 ? 2 : 0;
-  static constexpr int kVth = kRow ? 0 : (kFwdStreams >= 4 ? 3 : 2);
+  static constexpr int kVth = (kRow || MODE == MODE_LIN) ? 0 : (kFwdStreams >= 4 ? 3 : 2);
   static constexpr int kOmega = MODE == MODE_RFMOD ? 4 : (MODE == MODE_RF ? 2 : 0);
 };
 
@@ -569,6 +578,10 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
           b[j] = brow[j];
           th[j] = trow[j];
         }
+      } else if constexpr (MODE == MODE_LIN) {
+        fetch(MT::kBeta, k, b);
+#pragma unroll
+        for (int j = 0; j < V; ++j) th[j] = __int_as_float(0x7f800000);  // +inf: never fires
       } else {
         fetch(MT::kBeta, k, b);
         fetch(MT::kVth, k, th);
@@ -661,7 +674,10 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
           }
         }
       } else if constexpr (VEC) {
-        if constexpr (DENSE_TMA) IO::store_spikes(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + k * (32 * V), sp_);
+        if constexpr (DENSE_TMA && MODE == MODE_LIN)  // the dense output of the linear recurrence is V
+          IO::store(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + k * (32 * V), v);
+        else if constexpr (DENSE_TMA)
+          IO::store_spikes(const_cast<ST*>(sp) + MT::kDrive * TILE_ELEMS + k * (32 * V), sp_);
         if constexpr (DIRECT) {
           // a thread's V columns are all valid or all invalid
           if (!DENSE_TMA && o_spike && valid[0]) IO::store_spikes(o_spike + (size_t)k * row_elems, sp_);
@@ -673,7 +689,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
         for (int j = 0; j < V; ++j) {
           if (DIRECT && valid[j]) {
             const size_t off = (size_t)k * row_elems + (colj[j] - colj[0]);
-            if (o_spike) o_spike[off] = sp_[j] ? E::one() : E::zero();
+            if (o_spike) o_spike[off] = MODE == MODE_LIN ? E::from_f32(v[j]) : (sp_[j] ? E::one() : E::zero());
             if (o_vpost) o_vpost[off] = E::from_f32(v[j]);
             if (MT::kSecond && o_wout) o_wout[off] = E::from_f32(w[j]);
           }
@@ -1026,6 +1042,10 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
             b[j] = brow[j];
             th[j] = trow[j];
           }
+        } else if constexpr (MODE == MODE_LIN) {
+          fetch(MT::kBeta, k, b);
+#pragma unroll
+          for (int j = 0; j < V; ++j) th[j] = __int_as_float(0x7f800000);
         } else {
           fetch(MT::kBeta, k, b);
           fetch(MT::kVth, k, th);
@@ -1094,7 +1114,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
       const int k = C - 1 - kk;
       if (FULL || k < nsteps) {
         float sg[V], gs[V], tot[V], gssg[V], gpre[V], b[V], gb[V], gth[V], gd[V], gg[V], go[V];
-        surrogate_grad<SURR, V>(sg, xs[k], alpha, c1, c2);
+        if constexpr (MODE != MODE_LIN) surrogate_grad<SURR, V>(sg, xs[k], alpha, c1, c2);
         fetch(kGS, k, gs);
         if (has_gv) {
           float gv[V];
@@ -1104,7 +1124,13 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
 #pragma unroll
           for (int j = 0; j < V; ++j) tot[j] = acc[j];
         }
-        vmul<V>(gssg, gs, sg);
+        if constexpr (MODE == MODE_LIN) {
+          // the incoming stream is dL/dV[k]: g = acc + dV[k]; grad u = g; grad beta = g*V[k-1]; acc = g*beta
+#pragma unroll
+          for (int j = 0; j < V; ++j) gssg[j] = gs[j];
+        } else {
+          vmul<V>(gssg, gs, sg);
+        }
         vadd<V>(gpre, gssg, tot);
         vmul<V>(gb, gpre, vprev[k]);
         // grad v_th = -gS*sg - tot*spike = -(spike ? gpre : gS*sg)
@@ -1222,10 +1248,9 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
         if constexpr (MODE != MODE_RF && !MT::kMod) vmul<V>(acc, gpre, b);
 
         if constexpr (TMA) {
-          if constexpr (MODE != MODE_ROW) {
-            IO::store(wsp + MT::kBeta * TILE_ELEMS + k * (32 * V), gb);
+          if constexpr (MODE != MODE_ROW) IO::store(wsp + MT::kBeta * TILE_ELEMS + k * (32 * V), gb);
+          if constexpr (MODE != MODE_ROW && MODE != MODE_LIN)
             IO::store(wsp + MT::kVth * TILE_ELEMS + k * (32 * V), gth);
-          }
           if constexpr (MODE == MODE_RFMOD) IO::store(wsp + MT::kOmega * TILE_ELEMS + k * (32 * V), go);
           if constexpr (MT::kFwdStreams >= 4) {
             IO::store(wsp + MT::kDrive * TILE_ELEMS + k * (32 * V), gd);
@@ -1241,10 +1266,8 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
             for (int j = 0; j < V; ++j)
               if (valid[j]) dst[ro + j] = E::from_f32(val[j]);
           };
-          if constexpr (MODE != MODE_ROW) {
-            put(o_beta, gb);
-            put(o_vth, gth);
-          }
+          if constexpr (MODE != MODE_ROW) put(o_beta, gb);
+          if constexpr (MODE != MODE_ROW && MODE != MODE_LIN) put(o_vth, gth);
           if constexpr (MODE == MODE_RFMOD) put(o_omega, go);
           if constexpr (MT::kFwdStreams >= 4) {
             put(o_drive, gd);
@@ -1312,7 +1335,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
         const uint32_t src = data0 + (uint32_t)s_idx * stage_bytes;
         const int x = (int)col0, y = i * C;
         if (MODE != MODE_ROW && p.g_beta) tma_store_2d(&tmo_beta, src + MT::kBeta * TILE_BYTES, x, y);
-        if (MODE != MODE_ROW && p.g_vth) tma_store_2d(&tmo_vth, src + MT::kVth * TILE_BYTES, x, y);
+        if (MODE != MODE_ROW && MODE != MODE_LIN && p.g_vth) tma_store_2d(&tmo_vth, src + MT::kVth * TILE_BYTES, x, y);
         if (p.g_drive) tma_store_2d(&tmo_drive, src + MT::kDrive * TILE_BYTES, x, y);
         if (MT::kFwdStreams >= 4 && p.g_gain) tma_store_2d(&tmo_gain, src + MT::kGain * TILE_BYTES, x, y);
         if (MODE == MODE_RFMOD && p.g_extra) tma_store_2d(&tmo_omega, src + MT::kOmega * TILE_BYTES, x, y);
@@ -1406,7 +1429,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   } else if (NS >= 4) {
     streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.gain; streams[3] = a.vth; streams[4] = a.extra;
   } else {
-    streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.vth;
+    streams[0] = a.beta; streams[1] = a.drive; streams[2] = a.vth;  // (MODE_LIN: no v_th stream)
   }
   for (int i = 0; i < 5; ++i) p.s[i] = streams[i];
   for (int i = 0; i < 4; ++i) p.bias[i] = a.bias[i];
@@ -1727,6 +1750,73 @@ int scan_res_fwd_dispatch(const FwdArgs& a) {
 #undef NSB_RFWD_CASE
   if (C == 16) return launch_fwd_one<ST, MODE_ROWRES, false, 1, 16, false>(a, dev, tune, plan);
   if (C == 32) return launch_fwd_one<ST, MODE_ROWRES, false, 1, 32, false>(a, dev, tune, plan);
+  return NSB_ERR_INVALID_ARG;
+}
+
+// Linear recurrence (MODE_LIN): tiles of 8 steps (1, 2 or 4 lanes per thread) or 32 steps (1 lane).
+template <typename ST>
+int scan_lin_fwd_dispatch(const FwdArgs& a) {
+  DeviceInfo dev;
+  int r = get_device_info(&dev);
+  if (r != NSB_OK) return r;
+  if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
+  const Tuning tune = get_tuning();
+  bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
+  const void* ptrs[] = {a.beta, a.drive, a.spike, a.vpost, a.ckpt};
+  for (const void* q : ptrs) tma = tma && aligned16(q);
+  const int C = a.tile;
+  Plan plan;
+  if (tma) {
+    PlanQuery q;
+    q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
+    q.nstreams = 2;
+    q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;
+    plan = plan_scan(dev, q, tune);
+  }
+  const int V = plan.lanes;
+#define NSB_LFWD_CASE(V_, C_)                                                          \
+  if (V == V_ && C == C_) return launch_fwd_one<ST, MODE_LIN, false, V_, C_, true>(a, dev, tune, plan);
+  if (tma) {
+    NSB_LFWD_CASE(1, 8) NSB_LFWD_CASE(2, 8) NSB_LFWD_CASE(4, 8) NSB_LFWD_CASE(1, 32)
+    return NSB_ERR_INVALID_ARG;
+  }
+#undef NSB_LFWD_CASE
+  if (C == 8) return launch_fwd_one<ST, MODE_LIN, false, 1, 8, false>(a, dev, tune, plan);
+  if (C == 32) return launch_fwd_one<ST, MODE_LIN, false, 1, 32, false>(a, dev, tune, plan);
+  return NSB_ERR_INVALID_ARG;
+}
+
+template <typename ST>
+int scan_lin_bwd_dispatch(const BwdArgs& a) {
+  DeviceInfo dev;
+  int r = get_device_info(&dev);
+  if (r != NSB_OK) return r;
+  if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
+  if (a.g_vpost) return NSB_ERR_INVALID_ARG;
+  const Tuning tune = get_tuning();
+  bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
+  const void* ptrs[] = {a.beta, a.drive, a.ckpt, a.g_spike, a.g_beta, a.g_drive};
+  for (const void* q : ptrs) tma = tma && aligned16(q);
+  const int C = a.tile;
+  Plan plan;
+  if (tma) {
+    PlanQuery q;
+    q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
+    q.nstreams = 3;
+    q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : 1;
+    plan = plan_scan(dev, q, tune);
+  }
+  const int V = plan.lanes;
+#define NSB_LBWD_CASE(V_, C_)                                                          \
+  if (V == V_ && C == C_)                                                              \
+    return launch_bwd_impl<ST, MODE_LIN, NSB_SURR_SIGMOID, V_, C_, true, false>(a, dev, tune, plan);
+  if (tma) {
+    NSB_LBWD_CASE(1, 8) NSB_LBWD_CASE(2, 8) NSB_LBWD_CASE(4, 8) NSB_LBWD_CASE(1, 32)
+    return NSB_ERR_INVALID_ARG;
+  }
+#undef NSB_LBWD_CASE
+  if (C == 8) return launch_bwd_impl<ST, MODE_LIN, NSB_SURR_SIGMOID, 1, 8, false, false>(a, dev, tune, plan);
+  if (C == 32) return launch_bwd_impl<ST, MODE_LIN, NSB_SURR_SIGMOID, 1, 32, false, false>(a, dev, tune, plan);
   return NSB_ERR_INVALID_ARG;
 }
 

@@ -39,6 +39,20 @@ int run_res_fwd(const nsb::FwdArgs& a, int dtype) {
     default: return nsb::scan_res_fwd_f16(a);
   }
 }
+int run_lin_fwd(const nsb::FwdArgs& a, int dtype) {
+  switch (dtype) {
+    case NSB_F32: return nsb::scan_lin_fwd_f32(a);
+    case NSB_BF16: return nsb::scan_lin_fwd_bf16(a);
+    default: return nsb::scan_lin_fwd_f16(a);
+  }
+}
+int run_lin_bwd(const nsb::BwdArgs& a, int dtype) {
+  switch (dtype) {
+    case NSB_F32: return nsb::scan_lin_bwd_f32(a);
+    case NSB_BF16: return nsb::scan_lin_bwd_bf16(a);
+    default: return nsb::scan_lin_bwd_f16(a);
+  }
+}
 int run_mod_bwd(const nsb::BwdArgs& a, int dtype) {
   switch (dtype) {
     case NSB_F32: return nsb::scan_mod_bwd_f32(a);
@@ -406,6 +420,53 @@ int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const f
   a.T = T; a.cols = cols; a.mode = nsb::MODE_ROWRES; a.tile = ckpt_interval;
   a.stream = static_cast<cudaStream_t>(stream);
   return run_res_fwd(a, dtype);
+}
+
+int nsb_linear_recurrence_fwd(const void* beta, const void* u, const float* v_init, void* v_out,
+                              float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
+                              int ckpt_interval, void* stream) {
+  if (T < 0 || cols < 0 || !dtype_ok(dtype) || (ckpt_interval != 8 && ckpt_interval != 32))
+    return NSB_ERR_INVALID_ARG;
+  if (cols == 0) return NSB_OK;
+  if (!v_init || !v_last || !f32_aligned(v_init) || !f32_aligned(v_last) || !f32_aligned(v_ckpt))
+    return NSB_ERR_INVALID_ARG;
+  if (T == 0) {
+    NSB_CUDA_TRY(cudaMemcpyAsync(v_last, v_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice,
+                                 static_cast<cudaStream_t>(stream)), "copy v_init");
+    return NSB_OK;
+  }
+  if (!beta || !u || !v_out) return NSB_ERR_INVALID_ARG;
+  if (!elem_aligned(beta, dtype) || !elem_aligned(u, dtype) || !elem_aligned(v_out, dtype))
+    return NSB_ERR_INVALID_ARG;
+  nsb::FwdArgs a;
+  a.beta = beta; a.drive = u; a.v_init = v_init; a.spike = v_out; a.ckpt = v_ckpt; a.vlast = v_last;
+  a.T = T; a.cols = cols; a.mode = nsb::MODE_LIN; a.tile = ckpt_interval;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_lin_fwd(a, dtype);
+}
+
+int nsb_linear_recurrence_bwd(const void* beta, const void* u, const float* v_ckpt, const void* g_v,
+                              void* g_beta, void* g_u, float* g_vinit, int64_t T, int64_t cols, int dtype,
+                              int ckpt_interval, void* stream) {
+  if (T < 0 || cols < 0 || !dtype_ok(dtype) || (ckpt_interval != 8 && ckpt_interval != 32))
+    return NSB_ERR_INVALID_ARG;
+  if (cols == 0) return NSB_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!f32_aligned(v_ckpt) || !f32_aligned(g_vinit)) return NSB_ERR_INVALID_ARG;
+  if (T == 0) {
+    if (g_vinit) NSB_CUDA_TRY(cudaMemsetAsync(g_vinit, 0, sizeof(float) * cols, st), "memset grad v_init");
+    return NSB_OK;
+  }
+  if (!beta || !u || !v_ckpt || !g_v) return NSB_ERR_INVALID_ARG;
+  const void* ep[] = {beta, u, g_v, g_beta, g_u};
+  for (const void* p : ep)
+    if (!elem_aligned(p, dtype)) return NSB_ERR_INVALID_ARG;
+  nsb::BwdArgs a;
+  a.beta = beta; a.drive = u; a.ckpt = v_ckpt; a.g_spike = g_v; a.g_beta = g_beta; a.g_drive = g_u;
+  a.g_vinit = g_vinit;
+  a.T = T; a.cols = cols; a.mode = nsb::MODE_LIN; a.tile = ckpt_interval;
+  a.surrogate = NSB_SURR_SIGMOID; a.alpha = 1.0f; a.stream = st;
+  return run_lin_bwd(a, dtype);
 }
 
 }  // extern "C"

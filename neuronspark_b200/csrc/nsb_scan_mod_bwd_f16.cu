@@ -5,4 +5,5 @@
 
 namespace nsb {
 int scan_mod_bwd_f16(const BwdArgs& a) { return scan_mod_bwd_dispatch<__half>(a); }
+int scan_lin_bwd_f16(const BwdArgs& a) { return scan_lin_bwd_dispatch<__half>(a); }
 }  // namespace nsb

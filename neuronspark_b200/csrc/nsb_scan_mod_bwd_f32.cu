@@ -5,4 +5,5 @@
 
 namespace nsb {
 int scan_mod_bwd_f32(const BwdArgs& a) { return scan_mod_bwd_dispatch<float>(a); }
+int scan_lin_bwd_f32(const BwdArgs& a) { return scan_lin_bwd_dispatch<float>(a); }
 }  // namespace nsb

@@ -13,15 +13,15 @@ the originals back.
     import neuronspark_b200.install as nsb_install
     nsb_install.install()               # snn_block / snn_ffn / model now call the CUDA kernels
 
-Functions of the reference that this package does not replace (the linear
-recurrence, MoE combine) are left untouched.
+Functions of the reference that this package does not replace (e.g.
+``hillis_steele_scan``) are left untouched.
 """
 from __future__ import annotations
 
 import sys
 from types import ModuleType
 
-from . import fp16_codec, lateral_inhibition, parallel_scan
+from . import fp16_codec, lateral_inhibition, moe_kernels, parallel_scan
 
 #: reference module (by its name inside the ``atomic_ops`` package) -> replacement names
 REPLACEMENTS = {
@@ -30,11 +30,12 @@ REPLACEMENTS = {
         "plif_parallel_forward", "plif_rowparam_forward", "plif_rowparam_forward_alpha",
         "plif_rowparam_forward_recompute", "plif_fixed_param_forward",
         "_TritonRFPLIFForward", "_TritonRFPLIFRecompute", "rf_plif_parallel_forward",
-        "rf_plif_parallel_forward_recompute")),
+        "rf_plif_parallel_forward_recompute", "_TritonLinearRecurrence", "linear_recurrence")),
     "fp16_codec": (fp16_codec, (
         "fp16_encode", "fp16_decode", "binary_residual", "binary_encode_ste", "_BinaryResidual",
         "_BinaryEncodeSTE")),
     "lateral_inhibition": (lateral_inhibition, ("_LateralInhibitionTriton",)),
+    "moe_kernels": (moe_kernels, ("MoECombine", "moe_combine")),
 }
 
 _undo: list[tuple[ModuleType, str, object]] = []

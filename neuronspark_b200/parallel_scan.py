@@ -298,6 +298,64 @@ class PLIFSelectiveScanAI(torch.autograd.Function):
                 g_v0.to(dv).reshape(ctx.v_init_shape), None, None)
 
 
+# ------------------------------------------------------------- linear recurrence
+
+
+class PLIFLinearRecurrence(torch.autograd.Function):
+    """``V[k] = beta[k]*V[k-1] + u[k]``; contract of the reference's ``_TritonLinearRecurrence``
+    (atomic_ops/parallel_scan.py:143-190): returns V ``[K, ...]`` in ``u``'s dtype, gradients for
+    beta, u and v_init. The backward recomputes V from fp32 checkpoints instead of re-reading it."""
+
+    @staticmethod
+    def forward(ctx, beta, u, v_init):
+        dt = _common_stream_dtype(beta, u)
+        beta_c, u_c = _as_stream(beta, dt), _as_stream(u, dt)
+        shape = u.shape[1:]
+        v0 = _row_f32(v_init, shape)
+        dev = _lib.require_cuda(beta_c, u_c, v0)
+        T, cols = u_c.shape[0], _cols(u_c)
+        needs_grad = any(ctx.needs_input_grad[:3])
+        C = ctx.interval = 32 if _interval(cols) == 32 else 8
+        V = torch.empty_like(u_c)
+        ckpt = torch.empty((_n_tiles(T, C), cols), dtype=torch.float32, device=dev) if needs_grad else None
+        v_last = torch.empty(shape, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().nsb_linear_recurrence_fwd(
+                _lib.ptr(beta_c), _lib.ptr(u_c), _lib.ptr(v0), _lib.ptr(V), _lib.ptr(ckpt), _lib.ptr(v_last),
+                T, cols, _lib.dtype_code(dt), C, _lib.stream_ptr(dev)), "nsb_linear_recurrence_fwd")
+        if needs_grad:
+            ctx.save_for_backward(beta_c, u_c, ckpt)
+        ctx.in_dtypes = (beta.dtype, u.dtype, v_init.dtype)
+        ctx.v_init_shape = v_init.shape
+        return V if V.dtype == u.dtype else V.to(u.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_V):
+        beta_c, u_c, ckpt = ctx.saved_tensors
+        dt, dev = u_c.dtype, u_c.device
+        T, cols = u_c.shape[0], _cols(u_c)
+        if grad_V is None:
+            grad_V = torch.zeros_like(u_c)
+        gv = _grad_stream(grad_V, u_c, dt)
+        g_beta, g_u = torch.empty_like(u_c), torch.empty_like(u_c)
+        g_v0 = torch.empty(u_c.shape[1:], dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().nsb_linear_recurrence_bwd(
+                _lib.ptr(beta_c), _lib.ptr(u_c), _lib.ptr(ckpt), _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u),
+                _lib.ptr(g_v0), T, cols, _lib.dtype_code(dt), ctx.interval, _lib.stream_ptr(dev)),
+                "nsb_linear_recurrence_bwd")
+        db, du, dv = ctx.in_dtypes
+        return g_beta.to(db), g_u.to(du), g_v0.to(dv).reshape(ctx.v_init_shape)
+
+
+_TritonLinearRecurrence = PLIFLinearRecurrence  # the reference's name for the same contract
+
+
+def linear_recurrence(beta: torch.Tensor, u: torch.Tensor, v_init: torch.Tensor) -> torch.Tensor:
+    """Reference: atomic_ops/parallel_scan.py:1282-1302. Returns V ``(K, *shape)``."""
+    return PLIFLinearRecurrence.apply(beta, u, v_init)
+
+
 # ------------------------------------------------------------- row-param scans
 
 

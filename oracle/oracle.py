@@ -195,6 +195,50 @@ def plif_rf_bwd(beta, omega, u, vth, v_init, w_init, g_spike, g_vpost, alpha, ki
     return gb, go, gu, gt, gv, gw
 
 
+# ------------------------------------------------------------ linear recurrence
+
+
+def linear_recurrence_fwd(beta, u, v_init):
+    """V [T, ...] of V[k] = beta[k]*V[k-1] + u[k] (atomic_ops/parallel_scan.py:1282-1302)."""
+    beta, u, v_init = map(_f32, (beta, u, v_init))
+    T, cols = _tc(u)
+    out = np.empty_like(u)
+    lib().orc_linear_recurrence_fwd(_p(beta), _p(u), _p(v_init), _p(out), _i64(T), _i64(cols))
+    return out
+
+
+def linear_recurrence_bwd(beta, u, v_init, g_v):
+    """(g_beta, g_u, g_vinit) for a gradient arriving on V."""
+    beta, u, v_init, g_v = map(_f32, (beta, u, v_init, g_v))
+    T, cols = _tc(u)
+    gb, gu = np.empty_like(u), np.empty_like(u)
+    gv0 = np.empty_like(v_init)
+    lib().orc_linear_recurrence_bwd(_p(beta), _p(u), _p(v_init), _p(g_v), _p(gb), _p(gu), _p(gv0),
+                                    _i64(T), _i64(cols))
+    return gb, gu, gv0
+
+
+# ------------------------------------------------------------------ MoE combine
+
+
+def moe_combine_fwd(shared, experts, weights):
+    """out (N, D) = shared + sum_e experts[e] * weights[:, e] (atomic_ops/moe_kernels.py:210-224)."""
+    shared, experts, weights = map(_f32, (shared, experts, weights))
+    E, N, D = experts.shape
+    out = np.empty_like(shared)
+    lib().orc_moe_combine_fwd(_p(shared), _p(experts), _p(weights), _p(out), _i64(N), _i64(D), _i64(E))
+    return out
+
+
+def moe_combine_bwd(g_out, experts, weights):
+    """(g_experts (E, N, D), g_weights (N, E)); the gradient of ``shared`` is ``g_out``."""
+    g_out, experts, weights = map(_f32, (g_out, experts, weights))
+    E, N, D = experts.shape
+    ge, gw = np.empty_like(experts), np.empty_like(weights)
+    lib().orc_moe_combine_bwd(_p(g_out), _p(experts), _p(weights), _p(ge), _p(gw), _i64(N), _i64(D), _i64(E))
+    return ge, gw
+
+
 # ------------------------------------------------------- adaptive surrogate slope
 
 

@@ -832,3 +832,83 @@ static inline float round_f16(float f) {
 static inline float orc_mod_round(float f, int mode) {
   return mode == 1 ? round_bf16(f) : (mode == 2 ? round_f16(f) : f);
 }
+
+/* ------------------------------------------------------------------ */
+/* Linear recurrence V[k] = beta[k]*V[k-1] + u[k]                      */
+/* (atomic_ops/parallel_scan.py:65-141; public linear_recurrence       */
+/* :1282-1302). Forward in fp32, one rounded multiply and one rounded  */
+/* add per step; adjoint in double:                                    */
+/*   g += dV[k]; grad_u[k] = g; grad_beta[k] = g*V[k-1]; g *= beta[k]  */
+/* ------------------------------------------------------------------ */
+void orc_linear_recurrence_fwd(const float *beta, const float *u,
+                               const float *vinit, float *vout, int64_t T,
+                               int64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (int64_t c = 0; c < cols; ++c) {
+    float v = vinit[c];
+    for (int64_t k = 0; k < T; ++k) {
+      const float bv = beta[k * cols + c] * v;
+      v = bv + u[k * cols + c];
+      vout[k * cols + c] = v;
+    }
+  }
+}
+
+void orc_linear_recurrence_bwd(const float *beta, const float *u,
+                               const float *vinit, const float *g_v,
+                               float *g_beta, float *g_u, float *g_vinit,
+                               int64_t T, int64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (int64_t c = 0; c < cols; ++c) {
+    /* forward states in fp32, as the forward computes them */
+    float v = vinit[c];
+    float *vprev = (float *)g_u; /* reuse the output column as scratch for V[k-1] */
+    for (int64_t k = 0; k < T; ++k) {
+      vprev[k * cols + c] = v;
+      const float bv = beta[k * cols + c] * v;
+      v = bv + u[k * cols + c];
+    }
+    double g = 0.0;
+    for (int64_t k = T - 1; k >= 0; --k) {
+      g += (double)g_v[k * cols + c];
+      const double vp = (double)vprev[k * cols + c];
+      g_u[k * cols + c] = (float)g;
+      g_beta[k * cols + c] = (float)(g * vp);
+      g *= (double)beta[k * cols + c];
+    }
+    g_vinit[c] = (float)g;
+  }
+}
+
+/* ------------------------------------------------------------------ */
+/* MoE combine (atomic_ops/moe_kernels.py:1-13, 210-224): double       */
+/* accumulation, rounded once.                                         */
+/* ------------------------------------------------------------------ */
+void orc_moe_combine_fwd(const float *shared, const float *experts,
+                         const float *w, float *out, int64_t N, int64_t D,
+                         int64_t E) {
+#pragma omp parallel for schedule(static)
+  for (int64_t n = 0; n < N; ++n)
+    for (int64_t d = 0; d < D; ++d) {
+      double acc = shared[n * D + d];
+      for (int64_t e = 0; e < E; ++e)
+        acc += (double)experts[(e * N + n) * D + d] * (double)w[n * E + e];
+      out[n * D + d] = (float)acc;
+    }
+}
+
+void orc_moe_combine_bwd(const float *g_out, const float *experts,
+                         const float *w, float *g_experts, float *g_w,
+                         int64_t N, int64_t D, int64_t E) {
+#pragma omp parallel for schedule(static)
+  for (int64_t n = 0; n < N; ++n)
+    for (int64_t e = 0; e < E; ++e) {
+      double dot = 0.0;
+      for (int64_t d = 0; d < D; ++d) {
+        const double g = g_out[n * D + d];
+        g_experts[(e * N + n) * D + d] = (float)(g * (double)w[n * E + e]);
+        dot += g * (double)experts[(e * N + n) * D + d];
+      }
+      g_w[n * E + e] = (float)dot;
+    }
+}

@@ -31,6 +31,9 @@ What each fixture is produced by:
                   taken out of their files by name with ``ast`` (the modules need
                   SpikingJelly to import) and run eagerly, without their
                   torch.compile decorator, + autograd.
+  moe_a           moe_combine (atomic_ops/moe_kernels.py:210-224; its CPU branch) + autograd.
+  linrec_a        linear_recurrence (atomic_ops/parallel_scan.py:1282-1302; on CPU the
+                  Hillis-Steele scan, :1238-1275) + autograd.
   surrogate_alpha the four lines of PLIFNode.get_surrogate that derive the slope from
                   u.std() (atomic_ops/plif_node.py:93-100; the method itself needs
                   SpikingJelly), on fp32, bf16 and fp16 tensors.
@@ -322,6 +325,31 @@ def main():
         **{k: v for k, v in bias.items() if "omega" not in k}, v_th_min=np.float64(v_th_min),
         beta=beta, u=u, vth=vth, **{k: v for k, v in ups.items() if "omega" not in k},
         **{f"grad_{k}": v.grad for k, v in leaves.items()})
+
+    # ---- MoE combine
+    moe = load("ref_moe_kernels", "atomic_ops/moe_kernels.py")
+    torch.manual_seed(33)
+    E_, N_, D_ = 4, 10, 24
+    msh = torch.randn(N_, D_).requires_grad_()
+    mex = torch.randn(E_, N_, D_).requires_grad_()
+    mw = torch.softmax(torch.randn(N_, E_), -1).requires_grad_()
+    mout = moe.moe_combine(msh, mex, mw)
+    mg = torch.randn(N_, D_)
+    (mout * mg).sum().backward()
+    npz("moe_a", shared=msh, experts=mex, weights=mw, out=mout, g_out=mg, g_shared=msh.grad, g_experts=mex.grad,
+        g_weights=mw.grad)
+
+    # ---- linear recurrence (the reference's CPU branch is a Hillis-Steele scan: same numbers up to
+    # the association of the products, not bit-comparable with a sequential loop)
+    torch.manual_seed(21)
+    T, B, D = 37, 2, 24
+    lb = torch.sigmoid(torch.randn(T, B, D) + 1.0).requires_grad_()
+    lu = torch.randn(T, B, D).requires_grad_()
+    lv0 = torch.randn(B, D).requires_grad_()
+    Vl = ps.linear_recurrence(lb, lu, lv0)
+    gVl = torch.randn(T, B, D)
+    (Vl * gVl).sum().backward()
+    npz("linrec_a", beta=lb, u=lu, v_init=lv0, V=Vl, g_V=gVl, g_beta=lb.grad, g_u=lu.grad, g_vinit=lv0.grad)
 
     # ---- adaptive surrogate slope (atomic_ops/plif_node.py:93-100)
     torch.manual_seed(5)

@@ -13,7 +13,7 @@ def fake_reference():
     pkg.__path__ = []
     ps = types.ModuleType("fake_atomic_ops.parallel_scan")
     for n in ("plif_parallel_forward", "plif_rowparam_forward_recompute", "plif_fixed_param_forward",
-              "linear_recurrence"):
+              "linear_recurrence", "hillis_steele_scan"):
         setattr(ps, n, (lambda name: (lambda *a, **k: name))(n))
     ps._TritonPLIFForward = type("_TritonPLIFForward", (), {})
     codec = types.ModuleType("fake_atomic_ops.fp16_codec")
@@ -33,7 +33,7 @@ def fake_reference():
 def test_install_patches_definitions_and_by_name_imports(fake_reference):
     from neuronspark_b200 import fp16_codec, install as inst, parallel_scan
     ps, codec, ffn = fake_reference
-    rf = ps.linear_recurrence
+    rf = ps.hillis_steele_scan
     changed = inst.install("fake_atomic_ops")
     assert ps.plif_rowparam_forward_recompute is parallel_scan.plif_rowparam_forward_recompute
     assert ps._TritonPLIFForward is parallel_scan._TritonPLIFForward
@@ -43,7 +43,8 @@ def test_install_patches_definitions_and_by_name_imports(fake_reference):
     assert ffn.binary_residual is fp16_codec.binary_residual
     assert "fake_atomic_ops.snn_ffn.binary_residual" in changed
     # what this package does not implement stays the reference's
-    assert ps.linear_recurrence is rf and ffn.unrelated == 7
+    assert ps.linear_recurrence is parallel_scan.linear_recurrence
+    assert ps.hillis_steele_scan is rf and ffn.unrelated == 7
     assert inst.uninstall() == len(changed)
     assert ps.plif_rowparam_forward_recompute() == "plif_rowparam_forward_recompute"
     assert ffn.binary_residual() == "ref-residual"

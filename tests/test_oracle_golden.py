@@ -187,3 +187,21 @@ def test_surrogate_alpha(golden):
         storage = ("f32", "bf16", "f16")[int(g[f"dtype{i}"])]
         mine = orc.surrogate_alpha(g[f"u{i}"], float(g["alpha_0"]), float(g["sigma_0"]), storage)
         assert abs(mine - float(g[f"alpha{i}"])) <= 2e-6 * float(g[f"alpha{i}"]), (i, mine, float(g[f"alpha{i}"]))
+
+
+def test_linear_recurrence(golden):
+    """The reference's CPU branch is a Hillis-Steele scan (another association of the same
+    products), so the comparison is to a tolerance: 1e-5 of the largest value."""
+    g = golden("linrec_a")
+    V = orc.linear_recurrence_fwd(g["beta"], g["u"], g["v_init"])
+    assert rel_err(V, g["V"]) < TOL
+    gb, gu, gv0 = orc.linear_recurrence_bwd(g["beta"], g["u"], g["v_init"], g["g_V"])
+    assert rel_err(gb, g["g_beta"]) < TOL and rel_err(gu, g["g_u"]) < TOL and rel_err(gv0, g["g_vinit"]) < TOL
+
+
+def test_moe_combine(golden):
+    g = golden("moe_a")
+    assert rel_err(orc.moe_combine_fwd(g["shared"], g["experts"], g["weights"]), g["out"]) < TOL
+    ge, gw = orc.moe_combine_bwd(g["g_out"], g["experts"], g["weights"])
+    assert rel_err(ge, g["g_experts"]) < TOL and rel_err(gw, g["g_weights"]) < TOL
+    assert np.array_equal(g["g_shared"], g["g_out"])
