@@ -11,10 +11,13 @@
 namespace nsb {
 namespace {
 
-template <typename T, int VE>
+// EC > 0: the number of experts is the compile-time EC (all of a thread's loads are issued
+// before the first use); EC == 0: any E.
+template <typename T, int VE, int EC>
 __global__ void moe_combine_fwd_kernel(const T* __restrict__ shared, const T* __restrict__ experts,
                                        const float* __restrict__ w, T* __restrict__ out, long long N,
-                                       long long D, int E) {
+                                       long long D, int E_rt) {
+  const int E = EC > 0 ? EC : E_rt;
   const long long dv = D / VE;
   const long long total = N * dv;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -24,11 +27,26 @@ __global__ void moe_combine_fwd_kernel(const T* __restrict__ shared, const T* __
     float acc[VE];
 #pragma unroll
     for (int j = 0; j < VE; ++j) acc[j] = Elem<T>::to_f32(s.v[j]);
-    for (int e = 0; e < E; ++e) {
-      const float we = w[n * E + e];
-      const Vec<T, VE> x = *reinterpret_cast<const Vec<T, VE>*>(experts + ((long long)e * N + n) * D + d);
+    if constexpr (EC > 0) {
+      Vec<T, VE> x[EC];
+      float we[EC];
 #pragma unroll
-      for (int j = 0; j < VE; ++j) acc[j] = fmaf(Elem<T>::to_f32(x.v[j]), we, acc[j]);
+      for (int e = 0; e < EC; ++e) {
+        we[e] = w[n * EC + e];
+        x[e] = *reinterpret_cast<const Vec<T, VE>*>(experts + ((long long)e * N + n) * D + d);
+      }
+#pragma unroll
+      for (int e = 0; e < EC; ++e)
+#pragma unroll
+        for (int j = 0; j < VE; ++j) acc[j] = fmaf(Elem<T>::to_f32(x[e].v[j]), we[e], acc[j]);
+    } else {
+#pragma unroll 4
+      for (int e = 0; e < E; ++e) {
+        const float we = w[n * E + e];
+        const Vec<T, VE> x = *reinterpret_cast<const Vec<T, VE>*>(experts + ((long long)e * N + n) * D + d);
+#pragma unroll
+        for (int j = 0; j < VE; ++j) acc[j] = fmaf(Elem<T>::to_f32(x.v[j]), we, acc[j]);
+      }
     }
     Vec<T, VE> o;
 #pragma unroll
@@ -93,10 +111,17 @@ int moe_fwd(const void* shared, const void* experts, const float* w, void* out, 
   const int threads = 256;
   const int blocks = (int)std::max<long long>(1, std::min<long long>((items + threads - 1) / threads,
                                                                      (long long)dev.sm_count * 16));
+#define NSB_GO_E(VE_, EC_)                                                                               \
+  moe_combine_fwd_kernel<T, VE_, EC_><<<blocks, threads, 0, st>>>(static_cast<const T*>(shared),         \
+                                                                  static_cast<const T*>(experts), w,     \
+                                                                  static_cast<T*>(out), N, D, E)
 #define NSB_GO(VE_)                                                                                      \
-  moe_combine_fwd_kernel<T, VE_><<<blocks, threads, 0, st>>>(static_cast<const T*>(shared),              \
-                                                             static_cast<const T*>(experts), w,          \
-                                                             static_cast<T*>(out), N, D, E)
+  do {                                                                                                   \
+    if (E == 2) NSB_GO_E(VE_, 2);                                                                        \
+    else if (E == 4) NSB_GO_E(VE_, 4);                                                                   \
+    else if (E == 8) NSB_GO_E(VE_, 8);                                                                   \
+    else NSB_GO_E(VE_, 0);                                                                               \
+  } while (0)
   switch (ve) {
     case 8: NSB_GO((sizeof(T) == 2 ? 8 : 1)); break;
     case 4: NSB_GO(4); break;
@@ -104,6 +129,7 @@ int moe_fwd(const void* shared, const void* experts, const float* w, void* out, 
     default: NSB_GO(1); break;
   }
 #undef NSB_GO
+#undef NSB_GO_E
   NSB_CUDA_TRY(cudaGetLastError(), "launch moe_combine_fwd_kernel");
   return NSB_OK;
 }

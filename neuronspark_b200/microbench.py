@@ -16,6 +16,7 @@ import torch
 
 from . import fp16_codec as codec
 from . import lateral_inhibition as li
+from . import parallel_scan as ps
 
 
 def _time(fn, iters, flush):
@@ -81,8 +82,43 @@ def main():
             report("lateral_inhibition_bwd", (rows, D),
                    _time(lambda: fn.backward(ctx, go), args.iters, flush), rows * D * 4 * es)
 
+    # linear recurrence, forward and forward+backward (2 streams in, 1 out; backward 3 in, 2 out)
+    from . import moe_kernels as mk
+    if args.only in "linear_recurrence":
+        T, B, D = 8192, 32, 6144
+        beta = torch.rand(T, B, D, device=dev).to(dt)
+        u = torch.empty(T, B, D, dtype=dt, device=dev).normal_()
+        v0 = torch.zeros(B, D, device=dev)
+        with torch.no_grad():
+            report("linear_recurrence_fwd", (T, B, D), _time(lambda: ps.linear_recurrence(beta, u, v0), args.iters, flush),
+                   T * B * D * 3 * es)
+        bl, ul = beta.requires_grad_(), u.requires_grad_()
+        gV = torch.empty(T, B, D, dtype=dt, device=dev).normal_()
+
+        def fb():
+            ps.linear_recurrence(bl, ul, v0).backward(gV)
+            bl.grad = ul.grad = None
+        report("linear_recurrence_fwd_bwd", (T, B, D), _time(fb, args.iters, flush), T * B * D * 8 * es)
+        del beta, u, gV, bl, ul
+    if args.only in "moe_combine":
+        for E, N, D in [(4, 65536, 768), (8, 32768, 768)]:
+            sh = torch.empty(N, D, dtype=dt, device=dev).normal_()
+            ex = torch.empty(E, N, D, dtype=dt, device=dev).normal_()
+            w = torch.softmax(torch.randn(N, E, device=dev), -1)
+            with torch.no_grad():
+                report("moe_combine_fwd", (E, N, D), _time(lambda: mk.moe_combine(sh, ex, w), args.iters, flush),
+                       (E + 2) * N * D * es)
+            exl, wl = ex.requires_grad_(), w.requires_grad_()
+            go = torch.empty(N, D, dtype=dt, device=dev).normal_()
+            out = mk.moe_combine(sh, exl, wl)
+
+            def bw():
+                out.backward(go, retain_graph=True)
+                exl.grad = wl.grad = None
+            report("moe_combine_bwd", (E, N, D), _time(bw, args.iters, flush), (2 * E + 1) * N * D * es)
+            del sh, ex, w, exl, wl, go, out
+
     # adaptive surrogate slope: one read of u (the reference pays the same pass plus a host sync)
-    from . import parallel_scan as ps
     for shape in [(8192, 8, 768), (8192, 32, 6144)]:
         if args.only in "surrogate_alpha":
             u = torch.empty(shape, dtype=dt, device=dev).normal_()
