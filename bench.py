@@ -412,8 +412,8 @@ def run_modulated(args):
     def fwd():
         _lib.check(L.nsb_plif_modulated_fwd(
             p(raw_beta), p(raw_alpha), p(raw_th), p(raw_omega), p(cur), p(bias[0]), p(bias[1]), p(bias[2]),
-            p(bias[3]), 0.1, D, p(v0), p(w0), p(spike), None, p(ckv), p(ckw), p(v_last), p(w_last), T, cols,
-            _lib.BF16, C, stream), "nsb_plif_modulated_fwd")
+            p(bias[3]), 0.1, D, p(v0), p(w0), p(spike), None, p(ckv), p(ckw), p(v_last), p(w_last), 4.0, 0.4,
+            None, None, T, cols, _lib.BF16, C, stream), "nsb_plif_modulated_fwd")
         info.setdefault("fwd", _lib.last_launch_info())
 
     def bwd():
@@ -422,7 +422,7 @@ def run_modulated(args):
             p(bias[3]), 0.1, D, p(ckv), p(ckw), p(g_spike), p(grads[0]), p(grads[1]), p(grads[2]),
             p(grads[4]) if rf else None, p(grads[3]), p(g_bias[0]), p(g_bias[1]), p(g_bias[2]),
             p(g_bias[3]) if rf else None, p(scratch), p(g_v0), p(g_w0), T, cols, _lib.BF16, C,
-            _lib.SURR_SIGMOID, 4.0, stream), "nsb_plif_modulated_bwd")
+            _lib.SURR_SIGMOID, 4.0, None, stream), "nsb_plif_modulated_bwd")
         info.setdefault("bwd", _lib.last_launch_info())
 
     def barrier():

@@ -295,13 +295,22 @@ int nsb_lateral_inhibition_bwd_static(const void* g_out, const void* x, const vo
  * hardware approximations, relative error < 1e-6 against correct rounding;
  * the modulated values are not rounded to `dtype` (the reference rounds them
  * when its parameters are bf16).
+ * Adaptive surrogate slope (optional; both pointers or neither): the reference
+ * derives it from `u_hidden.std()` (atomic_ops/plif_node.py:93-100), a tensor
+ * that no longer exists here. The kernel accumulates the moments of
+ * u = alpha*I while it streams and *alpha_out (device) receives
+ * clamp(alpha0 * sigma0 / max(std(u), 1e-6), 1, 20), std taken at fp32;
+ * u_stats is scratch of nsb_plif_modulated_fwd_stats_doubles(cols) doubles.
+ * Give alpha_out to nsb_plif_modulated_bwd as alpha_dev.
  */
+int64_t nsb_plif_modulated_fwd_stats_doubles(int64_t cols);
 int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
                            const void* raw_omega, const void* cur, const float* b_beta,
                            const float* b_alpha, const float* b_th, const float* b_omega,
                            float v_th_min, int64_t channels, const float* v_init,
                            const float* w_init, void* spike_dense, uint32_t* spike_packed,
-                           float* v_ckpt, float* w_ckpt, float* v_last, float* w_last, int64_t T,
+                           float* v_ckpt, float* w_ckpt, float* v_last, float* w_last,
+                           float alpha0, float sigma0, double* u_stats, float* alpha_out, int64_t T,
                            int64_t cols, int dtype, int ckpt_interval, void* stream);
 
 /* Floats of scratch nsb_plif_modulated_bwd needs when any bias gradient is asked for. */
@@ -315,6 +324,7 @@ int64_t nsb_plif_modulated_bwd_scratch_floats(int64_t cols);
  * ([T, cols], `dtype`), of the biases (fp32 [channels], summed over time and
  * batch in a fixed order; needs `scratch`), of v_init / w_init (fp32 [cols]).
  * Replaces the autograd backward of the two reference functions named above.
+ * alpha_dev, when not NULL, is a device float that overrides `alpha`.
  */
 int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
                            const void* raw_omega, const void* cur, const float* b_beta,
@@ -324,7 +334,8 @@ int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const vo
                            void* g_raw_alpha, void* g_raw_th, void* g_raw_omega, void* g_cur,
                            float* g_b_beta, float* g_b_alpha, float* g_b_th, float* g_b_omega,
                            float* scratch, float* g_vinit, float* g_winit, int64_t T, int64_t cols,
-                           int dtype, int ckpt_interval, int surrogate, float alpha, void* stream);
+                           int dtype, int ckpt_interval, int surrogate, float alpha,
+                           const float* alpha_dev, void* stream);
 
 /*
  * Adaptive surrogate slope without a host round trip. Replaces the

@@ -25,6 +25,9 @@ struct Tuning {
   int warps_per_cta = 0, stages = 0, lanes_per_thread = 0, force_direct = 0;
 };
 Tuning get_tuning();
+// Adaptive surrogate slope from (sum, sum of squares) partials (nsb_surrogate.cu).
+int launch_alpha_finalize(const double* partial, int nparts, long long n, int dtype, float alpha0, float sigma0,
+                          float* alpha_out, cudaStream_t st);
 
 // Device properties that the launch heuristics need (cached per device).
 struct DeviceInfo {

@@ -41,7 +41,11 @@ namespace nsb {
 // the 16 frames of a second input stream, re-encoded, and those frames are the output.
 // MODE_RF is the second-order resonate-and-fire scan: it streams beta, u, omega, v_th
 // (omega in the slot the gain*cur form uses for the gain) and carries two states, V and W.
-enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3, MODE_MOD = 4, MODE_RFMOD = 5, MODE_ROWRES = 6, MODE_LIN = 7 };
+enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3, MODE_MOD = 4, MODE_RFMOD = 5, MODE_ROWRES = 6, MODE_LIN = 7,
+       // forward-only variants of MODE_MOD / MODE_RFMOD that also accumulate the moments of u = alpha*I (for
+       // the adaptive surrogate slope). Separate kernels: compiled into the same kernel, as a run-time or a
+       // per-tile choice, the extra accumulators cost 25-85 registers and a third of the resident warps.
+       MODE_MODS = 8, MODE_RFMODS = 9 };
 
 struct FwdArgs {
   const void* beta = nullptr;   // streams ([T, cols], stream dtype)
@@ -52,6 +56,11 @@ struct FwdArgs {
   const float* bias[4] = {nullptr, nullptr, nullptr, nullptr};  // modulated modes: b_beta, b_alpha, b_th, b_omega ([channels])
   long long channels = 0;                                         // cols is a multiple of it
   float v_th_min = 0.0f;
+  // modulated modes, optional: adaptive surrogate slope from the moments of u = alpha*I, which the
+  // kernel accumulates while it streams (u_stats: 2 doubles per warp of the launch)
+  double* u_stats = nullptr;
+  float* alpha_out = nullptr;
+  float alpha0 = 4.0f, sigma0 = 0.4f;
   const float* beta_row = nullptr;  // MODE_ROW
   const float* vth_row = nullptr;
   const float* v_init = nullptr;
@@ -315,6 +324,7 @@ struct FwdParams {
   const float* bias[4];  // modulated modes: b_beta, b_alpha, b_th, b_omega
   long long channels;
   float v_th_min;
+  double* u_stats;  // modulated modes, optional: per-warp (sum, sum of squares) of u
   const float* beta_row;
   const float* vth_row;
   const float* v_init;
@@ -333,8 +343,10 @@ struct FwdParams {
   uint32_t* err;
 };
 
-template <int MODE>
+template <int MODE_>
 struct ModeTraits {
+  static constexpr bool kStats = MODE_ == MODE_MODS || MODE_ == MODE_RFMODS;
+  static constexpr int MODE = MODE_ == MODE_MODS ? MODE_MOD : (MODE_ == MODE_RFMODS ? MODE_RFMOD : MODE_);
   static constexpr bool kSecond = MODE == MODE_RF || MODE == MODE_RFMOD;  // carries the second state W
   static constexpr bool kMod = MODE == MODE_MOD || MODE == MODE_RFMOD;    // modulation fused into the loads
   static constexpr bool kRow = MODE == MODE_ROW || MODE == MODE_ROWRES;  // per-column beta / v_th
@@ -408,13 +420,13 @@ __device__ __forceinline__ void rf_step(float (&v)[V], float (&w)[V], const floa
   }
 }
 
+// The forward scan. A device function so that it can sit behind two kernel entry points: one
+// without a register limit (ptxas' own choice; giving it an explicit 255 made it spend 30-100 more
+// registers on every variant), one held to 160 registers.
 template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
-__global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tm0,
-                                const __grid_constant__ CUtensorMap tm1,
-                                const __grid_constant__ CUtensorMap tm2,
-                                const __grid_constant__ CUtensorMap tm3,
-                                const __grid_constant__ CUtensorMap tm4,
-                                const __grid_constant__ CUtensorMap tm_spike) {
+__device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensorMap& tm0, const CUtensorMap& tm1,
+                                              const CUtensorMap& tm2, const CUtensorMap& tm3,
+                                              const CUtensorMap& tm4, const CUtensorMap& tm_spike) {
   using MT = ModeTraits<MODE>;
   using E = Elem<ST>;
   using IO = VecIO<ST, V>;
@@ -528,12 +540,14 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
   // bit-packing kernel). When a call asks for none of them the step loop is compiled
   // without their address arithmetic and predicated stores (they were ~40 % of the
   // instructions of a step, which is what bounds a launch with one warp per SM).
+  double st_s = 0.0, st_q = 0.0;  // modulated modes: this thread's moments of u
   const bool any_direct = p.vpost != nullptr || (MT::kSecond && p.w_out != nullptr) ||
                           (!DENSE_TMA && p.spike != nullptr);
 
   auto tile = [&](auto full_tag, auto direct_tag, int nsteps) {
     constexpr bool FULL = decltype(full_tag)::value;
     constexpr bool DIRECT = decltype(direct_tag)::value;
+    constexpr bool STATS = MT::kStats;  // accumulate the moments of u
     // On the vector path dense spikes are written over the consumed drive tile in
     // shared memory and leave through one TMA store per tile (which also clips the
     // ragged edges), so the step loop carries no global address arithmetic for them.
@@ -591,7 +605,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
         fetch(MT::kGain, k, gn);
         vmul<V>(dr, gn, dr);
       }
-      if constexpr (MODE == MODE_RF || MODE == MODE_RFMOD) fetch(MT::kOmega, k, om);
+      if constexpr (MT::kSecond) fetch(MT::kOmega, k, om);
       if constexpr (MT::kMod) {
         // Modulated modes: the raw projections of CH steps are turned into beta, u, v_th, omega
         // together, ahead of the steps that use them. The modulation is long chains of dependent
@@ -599,6 +613,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
         // serial scan, a warp stalls on every link (measured: 1.6 wait + 1.1 scoreboard cycles
         // per instruction). CH steps at once give the scheduler CH*V independent chains.
         if (k % CH == 0) {
+          float cs = 0.0f, cq = 0.0f;
 #pragma unroll
           for (int kk = 0; kk < CH; ++kk) {
             if (k + kk < C && (FULL || k + kk < nsteps)) {
@@ -610,7 +625,21 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
               if constexpr (MT::kSecond) fetch(MT::kOmega, k + kk, mom[kk]);
               mod::forward_lanes<MT::kSecond, V>(mb[kk], ra, mth[kk], mom[kk], mu[kk], bias, p.v_th_min, q0, q1,
                                                  q2, q3, q4);
+              // moments of u (for the adaptive surrogate slope): fp32 within the chunk, double across
+              // chunks (only in the kernels built for it).
+              if constexpr (STATS) {
+#pragma unroll
+                for (int j = 0; j < V; ++j) {
+                  const float uj = valid[j] ? mu[kk][j] : 0.0f;
+                  cs += uj;
+                  cq = fmaf(uj, uj, cq);
+                }
+              }
             }
+          }
+          if constexpr (STATS) {
+            st_s += (double)cs;
+            st_q += (double)cq;
           }
         }
 #pragma unroll
@@ -801,6 +830,44 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
       p.vlast[colj[j]] = v[j];
       if (MT::kSecond) p.wlast[colj[j]] = w[j];
     }
+  if constexpr (MT::kStats) {
+    if (p.u_stats) {  // one (sum, sum of squares) pair per warp, lanes added in a fixed order
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        st_s += __shfl_down_sync(0xffffffffu, st_s, o);
+        st_q += __shfl_down_sync(0xffffffffu, st_q, o);
+      }
+      if (lane == 0) {
+        const long long gw = (long long)blockIdx.x * wpc + warp;
+        p.u_stats[2 * gw] = st_s;
+        p.u_stats[2 * gw + 1] = st_q;
+      }
+    }
+  }
+}
+
+template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
+__global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tm0,
+                                const __grid_constant__ CUtensorMap tm1,
+                                const __grid_constant__ CUtensorMap tm2,
+                                const __grid_constant__ CUtensorMap tm3,
+                                const __grid_constant__ CUtensorMap tm4,
+                                const __grid_constant__ CUtensorMap tm_spike) {
+  plif_fwd_body<ST, MODE, PACKED, V, C, TMA>(p, tm0, tm1, tm2, tm3, tm4, tm_spike);
+}
+
+// Same, held to 160 registers: for the 4-lane resonate-and-fire kernel with the modulation fused in
+// that also accumulates the moments of u, so that 3 warps fit each SM sub-partition (12 per SM; at its
+// natural 180 it is 8, and that kernel lives on resident warps: measured 4.8 ms at 11 warps per SM,
+// 6.7-7.9 ms at 6).
+template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
+__global__ void __maxnreg__(160) plif_fwd_kernel_r160(const FwdParams p, const __grid_constant__ CUtensorMap tm0,
+                                                      const __grid_constant__ CUtensorMap tm1,
+                                                      const __grid_constant__ CUtensorMap tm2,
+                                                      const __grid_constant__ CUtensorMap tm3,
+                                                      const __grid_constant__ CUtensorMap tm4,
+                                                      const __grid_constant__ CUtensorMap tm_spike) {
+  plif_fwd_body<ST, MODE, PACKED, V, C, TMA>(p, tm0, tm1, tm2, tm3, tm4, tm_spike);
 }
 
 // ------------------------------------------------------------------ backward
@@ -1421,7 +1488,14 @@ template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
 int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, const Plan& planned) {
   using MT = ModeTraits<MODE>;
   constexpr int NS = MT::kFwdStreams;
-  auto kern = plif_fwd_kernel<ST, MODE, PACKED, V, C, TMA>;
+  // only the moment-accumulating 4-lane resonate-and-fire kernel needs the limit (natural count 180)
+  constexpr bool kCap160 = MODE == MODE_RFMODS && V == 4 && TMA;
+  auto kern = [] {
+    if constexpr (kCap160)
+      return plif_fwd_kernel_r160<ST, MODE, PACKED, V, C, TMA>;
+    else
+      return plif_fwd_kernel<ST, MODE, PACKED, V, C, TMA>;
+  }();
   FwdParams p = {};
   const void* streams[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
   if (MT::kRow) {
@@ -1434,6 +1508,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   for (int i = 0; i < 5; ++i) p.s[i] = streams[i];
   for (int i = 0; i < 4; ++i) p.bias[i] = a.bias[i];
   p.channels = a.channels > 0 ? a.channels : 1; p.v_th_min = a.v_th_min;
+  p.u_stats = MT::kStats ? a.u_stats : nullptr;
   p.beta_row = a.beta_row; p.vth_row = a.vth_row; p.v_init = a.v_init; p.w_init = a.w_init;
   p.spike = a.spike; p.packed = a.packed; p.vpost = a.vpost; p.w_out = a.w_out; p.ckpt = a.ckpt;
   p.ckpt_w = a.ckpt_w; p.vlast = a.vlast; p.wlast = a.wlast;
@@ -1471,6 +1546,12 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   p.defer = defer_refill(tune, plan, dev);
   kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
   NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_kernel");
+  if (MT::kStats && a.u_stats && a.alpha_out) {
+    // u is never stored, so its standard deviation is taken at fp32 (no rounding to a storage dtype)
+    int r = launch_alpha_finalize(a.u_stats, (int)nwarps, a.T * a.cols, NSB_F32, a.alpha0, a.sigma0, a.alpha_out,
+                                  a.stream);
+    if (r != NSB_OK) return r;
+  }
   li.used_tma = TMA; li.warps_per_cta = plan.wpc; li.stages = plan.stages; li.lanes_per_thread = V;
   li.grid = plan.grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = 1;
   return NSB_OK;
@@ -1702,6 +1783,19 @@ int scan_mod_fwd_dispatch(const FwdArgs& a) {
 #define NSB_MFWD_CASES(MODE_, PACKED_)                                                 \
   NSB_MFWD_CASE(MODE_, PACKED_, 1, 8) NSB_MFWD_CASE(MODE_, PACKED_, 2, 8)              \
   NSB_MFWD_CASE(MODE_, PACKED_, 4, 8) NSB_MFWD_CASE(MODE_, PACKED_, 1, 32)
+#define NSB_MFWD_STATS(MODE_, SMODE_, V_, C_)                                          \
+  if (a.mode == MODE_ && V == V_ && C == C_)                                           \
+    return launch_fwd_one<ST, SMODE_, false, V_, C_, true>(a, dev, tune, plan);
+#define NSB_MFWD_STATS_V(MODE_, SMODE_)                                                \
+  NSB_MFWD_STATS(MODE_, SMODE_, 1, 8) NSB_MFWD_STATS(MODE_, SMODE_, 2, 8)              \
+  NSB_MFWD_STATS(MODE_, SMODE_, 4, 8) NSB_MFWD_STATS(MODE_, SMODE_, 1, 32)
+  if (tma && a.u_stats) {  // also accumulate the moments of u (dense spikes only)
+    if (packed) return NSB_ERR_INVALID_ARG;
+    NSB_MFWD_STATS_V(MODE_MOD, MODE_MODS) NSB_MFWD_STATS_V(MODE_RFMOD, MODE_RFMODS)
+    return NSB_ERR_INVALID_ARG;
+  }
+#undef NSB_MFWD_STATS_V
+#undef NSB_MFWD_STATS
   if (tma) {
     NSB_MFWD_CASES(MODE_MOD, false) NSB_MFWD_CASES(MODE_MOD, true)
     NSB_MFWD_CASES(MODE_RFMOD, false) NSB_MFWD_CASES(MODE_RFMOD, true)
@@ -1713,6 +1807,14 @@ int scan_mod_fwd_dispatch(const FwdArgs& a) {
   if (a.mode == MODE_ && C == C_)                                                      \
     return packed ? launch_fwd_one<ST, MODE_, true, 1, C_, false>(a, dev, tune, plan)  \
                   : launch_fwd_one<ST, MODE_, false, 1, C_, false>(a, dev, tune, plan);
+  if (a.u_stats) {
+    if (packed) return NSB_ERR_INVALID_ARG;
+    if (a.mode == MODE_MOD && C == 8) return launch_fwd_one<ST, MODE_MODS, false, 1, 8, false>(a, dev, tune, plan);
+    if (a.mode == MODE_MOD && C == 32) return launch_fwd_one<ST, MODE_MODS, false, 1, 32, false>(a, dev, tune, plan);
+    if (a.mode == MODE_RFMOD && C == 8) return launch_fwd_one<ST, MODE_RFMODS, false, 1, 8, false>(a, dev, tune, plan);
+    if (a.mode == MODE_RFMOD && C == 32) return launch_fwd_one<ST, MODE_RFMODS, false, 1, 32, false>(a, dev, tune, plan);
+    return NSB_ERR_INVALID_ARG;
+  }
   NSB_MFWD_DIRECT(MODE_MOD, 8) NSB_MFWD_DIRECT(MODE_MOD, 32)
   NSB_MFWD_DIRECT(MODE_RFMOD, 8) NSB_MFWD_DIRECT(MODE_RFMOD, 32)
 #undef NSB_MFWD_DIRECT

@@ -298,8 +298,8 @@ int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const vo
                            const float* b_alpha, const float* b_th, const float* b_omega, float v_th_min,
                            int64_t channels, const float* v_init, const float* w_init, void* spike_dense,
                            uint32_t* spike_packed, float* v_ckpt, float* w_ckpt, float* v_last,
-                           float* w_last, int64_t T, int64_t cols, int dtype, int ckpt_interval,
-                           void* stream) {
+                           float* w_last, float alpha0, float sigma0, double* u_stats, float* alpha_out,
+                           int64_t T, int64_t cols, int dtype, int ckpt_interval, void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || (ckpt_interval != 8 && ckpt_interval != 32))
     return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
@@ -308,15 +308,19 @@ int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const vo
   if (!v_init || !v_last || !b_beta || !b_alpha || !b_th) return NSB_ERR_INVALID_ARG;
   if (rf && (!b_omega || !w_init || !w_last)) return NSB_ERR_INVALID_ARG;
   if (rf && (v_ckpt == nullptr) != (w_ckpt == nullptr)) return NSB_ERR_INVALID_ARG;
-  const void* fp[] = {v_init, w_init, v_last, w_last, v_ckpt, w_ckpt, spike_packed, b_beta, b_alpha, b_th, b_omega};
+  const void* fp[] = {v_init, w_init, v_last, w_last, v_ckpt, w_ckpt, spike_packed, b_beta, b_alpha, b_th, b_omega,
+                      alpha_out};
   for (const void* p : fp)
     if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
+  if ((u_stats == nullptr) != (alpha_out == nullptr) || (reinterpret_cast<uintptr_t>(u_stats) & 7u))
+    return NSB_ERR_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (T == 0) {
     NSB_CUDA_TRY(cudaMemcpyAsync(v_last, v_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice, st), "copy v_init");
     if (rf)
       NSB_CUDA_TRY(cudaMemcpyAsync(w_last, w_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice, st),
                    "copy w_init");
+    if (alpha_out) return nsb::launch_alpha_finalize(u_stats, 0, 0, NSB_F32, alpha0, sigma0, alpha_out, st);
     return NSB_OK;
   }
   if (!raw_beta || !raw_alpha || !raw_th || !cur || (rf && !raw_omega)) return NSB_ERR_INVALID_ARG;
@@ -329,12 +333,14 @@ int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const vo
   a.channels = channels; a.v_th_min = v_th_min;
   a.v_init = v_init; a.w_init = w_init; a.spike = spike_dense; a.packed = spike_packed;
   a.ckpt = v_ckpt; a.ckpt_w = w_ckpt; a.vlast = v_last; a.wlast = w_last;
+  a.u_stats = u_stats; a.alpha_out = alpha_out; a.alpha0 = alpha0; a.sigma0 = sigma0;
   a.T = T; a.cols = cols; a.mode = rf ? nsb::MODE_RFMOD : nsb::MODE_MOD; a.tile = ckpt_interval;
   a.stream = st;
   return run_mod_fwd(a, dtype);
 }
 
 int64_t nsb_plif_modulated_bwd_scratch_floats(int64_t cols) { return cols > 0 ? 4 * cols : 0; }
+int64_t nsb_plif_modulated_fwd_stats_doubles(int64_t cols) { return cols > 0 ? 2 * ((cols + 31) / 32) : 0; }
 
 int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
                            const void* raw_omega, const void* cur, const float* b_beta,
@@ -343,7 +349,8 @@ int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const vo
                            void* g_raw_beta, void* g_raw_alpha, void* g_raw_th, void* g_raw_omega,
                            void* g_cur, float* g_b_beta, float* g_b_alpha, float* g_b_th, float* g_b_omega,
                            float* scratch, float* g_vinit, float* g_winit, int64_t T, int64_t cols,
-                           int dtype, int ckpt_interval, int surrogate, float alpha, void* stream) {
+                           int dtype, int ckpt_interval, int surrogate, float alpha, const float* alpha_dev,
+                           void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || (ckpt_interval != 8 && ckpt_interval != 32))
     return NSB_ERR_INVALID_ARG;
   if (surrogate != NSB_SURR_SIGMOID && surrogate != NSB_SURR_ATAN) return NSB_ERR_INVALID_ARG;
@@ -384,7 +391,8 @@ int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const vo
     for (int i = 0; i < nb; ++i) a.g_bias[i] = scratch + (long long)i * cols;
   a.g_vinit = g_vinit; a.g_winit = g_winit;
   a.T = T; a.cols = cols; a.mode = rf ? nsb::MODE_RFMOD : nsb::MODE_MOD; a.tile = ckpt_interval;
-  a.surrogate = surrogate; a.alpha = alpha; a.stream = st;
+  a.surrogate = surrogate; a.alpha = alpha; a.alpha_dev = alpha_dev; a.stream = st;
+  if (!f32_aligned(alpha_dev)) return NSB_ERR_INVALID_ARG;
   int r = run_mod_bwd(a, dtype);
   if (r != NSB_OK || !want_bias) return r;
   const long long items = (long long)nb * channels;

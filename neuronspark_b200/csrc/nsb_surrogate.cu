@@ -88,11 +88,11 @@ __device__ __forceinline__ double round_like(double x, int dtype) {
   return (double)(float)x;
 }
 
-__global__ void alpha_finalize_kernel(const double* __restrict__ partial, long long n, int dtype, float alpha0,
-                                      float sigma0, float* __restrict__ alpha_out) {
+__global__ void alpha_finalize_kernel(const double* __restrict__ partial, int nparts, long long n, int dtype,
+                                      float alpha0, float sigma0, float* __restrict__ alpha_out) {
   const int lane = threadIdx.x;
   double s = 0.0, q = 0.0;
-  for (int b = lane; b < kBlocks; b += 32) {
+  for (int b = lane; b < nparts; b += 32) {
     s += partial[2 * b];
     q += partial[2 * b + 1];
   }
@@ -117,6 +117,16 @@ __global__ void alpha_finalize_kernel(const double* __restrict__ partial, long l
 }
 
 }  // namespace
+
+// Slope from `nparts` (sum, sum of squares) pairs over n values; used by nsb_surrogate_alpha and by
+// the modulated forward scan, which accumulates the moments of u = alpha*I while it streams.
+int launch_alpha_finalize(const double* partial, int nparts, long long n, int dtype, float alpha0, float sigma0,
+                          float* alpha_out, cudaStream_t st) {
+  alpha_finalize_kernel<<<1, 32, 0, st>>>(partial, nparts, n, dtype, alpha0, sigma0, alpha_out);
+  NSB_CUDA_TRY(cudaGetLastError(), "launch alpha_finalize_kernel");
+  return NSB_OK;
+}
+
 }  // namespace nsb
 
 using namespace nsb;
@@ -140,7 +150,5 @@ extern "C" int nsb_surrogate_alpha(const void* u, int64_t n, int dtype, float al
     default: moments_kernel<__half><<<kBlocks, kThreads, 0, st>>>(static_cast<const __half*>(u), n, scratch); break;
   }
   NSB_CUDA_TRY(cudaGetLastError(), "launch moments_kernel");
-  alpha_finalize_kernel<<<1, 32, 0, st>>>(scratch, n, dtype, alpha0, sigma0, alpha_out);
-  NSB_CUDA_TRY(cudaGetLastError(), "launch alpha_finalize_kernel");
-  return NSB_OK;
+  return launch_alpha_finalize(scratch, kBlocks, n, dtype, alpha0, sigma0, alpha_out, st);
 }

@@ -87,7 +87,7 @@ class ModulatedPLIFScan(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, raw_beta, raw_alpha, raw_th, I_all, raw_omega, b_beta, b_alpha, b_th, b_omega,
-                v_init, w_init, v_th_min, alpha, surrogate):
+                v_init, w_init, v_th_min, alpha, surrogate, sigma0=None):
         rf = raw_omega is not None
         streams = [raw_beta, raw_alpha, raw_th, I_all] + ([raw_omega] if rf else [])
         dt = ps._common_stream_dtype(*streams)
@@ -109,13 +109,22 @@ class ModulatedPLIFScan(torch.autograd.Function):
             ckw = torch.empty_like(ckv) if rf else None
         v_last = torch.empty(shape, dtype=torch.float32, device=dev)
         w_last = torch.empty_like(v_last) if rf else None
+        # adaptive slope: `alpha` is alpha_0; the kernel accumulates the moments of u and the slope
+        # lands in a device float that the backward reads (no host round trip)
+        stats = alpha_t = None
+        if sigma0 is not None and needs_grad:
+            stats = torch.empty(int(_lib.lib().nsb_plif_modulated_fwd_stats_doubles(cols)), dtype=torch.float64,
+                                device=dev)
+            alpha_t = torch.empty((), dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().nsb_plif_modulated_fwd(
                 _lib.ptr(rb), _lib.ptr(ra), _lib.ptr(rt), _lib.ptr(ro), _lib.ptr(ci), _lib.ptr(biases[0]),
                 _lib.ptr(biases[1]), _lib.ptr(biases[2]), _lib.ptr(biases[3]), float(v_th_min), ch,
                 _lib.ptr(v0), _lib.ptr(w0), _lib.ptr(spike), None, _lib.ptr(ckv), _lib.ptr(ckw),
-                _lib.ptr(v_last), _lib.ptr(w_last), T, cols, _lib.dtype_code(dt), C,
-                _lib.stream_ptr(dev)), "nsb_plif_modulated_fwd")
+                _lib.ptr(v_last), _lib.ptr(w_last), float(alpha), float(sigma0 or 0.0), _lib.ptr(stats),
+                _lib.ptr(alpha_t), T, cols, _lib.dtype_code(dt), C, _lib.stream_ptr(dev)),
+                "nsb_plif_modulated_fwd")
+        ctx.alpha_t = alpha_t
         if needs_grad:
             ctx.save_for_backward(rb, ra, rt, ci, ro, *biases[:3], biases[3], ckv, ckw)
         ctx.rf = rf
@@ -162,7 +171,7 @@ class ModulatedPLIFScan(torch.autograd.Function):
                 _lib.ptr(gs), _lib.ptr(g_rb), _lib.ptr(g_ra), _lib.ptr(g_rt), _lib.ptr(g_ro), _lib.ptr(g_ci),
                 _lib.ptr(g_bias[0]), _lib.ptr(g_bias[1]), _lib.ptr(g_bias[2]),
                 _lib.ptr(g_bias[3] if rf else None), _lib.ptr(scratch), _lib.ptr(g_v0), _lib.ptr(g_w0),
-                T, cols, _lib.dtype_code(dt), ctx.interval, ctx.surrogate, ctx.alpha,
+                T, cols, _lib.dtype_code(dt), ctx.interval, ctx.surrogate, ctx.alpha, _lib.ptr(ctx.alpha_t),
                 _lib.stream_ptr(dev)), "nsb_plif_modulated_bwd")
         d = ctx.in_dtypes
         sh = ctx.bias_shapes
@@ -173,35 +182,42 @@ class ModulatedPLIFScan(torch.autograd.Function):
         return (g_rb.to(d[0]), g_ra.to(d[1]), g_rt.to(d[2]), g_ci.to(d[3]),
                 g_ro.to(d[4]) if rf else None, bias_out(0), bias_out(1), bias_out(2),
                 bias_out(3) if rf else None, g_v0.to(d[9]).reshape(ctx.state_shapes[0]),
-                g_w0.to(d[10]).reshape(ctx.state_shapes[1]) if rf else None, None, None, None)
+                g_w0.to(d[10]).reshape(ctx.state_shapes[1]) if rf else None, None, None, None, None)
 
 
 def _apply(raw_beta, raw_alpha, raw_th, I_all, raw_omega, b_beta, b_alpha, b_th, b_omega, v_init, w_init,
-           v_th_min, surrogate_function):
+           v_th_min, surrogate_function, adaptive_sigma0=None):
     if surrogate_function is None:
         with torch.no_grad():
             return ModulatedPLIFScan.apply(raw_beta, raw_alpha, raw_th, I_all, raw_omega, b_beta, b_alpha,
                                            b_th, b_omega, v_init, w_init, v_th_min, 0.0, "sigmoid")
     alpha, kind = ps._alpha_and_kind(surrogate_function)
     return ModulatedPLIFScan.apply(raw_beta, raw_alpha, raw_th, I_all, raw_omega, b_beta, b_alpha, b_th,
-                                   b_omega, v_init, w_init, v_th_min, alpha, kind)
+                                   b_omega, v_init, w_init, v_th_min, float(alpha), kind, adaptive_sigma0)
 
 
 def modulated_plif_forward(raw_beta, b_beta, raw_alpha, b_alpha, raw_th, b_th, v_th_min, I_all, v_init,
-                           surrogate_function=None):
+                           surrogate_function=None, adaptive_sigma0=None):
     """First-order modulation + selective scan: ``_fused_modulation(...)`` followed by
     ``plif_parallel_forward(beta, u, v_th, v_init, surrogate_function=...)``
     (archive/atomic_ops_v75_pre/snn_block.py:186-199). Argument order of the modulation
-    function, then the scan's state. Returns ``(spike, V_last)``."""
+    function, then the scan's state. Returns ``(spike, V_last)``. ``adaptive_sigma0``: see
+    ``modulated_rf_plif_forward``."""
     s, v_last, _ = _apply(raw_beta, raw_alpha, raw_th, I_all, None, b_beta, b_alpha, b_th, None, v_init, None,
-                          v_th_min, surrogate_function)
+                          v_th_min, surrogate_function, adaptive_sigma0)
     return s, v_last
 
 
 def modulated_rf_plif_forward(raw_beta, b_beta, raw_alpha, b_alpha, raw_th, b_th, v_th_min, I_all, raw_omega,
-                              b_omega, v_init, w_init, surrogate_function=None):
+                              b_omega, v_init, w_init, surrogate_function=None, adaptive_sigma0=None):
     """Second-order modulation + resonate-and-fire scan: ``_fused_modulation_rf(...)`` followed by
     ``rf_plif_parallel_forward_recompute(...)`` (atomic_ops/snn_block.py:237-256). Returns
-    ``(spike, V_last, W_last)``."""
+    ``(spike, V_last, W_last)``.
+
+    ``adaptive_sigma0``: the reference adapts the surrogate slope to ``u_hidden.std()``
+    (``hidden_neuron.get_surrogate(u_hidden)``, atomic_ops/plif_node.py:78-101), a tensor the fused
+    kernel never writes. Pass the neuron's FIXED surrogate (slope alpha_0) as ``surrogate_function`` and
+    its ``sigma_0`` here: the kernel accumulates the moments of u while it streams, and the backward
+    uses ``clamp(alpha_0 * sigma_0 / max(std(u), 1e-6), 1, 20)`` read from device memory."""
     return _apply(raw_beta, raw_alpha, raw_th, I_all, raw_omega, b_beta, b_alpha, b_th, b_omega, v_init,
-                  w_init, v_th_min, surrogate_function)
+                  w_init, v_th_min, surrogate_function, adaptive_sigma0)

@@ -332,3 +332,37 @@ def test_fused_edge_cases(rf):
         bad = dict(b)
         bad["b_beta"] = b["b_beta"][:-1]
         run_fused(d, bad, v0, w0, rf)
+
+
+@pytest.mark.parametrize("rf", [False, True])
+def test_adaptive_slope_from_the_kernel(rf):
+    """With adaptive_sigma0 the forward accumulates the moments of u = alpha*I and the backward uses
+    clamp(alpha_0*sigma_0/std(u), 1, 20): same gradients as passing that slope by hand."""
+    T, B, D = 96, 2, 264
+    d, b, v0, w0 = mod_inputs(T, B, D, torch.bfloat16, 61, rf)
+    gS = (torch.randn(T, B, D, device=DEV) * 0.1).bfloat16()
+    u = run_modulation(d, b, rf)[1]                 # fp32 u as the kernel forms it
+    want_alpha = orc.surrogate_alpha(f32(u), 4.0, 0.4, "f32")
+    assert 1.0 < want_alpha < 20.0
+
+    def grads(surrogate, sigma0):
+        leaves = {k: v.clone().requires_grad_() for k, v in {**d, **b}.items()}
+        args = ([leaves[k] for k in ("raw_beta",)] + [leaves["b_beta"], leaves["raw_alpha"], leaves["b_alpha"],
+                                                       leaves["raw_th"], leaves["b_th"], V_TH_MIN, leaves["cur"]])
+        if rf:
+            s, _, _ = sb.modulated_rf_plif_forward(*args, leaves["raw_omega"], leaves["b_omega"], v0, w0,
+                                                   surrogate, adaptive_sigma0=sigma0)
+        else:
+            s, _ = sb.modulated_plif_forward(*args, v0, surrogate, adaptive_sigma0=sigma0)
+        s.backward(gS)
+        return {k: leaves[k].grad for k in leaves}
+
+    mine = grads(_Sigmoid(4.0), 0.4)
+    ref = grads(_Sigmoid(want_alpha), None)
+    for k in ref:
+        a, w = f32(mine[k]).reshape(-1), f32(ref[k]).astype(np.float64).reshape(-1)
+        # both sides are bf16-rounded: they may sit one unit in the last place apart (2^-7 relative)
+        bound = (2.0 ** -7 * np.abs(w) if mine[k].dtype == torch.bfloat16 else 0.0) + 1e-5 * np.abs(w).max()
+        assert (np.abs(a - w) <= bound).all(), k
+    fixed = grads(_Sigmoid(4.0), None)   # and it is not the fixed slope
+    assert not torch.equal(fixed["cur"], mine["cur"])
