@@ -1,9 +1,9 @@
 """Generate the golden vectors under tests/golden/ from the reference's own code.
 
-Run once, in a container that has the reference checkout (path given by
-NEURONSPARK_REF, default /root/reference) and PyTorch on CPU:
+Run once, where the reference checkout and PyTorch (CPU) are available; the
+checkout's path comes from the first argument or from NEURONSPARK_REF:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <path to the NeuronSpark checkout>
 
 The reference's ``atomic_ops`` package cannot be imported as a package here
 (it depends on SpikingJelly, which is not installed), so the two files that
@@ -48,7 +48,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(os.environ.get("NEURONSPARK_REF", "/root/reference"))
+if len(sys.argv) < 2 and "NEURONSPARK_REF" not in os.environ:
+    raise SystemExit("usage: make_golden.py <path to the NeuronSpark checkout>  (or set NEURONSPARK_REF)")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["NEURONSPARK_REF"])
 OUT = Path(__file__).resolve().parent
 
 
