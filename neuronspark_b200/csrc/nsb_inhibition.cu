@@ -127,15 +127,25 @@ __global__ void li_fwd_cached_kernel(const T* __restrict__ x, const TG* __restri
   const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
   const float inv_d = 1.0f / (float)D;
-  for (long long r = warp; r < rows; r += nwarps) {
+  // The next row of this warp is requested before the current one is reduced and written, so
+  // that a warp always has loads in flight (a row is only 1.5 KB at D = 768).
+  Vec<T, VE> xv[NV], xn[NV];
+  auto load_row = [&](long long r, Vec<T, VE> (&dst)[NV]) {
     const T* xr = x + r * D;
-    Vec<T, VE> xv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = (lane + 32 * i) * VE;
+      if (d < D) dst[i] = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+    }
+  };
+  if (warp < rows) load_row(warp, xv);
+  for (long long r = warp; r < rows; r += nwarps) {
+    if (r + nwarps < rows) load_row(r + nwarps, xn);
     float ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int d = (lane + 32 * i) * VE;
       if (d < D) {
-        xv[i] = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
           const float f = Elem<T>::to_f32(xv[i].v[j]);
@@ -158,6 +168,8 @@ __global__ void li_fwd_cached_kernel(const T* __restrict__ x, const TG* __restri
         *reinterpret_cast<Vec<T, VE>*>(orow + d) = o;
       }
     }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) xv[i] = xn[i];
   }
 }
 
@@ -177,17 +189,28 @@ __global__ void li_bwd_cached_kernel(const T* __restrict__ g_out, const T* __res
   for (int i = 0; i < NV; ++i)
 #pragma unroll
     for (int j = 0; j < VE; ++j) acc[i][j] = 0.0f;
-  for (long long r = warp; r < rows; r += nwarps) {
+  // next row requested before the current one is reduced (see the forward kernel)
+  Vec<T, VE> xv[NV], gv[NV], xn[NV], gn[NV];
+  auto load_row = [&](long long r, Vec<T, VE> (&dx)[NV], Vec<T, VE> (&dg)[NV]) {
     const T* xr = x + r * D;
     const T* gr = g_out + r * D;
-    Vec<T, VE> xv[NV], gv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = (lane + 32 * i) * VE;
+      if (d < D) {
+        dx[i] = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+        dg[i] = *reinterpret_cast<const Vec<T, VE>*>(gr + d);
+      }
+    }
+  };
+  if (warp < rows) load_row(warp, xv, gv);
+  for (long long r = warp; r < rows; r += nwarps) {
+    if (r + nwarps < rows) load_row(r + nwarps, xn, gn);
     float ss = 0.0f, dot = 0.0f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int d = (lane + 32 * i) * VE;
       if (d < D) {
-        xv[i] = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
-        gv[i] = *reinterpret_cast<const Vec<T, VE>*>(gr + d);
         const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);  // stays in L1
 #pragma unroll
         for (int j = 0; j < VE; ++j) {
@@ -217,6 +240,11 @@ __global__ void li_bwd_cached_kernel(const T* __restrict__ g_out, const T* __res
         }
         *reinterpret_cast<Vec<T, VE>*>(dxr + d) = o;
       }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      xv[i] = xn[i];
+      gv[i] = gn[i];
     }
   }
   float* mine = acc_smem + (size_t)wib * D;
