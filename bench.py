@@ -501,7 +501,11 @@ def run_modulated(args):
                        "l2": "inputs are far larger than L2" if T * cols * 2 > (512 << 20) else "L2 not flushed",
                        "ckpt_interval": C, "launch_fwd": info.get("fwd"), "launch_bwd": info.get("bwd")},
             "roofline": {"bound": "hbm", "kernel": "plif_bwd_kernel (modulated)", "achieved": ach(bytes_bwd, bwd_ms),
-                         "peak": peak, "unit": "GB/s", "frac": ach(bytes_bwd, bwd_ms) / peak, "traffic": None,
+                         "peak": peak, "unit": "GB/s", "frac": ach(bytes_bwd, bwd_ms) / peak,
+                         # DRAM bytes per neuron-step of the backward from the ncu capture of the T=512 case
+                         # (profiles/plif_modulated_ncu.md), times the neuron-steps of this launch
+                         "traffic": (22.66 if rf else 18.15) * ns,
+                         "traffic_source": "ncu capture of the T=512 case scaled by T (bytes per launch)",
                          "peak_source": peak_src, "algorithmic_bytes_per_neuron_step": bytes_bwd,
                          "avg_launch_ms": bwd_ms,
                          "forward": {"kernel": "plif_fwd_kernel (modulated)", "achieved": ach(bytes_fwd, fwd_ms),
