@@ -292,7 +292,8 @@ int nsb_lateral_inhibition_bwd_static(const void* g_out, const void* x, const vo
  * [cols] fp32. Outputs as nsb_plif_rf_fwd, without v_post / w_out.
  * ckpt_interval is 8 or 32.
  * Numerics: all arithmetic in fp32; sigmoid, softplus and rsqrt use the
- * hardware approximations, relative error < 1e-6 against correct rounding;
+ * hardware approximations: beta within 1e-6 relative of correct rounding,
+ * alpha and omega within 1e-6 relative or 2.5e-7 absolute, v_th exact;
  * the modulated values are not rounded to `dtype` (the reference rounds them
  * when its parameters are bf16).
  * Adaptive surrogate slope (optional; both pointers or neither): the reference

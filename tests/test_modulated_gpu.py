@@ -2,8 +2,8 @@
 
 Three links:
  1. the stand-alone modulation kernel against the CPU oracle (which is pinned to the
-    reference's functions by golden vectors): relative error <= 1e-6 on beta / u / omega
-    (hardware exp / reciprocal / rsqrt), v_th exact;
+    reference's functions by golden vectors): beta within 1e-6 relative, alpha*I and omega within
+    1e-6 relative or 3e-7 absolute (hardware exp / log / reciprocal / rsqrt), v_th exact;
  2. the fused scan against [stand-alone modulation (fp32 outputs) -> plain scan on those
     fp32 tensors]: BIT-EXACT, at every size, because both evaluate the same device
     functions and the same scan arithmetic;
@@ -135,8 +135,10 @@ def test_modulation_golden(golden, name):
         if ref == "vth":
             assert np.array_equal(mine, want)
             continue
-        # 2e-6 relative, or 1e-37 absolute where the reference's value is a subnormal / zero
-        bad = (rel(mine, want) > 2e-6) & (np.abs(mine.astype(np.float64) - want) > 1e-37)
+        # 2e-6 relative; the softplus outputs (alpha inside u, omega) also 3e-7 absolute (times |I| for
+        # u); beta 1e-37 absolute where the reference's value is a subnormal / zero
+        floor = {"beta": 1e-37, "omega": 3e-7}.get(ref, 3e-7 * np.abs(g["cur"]).astype(np.float64))
+        bad = (rel(mine, want) > 2e-6) & (np.abs(mine.astype(np.float64) - want) > floor)
         assert not bad.any(), (ref, rel(mine, want).max())
 
 
@@ -150,7 +152,9 @@ def test_modulation_vs_oracle(rf, dtype):
         if i == 2:
             assert np.array_equal(f32(mine), ref)
         else:
-            assert rel(f32(mine), ref).max() <= 1e-6, (i, rel(f32(mine), ref).max())
+            floor = 0.0 if i == 0 else (3e-7 * np.abs(f32(d["cur"])) if i == 1 else 3e-7)
+            err = np.abs(f32(mine).astype(np.float64) - ref)
+            assert (err <= 1e-6 * np.abs(ref) + floor).all(), (i, rel(f32(mine), ref).max())
     if dtype != torch.float32:  # low-precision outputs are the fp32 values rounded once
         low = run_modulation(d, b, rf, out_dtype=dtype)
         for a, c in zip(out, low):
