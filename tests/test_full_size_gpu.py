@@ -124,3 +124,61 @@ def test_decode_variant_carries_state():
     rs, _, rl = orc.plif_selective_ai_fwd(*ins, np.zeros(4096, np.float32), want_vpost=False)
     dense = ps.unpack_spikes(whole, (B, D)).reshape(T, cols)[:, sl]
     assert np.array_equal(f32(dense), rs) and np.array_equal(f32(v_end.reshape(cols)[sl]), rl)
+
+
+def test_more_than_2_31_elements():
+    """Tensors of more than 2^31 elements (B=44, T=8192, D=6144: 2.21 G per stream): element offsets
+    no longer fit 32 bits. The last column block - whose offsets are the largest - is checked
+    against the oracle, forward and backward, and the kernel that addresses global memory itself
+    (no tensor maps) must give the same bits as the tiled one over the whole output."""
+    B, T, D = 44, 8192, 6144
+    cols = B * D
+    assert T * cols > 2 ** 31
+    inp = bench.make_inputs(B, T, D, DEV, 4321)
+    names = ("beta", "cur", "gain", "vth")
+    leaves = [inp[k].requires_grad_() for k in names] + [inp["v0"].requires_grad_()]
+    spike, v_last = ps.plif_selective_scan_ai(*leaves, alpha=2.0, surrogate="atan")
+    assert nsb.last_launch_info()["used_tma"] == 1
+    spike.backward(inp["g_spike"])
+    flat = lambda t: t.detach().reshape(T, cols)
+    sl = slice(cols - 64, cols)
+    ins = [f32(flat(inp[k])[:, sl]) for k in names]
+    v0b = f32(inp["v0"].detach().reshape(cols)[sl])
+    rs, _, rl = orc.plif_selective_ai_fwd(*ins, v0b, want_vpost=False)
+    assert np.array_equal(f32(flat(spike)[:, sl]), rs)
+    assert np.array_equal(f32(v_last.detach().reshape(cols)[sl]), rl)
+    ref = orc.plif_selective_ai_bwd(*ins, v0b, f32(flat(inp["g_spike"])[:, sl]), None, 2.0, orc.SURR_ATAN)
+    for t, e, n in zip(leaves[:4], ref[:4], names):
+        assert_close_lowp(f32(flat(t.grad)[:, sl]), e, torch.bfloat16, f"grad {n}")
+    assert_close(f32(leaves[4].grad.reshape(cols)[sl]), ref[4], what="grad v_init")
+    g_tma = [t.grad for t in leaves]
+    for t in leaves:
+        t.grad = None
+
+    nsb.set_tuning(force_direct=1)
+    spike_d, v_last_d = ps.plif_selective_scan_ai(*leaves, alpha=2.0, surrogate="atan")
+    assert nsb.last_launch_info()["used_tma"] == 0
+    assert torch.equal(spike_d, spike) and torch.equal(v_last_d, v_last)
+    spike_d.backward(inp["g_spike"])
+    for a, t in zip(g_tma, leaves):
+        assert torch.equal(a, t.grad)
+
+
+def test_codec_more_than_2_31_frames():
+    """fp16_encode of 140 M values writes 2.24 G frames; decoding them returns every value rounded
+    to half, and the binary residual with an all-zero second stream is the identity."""
+    from neuronspark_b200 import fp16_codec as codec
+    Bv, S, Dv = 38, 600, 6144
+    assert Bv * S * Dv * 16 > 2 ** 31
+    g = torch.Generator(device=DEV).manual_seed(5)
+    x = (torch.randn(Bv, S, Dv, generator=g, device=DEV) * 3.0).bfloat16()
+    x[x.abs() < 1e-3] = 1.0  # keeps every value a normal half that bf16 holds exactly, and no -0
+    frames = codec.fp16_encode(x)
+    assert frames.shape == (S * 16, Bv, Dv) and frames.dtype == torch.bfloat16
+    back = codec.fp16_decode(frames, S)
+    assert torch.equal(back, x.half().to(torch.bfloat16))
+    # the last value's 16 frames, by hand
+    bits = int(x[-1, -1, -1].half().view(torch.int16)) & 0xFFFF
+    assert [int(v) for v in frames[-16:, -1, -1].float()] == [(bits >> (15 - k)) & 1 for k in range(16)]
+    zeros = torch.zeros_like(frames)
+    assert torch.equal(codec.binary_residual(frames, zeros), frames)
