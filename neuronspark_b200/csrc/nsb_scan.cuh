@@ -909,6 +909,35 @@ struct BwdParams {
   uint32_t* err;
 };
 
+// Warps that share one TMA box in the backward kernel. DRAM efficiency of the tiled copies
+// depends on the length of a row segment, not on the bytes per box (measured on the selective
+// backward, 9 streams: 8 x 128 B and 16 x 128 B boxes both stop at ~5.85 ms, 8 x 256 B reaches
+// 5.03 ms), while the modulated backward only fits 2 columns per lane in registers (128-byte
+// segments in bf16). There two neighbouring warps share boxes with 256-byte rows: the first one's
+// lane 0 issues the copies, both wait on the same mbarrier, and a named barrier of 64 threads
+// joins them before the box is stored.
+template <int MODE, int V, int C, bool TMA>
+struct BwdBox {
+  static constexpr int kWarps = (TMA && ModeTraits<MODE>::kMod && V == 2 && C == 8) ? 2 : 1;
+};
+
+// Named-barrier primitives for such a pair (id 1..15; all 64 threads must arrive).
+__device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ bool pair_or(int id, bool x) {
+  uint32_t r;
+  asm volatile(
+      "{\n"
+      ".reg .pred pin, pout;\n"
+      "setp.ne.u32 pin, %2, 0;\n"
+      "bar.red.or.pred pout, %1, 64, pin;\n"
+      "selp.u32 %0, 1, 0, pout;\n"
+      "}"
+      : "=r"(r)
+      : "r"(id), "r"((uint32_t)x)
+      : "memory");
+  return r != 0;
+}
+
 // Surrogate derivative on the V lanes of a thread.
 //   arctangent: (alpha/2) / (1 + (pi/2*alpha*x)^2)      c1 = pi/2*alpha, c2 = alpha/2
 //   sigmoid:    alpha*sig*(1-sig) = alpha*e/(1+e)^2 with e = exp(-alpha*|x|) in (0,1]
@@ -955,15 +984,23 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   using IO = VecIO<ST, V>;
   constexpr int NF = MT::kFwdStreams;  // forward inputs; then g_spike, then optional g_vpost
   constexpr int kGS = NF, kGV = NF + 1;
-  constexpr int TILE_ELEMS = C * 32 * V;
-  constexpr uint32_t TILE_BYTES = TILE_ELEMS * sizeof(ST);
+  constexpr int G = BwdBox<MODE, V, C, TMA>::kWarps;  // warps per TMA box
+  constexpr int ROW = 32 * V * G;                      // elements per shared-memory row of a box
+  constexpr int TILE_ELEMS = C * 32 * V;               // one warp's share of a box
+  constexpr int BOX_ELEMS = C * ROW;
+  constexpr uint32_t TILE_BYTES = BOX_ELEMS * sizeof(ST);
   extern __shared__ __align__(128) uint8_t smem_raw[];
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int wpc = blockDim.x >> 5;
-  const long long col0 = ((long long)blockIdx.x * wpc + warp) * (32 * V);
-  if (col0 >= p.cols) return;
+  const int box = warp / G, half = warp % G;
+  const int nbox = wpc / G;
+  const int pair_id = 1 + box;
+  const bool leader = half == 0 && lane == 0;
+  const long long boxcol0 = ((long long)blockIdx.x * nbox + box) * ROW;
+  if (boxcol0 >= p.cols) return;  // the same for every warp of a box
+  const long long col0 = boxcol0 + (long long)half * (32 * V);
 
   constexpr int nstreams = NF + 1 + (HAS_GV ? 1 : 0);
   constexpr bool has_gv = HAS_GV;
@@ -1013,19 +1050,20 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   float* stash = nullptr;
   if constexpr (TMA) {
     const uint32_t base = smem_u32(smem_raw);
-    bar0 = base + (uint32_t)(warp * stages) * 8u;
+    bar0 = base + (uint32_t)(box * stages) * 8u;
     const uint32_t data_base = (base + (uint32_t)(wpc * stages) * 8u + 127u) & ~127u;
-    data0 = data_base + (uint32_t)(warp * stages) * stage_bytes;
+    data0 = data_base + (uint32_t)(box * stages) * stage_bytes;
     data_ptr = smem_raw + (data0 - base);
     if constexpr (STASH)
-      stash = reinterpret_cast<float*>(smem_raw + (data_base - base) + (size_t)(wpc * stages) * stage_bytes) +
+      stash = reinterpret_cast<float*>(smem_raw + (data_base - base) + (size_t)(nbox * stages) * stage_bytes) +
               (size_t)warp * (NQ * TILE_ELEMS) + V * lane;
-    if (lane == 0) {
+    if (leader) {
       for (int s = 0; s < stages; ++s) mbar_init(bar0 + 8u * s, 1);
       mbar_init_fence();
       proxy_async_fence();
     }
     __syncwarp();
+    if constexpr (G > 1) pair_sync(pair_id);
   }
 
   auto issue = [&](int tile, int s) {
@@ -1033,7 +1071,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
       const uint32_t bar = bar0 + 8u * s;
       const uint32_t dst = data0 + (uint32_t)s * stage_bytes;
       mbar_arrive_expect_tx(bar, stage_bytes);
-      const int x = (int)col0, y = tile * C;
+      const int x = (int)boxcol0, y = tile * C;
       tma_load_2d(dst, &tm0, x, y, bar);
       tma_load_2d(dst + TILE_BYTES, &tm1, x, y, bar);
       if (nstreams > 2) tma_load_2d(dst + 2 * TILE_BYTES, &tm2, x, y, bar);
@@ -1046,7 +1084,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
 
   const int ntiles = p.ntiles;
   if constexpr (TMA) {
-    if (lane == 0) {
+    if (leader) {
       const int pre = ntiles < stages ? ntiles : stages;
       for (int s = 0; s < pre; ++s) issue(ntiles - 1 - s, s);
     }
@@ -1056,7 +1094,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   ST regs[TMA ? 1 : (NF + 2) * C * V] = {};
   auto fetch = [&](int stream, int k, float (&out)[V]) {
     if constexpr (TMA) {
-      IO::load(sp + stream * TILE_ELEMS + k * (32 * V), out);
+      IO::load(sp + stream * BOX_ELEMS + k * ROW, out);
     } else {
 #pragma unroll
       for (int j = 0; j < V; ++j) out[j] = E::to_f32(regs[(stream * C + k) * V + j]);
@@ -1315,15 +1353,15 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
         if constexpr (MODE != MODE_RF && !MT::kMod) vmul<V>(acc, gpre, b);
 
         if constexpr (TMA) {
-          if constexpr (MODE != MODE_ROW) IO::store(wsp + MT::kBeta * TILE_ELEMS + k * (32 * V), gb);
+          if constexpr (MODE != MODE_ROW) IO::store(wsp + MT::kBeta * BOX_ELEMS + k * ROW, gb);
           if constexpr (MODE != MODE_ROW && MODE != MODE_LIN)
-            IO::store(wsp + MT::kVth * TILE_ELEMS + k * (32 * V), gth);
-          if constexpr (MODE == MODE_RFMOD) IO::store(wsp + MT::kOmega * TILE_ELEMS + k * (32 * V), go);
+            IO::store(wsp + MT::kVth * BOX_ELEMS + k * ROW, gth);
+          if constexpr (MODE == MODE_RFMOD) IO::store(wsp + MT::kOmega * BOX_ELEMS + k * ROW, go);
           if constexpr (MT::kFwdStreams >= 4) {
-            IO::store(wsp + MT::kDrive * TILE_ELEMS + k * (32 * V), gd);
-            IO::store(wsp + MT::kGain * TILE_ELEMS + k * (32 * V), gg);
+            IO::store(wsp + MT::kDrive * BOX_ELEMS + k * ROW, gd);
+            IO::store(wsp + MT::kGain * BOX_ELEMS + k * ROW, gg);
           } else {
-            IO::store(wsp + MT::kDrive * TILE_ELEMS + k * (32 * V), gpre);
+            IO::store(wsp + MT::kDrive * BOX_ELEMS + k * ROW, gpre);
           }
         } else {
           const size_t ro = (size_t)k * row_elems;
@@ -1356,12 +1394,14 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
     if constexpr (TMA) {
       const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 2u);
-      if (!__any_sync(0xffffffffu, ok)) {
+      bool gave_up = !__any_sync(0xffffffffu, ok);
+      if constexpr (G > 1) gave_up = pair_or(pair_id, gave_up);  // both warps of a box take the same way out
+      if (gave_up) {
         failed = true;
         break;
       }
       const uint8_t* sp8 = data_ptr + (size_t)s_idx * stage_bytes;
-      sp = reinterpret_cast<const ST*>(sp8) + V * lane;
+      sp = reinterpret_cast<const ST*>(sp8) + half * (32 * V) + V * lane;
 #pragma unroll
       for (int j = 0; j < V; ++j) {
         v[j] = vnext[j];
@@ -1398,9 +1438,10 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     if constexpr (TMA) {
       proxy_async_fence();  // make this lane's shared-memory writes visible to TMA
       __syncwarp();
-      if (lane == 0) {
+      if constexpr (G > 1) pair_sync(pair_id);
+      if (leader) {
         const uint32_t src = data0 + (uint32_t)s_idx * stage_bytes;
-        const int x = (int)col0, y = i * C;
+        const int x = (int)boxcol0, y = i * C;
         if (MODE != MODE_ROW && p.g_beta) tma_store_2d(&tmo_beta, src + MT::kBeta * TILE_BYTES, x, y);
         if (MODE != MODE_ROW && MODE != MODE_LIN && p.g_vth) tma_store_2d(&tmo_vth, src + MT::kVth * TILE_BYTES, x, y);
         if (p.g_drive) tma_store_2d(&tmo_drive, src + MT::kDrive * TILE_BYTES, x, y);
@@ -1425,7 +1466,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   }
 
   if constexpr (TMA) {
-    if (lane == 0) bulk_wait_all();
+    if (leader) bulk_wait_all();
     if (failed) {
       for (int s = 0; s < stages; ++s)
         mbar_wait_bounded(bar0 + 8u * s, (s < s_idx) ? (phase ^ 1u) : phase, nullptr, 0u);
@@ -1469,16 +1510,17 @@ inline int defer_refill(const Tuning& tune, const Plan& plan, const DeviceInfo& 
 // The planner works from register estimates. If the CTA it chose does not fit an SM with the
 // registers the kernel really has, halve the warps per CTA (shared memory is per warp, so it
 // shrinks in proportion) until it does.
+// `group` = warps that must stay together in a CTA (those sharing a TMA box).
 template <typename K>
-int shrink_to_fit(K kern, Plan& plan, long long nwarps) {
+int shrink_to_fit(K kern, Plan& plan, long long nwarps, int group = 1) {
   for (;;) {
     int blocks = 0;
     NSB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kern, plan.wpc * 32, plan.smem),
                  "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
     if (blocks > 0) return NSB_OK;
-    if (plan.wpc == 1) return NSB_ERR_UNSUPPORTED;
+    if (plan.wpc <= group) return NSB_ERR_UNSUPPORTED;
     const size_t per_warp = (plan.smem - 256) / plan.wpc;
-    plan.wpc = (plan.wpc + 1) / 2;
+    plan.wpc = group * ((plan.wpc / group + 1) / 2);
     plan.smem = per_warp * plan.wpc + 256;
     plan.grid = (int)((nwarps + plan.wpc - 1) / plan.wpc);
   }
@@ -1589,28 +1631,40 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   p.has_gv = has_gv; p.nstreams = nstreams; p.alpha = a.alpha; p.alpha_dev = a.alpha_dev;
   p.err = device_error_word_ptr();
 
-  const long long nwarps = (a.cols + 32 * V - 1) / (32 * V);
+  // warps sharing one TMA box (and its shared-memory rows); the grid is counted in whole boxes
+  constexpr int G = BwdBox<MODE, V, C, TMA>::kWarps;
+  const long long nwarps = G * ((a.cols + 32 * V * G - 1) / (32 * V * G));
   CUtensorMap tm[12];
   memset(tm, 0, sizeof tm);
   Plan plan;
   if (TMA) {
     for (int i = 0; i < nstreams; ++i) {
       int r = make_tensor_map_2d(&tm[i], streams[i], Elem<ST>::kDtype, (uint64_t)a.T, (uint64_t)a.cols, C,
-                                 32 * V);
+                                 32 * V * G);
       if (r != NSB_OK) return r;
     }
     const void* outs[5] = {a.g_beta, a.g_drive, a.g_gain, a.g_vth, a.g_extra};
     for (int i = 0; i < 5; ++i) {
       if (!outs[i]) continue;
       int r = make_tensor_map_2d(&tm[7 + i], outs[i], Elem<ST>::kDtype, (uint64_t)a.T, (uint64_t)a.cols, C,
-                                 32 * V);
+                                 32 * V * G);
       if (r != NSB_OK) return r;
     }
     plan = planned;
     if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;
+    if (G > 1) {  // whole boxes per CTA; shared memory is per warp, so it scales with the warp count
+      const size_t per_warp = (plan.smem - 256) / plan.wpc;
+      plan.wpc = std::min(G * ((plan.wpc + G - 1) / G), 2 * 15);  // one named barrier (1..15) per box
+      plan.smem = per_warp * plan.wpc + 256;
+      if (plan.smem > (size_t)dev.max_smem_optin) {
+        plan.wpc = G;
+        plan.smem = per_warp * plan.wpc + 256;
+      }
+      plan.grid = (int)((nwarps + plan.wpc - 1) / plan.wpc);
+    }
     NSB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem),
                  "cudaFuncSetAttribute(bwd)");
-    if (int r = shrink_to_fit(kern, plan, nwarps); r != NSB_OK) return r;
+    if (int r = shrink_to_fit(kern, plan, nwarps, G); r != NSB_OK) return r;
   } else {
     plan.wpc = tune.warps_per_cta > 0 ? std::min(tune.warps_per_cta, kBwdMaxThreads / 32) : 4;
     plan.stages = 1;
@@ -1946,6 +2000,14 @@ int scan_mod_bwd_dispatch(const BwdArgs& a) {
     q.modulated = a.mode == MODE_RFMOD ? 2 : 1;
     // 4 lanes per thread spill heavily with the modulation's extra live values (measured 3x slower)
     q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 2 : 1;
+    // The 2-lane kernels work in pairs of warps per TMA box. With enough columns to fill the GPU,
+    // two boxes per CTA and a 2-deep ring measured best (B=32, T=8192, D=6144, bf16: first order
+    // 5.58 ms against 6.2 ms for 1 or 4 boxes per CTA or a 3-deep ring; resonate-and-fire 9.7 ms
+    // against 9.8-11.5 ms).
+    if (C == 8 && tune.lanes_per_thread != 1 && a.cols >= 64LL * 8 * std::max(1, dev.sm_count)) {
+      if (tune.warps_per_cta <= 0) tune.warps_per_cta = 4;
+      if (tune.stages <= 0) tune.stages = 2;
+    }
     plan = plan_scan(dev, q, tune);
   }
   const int V = plan.lanes;
