@@ -318,6 +318,25 @@ def test_fused_backward_variants(rf, tile, lanes, direct):
 
 
 @pytest.mark.parametrize("rf", [False, True])
+def test_fused_backward_launch_shapes(rf):
+    """The 2-lane backward kernels run as pairs of warps on one TMA box: any CTA size (odd requests
+    are rounded up to whole pairs) and ring depth gives the same bits, also where the last box is
+    only partly inside the tensor (1040 = 8 boxes of 128 columns + 16) and the last tile is short."""
+    T, B, D = 70, 2, 520
+    d, b, v0, w0 = mod_inputs(T, B, D, torch.bfloat16, 61, rf)
+    gS = (torch.randn(T, B, D, device=DEV) * 0.1).bfloat16()
+    ps.CKPT_INTERVAL = 8
+    nsb.set_tuning(lanes_per_thread=2)
+    base = _fused_grads(d, b, v0, w0, gS, _Sigmoid(4.0), rf)
+    for wpc, stages in [(1, 2), (2, 3), (3, 2), (4, 4), (6, 3), (8, 2)]:
+        nsb.set_tuning(warps_per_cta=wpc, stages=stages, lanes_per_thread=2)
+        got = _fused_grads(d, b, v0, w0, gS, _Sigmoid(4.0), rf)
+        for k, v in base.items():
+            if v is not None:
+                assert torch.equal(v, got[k]), (wpc, stages, k)
+
+
+@pytest.mark.parametrize("rf", [False, True])
 def test_fused_edge_cases(rf):
     # T = 0: the states pass through, nothing else is touched
     d, b, v0, w0 = mod_inputs(0, 2, 64, torch.bfloat16, 3, rf)
