@@ -420,6 +420,31 @@ int nsb_moe_combine_bwd(const void* g_out, const void* experts, const float* wei
                         void* stream);
 
 /*
+ * Expert merge of the mixture-of-experts SNN FFN in the frame domain
+ * (atomic_ops/moe_snn_ffn.py:377-393, training branch: fp16_decode of the
+ * shared output, of every expert's output and of the block input, weighted sum,
+ * two additions, binary_encode_ste), as one kernel per direction.
+ *   shared, residual, out: frames [S*16, B, D]; experts: [E, S*16, B, D];
+ *   weights: [S, B, E] (the reference's full_weights), all in `dtype`; E <= 16.
+ *   out = encode(((decode(shared) + sum_e decode(experts[e]) * w[e]) + decode(residual)))
+ * with every product, the sum over experts and both additions rounded to
+ * `dtype` as the reference's tensor arithmetic rounds them. Experts whose
+ * weight for a token is exactly 0 are not read.
+ * Backward (straight-through encode, atomic_ops/fp16_codec.py:208-226): g_total
+ * = mean over a value's 16 output-frame gradients; g_shared / g_residual =
+ * decode'(frames) * g_total; g_experts[e] = decode'(experts[e]) * g_total * w[e];
+ * g_weights[s, b, e] = sum_d g_total * decode(experts[e]) (fp32 sum, fixed
+ * order). Any of the four outputs may be NULL.
+ */
+int nsb_frames_combine_fwd(const void* shared, const void* experts, const void* weights,
+                           const void* residual, void* out, int64_t B, int64_t S, int64_t D, int E,
+                           int dtype, void* stream);
+int nsb_frames_combine_bwd(const void* g_out, const void* shared, const void* experts,
+                           const void* weights, const void* residual, void* g_shared, void* g_experts,
+                           void* g_weights, void* g_residual, int64_t B, int64_t S, int64_t D, int E,
+                           int dtype, void* stream);
+
+/*
  * The modulation alone, written out: beta, u, v_th (and omega when raw_omega is
  * given) as [rows, channels] tensors in dtype_out (NSB_F32, or dtype_in). A
  * drop-in for the reference's _fused_modulation(_rf) functions in code that

@@ -58,6 +58,8 @@ _SIGNATURES = {
     "nsb_linear_recurrence_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_moe_combine_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_moe_combine_bwd": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_frames_combine_fwd": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
+    "nsb_frames_combine_bwd": (c_int, [c_void_p] * 9 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "nsb_modulation_fwd": (c_int, [c_void_p] * 9 + [c_float, c_int64, c_int64] + [c_void_p] * 4 +
                            [c_int, c_int, c_void_p]),
     "nsb_fp16_encode": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),

@@ -94,31 +94,10 @@ __global__ void decode_bwd_kernel(const T* __restrict__ frames, const T* __restr
       float bit[16];
 #pragma unroll
       for (int k = 0; k < 16; ++k) bit[k] = Elem<T>::to_f32(f[k].v[j]);
-      const float g = Elem<T>::to_f32(gv.v[j]);
-      const float sign = 1.0f - 2.0f * bit[0];
-      const float e = 16.0f * bit[1] + 8.0f * bit[2] + 4.0f * bit[3] + 2.0f * bit[4] + bit[5];
-      float m = 0.0f, w = 0.5f;
+      float gk[16];
+      codec::decode16_bwd(bit, Elem<T>::to_f32(gv.v[j]), gk);
 #pragma unroll
-      for (int i = 0; i < 10; ++i) {
-        m += bit[6 + i] * w;
-        w *= 0.5f;
-      }
-      const bool normal = e > 0.0f;
-      const float scale = normal ? exp2f(e - 15.0f) : 6.103515625e-05f;
-      const float mag = normal ? scale * (1.0f + m) : scale * m;
-      out[0].v[j] = Elem<T>::from_f32(-2.0f * mag * g);
-      const float ge = normal ? g * sign * mag * 0.6931471805599453f : 0.0f;
-      out[1].v[j] = Elem<T>::from_f32(ge * 16.0f);
-      out[2].v[j] = Elem<T>::from_f32(ge * 8.0f);
-      out[3].v[j] = Elem<T>::from_f32(ge * 4.0f);
-      out[4].v[j] = Elem<T>::from_f32(ge * 2.0f);
-      out[5].v[j] = Elem<T>::from_f32(ge);
-      float gm = g * sign * scale * 0.5f;
-#pragma unroll
-      for (int i = 0; i < 10; ++i) {
-        out[6 + i].v[j] = Elem<T>::from_f32(gm);
-        gm *= 0.5f;
-      }
+      for (int k = 0; k < 16; ++k) out[k].v[j] = Elem<T>::from_f32(gk[k]);
     }
     T* o = g_frames + (s * 16 * B + b) * D + d;
 #pragma unroll

@@ -58,6 +58,35 @@ __device__ __forceinline__ float decode16(const float (&bit)[16]) {
   return val;
 }
 
+// Gradient of decode16 with respect to its 16 frame values, times g (fp32 formula; the frames
+// are differentiated as reals: sign = 1 - 2*bit0, exponent and mantissa sums linear in their bits).
+__device__ __forceinline__ void decode16_bwd(const float (&bit)[16], float g, float (&out)[16]) {
+  const float sign = 1.0f - 2.0f * bit[0];
+  const float e = 16.0f * bit[1] + 8.0f * bit[2] + 4.0f * bit[3] + 2.0f * bit[4] + bit[5];
+  float m = 0.0f, w = 0.5f;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    m += bit[6 + i] * w;
+    w *= 0.5f;
+  }
+  const bool normal = e > 0.0f;
+  const float scale = normal ? exp2f(e - 15.0f) : 6.103515625e-05f;
+  const float mag = normal ? scale * (1.0f + m) : scale * m;
+  out[0] = -2.0f * mag * g;
+  const float ge = normal ? g * sign * mag * 0.6931471805599453f : 0.0f;
+  out[1] = ge * 16.0f;
+  out[2] = ge * 8.0f;
+  out[3] = ge * 4.0f;
+  out[4] = ge * 2.0f;
+  out[5] = ge;
+  float gm = g * sign * scale * 0.5f;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    out[6 + i] = gm;
+    gm *= 0.5f;
+  }
+}
+
 // Half bit pattern of decode(a) + decode(b) for frames stored in DTYPE, with the roundings
 // the reference's arithmetic in that dtype performs (atomic_ops/fp16_codec.py:115-164).
 template <int DTYPE>

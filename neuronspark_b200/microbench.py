@@ -118,6 +118,35 @@ def main():
             report("moe_combine_bwd", (E, N, D), _time(bw, args.iters, flush), (2 * E + 1) * N * D * es)
             del sh, ex, w, exl, wl, go, out
 
+    if args.only in "frames_combine":
+        for E, top_k, B, S, D in [(4, 2, 8, 512, 768), (8, 2, 8, 512, 768)]:
+            mkf = lambda: codec.fp16_encode(torch.empty(B, S, D, dtype=dt, device=dev).normal_())
+            sh, rs = mkf(), mkf()
+            ex = torch.stack([mkf() for _ in range(E)])
+            w = torch.rand(S, B, E, device=dev)
+            w = w.masked_fill(torch.rand(S, B, E, device=dev).argsort(-1) >= top_k, 0.0).to(dt)
+            fb = B * S * D * 16 * es                      # bytes of one frame tensor
+            with torch.no_grad():
+                report("frames_combine_fwd", (E, top_k, B, S, D),
+                       _time(lambda: mk.frames_combine(sh, ex, w, rs), args.iters, flush), (top_k + 3) * fb)
+
+                def unfused():
+                    vals = torch.stack([codec.fp16_decode(ex[e], S) for e in range(E)])
+                    tot = codec.fp16_decode(sh, S) + (vals * w.permute(2, 1, 0).unsqueeze(-1)).sum(0)
+                    return codec.fp16_encode(tot + codec.fp16_decode(rs, S))
+                report("frames_combine_fwd_unfused (codec kernels + torch ops)", (E, top_k, B, S, D),
+                       _time(unfused, args.iters, flush), (E + 3) * fb)
+            leaves = [t.requires_grad_() for t in (sh, ex, w, rs)]
+            go = torch.empty_like(sh).normal_()
+            out = mk.frames_combine(*leaves)
+
+            def bw():
+                out.backward(go, retain_graph=True)
+                for t in leaves:
+                    t.grad = None
+            report("frames_combine_bwd", (E, top_k, B, S, D), _time(bw, args.iters, flush), (2 * E + 5) * fb)
+            del sh, rs, ex, w, leaves, go, out
+
     # adaptive surrogate slope: one read of u (the reference pays the same pass plus a host sync)
     for shape in [(8192, 8, 768), (8192, 32, 6144)]:
         if args.only in "surrogate_alpha":

@@ -392,6 +392,51 @@ def encode_ste_bwd(g_frames):
     return g
 
 
+def _round_storage(x, storage):
+    """fp32 array rounded through the storage dtype ("f32", "bf16" or "f16"), nearest even."""
+    x = np.ascontiguousarray(x, np.float32)
+    if storage == "bf16":
+        u = x.view(np.uint32).astype(np.uint64)
+        u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+        return u.astype(np.uint32).view(np.float32)
+    if storage == "f16":
+        return x.astype(np.float16).astype(np.float32)
+    return x
+
+
+def frames_combine_fwd(shared, experts, weights, residual, storage="f32"):
+    """(out frames (T*16, B, D), total (B, T, D)) of the expert merge in the frame domain
+    (atomic_ops/moe_snn_ffn.py:377-393): every product, the sum over the experts (accumulated in
+    fp32 in expert order, as a sum over the leading dimension is) and both additions rounded to the
+    tensors' dtype. weights is the reference's full_weights, (T, B, E)."""
+    rnd = lambda a: _round_storage(a, storage)
+    dec = lambda f: rnd(fp16_decode(f, bf16_intermediates=(storage == "bf16")))
+    weights = _f32(weights)
+    acc = np.zeros_like(dec(shared))
+    for e in range(len(experts)):
+        w = weights[:, :, e].T[:, :, None]          # (B, T, 1)
+        acc = (acc + rnd(dec(experts[e]) * w)).astype(np.float32)
+    total = rnd(rnd(dec(shared) + rnd(acc)) + dec(residual))
+    return fp16_encode(total), total
+
+
+def frames_combine_bwd(g_out, shared, experts, weights, residual, storage="f32"):
+    """(g_shared, g_experts, g_weights, g_residual): straight-through encode (mean over the 16 frame
+    gradients, atomic_ops/fp16_codec.py:222-226), then the decode adjoint of every stream."""
+    rnd = lambda a: _round_storage(a, storage)
+    weights = _f32(weights)
+    g_total = rnd(encode_ste_bwd(g_out))
+    g_shared, g_res = fp16_decode_bwd(shared, g_total), fp16_decode_bwd(residual, g_total)
+    g_exp, g_w = [], np.zeros_like(weights)
+    for e in range(len(experts)):
+        w = weights[:, :, e].T[:, :, None]
+        g_exp.append(fp16_decode_bwd(experts[e], rnd(g_total * w)))
+        val = rnd(fp16_decode(experts[e], bf16_intermediates=(storage == "bf16")))
+        g_w[:, :, e] = (g_total.astype(np.float64) * val).sum(-1).T
+    g_exp = np.stack(g_exp) if g_exp else np.zeros((0,) + g_shared.shape, np.float32)
+    return g_shared, g_exp, rnd(g_w), g_res
+
+
 # ---------------------------------------------------------------- normaliser
 
 

@@ -32,6 +32,10 @@ What each fixture is produced by:
                   SpikingJelly to import) and run eagerly, without their
                   torch.compile decorator, + autograd.
   moe_a           moe_combine (atomic_ops/moe_kernels.py:210-224; its CPU branch) + autograd.
+  frames_combine_* the training branch of MoESNNFFN.forward_parallel that merges the experts
+                  (atomic_ops/moe_snn_ffn.py:377-393: fp16_decode of every stream, weighted
+                  sum, + shared, + residual, binary_encode_ste), restated with the
+                  reference's own fp16_decode / binary_encode_ste, in fp32 and bf16, + autograd.
   linrec_a        linear_recurrence (atomic_ops/parallel_scan.py:1282-1302; on CPU the
                   Hillis-Steele scan, :1238-1275) + autograd.
   surrogate_alpha the four lines of PLIFNode.get_surrogate that derive the slope from
@@ -52,6 +56,8 @@ if len(sys.argv) < 2 and "NEURONSPARK_REF" not in os.environ:
     raise SystemExit("usage: make_golden.py <path to the NeuronSpark checkout>  (or set NEURONSPARK_REF)")
 REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["NEURONSPARK_REF"])
 OUT = Path(__file__).resolve().parent
+# optional: `--only PREFIX` rewrites just the fixtures whose name starts with PREFIX
+ONLY = sys.argv[sys.argv.index("--only") + 1] if "--only" in sys.argv else ""
 
 
 def load(name, rel):
@@ -110,6 +116,8 @@ def function_from_source(rel, name):
 
 
 def npz(name, **arrs):
+    if not name.startswith(ONLY):
+        return
     out = {}
     for k, v in arrs.items():
         if isinstance(v, torch.Tensor):
@@ -340,6 +348,27 @@ def main():
     (mout * mg).sum().backward()
     npz("moe_a", shared=msh, experts=mex, weights=mw, out=mout, g_out=mg, g_shared=msh.grad, g_experts=mex.grad,
         g_weights=mw.grad)
+
+    # ---- expert merge in the frame domain (atomic_ops/moe_snn_ffn.py:377-393)
+    for tag, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        torch.manual_seed(33)
+        T_, K_, B_, D_, E_ = 6, 16, 2, 24, 4
+        mk = lambda scale: codec.fp16_encode((torch.randn(B_, T_, D_) * scale).to(dt), K_).requires_grad_()
+        f_shared, f_res = mk(1.0), mk(2.0)
+        f_exp = [mk(0.7) for _ in range(E_)]
+        fw = torch.rand(T_, B_, E_) * (torch.rand(T_, B_, E_) < 0.5)      # sparse routing weights
+        fw = fw.to(dt).requires_grad_()
+        shared_val = codec.fp16_decode(f_shared, T_, K_)
+        expert_vals = torch.stack([codec.fp16_decode(f_exp[e], T_, K_) for e in range(E_)], dim=0)
+        w = fw.permute(2, 1, 0).unsqueeze(-1)
+        combined = shared_val + (expert_vals * w).sum(dim=0)
+        total = combined + codec.fp16_decode(f_res, T_, K_)
+        out = codec.binary_encode_ste(total)
+        g_out = (torch.randn(T_ * K_, B_, D_) * 0.1).to(dt)
+        (out.float() * g_out.float()).sum().backward()
+        npz(f"frames_combine_{tag}", shared=f_shared, residual=f_res, experts=torch.stack(f_exp), weights=fw,
+            total=total, out=out, g_out=g_out, g_shared=f_shared.grad, g_residual=f_res.grad,
+            g_experts=torch.stack([f.grad for f in f_exp]), g_weights=fw.grad)
 
     # ---- linear recurrence (the reference's CPU branch is a Hillis-Steele scan: same numbers up to
     # the association of the products, not bit-comparable with a sequential loop)

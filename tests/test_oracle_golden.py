@@ -205,3 +205,21 @@ def test_moe_combine(golden):
     ge, gw = orc.moe_combine_bwd(g["g_out"], g["experts"], g["weights"])
     assert rel_err(ge, g["g_experts"]) < TOL and rel_err(gw, g["g_weights"]) < TOL
     assert np.array_equal(g["g_shared"], g["g_out"])
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_frames_combine(golden, tag):
+    """Expert merge in the frame domain against the reference's own decode / weighted sum / add /
+    binary_encode_ste sequence: the re-encoded frames and the value they encode must be identical
+    (every rounding of the reference's tensor arithmetic is restated); gradients to a tolerance
+    (fp32: 1e-5 of the largest; bf16: the reference's autograd rounds every intermediate to bf16,
+    so 2^-6 of the largest)."""
+    g = golden(f"frames_combine_{tag}")
+    out, total = orc.frames_combine_fwd(g["shared"], g["experts"], g["weights"], g["residual"], storage=tag)
+    assert np.array_equal(total, g["total"])
+    assert np.array_equal(out, g["out"])
+    gs, ge, gw, gr = orc.frames_combine_bwd(g["g_out"], g["shared"], g["experts"], g["weights"], g["residual"],
+                                            storage=tag)
+    tol = TOL if tag == "f32" else 2.0 ** -6
+    assert rel_err(gs, g["g_shared"]) < tol and rel_err(gr, g["g_residual"]) < tol
+    assert rel_err(ge, g["g_experts"]) < tol and rel_err(gw, g["g_weights"]) < tol
