@@ -155,42 +155,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 
 // One 2-D TMA tile load into this CTA's shared memory, completion counted in
 // bytes on `bar`. x = innermost (column) coordinate, y = row (time) coordinate.
-#ifndef NSB_L2_HINT
-#define NSB_L2_HINT 0
-#endif
-__device__ __forceinline__ uint64_t l2_evict_first_policy() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y,
                                             uint32_t bar) {
-#if NSB_L2_HINT & 1
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
-      " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
-      "l"(tm), "r"(x), "r"(y), "r"(bar), "l"(l2_evict_first_policy())
-      : "memory");
-#else
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
       "l"(tm), "r"(x), "r"(y), "r"(bar)
       : "memory");
-#endif
 }
 // One 2-D TMA tile store from this CTA's shared memory (bulk async group).
 // Rows / columns of the box that fall outside the tensor are not written.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
-#if NSB_L2_HINT & 2
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;" ::"l"(tm),
-               "r"(x), "r"(y), "r"(src), "l"(l2_evict_first_policy())
-               : "memory");
-#else
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tm),
                "r"(x), "r"(y), "r"(src)
                : "memory");
-#endif
 }
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
