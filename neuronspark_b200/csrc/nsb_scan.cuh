@@ -915,10 +915,13 @@ struct BwdParams {
 // 5.03 ms), while the modulated backward only fits 2 columns per lane in registers (128-byte
 // segments in bf16). There two neighbouring warps share boxes with 256-byte rows: the first one's
 // lane 0 issues the copies, both wait on the same mbarrier, and a named barrier of 64 threads
-// joins them before the box is stored.
+// joins them before the box is stored. The plain resonate-and-fire backward gains a little the same
+// way over its 4-lane form (timed alone 5.07 against 5.22 ms at B=32, T=8192, D=6144; alternating
+// with its forward 5.27 against 5.30 ms); the first-order selective backward does not (5.37 against
+// 5.06 ms) and keeps one warp per box.
 template <int MODE, int V, int C, bool TMA>
 struct BwdBox {
-  static constexpr int kWarps = (TMA && ModeTraits<MODE>::kMod && V == 2 && C == 8) ? 2 : 1;
+  static constexpr int kWarps = (TMA && (ModeTraits<MODE>::kMod || MODE == MODE_RF) && V == 2 && C == 8) ? 2 : 1;
 };
 
 // Named-barrier primitives for such a pair (id 1..15; all 64 threads must arrive).
@@ -1765,11 +1768,20 @@ int scan_bwd_dispatch(const BwdArgs& a) {
   const int C = a.tile;
   Plan plan;
   if (tma) {
+    // resonate-and-fire with enough columns to fill the GPU: 2 lanes per thread as pairs of warps
+    // per TMA box, two boxes per CTA, 3-deep ring (measured best, see BwdBox)
+    Tuning tune_rf = tune;
+    if (a.mode == MODE_RF && C == 8 && !a.g_vpost && tune.lanes_per_thread <= 0 &&
+        a.cols >= 64LL * 8 * std::max(1, dev.sm_count)) {
+      tune_rf.lanes_per_thread = 2;
+      if (tune_rf.warps_per_cta <= 0) tune_rf.warps_per_cta = 4;
+      if (tune_rf.stages <= 0) tune_rf.stages = 3;
+    }
     PlanQuery q;
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
     q.nstreams = (a.mode == MODE_ROW ? 1 : ((a.mode == MODE_AI || a.mode == MODE_RF) ? 4 : 3)) + 1 + (a.g_vpost ? 1 : 0);
     q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : (C == 16 ? 2 : 1);
-    plan = plan_scan(dev, q, tune);
+    plan = plan_scan(dev, q, tune_rf);
   }
   const int V = plan.lanes;
 
