@@ -58,7 +58,7 @@ struct FrameBlock {
 };
 
 template <typename T, int VE>
-__global__ void frames_combine_fwd_kernel(const T* __restrict__ shared, const T* __restrict__ experts,
+__global__ void __maxnreg__(80) frames_combine_fwd_kernel(const T* __restrict__ shared, const T* __restrict__ experts,
                                           const T* __restrict__ weights, const T* __restrict__ residual,
                                           T* __restrict__ out, long long B, long long S, long long D, int E) {
   const long long dv = D / VE;
@@ -104,7 +104,7 @@ constexpr int kMaxWarps = 32;
 
 // One CTA per token at a time (grid-stride over tokens); its threads cover the channels.
 template <typename T, int VE>
-__global__ void frames_combine_bwd_kernel(const T* __restrict__ g_out, const T* __restrict__ shared,
+__global__ void __maxnreg__(96) frames_combine_bwd_kernel(const T* __restrict__ g_out, const T* __restrict__ shared,
                                           const T* __restrict__ experts, const T* __restrict__ weights,
                                           const T* __restrict__ residual, T* __restrict__ g_shared,
                                           T* __restrict__ g_experts, T* __restrict__ g_weights,
