@@ -72,6 +72,12 @@ INFERENCE_WORKLOADS = {
 # algorithmic bytes per neuron-step with 2-byte streams
 BYTES_FWD = 4 * 2 + 2          # beta, I, alpha, V_th in; spikes out
 BYTES_BWD = 4 * 2 + 2 + 4 * 2  # the four inputs again, dL/dspike in; four gradients out
+# The reference's own model (config 3): HEAD's SNNLanguageModel, staged untouched under oracle/_ref,
+# with only the scan / codec / normaliser calls rebound to this library by install().
+MODEL_WORKLOADS = {
+    "c3": dict(vocab=6144, D=768, N=8, K=16, layers=20, D_ff=2304, B=8, seq=512),
+    "c3-small": dict(vocab=6144, D=768, N=8, K=16, layers=2, D_ff=2304, B=2, seq=128),
+}
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per neuron-step measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
 # reduced-T case "c2-short" (same grid, T=512); traffic of these kernels is proportional to T, so a
@@ -87,7 +93,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2",
-                    choices=sorted(WORKLOADS) + sorted(INFERENCE_WORKLOADS) + sorted(MODULATED_WORKLOADS))
+                    choices=sorted(WORKLOADS) + sorted(INFERENCE_WORKLOADS) + sorted(MODULATED_WORKLOADS)
+                    + sorted(MODEL_WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     return ap.parse_args()
@@ -683,6 +690,164 @@ def run_inference(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------- the reference's model (config 3)
+
+
+def run_model(args):
+    """Forward of the reference's SNNLanguageModel with the scan / codec / normaliser calls served by
+    this library, and — where Triton can compile on this machine — by the reference's own kernels.
+    Everything else (projections, gating, embedding, logits) is the reference's PyTorch in both arms."""
+    import torch
+    from oracle import ref_harness as rh
+    from neuronspark_b200 import _lib, install as inst
+    import neuronspark_b200 as nsb
+    cfg = MODEL_WORKLOADS[args.workload]
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    if not rh.available():
+        print(json.dumps({"metric": "SNN LM forward tokens/s", "unavailable":
+                          "oracle/_ref is empty: python oracle/make_ref.py <NeuronSpark checkout>"}), flush=True)
+        return
+    SWAPPED = {"atomic_ops.snn_block": ("rf_plif_parallel_forward_recompute", "plif_rowparam_forward_recompute",
+                                        "binary_residual"),
+               "atomic_ops.snn_ffn": ("plif_rowparam_forward_recompute", "binary_residual"),
+               "model": ("fp16_encode", "fp16_decode")}
+
+    def build(eager):
+        rh.unload_reference()
+        _, model_mod = rh.load_reference(eager_elementwise=eager)
+        torch.manual_seed(1234)
+        m = model_mod.SNNLanguageModel(vocab_size=cfg["vocab"], D=cfg["D"], N=cfg["N"], K=cfg["K"],
+                                       num_layers=cfg["layers"], D_ff=cfg["D_ff"])
+        with torch.no_grad():  # N(0, 0.02) weights as the configuration asks; biases keep their structured init
+            for name, p in m.named_parameters():
+                if p.dim() == 2:
+                    p.normal_(0.0, 0.02)
+        return m.to(dev).to(torch.bfloat16).eval()
+
+    tokens = torch.randint(0, cfg["vocab"], (cfg["B"], cfg["seq"]), device=dev,
+                           generator=torch.Generator(device=dev).manual_seed(1234))
+
+    class KernelClock:
+        """CUDA events around every swapped call, to report their share of the forward."""
+
+        def __init__(self):
+            self.pairs, self.undo = [], []
+
+        def attach(self):
+            for mod_name, names in SWAPPED.items():
+                mod = sys.modules[mod_name]
+                for n in names:
+                    fn = getattr(mod, n)
+                    self.undo.append((mod, n, fn))
+                    setattr(mod, n, self.wrap(n, fn))
+            norm_cls = sys.modules["atomic_ops.lateral_inhibition"].LateralInhibition
+            fwd = norm_cls.forward
+            self.undo.append((norm_cls, "forward", fwd))
+            norm_cls.forward = self.wrap("lateral_inhibition", fwd)
+
+        def wrap(self, name, fn):
+            def timed(*a, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = fn(*a, **k)
+                e1.record()
+                self.pairs.append((name, e0, e1))
+                return out
+            return timed
+
+        def detach(self):
+            for mod, n, fn in reversed(self.undo):
+                setattr(mod, n, fn)
+            self.undo.clear()
+
+        def totals(self, reps):
+            tot = {}
+            for name, e0, e1 in self.pairs:
+                tot[name] = tot.get(name, 0.0) + e0.elapsed_time(e1) / reps
+            return tot
+
+    def time_arm(m, steps, warmup):
+        with torch.no_grad():
+            for _ in range(warmup):
+                m(tokens)
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(steps):
+                logits = m(tokens).logits
+            end.record()
+            torch.cuda.synchronize()
+            ms = start.elapsed_time(end) / steps
+            clock = KernelClock()
+            clock.attach()
+            try:
+                for _ in range(2):
+                    m(tokens)
+                torch.cuda.synchronize()
+            finally:
+                clock.detach()
+        return ms, clock.totals(2), logits
+
+    K, W = args.steps, max(args.warmup, 3)
+    note = {}
+    arms = {}
+    for eager in (False, True):
+        try:
+            m = build(eager)
+            changed = inst.install()
+            sampler = ClockSampler(dev.index)
+            sampler.start()
+            ms, parts, logits = time_arm(m, K, W)
+            clocks = sampler.stop()
+            arms["ours"] = (ms, parts)
+            note["elementwise_helpers"] = ("eager PyTorch (torch.compile could not run here)" if eager
+                                           else "torch.compile (inductor), as in the reference")
+            break
+        except Exception as e:  # inductor / Triton toolchain not usable: run those helpers eagerly
+            inst.uninstall()
+            if eager:
+                raise
+            note["compile_error"] = f"{type(e).__name__}: {str(e)[:200]}"
+    assert nsb.device_error_word() == 0
+    finite = bool(torch.isfinite(logits).all())
+    spike_calls = len(changed)
+    inst.uninstall()
+    try:  # the same model object on the reference's own Triton kernels
+        ms_ref, parts_ref, logits_ref = time_arm(m, K, W)
+        arms["reference_triton"] = (ms_ref, parts_ref)
+        note["argmax_agreement_with_reference"] = float((logits.argmax(-1) == logits_ref.argmax(-1)).float().mean())
+    except Exception as e:  # noqa: BLE001
+        note["reference_triton"] = f"unavailable: {type(e).__name__}: {str(e)[:200]}"
+    ms, parts = arms["ours"]
+    tok = cfg["B"] * cfg["seq"]
+    T = cfg["seq"] * cfg["K"]
+    # neuron-steps of the swapped scans in one forward: per layer D*N + D (block) + 2*D_ff + D (FFN)
+    ns = cfg["layers"] * T * cfg["B"] * (cfg["D"] * cfg["N"] + 2 * cfg["D"] + 2 * cfg["D_ff"])
+    scan_ms = sum(v for k, v in parts.items() if "plif" in k)
+    line = {
+        "metric": "SNN LM forward tokens/s (reference model, scan/codec/normaliser on this library)",
+        "value": tok / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['layers']}-layer SNNLanguageModel forward, D={cfg['D']}, N={cfg['N']}, "
+                               f"K={cfg['K']}, D_ff={cfg['D_ff']}, vocab {cfg['vocab']}, seq {cfg['seq']}, B={cfg['B']}, "
+                               "random-init N(0,0.02) weights, uniform token ids, bf16, no_grad",
+                   "names_rebound_by_install": spike_calls, **note},
+        "swapped_kernels_ms_per_forward": parts,
+        "swapped_share_of_forward": sum(parts.values()) / ms,
+        "scan_neuron_steps_per_forward": ns,
+        "scan_neuron_steps_per_s": ns / (scan_ms * 1e-3) if scan_ms else None,
+        "clocks": clocks, "validation": {"finite_logits": finite},
+        "gpu_launches": K * (cfg["layers"] * 6 + 3),
+    }
+    if "reference_triton" in arms:
+        line["reference_triton"] = {"ms_per_step": arms["reference_triton"][0],
+                                    "swapped_kernels_ms_per_forward": arms["reference_triton"][1]}
+    print(json.dumps(line), flush=True)
+
+
 # --------------------------------------------------------------------- main
 
 
@@ -696,6 +861,9 @@ def main():
         return
     if args.workload in INFERENCE_WORKLOADS:
         run_inference(args)
+        return
+    if args.workload in MODEL_WORKLOADS:
+        run_model(args)
         return
     import torch
     import torch.distributed as dist

@@ -1,6 +1,8 @@
+#!/usr/bin/env python
 """Timing of the boundary kernels (FP16 codec, lateral inhibition, adaptive surrogate slope) on one GPU.
 
-    python -m neuronspark_b200.microbench [--dtype bf16|f32] [--iters N]
+    python microbench.py [--dtype bf16|f32] [--iters N] [--only SUBSTRING]
+    python microbench.py --triton-reference       the reference's own Triton scans beside this library's
 
 Prints one JSON line per kernel and shape: microseconds per call (CUDA events,
 best of N, 256 MB written between calls so that nothing is served from L2),
@@ -11,12 +13,18 @@ from __future__ import annotations
 
 import argparse
 import json
+import sys
+from pathlib import Path
 
 import torch
 
-from . import fp16_codec as codec
-from . import lateral_inhibition as li
-from . import parallel_scan as ps
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from neuronspark_b200 import fp16_codec as codec  # noqa: E402
+from neuronspark_b200 import lateral_inhibition as li  # noqa: E402
+from neuronspark_b200 import parallel_scan as ps  # noqa: E402
 
 
 def _time(fn, iters, flush):
@@ -39,7 +47,13 @@ def main():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default="", help="substring filter on the kernel name")
+    ap.add_argument("--triton-reference", action="store_true",
+                    help="time the reference's Triton scan kernels (staged under oracle/_ref) and this "
+                         "library's on the same inputs; nothing else")
     args = ap.parse_args()
+    if args.triton_reference:
+        triton_reference(args.iters)
+        return
     dt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     es = 2 if dt == torch.bfloat16 else 4
     dev = torch.device("cuda", 0)
@@ -83,7 +97,7 @@ def main():
                    _time(lambda: fn.backward(ctx, go), args.iters, flush), rows * D * 4 * es)
 
     # linear recurrence, forward and forward+backward (2 streams in, 1 out; backward 3 in, 2 out)
-    from . import moe_kernels as mk
+    from neuronspark_b200 import moe_kernels as mk
     if args.only in "linear_recurrence":
         T, B, D = 8192, 32, 6144
         beta = torch.rand(T, B, D, device=dev).to(dt)
@@ -154,6 +168,86 @@ def main():
             report("surrogate_alpha", shape, _time(lambda: ps.adaptive_alpha(u, 4.0, 0.4), args.iters, flush),
                    u.numel() * es)
             del u
+
+
+def triton_reference(iters):
+    """The kernels to beat: ``_TritonPLIFForward`` and ``_TritonPLIFRowParamRecompute`` of the
+    reference (atomic_ops/parallel_scan.py:690-768, 614-688), forward + backward, at the shapes of
+    the reference's own bench (exp/bench_fused_plif.py:156-158: T=8192, batch 2, D*N = 6144 and
+    D = 768, bf16) and at the headline shape (batch 32), next to this library's Functions of the
+    same names on the same tensors. One JSON line per (implementation, kernel, shape); where the
+    reference cannot run (no staged copy, Triton cannot compile) the line says why."""
+    import importlib.util
+    ref_file = ROOT / "oracle" / "_ref" / "atomic_ops" / "parallel_scan.py"
+    dev = torch.device("cuda", 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ref = None
+    why = None
+    if not ref_file.exists():
+        why = "oracle/_ref is empty (python oracle/make_ref.py <NeuronSpark checkout>)"
+    else:
+        try:
+            spec = importlib.util.spec_from_file_location("ref_parallel_scan", ref_file)
+            ref = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(ref)
+            if not getattr(ref, "_HAS_TRITON", False):
+                ref, why = None, "the reference found no Triton"
+        except Exception as e:  # noqa: BLE001
+            ref, why = None, f"{type(e).__name__}: {e}"
+
+    def inputs(T, B, D, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+
+        def rn():
+            out = torch.empty((T, B, D), dtype=torch.bfloat16, device=dev)
+            for t0 in range(0, T, 512):
+                out[t0:t0 + 512] = torch.randn(out[t0:t0 + 512].shape, generator=g, device=dev)
+            return out
+        beta = rn().float().mul_(0.5).add_(2).sigmoid_().bfloat16()
+        u = rn()
+        vth = torch.nn.functional.softplus(rn().float()).add_(0.1).bfloat16()
+        gs = rn().mul_(0.1)
+        return beta, u, vth, gs
+
+    def fwd_bwd(fn, tensors, gs, n_out_grads):
+        leaves = [t.detach().clone().requires_grad_() for t in tensors]  # the reference overwrites u in place
+
+        def run():
+            out = fn(*leaves)
+            out[0].backward(gs)
+            for t in leaves:
+                t.grad = None
+        return run
+
+    for T, B, D in [(8192, 2, 6144), (8192, 2, 768), (8192, 32, 6144)]:
+        beta, u, vth, gs = inputs(T, B, D, 1234)
+        v0 = torch.zeros(B, D, dtype=torch.bfloat16, device=dev)
+        beta_row, vth_row = beta[0].contiguous(), vth[0].contiguous()
+        ns = T * B * D
+        cases = [
+            # u-form selective scan: fwd 3 in + spike + V_post out; bwd 3 in + V_post, spike, gS in + 3 out
+            ("selective fwd+bwd (_TritonPLIFForward)", "_TritonPLIFForward", (beta, u, vth, v0), None),
+            ("row-param recompute fwd+bwd (_TritonPLIFRowParamRecompute)", "_TritonPLIFRowParamRecompute",
+             (beta_row, u, vth_row, v0), None),
+        ]
+        for label, cls, tensors, _ in cases:
+            for impl, mod in (("reference-triton", ref), ("neuronspark_b200", ps)):
+                line = {"impl": impl, "kernel": label, "shape": [T, B, D], "dtype": "bf16"}
+                if mod is None:
+                    line["unavailable"] = why
+                    print(json.dumps(line), flush=True)
+                    continue
+                try:
+                    f = getattr(mod, cls)
+                    run = fwd_bwd(lambda *a, f=f: f.apply(*a, 4.0), tensors, gs, 0)
+                    us = _time(run, iters, flush)
+                    line.update({"us": round(us, 1), "G_neuron_steps_per_s": round(ns / us / 1e3, 2)})
+                except Exception as e:  # noqa: BLE001
+                    line["unavailable"] = f"{type(e).__name__}: {str(e)[:300]}"
+                    if impl == "reference-triton":
+                        ref, why = None, line["unavailable"]
+                print(json.dumps(line), flush=True)
+        del beta, u, vth, gs
 
 
 class _Ctx:

@@ -38,6 +38,13 @@ REPLACEMENTS = {
     "moe_kernels": (moe_kernels, ("MoECombine", "moe_combine")),
 }
 
+#: modules of the reference whose ``forward`` takes its kernel branch only when its module-level
+#: ``_HAS_TRITON`` is true (atomic_ops/lateral_inhibition.py:206, atomic_ops/rms_norm.py:40). Without
+#: Triton the reference does not even define ``_LateralInhibitionTriton`` (:122, under ``if
+#: _HAS_TRITON``), so both names are set there regardless of what the import found.
+_GATED = {"lateral_inhibition": ("_LateralInhibitionTriton",), "rms_norm": ("_LateralInhibitionTriton",)}
+
+_ABSENT = object()
 _undo: list[tuple[ModuleType, str, object]] = []
 
 
@@ -70,6 +77,17 @@ def install(package: str = "atomic_ops", extra_modules=()) -> list[str]:
                 _undo.append((ref_mod, name, old))
                 setattr(ref_mod, name, getattr(ours, name))
                 changed.append(f"{ref_mod.__name__}.{name}")
+    for short, names in _GATED.items():
+        mod = sys.modules.get(f"{package}.{short}")
+        if mod is None:
+            continue
+        for name, new in [("_HAS_TRITON", True)] + [(n, getattr(lateral_inhibition, n)) for n in names]:
+            old = getattr(mod, name, _ABSENT)
+            if old is not new:
+                _undo.append((mod, name, old))
+                setattr(mod, name, new)
+                if name != "_HAS_TRITON" or old is not True:
+                    changed.append(f"{mod.__name__}.{name}")
     # modules that did `from .parallel_scan import name` hold their own reference
     scan = [m for n, m in list(sys.modules.items())
             if m is not None and (n == package or n.startswith(package + ".") or n == "model")]
@@ -91,6 +109,9 @@ def uninstall() -> int:
     n = 0
     while _undo:
         mod, name, old = _undo.pop()
-        setattr(mod, name, old)
+        if old is _ABSENT:
+            delattr(mod, name)
+        else:
+            setattr(mod, name, old)
         n += 1
     return n

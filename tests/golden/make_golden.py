@@ -22,6 +22,11 @@ What each fixture is produced by:
                   (heaviside forward, alpha*sig*(1-sig) backward).
   scan_ai_*       the same loop with v_pre = beta*v + alpha*x
                   (atomic_ops/selective_plif.py:127).
+  scan_ai_bwd_atan the same loop with the arctangent surrogate (BASELINE config 2: atan,
+                  alpha = 2; the reference's fused kernels have sigmoid only). The surrogate is
+                  given by its PRIMITIVE, g(x) = atan(pi/2 * alpha * x) / pi + 1/2 (the published
+                  form of SpikingJelly's ATan), and torch autograd derives g' from it: no
+                  hand-written derivative enters the fixture. Inputs with config 2's distributions.
   rowparam_*      the same loops with per-column beta / v_th.
   codec_*         fp16_encode, fp16_decode (+ autograd), _binary_residual_fwd,
                   _binary_residual_naive, _BinaryEncodeSTE from
@@ -83,7 +88,31 @@ class SigmoidSurrogate(torch.autograd.Function):
         return g * ctx.alpha * s * (1 - s), None
 
 
-def seq_loop(beta, u, vth, v_init, alpha, rowparam=False, gain=None, cur=None):
+class PrimitiveSurrogate(torch.autograd.Function):
+    """heaviside(x) forward; backward multiplies by the derivative of ``primitive`` at x, which
+    torch autograd computes from the primitive itself."""
+
+    @staticmethod
+    def forward(ctx, x, primitive):
+        ctx.save_for_backward(x)
+        ctx.primitive = primitive
+        return (x >= 0).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        with torch.enable_grad():
+            xx = x.detach().requires_grad_()
+            (d,) = torch.autograd.grad(ctx.primitive(xx).sum(), xx)
+        return g * d, None
+
+
+def atan_primitive(alpha):
+    import math
+    return lambda x: torch.atan(math.pi / 2 * alpha * x) / math.pi + 0.5
+
+
+def seq_loop(beta, u, vth, v_init, alpha, rowparam=False, gain=None, cur=None, primitive=None):
     """The reference test's ground-truth loop (exp/verify_fused_plif.py:111-124)."""
     v = v_init
     T = (u if u is not None else cur).shape[0]
@@ -95,7 +124,8 @@ def seq_loop(beta, u, vth, v_init, alpha, rowparam=False, gain=None, cur=None):
         v_pre = b * v + drive
         sp = (v_pre.detach() >= th.detach()).to(v_pre.dtype)
         v = v_pre - th * sp
-        S.append(SigmoidSurrogate.apply(v_pre - th, alpha))
+        S.append(SigmoidSurrogate.apply(v_pre - th, alpha) if primitive is None
+                 else PrimitiveSurrogate.apply(v_pre - th, primitive))
         V.append(v)
     return torch.stack(S), torch.stack(V)
 
@@ -193,6 +223,29 @@ def main():
     npz("scan_ai_bwd", beta=beta, cur=cur, gain=gain, vth=vth, v_init=v0, g_spike=gS,
         alpha=np.float64(4.0), spike=S, vpost=V, g_beta=beta.grad, g_cur=cur.grad,
         g_gain=gain.grad, g_vth=vth.grad, g_vinit=v0.grad)
+
+    # ---- alpha*I form backward, arctangent surrogate (alpha = 2) through its primitive, config-2 inputs
+    g = torch.Generator().manual_seed(2024)
+    T, B, D = 96, 2, 48
+    rn = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)
+    cur = rn(T, B, D).requires_grad_()
+    beta = torch.sigmoid(2 + 0.5 * rn(T, B, D)).requires_grad_()
+    gain = torch.nn.functional.softplus(rn(T, B, D)).requires_grad_()
+    vth = (0.1 + torch.nn.functional.softplus(rn(T, B, D))).requires_grad_()
+    v0 = (rn(B, D) * 0.1).requires_grad_()
+    gS = rn(T, B, D) * 0.1
+    # fp32-representable inputs, adjoint in double: the spikes are those of the fp32 recurrence
+    # (asserted), the gradients carry no fp32 accumulation error of the generator's own
+    with torch.no_grad():
+        for t in (cur, beta, gain, vth, v0, gS):
+            t.copy_(t.float().double())
+        s32, V32 = seq_loop(beta.float(), None, vth.float(), v0.float(), 2.0, gain=gain.float(), cur=cur.float())
+    S, V = seq_loop(beta, None, vth, v0, 2.0, gain=gain, cur=cur, primitive=atan_primitive(2.0))
+    assert torch.equal(S.detach().float(), s32), "double and fp32 recurrences spike differently on this seed"
+    (S * gS).sum().backward()
+    npz("scan_ai_bwd_atan", beta=beta, cur=cur, gain=gain, vth=vth, v_init=v0, g_spike=gS,
+        alpha=np.float64(2.0), spike=S, g_beta=beta.grad, g_cur=cur.grad, g_gain=gain.grad,
+        g_vth=vth.grad, g_vinit=v0.grad)
 
     # ---- row-param, the inputs of test_recompute.py:27-31 (K=16,B=2,dim=256, seed 42)
     torch.manual_seed(42)

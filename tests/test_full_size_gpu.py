@@ -2,7 +2,8 @@
 
 Where the CPU oracle finishes in seconds (configs 0 and 1) the whole output is
 compared. At the headline size (config 2: 1.6 G neuron-steps) the oracle runs on
-column blocks taken from the full problem, and the rest is covered by
+a strided sample of columns that reaches every warp of the forward launch and
+every CTA of the backward launch, and the rest is covered by
 size-independent properties: gradients are linear in the upstream gradient,
 packed and dense spikes agree, and a scan cut in two with the state carried
 equals the uncut scan."""
@@ -53,26 +54,37 @@ def test_config2_full_size_properties():
     names = ("beta", "cur", "gain", "vth")
     leaves = [inp[k].requires_grad_() for k in names] + [inp["v0"].requires_grad_()]
     spike, v_last = ps.plif_selective_scan_ai(*leaves, alpha=2.0, surrogate="atan")
+    nsb_launch = {"fwd": nsb.last_launch_info()}
     spike.backward(inp["g_spike"])
+    nsb_launch["bwd"] = nsb.last_launch_info()
     g1 = [t.grad for t in leaves]
     for t in leaves:
         t.grad = None
 
-    # (1) the oracle on column blocks cut out of the full problem (left edge, middle, right edge)
+    # (1) the oracle on columns cut out of the full problem: the two edge blocks, and one column out
+    # of every 128 across the whole width - every warp of the forward launch (32 lanes x 4 columns)
+    # and every CTA of the backward launch (256 columns) has a column in the sample, and the offset
+    # inside the 128 rotates so that all lanes and all four vector positions are hit - over all
+    # 8192 steps, forward and the five gradients
     cols = B * D
-    blocks = [slice(0, 96), slice(cols // 2 - 40, cols // 2 + 56), slice(cols - 96, cols)]
+    lf, lb = nsb_launch["fwd"], nsb_launch["bwd"]
+    assert 32 * lf["lanes_per_thread"] <= 128 and 32 * lb["lanes_per_thread"] * lb["warps_per_cta"] <= 256
+    w = np.arange(cols // 128)
+    strided = torch.from_numpy(128 * w + (37 * w) % 128).to(DEV)
+    assert len(strided) >= 1536 and len(set(((37 * w) % 128).tolist())) == 128
+    edges = torch.cat([torch.arange(0, 96), torch.arange(cols - 96, cols)]).to(DEV)
     flat = lambda t: t.detach().reshape(T, cols)
-    for sl in blocks:
-        ins = [f32(flat(inp[k])[:, sl]) for k in names]
-        v0b = f32(inp["v0"].detach().reshape(cols)[sl])
+    for idx in (edges, strided):
+        pick = lambda t: f32(flat(t).index_select(1, idx))
+        ins = [pick(inp[k]) for k in names]
+        v0b = f32(inp["v0"].detach().reshape(cols)[idx])
         rs, _, rl = orc.plif_selective_ai_fwd(*ins, v0b, want_vpost=False)
-        assert np.array_equal(f32(flat(spike)[:, sl]), rs), "spikes must be bit-exact"
-        assert np.array_equal(f32(v_last.detach().reshape(cols)[sl]), rl)
-        ref = orc.plif_selective_ai_bwd(*ins, v0b, f32(flat(inp["g_spike"])[:, sl]), None, 2.0,
-                                        orc.SURR_ATAN)
+        assert np.array_equal(pick(spike), rs), "spikes must be bit-exact"
+        assert np.array_equal(f32(v_last.detach().reshape(cols)[idx]), rl)
+        ref = orc.plif_selective_ai_bwd(*ins, v0b, pick(inp["g_spike"]), None, 2.0, orc.SURR_ATAN)
         for g, e, n in zip(g1[:4], ref[:4], names):
-            assert_close_lowp(f32(flat(g)[:, sl]), e, torch.bfloat16, f"grad {n}")
-        assert_close(f32(g1[4].reshape(cols)[sl]), ref[4], what="grad v_init")
+            assert_close_lowp(pick(g), e, torch.bfloat16, f"grad {n}")
+        assert_close(f32(g1[4].reshape(cols)[idx]), ref[4], what="grad v_init")
 
     # (2) gradients are linear in the upstream gradient; doubling is exact in binary floating point
     spike2, _ = ps.plif_selective_scan_ai(*leaves, alpha=2.0, surrogate="atan")

@@ -60,6 +60,23 @@ def test_selective_ai_bwd(golden):
         assert rel_err(mine, g[ref]) < TOL, ref
 
 
+def test_selective_ai_backward_atan(golden):
+    """The arctangent surrogate (alpha = 2, the headline benchmark's) against torch autograd through
+    the surrogate's primitive atan(pi/2*alpha*x)/pi + 1/2: the oracle's hand-written derivative
+    (alpha/2)/(1+(pi/2*alpha*x)^2) is what autograd derives."""
+    g = golden("scan_ai_bwd_atan")
+    s, _, _ = orc.plif_selective_ai_fwd(g["beta"], g["cur"], g["gain"], g["vth"], g["v_init"])
+    assert np.array_equal(s, g["spike"])
+    out = orc.plif_selective_ai_bwd(g["beta"], g["cur"], g["gain"], g["vth"], g["v_init"],
+                                    g["g_spike"], None, float(g["alpha"]), orc.SURR_ATAN)
+    for mine, ref in zip(out, ("g_beta", "g_cur", "g_gain", "g_vth", "g_vinit")):
+        assert rel_err(mine, g[ref]) < TOL, ref
+    # and it is not the sigmoid surrogate that passes
+    wrong = orc.plif_selective_ai_bwd(g["beta"], g["cur"], g["gain"], g["vth"], g["v_init"],
+                                      g["g_spike"], None, float(g["alpha"]), orc.SURR_SIGMOID)
+    assert rel_err(wrong[1], g["g_cur"]) > 1e-2
+
+
 @pytest.mark.parametrize("name", ["rowparam_a", "rowparam_c1"])
 def test_rowparam(golden, name):
     g = golden(name)

@@ -86,6 +86,32 @@ def test_golden_ai_backward(golden):
         assert_close(f32(t.grad), g[k], what=k)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_golden_ai_backward_atan(golden, dtype):
+    """Arctangent surrogate, alpha = 2 (the headline benchmark's): gradients against torch autograd
+    through the surrogate's primitive (tests/golden/make_golden.py, fixture scan_ai_bwd_atan)."""
+    g = golden("scan_ai_bwd_atan")
+    ins = [cuda(g[k]).requires_grad_() for k in ("beta", "cur", "gain", "vth", "v_init")]
+    if dtype != torch.float32:
+        # bf16 streams: round the inputs, regenerate the expectation from the oracle (itself pinned to
+        # the fixture in fp32 by tests/test_oracle_golden.py) on the rounded values
+        ins = [t.detach().to(dtype).requires_grad_() for t in ins[:4]] + [ins[4]]
+    spike, _ = ps.plif_selective_scan_ai(*ins, alpha=float(g["alpha"]), surrogate="atan")
+    gs = cuda(g["g_spike"]).to(dtype)
+    (spike.float() * gs.float()).sum().backward()
+    if dtype == torch.float32:
+        assert np.array_equal(f32(spike), g["spike"])
+        for t, k in zip(ins, ("g_beta", "g_cur", "g_gain", "g_vth", "g_vinit")):
+            assert_close(f32(t.grad), g[k], what=k)
+    else:
+        hb, hc, hg, ht, hv = (f32(t) for t in ins)
+        s, _, _ = orc.plif_selective_ai_fwd(hb, hc, hg, ht, hv)
+        assert np.array_equal(f32(spike), s)
+        ref = orc.plif_selective_ai_bwd(hb, hc, hg, ht, hv, f32(gs), None, float(g["alpha"]), orc.SURR_ATAN)
+        for t, e, k in zip(ins, ref, ("g_beta", "g_cur", "g_gain", "g_vth", "g_vinit")):
+            assert_close_lowp(f32(t.grad), e, t.dtype, what=k)
+
+
 @pytest.mark.parametrize("name", ["rowparam_a", "rowparam_c1"])
 @pytest.mark.parametrize("recompute", [False, True])
 def test_golden_rowparam(golden, name, recompute):
