@@ -572,7 +572,8 @@ def run_inference(args):
         def step():
             _lib.check(L.nsb_plif_rowparam_residual_fwd(p(beta_row), p(u), p(vth_row), p(v_a), p(frames_in),
                                                         p(frames_out), None, p(v_b), T, cols, _lib.BF16,
-                                                        tile_steps, stream), "rowparam_residual_fwd")
+                                                        tile_steps, _lib.RESIDUAL_COMPILED, stream),
+                       "rowparam_residual_fwd")
 
         def unfused():
             with torch.no_grad():

@@ -41,11 +41,29 @@ extern "C" {
 #define NSB_BF16 1
 #define NSB_F16 2
 
+/* ---- rounding of the binary residual on bf16 frames ----
+ * fp32 and fp16 frames leave no choice (every intermediate of decode + add is
+ * exact in them); for bf16 frames the reference behaves in two ways:
+ *   EAGER     its ops run one by one (_binary_residual_naive, or
+ *             _binary_residual_fwd called directly, atomic_ops/fp16_codec.py:103-164):
+ *             mantissa sum, 1+m, both decoded values and their sum are each
+ *             rounded to bf16;
+ *   COMPILED  binary_residual() as it runs on a GPU, through
+ *             torch.compile(_binary_residual_fwd) (:168-186): the decode stays in
+ *             fp32 inside inductor's fused kernel and only the sum - a bf16 tensor
+ *             between two kernels - is rounded to bf16 (observed bit for bit on a
+ *             B200, torch 2.11, on the frames of the reference's own layers).   */
+#define NSB_RESIDUAL_EAGER 0
+#define NSB_RESIDUAL_COMPILED 1
+
 /* ---- surrogate gradients ---- */
 #define NSB_SURR_SIGMOID 0 /* a*sig(ax)*(1-sig(ax)), exp argument clamped at 88
                               (atomic_ops/parallel_scan.py:291-296)            */
-#define NSB_SURR_ATAN 1    /* (a/2)/(1+(pi/2*a*x)^2); no counterpart in the
-                              reference's fused kernels                        */
+#define NSB_SURR_ATAN 1    /* (a/2)/(1+(pi/2*a*x)^2), the derivative of
+                              atan(pi/2*a*x)/pi + 1/2 (SpikingJelly's ATan); the
+                              reference's fused kernels have sigmoid only, so
+                              this one is checked against torch autograd
+                              through that primitive                           */
 
 /* Library version (major*10000 + minor*100 + patch). */
 int nsb_version(void);
@@ -58,8 +76,29 @@ const char* nsb_last_cuda_error(void);
 
 /* Reads and clears the device-side error word (set when a bounded wait inside
  * a kernel gave up). Synchronises nothing: the word lives in mapped host
- * memory; call after synchronising the stream you care about. */
+ * memory; call after synchronising the stream you care about.
+ *
+ * The word is sticky: while it is non-zero every entry point of the scan family
+ * (nsb_plif_*, nsb_linear_recurrence_*) returns NSB_ERR_DEVICE_TIMEOUT before it
+ * launches anything, so a caller that never looks at the word still learns of a
+ * timed-out scan at its next call; this function is what clears it. A warp that
+ * gives up leaves NaN in its columns of V_last / W_last (forward) or grad_v_init
+ * (backward) and does not write the rest of its outputs.
+ * The first scan call of a process allocates the (64-byte, mapped, pinned) word:
+ * make that call outside CUDA stream capture.
+ * The reference has no counterpart: its Triton kernels have no waits to bound. */
 int nsb_device_error_word(uint32_t* out);
+
+/* Limit of every bounded device-side wait in nanoseconds; 0 restores the default
+ * of 2 s. Process-global, read at each launch. */
+int nsb_set_wait_limit_ns(uint64_t ns);
+
+/* Self-test of the timeout path, for test suites: launches one warp that waits,
+ * with the current limit, on a barrier that nothing will ever complete. The warp
+ * gives up, sets bit 31 of the error word and returns; nothing faults and no
+ * memory operation is left in flight. Set a short limit first
+ * (nsb_set_wait_limit_ns) unless a 2 s kernel is wanted. */
+int nsb_selftest_wait_timeout(void* stream);
 
 /* Tuning override for the scan kernels, used by sweeps and tests. Any field
  * <= 0 keeps the built-in heuristic. warps_per_cta: warps of one CTA (each
@@ -206,8 +245,9 @@ int nsb_plif_rf_bwd(const void* beta, const void* omega, const void* u, const vo
  *                        arithmetic does.
  * nsb_fp16_decode_bwd    autograd of that formula: g_values [B,S,D] and the
  *                        frames -> g_frames [S*16,B,D].
- * nsb_binary_residual    _binary_residual_fwd (:115-164):
- *                        encode(decode(a)+decode(b)).
+ * nsb_binary_residual    binary_residual / _binary_residual_fwd (:115-197):
+ *                        encode(decode(a)+decode(b)); `rounding` is one of
+ *                        NSB_RESIDUAL_* (it matters for bf16 frames only).
  * nsb_encode_ste_bwd     _BinaryEncodeSTE.backward (:220-224): mean over the 16
  *                        frames of each token.
  */
@@ -218,7 +258,7 @@ int nsb_fp16_decode_fwd(const void* frames, void* values, int64_t B, int64_t S, 
 int nsb_fp16_decode_bwd(const void* frames, const void* g_values, void* g_frames,
                         int64_t B, int64_t S, int64_t D, int dtype, void* stream);
 int nsb_binary_residual(const void* frames_a, const void* frames_b, void* frames_out,
-                        int64_t B, int64_t S, int64_t D, int dtype, void* stream);
+                        int64_t B, int64_t S, int64_t D, int dtype, int rounding, void* stream);
 int nsb_encode_ste_bwd(const void* g_frames, void* g_values, int64_t B, int64_t S,
                        int64_t D, int dtype, void* stream);
 
@@ -372,7 +412,8 @@ int nsb_plif_rf_bwd_dalpha(const void* beta, const void* omega, const void* u, c
  *   return binary_residual(spike_out, spike_in_seq)          (atomic_ops/fp16_codec.py:115-197)
  * Every 16 steps of a column are one IEEE half bit pattern (frame 0 = sign):
  * frames_out = encode(decode(spikes) + decode(frames_in)), with the reference's
- * roundings for frames stored in `dtype`. The spikes themselves are never
+ * roundings for frames stored in `dtype` (`rounding`: NSB_RESIDUAL_*, as for
+ * nsb_binary_residual). The spikes themselves are never
  * written. u, frames_in, frames_out are [T, cols] in `dtype`, T a multiple of
  * 16; ckpt_interval is 16 or 32; v_ckpt ([T/ckpt_interval, cols] fp32) is what
  * nsb_plif_rowparam_bwd needs - the residual's backward is the identity on both
@@ -382,7 +423,7 @@ int nsb_plif_rf_bwd_dalpha(const void* beta, const void* omega, const void* u, c
 int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const float* vth_row,
                                    const float* v_init, const void* frames_in, void* frames_out,
                                    float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
-                                   int ckpt_interval, void* stream);
+                                   int ckpt_interval, int rounding, void* stream);
 
 /*
  * Linear recurrence V[k] = beta[k]*V[k-1] + u[k], V[-1] = v_init. Replaces

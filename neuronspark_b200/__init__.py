@@ -4,6 +4,7 @@ Submodules mirror the reference's ``atomic_ops`` files for this path:
 ``parallel_scan``, ``fp16_codec``, ``lateral_inhibition``. ``install`` rebinds
 the reference's own modules to these implementations.
 """
-from ._lib import NSBError, set_tuning, last_launch_info, device_error_word, LIB_PATH  # noqa: F401
+from ._lib import (NSBError, set_tuning, set_wait_limit_ns, last_launch_info,  # noqa: F401
+                   device_error_word, LIB_PATH)
 
 __version__ = "0.1.0"

@@ -18,6 +18,7 @@ LIB_PATH = _PKG / "libneuronspark_b200.so"
 NSB_OK = 0
 F32, BF16, F16 = 0, 1, 2
 SURR_SIGMOID, SURR_ATAN = 0, 1
+RESIDUAL_EAGER, RESIDUAL_COMPILED = 0, 1
 
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
@@ -28,6 +29,8 @@ _SIGNATURES = {
     "nsb_status_string": (ctypes.c_char_p, [c_int]),
     "nsb_last_cuda_error": (ctypes.c_char_p, []),
     "nsb_device_error_word": (c_int, [ctypes.POINTER(c_uint32)]),
+    "nsb_set_wait_limit_ns": (c_int, [ctypes.c_uint64]),
+    "nsb_selftest_wait_timeout": (c_int, [c_void_p]),
     "nsb_set_tuning": (c_int, [c_int, c_int, c_int, c_int]),
     "nsb_last_launch_info": (c_int, [ctypes.POINTER(c_int32)]),
     "nsb_scan_plan_query": (c_int, [c_int, c_int, c_int, c_int64, c_int64, c_int,
@@ -53,7 +56,7 @@ _SIGNATURES = {
                                                                 c_void_p, c_void_p]),
     "nsb_plif_rf_bwd_dalpha": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
                                                           c_void_p]),
-    "nsb_plif_rowparam_residual_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_plif_rowparam_residual_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
     "nsb_linear_recurrence_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_linear_recurrence_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_moe_combine_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_int, c_int, c_void_p]),
@@ -66,7 +69,7 @@ _SIGNATURES = {
     "nsb_fp16_decode_fwd": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "nsb_fp16_decode_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                     c_void_p]),
-    "nsb_binary_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+    "nsb_binary_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                                     c_void_p]),
     "nsb_encode_ste_bwd": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "nsb_lateral_inhibition_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float,
@@ -108,6 +111,9 @@ def check(status: int, what: str) -> None:
         msg = L.nsb_status_string(status).decode()
         if status == 3:
             msg += " — " + L.nsb_last_cuda_error().decode()
+        if status == 4:
+            msg += (" — an earlier kernel of this process gave up on a bounded wait; its outputs are "
+                    "invalid. device_error_word() reads and clears the record")
         raise NSBError(f"{what}: {msg} (status {status})")
 
 
@@ -169,6 +175,11 @@ def scan_plan(backward: bool, nstreams: int, elem_size: int, T: int, cols: int, 
     check(lib().nsb_scan_plan_query(int(backward), nstreams, elem_size, T, cols, tile, out),
           "nsb_scan_plan_query")
     return dict(zip(("lanes_per_thread", "warps_per_cta", "stages", "grid", "smem_bytes"), out))
+
+
+def set_wait_limit_ns(ns: int = 0) -> None:
+    """Limit of the kernels' bounded waits in nanoseconds (0 = the default, 2 s). Process-global."""
+    check(lib().nsb_set_wait_limit_ns(int(ns)), "nsb_set_wait_limit_ns")
 
 
 def device_error_word() -> int:

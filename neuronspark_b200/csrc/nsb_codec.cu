@@ -107,8 +107,7 @@ __global__ void decode_bwd_kernel(const T* __restrict__ frames, const T* __restr
 
 template <typename T, int VE>
 __global__ void residual_kernel(const T* __restrict__ fa, const T* __restrict__ fb, T* __restrict__ fo,
-                                long long B, long long S, long long D) {
-  constexpr bool EMU = Elem<T>::kDtype == NSB_BF16;
+                                int compiled, long long B, long long S, long long D) {
   const long long dv = D / VE;
   const long long total = B * S * dv;
   const long long frame_stride = B * D;
@@ -133,7 +132,7 @@ __global__ void residual_kernel(const T* __restrict__ fa, const T* __restrict__ 
         ba[k] = Elem<T>::to_f32(a[k].v[j]);
         bb[k] = Elem<T>::to_f32(c[k].v[j]);
       }
-      h[j] = residual_half_bits<Elem<T>::kDtype>(ba, bb);
+      h[j] = residual_half_bits<Elem<T>::kDtype>(ba, bb, compiled != 0);
     }
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
@@ -300,14 +299,17 @@ int nsb_fp16_decode_bwd(const void* frames, const void* g_values, void* g_frames
 }
 
 int nsb_binary_residual(const void* frames_a, const void* frames_b, void* frames_out, int64_t B,
-                        int64_t S, int64_t D, int dtype, void* stream) {
-  if (B < 0 || S < 0 || D < 0 || !dtype_ok(dtype)) return NSB_ERR_INVALID_ARG;
+                        int64_t S, int64_t D, int dtype, int rounding, void* stream) {
+  if (B < 0 || S < 0 || D < 0 || !dtype_ok(dtype) ||
+      (rounding != NSB_RESIDUAL_EAGER && rounding != NSB_RESIDUAL_COMPILED))
+    return NSB_ERR_INVALID_ARG;
+  const int compiled = rounding == NSB_RESIDUAL_COMPILED;
   if (B * S * D == 0) return NSB_OK;
   if (!frames_a || !frames_b || !frames_out) return NSB_ERR_INVALID_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   NSB_CODEC_LAUNCH(residual_kernel, "launch residual_kernel", 8, NSB_PTRS(frames_a, frames_b, frames_out),
                    static_cast<const T*>(frames_a), static_cast<const T*>(frames_b),
-                   static_cast<T*>(frames_out));
+                   static_cast<T*>(frames_out), compiled);
 }
 
 int nsb_encode_ste_bwd(const void* g_frames, void* g_values, int64_t B, int64_t S, int64_t D, int dtype,

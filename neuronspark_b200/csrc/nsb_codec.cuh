@@ -89,10 +89,20 @@ __device__ __forceinline__ void decode16_bwd(const float (&bit)[16], float g, fl
 
 // Half bit pattern of decode(a) + decode(b) for frames stored in DTYPE, with the roundings
 // the reference's arithmetic in that dtype performs (atomic_ops/fp16_codec.py:115-164).
+// bf16 frames have two reference behaviours (fp32 and fp16 frames have one: every intermediate
+// is exact there). `compiled` = false: the ops evaluated one by one, each intermediate rounded
+// to bf16 (eager PyTorch). `compiled` = true: the torch.compile'd residual (:168-170) as a GPU
+// runs it: the decode stays in fp32 and only the sum, stored as a bf16 tensor between two fused
+// kernels, is rounded. The flag is uniform over a launch.
 template <int DTYPE>
-__device__ __forceinline__ uint32_t residual_half_bits(const float (&a)[16], const float (&b)[16]) {
+__device__ __forceinline__ uint32_t residual_half_bits(const float (&a)[16], const float (&b)[16],
+                                                       bool compiled) {
   constexpr bool EMU = DTYPE == NSB_BF16;
-  float sum = decode16<EMU>(a) + decode16<EMU>(b);
+  float sum;
+  if (EMU && !compiled)
+    sum = decode16<true>(a) + decode16<true>(b);
+  else
+    sum = decode16<false>(a) + decode16<false>(b);
   if (EMU) sum = round_through_bf16(sum);
   if (DTYPE == NSB_F16) sum = __half2float(__float2half_rn(sum));
   return half_bits_clamped(sum);

@@ -43,6 +43,11 @@ int get_device_info(DeviceInfo* out);  // returns NSB status
 // Pointer to the device-visible error word (mapped pinned host memory, one per
 // process). Returns nullptr if it could not be set up.
 uint32_t* device_error_word_ptr();
+// NSB_ERR_DEVICE_TIMEOUT while the error word is non-zero (a plain host load, no
+// synchronisation), NSB_OK otherwise. The word stays set until nsb_device_error_word reads it.
+int sticky_device_error();
+// Limit of every bounded device-side wait, in nanoseconds (nsb_set_wait_limit_ns; default 2 s).
+unsigned long long get_wait_limit_ns();
 
 // 2-D tiled tensor map over a row-major [rows, cols] tensor; box = [box_rows, box_cols].
 // elem: NSB dtype, or 100 for raw fp32/uint32 words.
@@ -135,22 +140,33 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// Bounded wait on an mbarrier phase: gives up after ~2 s of wall time, records
-// `code` in the error word and returns false. Never spins forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  uint32_t* err_word, uint32_t code) {
+// Bounded wait on an mbarrier phase: gives up after `limit_ns` of wall time (or 2^28 polls,
+// whichever comes first), records `code` in the error word and returns false. Never spins forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t* err_word,
+                                                  uint32_t code, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++it & 0xFF) == 0) {
-      if (global_timer_ns() - t0 > 2000000000ull || it > (1u << 28)) {
+    if ((++it & 0x3F) == 0) {
+      if (global_timer_ns() - t0 > limit_ns || it > (1u << 28)) {
         if (err_word) atomicOr(reinterpret_cast<unsigned int*>(err_word), code);
         return false;
       }
     }
   }
   return true;
+}
+// After a give-up: one shared allowance of `limit_ns` for all of a warp's stages whose loads may
+// still be in flight, so that they can land before the CTA's shared memory is released.
+__device__ __forceinline__ void mbar_drain(uint32_t bar0, int stages, int s_idx, uint32_t phase,
+                                           unsigned long long limit_ns) {
+  const uint64_t t0 = global_timer_ns();
+  for (int s = 0; s < stages; ++s) {
+    const uint64_t used = global_timer_ns() - t0;
+    mbar_wait_bounded(bar0 + 8u * s, (s < s_idx) ? (phase ^ 1u) : phase, nullptr, 0u,
+                      used < limit_ns ? limit_ns - used : 0ull);
+  }
 }
 
 // One 2-D TMA tile load into this CTA's shared memory, completion counted in

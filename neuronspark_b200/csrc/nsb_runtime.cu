@@ -18,6 +18,8 @@ DeviceInfo g_dev_cache[16];
 bool g_dev_cached[16] = {};
 uint32_t* g_err_host = nullptr;
 uint32_t* g_err_dev = nullptr;
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;
+std::atomic<unsigned long long> g_wait_ns{kDefaultWaitNs};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -86,6 +88,35 @@ uint32_t* device_error_word_ptr() {
   g_err_dev = static_cast<uint32_t*>(d);
   return g_err_dev;
 }
+
+int sticky_device_error() {
+  // g_err_host is written once, under the mutex, before any kernel can set the word; a racing
+  // first call sees nullptr and reports no error, which is true at that point.
+  volatile uint32_t* w = g_err_host;
+  return (w && *w) ? NSB_ERR_DEVICE_TIMEOUT : NSB_OK;
+}
+
+unsigned long long get_wait_limit_ns() { return g_wait_ns.load(std::memory_order_relaxed); }
+
+namespace {
+// One warp arms an mbarrier with bytes that no copy will ever deliver and waits for it with the
+// library's bounded wait: the wait runs out, the error word is set, the kernel returns. Nothing
+// is in flight when it exits.
+__global__ void wait_timeout_selftest_kernel(uint32_t* err, unsigned long long limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    mbar_init_fence();
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) mbar_arrive_expect_tx(b, 16);
+  __syncwarp();
+  const bool ok = mbar_wait_bounded(b, 0, err, 0x80000000u, limit_ns);
+  (void)__all_sync(0xffffffffu, ok);
+  if (threadIdx.x == 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(b) : "memory");
+}
+}  // namespace
 
 int make_tensor_map_2d(CUtensorMap* out, const void* base, int dtype, uint64_t rows, uint64_t cols,
                        uint32_t box_rows, uint32_t box_cols) {
@@ -161,6 +192,19 @@ int nsb_device_error_word(uint32_t* out) {
   volatile uint32_t* w = nsb::g_err_host;
   *out = *w;
   *w = 0;
+  return NSB_OK;
+}
+
+int nsb_set_wait_limit_ns(uint64_t ns) {
+  nsb::g_wait_ns.store(ns ? ns : nsb::kDefaultWaitNs, std::memory_order_relaxed);
+  return NSB_OK;
+}
+
+int nsb_selftest_wait_timeout(void* stream) {
+  uint32_t* err = nsb::device_error_word_ptr();
+  if (!err) return NSB_ERR_CUDA;
+  nsb::wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(err, nsb::get_wait_limit_ns());
+  NSB_CUDA_TRY(cudaGetLastError(), "launch wait_timeout_selftest_kernel");
   return NSB_OK;
 }
 

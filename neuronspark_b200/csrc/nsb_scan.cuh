@@ -76,6 +76,7 @@ struct FwdArgs {
   long long T = 0, cols = 0;
   int mode = MODE_U;
   int tile = 8;  // C
+  int residual_compiled = 0;  // MODE_ROWRES, bf16 frames: rounding of the residual (NSB_RESIDUAL_*)
   cudaStream_t stream = nullptr;
 };
 
@@ -341,6 +342,8 @@ struct FwdParams {
   int ntiles, stages;
   int defer;  // 1: a stage is refilled one tile after its outputs were handed to TMA
   uint32_t* err;
+  unsigned long long wait_ns;  // limit of the bounded barrier waits
+  int residual_compiled;
 };
 
 template <int MODE_>
@@ -685,7 +688,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
               a_[i] = ((hb[j] >> (15 - i)) & 1u) ? 1.0f : 0.0f;
               b_[i] = fb[i][j];
             }
-            h[j] = codec::residual_half_bits<E::kDtype>(a_, b_);
+            h[j] = codec::residual_half_bits<E::kDtype>(a_, b_, p.residual_compiled != 0);
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -756,8 +759,8 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
     t0 = (long long)i * C;
     const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
     if constexpr (TMA) {
-      const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 1u);
-      if (!__any_sync(0xffffffffu, ok)) {
+      const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 1u, p.wait_ns);
+      if (!__all_sync(0xffffffffu, ok)) {  // a lane that ran out of time takes the whole warp out
         failed = true;
         break;
       }
@@ -817,10 +820,16 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
   if constexpr (TMA) {
     if (lane == 0) bulk_wait_all();
     if (failed) {
-      // Give every load that may still be in flight a bounded chance to land
-      // before the CTA's shared memory is released.
-      for (int s = 0; s < stages; ++s)
-        mbar_wait_bounded(bar0 + 8u * s, (s < s_idx) ? (phase ^ 1u) : phase, nullptr, 0u);
+      // Give every load that may still be in flight a bounded chance to land before the CTA's
+      // shared memory is released, and leave NaN in the per-column outputs: the error word says
+      // why, and nothing downstream can mistake unwritten memory for a result.
+      mbar_drain(bar0, stages, s_idx, phase, p.wait_ns);
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        if (valid[j]) {
+          p.vlast[colj[j]] = __int_as_float(0x7fc00000);
+          if (MT::kSecond) p.wlast[colj[j]] = __int_as_float(0x7fc00000);
+        }
       return;
     }
   }
@@ -907,6 +916,7 @@ struct BwdParams {
   float alpha;
   const float* alpha_dev;
   uint32_t* err;
+  unsigned long long wait_ns;  // limit of the bounded barrier waits
 };
 
 // Warps that share one TMA box in the backward kernel. DRAM efficiency of the tiled copies
@@ -1396,8 +1406,8 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     t0 = (long long)i * C;
     const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
     if constexpr (TMA) {
-      const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 2u);
-      bool gave_up = !__any_sync(0xffffffffu, ok);
+      const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 2u, p.wait_ns);
+      bool gave_up = !__all_sync(0xffffffffu, ok);
       if constexpr (G > 1) gave_up = pair_or(pair_id, gave_up);  // both warps of a box take the same way out
       if (gave_up) {
         failed = true;
@@ -1471,8 +1481,10 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   if constexpr (TMA) {
     if (leader) bulk_wait_all();
     if (failed) {
-      for (int s = 0; s < stages; ++s)
-        mbar_wait_bounded(bar0 + 8u * s, (s < s_idx) ? (phase ^ 1u) : phase, nullptr, 0u);
+      mbar_drain(bar0, stages, s_idx, phase, p.wait_ns);
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        if (valid[j] && p.g_vinit) p.g_vinit[colj[j]] = __int_as_float(0x7fc00000);
       return;
     }
   }
@@ -1531,6 +1543,7 @@ int shrink_to_fit(K kern, Plan& plan, long long nwarps, int group = 1) {
 
 template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
 int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, const Plan& planned) {
+  if (int r = sticky_device_error(); r != NSB_OK) return r;  // an earlier kernel gave up: say so, launch nothing
   using MT = ModeTraits<MODE>;
   constexpr int NS = MT::kFwdStreams;
   // only the moment-accumulating 4-lane resonate-and-fire kernel needs the limit (natural count 180)
@@ -1558,8 +1571,10 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   p.spike = a.spike; p.packed = a.packed; p.vpost = a.vpost; p.w_out = a.w_out; p.ckpt = a.ckpt;
   p.ckpt_w = a.ckpt_w; p.vlast = a.vlast; p.wlast = a.wlast;
   p.T = a.T; p.cols = a.cols; p.words_per_row = (a.cols + 31) / 32;
+  p.residual_compiled = a.residual_compiled;
   p.ntiles = (int)((a.T + C - 1) / C);
   p.err = device_error_word_ptr();
+  p.wait_ns = get_wait_limit_ns();
 
   const long long nwarps = (a.cols + 32 * V - 1) / (32 * V);
   CUtensorMap tm[6];
@@ -1604,6 +1619,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
 
 template <typename ST, int MODE, int SURR, int V, int C, bool TMA, bool HAS_GV>
 int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune, const Plan& planned) {
+  if (int r = sticky_device_error(); r != NSB_OK) return r;
   using MT = ModeTraits<MODE>;
   constexpr int NF = MT::kFwdStreams;
   auto kern = plif_bwd_kernel<ST, MODE, SURR, V, C, TMA, HAS_GV>;
@@ -1633,6 +1649,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   p.ntiles = (int)((a.T + C - 1) / C);
   p.has_gv = has_gv; p.nstreams = nstreams; p.alpha = a.alpha; p.alpha_dev = a.alpha_dev;
   p.err = device_error_word_ptr();
+  p.wait_ns = get_wait_limit_ns();
 
   // warps sharing one TMA box (and its shared-memory rows); the grid is counted in whole boxes
   constexpr int G = BwdBox<MODE, V, C, TMA>::kWarps;
@@ -1721,6 +1738,7 @@ int scan_fwd_dispatch(const FwdArgs& a) {
     q.nstreams = a.mode == MODE_ROW ? 1 : ((a.mode == MODE_AI || a.mode == MODE_RF) ? 4 : 3);
     q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;  // 32-step tiles: 1 lane per thread only
     plan = plan_scan(dev, q, tune);
+    if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;  // the tuning override admits no launch shape
   }
   const int V = plan.lanes;
 
@@ -1782,6 +1800,7 @@ int scan_bwd_dispatch(const BwdArgs& a) {
     q.nstreams = (a.mode == MODE_ROW ? 1 : ((a.mode == MODE_AI || a.mode == MODE_RF) ? 4 : 3)) + 1 + (a.g_vpost ? 1 : 0);
     q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : (C == 16 ? 2 : 1);
     plan = plan_scan(dev, q, tune_rf);
+    if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;  // the tuning override admits no launch shape
   }
   const int V = plan.lanes;
 
@@ -1841,6 +1860,7 @@ int scan_mod_fwd_dispatch(const FwdArgs& a) {
     q.modulated = a.mode == MODE_RFMOD ? 2 : 1;
     q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;
     plan = plan_scan(dev, q, tune);
+    if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;  // the tuning override admits no launch shape
   }
   const int V = plan.lanes;
 #define NSB_MFWD_CASE(MODE_, PACKED_, V_, C_)                                          \
@@ -1907,6 +1927,7 @@ int scan_res_fwd_dispatch(const FwdArgs& a) {
     q.nstreams = 2;
     q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;
     plan = plan_scan(dev, q, tune);
+    if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;  // the tuning override admits no launch shape
   }
   const int V = plan.lanes;
 #define NSB_RFWD_CASE(V_, C_)                                                          \
@@ -1940,6 +1961,7 @@ int scan_lin_fwd_dispatch(const FwdArgs& a) {
     q.nstreams = 2;
     q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;
     plan = plan_scan(dev, q, tune);
+    if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;  // the tuning override admits no launch shape
   }
   const int V = plan.lanes;
 #define NSB_LFWD_CASE(V_, C_)                                                          \
@@ -1973,6 +1995,7 @@ int scan_lin_bwd_dispatch(const BwdArgs& a) {
     q.nstreams = 3;
     q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 4 : 1;
     plan = plan_scan(dev, q, tune);
+    if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;  // the tuning override admits no launch shape
   }
   const int V = plan.lanes;
 #define NSB_LBWD_CASE(V_, C_)                                                          \
@@ -2021,6 +2044,7 @@ int scan_mod_bwd_dispatch(const BwdArgs& a) {
       if (tune.stages <= 0) tune.stages = 2;
     }
     plan = plan_scan(dev, q, tune);
+    if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;  // the tuning override admits no launch shape
   }
   const int V = plan.lanes;
 #define NSB_MBWD_CASE(MODE_, SURR_, V_, C_)                                            \

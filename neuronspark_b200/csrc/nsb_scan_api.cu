@@ -406,8 +406,9 @@ int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const vo
 int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const float* vth_row,
                                    const float* v_init, const void* frames_in, void* frames_out,
                                    float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
-                                   int ckpt_interval, void* stream) {
-  if (T < 0 || cols < 0 || T % 16 != 0 || !dtype_ok(dtype) || (ckpt_interval != 16 && ckpt_interval != 32))
+                                   int ckpt_interval, int rounding, void* stream) {
+  if (T < 0 || cols < 0 || T % 16 != 0 || !dtype_ok(dtype) || (ckpt_interval != 16 && ckpt_interval != 32) ||
+      (rounding != NSB_RESIDUAL_EAGER && rounding != NSB_RESIDUAL_COMPILED))
     return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
   if (!beta_row || !vth_row || !v_init || !v_last) return NSB_ERR_INVALID_ARG;
@@ -426,6 +427,7 @@ int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const f
   a.drive = u; a.extra = frames_in; a.beta_row = beta_row; a.vth_row = vth_row; a.v_init = v_init;
   a.spike = frames_out; a.ckpt = v_ckpt; a.vlast = v_last;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_ROWRES; a.tile = ckpt_interval;
+  a.residual_compiled = rounding == NSB_RESIDUAL_COMPILED;
   a.stream = static_cast<cudaStream_t>(stream);
   return run_res_fwd(a, dtype);
 }

@@ -7,6 +7,15 @@
     binary_encode_ste(x)                reference :208-241
 
 CUDA tensors only; K must be 16 (one frame per bit of an IEEE half).
+
+bf16 frames and the residual: the reference's ``binary_residual`` runs
+``torch.compile(_binary_residual_fwd)`` (:168-186), and on a GPU inductor's fused kernel keeps
+the decode in fp32 and rounds only the sum to bf16, whereas the same function called eagerly
+(or ``_binary_residual_naive``, :103-112) rounds every intermediate to bf16 - the two differ in
+about 1 % of the frames of real layer activations. ``binary_residual`` here follows the compiled
+behaviour, since that is what the reference's layers get; ``RESIDUAL_ROUNDING = "eager"`` (or
+the ``rounding`` argument of ``binary_residual_with``) selects the other. fp32 and fp16 frames
+are unaffected: all their intermediates are exact.
 """
 from __future__ import annotations
 
@@ -14,6 +23,20 @@ import torch
 
 from . import _lib
 from ._lib import NSBError
+
+
+#: "compiled" (default) or "eager": rounding of the residual on bf16 frames, see the module text.
+RESIDUAL_ROUNDING = "compiled"
+
+_ROUNDINGS = {"eager": _lib.RESIDUAL_EAGER, "compiled": _lib.RESIDUAL_COMPILED}
+
+
+def residual_rounding_code(rounding=None) -> int:
+    r = RESIDUAL_ROUNDING if rounding is None else rounding
+    try:
+        return _ROUNDINGS[r]
+    except KeyError:
+        raise NSBError(f"unknown residual rounding {r!r}; expected 'compiled' or 'eager'") from None
 
 
 def _check_k(K: int) -> None:
@@ -92,7 +115,7 @@ class _BinaryResidual(torch.autograd.Function):
     unchanged (straight-through), as the reference's class of the same name."""
 
     @staticmethod
-    def forward(ctx, spike_a, spike_b):
+    def forward(ctx, spike_a, spike_b, rounding=None):
         dev = _lib.require_cuda(spike_a, spike_b)
         if spike_a.shape != spike_b.shape or spike_a.dim() != 3 or spike_a.shape[0] % 16:
             raise NSBError("binary_residual expects two (T*16, B, D) tensors of equal shape")
@@ -106,16 +129,22 @@ class _BinaryResidual(torch.autograd.Function):
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().nsb_binary_residual(
                 _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), B, TK // 16, D, _lib.dtype_code(dt),
-                _lib.stream_ptr(dev)), "nsb_binary_residual")
+                residual_rounding_code(rounding), _lib.stream_ptr(dev)), "nsb_binary_residual")
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
-        return grad_output, grad_output
+        return grad_output, grad_output, None
 
 
 def binary_residual(spike_a: torch.Tensor, spike_b: torch.Tensor) -> torch.Tensor:
+    """Reference: atomic_ops/fp16_codec.py:189-205."""
     return _BinaryResidual.apply(spike_a, spike_b)
+
+
+def binary_residual_with(spike_a: torch.Tensor, spike_b: torch.Tensor, rounding: str) -> torch.Tensor:
+    """``binary_residual`` with the rounding for bf16 frames given explicitly: "compiled" or "eager"."""
+    return _BinaryResidual.apply(spike_a, spike_b, rounding)
 
 
 class _BinaryEncodeSTE(torch.autograd.Function):

@@ -35,7 +35,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, fp16_codec
 from ._lib import NSBError
 
 #: Steps per time tile = spacing of the fp32 state checkpoints kept for backward
@@ -646,7 +646,8 @@ class PLIFRowParamResidualScan(torch.autograd.Function):
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().nsb_plif_rowparam_residual_fwd(
                 _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(v0), _lib.ptr(fin), _lib.ptr(out),
-                _lib.ptr(ckpt), _lib.ptr(v_last), T, cols, _lib.dtype_code(dt), C, _lib.stream_ptr(dev)),
+                _lib.ptr(ckpt), _lib.ptr(v_last), T, cols, _lib.dtype_code(dt), C,
+                fp16_codec.residual_rounding_code(), _lib.stream_ptr(dev)),
                 "nsb_plif_rowparam_residual_fwd")
         if needs_grad:
             ctx.save_for_backward(beta32, vth32, u_c, ckpt)

@@ -374,12 +374,17 @@ def fp16_decode_bwd(frames, g_out):
     return g
 
 
-def binary_residual(fa, fb, bf16_intermediates=False):
+def binary_residual(fa, fb, bf16_intermediates=False, bf16_compiled=False):
+    """encode(decode(fa) + decode(fb)). For bf16 frames the reference has two behaviours:
+    ``bf16_intermediates`` = its ops run one by one (every intermediate rounded to bf16),
+    ``bf16_compiled`` = its torch.compile'd residual as a GPU evaluates it (decode in fp32, the
+    sum rounded to bf16). Neither flag = fp32 / fp16 frames (no intermediate rounds there)."""
     fa, fb = _f32(fa), _f32(fb)
     TK, B, D = fa.shape
     out = np.empty_like(fa)
+    mode = 2 if bf16_compiled else (1 if bf16_intermediates else 0)
     lib().orc_binary_residual(_p(fa), _p(fb), _p(out), _i64(B), _i64(TK // 16), _i64(D),
-                              ctypes.c_int(1 if bf16_intermediates else 0))
+                              ctypes.c_int(mode))
     return out
 
 

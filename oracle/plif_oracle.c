@@ -575,7 +575,14 @@ void orc_fp16_decode_bwd(const float *frames, const float *g_out,
 }
 
 /* Binary residual: encode(decode(a) + decode(b)), frames [T*16, B, D]
- * (atomic_ops/fp16_codec.py:115-164). */
+ * (atomic_ops/fp16_codec.py:115-164).
+ * mode 0: fp32 throughout (what fp32 and fp16 frames give: every intermediate is exact there).
+ * mode 1: bf16 frames evaluated op by op, as eager PyTorch does (_binary_residual_naive, or
+ *         _binary_residual_fwd called directly): mantissa sum, 1+m, each decoded value and their
+ *         sum are rounded to bf16.
+ * mode 2: bf16 frames through the reference's torch.compile'd residual (:168-170), observed on a
+ *         B200 with torch 2.11: the decode stays in fp32 inside the fused kernel and only the
+ *         sum, which is materialised as a bf16 tensor between two kernels, is rounded to bf16. */
 void orc_binary_residual(const float *fa, const float *fb, float *out,
                          int64_t B, int64_t S, int64_t D, int mode) {
 #pragma omp parallel for collapse(2) schedule(static)
@@ -606,7 +613,7 @@ void orc_binary_residual(const float *fa, const float *fb, float *out,
           if (mode == 1) val[w] = round_bf16(val[w]);
         }
         float sum = val[0] + val[1];
-        if (mode == 1) sum = round_bf16(sum);
+        if (mode == 1 || mode == 2) sum = round_bf16(sum);
         uint16_t h = f32_to_f16_bits(sum);
         for (int k = 0; k < 16; ++k)
           out[((s * 16 + k) * B + b) * D + d] = (float)((h >> (15 - k)) & 1u);

@@ -134,7 +134,7 @@ def _check_forward_calls(calls, dtype):
             assert np.array_equal(f32(out[0]), s), c["label"]
             assert np.array_equal(f32(out[1]), f32(torch.from_numpy(vl).to(out[1].dtype)))
         elif kind == "binary_residual":
-            want = orc.binary_residual(f32(a[0]), f32(a[1]), bf16_intermediates=lowp)
+            want = orc.binary_residual(f32(a[0]), f32(a[1]), bf16_compiled=lowp)
             assert np.array_equal(f32(out), want), c["label"]
         elif kind == "fp16_encode":
             assert np.array_equal(f32(out), orc.fp16_encode(f32(a[0])))
@@ -217,7 +217,7 @@ def test_state_carried_across_calls_equals_one_long_forward(reference):
     thresholds, hence a bound on the differing frames rather than equality. Without the carried state
     a quarter of the frames differ."""
     ao, model = reference
-    m = tiny_model(model, torch.bfloat16)
+    m = tiny_model(model, torch.float32)  # a bf16 model rounds the carried V / W to bf16 between calls
     x = torch.randint(0, 256, (2, 12), device=DEV, generator=torch.Generator(device=DEV).manual_seed(5))
     with torch.no_grad():
         frames = m.encode(x)

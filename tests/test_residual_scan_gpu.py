@@ -53,11 +53,25 @@ def test_fused_equals_oracle_and_unfused(dtype, shape):
     assert out.dtype == dtype and torch.equal(out, ref_out) and torch.equal(v_last, ref_v)
     assert 0.05 < float(spikes.float().mean()) < 0.9
     so, _, vlo = orc.plif_rowparam_fwd(f32(beta_row), f32(u), f32(vth_row), f32(v0), want_vpost=False)
-    want = orc.binary_residual(so, f32(fin), bf16_intermediates=(dtype == torch.bfloat16))
+    want = orc.binary_residual(so, f32(fin), bf16_compiled=(dtype == torch.bfloat16))
     if dtype == torch.float16:  # the reference adds the two decoded values in half precision
         want = f32(codec.binary_residual(torch.as_tensor(so, device=DEV).half(), fin))
     assert np.array_equal(f32(out), want)
     assert np.array_equal(f32(v_last), vlo)
+
+
+def test_eager_rounding_of_bf16_frames(monkeypatch):
+    """The other rounding of the residual on bf16 frames (every intermediate rounded to bf16, as the
+    reference's ops give when run one by one) is selectable and differs from the default."""
+    beta_row, u, vth_row, v0, fin = inputs(6, 2, 520, torch.bfloat16, 13)
+    fin = (torch.rand_like(fin.float()) < 0.5).to(torch.bfloat16)  # full 10-bit mantissas, as layers produce
+    default, _ = ps.plif_rowparam_residual_forward(beta_row, u, vth_row, v0, fin, 4.0)
+    monkeypatch.setattr(codec, "RESIDUAL_ROUNDING", "eager")
+    out, _ = ps.plif_rowparam_residual_forward(beta_row, u, vth_row, v0, fin, 4.0)
+    so, _, _ = orc.plif_rowparam_fwd(f32(beta_row), f32(u), f32(vth_row), f32(v0), want_vpost=False)
+    assert np.array_equal(f32(out), orc.binary_residual(so, f32(fin), bf16_intermediates=True))
+    assert np.array_equal(f32(default), orc.binary_residual(so, f32(fin), bf16_compiled=True))
+    assert not torch.equal(out, default)
 
 
 @pytest.mark.parametrize("tile", [16, 32])
