@@ -275,6 +275,55 @@ class ClockSampler:
         return out
 
 
+# ------------------------------------------------------ host memory placement
+
+
+def host_mem_available():
+    """MemAvailable of this machine in bytes (None if it cannot be read)."""
+    try:
+        for line in Path("/proc/meminfo").read_text().splitlines():
+            if line.startswith("MemAvailable:"):
+                return int(line.split()[1]) * 1024
+    except OSError:
+        pass
+    return None
+
+
+def bind_host_memory_near_gpu(gpu_index):
+    """Makes this process prefer the NUMA node the GPU hangs off, for the pinned buffers allocated
+    afterwards (set_mempolicy(MPOL_PREFERRED) + CPU affinity to that node's cores; first touch then
+    lands there). With one process per GPU each rank pins its gigabytes next to its own GPU instead
+    of all ranks crowding one node. Returns a record of what was found and done; a machine that
+    shows a single node (or none) is left alone."""
+    import torch
+    info = {"gpu_numa_node": None, "nodes": None, "bound": False}
+    try:
+        props = torch.cuda.get_device_properties(gpu_index)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        node = int(Path(f"/sys/bus/pci/devices/{bdf}/numa_node").read_text())
+        nodes = sorted(int(p.name[4:]) for p in Path("/sys/devices/system/node").glob("node[0-9]*"))
+        info.update(gpu_numa_node=node, nodes=len(nodes), pci=bdf)
+        if node < 0 or len(nodes) < 2:
+            info["note"] = "single NUMA node visible (or none reported for the GPU): nothing to bind"
+            return info
+        cpus = set()
+        for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        libc = ctypes.CDLL(None, use_errno=True)
+        mask = ctypes.c_ulong(1 << node)
+        MPOL_PREFERRED, SYS_set_mempolicy = 1, 238  # x86_64
+        rc = libc.syscall(SYS_set_mempolicy, MPOL_PREFERRED, ctypes.byref(mask), ctypes.c_ulong(node + 2))
+        info["bound"] = rc == 0
+        info["cpus"] = len(allowed)
+    except Exception as e:  # noqa: BLE001 - placement is an optimisation, never a failure
+        info["note"] = f"{type(e).__name__}: {e}"
+    return info
+
+
 # ---------------------------------------------------------------- CPU baseline
 
 
@@ -329,8 +378,44 @@ def cpu_baseline(B, T, D, budget_s=12.0):
                       "lanes are independent so work scales linearly in B"}
 
 
+def reference_loop_forward(B, T, D, steps=3):
+    """The reference's own sequential CPU path, forward only, timed on a batch slice:
+    ``rf_plif_parallel_forward`` with omega = 0 (its CPU branch is a Python time loop over torch ops,
+    atomic_ops/parallel_scan.py:1655-1683; with omega = 0 it is the first-order scan) on u = gain*cur
+    formed by torch as the reference's callers do, all host threads, loaded by path from the copy
+    that oracle/make_ref.py stages. Forward only: torch autograd through that loop costs O(T^2)
+    (every ``beta[k]`` index node allocates a full [T, ...] gradient), minutes per step at T = 8192,
+    so the forward+backward CPU arm is the C port. Returns None when the staged copy is absent."""
+    ref_file = ROOT / "oracle" / "_ref" / "atomic_ops" / "parallel_scan.py"
+    if not ref_file.exists():
+        return None
+    import importlib.util
+    import torch
+    spec = importlib.util.spec_from_file_location("ref_parallel_scan_cpu", ref_file)
+    ref_ps = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_ps)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    beta, cur, gain, vth, v0, _ = (torch.from_numpy(a) for a in cpu_sample(B, T, D, 99, 1))
+    zeros, w0 = torch.zeros_like(beta), torch.zeros_like(v0)
+
+    def one():
+        with torch.no_grad():
+            return ref_ps.rf_plif_parallel_forward(beta, zeros, gain * cur, vth, v0, w0, None)[0]
+
+    one()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one()
+    el = time.perf_counter() - t0
+    return {"value": steps * T * D / el, "unit": UNIT + " (forward only)", "cores": cores, "kind": "reference",
+            "sample": f"batch slice B=1 of B={B} (T={T}, D={D}), forward only, the reference's Python time loop "
+                      f"on CPU, {steps} repeats in {el:.1f} s"}
+
+
 def run_reference(args):
-    """The reference arm: the CPU port of the reference's sequential path."""
+    """The reference arm: the C port of the reference's sequential CPU path (forward + backward), with
+    the reference's own Python loop (forward only) beside it when the staged copy is present."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -359,6 +444,9 @@ def run_reference(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    loop = reference_loop_forward(B, T, D)
+    if loop is not None:
+        line["cpu_reference_loop"] = loop
     print(json.dumps(line), flush=True)
 
 
@@ -947,48 +1035,114 @@ def main():
     else:
         allchk = [chk]
     finite = all(bool(torch.isfinite(c).all()) for c in allchk)
+    step_meta = {"C": step.C, "fwd": step.launch_fwd, "bwd": step.launch_bwd}
 
-    # ---- end-to-end through the public API with host buffers
+    # ---- end-to-end through the public API with host buffers: every step copies its inputs in
+    # from pinned host memory and ALL of its results back out (spikes, the four gradient tensors,
+    # V_last, grad V0). The batch lives on the host as micro-batches (columns are independent, so
+    # a caller is free to feed the scan any slice of the batch): copy-in of micro-batch i+1,
+    # forward+backward of i and copy-out of i-1 overlap on three streams.
     e2e = None
     if not args.no_e2e:
-        host = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True).copy_(v)
-                for k, v in inp.items()}
-        dev_in = {k: torch.empty_like(v) for k, v in inp.items()}
-        h2d = sum(v.numel() * v.element_size() for v in host.values())
-        res_host = torch.empty((2, B, D), dtype=torch.float32, pin_memory=True)
+        del step  # frees the device-resident outputs of the kernel-only leg
+        torch.cuda.empty_cache()
+        numa = bind_host_memory_near_gpu(local)
+        n_mb = 8 if B % 8 == 0 else (4 if B % 4 == 0 else 1)
+        Bm = B // n_mb
+        names_in = ("beta", "cur", "gain", "vth", "g_spike")
+        names_out = ("spike", "g_beta", "g_cur", "g_gain", "g_vth")
+        # Pinned memory is bounded by what the host has: every rank of this box may take its share of
+        # 40 % of the available RAM. If that holds fewer than n_mb micro-batches, the host buffers are
+        # reused round-robin - the bytes copied per step stay the same, only their source and
+        # destination pages repeat.
+        per_mb = 10 * T * Bm * D * 2 + 3 * Bm * D * 4
+        avail = host_mem_available()
+        local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
+        n_host = n_mb if avail is None else max(1, min(n_mb, int(0.4 * avail / local_world // per_mb)))
+        host_in = [{k: torch.empty((T, Bm, D), dtype=torch.bfloat16, pin_memory=True).copy_(
+            inp[k][:, i * Bm:(i + 1) * Bm]) for k in names_in} for i in range(n_host)]
+        host_v0 = [torch.zeros((Bm, D), dtype=torch.float32, pin_memory=True) for _ in range(n_host)]
+        host_out = [{k: torch.empty((T, Bm, D), dtype=torch.bfloat16, pin_memory=True) for k in names_out}
+                    for _ in range(n_host)]
+        host_small = [torch.empty((2, Bm, D), dtype=torch.float32, pin_memory=True) for _ in range(n_host)]
+        del inp
+        torch.cuda.empty_cache()
+        dev_in = [{k: torch.empty((T, Bm, D), dtype=torch.bfloat16, device=dev) for k in names_in}
+                  for _ in range(2)]
+        dev_v0 = [torch.empty((Bm, D), dtype=torch.float32, device=dev) for _ in range(2)]
+        h2d = n_mb * (sum(v.numel() * v.element_size() for v in host_in[0].values()) + host_v0[0].numel() * 4)
+        d2h = n_mb * (sum(v.numel() * v.element_size() for v in host_out[0].values()) + host_small[0].numel() * 4)
+        s_in, s_cmp, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
 
         def e2e_step():
-            for k in dev_in:
-                dev_in[k].copy_(host[k], non_blocking=True)
-            leaves = [dev_in[k].requires_grad_() for k in ("beta", "cur", "gain", "vth", "v0")]
-            spike, v_last = ps.plif_selective_scan_ai(*leaves, alpha=ALPHA, surrogate="atan")
-            spike.backward(dev_in["g_spike"])
-            res_host[0].copy_(v_last, non_blocking=True)
-            res_host[1].copy_(leaves[4].grad, non_blocking=True)
-            for t in leaves:
-                t.grad = None
-                t.requires_grad_(False)
+            keep = []  # tensors read by another stream than the one that made them stay referenced
+            cmp_done = [None, None]
+            for i in range(n_mb):
+                slot = i % 2
+                with torch.cuda.stream(s_in):
+                    if cmp_done[slot] is not None:
+                        s_in.wait_event(cmp_done[slot])  # micro-batch i-2 is done with this buffer
+                    for k in names_in:
+                        dev_in[slot][k].copy_(host_in[i % n_host][k], non_blocking=True)
+                    dev_v0[slot].copy_(host_v0[i % n_host], non_blocking=True)
+                    ready = torch.cuda.Event()
+                    ready.record(s_in)
+                with torch.cuda.stream(s_cmp):
+                    s_cmp.wait_event(ready)
+                    d = dev_in[slot]
+                    leaves = [d[k].requires_grad_() for k in ("beta", "cur", "gain", "vth")]
+                    leaves.append(dev_v0[slot].requires_grad_())
+                    spike, v_last = ps.plif_selective_scan_ai(*leaves, alpha=ALPHA, surrogate="atan")
+                    spike.backward(d["g_spike"])
+                    grads = [t.grad for t in leaves]
+                    for t in leaves:
+                        t.grad = None
+                        t.requires_grad_(False)
+                    done = torch.cuda.Event()
+                    done.record(s_cmp)
+                    cmp_done[slot] = done
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(done)
+                    for k, t in zip(names_out, [spike.detach()] + grads[:4]):
+                        host_out[i % n_host][k].copy_(t, non_blocking=True)
+                    host_small[i % n_host][0].copy_(v_last, non_blocking=True)
+                    host_small[i % n_host][1].copy_(grads[4], non_blocking=True)
+                keep.append((spike, v_last, grads))
+            return keep
+
+        def run_steps(n):
+            s_in.wait_stream(torch.cuda.current_stream(dev))
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(s_in)
+            keep = []
+            for _ in range(n):
+                keep = e2e_step()  # the previous step's tensors stay alive until this one is queued
+                s_in.wait_stream(s_out)  # next step's inputs may not overtake this step's read-back
+            t1.record(s_out)
+            torch.cuda.synchronize()
+            del keep
+            return t0.elapsed_time(t1) / n
 
         ke = min(K, 4)
-        e2e_step()
+        run_steps(1)
         barrier()
-        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s2.record()
-        for _ in range(ke):
-            e2e_step()
-        e2.record()
+        ms_e2e = run_steps(ke)
         barrier()
-        ms_e2e = s2.elapsed_time(e2) / ke
         if world > 1:
             t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms_e2e = float(t[0])
+        e2e_ok = bool(torch.isfinite(host_small[0]).all()) and 0.0 < float(host_out[-1]["spike"].float().mean()) < 1.0
         e2e = {"value": world * neuron_steps / (ms_e2e * 1e-3), "unit": UNIT,
-               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(res_host.numel() * 4),
-               "ms_per_step": ms_e2e, "steps": ke,
-               "api": "neuronspark_b200.parallel_scan.plif_selective_scan_ai + autograd backward, "
-                      "inputs copied from pinned host memory every step, V_last and grad V0 read back"}
-        del host, dev_in
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "ms_per_step": ms_e2e, "steps": ke, "micro_batches": n_mb, "host_buffer_sets": n_host,
+               "results_valid": e2e_ok,
+               "host_memory": numa,
+               "api": "neuronspark_b200.parallel_scan.plif_selective_scan_ai + autograd backward per micro-batch "
+                      f"of {Bm} samples; every step copies all inputs in from pinned host memory and all results "
+                      "(spikes, four gradient tensors, V_last, grad V0) back out; copy-in, compute and copy-out "
+                      "overlap across micro-batches"}
+        del host_in, host_out, dev_in
 
     if rank == 0:
         peak, peak_src = hbm_peak()
@@ -1009,8 +1163,8 @@ def main():
                              "beta/omega/u/V_th/V0/W0"),
                 "parallelism": f"batch-sharded x{world}, no collective in the timed region",
                 "l2": "inputs (16 GB per GPU) are far larger than L2; no flush needed",
-                "storage_dtype": "bf16", "ckpt_interval": step.C,
-                "launch_fwd": step.launch_fwd, "launch_bwd": step.launch_bwd,
+                "storage_dtype": "bf16", "ckpt_interval": step_meta["C"],
+                "launch_fwd": step_meta["fwd"], "launch_bwd": step_meta["bwd"],
             },
             "roofline": {
                 "bound": "hbm", "kernel": "plif_bwd_kernel", "achieved": bwd_ach, "peak": peak,
@@ -1037,6 +1191,9 @@ def main():
             line["e2e"] = e2e
         if world == 1 and not args.no_cpu and not is_rf:
             line["cpu_baseline"] = cpu_baseline(B, T, D)
+            loop = reference_loop_forward(B, T, D)
+            if loop is not None:  # the reference's own Python time loop on the same slice, for scale
+                line["cpu_reference_loop"] = loop
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -27,6 +27,7 @@ from __future__ import annotations
 
 import copy
 import importlib
+import math
 import sys
 import types
 from pathlib import Path
@@ -95,6 +96,34 @@ class Sigmoid(nn.Module):
         return f"alpha={self.alpha}, spiking={self.spiking}"
 
 
+class _ATanSurrogateFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, alpha):
+        if x.requires_grad:
+            ctx.save_for_backward(x)
+            ctx.alpha = alpha
+        return (x >= 0).to(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        return g * (ctx.alpha / 2) / (1 + (math.pi / 2 * ctx.alpha * x) ** 2), None
+
+
+class ATan(nn.Module):
+    """Heaviside step whose gradient is that of ``atan(pi/2*alpha*x)/pi + 1/2``. The reference never
+    names it; BASELINE's headline configuration does, and the reference's CPU scan accepts any
+    surrogate callable (atomic_ops/parallel_scan.py:1667-1677)."""
+
+    def __init__(self, alpha: float = 2.0, spiking: bool = True):
+        super().__init__()
+        self.alpha = alpha
+        self.spiking = spiking
+
+    def forward(self, x):
+        return _ATanSurrogateFn.apply(x, self.alpha)
+
+
 class BaseNode(MemoryModule):
     def __init__(self, v_threshold: float = 1.0, v_reset=0.0, surrogate_function=None,
                  detach_reset: bool = False, step_mode: str = "s", backend: str = "torch",
@@ -149,7 +178,7 @@ def install_spikingjelly_shim(force: bool = False) -> bool:
     for name, members in (("base", {"MemoryModule": MemoryModule}),
                           ("neuron", {"BaseNode": BaseNode}),
                           ("layer", {"Linear": Linear}),
-                          ("surrogate", {"Sigmoid": Sigmoid}),
+                          ("surrogate", {"Sigmoid": Sigmoid, "ATan": ATan}),
                           ("functional", {"reset_net": reset_net})):
         m = types.ModuleType(f"spikingjelly.activation_based.{name}")
         for k, v in members.items():
