@@ -405,6 +405,48 @@ int nsb_plif_rf_bwd_dalpha(const void* beta, const void* omega, const void* u, c
                            void* stream);
 
 /*
+ * Spikes packed in time: the 16 frames of one token and column as one uint16, the IEEE half bit
+ * pattern they spell (frame 0 = sign = bit 15), in [S, B, D] (S = T/16) - 2 bytes per value
+ * where the reference's dense frames (atomic_ops/fp16_codec.py:17-46) take 16 elements. The
+ * reference has no packed form: it moves {0,1} frames in the activation dtype between layers
+ * (atomic_ops/snn_block.py:281-285, atomic_ops/snn_ffn.py:188-195, model.py:155-157). These
+ * entry points keep the reference's arithmetic and change only the storage:
+ *
+ * nsb_frames_pack / nsb_frames_unpack   dense frames [S*16,B,D] in `dtype` <-> patterns.
+ * nsb_fp16_decode_packed_fwd            fp16_decode (:49-98) from patterns: values [B,S,D] in
+ *                                       `dtype`, with the roundings that dtype's frames give.
+ * nsb_fp16_decode_packed_bwd            its autograd: g_values [B,S,D] -> the 16 frame gradients of
+ *                                       every value, dense [S*16,B,D] (what a scan's backward takes
+ *                                       as g_spike).
+ * nsb_binary_residual_packed            binary_residual (:115-197) on two pattern arrays of n values;
+ *                                       `frame_dtype` names the frame dtype whose roundings apply,
+ *                                       `rounding` is NSB_RESIDUAL_*.
+ * nsb_plif_rowparam_pattern_fwd         the row-parameter scan (plif_rowparam_forward_recompute,
+ *                                       atomic_ops/parallel_scan.py:1499-1535) writing its spikes as
+ *                                       patterns [T/16, cols]; with patterns_in (may be NULL) the
+ *                                       binary residual with that array is applied first, as
+ *                                       nsb_plif_rowparam_residual_fwd does on frames. u is [T, cols]
+ *                                       in `dtype`, T a multiple of 16, ckpt_interval 16 or 32; the
+ *                                       backward is nsb_plif_rowparam_bwd on dense frame gradients.
+ */
+int nsb_frames_pack(const void* frames, uint16_t* patterns, int64_t B, int64_t S, int64_t D, int dtype,
+                    void* stream);
+int nsb_frames_unpack(const uint16_t* patterns, void* frames, int64_t B, int64_t S, int64_t D, int dtype,
+                      void* stream);
+int nsb_fp16_decode_packed_fwd(const uint16_t* patterns, void* values, int64_t B, int64_t S, int64_t D,
+                               int dtype, void* stream);
+int nsb_fp16_decode_packed_bwd(const uint16_t* patterns, const void* g_values, void* g_frames,
+                               int64_t B, int64_t S, int64_t D, int dtype, void* stream);
+int nsb_binary_residual_packed(const uint16_t* patterns_a, const uint16_t* patterns_b,
+                               uint16_t* patterns_out, int64_t n, int frame_dtype, int rounding,
+                               void* stream);
+int nsb_plif_rowparam_pattern_fwd(const float* beta_row, const void* u, const float* vth_row,
+                                  const float* v_init, const uint16_t* patterns_in,
+                                  uint16_t* patterns_out, float* v_ckpt, float* v_last, int64_t T,
+                                  int64_t cols, int dtype, int ckpt_interval, int frame_dtype,
+                                  int rounding, void* stream);
+
+/*
  * Row-parameter scan followed by the binary residual, in one pass. Replaces the
  * pair that ends SNNBlock.forward_parallel and SNNFFN.forward_parallel
  * (atomic_ops/snn_block.py:281-285, atomic_ops/snn_ffn.py:188-195):

@@ -82,6 +82,40 @@ def main():
             if args.only in name:
                 report(name, shape, _time(fn, args.iters, flush), nbytes)
 
+    # spikes packed in time (one int16 pattern per token and channel) beside the dense kernels above
+    if args.only in "packed":
+        for shape in [(8, 512, 768), (32, 512, 768)]:
+            B, S, D = shape
+            n = B * S * D
+            x = torch.randn(B, S, D, device=dev).to(dt)
+            pa = codec.pack_frames(codec.fp16_encode(x))
+            pb = codec.pack_frames(codec.fp16_encode(-0.5 * x))
+            gv = torch.randn(B, S, D, device=dev).to(dt)
+            cases = {
+                "packed: fp16_decode_packed": (lambda: codec.fp16_decode_packed(pa, dt), n * (2 + es)),
+                "packed: fp16_decode_packed_backward": (lambda: codec.fp16_decode_packed_backward(pa, gv), n * (2 + 17 * es)),
+                "packed: binary_residual_packed": (lambda: codec.binary_residual_packed(pa, pb, dt), n * 6),
+                "packed: unpack_frames": (lambda: codec.unpack_frames(pa, dt), n * (2 + 16 * es)),
+                "packed: pack_frames": (lambda fr=codec.unpack_frames(pa, dt): codec.pack_frames(fr), n * (2 + 16 * es)),
+            }
+            for name, (fn, nbytes) in cases.items():
+                report(name, shape, _time(fn, args.iters, flush), nbytes)
+            # the output neuron of a block: scan + residual, dense frames against packed patterns
+            T = S * 16
+            g = torch.Generator(device=dev).manual_seed(3)
+            bd = torch.sigmoid(2 + 0.5 * torch.randn(D, generator=g, device=dev)).expand(B, D).contiguous()
+            td = torch.full((B, D), 0.4, device=dev)
+            u = (0.5 * torch.randn(T, B, D, generator=g, device=dev)).to(dt)
+            v0 = torch.zeros(B, D, device=dev)
+            fin = codec.unpack_frames(pb.reshape(S, B, D) if pb.shape == (S, B, D) else pb, dt)
+            with torch.no_grad():
+                report("packed: row-param scan + residual, dense frames in/out", (T, B, D),
+                       _time(lambda: ps.plif_rowparam_residual_forward(bd, u, td, v0, fin, 4.0), args.iters, flush),
+                       T * B * D * 3 * es)
+                report("packed: row-param scan + residual, patterns in/out", (T, B, D),
+                       _time(lambda: ps.plif_rowparam_forward_patterns(bd, u, td, v0, patterns_in=pb), args.iters, flush),
+                       T * B * D * es + 2 * n * 2)
+
     for rows, D in [(4096, 768), (65536, 768), (8192, 6144)]:
         x = torch.randn(rows, D, device=dev).to(dt)
         gain = 1 + 0.1 * torch.randn(D, device=dev)

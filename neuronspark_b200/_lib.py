@@ -57,6 +57,14 @@ _SIGNATURES = {
     "nsb_plif_rf_bwd_dalpha": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
                                                           c_void_p]),
     "nsb_plif_rowparam_residual_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
+    "nsb_frames_pack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "nsb_frames_unpack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "nsb_fp16_decode_packed_fwd": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "nsb_fp16_decode_packed_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                           c_void_p]),
+    "nsb_binary_residual_packed": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "nsb_plif_rowparam_pattern_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_int,
+                                                               c_void_p]),
     "nsb_linear_recurrence_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_linear_recurrence_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_moe_combine_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_int, c_int, c_void_p]),

@@ -108,5 +108,22 @@ __device__ __forceinline__ uint32_t residual_half_bits(const float (&a)[16], con
   return half_bits_clamped(sum);
 }
 
+// The 16 frames a half bit pattern stands for, as reals in {0,1} (frame 0 = sign = bit 15).
+__device__ __forceinline__ void pattern_to_bits(uint32_t pat, float (&bit)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) bit[i] = ((pat >> (15 - i)) & 1u) ? 1.0f : 0.0f;
+}
+
+// residual_half_bits on two patterns, with the roundings of frames stored in `frame_dtype`
+// (a run-time value here: packed patterns have no element type of their own).
+__device__ __forceinline__ uint32_t residual_of_patterns(uint32_t pa, uint32_t pb, int frame_dtype, bool compiled) {
+  float a[16], b[16];
+  pattern_to_bits(pa, a);
+  pattern_to_bits(pb, b);
+  if (frame_dtype == NSB_BF16) return residual_half_bits<NSB_BF16>(a, b, compiled);
+  if (frame_dtype == NSB_F16) return residual_half_bits<NSB_F16>(a, b, compiled);
+  return residual_half_bits<NSB_F32>(a, b, compiled);
+}
+
 }  // namespace codec
 }  // namespace nsb

@@ -75,6 +75,31 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
   const int sms = std::max(1, d.sm_count);
   const int reserved = d.reserved_smem_per_cta > 0 ? d.reserved_smem_per_cta : 1024;
   const int ntiles = (int)((q.T + q.tile - 1) / q.tile);
+  // Plain forward scans over many columns (a full chip's worth of 4-lane warps and more): measured
+  // over 196 K .. 6.3 M columns the wave model below misjudges them (it once chose 7-warp CTAs for
+  // 786 K columns: 0.87 of the HBM peak where 2- and 4-warp CTAs reach 0.98), while one shape is
+  // within 2 % of the best everywhere: long scans, 4 lanes x 4 warps x 2 stages; scans of a few
+  // tiles (per-token decoding), where CTA start-up dominates, 1- or 2-warp CTAs with 4 lanes per
+  // thread from 1.5 M columns on and 2 below.
+  if (!q.backward && !q.modulated && q.stash == 0 && q.tile == 8 && q.max_lanes >= 4 && q.cols >= 196608 &&
+      q.nstreams >= 3 &&
+      tune.warps_per_cta <= 0 && tune.stages <= 0 && tune.lanes_per_thread <= 0) {
+    const bool few_tiles = ntiles <= 8;
+    const int lanes = (few_tiles && q.cols < 1500000) ? 2 : 4;
+    const int wpc = few_tiles ? (lanes == 4 ? 1 : 2) : 4;
+    const size_t stage_bytes = (size_t)q.tile * 32 * lanes * q.elem_size * q.nstreams;
+    const size_t smem = (size_t)wpc * 2 * (stage_bytes + 8) + 256;
+    if (smem + reserved <= (size_t)d.smem_per_sm / 2) {
+      const long long nwarps = (q.cols + 32LL * lanes - 1) / (32LL * lanes);
+      best.lanes = lanes;
+      best.wpc = wpc;
+      best.stages = 2;
+      best.grid = (int)((nwarps + wpc - 1) / wpc);
+      best.smem = smem;
+      best.cost = 0.0;
+      return best;
+    }
+  }
   // Calibration constants (B200): HBM bytes per microsecond, SM clock in cycles per
   // microsecond, time from CTA start until its first tile has landed.
   const double hbm_bytes_per_us = 6.5e6, clk_per_us = 1.9e3, t_start_us = 4.0;

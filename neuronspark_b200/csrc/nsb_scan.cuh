@@ -39,13 +39,18 @@ namespace nsb {
 // MODE_ROWRES (forward only) is MODE_ROW followed by the binary residual of the FP16 codec: every 16
 // steps the column's spikes are one half bit pattern; it is decoded, added to the value decoded from
 // the 16 frames of a second input stream, re-encoded, and those frames are the output.
+// MODE_ROWPAT (forward only) is MODE_ROW whose output is PACKED IN TIME: the 16 spikes of a token
+// and column leave as one uint16 - the IEEE half bit pattern they spell, frame 0 = sign - in a
+// [T/16, cols] array, 2 bytes per value where dense frames take 16 elements. With a second
+// pattern array given, the binary residual is applied to the two patterns first (as MODE_ROWRES
+// does on frames). It streams the drive only.
 // MODE_RF is the second-order resonate-and-fire scan: it streams beta, u, omega, v_th
 // (omega in the slot the gain*cur form uses for the gain) and carries two states, V and W.
 enum { MODE_U = 0, MODE_AI = 1, MODE_ROW = 2, MODE_RF = 3, MODE_MOD = 4, MODE_RFMOD = 5, MODE_ROWRES = 6, MODE_LIN = 7,
        // forward-only variants of MODE_MOD / MODE_RFMOD that also accumulate the moments of u = alpha*I (for
        // the adaptive surrogate slope). Separate kernels: compiled into the same kernel, as a run-time or a
        // per-tile choice, the extra accumulators cost 25-85 registers and a third of the resident warps.
-       MODE_MODS = 8, MODE_RFMODS = 9 };
+       MODE_MODS = 8, MODE_RFMODS = 9, MODE_ROWPAT = 10 };
 
 struct FwdArgs {
   const void* beta = nullptr;   // streams ([T, cols], stream dtype)
@@ -77,6 +82,9 @@ struct FwdArgs {
   int mode = MODE_U;
   int tile = 8;  // C
   int residual_compiled = 0;  // MODE_ROWRES, bf16 frames: rounding of the residual (NSB_RESIDUAL_*)
+  const uint16_t* pat_in = nullptr;  // MODE_ROWPAT: optional [T/16, cols] patterns to add
+  uint16_t* pat_out = nullptr;       // MODE_ROWPAT: [T/16, cols] patterns out
+  int frame_dtype = NSB_F32;         // MODE_ROWPAT: the frame dtype whose residual roundings apply
   cudaStream_t stream = nullptr;
 };
 
@@ -125,6 +133,9 @@ int scan_bwd_f16(const BwdArgs& a);
 int scan_mod_fwd_f32(const FwdArgs& a);
 int scan_mod_fwd_bf16(const FwdArgs& a);
 int scan_mod_fwd_f16(const FwdArgs& a);
+int scan_pat_fwd_f32(const FwdArgs& a);  // MODE_ROWPAT, same translation units
+int scan_pat_fwd_bf16(const FwdArgs& a);
+int scan_pat_fwd_f16(const FwdArgs& a);
 int scan_res_fwd_f32(const FwdArgs& a);  // MODE_ROWRES, same translation units
 int scan_res_fwd_bf16(const FwdArgs& a);
 int scan_res_fwd_f16(const FwdArgs& a);
@@ -344,6 +355,9 @@ struct FwdParams {
   uint32_t* err;
   unsigned long long wait_ns;  // limit of the bounded barrier waits
   int residual_compiled;
+  const uint16_t* pat_in;
+  uint16_t* pat_out;
+  int frame_dtype;
 };
 
 template <int MODE_>
@@ -352,9 +366,9 @@ struct ModeTraits {
   static constexpr int MODE = MODE_ == MODE_MODS ? MODE_MOD : (MODE_ == MODE_RFMODS ? MODE_RFMOD : MODE_);
   static constexpr bool kSecond = MODE == MODE_RF || MODE == MODE_RFMOD;  // carries the second state W
   static constexpr bool kMod = MODE == MODE_MOD || MODE == MODE_RFMOD;    // modulation fused into the loads
-  static constexpr bool kRow = MODE == MODE_ROW || MODE == MODE_ROWRES;  // per-column beta / v_th
+  static constexpr bool kRow = MODE == MODE_ROW || MODE == MODE_ROWRES || MODE == MODE_ROWPAT;  // per-column beta / v_th
   static constexpr int kFwdStreams =
-      MODE == MODE_ROW ? 1 : ((MODE == MODE_ROWRES || MODE == MODE_LIN) ? 2 : (MODE == MODE_RFMOD ? 5 : ((MODE == MODE_AI || MODE == MODE_RF || MODE == MODE_MOD) ? 4 : 3)));
+      (MODE == MODE_ROW || MODE == MODE_ROWPAT) ? 1 : ((MODE == MODE_ROWRES || MODE == MODE_LIN) ? 2 : (MODE == MODE_RFMOD ? 5 : ((MODE == MODE_AI || MODE == MODE_RF || MODE == MODE_MOD) ? 4 : 3)));
   // index of each role inside the stage / pointer table (roles that a mode
   // does not stream alias slot 0 and are never read)
   static constexpr int kBeta = 0;
@@ -441,6 +455,8 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
   // Dense spikes leave through shared memory + TMA only in the kernels built for them; a
   // bit-packing kernel that is also asked for dense spikes writes them from registers.
   constexpr bool DENSE_TMA = VEC && !PACKED;
+  // MODE_ROWPAT is built with PACKED = true (no dense output path) but packs in time, not by ballot
+  constexpr bool BALLOT = PACKED && MODE != MODE_ROWPAT;
   // Bit packing: a 32-column word belongs to the 32/V lanes that own those columns.
   constexpr int G = 32 / V;
   constexpr int NSLOT = (C + G - 1) / G;
@@ -547,6 +563,28 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
   const bool any_direct = p.vpost != nullptr || (MT::kSecond && p.w_out != nullptr) ||
                           (!DENSE_TMA && p.spike != nullptr);
 
+  // MODE_ROWPAT with a residual: the patterns to add to the tokens of the current tile and of the
+  // next one. They come straight from global memory (2 bytes per token and column), requested a
+  // whole tile ahead so that the serial scan never waits for them.
+  constexpr int TOK = (MODE == MODE_ROWPAT) ? (C / 16 > 0 ? C / 16 : 1) : 1;
+  Vec<uint16_t, V> pin_cur[TOK] = {}, pin_nxt[TOK] = {};
+  auto load_patterns = [&](int tile_idx, Vec<uint16_t, V> (&dst)[TOK]) {
+    if constexpr (MODE == MODE_ROWPAT) {
+#pragma unroll
+      for (int q = 0; q < TOK; ++q) {
+        const long long tok = (long long)tile_idx * TOK + q;
+        if (tok * 16 >= p.T) break;
+        if constexpr (VEC) {
+          if (valid[0]) dst[q] = *reinterpret_cast<const Vec<uint16_t, V>*>(p.pat_in + tok * row_elems + colj[0]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j)
+            if (valid[j]) dst[q].v[j] = p.pat_in[tok * row_elems + colj[j]];
+        }
+      }
+    }
+  };
+
   auto tile = [&](auto full_tag, auto direct_tag, int nsteps) {
     constexpr bool FULL = decltype(full_tag)::value;
     constexpr bool DIRECT = decltype(direct_tag)::value;
@@ -556,7 +594,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
     // ragged edges), so the step loop carries no global address arithmetic for them.
     ST* o_spike = (DIRECT && !DENSE_TMA && MODE != MODE_ROWRES && p.spike)
                       ? static_cast<ST*>(p.spike) + t0 * row_elems + colj[0] : nullptr;
-    uint32_t hb[V];  // MODE_ROWRES: the spikes of the current token as a half bit pattern
+    uint32_t hb[V];  // MODE_ROWRES / MODE_ROWPAT: the spikes of the current token as a half bit pattern
 #pragma unroll
     for (int j = 0; j < V; ++j) hb[j] = 0u;
     ST* o_vpost = (DIRECT && p.vpost) ? static_cast<ST*>(p.vpost) + t0 * row_elems + colj[0] : nullptr;
@@ -659,6 +697,30 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
         plif_step<V>(v, b, dr, th, x, sp_);
       }
 
+      if constexpr (MODE == MODE_ROWPAT) {
+        // Step k is bit 15 - (k mod 16) of the token's half pattern; the patterns to add, if any,
+        // were requested one tile ahead (pin_cur).
+#pragma unroll
+        for (int j = 0; j < V; ++j) hb[j] = (k % 16 == 0 ? 0u : hb[j]) | (sp_[j] ? (1u << (15 - k % 16)) : 0u);
+        const long long tok_off = ((t0 + k) / 16) * row_elems;
+        if (k % 16 == 15) {
+          Vec<uint16_t, V> po;
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            uint32_t h = hb[j];
+            if (p.pat_in)
+              h = codec::residual_of_patterns(hb[j], pin_cur[k / 16].v[j], p.frame_dtype, p.residual_compiled != 0);
+            po.v[j] = (uint16_t)h;
+          }
+          if constexpr (VEC) {
+            if (valid[0]) *reinterpret_cast<Vec<uint16_t, V>*>(p.pat_out + tok_off + colj[0]) = po;
+          } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+              if (valid[j]) p.pat_out[tok_off + colj[j]] = po.v[j];
+          }
+        }
+      }
       if constexpr (MODE == MODE_ROWRES) {
         // Step k is bit 15 - (k mod 16) of the token's half pattern (frame 0 = sign). After the
         // token's last step: decode it, add the value decoded from the 16 input frames, re-encode,
@@ -727,7 +789,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
           }
         }
       }
-      if constexpr (PACKED) {
+      if constexpr (BALLOT) {
         // one ballot per lane slot j: bit l = spike of column col0 + V*l + j. Lane (k mod G) of
         // every group of G lanes keeps the V ballots of step k and interleaves them into the
         // word it stores once the tile is done.
@@ -738,7 +800,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
         }
       }
     }
-    if constexpr (PACKED) {
+    if constexpr (BALLOT) {
       if (p.packed) {
         const long long widx = col0 / 32 + lane / G;
 #pragma unroll
@@ -755,9 +817,15 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
     }
   };
 
+  if constexpr (MODE == MODE_ROWPAT) {
+    if (p.pat_in) load_patterns(0, pin_cur);
+  }
   for (int i = 0; i < ntiles; ++i) {
     t0 = (long long)i * C;
     const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
+    if constexpr (MODE == MODE_ROWPAT) {
+      if (p.pat_in && i + 1 < ntiles) load_patterns(i + 1, pin_nxt);
+    }
     if constexpr (TMA) {
       const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 1u, p.wait_ns);
       if (!__all_sync(0xffffffffu, ok)) {  // a lane that ran out of time takes the whole warp out
@@ -786,6 +854,10 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
         tile(std::true_type{}, std::false_type{}, C);
     } else {
       tile(std::false_type{}, std::true_type{}, nsteps);
+    }
+    if constexpr (MODE == MODE_ROWPAT) {
+#pragma unroll
+      for (int q = 0; q < TOK; ++q) pin_cur[q] = pin_nxt[q];
     }
 
     if constexpr (TMA) {
@@ -1572,6 +1644,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   p.ckpt_w = a.ckpt_w; p.vlast = a.vlast; p.wlast = a.wlast;
   p.T = a.T; p.cols = a.cols; p.words_per_row = (a.cols + 31) / 32;
   p.residual_compiled = a.residual_compiled;
+  p.pat_in = a.pat_in; p.pat_out = a.pat_out; p.frame_dtype = a.frame_dtype;
   p.ntiles = (int)((a.T + C - 1) / C);
   p.err = device_error_word_ptr();
   p.wait_ns = get_wait_limit_ns();
@@ -1939,6 +2012,41 @@ int scan_res_fwd_dispatch(const FwdArgs& a) {
 #undef NSB_RFWD_CASE
   if (C == 16) return launch_fwd_one<ST, MODE_ROWRES, false, 1, 16, false>(a, dev, tune, plan);
   if (C == 32) return launch_fwd_one<ST, MODE_ROWRES, false, 1, 32, false>(a, dev, tune, plan);
+  return NSB_ERR_INVALID_ARG;
+}
+
+// Row-parameter scan with spikes packed in time (MODE_ROWPAT): as the residual scan, one streamed input.
+template <typename ST>
+int scan_pat_fwd_dispatch(const FwdArgs& a) {
+  DeviceInfo dev;
+  int r = get_device_info(&dev);
+  if (r != NSB_OK) return r;
+  if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
+  const Tuning tune = get_tuning();
+  bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
+  // a thread moves its V patterns with one access: the pattern rows must keep V*2-byte alignment
+  tma = tma && aligned16(a.drive) && aligned16(a.ckpt) && a.cols % 8 == 0 &&
+        (reinterpret_cast<uintptr_t>(a.pat_out) % 8 == 0) && (reinterpret_cast<uintptr_t>(a.pat_in) % 8 == 0);
+  const int C = a.tile;
+  Plan plan;
+  if (tma) {
+    PlanQuery q;
+    q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
+    q.nstreams = 1;
+    q.tile = C; q.backward = false; q.max_lanes = C == 32 ? 1 : 4;
+    plan = plan_scan(dev, q, tune);
+    if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;  // the tuning override admits no launch shape
+  }
+  const int V = plan.lanes;
+#define NSB_PFWD_CASE(V_, C_)                                                          \
+  if (V == V_ && C == C_) return launch_fwd_one<ST, MODE_ROWPAT, true, V_, C_, true>(a, dev, tune, plan);
+  if (tma) {
+    NSB_PFWD_CASE(1, 16) NSB_PFWD_CASE(2, 16) NSB_PFWD_CASE(4, 16) NSB_PFWD_CASE(1, 32)
+    return NSB_ERR_INVALID_ARG;
+  }
+#undef NSB_PFWD_CASE
+  if (C == 16) return launch_fwd_one<ST, MODE_ROWPAT, true, 1, 16, false>(a, dev, tune, plan);
+  if (C == 32) return launch_fwd_one<ST, MODE_ROWPAT, true, 1, 32, false>(a, dev, tune, plan);
   return NSB_ERR_INVALID_ARG;
 }
 

@@ -39,6 +39,13 @@ int run_res_fwd(const nsb::FwdArgs& a, int dtype) {
     default: return nsb::scan_res_fwd_f16(a);
   }
 }
+int run_pat_fwd(const nsb::FwdArgs& a, int dtype) {
+  switch (dtype) {
+    case NSB_F32: return nsb::scan_pat_fwd_f32(a);
+    case NSB_BF16: return nsb::scan_pat_fwd_bf16(a);
+    default: return nsb::scan_pat_fwd_f16(a);
+  }
+}
 int run_lin_fwd(const nsb::FwdArgs& a, int dtype) {
   switch (dtype) {
     case NSB_F32: return nsb::scan_lin_fwd_f32(a);
@@ -430,6 +437,37 @@ int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const f
   a.residual_compiled = rounding == NSB_RESIDUAL_COMPILED;
   a.stream = static_cast<cudaStream_t>(stream);
   return run_res_fwd(a, dtype);
+}
+
+int nsb_plif_rowparam_pattern_fwd(const float* beta_row, const void* u, const float* vth_row,
+                                  const float* v_init, const uint16_t* patterns_in, uint16_t* patterns_out,
+                                  float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
+                                  int ckpt_interval, int frame_dtype, int rounding, void* stream) {
+  if (T < 0 || cols < 0 || T % 16 != 0 || !dtype_ok(dtype) || !dtype_ok(frame_dtype) ||
+      (ckpt_interval != 16 && ckpt_interval != 32) ||
+      (rounding != NSB_RESIDUAL_EAGER && rounding != NSB_RESIDUAL_COMPILED))
+    return NSB_ERR_INVALID_ARG;
+  if (cols == 0) return NSB_OK;
+  if (!beta_row || !vth_row || !v_init || !v_last) return NSB_ERR_INVALID_ARG;
+  const void* fp[] = {beta_row, vth_row, v_init, v_last, v_ckpt};
+  for (const void* p : fp)
+    if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
+  if (T == 0) {
+    NSB_CUDA_TRY(cudaMemcpyAsync(v_last, v_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice,
+                                 static_cast<cudaStream_t>(stream)), "copy v_init");
+    return NSB_OK;
+  }
+  if (!u || !patterns_out || !elem_aligned(u, dtype)) return NSB_ERR_INVALID_ARG;
+  if (reinterpret_cast<uintptr_t>(patterns_out) % 2 || reinterpret_cast<uintptr_t>(patterns_in) % 2)
+    return NSB_ERR_INVALID_ARG;
+  nsb::FwdArgs a;
+  a.drive = u; a.beta_row = beta_row; a.vth_row = vth_row; a.v_init = v_init;
+  a.pat_in = patterns_in; a.pat_out = patterns_out; a.frame_dtype = frame_dtype;
+  a.ckpt = v_ckpt; a.vlast = v_last;
+  a.T = T; a.cols = cols; a.mode = nsb::MODE_ROWPAT; a.tile = ckpt_interval;
+  a.residual_compiled = rounding == NSB_RESIDUAL_COMPILED;
+  a.stream = static_cast<cudaStream_t>(stream);
+  return run_pat_fwd(a, dtype);
 }
 
 int nsb_linear_recurrence_fwd(const void* beta, const void* u, const float* v_init, void* v_out,

@@ -7,5 +7,6 @@
 namespace nsb {
 int scan_mod_fwd_bf16(const FwdArgs& a) { return scan_mod_fwd_dispatch<__nv_bfloat16>(a); }
 int scan_res_fwd_bf16(const FwdArgs& a) { return scan_res_fwd_dispatch<__nv_bfloat16>(a); }
+int scan_pat_fwd_bf16(const FwdArgs& a) { return scan_pat_fwd_dispatch<__nv_bfloat16>(a); }
 int scan_lin_fwd_bf16(const FwdArgs& a) { return scan_lin_fwd_dispatch<__nv_bfloat16>(a); }
 }  // namespace nsb

@@ -7,5 +7,6 @@
 namespace nsb {
 int scan_mod_fwd_f16(const FwdArgs& a) { return scan_mod_fwd_dispatch<__half>(a); }
 int scan_res_fwd_f16(const FwdArgs& a) { return scan_res_fwd_dispatch<__half>(a); }
+int scan_pat_fwd_f16(const FwdArgs& a) { return scan_pat_fwd_dispatch<__half>(a); }
 int scan_lin_fwd_f16(const FwdArgs& a) { return scan_lin_fwd_dispatch<__half>(a); }
 }  // namespace nsb

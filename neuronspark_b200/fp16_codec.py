@@ -172,3 +172,101 @@ class _BinaryEncodeSTE(torch.autograd.Function):
 
 def binary_encode_ste(continuous_btd: torch.Tensor) -> torch.Tensor:
     return _BinaryEncodeSTE.apply(continuous_btd)
+
+
+# ------------------------------------------------------------ spikes packed in time
+#
+# The 16 frames of a token and channel as one int16 (the IEEE half bit pattern they spell,
+# frame 0 = sign = bit 15): (S, B, D) patterns for (S*16, B, D) frames, 2 bytes per value instead
+# of 16 elements. The reference moves dense frames between layers (atomic_ops/snn_block.py:281-285,
+# atomic_ops/snn_ffn.py:188-195, model.py:155-157); these functions keep its arithmetic and change
+# only the storage. Patterns are integers, so autograd does not flow through them: the backward
+# pieces are plain functions for a caller that wires its own Function.
+
+
+def _frame_dtype(dt: torch.dtype) -> torch.dtype:
+    if dt not in (torch.float32, torch.bfloat16, torch.float16):
+        raise NSBError(f"unsupported frame dtype {dt}")
+    return dt
+
+
+@torch.no_grad()
+def pack_frames(frames: torch.Tensor) -> torch.Tensor:
+    """(S*16, B, D) frames in {0,1} -> (S, B, D) int16 patterns."""
+    dev = _lib.require_cuda(frames)
+    if frames.dim() != 3 or frames.shape[0] % 16:
+        raise NSBError("pack_frames expects (S*16, B, D)")
+    f = frames.contiguous()
+    _frame_dtype(f.dtype)
+    TK, B, D = f.shape
+    out = torch.empty((TK // 16, B, D), dtype=torch.int16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_frames_pack(_lib.ptr(f), _lib.ptr(out), B, TK // 16, D, _lib.dtype_code(f.dtype),
+                                              _lib.stream_ptr(dev)), "nsb_frames_pack")
+    return out
+
+
+def _patterns(p: torch.Tensor):
+    dev = _lib.require_cuda(p)
+    if p.dtype != torch.int16 or p.dim() != 3:
+        raise NSBError("patterns are (S, B, D) int16")
+    return dev, p.contiguous()
+
+
+@torch.no_grad()
+def unpack_frames(patterns: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """(S, B, D) int16 patterns -> (S*16, B, D) frames in {0,1} of ``dtype``."""
+    dev, p = _patterns(patterns)
+    S, B, D = p.shape
+    out = torch.empty((S * 16, B, D), dtype=_frame_dtype(dtype), device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_frames_unpack(_lib.ptr(p), _lib.ptr(out), B, S, D, _lib.dtype_code(dtype),
+                                                _lib.stream_ptr(dev)), "nsb_frames_unpack")
+    return out
+
+
+@torch.no_grad()
+def fp16_decode_packed(patterns: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``fp16_decode(unpack_frames(patterns, dtype), S)`` without the frames: (B, S, D) values."""
+    dev, p = _patterns(patterns)
+    S, B, D = p.shape
+    out = torch.empty((B, S, D), dtype=_frame_dtype(dtype), device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_fp16_decode_packed_fwd(_lib.ptr(p), _lib.ptr(out), B, S, D, _lib.dtype_code(dtype),
+                                                         _lib.stream_ptr(dev)), "nsb_fp16_decode_packed_fwd")
+    return out
+
+
+@torch.no_grad()
+def fp16_decode_packed_backward(patterns: torch.Tensor, grad_values: torch.Tensor) -> torch.Tensor:
+    """Gradient of the decode with respect to the 16 frames of every value: (B, S, D) value
+    gradients -> (S*16, B, D) frame gradients in ``grad_values``' dtype."""
+    dev, p = _patterns(patterns)
+    S, B, D = p.shape
+    g = grad_values.contiguous()
+    if tuple(g.shape) != (B, S, D):
+        raise NSBError(f"grad_values has shape {tuple(g.shape)}, expected {(B, S, D)}")
+    out = torch.empty((S * 16, B, D), dtype=_frame_dtype(g.dtype), device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_fp16_decode_packed_bwd(_lib.ptr(p), _lib.ptr(g), _lib.ptr(out), B, S, D,
+                                                         _lib.dtype_code(g.dtype), _lib.stream_ptr(dev)),
+                   "nsb_fp16_decode_packed_bwd")
+    return out
+
+
+@torch.no_grad()
+def binary_residual_packed(patterns_a: torch.Tensor, patterns_b: torch.Tensor,
+                           frame_dtype: torch.dtype = torch.bfloat16, rounding=None) -> torch.Tensor:
+    """``pack_frames(binary_residual(unpack(a), unpack(b)))`` on the patterns themselves; ``frame_dtype``
+    names the frame dtype whose roundings apply (they matter for bfloat16 only)."""
+    dev, a = _patterns(patterns_a)
+    _, b = _patterns(patterns_b)
+    if a.shape != b.shape:
+        raise NSBError("pattern arrays of different shapes")
+    out = torch.empty_like(a)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_binary_residual_packed(_lib.ptr(a), _lib.ptr(b), _lib.ptr(out), a.numel(),
+                                                         _lib.dtype_code(_frame_dtype(frame_dtype)),
+                                                         residual_rounding_code(rounding), _lib.stream_ptr(dev)),
+                   "nsb_binary_residual_packed")
+    return out

@@ -676,6 +676,65 @@ def plif_rowparam_residual_forward(beta_row, u, v_th_row, v_init, spike_in, alph
     return PLIFRowParamResidualScan.apply(beta_row, u, v_th_row, v_init, spike_in, alpha)
 
 
+@torch.no_grad()
+def plif_rowparam_forward_patterns(beta_row, u, v_th_row, v_init, patterns_in=None,
+                                   frame_dtype: torch.dtype = None, want_ckpt: bool = False):
+    """The row-parameter scan with its spikes packed in time: returns ``(patterns, V_last, ckpt)``
+    where ``patterns`` is int16 ``(T/16, ...)`` - per token and column the half bit pattern the 16
+    spikes spell (``fp16_codec.pack_frames`` of the dense spikes). With ``patterns_in`` the binary
+    residual with that array is applied first (``frame_dtype``: the frame dtype whose roundings
+    apply, default ``u``'s). ``ckpt`` (when asked for) and ``(beta_row, u, v_th_row)`` are what
+    ``plif_rowparam_patterns_backward`` needs."""
+    beta_row, v_th_row, v_init = _rows(u, beta_row, v_th_row, v_init)
+    shape = u.shape[1:]
+    if u.shape[0] % 16:
+        raise NSBError("T must be a multiple of 16")
+    dt = u.dtype if u.dtype in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+    u_c = _as_stream(u, dt)
+    beta32, vth32, v0 = (_row_f32(t, shape) for t in (beta_row, v_th_row, v_init))
+    dev = _lib.require_cuda(u_c, beta32, vth32, v0, patterns_in)
+    T, cols = u_c.shape[0], _cols(u_c)
+    if patterns_in is not None:
+        if patterns_in.dtype != torch.int16 or tuple(patterns_in.shape) != (T // 16, *shape):
+            raise NSBError("patterns_in must be int16 of shape (T/16, ...)")
+        patterns_in = patterns_in.contiguous()
+    C = 32 if _interval(cols, row_param=True) == 32 else 16
+    out = torch.empty((T // 16, *shape), dtype=torch.int16, device=dev)
+    ckpt = torch.empty((_n_tiles(T, C), cols), dtype=torch.float32, device=dev) if want_ckpt else None
+    v_last = torch.empty(shape, dtype=torch.float32, device=dev)
+    fdt = frame_dtype if frame_dtype is not None else dt
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_plif_rowparam_pattern_fwd(
+            _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(v0), _lib.ptr(patterns_in), _lib.ptr(out),
+            _lib.ptr(ckpt), _lib.ptr(v_last), T, cols, _lib.dtype_code(dt), C, _lib.dtype_code(fdt),
+            fp16_codec.residual_rounding_code(), _lib.stream_ptr(dev)), "nsb_plif_rowparam_pattern_fwd")
+    return out, v_last, (ckpt, C)
+
+
+@torch.no_grad()
+def plif_rowparam_patterns_backward(beta_row, u, v_th_row, ckpt, grad_frames, alpha: float):
+    """Backward of ``plif_rowparam_forward_patterns``: ``grad_frames`` is the dense ``(T, ...)``
+    gradient of the spikes (e.g. from ``fp16_codec.fp16_decode_packed_backward``); ``ckpt`` the third
+    value the forward returned. Returns ``(grad_beta_row, grad_u, grad_v_th_row, grad_v_init)``."""
+    ck, C = ckpt
+    beta_row, v_th_row = _rows(u, beta_row, v_th_row)
+    shape = u.shape[1:]
+    dt = u.dtype if u.dtype in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+    u_c = _as_stream(u, dt)
+    gs = _as_stream(grad_frames, dt)
+    beta32, vth32 = _row_f32(beta_row, shape), _row_f32(v_th_row, shape)
+    dev = _lib.require_cuda(u_c, gs, beta32, vth32, ck)
+    T, cols = u_c.shape[0], _cols(u_c)
+    g_u = torch.empty_like(u_c)
+    g_beta, g_vth, g_v0 = (torch.empty(shape, dtype=torch.float32, device=dev) for _ in range(3))
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().nsb_plif_rowparam_bwd(
+            _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(ck), _lib.ptr(gs), None, _lib.ptr(g_beta),
+            _lib.ptr(g_u), _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols, _lib.dtype_code(dt), C, _lib.SURR_SIGMOID,
+            float(alpha), _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd")
+    return g_beta, g_u, g_vth, g_v0
+
+
 def _rf_apply(fn, beta, omega, u, v_th, v_init, w_init, surrogate_function):
     if surrogate_function is None:
         with torch.no_grad():
