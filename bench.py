@@ -646,6 +646,8 @@ def run_inference(args):
     v_a = torch.zeros((B, D), dtype=torch.float32, device=dev)
     v_b = torch.empty_like(v_a)
     unfused = None
+    # scratch that lets the library cut a scan over few columns along time (NULL for the others)
+    split_scratch = ps._split_scratch(T, cols, dev)
     if w["kind"] == "rowres":
         from neuronspark_b200 import fp16_codec as codec
         g = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -660,7 +662,7 @@ def run_inference(args):
         def step():
             _lib.check(L.nsb_plif_rowparam_residual_fwd(p(beta_row), p(u), p(vth_row), p(v_a), p(frames_in),
                                                         p(frames_out), None, p(v_b), T, cols, _lib.BF16,
-                                                        tile_steps, _lib.RESIDUAL_COMPILED, stream),
+                                                        tile_steps, _lib.RESIDUAL_COMPILED, p(split_scratch), stream),
                        "rowparam_residual_fwd")
 
         def unfused():
@@ -678,7 +680,8 @@ def run_inference(args):
 
         def step():
             _lib.check(L.nsb_plif_rowparam_fwd(p(beta_row), p(u), p(vth_row), p(v_a), None, p(packed), None,
-                                               None, p(v_b), T, cols, _lib.BF16, tile_steps, stream), "rowparam_fwd")
+                                               None, p(v_b), T, cols, _lib.BF16, tile_steps, p(split_scratch), stream),
+                       "rowparam_fwd")
     else:
         inp = make_inputs(B, T * calls, D, dev, 1234 + rank)
         esz = 2 * cols

@@ -100,6 +100,33 @@ int nsb_set_wait_limit_ns(uint64_t ns);
  * (nsb_set_wait_limit_ns) unless a 2 s kernel is wanted. */
 int nsb_selftest_wait_timeout(void* stream);
 
+/*
+ * Time split of the row-parameter forward scans over few columns. A scan over a few thousand
+ * columns occupies a few hundred warps while each warp is bound by its own serial chain over T;
+ * the other SMs idle. Given scratch memory (`split_scratch` of nsb_plif_rowparam_fwd,
+ * nsb_plif_rowparam_residual_fwd and nsb_plif_rowparam_pattern_fwd: NULL, or
+ * nsb_time_split_scratch_floats(cols) floats of device memory that the call may overwrite), such a
+ * scan is cut along time into up to 16 segments that run side by side: a later segment is entered
+ * `warm_steps` early from V = 0 and keeps what it computes from its own first step on - PLIF
+ * trajectories driven by the same input become bit-identical a few hundred steps after they
+ * started apart - and a second launch compares every segment's assumed starting state with the
+ * exact one, bit for bit, and rescans the segments where they differ. Results therefore equal the
+ * unsplit scan's exactly for every input; only the time taken depends on how often a rescan is
+ * needed. The reference has no counterpart (its kernels walk T serially, one program per 128
+ * columns, atomic_ops/parallel_scan.py:496-530).
+ *
+ * nsb_set_time_split      max_segments: 0 = automatic, 1 = never split, 2..16 = at most that many
+ *                         (and split even where the planner expects little gain); warm_steps: 0 =
+ *                         default (1024). Process-global, read at each launch.
+ * nsb_last_time_split     {segments, tiles per segment, warm-up tiles} of the calling thread's last
+ *                         forward scan launch (segments = 1: it was not split). After a split
+ *                         launch the number of rescanned (warp, segment) pairs is the uint32 at
+ *                         split_scratch[2*segments*cols].
+ */
+int nsb_set_time_split(int max_segments, int warm_steps);
+int64_t nsb_time_split_scratch_floats(int64_t cols);
+int nsb_last_time_split(int32_t out[3]);
+
 /* Tuning override for the scan kernels, used by sweeps and tests. Any field
  * <= 0 keeps the built-in heuristic. warps_per_cta: warps of one CTA (each
  * warp owns 32*lanes_per_thread columns and its own TMA pipeline); stages:
@@ -184,7 +211,7 @@ int nsb_plif_selective_bwd(const void* beta, const void* u_or_cur, const void* g
 int nsb_plif_rowparam_fwd(const float* beta_row, const void* u, const float* vth_row,
                           const float* v_init, void* spike_dense, uint32_t* spike_packed,
                           void* v_post, float* v_ckpt, float* v_last, int64_t T,
-                          int64_t cols, int dtype, int ckpt_interval, void* stream);
+                          int64_t cols, int dtype, int ckpt_interval, float* split_scratch, void* stream);
 
 /*
  * Reverse pass of the row-parameter scan. Replaces
@@ -444,7 +471,7 @@ int nsb_plif_rowparam_pattern_fwd(const float* beta_row, const void* u, const fl
                                   const float* v_init, const uint16_t* patterns_in,
                                   uint16_t* patterns_out, float* v_ckpt, float* v_last, int64_t T,
                                   int64_t cols, int dtype, int ckpt_interval, int frame_dtype,
-                                  int rounding, void* stream);
+                                  int rounding, float* split_scratch, void* stream);
 
 /*
  * Row-parameter scan followed by the binary residual, in one pass. Replaces the
@@ -465,7 +492,7 @@ int nsb_plif_rowparam_pattern_fwd(const float* beta_row, const void* u, const fl
 int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const float* vth_row,
                                    const float* v_init, const void* frames_in, void* frames_out,
                                    float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
-                                   int ckpt_interval, int rounding, void* stream);
+                                   int ckpt_interval, int rounding, float* split_scratch, void* stream);
 
 /*
  * Linear recurrence V[k] = beta[k]*V[k-1] + u[k], V[-1] = v_init. Replaces

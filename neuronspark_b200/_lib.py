@@ -38,7 +38,10 @@ _SIGNATURES = {
     "nsb_plif_selective_fwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_plif_selective_bwd": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int,
                                                           c_float, c_void_p]),
-    "nsb_plif_rowparam_fwd": (c_int, [c_void_p] * 9 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_plif_rowparam_fwd": (c_int, [c_void_p] * 9 + [c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "nsb_set_time_split": (c_int, [c_int, c_int]),
+    "nsb_time_split_scratch_floats": (c_int64, [c_int64]),
+    "nsb_last_time_split": (c_int, [ctypes.POINTER(c_int32)]),
     "nsb_plif_rowparam_bwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_int,
                                                          c_float, c_void_p]),
     "nsb_plif_rf_fwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_void_p]),
@@ -56,7 +59,8 @@ _SIGNATURES = {
                                                                 c_void_p, c_void_p]),
     "nsb_plif_rf_bwd_dalpha": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
                                                           c_void_p]),
-    "nsb_plif_rowparam_residual_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
+    "nsb_plif_rowparam_residual_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
+                                                                c_void_p]),
     "nsb_frames_pack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "nsb_frames_unpack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "nsb_fp16_decode_packed_fwd": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
@@ -64,7 +68,7 @@ _SIGNATURES = {
                                            c_void_p]),
     "nsb_binary_residual_packed": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "nsb_plif_rowparam_pattern_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_int,
-                                                               c_void_p]),
+                                                               c_void_p, c_void_p]),
     "nsb_linear_recurrence_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_linear_recurrence_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_moe_combine_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_int, c_int, c_void_p]),
@@ -183,6 +187,18 @@ def scan_plan(backward: bool, nstreams: int, elem_size: int, T: int, cols: int, 
     check(lib().nsb_scan_plan_query(int(backward), nstreams, elem_size, T, cols, tile, out),
           "nsb_scan_plan_query")
     return dict(zip(("lanes_per_thread", "warps_per_cta", "stages", "grid", "smem_bytes"), out))
+
+
+def set_time_split(max_segments: int = 0, warm_steps: int = 0) -> None:
+    """Time split of the row-parameter forward scans over few columns: ``max_segments`` 0 = automatic,
+    1 = off, 2..16 = at most that many; ``warm_steps`` 0 = default (1024). Process-global."""
+    check(lib().nsb_set_time_split(int(max_segments), int(warm_steps)), "nsb_set_time_split")
+
+
+def last_time_split() -> dict:
+    out = (c_int32 * 3)()
+    check(lib().nsb_last_time_split(out), "nsb_last_time_split")
+    return dict(zip(("segments", "seg_tiles", "warm_tiles"), out))
 
 
 def set_wait_limit_ns(ns: int = 0) -> None:

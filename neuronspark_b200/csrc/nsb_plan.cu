@@ -11,6 +11,7 @@
 // 1 KB: ~0.78, 2 KB: ~0.92, >= 4 KB: ~1). The cost of a candidate is the sum over
 // its waves of max(bandwidth time, latency time, issue time) in microseconds.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 
 #include "nsb_scan.cuh"
@@ -175,7 +176,80 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
   return best;
 }
 
+// ---- time split of forward scans over few columns
+//
+// A scan over a few thousand columns keeps a few hundred warps busy while the chip has 592 warp
+// schedulers, and each warp is bound by its own serial chain over T. Spare schedulers can take
+// later parts of the time axis: a segment is entered `warm` steps early from V = 0, and by its
+// own first step its state equals the exact one bit for bit (two PLIF trajectories driven by the
+// same input merge once their difference has decayed below one unit in the last place: within
+// 200-650 steps for the benchmark distributions, measured on CPU). A second launch verifies this
+// per column and rescans what differs, so the result is exact whatever the inputs.
+namespace {
+std::atomic<int> g_split_max_segments{0};  // 0 = automatic, 1 = never split
+std::atomic<int> g_split_warm_steps{0};    // 0 = default
+thread_local TimeSplit g_last_split;
+constexpr int kDefaultWarmSteps = 1024;
+constexpr int kMaxSegments = 16;
+}  // namespace
+
+TimeSplit& last_time_split() { return g_last_split; }
+
+long long time_split_scratch_floats(long long cols) { return 2LL * kMaxSegments * cols + 4; }
+
+TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, int tile, int lanes, int wpc) {
+  TimeSplit ts;
+  const int cap = g_split_max_segments.load(std::memory_order_relaxed);
+  if (cap == 1 || tile <= 0) return ts;
+  const long long ntiles = (T + tile - 1) / tile;
+  const long long nwarps = (cols + 32LL * lanes - 1) / (32LL * lanes);
+  const long long ctas = (nwarps + wpc - 1) / wpc;
+  const long long slots = 4LL * std::max(1, dev.sm_count);  // one warp per scheduler
+  long long pmax = slots / std::max(1LL, ctas * wpc);
+  pmax = std::min<long long>(pmax, cap > 1 ? cap : kMaxSegments);
+  pmax = std::min<long long>(pmax, kMaxSegments);
+  const int warm_steps = g_split_warm_steps.load(std::memory_order_relaxed);
+  const long long warm = ((warm_steps > 0 ? warm_steps : kDefaultWarmSteps) + tile - 1) / tile;
+  long long best_p = 1, best_cost = ntiles;
+  for (long long pseg = 2; pseg <= pmax; ++pseg) {
+    const long long seg = (ntiles + pseg - 1) / pseg;
+    if (seg < warm || seg * (pseg - 1) >= ntiles) continue;  // warm-up would reach before t = 0 / an empty last segment
+    const long long cost = seg + warm;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best_p = pseg;
+    }
+  }
+  // worth two launches only if a quarter of the serial chain goes away (an explicit cap > 1 is obeyed as is)
+  if (best_p > 1 && (cap > 1 || best_cost * 4 <= ntiles * 3)) {
+    ts.nseg = (int)best_p;
+    ts.seg_tiles = (int)((ntiles + best_p - 1) / best_p);
+    ts.warm_tiles = (int)warm;
+  }
+  return ts;
+}
+
 }  // namespace nsb
+
+extern "C" int nsb_set_time_split(int max_segments, int warm_steps) {
+  if (max_segments < 0 || max_segments > 16 || warm_steps < 0) return NSB_ERR_INVALID_ARG;
+  nsb::g_split_max_segments.store(max_segments, std::memory_order_relaxed);
+  nsb::g_split_warm_steps.store(warm_steps, std::memory_order_relaxed);
+  return NSB_OK;
+}
+
+extern "C" int64_t nsb_time_split_scratch_floats(int64_t cols) {
+  return cols > 0 ? nsb::time_split_scratch_floats(cols) : 0;
+}
+
+extern "C" int nsb_last_time_split(int32_t out[3]) {
+  if (!out) return NSB_ERR_INVALID_ARG;
+  const nsb::TimeSplit& ts = nsb::last_time_split();
+  out[0] = ts.nseg;
+  out[1] = ts.seg_tiles;
+  out[2] = ts.warm_tiles;
+  return NSB_OK;
+}
 
 extern "C" int nsb_scan_plan_query(int backward, int nstreams, int elem_size, int64_t T, int64_t cols,
                                    int tile, int32_t out[5]) {

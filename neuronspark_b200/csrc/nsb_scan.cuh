@@ -85,6 +85,7 @@ struct FwdArgs {
   const uint16_t* pat_in = nullptr;  // MODE_ROWPAT: optional [T/16, cols] patterns to add
   uint16_t* pat_out = nullptr;       // MODE_ROWPAT: [T/16, cols] patterns out
   int frame_dtype = NSB_F32;         // MODE_ROWPAT: the frame dtype whose residual roundings apply
+  float* split_scratch = nullptr;    // optional: nsb_time_split_scratch_floats(cols) floats; enables the time split
   cudaStream_t stream = nullptr;
 };
 
@@ -173,6 +174,15 @@ struct Plan {
 // Chooses lanes per thread, warps per CTA and ring depth. Pure host arithmetic
 // (no CUDA calls), so it can be unit-tested without a GPU.
 Plan plan_scan(const DeviceInfo& dev, const PlanQuery& q, const Tuning& tune);
+
+// Time split of a forward scan over few columns (nseg == 1: none). Host arithmetic (nsb_plan.cu).
+struct TimeSplit {
+  int nseg = 1, seg_tiles = 0, warm_tiles = 0;
+};
+TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, int tile, int lanes, int wpc);
+TimeSplit& last_time_split();  // of the calling thread's last forward launch
+// floats of scratch a time-split launch over `cols` columns may need (boundary states + a counter)
+long long time_split_scratch_floats(long long cols);
 
 // Device description of a B200 for planning when no GPU is present.
 DeviceInfo b200_device_info();
@@ -358,6 +368,15 @@ struct FwdParams {
   const uint16_t* pat_in;
   uint16_t* pat_out;
   int frame_dtype;
+  // Time split (few columns): nseg > 1 cuts the scan into nseg segments of seg_tiles tiles that
+  // run side by side (grid.y); a segment after the first starts warm_tiles tiles early from V = 0
+  // and keeps only what it computes from its own start on. vspec / vend are [nseg, cols]: the
+  // state a segment reached at its own start, and at its end. fixup = 1 is the second launch,
+  // which checks every vspec against the exact state and redoes the segments that differ.
+  int nseg, seg_tiles, warm_tiles, fixup;
+  float* vspec;
+  float* vend;
+  unsigned int* fix_count;
 };
 
 template <int MODE_>
@@ -440,7 +459,7 @@ __device__ __forceinline__ void rf_step(float (&v)[V], float (&w)[V], const floa
 // The forward scan. A device function so that it can sit behind two kernel entry points: one
 // without a register limit (ptxas' own choice; giving it an explicit 255 made it spend 30-100 more
 // registers on every variant), one held to 160 registers.
-template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
+template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA, bool SPLIT = false>
 __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensorMap& tm0, const CUtensorMap& tm1,
                                               const CUtensorMap& tm2, const CUtensorMap& tm3,
                                               const CUtensorMap& tm4, const CUtensorMap& tm_spike) {
@@ -528,13 +547,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
     }
   };
 
-  const int ntiles = p.ntiles;
-  if constexpr (TMA) {
-    if (lane == 0) {
-      const int pre = ntiles < stages ? ntiles : stages;
-      for (int s = 0; s < pre; ++s) issue(s, s);
-    }
-  }
+  const int ntiles_total = p.ntiles;
 
   // The direct path stages KB steps of every stream in registers at a time.
   constexpr int KB = TMA ? C : 8;
@@ -585,9 +598,11 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
     }
   };
 
-  auto tile = [&](auto full_tag, auto direct_tag, int nsteps) {
+  // emit_tag = false: a warm-up tile of a time-split scan; the state advances, nothing is written
+  auto tile = [&](auto full_tag, auto direct_tag, auto emit_tag, int nsteps) {
     constexpr bool FULL = decltype(full_tag)::value;
-    constexpr bool DIRECT = decltype(direct_tag)::value;
+    constexpr bool EMIT = decltype(emit_tag)::value;
+    constexpr bool DIRECT = decltype(direct_tag)::value && EMIT;
     constexpr bool STATS = MT::kStats;  // accumulate the moments of u
     // On the vector path dense spikes are written over the consumed drive tile in
     // shared memory and leave through one TMA store per tile (which also clips the
@@ -713,11 +728,11 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
             po.v[j] = (uint16_t)h;
           }
           if constexpr (VEC) {
-            if (valid[0]) *reinterpret_cast<Vec<uint16_t, V>*>(p.pat_out + tok_off + colj[0]) = po;
+            if (valid[0] && EMIT) *reinterpret_cast<Vec<uint16_t, V>*>(p.pat_out + tok_off + colj[0]) = po;
           } else {
 #pragma unroll
             for (int j = 0; j < V; ++j)
-              if (valid[j]) p.pat_out[tok_off + colj[j]] = po.v[j];
+              if (valid[j] && EMIT) p.pat_out[tok_off + colj[j]] = po.v[j];
           }
         }
       }
@@ -763,7 +778,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
               ST* g_out = static_cast<ST*>(p.spike);
 #pragma unroll
               for (int j = 0; j < V; ++j)
-                if (valid[j]) g_out[(t0 + k0 + i) * row_elems + colj[j]] = ob[j] ? E::one() : E::zero();
+                if (valid[j] && EMIT) g_out[(t0 + k0 + i) * row_elems + colj[j]] = ob[j] ? E::one() : E::zero();
             }
           }
         }
@@ -789,7 +804,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
           }
         }
       }
-      if constexpr (BALLOT) {
+      if constexpr (BALLOT && EMIT) {
         // one ballot per lane slot j: bit l = spike of column col0 + V*l + j. Lane (k mod G) of
         // every group of G lanes keeps the V ballots of step k and interleaves them into the
         // word it stores once the tile is done.
@@ -801,7 +816,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
       }
     }
     if constexpr (BALLOT) {
-      if (p.packed) {
+      if (EMIT && p.packed) {
         const long long widx = col0 / 32 + lane / G;
 #pragma unroll
         for (int q = 0; q < NSLOT; ++q) {
@@ -817,80 +832,165 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
     }
   };
 
-  if constexpr (MODE == MODE_ROWPAT) {
-    if (p.pat_in) load_patterns(0, pin_cur);
+  // ---- which tiles this warp scans. An ordinary launch: all of them, once. A time-split launch
+  // (few columns: spare SMs take later parts of the time axis): segment blockIdx.y, entered
+  // warm_tiles early from V = 0 with its outputs held back until its own first tile - PLIF
+  // trajectories driven by the same input become bit-identical after a few hundred steps, whatever
+  // state they started from. The fix-up launch then walks the segments in order with the exact
+  // state in hand, and rescans only those whose warmed-up state does not equal it bit for bit.
+  // SPLIT is a template parameter: the kernels of ordinary launches carry none of this (with the
+  // choice made at run time the packed row-parameter scan took 16 instead of 13 instructions per
+  // step and half as long again).
+  static_assert(!SPLIT || (!MT::kSecond && !MT::kStats && !MT::kMod), "no time split for this mode");
+  constexpr bool split = SPLIT;
+  const int seg_lo = split ? (p.fixup ? 1 : (int)blockIdx.y) : 0;
+  const int seg_hi = split ? (p.fixup ? p.nseg : (int)blockIdx.y + 1) : 1;
+  float carry[V];
+  if (split && p.fixup) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) carry[j] = valid[j] ? p.vend[colj[j]] : 0.0f;
   }
-  for (int i = 0; i < ntiles; ++i) {
-    t0 = (long long)i * C;
-    const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
+  for (int seg = seg_lo; seg < seg_hi && !failed; ++seg) {
+    int tile_begin = 0, tile_emit = 0, tile_end = ntiles_total;
+    if (split) {
+      tile_emit = seg * p.seg_tiles;
+      tile_end = tile_emit + p.seg_tiles < ntiles_total ? tile_emit + p.seg_tiles : ntiles_total;
+      if (p.fixup) {
+        bool differs = false;
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+          if (valid[j])
+            differs |= __float_as_uint(p.vspec[(long long)seg * row_elems + colj[j]]) != __float_as_uint(carry[j]);
+        if (!__any_sync(0xffffffffu, differs)) {  // the speculation held: this segment's results stand
+#pragma unroll
+          for (int j = 0; j < V; ++j) carry[j] = valid[j] ? p.vend[(long long)seg * row_elems + colj[j]] : 0.0f;
+          continue;
+        }
+        if (lane == 0 && p.fix_count) atomicAdd(p.fix_count, 1u);
+        tile_begin = tile_emit;
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[j] = carry[j];
+      } else {
+        tile_begin = seg == 0 ? 0 : tile_emit - p.warm_tiles;
+        if (seg > 0) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) v[j] = 0.0f;
+        }
+      }
+    }
+    const int nt = tile_end - tile_begin;
+    if constexpr (TMA) {
+      if (lane == 0) {  // prime the ring from the stage that is consumed next
+        const int pre = nt < stages ? nt : stages;
+        for (int q = 0; q < pre; ++q) issue(tile_begin + q, (s_idx + q) % stages);
+      }
+    }
     if constexpr (MODE == MODE_ROWPAT) {
-      if (p.pat_in && i + 1 < ntiles) load_patterns(i + 1, pin_nxt);
+      if (p.pat_in) load_patterns(tile_begin, pin_cur);
+    }
+    for (int i = 0; i < nt; ++i) {
+      const int ia = tile_begin + i;  // absolute tile index
+      t0 = (long long)ia * C;
+      const bool emit = !split || ia >= tile_emit;
+      const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
+      if (split && !p.fixup && seg > 0 && ia == tile_emit) {  // warmed up: what this segment assumes it starts from
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+          if (valid[j]) p.vspec[(long long)seg * row_elems + colj[j]] = v[j];
+      }
+      if constexpr (MODE == MODE_ROWPAT) {
+        if (p.pat_in && i + 1 < nt) load_patterns(ia + 1, pin_nxt);
+      }
+      if constexpr (TMA) {
+        const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 1u, p.wait_ns);
+        if (!__all_sync(0xffffffffu, ok)) {  // a lane that ran out of time takes the whole warp out
+          failed = true;
+          break;
+        }
+        sp = reinterpret_cast<const ST*>(data_ptr + (size_t)s_idx * STAGE_BYTES) + V * lane;
+      }
+      if (p.ckpt && emit) {
+        if constexpr (VEC) {
+          if (valid[0]) VecIO<float, V>::store(p.ckpt + (long long)ia * row_elems + colj[0], v);
+          if (MT::kSecond && valid[0]) VecIO<float, V>::store(p.ckpt_w + (long long)ia * row_elems + colj[0], w);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j)
+            if (valid[j]) {
+              p.ckpt[(long long)ia * row_elems + colj[j]] = v[j];
+              if (MT::kSecond) p.ckpt_w[(long long)ia * row_elems + colj[j]] = w[j];
+            }
+        }
+      }
+      bool warm_tile = false;
+      if constexpr (SPLIT) warm_tile = !emit;
+      if (warm_tile) {  // always a full tile: warm-up ends before the segment's own first step
+        if constexpr (SPLIT) tile(std::true_type{}, std::false_type{}, std::false_type{}, C);
+      } else if (nsteps == C) {
+        if (any_direct)
+          tile(std::true_type{}, std::true_type{}, std::true_type{}, C);
+        else
+          tile(std::true_type{}, std::false_type{}, std::true_type{}, C);
+      } else {
+        tile(std::false_type{}, std::true_type{}, std::true_type{}, nsteps);
+      }
+      if constexpr (MODE == MODE_ROWPAT) {
+#pragma unroll
+        for (int q = 0; q < TOK; ++q) pin_cur[q] = pin_nxt[q];
+      }
+
+      if constexpr (TMA) {
+        const bool store_spikes = DENSE_TMA && p.spike != nullptr && emit;
+        if (store_spikes) proxy_async_fence();  // make this lane's shared-memory writes visible to TMA
+        __syncwarp();
+        if (lane == 0) {
+          if (store_spikes) {
+            tma_store_2d(&tm_spike, data0 + (uint32_t)s_idx * STAGE_BYTES + MT::kDrive * TILE_BYTES, (int)col0,
+                         ia * C);
+            bulk_commit_group();
+          }
+          if (store_spikes && p.defer) {
+            // Refill the stage of the PREVIOUS tile: its store has had a whole tile of
+            // compute to read shared memory, so this wait returns at once and the warp
+            // never stands still behind its own store.
+            bulk_wait_read_keep1();
+            const int sp_idx = s_idx == 0 ? stages - 1 : s_idx - 1;
+            if (i >= 1 && i - 1 + stages < nt) issue(ia - 1 + stages, sp_idx);
+          } else if (p.defer && DENSE_TMA && p.spike != nullptr) {
+            // (a warm-up tile of a deferring launch: nothing was stored, keep the refill order)
+            const int sp_idx = s_idx == 0 ? stages - 1 : s_idx - 1;
+            if (i >= 1 && i - 1 + stages < nt) issue(ia - 1 + stages, sp_idx);
+          } else {
+            if (store_spikes) bulk_wait_read_all();  // the stage is refilled next
+            if (i + stages < nt) issue(ia + stages, s_idx);
+          }
+        }
+        if (++s_idx == stages) {
+          s_idx = 0;
+          phase ^= 1u;
+        }
+      }
     }
     if constexpr (TMA) {
-      const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 1u, p.wait_ns);
-      if (!__all_sync(0xffffffffu, ok)) {  // a lane that ran out of time takes the whole warp out
-        failed = true;
-        break;
-      }
-      sp = reinterpret_cast<const ST*>(data_ptr + (size_t)s_idx * STAGE_BYTES) + V * lane;
+      if (lane == 0) bulk_wait_all();  // every store of this range has left shared memory
+      __syncwarp();
     }
-    if (p.ckpt) {
-      if constexpr (VEC) {
-        if (valid[0]) VecIO<float, V>::store(p.ckpt + (long long)i * row_elems + colj[0], v);
-        if (MT::kSecond && valid[0]) VecIO<float, V>::store(p.ckpt_w + (long long)i * row_elems + colj[0], w);
+    if (split && !failed) {
+      if (p.fixup) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          carry[j] = v[j];
+          if (valid[j]) p.vend[(long long)seg * row_elems + colj[j]] = v[j];
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < V; ++j)
-          if (valid[j]) {
-            p.ckpt[(long long)i * row_elems + colj[j]] = v[j];
-            if (MT::kSecond) p.ckpt_w[(long long)i * row_elems + colj[j]] = w[j];
-          }
-      }
-    }
-    if (nsteps == C) {
-      if (any_direct)
-        tile(std::true_type{}, std::true_type{}, C);
-      else
-        tile(std::true_type{}, std::false_type{}, C);
-    } else {
-      tile(std::false_type{}, std::true_type{}, nsteps);
-    }
-    if constexpr (MODE == MODE_ROWPAT) {
-#pragma unroll
-      for (int q = 0; q < TOK; ++q) pin_cur[q] = pin_nxt[q];
-    }
-
-    if constexpr (TMA) {
-      const bool store_spikes = DENSE_TMA && p.spike != nullptr;
-      if (store_spikes) proxy_async_fence();  // make this lane's shared-memory writes visible to TMA
-      __syncwarp();
-      if (lane == 0) {
-        if (store_spikes) {
-          tma_store_2d(&tm_spike, data0 + (uint32_t)s_idx * STAGE_BYTES + MT::kDrive * TILE_BYTES, (int)col0,
-                       i * C);
-          bulk_commit_group();
-        }
-        if (store_spikes && p.defer) {
-          // Refill the stage of the PREVIOUS tile: its store has had a whole tile of
-          // compute to read shared memory, so this wait returns at once and the warp
-          // never stands still behind its own store.
-          bulk_wait_read_keep1();
-          const int sp_idx = s_idx == 0 ? stages - 1 : s_idx - 1;
-          if (i >= 1 && i - 1 + stages < ntiles) issue(i - 1 + stages, sp_idx);
-        } else {
-          if (store_spikes) bulk_wait_read_all();  // the stage is refilled next
-          if (i + stages < ntiles) issue(i + stages, s_idx);
-        }
-      }
-      if (++s_idx == stages) {
-        s_idx = 0;
-        phase ^= 1u;
+          if (valid[j]) p.vend[(long long)seg * row_elems + colj[j]] = v[j];
       }
     }
   }
 
   if constexpr (TMA) {
-    if (lane == 0) bulk_wait_all();
     if (failed) {
       // Give every load that may still be in flight a bounded chance to land before the CTA's
       // shared memory is released, and leave NaN in the per-column outputs: the error word says
@@ -905,12 +1005,18 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
       return;
     }
   }
+  if (split && p.fixup) {
 #pragma unroll
-  for (int j = 0; j < V; ++j)
-    if (valid[j]) {
-      p.vlast[colj[j]] = v[j];
-      if (MT::kSecond) p.wlast[colj[j]] = w[j];
-    }
+    for (int j = 0; j < V; ++j) v[j] = carry[j];
+  }
+  if (!split || p.fixup) {
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+      if (valid[j]) {
+        p.vlast[colj[j]] = v[j];
+        if (MT::kSecond) p.wlast[colj[j]] = w[j];
+      }
+  }
   if constexpr (MT::kStats) {
     if (p.u_stats) {  // one (sum, sum of squares) pair per warp, lanes added in a fixed order
 #pragma unroll
@@ -935,6 +1041,18 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
                                 const __grid_constant__ CUtensorMap tm4,
                                 const __grid_constant__ CUtensorMap tm_spike) {
   plif_fwd_body<ST, MODE, PACKED, V, C, TMA>(p, tm0, tm1, tm2, tm3, tm4, tm_spike);
+}
+
+// The same scan cut along time (few columns): grid.y = segment in the first launch, and the checking
+// launch (p.fixup) afterwards. Built for the row-parameter family with one lane per thread only.
+template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
+__global__ void plif_fwd_split_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tm0,
+                                      const __grid_constant__ CUtensorMap tm1,
+                                      const __grid_constant__ CUtensorMap tm2,
+                                      const __grid_constant__ CUtensorMap tm3,
+                                      const __grid_constant__ CUtensorMap tm4,
+                                      const __grid_constant__ CUtensorMap tm_spike) {
+  plif_fwd_body<ST, MODE, PACKED, V, C, TMA, true>(p, tm0, tm1, tm2, tm3, tm4, tm_spike);
 }
 
 // Same, held to 160 registers: for the 4-lane resonate-and-fire kernel with the modulation fused in
@@ -1677,8 +1795,35 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   }
   p.stages = plan.stages;
   p.defer = defer_refill(tune, plan, dev);
-  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
-  NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_kernel");
+  // Few columns: cut the time axis into segments that run side by side (see the kernel); needs the
+  // caller's scratch for the segment boundary states.
+  TimeSplit ts;
+  // built for: row-parameter family, tiled copies, one lane per thread, tiles of 16 or 32 steps
+  constexpr bool kSplitBuilt = (MODE == MODE_ROW || MODE == MODE_ROWRES || MODE == MODE_ROWPAT) && TMA && V == 1 &&
+                               (C == 16 || C == 32);
+  if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc);
+  last_time_split() = ts;
+  if (ts.nseg > 1) {
+    if constexpr (kSplitBuilt) {
+      auto skern = plif_fwd_split_kernel<ST, MODE, PACKED, V, C, TMA>;
+      NSB_CUDA_TRY(cudaFuncSetAttribute(skern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem),
+                   "cudaFuncSetAttribute(fwd split)");
+      p.nseg = ts.nseg; p.seg_tiles = ts.seg_tiles; p.warm_tiles = ts.warm_tiles;
+      p.vspec = a.split_scratch;
+      p.vend = a.split_scratch + (size_t)ts.nseg * a.cols;
+      p.fix_count = reinterpret_cast<unsigned int*>(a.split_scratch + 2 * (size_t)ts.nseg * a.cols);
+      NSB_CUDA_TRY(cudaMemsetAsync(p.fix_count, 0, sizeof(unsigned int), a.stream), "clear the rescan counter");
+      p.fixup = 0;
+      skern<<<dim3(plan.grid, ts.nseg), plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
+      NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_split_kernel");
+      p.fixup = 1;
+      skern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
+      NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_split_kernel (check)");
+    }
+  } else {
+    kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
+    NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_kernel");
+  }
   if (MT::kStats && a.u_stats && a.alpha_out) {
     // u is never stored, so its standard deviation is taken at fp32 (no rounding to a storage dtype)
     int r = launch_alpha_finalize(a.u_stats, (int)nwarps, a.T * a.cols, NSB_F32, a.alpha0, a.sigma0, a.alpha_out,
@@ -1686,7 +1831,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
     if (r != NSB_OK) return r;
   }
   li.used_tma = TMA; li.warps_per_cta = plan.wpc; li.stages = plan.stages; li.lanes_per_thread = V;
-  li.grid = plan.grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = 1;
+  li.grid = plan.grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = ts.nseg > 1 ? 2 : 1;
   return NSB_OK;
 }
 

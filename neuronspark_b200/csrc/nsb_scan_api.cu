@@ -116,11 +116,11 @@ int nsb_plif_selective_fwd(const void* beta, const void* u_or_cur, const void* g
 int nsb_plif_rowparam_fwd(const float* beta_row, const void* u, const float* vth_row, const float* v_init,
                           void* spike_dense, uint32_t* spike_packed, void* v_post, float* v_ckpt,
                           float* v_last, int64_t T, int64_t cols, int dtype, int ckpt_interval,
-                          void* stream) {
+                          float* split_scratch, void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
   if (!beta_row || !vth_row || !v_init || !v_last) return NSB_ERR_INVALID_ARG;
-  const void* fp[] = {beta_row, vth_row, v_init, v_last, v_ckpt, spike_packed};
+  const void* fp[] = {beta_row, vth_row, v_init, v_last, v_ckpt, spike_packed, split_scratch};
   for (const void* p : fp)
     if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
   if (T == 0) {
@@ -136,6 +136,7 @@ int nsb_plif_rowparam_fwd(const float* beta_row, const void* u, const float* vth
   a.drive = u; a.beta_row = beta_row; a.vth_row = vth_row; a.v_init = v_init;
   a.spike = spike_dense; a.packed = spike_packed; a.vpost = v_post; a.ckpt = v_ckpt; a.vlast = v_last;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_ROW; a.tile = ckpt_interval;
+  a.split_scratch = split_scratch;
   a.stream = static_cast<cudaStream_t>(stream);
   return run_fwd(a, dtype);
 }
@@ -413,13 +414,13 @@ int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const vo
 int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const float* vth_row,
                                    const float* v_init, const void* frames_in, void* frames_out,
                                    float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
-                                   int ckpt_interval, int rounding, void* stream) {
+                                   int ckpt_interval, int rounding, float* split_scratch, void* stream) {
   if (T < 0 || cols < 0 || T % 16 != 0 || !dtype_ok(dtype) || (ckpt_interval != 16 && ckpt_interval != 32) ||
       (rounding != NSB_RESIDUAL_EAGER && rounding != NSB_RESIDUAL_COMPILED))
     return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
   if (!beta_row || !vth_row || !v_init || !v_last) return NSB_ERR_INVALID_ARG;
-  const void* fp[] = {beta_row, vth_row, v_init, v_last, v_ckpt};
+  const void* fp[] = {beta_row, vth_row, v_init, v_last, v_ckpt, split_scratch};
   for (const void* p : fp)
     if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
   if (T == 0) {
@@ -435,6 +436,7 @@ int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const f
   a.spike = frames_out; a.ckpt = v_ckpt; a.vlast = v_last;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_ROWRES; a.tile = ckpt_interval;
   a.residual_compiled = rounding == NSB_RESIDUAL_COMPILED;
+  a.split_scratch = split_scratch;
   a.stream = static_cast<cudaStream_t>(stream);
   return run_res_fwd(a, dtype);
 }
@@ -442,14 +444,15 @@ int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const f
 int nsb_plif_rowparam_pattern_fwd(const float* beta_row, const void* u, const float* vth_row,
                                   const float* v_init, const uint16_t* patterns_in, uint16_t* patterns_out,
                                   float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
-                                  int ckpt_interval, int frame_dtype, int rounding, void* stream) {
+                                  int ckpt_interval, int frame_dtype, int rounding, float* split_scratch,
+                                  void* stream) {
   if (T < 0 || cols < 0 || T % 16 != 0 || !dtype_ok(dtype) || !dtype_ok(frame_dtype) ||
       (ckpt_interval != 16 && ckpt_interval != 32) ||
       (rounding != NSB_RESIDUAL_EAGER && rounding != NSB_RESIDUAL_COMPILED))
     return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
   if (!beta_row || !vth_row || !v_init || !v_last) return NSB_ERR_INVALID_ARG;
-  const void* fp[] = {beta_row, vth_row, v_init, v_last, v_ckpt};
+  const void* fp[] = {beta_row, vth_row, v_init, v_last, v_ckpt, split_scratch};
   for (const void* p : fp)
     if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
   if (T == 0) {
@@ -466,6 +469,7 @@ int nsb_plif_rowparam_pattern_fwd(const float* beta_row, const void* u, const fl
   a.ckpt = v_ckpt; a.vlast = v_last;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_ROWPAT; a.tile = ckpt_interval;
   a.residual_compiled = rounding == NSB_RESIDUAL_COMPILED;
+  a.split_scratch = split_scratch;
   a.stream = static_cast<cudaStream_t>(stream);
   return run_pat_fwd(a, dtype);
 }

@@ -171,13 +171,27 @@ def _launch_rowparam_fwd(beta_row32, u, vth_row32, v_init32, *, want_spike, want
     C = _interval(cols, row_param=True)
     ckpt = (torch.empty((_n_tiles(T, C), cols), dtype=torch.float32, device=dev) if want_ckpt else None)
     v_last = torch.empty(u.shape[1:], dtype=torch.float32, device=dev)
+    scratch = None if want_vpost else _split_scratch(T, cols, dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().nsb_plif_rowparam_fwd(
             _lib.ptr(beta_row32), _lib.ptr(u), _lib.ptr(vth_row32), _lib.ptr(v_init32),
             _lib.ptr(spike), _lib.ptr(packed), _lib.ptr(vpost), _lib.ptr(ckpt), _lib.ptr(v_last),
-            T, cols, _lib.dtype_code(u.dtype), C, _lib.stream_ptr(dev)),
+            T, cols, _lib.dtype_code(u.dtype), C, _lib.ptr(scratch), _lib.stream_ptr(dev)),
             "nsb_plif_rowparam_fwd")
     return spike, packed, vpost, ckpt, v_last, C
+
+
+#: Scans over at most this many columns and at least this many steps are given scratch memory,
+#: which lets the library cut them along time (see nsb_set_time_split); 592 warp schedulers / 2
+#: segments x 32 columns, and a scan several warm-ups long.
+TIME_SPLIT_MAX_COLS = 9472
+TIME_SPLIT_MIN_STEPS = 4096
+
+
+def _split_scratch(T: int, cols: int, dev):
+    if cols > TIME_SPLIT_MAX_COLS or T < TIME_SPLIT_MIN_STEPS:
+        return None
+    return torch.empty(int(_lib.lib().nsb_time_split_scratch_floats(cols)), dtype=torch.float32, device=dev)
 
 
 def _grad_stream(g, like, dt):
@@ -647,7 +661,7 @@ class PLIFRowParamResidualScan(torch.autograd.Function):
             _lib.check(_lib.lib().nsb_plif_rowparam_residual_fwd(
                 _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(v0), _lib.ptr(fin), _lib.ptr(out),
                 _lib.ptr(ckpt), _lib.ptr(v_last), T, cols, _lib.dtype_code(dt), C,
-                fp16_codec.residual_rounding_code(), _lib.stream_ptr(dev)),
+                fp16_codec.residual_rounding_code(), _lib.ptr(_split_scratch(T, cols, dev)), _lib.stream_ptr(dev)),
                 "nsb_plif_rowparam_residual_fwd")
         if needs_grad:
             ctx.save_for_backward(beta32, vth32, u_c, ckpt)
@@ -707,7 +721,8 @@ def plif_rowparam_forward_patterns(beta_row, u, v_th_row, v_init, patterns_in=No
         _lib.check(_lib.lib().nsb_plif_rowparam_pattern_fwd(
             _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(v0), _lib.ptr(patterns_in), _lib.ptr(out),
             _lib.ptr(ckpt), _lib.ptr(v_last), T, cols, _lib.dtype_code(dt), C, _lib.dtype_code(fdt),
-            fp16_codec.residual_rounding_code(), _lib.stream_ptr(dev)), "nsb_plif_rowparam_pattern_fwd")
+            fp16_codec.residual_rounding_code(), _lib.ptr(_split_scratch(T, cols, dev)), _lib.stream_ptr(dev)),
+            "nsb_plif_rowparam_pattern_fwd")
     return out, v_last, (ckpt, C)
 
 

@@ -1,0 +1,132 @@
+"""Row-parameter forward scans over few columns, cut along time into segments that run side by side
+(nsb_set_time_split): results equal the unsplit scan's bit for bit - with the default warm-up, where
+no segment needs a second pass, and with a warm-up far too short, where the checking launch finds
+the segments whose assumed starting state was wrong and rescans them."""
+import numpy as np
+import pytest
+import torch
+
+import neuronspark_b200 as nsb
+from neuronspark_b200 import _lib, fp16_codec as codec, parallel_scan as ps
+from oracle import oracle as orc
+from util import f32, rowparam_inputs
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+
+
+@pytest.fixture(autouse=True)
+def _clean():
+    nsb.set_tuning()
+    nsb.set_time_split()
+    ps.CKPT_INTERVAL = None
+    yield
+    nsb.set_tuning()
+    nsb.set_time_split()
+    ps.CKPT_INTERVAL = None
+    assert nsb.device_error_word() == 0
+
+
+def unsplit(fn):
+    nsb.set_time_split(1)
+    try:
+        out = fn()
+        assert nsb.last_time_split()["segments"] == 1
+        return out
+    finally:
+        nsb.set_time_split()
+
+
+def test_config1_is_split_and_exact():
+    """B=8, T=8192, D=768 (6144 columns = 192 warps for 592 schedulers): three segments, no rescans,
+    every packed word and final state equal to the unsplit scan and to the oracle."""
+    br, u, tr, v0 = rowparam_inputs(8192, 8, 768, torch.bfloat16, DEV, seed=1234)
+    packed, v_last = ps.plif_rowparam_forward_packed(br, u, tr, v0)
+    ts = nsb.last_time_split()
+    assert ts["segments"] >= 2 and nsb.last_launch_info()["launches"] == 2, ts
+    ref_packed, ref_v = unsplit(lambda: ps.plif_rowparam_forward_packed(br, u, tr, v0))
+    assert torch.equal(packed, ref_packed) and torch.equal(v_last, ref_v)
+    rs, _, rl = orc.plif_rowparam_fwd(f32(br), f32(u), f32(tr), f32(v0), want_vpost=False)
+    assert np.array_equal(f32(ps.unpack_spikes(packed, (8, 768))), rs) and np.array_equal(f32(v_last), rl)
+
+
+def raw_packed_scan(br, u, tr, v0, tile=32):
+    """nsb_plif_rowparam_fwd through the C ABI with the test's own scratch, so that the rescan
+    counter can be read back."""
+    T, cols = u.shape[0], u.shape[1] * u.shape[2]
+    L = _lib.lib()
+    scratch = torch.zeros(int(L.nsb_time_split_scratch_floats(cols)), dtype=torch.float32, device=DEV)
+    packed = torch.empty((T, (cols + 31) // 32), dtype=torch.int32, device=DEV)
+    v_last = torch.empty(u.shape[1:], dtype=torch.float32, device=DEV)
+    p = _lib.ptr
+    _lib.check(L.nsb_plif_rowparam_fwd(p(br), p(u), p(tr), p(v0), None, p(packed), None, None, p(v_last), T, cols,
+                                       _lib.dtype_code(u.dtype), tile, p(scratch), _lib.stream_ptr(DEV)), "fwd")
+    torch.cuda.synchronize()
+    ts = nsb.last_time_split()
+    rescans = int(scratch[2 * ts["segments"] * cols:].view(torch.int32)[0]) if ts["segments"] > 1 else 0
+    return packed, v_last, ts, rescans
+
+
+@pytest.mark.parametrize("segments", [2, 3, 5, 16])
+def test_too_short_a_warm_up_is_caught_and_repaired(segments):
+    br, u, tr, v0 = rowparam_inputs(4096, 2, 200, torch.bfloat16, DEV, seed=segments)
+    ref_packed, ref_v, ts0, _ = unsplit(lambda: raw_packed_scan(br, u, tr, v0))
+    nsb.set_time_split(segments, 32)  # one tile of warm-up: most lanes have not merged by then
+    packed, v_last, ts, rescans = raw_packed_scan(br, u, tr, v0)
+    assert ts["segments"] == segments and ts["warm_tiles"] == 1
+    assert rescans > 0, "a 32-step warm-up cannot have brought every lane to the exact state"
+    assert torch.equal(packed, ref_packed) and torch.equal(v_last, ref_v)
+    nsb.set_time_split(segments, 2048 if segments <= 2 else 4096 // segments // 32 * 32)
+    packed, v_last, ts, rescans = raw_packed_scan(br, u, tr, v0)
+    assert torch.equal(packed, ref_packed) and torch.equal(v_last, ref_v)
+
+
+@pytest.mark.parametrize("shape", [(4096, 2, 96), (4100, 3, 333), (5000, 1, 1001), (4128, 9, 1024)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("warm", [0, 64])
+def test_training_forward_and_gradients_equal_unsplit(shape, dtype, warm):
+    T, B, D = shape
+    br, u, tr, v0 = rowparam_inputs(T, B, D, dtype, DEV, seed=T + D)
+    v0 = 0.1 * torch.randn(B, D, device=DEV)
+    g = (torch.randn(T, B, D, device=DEV) * 0.1).to(dtype)
+
+    def run():
+        leaves = [t.clone().requires_grad_() for t in (br, u, tr, v0)]
+        spike, v_last = ps.plif_rowparam_forward_recompute(*leaves, 4.0)
+        spike.backward(g)
+        return [spike.detach(), v_last.detach()] + [t.grad for t in leaves]
+
+    ref = unsplit(run)
+    nsb.set_time_split(0 if warm == 0 else 4, warm)
+    out = run()
+    if warm:
+        assert nsb.last_launch_info()["launches"] in (1, 2)
+    for a, b, name in zip(out, ref, ("spike", "v_last", "g_beta", "g_u", "g_vth", "g_v0")):
+        assert torch.equal(a, b), name
+    so, _, vl = orc.plif_rowparam_fwd(f32(br), f32(u), f32(tr), f32(v0), want_vpost=False)
+    assert np.array_equal(f32(out[0]), so) and np.array_equal(f32(out[1]), vl)
+
+
+@pytest.mark.parametrize("warm", [0, 32])
+def test_residual_and_pattern_scans_equal_unsplit(warm):
+    S, B, D = 256, 4, 768
+    br, u, tr, v0 = rowparam_inputs(S * 16, B, D, torch.bfloat16, DEV, seed=21)
+    u = u * 3.0
+    fin = (torch.rand(S * 16, B, D, device=DEV) < 0.4).to(torch.bfloat16)
+    pin = codec.pack_frames(fin)
+    ref_res = unsplit(lambda: ps.plif_rowparam_residual_forward(br, u, tr, v0, fin, 4.0))
+    ref_pat = unsplit(lambda: ps.plif_rowparam_forward_patterns(br, u, tr, v0, patterns_in=pin))
+    nsb.set_time_split(0 if warm == 0 else 6, warm)
+    res = ps.plif_rowparam_residual_forward(br, u, tr, v0, fin, 4.0)
+    assert nsb.last_time_split()["segments"] >= 2
+    pat = ps.plif_rowparam_forward_patterns(br, u, tr, v0, patterns_in=pin)
+    assert nsb.last_time_split()["segments"] >= 2
+    assert torch.equal(res[0], ref_res[0]) and torch.equal(res[1], ref_res[1])
+    assert torch.equal(pat[0], ref_pat[0]) and torch.equal(pat[1], ref_pat[1])
+    assert torch.equal(pat[0], codec.pack_frames(res[0]))
+
+
+def test_large_problems_are_left_alone():
+    br, u, tr, v0 = rowparam_inputs(4096, 16, 768, torch.bfloat16, DEV, seed=2)  # 12 288 columns
+    ps.plif_rowparam_forward_packed(br, u, tr, v0)
+    assert nsb.last_time_split()["segments"] == 1 and nsb.last_launch_info()["launches"] == 1
