@@ -101,6 +101,20 @@ int nsb_set_wait_limit_ns(uint64_t ns);
 int nsb_selftest_wait_timeout(void* stream);
 
 /*
+ * One element type per call. Every [T, cols] tensor of a scan call ("stream") has the call's
+ * `dtype`; per-column vectors are fp32. The reference widens each pointer from its own element
+ * type (tl.load(...).to(tl.float32), atomic_ops/parallel_scan.py:223-225) and returns each
+ * gradient in its input's type (:752-755), so a call with, say, fp32 beta and bf16 u is legal
+ * there. Here such a caller first brings the streams to one type - fp32 if they differ, which
+ * is exact - and converts outputs back where it needs to, with this kernel (widening exact,
+ * narrowing round-to-nearest-even); the Python mirror does exactly that. A type per tensor
+ * would multiply the scan kernels by 3^4 instantiations for a case the reference's own layers
+ * do not produce (under autocast all modulation outputs are fp32, under bf16 parameters all
+ * are bf16).
+ */
+int nsb_convert(const void* src, void* dst, int64_t n, int src_dtype, int dst_dtype, void* stream);
+
+/*
  * Time split of the row-parameter forward scans over few columns. A scan over a few thousand
  * columns occupies a few hundred warps while each warp is bound by its own serial chain over T;
  * the other SMs idle. Given scratch memory (`split_scratch` of nsb_plif_rowparam_fwd,
@@ -324,9 +338,12 @@ int nsb_lateral_inhibition_bwd(const void* g_out, const void* x, const void* gai
  * Cost and limits:
  *  - the array is 524 288 floats (2 MiB) of device memory on every GPU that
  *    loads the library, held until the process exits;
- *  - D may not exceed 524 288 (NSB_ERR_TOO_LARGE otherwise); when
- *    (CTAs the normal entry point would use) * D exceeds the array, fewer CTAs
- *    are launched, so very wide rows run slower than with caller scratch;
+ *  - D may not exceed 58 112 (NSB_ERR_TOO_LARGE otherwise): one warp's fp32 row of
+ *    partial sums has to fit the 227 KB of shared memory a CTA can have, which is
+ *    the bound of nsb_lateral_inhibition_bwd as well; the array itself would hold
+ *    rows of up to 524 288. When (CTAs the normal entry point would use) * D
+ *    exceeds the array, fewer CTAs are launched, so rows wider than 1 771 floats
+ *    run slower than with caller scratch;
  *  - the first call on each device looks up the array's device address
  *    (with that device current). Make that first call outside any stream
  *    capture; later calls do no set-up;

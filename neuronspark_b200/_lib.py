@@ -39,6 +39,7 @@ _SIGNATURES = {
     "nsb_plif_selective_bwd": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int,
                                                           c_float, c_void_p]),
     "nsb_plif_rowparam_fwd": (c_int, [c_void_p] * 9 + [c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "nsb_convert": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "nsb_set_time_split": (c_int, [c_int, c_int]),
     "nsb_time_split_scratch_floats": (c_int64, [c_int64]),
     "nsb_last_time_split": (c_int, [ctypes.POINTER(c_int32)]),
@@ -187,6 +188,23 @@ def scan_plan(backward: bool, nstreams: int, elem_size: int, T: int, cols: int, 
     check(lib().nsb_scan_plan_query(int(backward), nstreams, elem_size, T, cols, tile, out),
           "nsb_scan_plan_query")
     return dict(zip(("lanes_per_thread", "warps_per_cta", "stages", "grid", "smem_bytes"), out))
+
+
+def convert(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """``t`` as a contiguous tensor of ``dtype`` (fp32 / bf16 / fp16), converted by the library's own
+    kernel: no framework elementwise op on the path. Detached; a tensor that already has the type is
+    returned as it is (made contiguous)."""
+    t = t.detach()
+    if t.dtype == dtype:
+        return t.contiguous()
+    if t.dtype not in _DTYPES or not t.is_cuda:
+        return t.to(dtype).contiguous()  # integer / double / CPU inputs: not a stream the kernels take anyway
+    src = t.contiguous()
+    out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        check(lib().nsb_convert(ptr(src), ptr(out), src.numel(), dtype_code(src.dtype), dtype_code(dtype),
+                                stream_ptr(src.device)), "nsb_convert")
+    return out
 
 
 def set_time_split(max_segments: int = 0, warm_steps: int = 0) -> None:

@@ -114,6 +114,12 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
     // Scans of a few tiles only (per-token decoding) are dominated by CTA start-up;
     // measured: 2 lanes per thread (twice the CTAs per SM) beat 4 by ~20 % at T = 16.
     if (tune.lanes_per_thread <= 0 && ntiles <= 8 && lanes > 2) continue;
+    // 16-step tiles of the selective / resonate-and-fire scans over 32 K columns and more: 2 lanes per
+    // thread (measured at 49 152 columns, T = 8192, bf16: forward 649 us against 742 with 1 lane,
+    // forward + backward 2.16 ms against 2.27)
+    if (tune.lanes_per_thread <= 0 && q.tile == 16 && q.nstreams >= 3 && q.cols >= 32768 && q.max_lanes >= 2 &&
+        lanes != 2)
+      continue;
     const long long nwarps = (q.cols + 32LL * lanes - 1) / (32LL * lanes);
     const size_t tile_bytes = (size_t)q.tile * 32 * lanes * q.elem_size;
     const size_t stage_bytes = tile_bytes * q.nstreams;

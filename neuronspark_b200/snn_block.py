@@ -136,9 +136,7 @@ class ModulatedPLIFScan(torch.autograd.Function):
                                v_init, w_init))
         ctx.bias_shapes = tuple(None if b is None else b.shape for b in (b_beta, b_alpha, b_th, b_omega))
         ctx.state_shapes = (v_init.shape, None if w_init is None else w_init.shape)
-        out_dtype = I_all.dtype
-        if spike.dtype != out_dtype:
-            spike = spike.to(out_dtype)
+        spike = ps._cast(spike, I_all.dtype)
         v_last = v_last.to(v_init.dtype)
         if rf:
             w_last = w_last.to(w_init.dtype)
@@ -179,8 +177,8 @@ class ModulatedPLIFScan(torch.autograd.Function):
         def bias_out(i):
             return g_bias[i].to(d[5 + i]).reshape(sh[i])
 
-        return (g_rb.to(d[0]), g_ra.to(d[1]), g_rt.to(d[2]), g_ci.to(d[3]),
-                g_ro.to(d[4]) if rf else None, bias_out(0), bias_out(1), bias_out(2),
+        return (ps._cast(g_rb, d[0]), ps._cast(g_ra, d[1]), ps._cast(g_rt, d[2]), ps._cast(g_ci, d[3]),
+                ps._cast(g_ro, d[4]) if rf else None, bias_out(0), bias_out(1), bias_out(2),
                 bias_out(3) if rf else None, g_v0.to(d[9]).reshape(ctx.state_shapes[0]),
                 g_w0.to(d[10]).reshape(ctx.state_shapes[1]) if rf else None, None, None, None, None)
 
