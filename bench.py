@@ -81,9 +81,12 @@ MODEL_WORKLOADS = {
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per neuron-step measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
 # reduced-T case "c2-short" (same grid, T=512); traffic of these kernels is proportional to T, so a
-# full launch moves this many bytes per neuron-step too (profiles/plif_scan_c2short_ncu_full.md).
-NCU_TRAFFIC_FWD = (806.124e6 + 229.413e6) / (32 * 512 * 6144)
-NCU_TRAFFIC_BWD = (1057.017e6 + 765.601e6) / (32 * 512 * 6144)
+# full launch moves this many bytes per neuron-step too. The figures are those of the capture
+# summarised in profiles/plif_scan_c2short_ncu_full.md, taken on the kernels as they are after the
+# forward body gained its time-split and pattern-output variants and 4-warp CTAs; re-take that
+# capture (the T=512 case only) whenever csrc/nsb_scan.cuh changes - the bench does not measure it.
+NCU_TRAFFIC_FWD = (806.145e6 + 230.985e6) / (32 * 512 * 6144)
+NCU_TRAFFIC_BWD = (1057.019e6 + 764.452e6) / (32 * 512 * 6144)
 
 
 def parse_args():
@@ -97,6 +100,8 @@ def parse_args():
                     + sorted(MODEL_WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-split", action="store_true",
+                    help="few-column workloads (c1, res): run the scan as one serial launch, not cut along time")
     return ap.parse_args()
 
 
@@ -648,6 +653,8 @@ def run_inference(args):
     unfused = None
     # scratch that lets the library cut a scan over few columns along time (NULL for the others)
     split_scratch = ps._split_scratch(T, cols, dev)
+    if args.no_split:
+        _lib.set_time_split(1)
     if w["kind"] == "rowres":
         from neuronspark_b200 import fp16_codec as codec
         g = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -778,7 +785,16 @@ def run_inference(args):
             "config": {"workload": f"{args.workload}: {w['kind']} forward, {'residual frames out' if w['kind'] == 'rowres' else 'packed spikes'}, B={total_b} global "
                                    f"({B} on this GPU), T={T} x {calls} call(s), D={D}, bf16 streams, fp32 state",
                        "l2": "L2 flushed between iterations" if flush is not None else "inputs larger than L2",
-                       "launch": info, "call_loop": graph_note, "eager_ms_per_step": eager_ms},
+                       "launch": info, "time_split": _lib.last_time_split(), "call_loop": graph_note,
+                       "eager_ms_per_step": eager_ms,
+                       # the serial chain bound for scans over few columns: ~4 dependent fp32 operations of
+                       # ~4-5 cycles each per step, against the cycles a warp actually spends per step
+                       "cycles_per_step_per_warp": (ms * 1e-3 * (clocks or {}).get("sm_mhz", 0) * 1e6
+                                                    / max(1, (T * calls if _lib.last_time_split()["segments"] == 1 else
+                                                              (_lib.last_time_split()["seg_tiles"]
+                                                               + _lib.last_time_split()["warm_tiles"]) * info["tile_steps"])))
+                       if cols < 100000 and clocks and clocks.get("sm_mhz") else None,
+                       "chain_bound_cycles_per_step": "16-24" if cols < 100000 else None},
             "roofline": {"bound": "hbm", "kernel": "plif_fwd_kernel", "achieved": ach, "peak": peak,
                          "unit": "GB/s", "frac": ach / peak, "traffic": None, "peak_source": peak_src,
                          "algorithmic_bytes_per_neuron_step": w["bytes_per_ns"],

@@ -3,7 +3,8 @@
 TEST INFRASTRUCTURE ONLY: imported by the test suite, by the smoke check and by
 the benchmark's CPU-baseline leg, never by the shipped package. Parity of the
 C restatement against the reference is pinned by the committed golden vectors
-(see ``tests/golden/make_golden.py``); the arctangent surrogate is unpinned.
+(see ``tests/golden/make_golden.py``); the arctangent surrogate, which the reference's fused
+kernels lack, is pinned to torch autograd through its published primitive by the same script.
 
 Every function takes and returns ``numpy.float32`` arrays in the reference's
 layouts: scans are time-major ``[T, ...]`` with the trailing dims flattened to

@@ -10,8 +10,11 @@
  * Parity status: PINNED for the forward scans, the sigmoid-surrogate backward,
  * the codec and the normaliser (checked in the test suite against vectors
  * produced by running the reference's own Python on CPU). The arctangent
- * surrogate has no counterpart in the reference: its parity is UNPINNED and it
- * is defined here as g'(x) = (a/2) / (1 + (pi/2 * a * x)^2).
+ * surrogate has no counterpart in the reference's fused kernels; it is pinned
+ * to its published definition instead: g'(x) = (a/2) / (1 + (pi/2 * a * x)^2)
+ * written here by hand must equal, to 1e-5, what torch autograd derives from
+ * the primitive g(x) = atan(pi/2 * a * x) / pi + 1/2 through the reference
+ * test's time loop (fixture scan_ai_bwd_atan of tests/golden/make_golden.py).
  *
  * Arithmetic contract: every state update is one rounded fp32 multiply
  * followed by one rounded fp32 add (no fused multiply-add), which is what the
@@ -152,7 +155,8 @@ void orc_plif_rowparam_fwd(const float *beta_row, const float *u,
 /* Surrogate derivative, evaluated in double so that the oracle is the
  * "true" value the fp32 kernels are compared against.
  * Sigmoid: atomic_ops/parallel_scan.py:291-296 (argument of exp clamped at
- * 88). Arctangent: no counterpart in the reference (unpinned). */
+ * 88). Arctangent: derivative of atan(pi/2*a*x)/pi + 1/2 (checked against
+ * autograd through that primitive by the golden fixture scan_ai_bwd_atan). */
 static inline double surr_grad(double x, double a, int kind) {
   if (kind == ORC_SURR_ATAN) {
     double z = 1.5707963267948966 * a * x;
