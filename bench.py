@@ -100,6 +100,8 @@ def parse_args():
                     + sorted(MODEL_WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--fused-layers", action="store_true",
+                    help="c3: also time install(fused_layers=True), the layers on the fused kernels")
     ap.add_argument("--no-split", action="store_true",
                     help="few-column workloads (c1, res): run the scan as one serial launch, not cut along time")
     return ap.parse_args()
@@ -947,6 +949,21 @@ def run_model(args):
     finite = bool(torch.isfinite(logits).all())
     spike_calls = len(changed)
     inst.uninstall()
+    if args.fused_layers:  # the layers' call sequence changed as well: neuronspark_b200.layers
+        inst.install(fused_layers=True)
+        with torch.no_grad():
+            for _ in range(W):
+                m(tokens)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(K):
+                logits_f = m(tokens).logits
+            b.record()
+            torch.cuda.synchronize()
+        note["fused_layers"] = {"ms_per_step": a.elapsed_time(b) / K,
+                                "argmax_agreement_with_unfused": float((logits_f.argmax(-1) == logits.argmax(-1)).float().mean())}
+        inst.uninstall()
     try:  # the same model object on the reference's own Triton kernels
         ms_ref, parts_ref, logits_ref = time_arm(m, K, W)
         arms["reference_triton"] = (ms_ref, parts_ref)

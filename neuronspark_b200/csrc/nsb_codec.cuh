@@ -114,15 +114,54 @@ __device__ __forceinline__ void pattern_to_bits(uint32_t pat, float (&bit)[16]) 
   for (int i = 0; i < 16; ++i) bit[i] = ((pat >> (15 - i)) & 1u) ? 1.0f : 0.0f;
 }
 
+// decode16<false> of the frames a pattern stands for, straight from the bits. With frames in
+// {0,1} every intermediate of the reference's formula is exact in fp32 (the mantissa sum has 10
+// bits, 1+m has 11, the scale is a power of two), so the value is the fp32 number with the
+// pattern's sign, exponent e + 112 and mantissa m << 13 - for every e from 1 to 31, an all-ones
+// exponent included (the formula reads it as an ordinary normal number) - and sign * m * 2^-24
+// for e = 0. A handful of integer instructions instead of sixteen selects and forty flops.
+__device__ __forceinline__ float decode_pattern_exact(uint32_t pat) {
+  const uint32_t sign = (pat & 0x8000u) << 16, e = (pat >> 10) & 31u, m = pat & 1023u;
+  const float normal = __uint_as_float(sign | ((e + 112u) << 23) | (m << 13));
+  const float sub = __uint_as_float(sign | __float_as_uint((float)m * 5.9604644775390625e-08f));
+  return e ? normal : sub;
+}
+
+// encode(decode(a) + decode(b)) given the two decoded values: the sum's rounding for frames stored
+// in DTYPE, then the half pattern.
+template <int DTYPE>
+__device__ __forceinline__ uint32_t half_bits_of_sum(float va, float vb) {
+  float sum = va + vb;
+  if (DTYPE == NSB_BF16) sum = round_through_bf16(sum);
+  if (DTYPE == NSB_F16) sum = __half2float(__float2half_rn(sum));
+  return half_bits_clamped(sum);
+}
+
+// residual_half_bits with the first operand given as a pattern (the scan's own spikes) and the
+// second as 16 frames.
+template <int DTYPE>
+__device__ __forceinline__ uint32_t residual_pattern_frames(uint32_t pa, const float (&b)[16], bool compiled) {
+  if (DTYPE == NSB_BF16 && !compiled) {
+    float a[16];
+    pattern_to_bits(pa, a);
+    return residual_half_bits<DTYPE>(a, b, false);
+  }
+  return half_bits_of_sum<DTYPE>(decode_pattern_exact(pa), decode16<false>(b));
+}
+
 // residual_half_bits on two patterns, with the roundings of frames stored in `frame_dtype`
 // (a run-time value here: packed patterns have no element type of their own).
 __device__ __forceinline__ uint32_t residual_of_patterns(uint32_t pa, uint32_t pb, int frame_dtype, bool compiled) {
-  float a[16], b[16];
-  pattern_to_bits(pa, a);
-  pattern_to_bits(pb, b);
-  if (frame_dtype == NSB_BF16) return residual_half_bits<NSB_BF16>(a, b, compiled);
-  if (frame_dtype == NSB_F16) return residual_half_bits<NSB_F16>(a, b, compiled);
-  return residual_half_bits<NSB_F32>(a, b, compiled);
+  if (frame_dtype == NSB_BF16 && !compiled) {
+    float a[16], b[16];
+    pattern_to_bits(pa, a);
+    pattern_to_bits(pb, b);
+    return residual_half_bits<NSB_BF16>(a, b, false);
+  }
+  const float va = decode_pattern_exact(pa), vb = decode_pattern_exact(pb);
+  if (frame_dtype == NSB_BF16) return half_bits_of_sum<NSB_BF16>(va, vb);
+  if (frame_dtype == NSB_F16) return half_bits_of_sum<NSB_F16>(va, vb);
+  return half_bits_of_sum<NSB_F32>(va, vb);
 }
 
 }  // namespace codec

@@ -117,9 +117,13 @@ __global__ void decode_packed_fwd_kernel(const uint16_t* __restrict__ pats, T* _
     Vec<T, VE> o;
 #pragma unroll
     for (int j = 0; j < VE; ++j) {
-      float bit[16];
-      pattern_to_bits(p.v[j], bit);
-      o.v[j] = Elem<T>::from_f32(decode16<EMU>(bit));
+      if constexpr (EMU) {  // bf16 frames decode with bf16 intermediates (the reference calls fp16_decode eagerly)
+        float bit[16];
+        pattern_to_bits(p.v[j], bit);
+        o.v[j] = Elem<T>::from_f32(decode16<true>(bit));
+      } else {
+        o.v[j] = Elem<T>::from_f32(codec::decode_pattern_exact(p.v[j]));
+      }
     }
     *reinterpret_cast<Vec<T, VE>*>(values + (t.b * S + t.s) * D + t.d) = o;
   }

@@ -759,13 +759,10 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
           uint32_t h[V];
 #pragma unroll
           for (int j = 0; j < V; ++j) {
-            float a_[16], b_[16];
+            float b_[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              a_[i] = ((hb[j] >> (15 - i)) & 1u) ? 1.0f : 0.0f;
-              b_[i] = fb[i][j];
-            }
-            h[j] = codec::residual_half_bits<E::kDtype>(a_, b_, p.residual_compiled != 0);
+            for (int i = 0; i < 16; ++i) b_[i] = fb[i][j];
+            h[j] = codec::residual_pattern_frames<E::kDtype>(hb[j], b_, p.residual_compiled != 0);
           }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {

@@ -57,12 +57,16 @@ def _reference_modules(package: str) -> dict[str, ModuleType]:
     return found
 
 
-def install(package: str = "atomic_ops", extra_modules=()) -> list[str]:
+def install(package: str = "atomic_ops", extra_modules=(), fused_layers: bool = False) -> list[str]:
     """Patches the imported reference modules; returns ``module.name`` strings changed.
 
     ``package`` is the import name of the reference's operator package.
     ``extra_modules`` are further already-imported modules to scan for
-    by-name imports (``model`` is scanned automatically when present)."""
+    by-name imports (``model`` is scanned automatically when present).
+    ``fused_layers``: also replace ``SNNBlock.forward_parallel`` and ``SNNFFN.forward_parallel`` by
+    the bodies of ``neuronspark_b200.layers``, which call the fused kernels (modulation inside the
+    resonate-and-fire scan, output scan + residual in one kernel, surrogate slope kept on the
+    device). Off by default: it changes the layers' call sequence, not just the kernels under it."""
     refs = _reference_modules(package)
     if not refs:
         raise RuntimeError(f"no module of the reference package {package!r} has been imported")
@@ -101,6 +105,16 @@ def install(package: str = "atomic_ops", extra_modules=()) -> list[str]:
                 _undo.append((mod, attr, val))
                 setattr(mod, attr, hit[1])
                 changed.append(f"{mod.__name__}.{attr}")
+    if fused_layers:
+        from . import layers
+        for short, cls_name, body in (("snn_block", "SNNBlock", layers.snn_block_forward_parallel),
+                                      ("snn_ffn", "SNNFFN", layers.snn_ffn_forward_parallel)):
+            mod = sys.modules.get(f"{package}.{short}")
+            cls = getattr(mod, cls_name, None) if mod is not None else None
+            if cls is not None:
+                _undo.append((cls, "forward_parallel", cls.__dict__["forward_parallel"]))
+                cls.forward_parallel = body
+                changed.append(f"{mod.__name__}.{cls_name}.forward_parallel")
     return changed
 
 

@@ -91,6 +91,17 @@ def test_install_rebinds_the_real_reference(reference):
     assert model.fp16_encode.__module__ == "atomic_ops.fp16_codec"
 
 
+def test_fused_layers_are_patched_and_restored(reference):
+    ao, _ = reference
+    from neuronspark_b200 import install as inst, layers
+    block_fwd, ffn_fwd = ao.snn_block.SNNBlock.forward_parallel, ao.snn_ffn.SNNFFN.forward_parallel
+    changed = inst.install(fused_layers=True)
+    assert ao.snn_block.SNNBlock.forward_parallel is layers.snn_block_forward_parallel
+    assert ao.snn_ffn.SNNFFN.forward_parallel is layers.snn_ffn_forward_parallel
+    assert inst.uninstall() == len(changed)
+    assert ao.snn_block.SNNBlock.forward_parallel is block_fwd and ao.snn_ffn.SNNFFN.forward_parallel is ffn_fwd
+
+
 def test_library_refuses_cpu_tensors_when_installed(reference):
     """No silent fallback: the reference's model on CPU tensors, once rebound, raises."""
     _, model = reference

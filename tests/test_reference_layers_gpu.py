@@ -256,3 +256,47 @@ def test_reference_triton_path_agrees(reference):
         except Exception as e:  # Triton JIT / ptxas not usable here
             pytest.skip(f"the reference's Triton path does not run here: {type(e).__name__}: {str(e)[:200]}")
     assert abs(ours - theirs) <= 0.05 * abs(theirs), (ours, theirs)
+
+
+def test_fused_layers_train_and_agree_with_the_unfused_ones(abi_calls):
+    """``install(fused_layers=True)``: the reference's layers on the fused kernels (modulation inside the
+    hidden scan, output scan + residual in one kernel, no host round trip for the surrogate slope). The
+    calls land where they should, every parameter still gets a gradient, and in fp32 the outputs agree
+    with the kernel-for-kernel installation except where a hidden membrane potential sits within
+    rounding of its threshold. (A bf16 model differs more: the unfused layer rounds beta, u, v_th and
+    omega to bf16 between modulation and scan, the fused one never does.)"""
+    from neuronspark_b200 import install as inst
+    ao, model = rh.load_reference(eager_elementwise=True)
+    try:
+        g = torch.Generator(device=DEV).manual_seed(7)
+        x = torch.randint(0, 256, (2, 16), device=DEV, generator=g)
+        y = torch.randint(1, 256, (2, 16), device=DEV, generator=g)
+        m32, m16 = tiny_model(model, torch.float32), tiny_model(model, torch.bfloat16)
+        inst.install()
+        with torch.no_grad():
+            ref_logits = m32(x).logits
+        ref_loss = m16(x, y).last_loss.float().mean().item()
+        inst.uninstall()
+        changed = inst.install(fused_layers=True)
+        assert "atomic_ops.snn_block.SNNBlock.forward_parallel" in changed
+        abi_calls.clear()
+        with torch.no_grad():
+            logits = m32(x).logits
+        L = len(m32.layers)
+        assert abi_calls["nsb_plif_modulated_fwd"] == L and abi_calls["nsb_plif_rf_fwd"] == 0
+        assert abi_calls["nsb_plif_rowparam_residual_fwd"] == 2 * L and abi_calls["nsb_binary_residual"] == 0
+        assert abi_calls["nsb_plif_rowparam_fwd"] == L  # the FFN's gate + up scan keeps its spikes for the AND
+        agree = (logits.argmax(-1) == ref_logits.argmax(-1)).float().mean().item()
+        assert agree >= 0.9, agree
+        abi_calls.clear()
+        loss = m16(x, y).last_loss.mean()
+        loss.backward()
+        torch.cuda.synchronize()
+        assert abs(loss.item() - ref_loss) <= 0.1 * abs(ref_loss), (loss.item(), ref_loss)
+        bad = [n for n, p in m16.named_parameters()
+               if p.grad is None or not torch.isfinite(p.grad).all() or not p.grad.abs().sum() > 0]
+        assert not bad, bad
+        assert abi_calls["nsb_plif_modulated_bwd"] == L and abi_calls["nsb_surrogate_alpha"] >= 3 * L
+    finally:
+        inst.uninstall()
+    assert ao.snn_block.SNNBlock.forward_parallel.__module__ == "atomic_ops.snn_block"
