@@ -42,7 +42,7 @@ def test_install_patches_definitions_and_by_name_imports(fake_reference):
     assert ffn.plif_rowparam_forward_recompute is parallel_scan.plif_rowparam_forward_recompute
     assert ffn.binary_residual is fp16_codec.binary_residual
     assert "fake_atomic_ops.snn_ffn.binary_residual" in changed
-    # what this package does not implement stays the reference's
+    # the linear recurrence is rebound too; what this package has no kernel for stays the reference's
     assert ps.linear_recurrence is parallel_scan.linear_recurrence
     assert ps.hillis_steele_scan is rf and ffn.unrelated == 7
     assert inst.uninstall() == len(changed)
