@@ -118,7 +118,8 @@ int nsb_convert(const void* src, void* dst, int64_t n, int src_dtype, int dst_dt
  * Time split of the row-parameter forward scans over few columns. A scan over a few thousand
  * columns occupies a few hundred warps while each warp is bound by its own serial chain over T;
  * the other SMs idle. Given scratch memory (`split_scratch` of nsb_plif_rowparam_fwd,
- * nsb_plif_rowparam_residual_fwd and nsb_plif_rowparam_pattern_fwd: NULL, or
+ * nsb_plif_rowparam_residual_fwd, nsb_plif_rowparam_pattern_fwd, nsb_plif_rowparam_bwd and
+ * nsb_plif_rowparam_bwd_dalpha: NULL, or
  * nsb_time_split_scratch_floats(cols) floats of device memory that the call may overwrite), such a
  * scan is cut along time into up to 16 segments that run side by side: a later segment is entered
  * `warm_steps` early from V = 0 and keeps what it computes from its own first step on - PLIF
@@ -126,7 +127,11 @@ int nsb_convert(const void* src, void* dst, int64_t n, int src_dtype, int dst_dt
  * started apart - and a second launch compares every segment's assumed starting state with the
  * exact one, bit for bit, and rescans the segments where they differ. Results therefore equal the
  * unsplit scan's exactly for every input; only the time taken depends on how often a rescan is
- * needed. The reference has no counterpart (its kernels walk T serially, one program per 128
+ * needed. The backward is cut the same way, walking each segment from its last step to its first:
+ * its adjoint recurrence acc' = beta*(acc + ...) forgets its starting value as the forward forgets
+ * its state, grad_u and grad_v_init come out bit-identical to the serial launch, and the sums over
+ * time of grad_beta_row / grad_v_th_row are added up segment by segment (same terms, another
+ * association: equal to the serial sums to fp32 rounding, and deterministic). The reference has no counterpart (its kernels walk T serially, one program per 128
  * columns, atomic_ops/parallel_scan.py:496-530).
  *
  * nsb_set_time_split      max_segments: 0 = automatic, 1 = never split, 2..16 = at most that many
@@ -135,7 +140,7 @@ int nsb_convert(const void* src, void* dst, int64_t n, int src_dtype, int dst_dt
  * nsb_last_time_split     {segments, tiles per segment, warm-up tiles} of the calling thread's last
  *                         forward scan launch (segments = 1: it was not split). After a split
  *                         launch the number of rescanned (warp, segment) pairs is the uint32 at
- *                         split_scratch[2*segments*cols].
+ *                         split_scratch[2*segments*cols] (forward) / [4*segments*cols] (backward).
  */
 int nsb_set_time_split(int max_segments, int warm_steps);
 int64_t nsb_time_split_scratch_floats(int64_t cols);
@@ -237,7 +242,8 @@ int nsb_plif_rowparam_bwd(const float* beta_row, const void* u, const float* vth
                           const float* v_ckpt, const void* g_spike, const void* g_vpost,
                           float* g_beta_row, void* g_u, float* g_vth_row, float* g_vinit,
                           int64_t T, int64_t cols, int dtype, int ckpt_interval,
-                          int surrogate, float alpha, void* stream);
+                          int surrogate, float alpha, float* split_scratch,
+                          void* stream);
 
 /*
  * Resonate-and-fire (second-order) PLIF scan, forward. Replaces
@@ -440,7 +446,8 @@ int nsb_plif_rowparam_bwd_dalpha(const float* beta_row, const void* u, const flo
                                  const float* v_ckpt, const void* g_spike, const void* g_vpost,
                                  float* g_beta_row, void* g_u, float* g_vth_row, float* g_vinit,
                                  int64_t T, int64_t cols, int dtype, int ckpt_interval,
-                                 int surrogate, const float* alpha_dev, void* stream);
+                                 int surrogate, const float* alpha_dev,
+                                 float* split_scratch, void* stream);
 int nsb_plif_rf_bwd_dalpha(const void* beta, const void* omega, const void* u, const void* v_th,
                            const float* v_ckpt, const float* w_ckpt, const void* g_spike,
                            const void* g_vpost, void* g_beta, void* g_omega, void* g_u,

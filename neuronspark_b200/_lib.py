@@ -44,7 +44,7 @@ _SIGNATURES = {
     "nsb_time_split_scratch_floats": (c_int64, [c_int64]),
     "nsb_last_time_split": (c_int, [ctypes.POINTER(c_int32)]),
     "nsb_plif_rowparam_bwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_int,
-                                                         c_float, c_void_p]),
+                                                         c_float, c_void_p, c_void_p]),
     "nsb_plif_rf_fwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_plif_rf_bwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_float,
                                                    c_void_p]),
@@ -57,7 +57,7 @@ _SIGNATURES = {
     "nsb_surrogate_alpha_scratch_doubles": (c_int64, []),
     "nsb_surrogate_alpha": (c_int, [c_void_p, c_int64, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p]),
     "nsb_plif_rowparam_bwd_dalpha": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_int,
-                                                                c_void_p, c_void_p]),
+                                                                c_void_p, c_void_p, c_void_p]),
     "nsb_plif_rf_bwd_dalpha": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
                                                           c_void_p]),
     "nsb_plif_rowparam_residual_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,

@@ -201,7 +201,7 @@ constexpr int kMaxSegments = 16;
 
 TimeSplit& last_time_split() { return g_last_split; }
 
-long long time_split_scratch_floats(long long cols) { return 2LL * kMaxSegments * cols + 4; }
+long long time_split_scratch_floats(long long cols) { return 4LL * kMaxSegments * cols + 4; }  // the backward keeps 4 rows per segment
 
 TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, int tile, int lanes, int wpc) {
   TimeSplit ts;

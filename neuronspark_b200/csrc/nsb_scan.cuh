@@ -120,6 +120,7 @@ struct BwdArgs {
   int surrogate = NSB_SURR_SIGMOID;
   float alpha = 4.0f;
   const float* alpha_dev = nullptr;  // when set, the surrogate slope is read from device memory
+  float* split_scratch = nullptr;    // optional: nsb_time_split_scratch_floats(cols) floats; enables the time split
   cudaStream_t stream = nullptr;
 };
 
@@ -1104,6 +1105,18 @@ struct BwdParams {
   const float* alpha_dev;
   uint32_t* err;
   unsigned long long wait_ns;  // limit of the bounded barrier waits
+  // Time split (few columns, row-parameter scan), as in the forward: nseg segments of seg_tiles
+  // tiles run side by side, here from their last tile to their first. A segment other than the
+  // last one starts warm_tiles later in time with a zero adjoint and keeps only what it computes
+  // from its own last tile on. [nseg, cols] arrays: aspec = the adjoint a segment assumed on
+  // entering its own part, aend = the adjoint it handed on, partb / partt = its share of the sums
+  // over time of the row gradients. fixup = 1: the checking launch.
+  int nseg, seg_tiles, warm_tiles, fixup;
+  float* aspec;
+  float* aend;
+  float* partb;
+  float* partt;
+  unsigned int* fix_count;
 };
 
 // Warps that share one TMA box in the backward kernel. DRAM efficiency of the tiled copies
@@ -1166,7 +1179,7 @@ __device__ __forceinline__ void surrogate_grad(float (&sg)[V], const float (&x)[
   }
 }
 
-template <typename ST, int MODE, int SURR, int V, int C, bool TMA, bool HAS_GV>
+template <typename ST, int MODE, int SURR, int V, int C, bool TMA, bool HAS_GV, bool SPLIT = false>
 __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == MODE_MOD) ? 128 : (MODE == MODE_RFMOD ? 168 : kBwdMaxRegs)) : ((TMA && C * V == 32 && MODE != MODE_RF && MODE != MODE_RFMOD) ? kBwdMaxRegsV4 : 255)) plif_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tm0,
                                 const __grid_constant__ CUtensorMap tm1,
                                 const __grid_constant__ CUtensorMap tm2,
@@ -1283,12 +1296,6 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   };
 
   const int ntiles = p.ntiles;
-  if constexpr (TMA) {
-    if (leader) {
-      const int pre = ntiles < stages ? ntiles : stages;
-      for (int s = 0; s < pre; ++s) issue(ntiles - 1 - s, s);
-    }
-  }
 
   const ST* sp = nullptr;  // this thread's first element inside the current stage
   ST regs[TMA ? 1 : (NF + 2) * C * V] = {};
@@ -1313,15 +1320,10 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   float vnext[V], w[V], wnext[V];
 #pragma unroll
   for (int j = 0; j < V; ++j) vnext[j] = w[j] = wnext[j] = 0.0f;
-  if constexpr (TMA) {
-    if (ntiles > 0 && valid[0]) {
-      VecIO<float, V>::load(p.ckpt + (long long)(ntiles - 1) * row_elems + colj[0], vnext);
-      if (MT::kSecond) VecIO<float, V>::load(p.ckpt_w + (long long)(ntiles - 1) * row_elems + colj[0], wnext);
-    }
-  }
-
-  auto tile = [&](auto full_tag, int nsteps) {
+  // emit_tag = false: a warm-up tile of a time-split scan; the adjoint advances, nothing is written or summed
+  auto tile = [&](auto full_tag, auto emit_tag, int nsteps) {
     constexpr bool FULL = decltype(full_tag)::value;
+    constexpr bool EMIT = decltype(emit_tag)::value;
     // recompute the tile forward, keeping V[k-1] and x[k] = V_pre[k] - V_th[k]
     float vprev[C][V], xs[C][V], wprev[MT::kSecond ? C : 1][V];
     // Modulated modes: steps whose modulation is evaluated together. 1 here: evaluating several
@@ -1538,8 +1540,10 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
         } else if constexpr (MODE == MODE_ROW) {
 #pragma unroll
           for (int j = 0; j < V; ++j) b[j] = brow[j];
-          vadd<V>(accb, accb, gb);
-          vadd<V>(acct, acct, gth);
+          if constexpr (EMIT) {
+            vadd<V>(accb, accb, gb);
+            vadd<V>(acct, acct, gth);
+          }
         } else if constexpr (MODE != MODE_RF) {
           fetch(MT::kBeta, k, b);
         }
@@ -1552,7 +1556,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
         }
         if constexpr (MODE != MODE_RF && !MT::kMod) vmul<V>(acc, gpre, b);
 
-        if constexpr (TMA) {
+        if constexpr (TMA && EMIT) {
           if constexpr (MODE != MODE_ROW) IO::store(wsp + MT::kBeta * BOX_ELEMS + k * ROW, gb);
           if constexpr (MODE != MODE_ROW && MODE != MODE_LIN)
             IO::store(wsp + MT::kVth * BOX_ELEMS + k * ROW, gth);
@@ -1563,7 +1567,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
           } else {
             IO::store(wsp + MT::kDrive * BOX_ELEMS + k * ROW, gpre);
           }
-        } else {
+        } else if constexpr (!TMA) {
           const size_t ro = (size_t)k * row_elems;
           auto put = [&](ST* dst, const float (&val)[V]) {
             if (!dst) return;
@@ -1588,91 +1592,208 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   int s_idx = 0;
   uint32_t phase = 0;
   bool failed = false;
-  for (int n = 0; n < ntiles; ++n) {
-    const int i = ntiles - 1 - n;
-    t0 = (long long)i * C;
-    const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
-    if constexpr (TMA) {
-      const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 2u, p.wait_ns);
-      bool gave_up = !__all_sync(0xffffffffu, ok);
-      if constexpr (G > 1) gave_up = pair_or(pair_id, gave_up);  // both warps of a box take the same way out
-      if (gave_up) {
-        failed = true;
-        break;
-      }
-      const uint8_t* sp8 = data_ptr + (size_t)s_idx * stage_bytes;
-      sp = reinterpret_cast<const ST*>(sp8) + half * (32 * V) + V * lane;
+  // ---- which tiles this warp walks (from the last to the first). An ordinary launch: all of them.
+  // A time-split launch: segment blockIdx.y, entered warm_tiles later in time with a zero adjoint
+  // (the adjoint recurrence acc' = beta*(acc + ...) forgets its starting value just as the forward
+  // forgets its state) and silent until it reaches its own last tile. The checking launch walks
+  // the segments from the last one (exact: the adjoint is zero beyond T) to the first, compares
+  // the adjoint each one assumed with the exact one bit for bit and redoes those that differ.
+  static_assert(!SPLIT || (MODE == MODE_ROW && TMA && !HAS_GV && G == 1), "time split: row-parameter scan only");
+  constexpr bool split = SPLIT;
+  float carry[V], sumb[V], sumt[V];
+  int seg_first = 0, seg_last = 0;  // inclusive, walked downwards
+  if constexpr (SPLIT) {
+    if (p.fixup) {
+      seg_first = p.nseg - 2;
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        v[j] = vnext[j];
-        w[j] = wnext[j];
-      }
-      if (i > 0 && valid[0]) {
-        VecIO<float, V>::load(p.ckpt + (long long)(i - 1) * row_elems + colj[0], vnext);
-        if (MT::kSecond) VecIO<float, V>::load(p.ckpt_w + (long long)(i - 1) * row_elems + colj[0], wnext);
+        const long long o = (long long)(p.nseg - 1) * row_elems + colj[j];
+        carry[j] = valid[j] ? p.aend[o] : 0.0f;
+        sumb[j] = valid[j] ? p.partb[o] : 0.0f;
+        sumt[j] = valid[j] ? p.partt[o] : 0.0f;
       }
     } else {
+      seg_first = seg_last = (int)blockIdx.y;
+    }
+  }
+  for (int seg = seg_first; seg >= seg_last && !failed; --seg) {
+    int tile_lo = 0, tile_top = ntiles, tile_emit_top = ntiles;  // walk tiles tile_top-1 .. tile_lo; emit below tile_emit_top
+    if constexpr (SPLIT) {
+      tile_lo = seg * p.seg_tiles;
+      tile_emit_top = tile_lo + p.seg_tiles < ntiles ? tile_lo + p.seg_tiles : ntiles;
+      if (p.fixup) {
+        bool differs = false;
 #pragma unroll
-      for (int st = 0; st < NF + 2; ++st) {
-        const ST* g = static_cast<const ST*>(p.s[st]);
-        const bool present = st < nstreams;
+        for (int j = 0; j < V; ++j)
+          if (valid[j])
+            differs |= __float_as_uint(p.aspec[(long long)seg * row_elems + colj[j]]) != __float_as_uint(carry[j]);
+        if (!__any_sync(0xffffffffu, differs)) {  // the speculation held: this segment's results stand
 #pragma unroll
-        for (int k = 0; k < C; ++k)
+          for (int j = 0; j < V; ++j) {
+            const long long o = (long long)seg * row_elems + colj[j];
+            carry[j] = valid[j] ? p.aend[o] : 0.0f;
+            sumb[j] += valid[j] ? p.partb[o] : 0.0f;
+            sumt[j] += valid[j] ? p.partt[o] : 0.0f;
+          }
+          continue;
+        }
+        if (lane == 0 && p.fix_count) atomicAdd(p.fix_count, 1u);
+        tile_top = tile_emit_top;
 #pragma unroll
-          for (int j = 0; j < V; ++j)
-            regs[(st * C + k) * V + j] =
-                (present && k < nsteps && valid[j]) ? g[(t0 + k) * row_elems + colj[j]] : E::zero();
+        for (int j = 0; j < V; ++j) acc[j] = carry[j];
+      } else {
+        tile_top = tile_emit_top + p.warm_tiles < ntiles ? tile_emit_top + p.warm_tiles : ntiles;
       }
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        v[j] = valid[j] ? p.ckpt[(long long)i * row_elems + colj[j]] : 0.0f;
-        w[j] = (MT::kSecond && valid[j]) ? p.ckpt_w[(long long)i * row_elems + colj[j]] : 0.0f;
+      for (int j = 0; j < V; ++j) accb[j] = acct[j] = 0.0f;
+    }
+    const int nt = tile_top - tile_lo;
+    if constexpr (TMA) {
+      if (leader) {  // prime the ring from the stage that is consumed next
+        const int pre = nt < stages ? nt : stages;
+        for (int q = 0; q < pre; ++q) issue(tile_top - 1 - q, (s_idx + q) % stages);
+      }
+      if (nt > 0 && valid[0]) {  // the checkpoint of the first tile walked; the others are fetched one tile ahead
+        VecIO<float, V>::load(p.ckpt + (long long)(tile_top - 1) * row_elems + colj[0], vnext);
+        if (MT::kSecond) VecIO<float, V>::load(p.ckpt_w + (long long)(tile_top - 1) * row_elems + colj[0], wnext);
       }
     }
-
-    if (nsteps == C)
-      tile(std::true_type{}, C);
-    else
-      tile(std::false_type{}, nsteps);
-
-    if constexpr (TMA) {
-      proxy_async_fence();  // make this lane's shared-memory writes visible to TMA
-      __syncwarp();
-      if constexpr (G > 1) pair_sync(pair_id);
-      if (leader) {
-        const uint32_t src = data0 + (uint32_t)s_idx * stage_bytes;
-        const int x = (int)boxcol0, y = i * C;
-        if (MODE != MODE_ROW && p.g_beta) tma_store_2d(&tmo_beta, src + MT::kBeta * TILE_BYTES, x, y);
-        if (MODE != MODE_ROW && MODE != MODE_LIN && p.g_vth) tma_store_2d(&tmo_vth, src + MT::kVth * TILE_BYTES, x, y);
-        if (p.g_drive) tma_store_2d(&tmo_drive, src + MT::kDrive * TILE_BYTES, x, y);
-        if (MT::kFwdStreams >= 4 && p.g_gain) tma_store_2d(&tmo_gain, src + MT::kGain * TILE_BYTES, x, y);
-        if (MODE == MODE_RFMOD && p.g_extra) tma_store_2d(&tmo_omega, src + MT::kOmega * TILE_BYTES, x, y);
-        bulk_commit_group();
-        if (p.defer) {
-          // see the forward kernel: refill the stage of the previous tile
-          bulk_wait_read_keep1();
-          const int sp_idx = s_idx == 0 ? stages - 1 : s_idx - 1;
-          if (i + 1 <= ntiles - 1 && i + 1 - stages >= 0) issue(i + 1 - stages, sp_idx);
-        } else {
-          bulk_wait_read_all();  // the stage is refilled next
-          if (i - stages >= 0) issue(i - stages, s_idx);
+    for (int n = 0; n < nt; ++n) {
+      const int i = tile_top - 1 - n;
+      t0 = (long long)i * C;
+      const bool emit = !split || i < tile_emit_top;
+      const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
+      if constexpr (SPLIT) {
+        if (!p.fixup && i == tile_emit_top - 1 && tile_emit_top < ntiles) {  // warmed up: the adjoint this segment assumes
+#pragma unroll
+          for (int j = 0; j < V; ++j)
+            if (valid[j]) p.aspec[(long long)seg * row_elems + colj[j]] = acc[j];
         }
       }
-      if (++s_idx == stages) {
-        s_idx = 0;
-        phase ^= 1u;
+      if constexpr (TMA) {
+        const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 2u, p.wait_ns);
+        bool gave_up = !__all_sync(0xffffffffu, ok);
+        if constexpr (G > 1) gave_up = pair_or(pair_id, gave_up);  // both warps of a box take the same way out
+        if (gave_up) {
+          failed = true;
+          break;
+        }
+        const uint8_t* sp8 = data_ptr + (size_t)s_idx * stage_bytes;
+        sp = reinterpret_cast<const ST*>(sp8) + half * (32 * V) + V * lane;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          v[j] = vnext[j];
+          w[j] = wnext[j];
+        }
+        if (i > tile_lo && valid[0]) {
+          VecIO<float, V>::load(p.ckpt + (long long)(i - 1) * row_elems + colj[0], vnext);
+          if (MT::kSecond) VecIO<float, V>::load(p.ckpt_w + (long long)(i - 1) * row_elems + colj[0], wnext);
+        }
+      } else {
+#pragma unroll
+        for (int st = 0; st < NF + 2; ++st) {
+          const ST* g = static_cast<const ST*>(p.s[st]);
+          const bool present = st < nstreams;
+#pragma unroll
+          for (int k = 0; k < C; ++k)
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+              regs[(st * C + k) * V + j] =
+                  (present && k < nsteps && valid[j]) ? g[(t0 + k) * row_elems + colj[j]] : E::zero();
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          v[j] = valid[j] ? p.ckpt[(long long)i * row_elems + colj[j]] : 0.0f;
+          w[j] = (MT::kSecond && valid[j]) ? p.ckpt_w[(long long)i * row_elems + colj[j]] : 0.0f;
+        }
+      }
+
+      bool warm_tile = false;
+      if constexpr (SPLIT) warm_tile = !emit;
+      if (warm_tile) {  // (a warm-up tile lies before the end of time only if it is a full one or the very last)
+        if constexpr (SPLIT) {
+          if (nsteps == C)
+            tile(std::true_type{}, std::false_type{}, C);
+          else
+            tile(std::false_type{}, std::false_type{}, nsteps);
+        }
+      } else if (nsteps == C) {
+        tile(std::true_type{}, std::true_type{}, C);
+      } else {
+        tile(std::false_type{}, std::true_type{}, nsteps);
+      }
+
+      if constexpr (TMA) {
+        proxy_async_fence();  // make this lane's shared-memory writes visible to TMA
+        __syncwarp();
+        if constexpr (G > 1) pair_sync(pair_id);
+        if (leader) {
+          const uint32_t src = data0 + (uint32_t)s_idx * stage_bytes;
+          const int x = (int)boxcol0, y = i * C;
+          if (emit) {
+            if (MODE != MODE_ROW && p.g_beta) tma_store_2d(&tmo_beta, src + MT::kBeta * TILE_BYTES, x, y);
+            if (MODE != MODE_ROW && MODE != MODE_LIN && p.g_vth) tma_store_2d(&tmo_vth, src + MT::kVth * TILE_BYTES, x, y);
+            if (p.g_drive) tma_store_2d(&tmo_drive, src + MT::kDrive * TILE_BYTES, x, y);
+            if (MT::kFwdStreams >= 4 && p.g_gain) tma_store_2d(&tmo_gain, src + MT::kGain * TILE_BYTES, x, y);
+            if (MODE == MODE_RFMOD && p.g_extra) tma_store_2d(&tmo_omega, src + MT::kOmega * TILE_BYTES, x, y);
+          }
+          bulk_commit_group();
+          if (p.defer) {
+            // see the forward kernel: refill the stage of the previous tile
+            bulk_wait_read_keep1();
+            const int sp_idx = s_idx == 0 ? stages - 1 : s_idx - 1;
+            if (i + 1 <= tile_top - 1 && i + 1 - stages >= tile_lo) issue(i + 1 - stages, sp_idx);
+          } else {
+            bulk_wait_read_all();  // the stage is refilled next
+            if (i - stages >= tile_lo) issue(i - stages, s_idx);
+          }
+        }
+        if (++s_idx == stages) {
+          s_idx = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    if constexpr (TMA) {
+      if (leader) bulk_wait_all();  // every store of this range has left shared memory
+      __syncwarp();
+    }
+    if constexpr (SPLIT) {
+      if (!failed) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const long long o = (long long)seg * row_elems + colj[j];
+          if (valid[j]) {
+            p.aend[o] = acc[j];
+            p.partb[o] = accb[j];
+            p.partt[o] = acct[j];
+          }
+          if (p.fixup) {
+            carry[j] = acc[j];
+            sumb[j] += accb[j];
+            sumt[j] += acct[j];
+          }
+        }
       }
     }
   }
 
   if constexpr (TMA) {
-    if (leader) bulk_wait_all();
     if (failed) {
       mbar_drain(bar0, stages, s_idx, phase, p.wait_ns);
 #pragma unroll
       for (int j = 0; j < V; ++j)
         if (valid[j] && p.g_vinit) p.g_vinit[colj[j]] = __int_as_float(0x7fc00000);
       return;
+    }
+  }
+  if constexpr (SPLIT) {
+    if (!p.fixup) return;  // the checking launch writes the per-column results
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      acc[j] = carry[j];
+      accb[j] = sumb[j];
+      acct[j] = sumt[j];
     }
   }
 #pragma unroll
@@ -1908,12 +2029,39 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   }
   p.stages = plan.stages;
   p.defer = defer_refill(tune, plan, dev);
-  kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8],
-                                                          tm[9], tm[10], tm[11]);
-  NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel");
+  // Few columns: the time axis cut into segments that run side by side (see the kernel)
+  TimeSplit ts;
+  constexpr bool kSplitBuilt = MODE == MODE_ROW && TMA && !HAS_GV && V == 1 && (C == 16 || C == 32);
+  if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc);
+  last_time_split() = ts;
+  if (ts.nseg > 1) {
+    if constexpr (kSplitBuilt) {
+      auto skern = plif_bwd_kernel<ST, MODE, SURR, V, C, TMA, HAS_GV, true>;
+      NSB_CUDA_TRY(cudaFuncSetAttribute(skern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem),
+                   "cudaFuncSetAttribute(bwd split)");
+      const size_t n = (size_t)ts.nseg * a.cols;
+      p.nseg = ts.nseg; p.seg_tiles = ts.seg_tiles; p.warm_tiles = ts.warm_tiles;
+      p.aspec = a.split_scratch; p.aend = a.split_scratch + n;
+      p.partb = a.split_scratch + 2 * n; p.partt = a.split_scratch + 3 * n;
+      p.fix_count = reinterpret_cast<unsigned int*>(a.split_scratch + 4 * n);
+      NSB_CUDA_TRY(cudaMemsetAsync(p.fix_count, 0, sizeof(unsigned int), a.stream), "clear the rescan counter");
+      p.fixup = 0;
+      skern<<<dim3(plan.grid, ts.nseg), plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6],
+                                                                                tm[7], tm[8], tm[9], tm[10], tm[11]);
+      NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel (time-split)");
+      p.fixup = 1;
+      skern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8],
+                                                                tm[9], tm[10], tm[11]);
+      NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel (time-split check)");
+    }
+  } else {
+    kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8],
+                                                            tm[9], tm[10], tm[11]);
+    NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel");
+  }
   LaunchInfo& li = last_launch();
   li.used_tma = TMA; li.warps_per_cta = plan.wpc; li.stages = plan.stages; li.lanes_per_thread = V;
-  li.grid = plan.grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = 1;
+  li.grid = plan.grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = ts.nseg > 1 ? 2 : 1;
   return NSB_OK;
 }
 

@@ -174,9 +174,10 @@ static int rowparam_bwd_impl(const float* beta_row, const void* u, const float* 
                              const void* g_spike, const void* g_vpost, float* g_beta_row, void* g_u,
                              float* g_vth_row, float* g_vinit, int64_t T, int64_t cols, int dtype,
                              int ckpt_interval, int surrogate, float alpha, const float* alpha_dev,
-                             void* stream) {
+                             float* split_scratch, void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
   if (surrogate != NSB_SURR_SIGMOID && surrogate != NSB_SURR_ATAN) return NSB_ERR_INVALID_ARG;
+  if (!f32_aligned(split_scratch)) return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (T == 0) {
@@ -198,25 +199,26 @@ static int rowparam_bwd_impl(const float* beta_row, const void* u, const float* 
   a.g_beta_row = g_beta_row; a.g_vth_row = g_vth_row; a.g_vinit = g_vinit;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_ROW; a.tile = ckpt_interval;
   a.surrogate = surrogate; a.alpha = alpha; a.alpha_dev = alpha_dev; a.stream = st;
+  a.split_scratch = split_scratch;
   return run_bwd(a, dtype);
 }
 
 int nsb_plif_rowparam_bwd(const float* beta_row, const void* u, const float* vth_row, const float* v_ckpt,
                           const void* g_spike, const void* g_vpost, float* g_beta_row, void* g_u,
                           float* g_vth_row, float* g_vinit, int64_t T, int64_t cols, int dtype,
-                          int ckpt_interval, int surrogate, float alpha, void* stream) {
+                          int ckpt_interval, int surrogate, float alpha, float* split_scratch, void* stream) {
   return rowparam_bwd_impl(beta_row, u, vth_row, v_ckpt, g_spike, g_vpost, g_beta_row, g_u, g_vth_row, g_vinit,
-                           T, cols, dtype, ckpt_interval, surrogate, alpha, nullptr, stream);
+                           T, cols, dtype, ckpt_interval, surrogate, alpha, nullptr, split_scratch, stream);
 }
 
 int nsb_plif_rowparam_bwd_dalpha(const float* beta_row, const void* u, const float* vth_row,
                                  const float* v_ckpt, const void* g_spike, const void* g_vpost,
                                  float* g_beta_row, void* g_u, float* g_vth_row, float* g_vinit, int64_t T,
                                  int64_t cols, int dtype, int ckpt_interval, int surrogate,
-                                 const float* alpha_dev, void* stream) {
+                                 const float* alpha_dev, float* split_scratch, void* stream) {
   if (!alpha_dev || !f32_aligned(alpha_dev)) return NSB_ERR_INVALID_ARG;
   return rowparam_bwd_impl(beta_row, u, vth_row, v_ckpt, g_spike, g_vpost, g_beta_row, g_u, g_vth_row, g_vinit,
-                           T, cols, dtype, ckpt_interval, surrogate, 0.0f, alpha_dev, stream);
+                           T, cols, dtype, ckpt_interval, surrogate, 0.0f, alpha_dev, split_scratch, stream);
 }
 
 int nsb_plif_rf_fwd(const void* beta, const void* omega, const void* u, const void* v_th,

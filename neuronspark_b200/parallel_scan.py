@@ -389,18 +389,19 @@ def _rowparam_backward(ctx, grad_spike, grad_V_post):
     g_beta, g_vth, g_v0 = (torch.empty(u_c.shape[1:], dtype=torch.float32, device=dev)
                            for _ in range(3))
     alpha_t = getattr(ctx, "alpha_t", None)
+    scratch = None if gv is not None else _split_scratch(T, cols, dev)
     with torch.cuda.device(dev):
         if alpha_t is not None:
             _lib.check(_lib.lib().nsb_plif_rowparam_bwd_dalpha(
                 _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(ckpt), _lib.ptr(gs),
                 _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols,
-                _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), _lib.ptr(alpha_t),
+                _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), _lib.ptr(alpha_t), _lib.ptr(scratch),
                 _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd_dalpha")
         else:
             _lib.check(_lib.lib().nsb_plif_rowparam_bwd(
                 _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(ckpt), _lib.ptr(gs),
                 _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols,
-                _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), ctx.alpha,
+                _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), ctx.alpha, _lib.ptr(scratch),
                 _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd")
     db, du, dth, dv = ctx.in_dtypes
     return (g_beta.to(db).reshape(ctx.row_shapes[0]), _cast(g_u, du),
@@ -745,7 +746,7 @@ def plif_rowparam_patterns_backward(beta_row, u, v_th_row, ckpt, grad_frames, al
         _lib.check(_lib.lib().nsb_plif_rowparam_bwd(
             _lib.ptr(beta32), _lib.ptr(u_c), _lib.ptr(vth32), _lib.ptr(ck), _lib.ptr(gs), None, _lib.ptr(g_beta),
             _lib.ptr(g_u), _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols, _lib.dtype_code(dt), C, _lib.SURR_SIGMOID,
-            float(alpha), _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd")
+            float(alpha), _lib.ptr(_split_scratch(T, cols, dev)), _lib.stream_ptr(dev)), "nsb_plif_rowparam_bwd")
     return g_beta, g_u, g_vth, g_v0
 
 
