@@ -136,7 +136,8 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
       for (int st = 2; st <= 6; ++st) {
         if (tune.stages > 0 && st != tune.stages) continue;
         if (tune.stages <= 0 && (st > 4 || st > std::max(2, ntiles))) continue;
-        const size_t smem = (size_t)wpc * (st * (stage_bytes + 8) + (size_t)q.stash * q.tile * 32 * lanes * 4) + 256;
+        const int stash = (lanes == 2 && q.stash_2lanes >= 0) ? q.stash_2lanes : q.stash;
+        const size_t smem = (size_t)wpc * (st * (stage_bytes + 8) + (size_t)stash * q.tile * 32 * lanes * 4) + 256;
         if (smem > (size_t)d.max_smem_optin) continue;
         long long res = std::min<long long>(32, d.smem_per_sm / (long long)(smem + reserved));
         res = std::min<long long>(res, 64 / wpc);

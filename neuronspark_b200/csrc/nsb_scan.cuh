@@ -162,6 +162,7 @@ struct PlanQuery {
   bool backward = false;
   int max_lanes = 4;   // largest lanes-per-thread the kernel family is built for
   int stash = 0;       // fp32 values per element of a tile that each warp keeps in shared memory
+  int stash_2lanes = -1;  // the same when a thread owns 2 lanes, where that differs (-1: it does not)
   int modulated = 0;   // 0 plain scan, 1 first-order modulation fused in, 2 resonate-and-fire modulation
 };
 
@@ -252,6 +253,23 @@ struct VecIO {
     *reinterpret_cast<Vec<ST, V>*>(p) = t;
   }
 };
+
+// One fp32 value kept in the four bytes of the two 16-bit elements a thread owns in a staged tile
+// (a slot whose input has been consumed and whose output is not written yet). The access has the
+// type VecIO uses on the same address, so the compiler orders it with those loads and stores.
+template <typename ST>
+__device__ __forceinline__ void slot_put(ST* p, float x) {
+  static_assert(sizeof(ST) == 2, "a slot is two 16-bit elements");
+  Vec<ST, 2> t;
+  *reinterpret_cast<uint32_t*>(&t) = __float_as_uint(x);
+  *reinterpret_cast<Vec<ST, 2>*>(p) = t;
+}
+template <typename ST>
+__device__ __forceinline__ float slot_get(const ST* p) {
+  static_assert(sizeof(ST) == 2, "a slot is two 16-bit elements");
+  const Vec<ST, 2> t = *reinterpret_cast<const Vec<ST, 2>*>(p);
+  return __uint_as_float(*reinterpret_cast<const uint32_t*>(&t));
+}
 
 // Lane-wise fp32 arithmetic on the V values of a thread.
 //
@@ -1129,36 +1147,49 @@ struct BwdParams {
 // way over its 4-lane form (timed alone 5.07 against 5.22 ms at B=32, T=8192, D=6144; alternating
 // with its forward 5.27 against 5.30 ms); the first-order selective backward does not (5.37 against
 // 5.06 ms) and keeps one warp per box.
+// Whether the backward keeps two of the five modulation intermediates of the resonate-and-fire scan in
+// dead input slots of the staged tile (see the kernel): 2 lanes of 16-bit elements only.
+template <int MODE, int V, int C, bool TMA, size_t ELEM>
+inline constexpr bool kBwdSlotStash = TMA && MODE == MODE_RFMOD && V == 2 && ELEM == 2;
+
 template <int MODE, int V, int C, bool TMA>
 struct BwdBox {
   static constexpr int kWarps = (TMA && (ModeTraits<MODE>::kMod || MODE == MODE_RF) && V == 2 && C == 8) ? 2 : 1;
 };
 
-// Named-barrier primitives for such a pair (id 1..15; all 64 threads must arrive).
+// Named-barrier primitives for such a pair (id 1..15; all 64 threads must arrive). At the end of a
+// tile only the first warp of a pair waits (it hands the box to TMA); the second one arrives and goes
+// on to the next tile, whose stage it can enter as soon as its data has landed. It can therefore be
+// up to one ring of tiles ahead, so every stage of a box has a barrier id of its own: a second
+// arrival on an id comes only after the stage was refilled, i.e. after the first warp consumed the
+// first one. Writes made before the arrival are visible to the waiting warp (producer/consumer form).
 __device__ __forceinline__ void pair_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
-__device__ __forceinline__ bool pair_or(int id, bool x) {
-  uint32_t r;
-  asm volatile(
-      "{\n"
-      ".reg .pred pin, pout;\n"
-      "setp.ne.u32 pin, %2, 0;\n"
-      "bar.red.or.pred pout, %1, 64, pin;\n"
-      "selp.u32 %0, 1, 0, pout;\n"
-      "}"
-      : "=r"(r)
-      : "r"(id), "r"((uint32_t)x)
-      : "memory");
-  return r != 0;
-}
+__device__ __forceinline__ void pair_arrive(int id) { asm volatile("bar.arrive %0, 64;" ::"r"(id) : "memory"); }
 
 // Surrogate derivative on the V lanes of a thread.
 //   arctangent: (alpha/2) / (1 + (pi/2*alpha*x)^2)      c1 = pi/2*alpha, c2 = alpha/2
 //   sigmoid:    alpha*sig*(1-sig) = alpha*e/(1+e)^2 with e = exp(-alpha*|x|) in (0,1]
 //               (even in x, so it cannot overflow and needs no clamp)  c1 = -alpha*log2(e)
-template <int SURR, int V>
+// PAIRS: two lanes at a time on the packed fp32x2 instructions (the modulated scans, which are bound
+// by instruction issue; the results differ from the scalar form in the last place at most).
+template <int SURR, int V, bool PAIRS = false>
 __device__ __forceinline__ void surrogate_grad(float (&sg)[V], const float (&x)[V], float alpha, float c1,
                                                float c2) {
-  if constexpr (SURR == NSB_SURR_ATAN) {
+  if constexpr (PAIRS && V % 2 == 0) {
+    using P = mod::Pack<2>;
+#pragma unroll
+    for (int j = 0; j < V; j += 2) {
+      if constexpr (SURR == NSB_SURR_ATAN) {
+        const P z = mul(P::load(&x[j]), P::splat(c1));
+        const P r = fma(z, z, P::splat(1.0f)).map([](float d) { return mod::rcp_approx(d); });
+        mul(P::splat(c2), r).store(&sg[j]);
+      } else {
+        const P e = P::load(&x[j]).map([c1](float xx) { return mod::ex2_approx(c1 * fabsf(xx)); });
+        const P r = add(P::splat(1.0f), e).map([](float d) { return mod::rcp_approx(d); });
+        mul(mul(P::splat(alpha), e), mul(r, r)).store(&sg[j]);
+      }
+    }
+  } else if constexpr (SURR == NSB_SURR_ATAN) {
     float z[V], d[V], one[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) one[j] = 1.0f;
@@ -1209,7 +1240,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   const int wpc = blockDim.x >> 5;
   const int box = warp / G, half = warp % G;
   const int nbox = wpc / G;
-  const int pair_id = 1 + box;
+  const int pair_id = 1 + box * p.stages;  // + the stage index (the host keeps boxes x stages <= 15)
   const bool leader = half == 0 && lane == 0;
   const long long boxcol0 = ((long long)blockIdx.x * nbox + box) * ROW;
   if (boxcol0 >= p.cols) return;  // the same for every warp of a box
@@ -1223,6 +1254,13 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   // fp32 region of shared memory, so that the transcendental work is done once per element.
   constexpr int NQ = ModeTraits<MODE>::kMod ? (ModeTraits<MODE>::kSecond ? 5 : 3) : 0;
   constexpr bool STASH = TMA && NQ > 0;
+  // Resonate-and-fire, 2 lanes of 16-bit elements: two of the five go into staged input slots that are
+  // dead between the two passes (a thread's 2 elements of a stream are one 32-bit word: raw_alpha's and
+  // I's take the two lanes of I*sigmoid(z_alpha), raw_beta's and raw_omega's those of sigmoid(z_omega)).
+  // The private region shrinks from 10 to 6 KB per warp, which lets a third CTA of 4 warps onto an SM:
+  // 196 608 columns are 3 072 warps, i.e. 2.6 rounds of 8 resident warps per SM but 1.7 rounds of 12.
+  constexpr bool SLOT = STASH && kBwdSlotStash<MODE, V, C, TMA, sizeof(ST)>;
+  constexpr int NQS = SLOT ? 3 : NQ;  // arrays in the private region
 
   long long colj[V];
   bool valid[V];
@@ -1261,6 +1299,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   uint32_t bar0 = 0, data0 = 0;
   const uint8_t* data_ptr = nullptr;
   float* stash = nullptr;
+  volatile uint32_t* box_fail = nullptr;
   if constexpr (TMA) {
     const uint32_t base = smem_u32(smem_raw);
     bar0 = base + (uint32_t)(box * stages) * 8u;
@@ -1269,9 +1308,12 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     data_ptr = smem_raw + (data0 - base);
     if constexpr (STASH)
       stash = reinterpret_cast<float*>(smem_raw + (data_base - base) + (size_t)(nbox * stages) * stage_bytes) +
-              (size_t)warp * (NQ * TILE_ELEMS) + V * lane;
+              (size_t)warp * (NQS * TILE_ELEMS) + V * lane;
+    if constexpr (G > 1)  // set by the second warp of a pair when it gives up a wait; read by the first
+      box_fail = reinterpret_cast<volatile uint32_t*>(smem_raw + (size_t)(nbox * stages) * 8u + (size_t)box * 4u);
     if (leader) {
       for (int s = 0; s < stages; ++s) mbar_init(bar0 + 8u * s, 1);
+      if constexpr (G > 1) *box_fail = 0u;
       mbar_init_fence();
       proxy_async_fence();
     }
@@ -1374,15 +1416,30 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
                 fetch(MT::kDrive, k + kk, mu[kk]);
                 fetch(MT::kGain, k + kk, ra);
                 if constexpr (MT::kSecond) fetch(MT::kOmega, k + kk, mom[kk]);
+                float cin[V];
+#pragma unroll
+                for (int j = 0; j < V; ++j) cin[j] = mu[kk][j];
                 mod::forward_lanes<MT::kSecond, V>(mb[kk], ra, mth[kk], mom[kk], mu[kk], bias, p.v_th_min, q0, q1,
                                                    q2, q3, q4);
                 if constexpr (STASH) {
+                  // q2 := I * sigmoid(z_alpha), the factor of grad raw_alpha (the adjoint pass then needs no I)
+#pragma unroll
+                  for (int j = 0; j < V; ++j) q2[j] = __fmul_rn(cin[j], q2[j]);
                   VecIO<float, V>::store(stash + (0 * C + k + kk) * (32 * V), q0);
                   VecIO<float, V>::store(stash + (1 * C + k + kk) * (32 * V), q1);
-                  VecIO<float, V>::store(stash + (2 * C + k + kk) * (32 * V), q2);
-                  if constexpr (MT::kSecond) {
-                    VecIO<float, V>::store(stash + (3 * C + k + kk) * (32 * V), q3);
-                    VecIO<float, V>::store(stash + (4 * C + k + kk) * (32 * V), q4);
+                  if constexpr (SLOT) {
+                    ST* slot = const_cast<ST*>(sp) + (k + kk) * ROW;
+                    VecIO<float, V>::store(stash + (2 * C + k + kk) * (32 * V), q3);
+                    slot_put(slot + MT::kGain * BOX_ELEMS, q2[0]);
+                    slot_put(slot + MT::kDrive * BOX_ELEMS, q2[V - 1]);
+                    slot_put(slot + MT::kBeta * BOX_ELEMS, q4[0]);
+                    slot_put(slot + MT::kOmega * BOX_ELEMS, q4[V - 1]);
+                  } else {
+                    VecIO<float, V>::store(stash + (2 * C + k + kk) * (32 * V), q2);
+                    if constexpr (MT::kSecond) {
+                      VecIO<float, V>::store(stash + (3 * C + k + kk) * (32 * V), q3);
+                      VecIO<float, V>::store(stash + (4 * C + k + kk) * (32 * V), q4);
+                    }
                   }
                 }
               }
@@ -1421,7 +1478,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
       const int k = C - 1 - kk;
       if (FULL || k < nsteps) {
         float sg[V], gs[V], tot[V], gssg[V], gpre[V], b[V], gb[V], gth[V], gd[V], gg[V], go[V];
-        if constexpr (MODE != MODE_LIN) surrogate_grad<SURR, V>(sg, xs[k], alpha, c1, c2);
+        if constexpr (MODE != MODE_LIN) surrogate_grad<SURR, V, MT::kMod>(sg, xs[k], alpha, c1, c2);
         fetch(kGS, k, gs);
         if (has_gv) {
           float gv[V];
@@ -1436,10 +1493,26 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
 #pragma unroll
           for (int j = 0; j < V; ++j) gssg[j] = gs[j];
         } else {
-          vmul<V>(gssg, gs, sg);
+          if constexpr (MT::kMod && V % 2 == 0) {
+            using P2 = mod::Pack<2>;
+#pragma unroll
+            for (int j = 0; j < V; j += 2) mul(P2::load(&gs[j]), P2::load(&sg[j])).store(&gssg[j]);
+          } else {
+            vmul<V>(gssg, gs, sg);
+          }
         }
-        vadd<V>(gpre, gssg, tot);
-        vmul<V>(gb, gpre, vprev[k]);
+        if constexpr (MT::kMod && V % 2 == 0) {
+          using P2 = mod::Pack<2>;
+#pragma unroll
+          for (int j = 0; j < V; j += 2) {
+            const P2 g = add(P2::load(&gssg[j]), P2::load(&tot[j]));
+            g.store(&gpre[j]);
+            mul(g, P2::load(&vprev[k][j])).store(&gb[j]);
+          }
+        } else {
+          vadd<V>(gpre, gssg, tot);
+          vmul<V>(gb, gpre, vprev[k]);
+        }
         // grad v_th = -gS*sg - tot*spike = -(spike ? gpre : gS*sg)
 #pragma unroll
         for (int j = 0; j < V; ++j) gth[j] = -(xs[k][j] >= 0.0f ? gpre[j] : gssg[j]);
@@ -1466,10 +1539,19 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
           //   d sigmoid = s(1-s); d softplus(z) = sigmoid(z); d|z| = sign(z);
           //   rescale active (beta, omega) = scale*(b0, o0), scale = 0.999/r:
           //     G_b0 = scale*(G_beta - dot*b0), G_o0 = scale*(G_omega - dot*o0), dot = (G_beta*b0 + G_omega*o0)/r2
-          float rt[V], ci[V], b0v[V], alv[V], sav[V], o0v[V], sov[V];
+          // sav: I * sigmoid(z_alpha)
+          float rt[V], b0v[V], alv[V], sav[V], o0v[V], sov[V];
           fetch(MT::kVth, k, rt);
-          fetch(MT::kDrive, k, ci);
-          if constexpr (STASH) {
+          if constexpr (SLOT) {
+            const ST* slot = sp + k * ROW;
+            VecIO<float, V>::load(stash + (0 * C + k) * (32 * V), b0v);
+            VecIO<float, V>::load(stash + (1 * C + k) * (32 * V), alv);
+            VecIO<float, V>::load(stash + (2 * C + k) * (32 * V), o0v);
+            sav[0] = slot_get(slot + MT::kGain * BOX_ELEMS);
+            sav[V - 1] = slot_get(slot + MT::kDrive * BOX_ELEMS);
+            sov[0] = slot_get(slot + MT::kBeta * BOX_ELEMS);
+            sov[V - 1] = slot_get(slot + MT::kOmega * BOX_ELEMS);
+          } else if constexpr (STASH) {
             VecIO<float, V>::load(stash + (0 * C + k) * (32 * V), b0v);
             VecIO<float, V>::load(stash + (1 * C + k) * (32 * V), alv);
             VecIO<float, V>::load(stash + (2 * C + k) * (32 * V), sav);
@@ -1478,7 +1560,8 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
               VecIO<float, V>::load(stash + (4 * C + k) * (32 * V), sov);
             }
           } else {
-            float rb[V], ra[V], ro[V], th_[V], u_[V];
+            float rb[V], ra[V], ro[V], th_[V], u_[V], ci[V];
+            fetch(MT::kDrive, k, ci);
             fetch(MT::kBeta, k, rb);
             fetch(MT::kGain, k, ra);
             if constexpr (MT::kSecond) fetch(MT::kOmega, k, ro);
@@ -1488,6 +1571,8 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
               u_[j] = ci[j];
             }
             mod::forward_lanes<MT::kSecond, V>(rb, ra, th_, ro, u_, bias, p.v_th_min, b0v, alv, sav, o0v, sov);
+#pragma unroll
+            for (int j = 0; j < V; ++j) sav[j] = __fmul_rn(ci[j], sav[j]);
           }
           // pairs of lanes on the packed fp32x2 instructions where V is even (no rounding
           // contract here: gradients are compared to a tolerance)
@@ -1500,20 +1585,22 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
             P Gb = P::load(&gb[j]);
             if constexpr (MT::kSecond) {
               const P O0 = P::load(&o0v[j]);
-              P be = B0, om_ = O0, r2;
-              const P scale = mod::rf_rescale(be, om_, r2);
+              // the rescale as in the forward (same operations, so the same beta and omega), and for its
+              // adjoint nc = -1/r2 where it is active (r2 = (0.999/scale)^2 there), 0 where it is not
+              const P r2 = fma(B0, B0, mul(O0, O0));
+              const P scale = r2.map([](float x) { return x > mod::kRmaxSq ? __fmul_rn(mod::kRmax, mod::rsqrt_approx(x)) : 1.0f; });
+              const P nc = r2.map([](float x) { return x > mod::kRmaxSq ? (float)(-1.0 / (0.999 * 0.999)) : 0.0f; });
+              const P be = mul(B0, scale), om_ = mul(O0, scale);
               const P VP = P::load(&vprev[k][j]), WP = P::load(&wprev[MT::kSecond ? k : 0][j]);
               const P AW = P::load(&accw[j]), NG = mul(Gpre, minus1);
               Gb = fma(AW, WP, Gb);
               P Go = fma(NG, WP, mul(AW, VP));
               fma(Gpre, be, mul(AW, om_)).store(&acc[j]);
               fma(NG, om_, mul(AW, be)).store(&accw[j]);
-              // through the rescale where it is active (computed for every lane, selected per lane)
-              const P ndot = mul(mul(fma(Gb, B0, mul(Go, O0)), r2.map([](float x) { return mod::rcp_approx(x); })),
-                                 minus1);
-              const P Gb2 = mul(scale, fma(ndot, B0, Gb)), Go2 = mul(scale, fma(ndot, O0, Go));
-              Gb = zip(r2, Gb2, Gb, [](float rr, float a, float b_) { return rr > mod::kRmaxSq ? a : b_; });
-              Go = zip(r2, Go2, Go, [](float rr, float a, float b_) { return rr > mod::kRmaxSq ? a : b_; });
+              // through the rescale: where it is inactive scale = 1 and ndot = 0, which leave Gb and Go as they are
+              const P ndot = mul(mul(fma(Gb, B0, mul(Go, O0)), mul(scale, scale)), nc);
+              Gb = mul(scale, fma(ndot, B0, Gb));
+              Go = mul(scale, fma(ndot, O0, Go));
               const P g = mul(Go, P::load(&sov[j]));
               g.store(&go[j]);
               add(P::load(&acco[j]), g).store(&acco[j]);
@@ -1521,7 +1608,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
               mul(Gpre, B0).store(&acc[j]);
             }
             const P gB = mul(Gb, mul(B0, fma(B0, minus1, P::splat(1.0f))));
-            const P gA = mul(mul(Gpre, P::load(&ci[j])), P::load(&sav[j]));
+            const P gA = mul(Gpre, P::load(&sav[j]));
             gB.store(&gb[j]);
             gA.store(&gg[j]);
             mul(Gpre, P::load(&alv[j])).store(&gd[j]);
@@ -1672,9 +1759,15 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
       }
       if constexpr (TMA) {
         const bool ok = mbar_wait_bounded(bar0 + 8u * s_idx, phase, p.err, 2u, p.wait_ns);
-        bool gave_up = !__all_sync(0xffffffffu, ok);
-        if constexpr (G > 1) gave_up = pair_or(pair_id, gave_up);  // both warps of a box take the same way out
+        const bool gave_up = !__all_sync(0xffffffffu, ok);
         if (gave_up) {
+          if constexpr (G > 1) {
+            if (half != 0) {  // the first warp waits for this one at the end of the tile: tell it, and arrive
+              if (lane == 0) *box_fail = 1u;
+              __syncwarp();
+              pair_arrive(pair_id + s_idx);
+            }
+          }
           failed = true;
           break;
         }
@@ -1726,7 +1819,17 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
       if constexpr (TMA) {
         proxy_async_fence();  // make this lane's shared-memory writes visible to TMA
         __syncwarp();
-        if constexpr (G > 1) pair_sync(pair_id);
+        if constexpr (G > 1) {
+          if (half != 0) {
+            pair_arrive(pair_id + s_idx);
+          } else {
+            pair_sync(pair_id + s_idx);
+            if (*box_fail != 0u) {  // the other warp gave up: this box is lost
+              failed = true;
+              break;
+            }
+          }
+        }
         if (leader) {
           const uint32_t src = data0 + (uint32_t)s_idx * stage_bytes;
           const int x = (int)boxcol0, y = i * C;
@@ -2010,7 +2113,8 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
     if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;
     if (G > 1) {  // whole boxes per CTA; shared memory is per warp, so it scales with the warp count
       const size_t per_warp = (plan.smem - 256) / plan.wpc;
-      plan.wpc = std::min(G * ((plan.wpc + G - 1) / G), 2 * 15);  // one named barrier (1..15) per box
+      // one named barrier (ids 1..15) per box and stage
+      plan.wpc = std::min(G * ((plan.wpc + G - 1) / G), G * std::max(1, 15 / std::max(1, plan.stages)));
       plan.smem = per_warp * plan.wpc + 256;
       if (plan.smem > (size_t)dev.max_smem_optin) {
         plan.wpc = G;
@@ -2209,7 +2313,20 @@ int scan_mod_fwd_dispatch(const FwdArgs& a) {
   int r = get_device_info(&dev);
   if (r != NSB_OK) return r;
   if (dev.cc_major != 10) return NSB_ERR_UNSUPPORTED;
-  const Tuning tune = get_tuning();
+  Tuning tune = get_tuning();
+  // Measured launch shapes between the few-column regime and a full GPU (B200, bf16, T = 8192, 8-step tiles).
+  // 49 152 columns (the hidden layer of the 768-wide model at batch 8): 1 lane, 4 warps per CTA, 3 stages:
+  // resonate-and-fire 1.42 ms against 2.01 for the 2-lane single-warp CTAs the cost model picks, first
+  // order 0.93 against 1.16. 98 304 columns: 2 lanes, 4 warps: 2.43 against 3.15 ms (4 lanes, 1 warp) and
+  // 1.45 against 1.62.
+  if (a.tile == 8 && tune.lanes_per_thread <= 0 && tune.warps_per_cta <= 0 && tune.stages <= 0 && a.cols > 32768) {
+    const long long sms = std::max(1, dev.sm_count);
+    if (a.cols < 512 * sms) {
+      tune.lanes_per_thread = 1; tune.warps_per_cta = 4; tune.stages = 3;
+    } else if (a.cols < 1328 * sms) {
+      tune.lanes_per_thread = 2; tune.warps_per_cta = 4; tune.stages = a.mode == MODE_RFMOD ? 2 : 3;
+    }
+  }
   bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
   const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.extra, a.spike, a.ckpt, a.ckpt_w};
   for (const void* q : ptrs) tma = tma && aligned16(q);
@@ -2430,6 +2547,7 @@ int scan_mod_bwd_dispatch(const BwdArgs& a) {
     q.T = a.T; q.cols = a.cols; q.elem_size = (int)sizeof(ST);
     q.nstreams = (a.mode == MODE_RFMOD ? 5 : 4) + 1;
     q.stash = a.mode == MODE_RFMOD ? 5 : 3;
+    if (a.mode == MODE_RFMOD && sizeof(ST) == 2) q.stash_2lanes = 3;  // two of the five live in dead input slots
     q.modulated = a.mode == MODE_RFMOD ? 2 : 1;
     // 4 lanes per thread spill heavily with the modulation's extra live values (measured 3x slower)
     q.tile = C; q.backward = true; q.max_lanes = C == 8 ? 2 : 1;
@@ -2440,6 +2558,10 @@ int scan_mod_bwd_dispatch(const BwdArgs& a) {
     if (C == 8 && tune.lanes_per_thread != 1 && a.cols >= 64LL * 8 * std::max(1, dev.sm_count)) {
       if (tune.warps_per_cta <= 0) tune.warps_per_cta = 4;
       if (tune.stages <= 0) tune.stages = 2;
+    } else if (C == 8 && tune.lanes_per_thread <= 0 && tune.warps_per_cta <= 0 && tune.stages <= 0 && a.cols > 32768) {
+      // fewer columns (49 152, same sizes): 1 lane, 4 warps per CTA: 3.00 ms against 3.23 (resonate-and-fire),
+      // 2.05 against 2.11 (first order) for the cost model's 2 lanes in 2-warp CTAs
+      tune.lanes_per_thread = 1; tune.warps_per_cta = 4; tune.stages = 2;
     }
     plan = plan_scan(dev, q, tune);
     if (plan.grid == 0) return NSB_ERR_UNSUPPORTED;  // the tuning override admits no launch shape
