@@ -1370,7 +1370,8 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     float vprev[C][V], xs[C][V], wprev[MT::kSecond ? C : 1][V];
     // Modulated modes: steps whose modulation is evaluated together. 1 here: evaluating several
     // steps ahead, which pays in the forward kernel, costs the backward more in registers (and so
-    // in resident warps) than it gains (measured: 6.3 -> 6.5 ms first order, 10.3 -> 11.3 ms RF).
+    // in resident warps) than it gains (measured: 6.3 -> 6.5 ms first order, 10.3 -> 11.3 ms RF; with 1 lane
+    // per thread, where registers are plentiful, 4 steps at once change nothing: 2.97 against 3.00 ms).
     constexpr int CH = 1;
     float mb[CH][V], mu[CH][V], mth[CH][V], mom[CH][V];
 #pragma unroll
