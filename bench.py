@@ -61,6 +61,11 @@ MODULATED_WORKLOADS = {
     "rfmod": dict(rf=True, B=32, T=8192, D=6144),
     "mod-short": dict(rf=False, B=32, T=512, D=6144),     # 1/16 of the time steps: profiler captures
     "rfmod-short": dict(rf=True, B=32, T=512, D=6144),
+    # fewer columns: batch 8 is the hidden layer of the 768-wide model (49 152 columns), batch 16 twice that
+    "mod-b8": dict(rf=False, B=8, T=8192, D=6144),
+    "rfmod-b8": dict(rf=True, B=8, T=8192, D=6144),
+    "mod-b16": dict(rf=False, B=16, T=8192, D=6144),
+    "rfmod-b16": dict(rf=True, B=16, T=8192, D=6144),
 }
 INFERENCE_WORKLOADS = {
     "c1": dict(kind="row", B=8, T=8192, D=768, shard=False, calls=1, bytes_per_ns=2.125),
