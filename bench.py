@@ -107,6 +107,8 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--fused-layers", action="store_true",
                     help="c3: also time install(fused_layers=True), the layers on the fused kernels")
+    ap.add_argument("--no-chain", action="store_true",
+                    help="backward launches walk all of T in one CTA per column block (no chained chunks)")
     ap.add_argument("--no-split", action="store_true",
                     help="few-column workloads (c1, res): run the scan as one serial launch, not cut along time")
     return ap.parse_args()
@@ -176,6 +178,8 @@ class ScanStep:
         self.v_last = torch.empty((B, D), dtype=torch.float32, device=dev)
         self.g_beta, self.g_cur, self.g_gain, self.g_vth = (torch.empty((T, B, D), **bf) for _ in range(4))
         self.g_v0 = torch.empty((B, D), dtype=torch.float32, device=dev)
+        # a few KB that let a backward launch of more CTAs than the GPU holds chain chunks of the time axis
+        self.chain = ps._chain_scratch(T, B * D, dev)
         if rf:
             self.ckpt_w = torch.empty_like(self.ckpt)
             self.w_last, self.g_w0, self.w0 = (torch.zeros((B, D), dtype=torch.float32, device=dev)
@@ -207,17 +211,17 @@ class ScanStep:
                 p(i["beta"]), p(i["gain"]), p(i["cur"]), p(i["vth"]), p(self.ckpt), p(self.ckpt_w),
                 p(i["g_spike"]), None, p(self.g_beta), p(self.g_gain), p(self.g_cur), p(self.g_vth),
                 p(self.g_v0), p(self.g_w0), self.T, self.cols, self._lib.BF16, self.C,
-                self._lib.SURR_SIGMOID, 4.0, self.stream), "nsb_plif_rf_bwd")
+                self._lib.SURR_SIGMOID, 4.0, p(self.chain), self.stream), "nsb_plif_rf_bwd")
             if self.launch_bwd is None:
-                self.launch_bwd = self._lib.last_launch_info()
+                self.launch_bwd = dict(self._lib.last_launch_info(), chain_chunks=self._lib.last_chain_chunks())
             return
         self._lib.check(self.L.nsb_plif_selective_bwd(
             p(i["beta"]), p(i["cur"]), p(i["gain"]), p(i["vth"]), p(self.ckpt), p(i["g_spike"]), None,
             p(self.g_beta), p(self.g_cur), p(self.g_gain), p(self.g_vth), p(self.g_v0), self.T,
-            self.cols, self._lib.BF16, self.C, self._lib.SURR_ATAN, ALPHA, self.stream),
+            self.cols, self._lib.BF16, self.C, self._lib.SURR_ATAN, ALPHA, p(self.chain), self.stream),
             "nsb_plif_selective_bwd")
         if self.launch_bwd is None:
-            self.launch_bwd = self._lib.last_launch_info()
+            self.launch_bwd = dict(self._lib.last_launch_info(), chain_chunks=self._lib.last_chain_chunks())
 
 
 # ------------------------------------------------------------- clock sampling
@@ -530,7 +534,7 @@ def run_modulated(args):
             p(grads[4]) if rf else None, p(grads[3]), p(g_bias[0]), p(g_bias[1]), p(g_bias[2]),
             p(g_bias[3]) if rf else None, p(scratch), p(g_v0), p(g_w0), T, cols, _lib.BF16, C,
             _lib.SURR_SIGMOID, 4.0, None, stream), "nsb_plif_modulated_bwd")
-        info.setdefault("bwd", _lib.last_launch_info())
+        info.setdefault("bwd", dict(_lib.last_launch_info(), chain_chunks=_lib.last_chain_chunks()))
 
     def barrier():
         if world > 1:
@@ -1010,6 +1014,9 @@ def main():
     if args.impl == "reference":
         run_reference(args)
         return
+    if args.no_chain:
+        from neuronspark_b200 import _lib as _nsb_lib
+        _nsb_lib.set_chain_chunks(1)
     if args.workload in MODULATED_WORKLOADS:
         run_modulated(args)
         return

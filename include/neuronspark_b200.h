@@ -146,6 +146,33 @@ int nsb_set_time_split(int max_segments, int warm_steps);
 int64_t nsb_time_split_scratch_floats(int64_t cols);
 int nsb_last_time_split(int32_t out[3]);
 
+/*
+ * Chained chunks of a backward scan over many columns. A backward launch gives every block of
+ * columns to one CTA that walks all of T; with more CTAs than the GPU holds at once (768 for 444
+ * places at 196 608 columns) the last round of CTAs is partly empty and lasts as long as a full
+ * one, and at any moment the resident CTAs are spread over all of T. Given scratch, the library cuts the time axis into q chunks, launches q times as many CTAs
+ * and lets each take a ticket: tickets walk the chunks from the last to the first. The CTA of a
+ * chunk waits (bounded, see nsb_set_wait_limit_ns) until the CTA of the next chunk of its columns -
+ * an earlier ticket, so running or finished - has left the adjoint and the running sums over time
+ * in the per-column outputs (g_vinit, g_winit, the row / bias gradient rows), continues from
+ * them and leaves its own there. The operations and their order are those of one CTA walking all of
+ * T, so every output is bit-identical to the unchained launch. Used by the backward entry points
+ * that take chain_scratch (nsb_plif_selective_bwd, nsb_plif_rf_bwd[_dalpha]) and by
+ * nsb_plif_modulated_bwd (inside its own scratch), when g_vinit (and g_winit, and the bias
+ * gradients, where the scan has them) are requested. The reference has no counterpart (one Triton
+ * program per 128 columns walks T, atomic_ops/parallel_scan.py:234-307).
+ *
+ * nsb_chain_scratch_words  words (uint32) of scratch for a scan over `cols` columns.
+ * nsb_set_chain_chunks     0 = automatic (launches with more CTAs than the GPU holds: chunks of 128 steps,
+ *                          1024 with the modulation fused in), 1 = never, 2..1024 = that many chunks (at
+ *                          most one per tile) on every launch that is given the scratch, also where it
+ *                          fits the GPU. Process-global.
+ * nsb_last_chain_chunks    chunks of the last backward launch of the process (1 = not chained).
+ */
+int64_t nsb_chain_scratch_words(int64_t cols);
+int nsb_set_chain_chunks(int chunks);
+int nsb_last_chain_chunks(void);
+
 /* Tuning override for the scan kernels, used by sweeps and tests. Any field
  * <= 0 keeps the built-in heuristic. warps_per_cta: warps of one CTA (each
  * warp owns 32*lanes_per_thread columns and its own TMA pipeline); stages:
@@ -212,13 +239,16 @@ int nsb_plif_selective_fwd(const void* beta, const void* u_or_cur, const void* g
  *
  * g_vpost may be NULL (treated as zero). g_gain is ignored when gain == NULL.
  * Any of the gradient outputs may be NULL (not written).
+ * chain_scratch: NULL, or nsb_chain_scratch_words(cols) words of device memory that let a
+ * launch with more CTAs than the GPU holds at once cut the time axis into chained chunks
+ * (see nsb_set_chain_chunks); results are bit-identical either way.
  */
 int nsb_plif_selective_bwd(const void* beta, const void* u_or_cur, const void* gain,
                            const void* v_th, const float* v_ckpt, const void* g_spike,
                            const void* g_vpost, void* g_beta, void* g_u_or_cur,
                            void* g_gain, void* g_vth, float* g_vinit, int64_t T,
                            int64_t cols, int dtype, int ckpt_interval, int surrogate,
-                           float alpha, void* stream);
+                           float alpha, uint32_t* chain_scratch, void* stream);
 
 /*
  * Row-parameter PLIF forward scan (beta and v_th constant over time, one fp32
@@ -278,7 +308,8 @@ int nsb_plif_rf_bwd(const void* beta, const void* omega, const void* u, const vo
                     const float* v_ckpt, const float* w_ckpt, const void* g_spike,
                     const void* g_vpost, void* g_beta, void* g_omega, void* g_u, void* g_vth,
                     float* g_vinit, float* g_winit, int64_t T, int64_t cols, int dtype,
-                    int ckpt_interval, int surrogate, float alpha, void* stream);
+                    int ckpt_interval, int surrogate, float alpha, uint32_t* chain_scratch,
+                    void* stream);
 
 /*
  * FP16 boundary codec (atomic_ops/fp16_codec.py).
@@ -453,7 +484,7 @@ int nsb_plif_rf_bwd_dalpha(const void* beta, const void* omega, const void* u, c
                            const void* g_vpost, void* g_beta, void* g_omega, void* g_u,
                            void* g_vth, float* g_vinit, float* g_winit, int64_t T, int64_t cols,
                            int dtype, int ckpt_interval, int surrogate, const float* alpha_dev,
-                           void* stream);
+                           uint32_t* chain_scratch, void* stream);
 
 /*
  * Spikes packed in time: the 16 frames of one token and column as one uint16, the IEEE half bit

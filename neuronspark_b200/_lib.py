@@ -37,7 +37,10 @@ _SIGNATURES = {
                                     ctypes.POINTER(c_int32)]),
     "nsb_plif_selective_fwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_plif_selective_bwd": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int,
-                                                          c_float, c_void_p]),
+                                                          c_float, c_void_p, c_void_p]),
+    "nsb_chain_scratch_words": (c_int64, [c_int64]),
+    "nsb_set_chain_chunks": (c_int, [c_int]),
+    "nsb_last_chain_chunks": (c_int, []),
     "nsb_plif_rowparam_fwd": (c_int, [c_void_p] * 9 + [c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nsb_convert": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "nsb_set_time_split": (c_int, [c_int, c_int]),
@@ -47,7 +50,7 @@ _SIGNATURES = {
                                                          c_float, c_void_p, c_void_p]),
     "nsb_plif_rf_fwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_plif_rf_bwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_float,
-                                                   c_void_p]),
+                                                   c_void_p, c_void_p]),
     "nsb_plif_modulated_fwd_stats_doubles": (c_int64, [c_int64]),
     "nsb_plif_modulated_fwd": (c_int, [c_void_p] * 9 + [c_float, c_int64] + [c_void_p] * 8 +
                                [c_float, c_float, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
@@ -59,7 +62,7 @@ _SIGNATURES = {
     "nsb_plif_rowparam_bwd_dalpha": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_int,
                                                                 c_void_p, c_void_p, c_void_p]),
     "nsb_plif_rf_bwd_dalpha": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
-                                                          c_void_p]),
+                                                          c_void_p, c_void_p]),
     "nsb_plif_rowparam_residual_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p,
                                                                 c_void_p]),
     "nsb_frames_pack": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
@@ -217,6 +220,16 @@ def last_time_split() -> dict:
     out = (c_int32 * 3)()
     check(lib().nsb_last_time_split(out), "nsb_last_time_split")
     return dict(zip(("segments", "seg_tiles", "warm_tiles"), out))
+
+
+def set_chain_chunks(chunks: int = 0) -> None:
+    """Chained chunks of backward scans over more columns than the GPU holds at once: 0 = automatic,
+    1 = never, n = n chunks. Process-global."""
+    check(lib().nsb_set_chain_chunks(int(chunks)), "nsb_set_chain_chunks")
+
+
+def last_chain_chunks() -> int:
+    return int(lib().nsb_last_chain_chunks())
 
 
 def set_wait_limit_ns(ns: int = 0) -> None:

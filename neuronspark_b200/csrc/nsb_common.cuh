@@ -157,6 +157,35 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
   return true;
 }
+// Bounded wait until a counter in global memory, which other CTAs of the same launch advance with
+// counter_publish, has reached `want`. Same limits and error reporting as mbar_wait_bounded.
+__device__ __forceinline__ bool counter_wait_bounded(const unsigned int* counter, unsigned int want,
+                                                     uint32_t* err_word, uint32_t code,
+                                                     unsigned long long limit_ns) {
+  auto peek = [&] {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+    return v;
+  };
+  if (peek() >= want) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t it = 0;
+  while (peek() < want) {
+    __nanosleep(200);
+    if ((++it & 0x3F) == 0) {
+      if (global_timer_ns() - t0 > limit_ns || it > (1u << 28)) {
+        if (err_word) atomicOr(reinterpret_cast<unsigned int*>(err_word), code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+// Makes the calling thread's earlier global writes visible to a thread that then sees `value`.
+__device__ __forceinline__ void counter_publish(unsigned int* counter, unsigned int value) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(counter), "r"(value) : "memory");
+}
+
 // After a give-up: one shared allowance of `limit_ns` for all of a warp's stages whose loads may
 // still be in flight, so that they can land before the CTA's shared memory is released.
 __device__ __forceinline__ void mbar_drain(uint32_t bar0, int stages, int s_idx, uint32_t phase,

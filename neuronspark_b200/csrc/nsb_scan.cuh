@@ -121,6 +121,7 @@ struct BwdArgs {
   float alpha = 4.0f;
   const float* alpha_dev = nullptr;  // when set, the surrogate slope is read from device memory
   float* split_scratch = nullptr;    // optional: nsb_time_split_scratch_floats(cols) floats; enables the time split
+  unsigned int* chain_sync = nullptr;  // optional: chain_scratch_words(cols) words; enables chained chunks (backward)
   cudaStream_t stream = nullptr;
 };
 
@@ -185,6 +186,13 @@ TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, in
 TimeSplit& last_time_split();  // of the calling thread's last forward launch
 // floats of scratch a time-split launch over `cols` columns may need (boundary states + a counter)
 long long time_split_scratch_floats(long long cols);
+
+// Chained chunks of a backward launch of `grid` CTAs of which `slots` fit on the GPU at once: the number of
+// chunks of the time axis (1 = none). Host arithmetic (nsb_plan.cu).
+int plan_chain_chunks(long long grid, long long slots, int ntiles, int target_tiles);
+void set_last_chain_chunks(int q);
+int last_chain_chunks();  // of the process's last backward launch
+long long chain_scratch_words(long long cols);
 
 // Device description of a B200 for planning when no GPU is present.
 DeviceInfo b200_device_info();
@@ -1135,6 +1143,17 @@ struct BwdParams {
   float* partb;
   float* partt;
   unsigned int* fix_count;
+  // Chained chunks (more CTAs than fit on the GPU at once): the time axis in chain_q chunks of
+  // chain_tiles tiles; a CTA takes a ticket, tickets walk the chunks from the last to the first
+  // and, within a chunk, the column blocks. The CTA of a chunk waits until the one of the next
+  // chunk of its columns has finished, takes the adjoint (and the running sums over time) from the
+  // per-column outputs, where that CTA left them, and leaves its own there. Same operations in the
+  // same order as one CTA walking all of T: the results are bit-identical. What it buys: a column
+  // block is no longer one indivisible piece of work, so the GPU stays full until the end of the
+  // launch, and all resident CTAs read and write the same few rows of every tensor at a time.
+  // chain_sync[0] = ticket counter, chain_sync[1 + w] = chunks finished by global warp w.
+  int chain_q, chain_tiles;
+  unsigned int* chain_sync;
 };
 
 // Warps that share one TMA box in the backward kernel. DRAM efficiency of the tiled copies
@@ -1242,7 +1261,17 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   const int nbox = wpc / G;
   const int pair_id = 1 + box * p.stages;  // + the stage index (the host keeps boxes x stages <= 15)
   const bool leader = half == 0 && lane == 0;
-  const long long boxcol0 = ((long long)blockIdx.x * nbox + box) * ROW;
+  int vblock = blockIdx.x, chunk = 0;
+  const bool chained = !SPLIT && p.chain_q > 1;
+  if (chained) {
+    __shared__ unsigned int s_ticket;
+    if (threadIdx.x == 0) s_ticket = atomicAdd(p.chain_sync, 1u);
+    __syncthreads();
+    const unsigned int nb = gridDim.x / (unsigned int)p.chain_q;  // column blocks
+    chunk = p.chain_q - 1 - (int)(s_ticket / nb);
+    vblock = (int)(s_ticket % nb);
+  }
+  const long long boxcol0 = ((long long)vblock * nbox + box) * ROW;
   if (boxcol0 >= p.cols) return;  // the same for every warp of a box
   const long long col0 = boxcol0 + (long long)half * (32 * V);
 
@@ -1704,8 +1733,39 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
       seg_first = seg_last = (int)blockIdx.y;
     }
   }
+  unsigned int* const chain_flag = chained ? p.chain_sync + 1 + ((long long)vblock * wpc + warp) : nullptr;
+  if (chained && chunk < p.chain_q - 1) {
+    // the later chunk of these columns must be finished: its CTA holds an earlier ticket, so it is running or done
+    bool ok = true;
+    if (lane == 0) ok = counter_wait_bounded(chain_flag, (unsigned int)(p.chain_q - 1 - chunk), p.err, 2u, p.wait_ns);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) {
+      failed = true;
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        if (!valid[j]) continue;
+        acc[j] = __ldcg(p.g_vinit + colj[j]);
+        if constexpr (MT::kSecond) accw[j] = __ldcg(p.g_winit + colj[j]);
+        if constexpr (MT::kMod) {
+          accb[j] = __ldcg(p.g_bias[0] + colj[j]);
+          acca[j] = __ldcg(p.g_bias[1] + colj[j]);
+          acct[j] = __ldcg(p.g_bias[2] + colj[j]);
+          if constexpr (MT::kSecond) acco[j] = __ldcg(p.g_bias[3] + colj[j]);
+        }
+        if constexpr (MODE == MODE_ROW) {
+          accb[j] = __ldcg(p.g_beta_row + colj[j]);
+          acct[j] = __ldcg(p.g_vth_row + colj[j]);
+        }
+      }
+    }
+  }
   for (int seg = seg_first; seg >= seg_last && !failed; --seg) {
     int tile_lo = 0, tile_top = ntiles, tile_emit_top = ntiles;  // walk tiles tile_top-1 .. tile_lo; emit below tile_emit_top
+    if (chained) {
+      tile_lo = chunk * p.chain_tiles;
+      tile_top = tile_emit_top = tile_lo + p.chain_tiles < ntiles ? tile_lo + p.chain_tiles : ntiles;
+    }
     if constexpr (SPLIT) {
       tile_lo = seg * p.seg_tiles;
       tile_emit_top = tile_lo + p.seg_tiles < ntiles ? tile_lo + p.seg_tiles : ntiles;
@@ -1916,6 +1976,11 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
         if (p.g_vth_row) p.g_vth_row[colj[j]] = acct[j];
       }
     }
+  }
+  if (chained && chunk > 0) {  // hand over to the CTA of the chunk before this one
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) counter_publish(chain_flag, (unsigned int)(p.chain_q - chunk));
   }
 }
 
@@ -2139,6 +2204,8 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   constexpr bool kSplitBuilt = MODE == MODE_ROW && TMA && !HAS_GV && V == 1 && (C == 16 || C == 32);
   if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc);
   last_time_split() = ts;
+  set_last_chain_chunks(1);
+  int launched_grid = plan.grid;
   if (ts.nseg > 1) {
     if constexpr (kSplitBuilt) {
       auto skern = plif_bwd_kernel<ST, MODE, SURR, V, C, TMA, HAS_GV, true>;
@@ -2160,13 +2227,39 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
       NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel (time-split check)");
     }
   } else {
-    kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8],
-                                                            tm[9], tm[10], tm[11]);
+    // More CTAs than fit on the GPU at once: chunks of the time axis chained through the per-column
+    // outputs (see BwdParams), so that the last round of resident CTAs is a full one.
+    int chunks = 1;
+    if constexpr (TMA) {
+      const bool outputs = a.g_vinit && (!MT::kSecond || a.g_winit) &&
+                           (!MT::kMod || (a.g_bias[0] && a.g_bias[1] && a.g_bias[2] && (!MT::kSecond || a.g_bias[3]))) &&
+                           (MODE != MODE_ROW || (a.g_beta_row && a.g_vth_row));
+      if (a.chain_sync && outputs) {
+        int blocks = 0;
+        NSB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kern, plan.wpc * 32, plan.smem),
+                     "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+        chunks = plan_chain_chunks(plan.grid, (long long)blocks * std::max(1, dev.sm_count), p.ntiles,
+                                   (MT::kMod ? 1024 : 128) / C);
+      }
+    }
+    int grid = plan.grid;
+    if (chunks > 1) {
+      p.chain_tiles = (p.ntiles + chunks - 1) / chunks;
+      p.chain_q = (p.ntiles + p.chain_tiles - 1) / p.chain_tiles;  // no empty chunk
+      p.chain_sync = a.chain_sync;
+      NSB_CUDA_TRY(cudaMemsetAsync(a.chain_sync, 0, sizeof(unsigned int) * (1 + (size_t)plan.grid * plan.wpc), a.stream),
+                   "clear the chain counters");
+      grid = plan.grid * p.chain_q;
+      set_last_chain_chunks(p.chain_q);
+    }
+    launched_grid = grid;
+    kern<<<grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8],
+                                                       tm[9], tm[10], tm[11]);
     NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel");
   }
   LaunchInfo& li = last_launch();
   li.used_tma = TMA; li.warps_per_cta = plan.wpc; li.stages = plan.stages; li.lanes_per_thread = V;
-  li.grid = plan.grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = ts.nseg > 1 ? 2 : 1;
+  li.grid = launched_grid; li.smem_bytes = (int)plan.smem; li.tile_steps = C; li.launches = ts.nseg > 1 ? 2 : 1;
   return NSB_OK;
 }
 

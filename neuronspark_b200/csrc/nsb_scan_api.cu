@@ -145,9 +145,10 @@ int nsb_plif_selective_bwd(const void* beta, const void* u_or_cur, const void* g
                            const float* v_ckpt, const void* g_spike, const void* g_vpost, void* g_beta,
                            void* g_u_or_cur, void* g_gain, void* g_vth, float* g_vinit, int64_t T,
                            int64_t cols, int dtype, int ckpt_interval, int surrogate, float alpha,
-                           void* stream) {
+                           uint32_t* chain_scratch, void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
   if (surrogate != NSB_SURR_SIGMOID && surrogate != NSB_SURR_ATAN) return NSB_ERR_INVALID_ARG;
+  if (!f32_aligned(chain_scratch)) return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
   if (T == 0) {
     if (g_vinit) {
@@ -167,6 +168,7 @@ int nsb_plif_selective_bwd(const void* beta, const void* u_or_cur, const void* g
   a.g_gain = gain ? g_gain : nullptr; a.g_vth = g_vth; a.g_vinit = g_vinit;
   a.T = T; a.cols = cols; a.mode = gain ? nsb::MODE_AI : nsb::MODE_U; a.tile = ckpt_interval;
   a.surrogate = surrogate; a.alpha = alpha; a.stream = static_cast<cudaStream_t>(stream);
+  a.chain_sync = chain_scratch;
   return run_bwd(a, dtype);
 }
 
@@ -257,7 +259,7 @@ static int rf_bwd_impl(const void* beta, const void* omega, const void* u, const
                        const float* v_ckpt, const float* w_ckpt, const void* g_spike, const void* g_vpost,
                        void* g_beta, void* g_omega, void* g_u, void* g_vth, float* g_vinit, float* g_winit,
                        int64_t T, int64_t cols, int dtype, int ckpt_interval, int surrogate, float alpha,
-                       const float* alpha_dev, void* stream) {
+                       const float* alpha_dev, uint32_t* chain_scratch, void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
   if (surrogate != NSB_SURR_SIGMOID && surrogate != NSB_SURR_ATAN) return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
@@ -281,6 +283,8 @@ static int rf_bwd_impl(const void* beta, const void* omega, const void* u, const
   a.g_vth = g_vth; a.g_vinit = g_vinit; a.g_winit = g_winit;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_RF; a.tile = ckpt_interval;
   a.surrogate = surrogate; a.alpha = alpha; a.alpha_dev = alpha_dev; a.stream = st;
+  if (!f32_aligned(chain_scratch)) return NSB_ERR_INVALID_ARG;
+  a.chain_sync = chain_scratch;
   return run_bwd(a, dtype);
 }
 
@@ -288,19 +292,22 @@ int nsb_plif_rf_bwd(const void* beta, const void* omega, const void* u, const vo
                     const float* v_ckpt, const float* w_ckpt, const void* g_spike, const void* g_vpost,
                     void* g_beta, void* g_omega, void* g_u, void* g_vth, float* g_vinit, float* g_winit,
                     int64_t T, int64_t cols, int dtype, int ckpt_interval, int surrogate, float alpha,
-                    void* stream) {
+                    uint32_t* chain_scratch, void* stream) {
   return rf_bwd_impl(beta, omega, u, v_th, v_ckpt, w_ckpt, g_spike, g_vpost, g_beta, g_omega, g_u, g_vth,
-                     g_vinit, g_winit, T, cols, dtype, ckpt_interval, surrogate, alpha, nullptr, stream);
+                     g_vinit, g_winit, T, cols, dtype, ckpt_interval, surrogate, alpha, nullptr, chain_scratch,
+                     stream);
 }
 
 int nsb_plif_rf_bwd_dalpha(const void* beta, const void* omega, const void* u, const void* v_th,
                            const float* v_ckpt, const float* w_ckpt, const void* g_spike,
                            const void* g_vpost, void* g_beta, void* g_omega, void* g_u, void* g_vth,
                            float* g_vinit, float* g_winit, int64_t T, int64_t cols, int dtype,
-                           int ckpt_interval, int surrogate, const float* alpha_dev, void* stream) {
+                           int ckpt_interval, int surrogate, const float* alpha_dev, uint32_t* chain_scratch,
+                           void* stream) {
   if (!alpha_dev || !f32_aligned(alpha_dev)) return NSB_ERR_INVALID_ARG;
   return rf_bwd_impl(beta, omega, u, v_th, v_ckpt, w_ckpt, g_spike, g_vpost, g_beta, g_omega, g_u, g_vth,
-                     g_vinit, g_winit, T, cols, dtype, ckpt_interval, surrogate, 0.0f, alpha_dev, stream);
+                     g_vinit, g_winit, T, cols, dtype, ckpt_interval, surrogate, 0.0f, alpha_dev, chain_scratch,
+                     stream);
 }
 
 int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
@@ -349,7 +356,10 @@ int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const vo
   return run_mod_fwd(a, dtype);
 }
 
-int64_t nsb_plif_modulated_bwd_scratch_floats(int64_t cols) { return cols > 0 ? 4 * cols : 0; }
+// 4 per-column rows of bias-gradient sums, then the counters of a chained launch
+int64_t nsb_plif_modulated_bwd_scratch_floats(int64_t cols) {
+  return cols > 0 ? 4 * cols + nsb::chain_scratch_words(cols) : 0;
+}
 int64_t nsb_plif_modulated_fwd_stats_doubles(int64_t cols) { return cols > 0 ? 2 * ((cols + 31) / 32) : 0; }
 
 int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const void* raw_th,
@@ -399,6 +409,7 @@ int nsb_plif_modulated_bwd(const void* raw_beta, const void* raw_alpha, const vo
   const int nb = rf ? 4 : 3;
   if (want_bias)
     for (int i = 0; i < nb; ++i) a.g_bias[i] = scratch + (long long)i * cols;
+  if (scratch) a.chain_sync = reinterpret_cast<unsigned int*>(scratch + 4LL * cols);
   a.g_vinit = g_vinit; a.g_winit = g_winit;
   a.T = T; a.cols = cols; a.mode = rf ? nsb::MODE_RFMOD : nsb::MODE_MOD; a.tile = ckpt_interval;
   a.surrogate = surrogate; a.alpha = alpha; a.alpha_dev = alpha_dev; a.stream = st;

@@ -205,6 +205,19 @@ def _split_scratch(T: int, cols: int, dev):
     return torch.empty(int(_lib.lib().nsb_time_split_scratch_floats(cols)), dtype=torch.float32, device=dev)
 
 
+#: Backward scans over at least this many columns and steps get the few KB of scratch that let the
+#: library chain chunks of the time axis when the launch has more CTAs than the GPU holds at once
+#: (see nsb_set_chain_chunks); below, every launch fits the GPU.
+CHAIN_MIN_COLS = 65536
+CHAIN_MIN_STEPS = 2048
+
+
+def _chain_scratch(T: int, cols: int, dev):
+    if cols < CHAIN_MIN_COLS or T < CHAIN_MIN_STEPS:
+        return None
+    return torch.empty(int(_lib.lib().nsb_chain_scratch_words(cols)), dtype=torch.int32, device=dev)
+
+
 def _grad_stream(g, like, dt):
     """An incoming gradient as a contiguous stream tensor (None stays None)."""
     return _as_stream(g, dt)
@@ -258,7 +271,7 @@ class PLIFSelectiveScan(torch.autograd.Function):
                 _lib.ptr(beta_c), _lib.ptr(u_c), None, _lib.ptr(vth_c), _lib.ptr(ckpt), _lib.ptr(gs),
                 _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u), None, _lib.ptr(g_vth), _lib.ptr(g_v0),
                 T, cols, _lib.dtype_code(dt), ctx.interval, ctx_surrogate(ctx), ctx.alpha,
-                _lib.stream_ptr(dev)), "nsb_plif_selective_bwd")
+                _lib.ptr(_chain_scratch(T, cols, dev)), _lib.stream_ptr(dev)), "nsb_plif_selective_bwd")
         db, du, dth, dv = ctx.in_dtypes
         return (_cast(g_beta, db), _cast(g_u, du), _cast(g_vth, dth),
                 g_v0.to(dv).reshape(ctx.v_init_shape), None)
@@ -309,7 +322,8 @@ class PLIFSelectiveScanAI(torch.autograd.Function):
                 _lib.ptr(beta_c), _lib.ptr(cur_c), _lib.ptr(gain_c), _lib.ptr(vth_c), _lib.ptr(ckpt),
                 _lib.ptr(gs), None, _lib.ptr(g_beta), _lib.ptr(g_cur), _lib.ptr(g_gain),
                 _lib.ptr(g_vth), _lib.ptr(g_v0), T, cols, _lib.dtype_code(dt), ctx.interval,
-                ctx.surrogate, ctx.alpha, _lib.stream_ptr(dev)), "nsb_plif_selective_bwd")
+                ctx.surrogate, ctx.alpha, _lib.ptr(_chain_scratch(T, cols, dev)), _lib.stream_ptr(dev)),
+                "nsb_plif_selective_bwd")
         db, dc, dg, dth, dv = ctx.in_dtypes
         return (_cast(g_beta, db), _cast(g_cur, dc), _cast(g_gain, dg), _cast(g_vth, dth),
                 g_v0.to(dv).reshape(ctx.v_init_shape), None, None)
@@ -511,8 +525,8 @@ def _rf_backward(ctx, grad_spike, grad_V_post):
             _lib.ptr(beta_c), _lib.ptr(omega_c), _lib.ptr(u_c), _lib.ptr(vth_c), _lib.ptr(ckv),
             _lib.ptr(ckw), _lib.ptr(gs), _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_omega), _lib.ptr(g_u),
             _lib.ptr(g_vth), _lib.ptr(g_v0), _lib.ptr(g_w0), T, cols, _lib.dtype_code(dt), ctx.interval,
-            ctx_surrogate(ctx), ctx.alpha if alpha_t is None else _lib.ptr(alpha_t), _lib.stream_ptr(dev)),
-            "nsb_plif_rf_bwd")
+            ctx_surrogate(ctx), ctx.alpha if alpha_t is None else _lib.ptr(alpha_t),
+            _lib.ptr(_chain_scratch(T, cols, dev)), _lib.stream_ptr(dev)), "nsb_plif_rf_bwd")
     db, do, du, dth, dv, dw = ctx.in_dtypes
     return (_cast(g_beta, db), _cast(g_omega, do), _cast(g_u, du), _cast(g_vth, dth),
             g_v0.to(dv).reshape(ctx.state_shapes[0]), g_w0.to(dw).reshape(ctx.state_shapes[1]), None)

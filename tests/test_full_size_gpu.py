@@ -55,9 +55,24 @@ def test_config2_full_size_properties():
     leaves = [inp[k].requires_grad_() for k in names] + [inp["v0"].requires_grad_()]
     spike, v_last = ps.plif_selective_scan_ai(*leaves, alpha=2.0, surrogate="atan")
     nsb_launch = {"fwd": nsb.last_launch_info()}
-    spike.backward(inp["g_spike"])
+    spike.backward(inp["g_spike"], retain_graph=True)
+    torch.cuda.synchronize()
+    # the backward launch has more CTAs than the GPU holds: its time axis is cut into chained chunks
+    assert nsb._lib.last_chain_chunks() > 1
     g1 = [t.grad for t in leaves]
     for t in leaves:
+        t.grad = None
+
+    # (0) the same backward as one CTA per column block over all of T: every gradient bit-identical
+    nsb._lib.set_chain_chunks(1)
+    try:
+        spike.backward(inp["g_spike"], retain_graph=True)
+        torch.cuda.synchronize()
+        assert nsb._lib.last_chain_chunks() == 1
+    finally:
+        nsb._lib.set_chain_chunks()
+    for a, t, n in zip(g1, leaves, names + ("v0",)):
+        assert torch.equal(a, t.grad), f"chained and unchained backward differ in grad {n}"
         t.grad = None
 
     # (1) the oracle on columns cut out of the full problem: the two edge blocks, and one column out

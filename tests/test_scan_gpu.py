@@ -418,7 +418,7 @@ def test_empty_time_axis_and_empty_columns():
     dummy = torch.zeros(8, device=DEV)
     st = L.nsb_plif_selective_bwd(nsb._lib.ptr(dummy), nsb._lib.ptr(dummy), None, nsb._lib.ptr(dummy),
                                   nsb._lib.ptr(dummy), nsb._lib.ptr(dummy), None, None, None, None, None,
-                                  nsb._lib.ptr(g), 0, B * D, 0, 8, 0, 4.0, nsb._lib.stream_ptr(torch.device(DEV)))
+                                  nsb._lib.ptr(g), 0, B * D, 0, 8, 0, 4.0, None, nsb._lib.stream_ptr(torch.device(DEV)))
     assert st == 0 and float(g.abs().max()) == 0.0
 
 
