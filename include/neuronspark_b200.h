@@ -120,8 +120,10 @@ int nsb_convert(const void* src, void* dst, int64_t n, int src_dtype, int dst_dt
  * the other SMs idle. Given scratch memory (`split_scratch` of nsb_plif_rowparam_fwd,
  * nsb_plif_rowparam_residual_fwd, nsb_plif_rowparam_pattern_fwd, nsb_plif_rowparam_bwd and
  * nsb_plif_rowparam_bwd_dalpha: NULL, or
- * nsb_time_split_scratch_floats(cols) floats of device memory that the call may overwrite), such a
- * scan is cut along time into up to 16 segments that run side by side: a later segment is entered
+ * nsb_time_split_scratch_floats(cols) floats of device memory that the call may overwrite - 64 per
+ * column up to 9 472 columns, the widest scan that is ever split; beyond that only the few KB of
+ * counters that let the two backward entry points chain chunks of the time axis, see
+ * nsb_set_chain_chunks), such a scan is cut along time into up to 16 segments that run side by side: a later segment is entered
  * `warm_steps` early from V = 0 and keeps what it computes from its own first step on - PLIF
  * trajectories driven by the same input become bit-identical a few hundred steps after they
  * started apart - and a second launch compares every segment's assumed starting state with the
@@ -150,23 +152,27 @@ int nsb_last_time_split(int32_t out[3]);
  * Chained chunks of a backward scan over many columns. A backward launch gives every block of
  * columns to one CTA that walks all of T; with more CTAs than the GPU holds at once (768 for 444
  * places at 196 608 columns) the last round of CTAs is partly empty and lasts as long as a full
- * one, and at any moment the resident CTAs are spread over all of T. Given scratch, the library cuts the time axis into q chunks, launches q times as many CTAs
+ * one, and at any moment the resident CTAs are spread over all of T, where walking the same few
+ * rows of every [T, cols] tensor together suits DRAM better. Given scratch, the library cuts the time axis into q chunks, launches q times as many CTAs
  * and lets each take a ticket: tickets walk the chunks from the last to the first. The CTA of a
  * chunk waits (bounded, see nsb_set_wait_limit_ns) until the CTA of the next chunk of its columns -
  * an earlier ticket, so running or finished - has left the adjoint and the running sums over time
  * in the per-column outputs (g_vinit, g_winit, the row / bias gradient rows), continues from
  * them and leaves its own there. The operations and their order are those of one CTA walking all of
  * T, so every output is bit-identical to the unchained launch. Used by the backward entry points
- * that take chain_scratch (nsb_plif_selective_bwd, nsb_plif_rf_bwd[_dalpha]) and by
- * nsb_plif_modulated_bwd (inside its own scratch), when g_vinit (and g_winit, and the bias
+ * that take chain_scratch (nsb_plif_selective_bwd, nsb_plif_rf_bwd[_dalpha],
+ * nsb_linear_recurrence_bwd), by nsb_plif_modulated_bwd (inside its own scratch) and by
+ * nsb_plif_rowparam_bwd[_dalpha] (inside split_scratch, for scans too wide for the time split), when g_vinit (and g_winit, and the bias
  * gradients, where the scan has them) are requested. The reference has no counterpart (one Triton
  * program per 128 columns walks T, atomic_ops/parallel_scan.py:234-307).
  *
  * nsb_chain_scratch_words  words (uint32) of scratch for a scan over `cols` columns.
- * nsb_set_chain_chunks     0 = automatic (launches with more CTAs than the GPU holds: chunks of 128 steps,
- *                          1024 with the modulation fused in), 1 = never, 2..1024 = that many chunks (at
- *                          most one per tile) on every launch that is given the scratch, also where it
- *                          fits the GPU. Process-global.
+ * nsb_set_chain_chunks     0 = automatic (selective, resonate-and-fire and linear scans over 49 152
+ *                          columns and more: chunks of 512 steps, of 128 from 98 304 columns on; with the
+ *                          modulation fused in: chunks of 1024 steps where the launch has more CTAs than
+ *                          the GPU holds; row-parameter scans: never), 1 = never, 2..1024 = that many
+ *                          chunks (at most one per tile) on every launch that is given the scratch.
+ *                          Process-global.
  * nsb_last_chain_chunks    chunks of the last backward launch of the process (1 = not chained).
  */
 int64_t nsb_chain_scratch_words(int64_t cols);
@@ -558,14 +564,15 @@ int nsb_plif_rowparam_residual_fwd(const float* beta_row, const void* u, const f
  * backward recomputes V tile by tile from v_ckpt ([ceil(T/ckpt_interval), cols]
  * fp32, written by the forward when given) instead of reading a saved V:
  *   g += dV[k]; grad_u[k] = g; grad_beta[k] = g * V[k-1]; g *= beta[k]   (:110-141)
- * ckpt_interval is 8 or 32.
+ * ckpt_interval is 8 or 32. chain_scratch: see nsb_set_chain_chunks (NULL = one CTA per column
+ * block walks all of T).
  */
 int nsb_linear_recurrence_fwd(const void* beta, const void* u, const float* v_init, void* v_out,
                               float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
                               int ckpt_interval, void* stream);
 int nsb_linear_recurrence_bwd(const void* beta, const void* u, const float* v_ckpt, const void* g_v,
                               void* g_beta, void* g_u, float* g_vinit, int64_t T, int64_t cols,
-                              int dtype, int ckpt_interval, void* stream);
+                              int dtype, int ckpt_interval, uint32_t* chain_scratch, void* stream);
 
 /*
  * Mixture-of-experts output combine and its backward. Replaces

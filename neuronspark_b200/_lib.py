@@ -74,7 +74,7 @@ _SIGNATURES = {
     "nsb_plif_rowparam_pattern_fwd": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_int,
                                                                c_void_p, c_void_p]),
     "nsb_linear_recurrence_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int64, c_int, c_int, c_void_p]),
-    "nsb_linear_recurrence_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_linear_recurrence_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nsb_moe_combine_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_moe_combine_bwd": (c_int, [c_void_p] * 5 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_frames_combine_fwd": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),

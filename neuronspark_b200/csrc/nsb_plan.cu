@@ -198,16 +198,23 @@ std::atomic<int> g_split_warm_steps{0};    // 0 = default
 thread_local TimeSplit g_last_split;
 constexpr int kDefaultWarmSteps = 1024;
 constexpr int kMaxSegments = 16;
+constexpr long long kSplitMaxCols = 9472;
 }  // namespace
 
 TimeSplit& last_time_split() { return g_last_split; }
 
-long long time_split_scratch_floats(long long cols) { return 4LL * kMaxSegments * cols + 4; }  // the backward keeps 4 rows per segment
+// The backward keeps 4 rows per segment. Scans over more columns than the split ever takes (one warp per
+// scheduler and two segments: 9 472 columns) need only the counters of a chained backward launch.
+long long time_split_scratch_floats(long long cols) {
+  if (cols <= 0) return 0;
+  const long long split = cols <= kSplitMaxCols ? 4LL * kMaxSegments * cols + 4 : 0;
+  return std::max(split, chain_scratch_words(cols));
+}
 
 TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, int tile, int lanes, int wpc) {
   TimeSplit ts;
   const int cap = g_split_max_segments.load(std::memory_order_relaxed);
-  if (cap == 1 || tile <= 0) return ts;
+  if (cap == 1 || tile <= 0 || cols > kSplitMaxCols) return ts;
   const long long ntiles = (T + tile - 1) / tile;
   const long long nwarps = (cols + 32LL * lanes - 1) / (32LL * lanes);
   const long long ctas = (nwarps + wpc - 1) / wpc;
@@ -251,6 +258,12 @@ TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, in
 //   resonate-and-fire + mod.   8.96 / 7.85 / 7.80 / 7.81 / 8.27 / 8.43 (6 chunks: 7.73)
 // A chunk costs a pipeline start (ticket, first tiles' latency, and in the modulated kernels the
 // per-channel biases), so the plain scans take chunks of 128 steps and the modulated ones of 1024.
+// Launches that fit the GPU (same sizes, fewer columns; backward ms unchained / 16 / 64 chunks):
+//   selective, 98 304 columns  2.99 / 2.46 / 2.36      49 152 columns  1.42 / 1.29 / 1.40
+//   selective, 24 576 columns  0.69 / 0.71 / 0.89      linear recurrence, 196 608: 3.81 / 3.00 / 2.80 (128: 2.70)
+//   modulated, 49 152 - 98 304 columns: no gain or a loss; row-parameter, 196 608: 2.14 / 2.17 / 2.45
+// so plain scans are chained from 49 152 columns on (chunks of 512 steps below 98 304 columns), the
+// modulated ones only where the launch exceeds the GPU, the row-parameter one only on request.
 namespace {
 std::atomic<int> g_chain_chunks{0};  // 0 = automatic, 1 = never, n = n chunks on every launch that has the scratch
 std::atomic<int> g_last_chain{1};  // process-wide: the backward usually runs on a thread of the caller's autograd engine
@@ -263,10 +276,10 @@ int last_chain_chunks() { return g_last_chain.load(std::memory_order_relaxed); }
 
 long long chain_scratch_words(long long cols) { return cols > 0 ? cols / 32 + 128 : 0; }
 
-int plan_chain_chunks(long long grid, long long slots, int ntiles, int target_tiles) {
+int plan_chain_chunks(bool eligible, int ntiles, int target_tiles) {
   const int forced = g_chain_chunks.load(std::memory_order_relaxed);
-  if (forced > 1) return std::max(1, std::min(forced, ntiles));  // (also where the launch fits the GPU)
-  if (forced == 1 || grid <= slots || slots <= 0) return 1;
+  if (forced > 1) return std::max(1, std::min(forced, ntiles));  // (whatever the launch)
+  if (forced == 1 || !eligible) return 1;
   const int tiles = std::max(kMinChainTiles, target_tiles);
   const int q = std::min(kMaxChainChunks, ntiles / tiles);
   return q >= 2 ? q : 1;

@@ -189,7 +189,7 @@ long long time_split_scratch_floats(long long cols);
 
 // Chained chunks of a backward launch of `grid` CTAs of which `slots` fit on the GPU at once: the number of
 // chunks of the time axis (1 = none). Host arithmetic (nsb_plan.cu).
-int plan_chain_chunks(long long grid, long long slots, int ntiles, int target_tiles);
+int plan_chain_chunks(bool eligible, int ntiles, int target_tiles);
 void set_last_chain_chunks(int q);
 int last_chain_chunks();  // of the process's last backward launch
 long long chain_scratch_words(long long cols);
@@ -2230,24 +2230,35 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
     // More CTAs than fit on the GPU at once: chunks of the time axis chained through the per-column
     // outputs (see BwdParams), so that the last round of resident CTAs is a full one.
     int chunks = 1;
+    // (a row-parameter scan too wide for the time split uses its scratch for the chain)
+    unsigned int* chain_sync = a.chain_sync;
+    if (MODE == MODE_ROW && !chain_sync) chain_sync = reinterpret_cast<unsigned int*>(a.split_scratch);
     if constexpr (TMA) {
       const bool outputs = a.g_vinit && (!MT::kSecond || a.g_winit) &&
                            (!MT::kMod || (a.g_bias[0] && a.g_bias[1] && a.g_bias[2] && (!MT::kSecond || a.g_bias[3]))) &&
                            (MODE != MODE_ROW || (a.g_beta_row && a.g_vth_row));
-      if (a.chain_sync && outputs) {
-        int blocks = 0;
-        NSB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kern, plan.wpc * 32, plan.smem),
-                     "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
-        chunks = plan_chain_chunks(plan.grid, (long long)blocks * std::max(1, dev.sm_count), p.ntiles,
-                                   (MT::kMod ? 1024 : 128) / C);
+      if (chain_sync && outputs) {
+        bool eligible = false;  // measured, see plan_chain_chunks
+        int target_steps = 128;
+        if constexpr (MT::kMod) {
+          int blocks = 0;
+          NSB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kern, plan.wpc * 32, plan.smem),
+                       "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+          eligible = plan.grid > (long long)blocks * std::max(1, dev.sm_count);
+          target_steps = 1024;
+        } else if constexpr (MODE != MODE_ROW) {
+          eligible = a.cols >= 49152;
+          target_steps = a.cols >= 98304 ? 128 : 512;
+        }
+        chunks = plan_chain_chunks(eligible, p.ntiles, target_steps / C);
       }
     }
     int grid = plan.grid;
     if (chunks > 1) {
       p.chain_tiles = (p.ntiles + chunks - 1) / chunks;
       p.chain_q = (p.ntiles + p.chain_tiles - 1) / p.chain_tiles;  // no empty chunk
-      p.chain_sync = a.chain_sync;
-      NSB_CUDA_TRY(cudaMemsetAsync(a.chain_sync, 0, sizeof(unsigned int) * (1 + (size_t)plan.grid * plan.wpc), a.stream),
+      p.chain_sync = chain_sync;
+      NSB_CUDA_TRY(cudaMemsetAsync(chain_sync, 0, sizeof(unsigned int) * (1 + (size_t)plan.grid * plan.wpc), a.stream),
                    "clear the chain counters");
       grid = plan.grid * p.chain_q;
       set_last_chain_chunks(p.chain_q);

@@ -512,7 +512,7 @@ int nsb_linear_recurrence_fwd(const void* beta, const void* u, const float* v_in
 
 int nsb_linear_recurrence_bwd(const void* beta, const void* u, const float* v_ckpt, const void* g_v,
                               void* g_beta, void* g_u, float* g_vinit, int64_t T, int64_t cols, int dtype,
-                              int ckpt_interval, void* stream) {
+                              int ckpt_interval, uint32_t* chain_scratch, void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || (ckpt_interval != 8 && ckpt_interval != 32))
     return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
@@ -531,6 +531,8 @@ int nsb_linear_recurrence_bwd(const void* beta, const void* u, const float* v_ck
   a.g_vinit = g_vinit;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_LIN; a.tile = ckpt_interval;
   a.surrogate = NSB_SURR_SIGMOID; a.alpha = 1.0f; a.stream = st;
+  if (!f32_aligned(chain_scratch)) return NSB_ERR_INVALID_ARG;
+  a.chain_sync = chain_scratch;
   return run_lin_bwd(a, dtype);
 }
 

@@ -206,9 +206,9 @@ def _split_scratch(T: int, cols: int, dev):
 
 
 #: Backward scans over at least this many columns and steps get the few KB of scratch that let the
-#: library chain chunks of the time axis when the launch has more CTAs than the GPU holds at once
-#: (see nsb_set_chain_chunks); below, every launch fits the GPU.
-CHAIN_MIN_COLS = 65536
+#: library chain chunks of the time axis (see nsb_set_chain_chunks); narrower or shorter scans gain
+#: nothing from it.
+CHAIN_MIN_COLS = 49152
 CHAIN_MIN_STEPS = 2048
 
 
@@ -373,8 +373,8 @@ class PLIFLinearRecurrence(torch.autograd.Function):
         with torch.cuda.device(dev):
             _lib.check(_lib.lib().nsb_linear_recurrence_bwd(
                 _lib.ptr(beta_c), _lib.ptr(u_c), _lib.ptr(ckpt), _lib.ptr(gv), _lib.ptr(g_beta), _lib.ptr(g_u),
-                _lib.ptr(g_v0), T, cols, _lib.dtype_code(dt), ctx.interval, _lib.stream_ptr(dev)),
-                "nsb_linear_recurrence_bwd")
+                _lib.ptr(g_v0), T, cols, _lib.dtype_code(dt), ctx.interval,
+                _lib.ptr(_chain_scratch(T, cols, dev)), _lib.stream_ptr(dev)), "nsb_linear_recurrence_bwd")
         db, du, dv = ctx.in_dtypes
         return _cast(g_beta, db), _cast(g_u, du), g_v0.to(dv).reshape(ctx.v_init_shape)
 
@@ -403,7 +403,12 @@ def _rowparam_backward(ctx, grad_spike, grad_V_post):
     g_beta, g_vth, g_v0 = (torch.empty(u_c.shape[1:], dtype=torch.float32, device=dev)
                            for _ in range(3))
     alpha_t = getattr(ctx, "alpha_t", None)
-    scratch = None if gv is not None else _split_scratch(T, cols, dev)
+    # few columns: the time split (not built for a V_post gradient); many: the chained chunks
+    scratch = None
+    if cols >= CHAIN_MIN_COLS and T >= CHAIN_MIN_STEPS:
+        scratch = torch.empty(int(_lib.lib().nsb_time_split_scratch_floats(cols)), dtype=torch.float32, device=dev)
+    elif gv is None:
+        scratch = _split_scratch(T, cols, dev)
     with torch.cuda.device(dev):
         if alpha_t is not None:
             _lib.check(_lib.lib().nsb_plif_rowparam_bwd_dalpha(

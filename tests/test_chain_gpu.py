@@ -105,3 +105,20 @@ def test_automatic_choice_needs_more_ctas_than_the_gpu_holds():
     s.backward(torch.ones_like(s))
     torch.cuda.synchronize()
     assert _lib.last_chain_chunks() == 1
+
+
+def test_rowparam_and_linear_recurrence_chained_equal_unchained():
+    """The row-parameter backward takes the counters from its split scratch, the linear recurrence from
+    its own argument; both chained launches equal the unchained ones bit for bit."""
+    from util import rowparam_inputs
+    T, B, D = 192, 2, 640
+    br, u, tr, v0 = rowparam_inputs(T, B, D, torch.bfloat16, DEV, seed=23)
+    gS = (torch.randn(T, B, D, device=DEV) * 0.1).bfloat16()
+    nsb.set_time_split(1)  # (few columns: without this the scan would be split, not chained)
+    try:
+        check(lambda *a: ps.plif_rowparam_forward_recompute(*a, 4.0)[0], [br, u, tr, v0], gS, (2, 3))
+    finally:
+        nsb.set_time_split()
+    ps.CKPT_INTERVAL = 8
+    beta = torch.sigmoid(torch.randn(T, B, D, device=DEV) + 2).bfloat16()
+    check(lambda b, x, v: ps.linear_recurrence(b, x, v), [beta, u, v0], gS, (2, 5))
