@@ -82,8 +82,9 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
   // within 2 % of the best everywhere: long scans, 4 lanes x 4 warps x 2 stages; scans of a few
   // tiles (per-token decoding), where CTA start-up dominates, 1- or 2-warp CTAs with 4 lanes per
   // thread from 1.5 M columns on and 2 below.
+  // (The plain row-parameter scan, 1 stream, long: 196 608 columns 1.22 ms with this shape against 1.53.)
   if (!q.backward && !q.modulated && q.stash == 0 && q.tile == 8 && q.max_lanes >= 4 && q.cols >= 196608 &&
-      q.nstreams >= 3 &&
+      (q.nstreams >= 3 || (q.nstreams == 1 && ntiles > 8)) &&
       tune.warps_per_cta <= 0 && tune.stages <= 0 && tune.lanes_per_thread <= 0) {
     const bool few_tiles = ntiles <= 8;
     const int lanes = (few_tiles && q.cols < 1500000) ? 2 : 4;
@@ -95,6 +96,25 @@ Plan plan_scan(const DeviceInfo& d, const PlanQuery& q, const Tuning& tune) {
       best.lanes = lanes;
       best.wpc = wpc;
       best.stages = 2;
+      best.grid = (int)((nwarps + wpc - 1) / wpc);
+      best.smem = smem;
+      best.cost = 0.0;
+      return best;
+    }
+  }
+  // Row-parameter backward (the drive and the incoming gradient: 2 streams) over many columns: 4 lanes
+  // in 2-warp CTAs with a 3-deep ring, measured at T = 8192, bf16: 147 456 columns 1.37 ms against 1.49
+  // for the 2-lane shapes chosen below, 196 608 columns 1.78 against 2.14.
+  if (q.backward && !q.modulated && q.stash == 0 && q.tile == 8 && q.max_lanes >= 4 && q.nstreams <= 2 &&
+      q.cols >= 147456 && ntiles > 8 && tune.warps_per_cta <= 0 && tune.stages <= 0 && tune.lanes_per_thread <= 0) {
+    const int lanes = 4, wpc = 2, st = 3;
+    const size_t stage_bytes = (size_t)q.tile * 32 * lanes * q.elem_size * q.nstreams;
+    const size_t smem = (size_t)wpc * st * (stage_bytes + 8) + 256;
+    if (smem + reserved <= (size_t)d.smem_per_sm / 2) {
+      const long long nwarps = (q.cols + 32LL * lanes - 1) / (32LL * lanes);
+      best.lanes = lanes;
+      best.wpc = wpc;
+      best.stages = st;
       best.grid = (int)((nwarps + wpc - 1) / wpc);
       best.smem = smem;
       best.cost = 0.0;
