@@ -85,13 +85,13 @@ MODEL_WORKLOADS = {
 }
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per neuron-step measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
-# reduced-T case "c2-short" (same grid, T=512); traffic of these kernels is proportional to T, so a
-# full launch moves this many bytes per neuron-step too. The figures are those of the capture
-# summarised in profiles/plif_scan_c2short_ncu_full.md, taken on the kernels as they are after the
-# forward body gained its time-split and pattern-output variants and 4-warp CTAs; re-take that
+# reduced-T case "c2-short" (same column grid, T=512); traffic of these kernels is proportional to T,
+# so a full launch moves this many bytes per neuron-step too. The figures are those of the capture
+# summarised in profiles/plif_scan_c2short_ncu_full.md, taken on the kernels as they are with the
+# backward's chained chunks (4 chunks of 128 steps in that case, 64 in the full one); re-take that
 # capture (the T=512 case only) whenever csrc/nsb_scan.cuh changes - the bench does not measure it.
-NCU_TRAFFIC_FWD = (806.145e6 + 230.985e6) / (32 * 512 * 6144)
-NCU_TRAFFIC_BWD = (1057.019e6 + 764.452e6) / (32 * 512 * 6144)
+NCU_TRAFFIC_FWD = (806.131e6 + 229.811e6) / (32 * 512 * 6144)
+NCU_TRAFFIC_BWD = (1059.288e6 + 766.352e6) / (32 * 512 * 6144)
 
 
 def parse_args():
@@ -1245,9 +1245,9 @@ def main():
                 "traffic_source": "ncu capture of the T=512 case scaled by T (bytes per launch)",
                 "peak_source": peak_src,
                 "algorithmic_bytes_per_neuron_step": BYTES_BWD, "avg_launch_ms": bwd_ms,
-                "note": ("a build of this kernel with all arithmetic removed (TMA tiles loaded and stored straight "
-                         "back) takes 4.89-4.98 ms at the c2 shape: 5 reads + 4 writes over 9 arrays reach ~0.91 of "
-                         "the two-stream copy peak used as denominator here") if args.workload == "c2" else "",
+                "note": ("one CTA per column block over all of T (--no-chain) takes 5.1-5.2 ms at the c2 shape, and a "
+                         "build of that launch with all arithmetic removed took 4.89-4.98 ms; with the time axis in "
+                         "chained chunks all resident CTAs walk the same rows of the 9 arrays together") if args.workload == "c2" else "",
                 "forward": {"kernel": "plif_fwd_kernel", "achieved": fwd_ach, "frac": fwd_ach / peak,
                             "algorithmic_bytes_per_neuron_step": BYTES_FWD, "avg_launch_ms": fwd_ms},
                 "step": {"achieved": step_ach, "frac": step_ach / peak,

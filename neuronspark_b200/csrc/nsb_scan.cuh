@@ -1978,6 +1978,8 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     }
   }
   if (chained && chunk > 0) {  // hand over to the CTA of the chunk before this one
+    // (the fence costs each warp a few microseconds at the end of a chunk, which the other resident warps
+    // cover: publishing without it - a timing experiment only - ran no faster)
     __threadfence();
     __syncwarp();
     if (lane == 0) counter_publish(chain_flag, (unsigned int)(p.chain_q - chunk));

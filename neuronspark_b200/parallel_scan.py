@@ -209,7 +209,7 @@ def _split_scratch(T: int, cols: int, dev):
 #: library chain chunks of the time axis (see nsb_set_chain_chunks); narrower or shorter scans gain
 #: nothing from it.
 CHAIN_MIN_COLS = 49152
-CHAIN_MIN_STEPS = 2048
+CHAIN_MIN_STEPS = 512
 
 
 def _chain_scratch(T: int, cols: int, dev):
