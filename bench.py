@@ -1249,7 +1249,11 @@ def main():
                          "build of that launch with all arithmetic removed took 4.89-4.98 ms; with the time axis in "
                          "chained chunks all resident CTAs walk the same rows of the 9 arrays together") if args.workload == "c2" else "",
                 "forward": {"kernel": "plif_fwd_kernel", "achieved": fwd_ach, "frac": fwd_ach / peak,
-                            "algorithmic_bytes_per_neuron_step": BYTES_FWD, "avg_launch_ms": fwd_ms},
+                            "algorithmic_bytes_per_neuron_step": BYTES_FWD, "avg_launch_ms": fwd_ms,
+                            # the fp32 checkpoints the backward recomputes from (one state array per C steps;
+                            # the resonate-and-fire scan keeps two) are real traffic outside the 10 B figure
+                            "frac_with_checkpoints": (BYTES_FWD + (2 if args.workload == "rf" else 1) * 4.0 / step_meta["C"])
+                                                     * neuron_steps * gb / (fwd_ms * 1e-3) / peak},
                 "step": {"achieved": step_ach, "frac": step_ach / peak,
                          "algorithmic_bytes_per_neuron_step": BYTES_FWD + BYTES_BWD},
             },

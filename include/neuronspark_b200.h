@@ -94,10 +94,11 @@ int nsb_device_error_word(uint32_t* out);
 int nsb_set_wait_limit_ns(uint64_t ns);
 
 /* Self-test of the timeout path, for test suites: launches one warp that waits,
- * with the current limit, on a barrier that nothing will ever complete. The warp
- * gives up, sets bit 31 of the error word and returns; nothing faults and no
- * memory operation is left in flight. Set a short limit first
- * (nsb_set_wait_limit_ns) unless a 2 s kernel is wanted. */
+ * with the current limit, on a barrier that nothing will ever complete, and one
+ * that waits for a counter in global memory that nothing advances (the wait of a
+ * chained backward launch). Both give up, set bits 31 and 30 of the error word
+ * and return; nothing faults and no memory operation is left in flight. Set a
+ * short limit first (nsb_set_wait_limit_ns) unless a 2 s kernel is wanted. */
 int nsb_selftest_wait_timeout(void* stream);
 
 /*

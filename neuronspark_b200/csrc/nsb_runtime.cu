@@ -100,9 +100,19 @@ unsigned long long get_wait_limit_ns() { return g_wait_ns.load(std::memory_order
 
 namespace {
 // One warp arms an mbarrier with bytes that no copy will ever deliver and waits for it with the
-// library's bounded wait: the wait runs out, the error word is set, the kernel returns. Nothing
-// is in flight when it exits.
+// library's bounded wait: the wait runs out, the error word is set (bit 31), the kernel returns.
+// Nothing is in flight when it exits.
+// A second warp waits, with the bounded wait of the chained backward launches, for a counter in
+// global memory that nothing advances.
+__device__ unsigned int g_selftest_counter = 0;
+
 __global__ void wait_timeout_selftest_kernel(uint32_t* err, unsigned long long limit_ns) {
+  if (threadIdx.x >= 32) {
+    bool ok = true;
+    if (threadIdx.x == 32) ok = counter_wait_bounded(&g_selftest_counter, 1u, err, 0x40000000u, limit_ns);
+    (void)__all_sync(0xffffffffu, ok);
+    return;
+  }
   __shared__ __align__(8) uint64_t bar;
   const uint32_t b = smem_u32(&bar);
   if (threadIdx.x == 0) {
@@ -203,7 +213,7 @@ int nsb_set_wait_limit_ns(uint64_t ns) {
 int nsb_selftest_wait_timeout(void* stream) {
   uint32_t* err = nsb::device_error_word_ptr();
   if (!err) return NSB_ERR_CUDA;
-  nsb::wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(err, nsb::get_wait_limit_ns());
+  nsb::wait_timeout_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(err, nsb::get_wait_limit_ns());
   NSB_CUDA_TRY(cudaGetLastError(), "launch wait_timeout_selftest_kernel");
   return NSB_OK;
 }

@@ -32,7 +32,8 @@ def test_wait_runs_out_is_reported_and_the_library_recovers():
         with pytest.raises(NSBError, match="bounded device-side wait"):
             ps.plif_rowparam_forward_packed(br, u, tr, v0)
         word = nsb.device_error_word()
-        assert word & 0x80000000, hex(word)
+        assert word & 0x80000000, hex(word)  # the wait for a tile that never arrives
+        assert word & 0x40000000, hex(word)  # the wait for a chunk that never finishes (chained backward)
         assert nsb.device_error_word() == 0  # reading cleared it
     finally:
         nsb.set_wait_limit_ns(0)
