@@ -267,6 +267,165 @@ __global__ void li_bwd_cached_kernel(const T* __restrict__ g_out, const T* __res
 
 constexpr int kCacheVecs = 8;  // vectors of 16 bytes a lane keeps per row in the cached kernels
 
+// Wide rows (more than a warp can keep: 2048 elements of 16 bits, 1024 of 32): a CTA of 8 warps
+// owns a row at a time, thread t keeps the 16-byte vectors t, t+256, ... (NV of them) of the row in
+// registers, so the row is still read once. The row sums go through shared memory in a fixed order
+// (warp sums, then the 8 of them), two buffers alternating between rows so that one barrier per
+// row is enough. A thread owns the same channels in every row: the backward's gain gradient is
+// accumulated in registers and written as this CTA's partial row without any reduction.
+constexpr int kWideWarps = 8;
+
+template <int NSUM>
+__device__ __forceinline__ void block_sums(float (&v)[NSUM], float (*buf)[kWideWarps], int lane, int wib) {
+#pragma unroll
+  for (int q = 0; q < NSUM; ++q) {
+    v[q] = warp_sum(v[q]);
+    if (lane == 0) buf[q][wib] = v[q];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int q = 0; q < NSUM; ++q) {
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kWideWarps; ++w) s += buf[q][w];
+    v[q] = s;
+  }
+}
+
+template <typename T, typename TG, int VE, int NV>
+__global__ void __launch_bounds__(kWideWarps * 32)
+li_fwd_wide_kernel(const T* __restrict__ x, const TG* __restrict__ gain, T* __restrict__ out, long long rows,
+                   int D, float eps) {
+  __shared__ float sums[2][1][kWideWarps];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const float inv_d = 1.0f / (float)D;
+  Vec<T, VE> xv[NV], xn[NV];
+  auto load_row = [&](long long r, Vec<T, VE> (&dst)[NV]) {
+    const T* xr = x + r * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = ((int)threadIdx.x + kWideWarps * 32 * i) * VE;
+      if (d < D) dst[i] = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+    }
+  };
+  if (blockIdx.x < rows) load_row(blockIdx.x, xv);
+  int par = 0;
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x, par ^= 1) {
+    if (r + gridDim.x < rows) load_row(r + gridDim.x, xn);
+    float ss[1] = {0.0f};
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = ((int)threadIdx.x + kWideWarps * 32 * i) * VE;
+      if (d < D) {
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+          const float f = Elem<T>::to_f32(xv[i].v[j]);
+          ss[0] += f * f;
+        }
+      }
+    }
+    block_sums<1>(ss, sums[par], lane, wib);
+    const float rrms = 1.0f / sqrtf(ss[0] * inv_d + eps);
+    T* orow = out + r * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = ((int)threadIdx.x + kWideWarps * 32 * i) * VE;
+      if (d < D) {
+        const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);
+        Vec<T, VE> o;
+#pragma unroll
+        for (int j = 0; j < VE; ++j)
+          o.v[j] = Elem<T>::from_f32(Elem<T>::to_f32(xv[i].v[j]) * rrms * Elem<TG>::to_f32(g.v[j]));
+        *reinterpret_cast<Vec<T, VE>*>(orow + d) = o;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) xv[i] = xn[i];
+  }
+}
+
+template <typename T, typename TG, int VE, int NV>
+__global__ void __launch_bounds__(kWideWarps * 32)
+li_bwd_wide_kernel(const T* __restrict__ g_out, const T* __restrict__ x, const TG* __restrict__ gain,
+                   T* __restrict__ g_x, float* __restrict__ partial, long long rows, int D, float eps) {
+  __shared__ float sums[2][2][kWideWarps];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const float inv_d = 1.0f / (float)D;
+  float acc[NV][VE];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < VE; ++j) acc[i][j] = 0.0f;
+  Vec<T, VE> xv[NV], gv[NV], xn[NV], gn[NV];
+  auto load_row = [&](long long r, Vec<T, VE> (&dx)[NV], Vec<T, VE> (&dg)[NV]) {
+    const T* xr = x + r * D;
+    const T* gr = g_out + r * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = ((int)threadIdx.x + kWideWarps * 32 * i) * VE;
+      if (d < D) {
+        dx[i] = *reinterpret_cast<const Vec<T, VE>*>(xr + d);
+        dg[i] = *reinterpret_cast<const Vec<T, VE>*>(gr + d);
+      }
+    }
+  };
+  if (blockIdx.x < rows) load_row(blockIdx.x, xv, gv);
+  int par = 0;
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x, par ^= 1) {
+    if (r + gridDim.x < rows) load_row(r + gridDim.x, xn, gn);
+    float sd[2] = {0.0f, 0.0f};  // sum x^2, sum g_out*gain*x
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = ((int)threadIdx.x + kWideWarps * 32 * i) * VE;
+      if (d < D) {
+        const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+          const float f = Elem<T>::to_f32(xv[i].v[j]);
+          sd[0] += f * f;
+          sd[1] += Elem<T>::to_f32(gv[i].v[j]) * Elem<TG>::to_f32(g.v[j]) * f;
+        }
+      }
+    }
+    block_sums<2>(sd, sums[par], lane, wib);
+    const float rrms = 1.0f / sqrtf(sd[0] * inv_d + eps);
+    const float mean_dot = sd[1] * rrms * inv_d;
+    T* dxr = g_x + r * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int d = ((int)threadIdx.x + kWideWarps * 32 * i) * VE;
+      if (d < D) {
+        const Vec<TG, VE> g = *reinterpret_cast<const Vec<TG, VE>*>(gain + d);
+        Vec<T, VE> o;
+#pragma unroll
+        for (int j = 0; j < VE; ++j) {
+          const float xh = Elem<T>::to_f32(xv[i].v[j]) * rrms;
+          const float dout = Elem<T>::to_f32(gv[i].v[j]);
+          o.v[j] = Elem<T>::from_f32((dout * Elem<TG>::to_f32(g.v[j]) - xh * mean_dot) * rrms);
+          acc[i][j] += dout * xh;
+        }
+        *reinterpret_cast<Vec<T, VE>*>(dxr + d) = o;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      xv[i] = xn[i];
+      gv[i] = gn[i];
+    }
+  }
+  float* prow = partial + (size_t)blockIdx.x * D;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int d = ((int)threadIdx.x + kWideWarps * 32 * i) * VE;
+    if (d < D) {
+#pragma unroll
+      for (int j = 0; j < VE; ++j) prow[d + j] = acc[i][j];
+    }
+  }
+}
+
+constexpr int kWideVecs = 8;  // 16-byte vectors a thread of the wide kernels keeps per row at most
+
 // Backward, stage 2: g_gain[d] = sum over the partial rows. A block covers 32 channels with
 // 8 groups of threads; group g adds rows g, g+8, g+16, ... and the 8 group sums are then
 // added in a fixed order, so the result does not depend on scheduling.
@@ -352,6 +511,19 @@ int li_bwd_launch(const void* g_out, const void* x, const void* gain, void* g_x,
       NSB_LI_BWD((li_bwd_cached_kernel<T, TG, VMAX, 4>))
     else
       NSB_LI_BWD((li_bwd_cached_kernel<T, TG, VMAX, kCacheVecs>))
+  } else if (can_vec<T, TG>(VMAX, D, {g_out, x, g_x}, gain) && sizeof(TG) * VMAX <= 32 &&
+             D <= kWideWarps * 32 * VMAX * kWideVecs) {
+    const long long per = (long long)kWideWarps * 32 * VMAX;
+    const int nv = (int)((D + per - 1) / per);
+#define NSB_LI_BWD_WIDE(NV_)                                                                             \
+  li_bwd_wide_kernel<T, TG, VMAX, NV_><<<grid, kWideWarps * 32, 0, st>>>(gop, xp, gp, gxp, partial, rows, \
+                                                                          (int)D, eps);
+    if (nv <= 2) { NSB_LI_BWD_WIDE(2) }
+    else if (nv <= 3) { NSB_LI_BWD_WIDE(3) }
+    else if (nv <= 4) { NSB_LI_BWD_WIDE(4) }
+    else if (nv <= 6) { NSB_LI_BWD_WIDE(6) }
+    else { NSB_LI_BWD_WIDE(8) }
+#undef NSB_LI_BWD_WIDE
   } else if (can_vec<T, TG>(4, D, {g_out, x, g_x}, gain))
     NSB_LI_BWD((li_bwd_kernel<T, TG, 4>))
   else if (can_vec<T, TG>(2, D, {g_out, x, g_x}, gain))
@@ -401,6 +573,19 @@ int nsb_lateral_inhibition_fwd(const void* x, const void* gain, void* out, int64
           li_fwd_cached_kernel<T, TG, VMAX, 4><<<g, th, 0, st>>>(xp, gp, op, rows, (int)D, eps);
         else
           li_fwd_cached_kernel<T, TG, VMAX, kCacheVecs><<<g, th, 0, st>>>(xp, gp, op, rows, (int)D, eps);
+      } else if (can_vec<T, TG>(VMAX, D, {x, out}, gain) && sizeof(TG) * VMAX <= 32 &&
+                 D <= kWideWarps * 32 * VMAX * kWideVecs) {
+        const long long per = (long long)kWideWarps * 32 * VMAX;
+        const int nv = (int)((D + per - 1) / per);
+        const int g = (int)std::min<long long>(rows, (long long)dev.sm_count * 4);  // a CTA per row at a time
+#define NSB_LI_FWD_WIDE(NV_) \
+  li_fwd_wide_kernel<T, TG, VMAX, NV_><<<g, kWideWarps * 32, 0, st>>>(xp, gp, op, rows, (int)D, eps);
+        if (nv <= 2) { NSB_LI_FWD_WIDE(2) }
+        else if (nv <= 3) { NSB_LI_FWD_WIDE(3) }
+        else if (nv <= 4) { NSB_LI_FWD_WIDE(4) }
+        else if (nv <= 6) { NSB_LI_FWD_WIDE(6) }
+        else { NSB_LI_FWD_WIDE(8) }
+#undef NSB_LI_FWD_WIDE
       } else if (can_vec<T, TG>(4, D, {x, out}, gain))
         li_fwd_kernel<T, TG, 4><<<(int)grid, kWarpsPerCta * 32, 0, st>>>(xp, gp, op, rows, (int)D, eps);
       else if (can_vec<T, TG>(2, D, {x, out}, gain))

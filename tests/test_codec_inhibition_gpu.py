@@ -120,7 +120,7 @@ def test_golden_lateral_inhibition(golden):
 
 
 @pytest.mark.parametrize("rows,D", [(1, 1), (3, 7), (17, 768), (4096, 768), (64, 6144), (5, 1001),
-                                    (300, 48)])
+                                    (300, 48), (700, 6144), (9, 16384), (33, 4104), (2, 2056)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_lateral_inhibition_vs_oracle(rows, D, dtype):
     g = torch.Generator(device=DEV).manual_seed(rows + D)
