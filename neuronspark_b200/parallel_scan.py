@@ -55,7 +55,7 @@ def _interval(cols: int, row_param: bool = False) -> int:
         return int(CKPT_INTERVAL)
     if row_param:
         return 32 if cols <= 65536 else (16 if cols <= 131072 else 8)
-    return 32 if cols <= 32768 else (16 if cols <= 98304 else 8)
+    return 32 if cols <= 32768 else (16 if cols < 98304 else 8)  # 98 304 columns: 3.66 ms with 8, 3.77 with 16
 
 _SURROGATES = {"sigmoid": _lib.SURR_SIGMOID, "atan": _lib.SURR_ATAN}
 
