@@ -61,6 +61,13 @@ def test_selective_scan_chained_equals_unchained(dtype, shape):
     check(lambda b, c, g, th, v: ps.plif_selective_scan_ai(b, c, g, th, v, 2.0, "atan")[0],
           [beta, cur, gain, vth, v0], gS, (2, 5))
 
+    # with a gradient arriving through V_post as well (one more streamed input in the backward)
+    def spike_and_vpost(b, u, th, v):
+        s, vp, _ = ps.plif_parallel_forward(b, u, th, v, surrogate_function=_Sigmoid(4.0))
+        return s + 0.5 * vp
+
+    check(spike_and_vpost, [beta, cur, vth, v0], gS, (3,))
+
 
 @pytest.mark.parametrize("lanes", [1, 2])
 def test_resonate_and_fire_chained_equals_unchained(lanes):
