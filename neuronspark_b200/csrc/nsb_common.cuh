@@ -159,6 +159,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 }
 // Bounded wait until a counter in global memory, which other CTAs of the same launch advance with
 // counter_publish, has reached `want`. Same limits and error reporting as mbar_wait_bounded.
+// A counter that reads kCounterPoisoned was abandoned by its writer (which gave up a wait of its own and
+// has recorded why): the wait ends at once and reports failure, so that a chain of waiters does not
+// run out one limit after the other.
+constexpr unsigned int kCounterPoisoned = 0xffffffffu;
 __device__ __forceinline__ bool counter_wait_bounded(const unsigned int* counter, unsigned int want,
                                                      uint32_t* err_word, uint32_t code,
                                                      unsigned long long limit_ns) {
@@ -167,10 +171,11 @@ __device__ __forceinline__ bool counter_wait_bounded(const unsigned int* counter
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
     return v;
   };
-  if (peek() >= want) return true;
+  unsigned int seen = peek();
+  if (seen >= want) return seen != kCounterPoisoned;
   const uint64_t t0 = global_timer_ns();
   uint32_t it = 0;
-  while (peek() < want) {
+  while ((seen = peek()) < want) {
     __nanosleep(200);
     if ((++it & 0x3F) == 0) {
       if (global_timer_ns() - t0 > limit_ns || it > (1u << 28)) {
@@ -179,7 +184,7 @@ __device__ __forceinline__ bool counter_wait_bounded(const unsigned int* counter
       }
     }
   }
-  return true;
+  return seen != kCounterPoisoned;
 }
 // Makes the calling thread's earlier global writes visible to a thread that then sees `value`.
 __device__ __forceinline__ void counter_publish(unsigned int* counter, unsigned int value) {

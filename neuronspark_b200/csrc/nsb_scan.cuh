@@ -1776,6 +1776,14 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     if (lane == 0) ok = counter_wait_bounded(chain_flag, (unsigned int)(p.chain_q - 1 - chunk), p.err, 2u, p.wait_ns);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     __syncwarp();  // the other lanes' loads below are ordered after lane 0's acquire
+    if constexpr (G > 1) {
+      // Both warps of a box take the same way: one that went on alone would wait at the box's named
+      // barrier, which has no limit, for a partner that has left. Neither has entered the tile loop yet.
+      if (!ok && lane == 0) *box_fail = 1u;
+      __syncwarp();
+      pair_sync(pair_id);
+      ok = *box_fail == 0u;
+    }
     if (!ok) {
       failed = true;
     } else {
@@ -1797,7 +1805,9 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
       }
     }
   }
+  bool primed = false;  // whether any copy was issued (a CTA that gives up before has nothing in flight)
   for (int seg = seg_first; seg >= seg_last && !failed; --seg) {
+    primed = true;
     int tile_lo = 0, tile_top = ntiles, tile_emit_top = ntiles;  // walk tiles tile_top-1 .. tile_lo; emit below tile_emit_top
     if (chained) {
       tile_lo = chunk * p.chain_tiles;
@@ -1981,7 +1991,9 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
 
   if constexpr (TMA) {
     if (failed) {
-      mbar_drain(bar0, stages, s_idx, phase, p.wait_ns);
+      // a chained launch: the CTAs that wait for this chunk give up at once instead of running out their own limit
+      if (chained && chunk > 0 && lane == 0) counter_publish(chain_flag, kCounterPoisoned);
+      if (primed) mbar_drain(bar0, stages, s_idx, phase, p.wait_ns);
 #pragma unroll
       for (int j = 0; j < V; ++j)
         if (valid[j] && p.g_vinit) p.g_vinit[colj[j]] = __int_as_float(0x7fc00000);
