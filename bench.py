@@ -47,6 +47,7 @@ WORKLOADS = {
     # the second-order resonate-and-fire scan of the hidden neurons at the headline shape
     # (sigmoid surrogate alpha=4, u-form with an omega stream): same byte counts as c2
     "rf": (32, 8192, 6144),
+    "rf-b8": (8, 8192, 6144),      # the same at the width of the 768-wide model's hidden layer at batch 8 (49 152 columns)
 }
 # Secondary (forward-only, bit-packed spikes) workloads; not the default bench line.
 #   c1      row-parameter scan, per-channel beta / V_th, B=8 on every GPU
@@ -1045,7 +1046,7 @@ def main():
 
     B, T, D = WORKLOADS[args.workload]
     inp = make_inputs(B, T, D, dev, 1234 + rank)
-    is_rf = args.workload == "rf"
+    is_rf = args.workload.startswith("rf")
     if is_rf:
         # omega = 0.3*|gain|, then the reference's stability rescale sqrt(beta^2+omega^2) <= 0.999
         # (test_recompute.py:91-96); done in slices to bound temporaries
@@ -1252,7 +1253,7 @@ def main():
                             "algorithmic_bytes_per_neuron_step": BYTES_FWD, "avg_launch_ms": fwd_ms,
                             # the fp32 checkpoints the backward recomputes from (one state array per C steps;
                             # the resonate-and-fire scan keeps two) are real traffic outside the 10 B figure
-                            "frac_with_checkpoints": (BYTES_FWD + (2 if args.workload == "rf" else 1) * 4.0 / step_meta["C"])
+                            "frac_with_checkpoints": (BYTES_FWD + (2 if args.workload.startswith("rf") else 1) * 4.0 / step_meta["C"])
                                                      * neuron_steps * gb / (fwd_ms * 1e-3) / peak},
                 "step": {"achieved": step_ach, "frac": step_ach / peak,
                          "algorithmic_bytes_per_neuron_step": BYTES_FWD + BYTES_BWD},
