@@ -287,7 +287,12 @@ __device__ __forceinline__ float slot_get(const ST* p) {
 // multiply-add even when both carry an explicit .rn (as CUDA intrinsics and as
 // inline PTX alike), which changes the last bit of the membrane state in ~30 % of
 // the elements and so breaks bit-exact parity with an eager fp32 time loop. The
-// scalar __fmul_rn / __fadd_rn forms are never contracted.
+// scalar __fmul_rn / __fadd_rn forms are never contracted. (Writing the add as
+// fma.rn.f32x2(a, one, b) is contracted too when `one` is the literal 1.0; with a 1.0 the
+// assembler cannot see - a __constant__ the host could rewrite - the packed form is bit-exact,
+// all parity tests pass, and it is no faster than the scalar one: resonate-and-fire with
+// modulation, forward 3.94 against 4.00 ms, backward 7.90 against 7.80 ms. The contracted,
+// inexact form would run 7.23 ms: what it saves is the add, not the issue slot.)
 #ifndef NSB_X2
 #define NSB_X2 0
 #endif
