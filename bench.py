@@ -108,6 +108,9 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--fused-layers", action="store_true",
                     help="c3: also time install(fused_layers=True), the layers on the fused kernels")
+    ap.add_argument("--train", action="store_true",
+                    help="workload c3: time a training step (cross-entropy loss, forward + backward through the "
+                         "reference's per-layer activation checkpointing) instead of the forward alone")
     ap.add_argument("--no-chain", action="store_true",
                     help="backward launches walk all of T in one CTA per column block (no chained chunks)")
     ap.add_argument("--no-split", action="store_true",
@@ -935,6 +938,34 @@ def run_model(args):
                 clock.detach()
         return ms, clock.totals(2), logits
 
+    def time_train(m, steps, warmup):
+        """One training step = the reference's own forward with targets (cross-entropy per token,
+        model.py:271-278), mean, backward; gradients dropped, no optimiser."""
+        targets = torch.randint(1, cfg["vocab"], (cfg["B"], cfg["seq"]), device=dev,
+                                generator=torch.Generator(device=dev).manual_seed(4321))
+        m.train()
+
+        def step():
+            loss = m(tokens, targets).last_loss.float().mean()
+            loss.backward()
+            for p in m.parameters():
+                p.grad = None
+            return loss.detach()
+
+        try:
+            for _ in range(warmup):
+                step()
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(steps):
+                loss = step()
+            end.record()
+            torch.cuda.synchronize()
+        finally:
+            m.eval()
+        return start.elapsed_time(end) / steps, float(loss)
+
     K, W = args.steps, max(args.warmup, 3)
     note = {}
     arms = {}
@@ -958,6 +989,10 @@ def run_model(args):
     assert nsb.device_error_word() == 0
     finite = bool(torch.isfinite(logits).all())
     spike_calls = len(changed)
+    train = {}
+    if args.train:
+        train["ours"] = time_train(m, K, W)
+        assert nsb.device_error_word() == 0
     inst.uninstall()
     if args.fused_layers:  # the layers' call sequence changed as well: neuronspark_b200.layers
         inst.install(fused_layers=True)
@@ -973,11 +1008,16 @@ def run_model(args):
             torch.cuda.synchronize()
         note["fused_layers"] = {"ms_per_step": a.elapsed_time(b) / K,
                                 "argmax_agreement_with_unfused": float((logits_f.argmax(-1) == logits.argmax(-1)).float().mean())}
+        if args.train:
+            train["ours_fused_layers"] = time_train(m, K, W)
+            assert nsb.device_error_word() == 0
         inst.uninstall()
     try:  # the same model object on the reference's own Triton kernels
         ms_ref, parts_ref, logits_ref = time_arm(m, K, W)
         arms["reference_triton"] = (ms_ref, parts_ref)
         note["argmax_agreement_with_reference"] = float((logits.argmax(-1) == logits_ref.argmax(-1)).float().mean())
+        if args.train:
+            train["reference_triton"] = time_train(m, K, W)
     except Exception as e:  # noqa: BLE001
         note["reference_triton"] = f"unavailable: {type(e).__name__}: {str(e)[:200]}"
     ms, parts = arms["ours"]
@@ -1001,6 +1041,11 @@ def run_model(args):
         "clocks": clocks, "validation": {"finite_logits": finite},
         "gpu_launches": K * (cfg["layers"] * 6 + 3),
     }
+    if train:
+        line["training_step"] = {k: {"ms_per_step": v[0], "tokens_per_s": tok / (v[0] * 1e-3), "loss": v[1]}
+                                 for k, v in train.items()}
+        line["training_step"]["what"] = ("forward with targets (cross-entropy), mean, backward; the reference's per-layer "
+                                         "activation checkpointing recomputes each layer's forward in the backward")
     if "reference_triton" in arms:
         line["reference_triton"] = {"ms_per_step": arms["reference_triton"][0],
                                     "swapped_kernels_ms_per_forward": arms["reference_triton"][1]}
