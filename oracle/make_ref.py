@@ -16,6 +16,9 @@ copy exists so that
     ``SNNBlock`` / ``SNNFFN`` / ``SNNDecoderLayer`` / ``SNNLanguageModel`` and let
     them call this library through ``neuronspark_b200.install``;
   * a bench can time the reference's own Triton kernels on the same GPU;
+  * the reference's own test scripts for this path (``test_recompute.py``,
+    ``test_binary_residual.py``, ``exp/verify_fused_plif.py``) can be run as they are
+    against this library;
 
 on machines where the checkout itself is not mounted. Nothing is patched: the
 harness supplies a stand-in for the one third-party package the reference
@@ -33,8 +36,10 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 DEST = HERE / "_ref"
 
-#: files of the checkout that the harness imports, relative to its root
-WANTED = ("model.py", "atomic_ops/*.py")
+#: files of the checkout that the harness imports, relative to its root, and the reference's own
+#: test scripts for this path (run, unchanged, on this library by tests/test_reference_own_tests_gpu.py)
+WANTED = ("model.py", "atomic_ops/*.py", "test_recompute.py", "test_binary_residual.py",
+          "exp/verify_fused_plif.py")
 
 
 def stage(checkout: Path, dest: Path = DEST) -> dict:
