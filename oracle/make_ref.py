@@ -17,7 +17,7 @@ copy exists so that
     them call this library through ``neuronspark_b200.install``;
   * a bench can time the reference's own Triton kernels on the same GPU;
   * the reference's own test scripts for this path (``test_recompute.py``,
-    ``test_binary_residual.py``, ``exp/verify_fused_plif.py``) can be run as they are
+    ``test_binary_residual.py``, ``exp/verify_fused_plif.py``, ``exp/verify_triton_scan.py``) can be run as they are
     against this library;
 
 on machines where the checkout itself is not mounted. Nothing is patched: the
@@ -39,7 +39,7 @@ DEST = HERE / "_ref"
 #: files of the checkout that the harness imports, relative to its root, and the reference's own
 #: test scripts for this path (run, unchanged, on this library by tests/test_reference_own_tests_gpu.py)
 WANTED = ("model.py", "atomic_ops/*.py", "test_recompute.py", "test_binary_residual.py",
-          "exp/verify_fused_plif.py")
+          "exp/verify_fused_plif.py", "exp/verify_triton_scan.py")
 
 
 def stage(checkout: Path, dest: Path = DEST) -> dict:

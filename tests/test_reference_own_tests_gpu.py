@@ -4,7 +4,7 @@
 equal to the bit, forward and backward, row-parameter and resonate-and-fire), ``test_binary_residual.py``
 (codec round trips, straight-through gradients) and ``exp/verify_fused_plif.py`` (the fused scan against
 a sequential PyTorch loop, its gradients against autograd through that loop, the real training shapes)
-beside the reference's modules. Here the modules are imported, ``install()`` rebinds their kernels to
+and ``exp/verify_triton_scan.py`` (the linear recurrence against the Hillis-Steele scan) beside the reference's modules. Here the modules are imported, ``install()`` rebinds their kernels to
 this library, and each script is executed as ``__main__``. The scripts' own assertions and verdict lines
 are the acceptance. The only lines not executed are two machine-specific ones at the top of
 ``verify_fused_plif.py`` (a ptxas path and a home directory of the authors' machine)."""
@@ -74,4 +74,13 @@ def test_verify_fused_plif_script(reference_on_this_library):
     scan = sys.modules["atomic_ops.parallel_scan"]
     assert scan.plif_parallel_forward is ps.plif_parallel_forward
     text = run_script("exp/verify_fused_plif.py")
+    assert "ALL TESTS PASSED" in text and "FAIL" not in text.replace("SOME TESTS FAILED", ""), text
+
+
+def test_verify_triton_scan_script(reference_on_this_library):
+    """The linear recurrence against the reference's Hillis-Steele scan (forward in fp32 and bf16, gradients),
+    its no-grad path, and the PLIF forwards built on it, at the real training shapes."""
+    scan = sys.modules["atomic_ops.parallel_scan"]
+    assert scan.linear_recurrence is ps.linear_recurrence
+    text = run_script("exp/verify_triton_scan.py")
     assert "ALL TESTS PASSED" in text and "FAIL" not in text.replace("SOME TESTS FAILED", ""), text
