@@ -182,7 +182,8 @@ Plan plan_scan(const DeviceInfo& dev, const PlanQuery& q, const Tuning& tune);
 struct TimeSplit {
   int nseg = 1, seg_tiles = 0, warm_tiles = 0;
 };
-TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, int tile, int lanes, int wpc);
+TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, int tile, int lanes, int wpc,
+                          bool backward);
 TimeSplit& last_time_split();  // of the calling thread's last forward launch
 // floats of scratch a time-split launch over `cols` columns may need (boundary states + a counter)
 long long time_split_scratch_floats(long long cols);
@@ -2144,7 +2145,7 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   // built for: row-parameter family, tiled copies, one lane per thread, tiles of 16 or 32 steps
   constexpr bool kSplitBuilt = (MODE == MODE_ROW || MODE == MODE_ROWRES || MODE == MODE_ROWPAT) && TMA && V == 1 &&
                                (C == 16 || C == 32);
-  if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc);
+  if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc, false);
   last_time_split() = ts;
   if (ts.nseg > 1) {
     if constexpr (kSplitBuilt) {
@@ -2258,7 +2259,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   // Few columns: the time axis cut into segments that run side by side (see the kernel)
   TimeSplit ts;
   constexpr bool kSplitBuilt = MODE == MODE_ROW && TMA && !HAS_GV && V == 1 && (C == 16 || C == 32);
-  if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc);
+  if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc, true);
   last_time_split() = ts;
   set_last_chain_chunks(1);
   int launched_grid = plan.grid;
