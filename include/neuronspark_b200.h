@@ -122,7 +122,7 @@ int nsb_convert(const void* src, void* dst, int64_t n, int src_dtype, int dst_dt
  * nsb_plif_rowparam_residual_fwd, nsb_plif_rowparam_pattern_fwd, nsb_plif_rowparam_bwd and
  * nsb_plif_rowparam_bwd_dalpha: NULL, or
  * nsb_time_split_scratch_floats(cols) floats of device memory that the call may overwrite - 64 per
- * column up to 18 944 columns, the widest scan that is ever split; beyond that only the few KB of
+ * column up to 37 888 columns, the widest scan that is ever split; beyond that only the few KB of
  * counters that let the two backward entry points chain chunks of the time axis, see
  * nsb_set_chain_chunks), such a scan is cut along time into up to 16 segments that run side by side: a later segment is entered
  * `warm_steps` early from V = 0 and keeps what it computes from its own first step on - PLIF

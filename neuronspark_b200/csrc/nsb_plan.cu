@@ -218,13 +218,13 @@ std::atomic<int> g_split_warm_steps{0};    // 0 = default
 thread_local TimeSplit g_last_split;
 constexpr int kDefaultWarmSteps = 1024;
 constexpr int kMaxSegments = 16;
-constexpr long long kSplitMaxCols = 18944;  // two warps per scheduler and two segments
+constexpr long long kSplitMaxCols = 37888;  // four warps per scheduler and two segments
 }  // namespace
 
 TimeSplit& last_time_split() { return g_last_split; }
 
-// The backward keeps 4 rows per segment. Scans over more columns than the split ever takes (two warps per
-// scheduler and two segments: 18 944 columns) need only the counters of a chained backward launch.
+// The backward keeps 4 rows per segment. Scans over more columns than the split ever takes (four warps per
+// scheduler and two segments: 37 888 columns) need only the counters of a chained backward launch.
 long long time_split_scratch_floats(long long cols) {
   if (cols <= 0) return 0;
   const long long split = cols <= kSplitMaxCols ? 4LL * kMaxSegments * cols + 4 : 0;
@@ -239,32 +239,39 @@ TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, in
   const long long ntiles = (T + tile - 1) / tile;
   const long long nwarps = (cols + 32LL * lanes - 1) / (32LL * lanes);
   const long long ctas = (nwarps + wpc - 1) / wpc;
-  // Up to two warps per scheduler. A scheduler with two warps of this chain-bound code advances each of
-  // them more slowly than a lone one - measured at T = 8192 with 192 column warps: forward 30.3 ns per
-  // step with 3 segments (one warp per scheduler), 34.7 with 6; backward 41.8 and 58.2 - but twice the
-  // segments still win: forward 114 -> 83 us, backward 157 -> 139 us at 6 144 columns; 148 -> 105 and
-  // 196 -> 163 us at 9 216. (96 column warps: 8 segments instead of 6 put a second warp on a third of
-  // the schedulers and cost the backward 107 -> 115 us: the slowest scheduler sets the time.)
+  // Up to four warps per scheduler. A scheduler with several warps of this chain-bound code advances each
+  // of them more slowly than a lone one, but more segments still win while the product falls. Measured at
+  // T = 8192, ns per step and warp with 1 / 2 / 3 / 4 warps on the busiest scheduler: forward 27 / 33 / 38 /
+  // 45, backward 38 / 52 / 65 / 95 (384 and 768 column warps cut into 1-6 segments). Examples: 6 144 columns
+  // forward 114 us with 3 segments (one warp per scheduler), 83 with 6; backward 157 -> 139 us; 12 288 columns,
+  // which one warp per scheduler cannot split, forward 220 -> 109 us (6 segments), backward 313 -> 198 (3);
+  // 24 576 columns forward 239 -> 171 us (3), backward 417 -> 313 (2). The slowest scheduler sets the time,
+  // so the factor goes by the rounded-up number of warps per scheduler.
   const long long schedulers = 4LL * std::max(1, dev.sm_count);
-  const double two_warps = backward ? 1.4 : 1.15;
-  long long pmax = 2 * schedulers / std::max(1LL, ctas * wpc);
+  static const double kFwd[5] = {1.0, 1.0, 1.23, 1.41, 1.68}, kBwd[5] = {1.0, 1.0, 1.37, 1.7, 2.5};
+  auto crowd = [&](long long warps) {
+    const long long w = std::min<long long>(4, std::max<long long>(1, (warps + schedulers - 1) / schedulers));
+    return backward ? kBwd[w] : kFwd[w];
+  };
+  long long pmax = 4 * schedulers / std::max(1LL, ctas * wpc);
   pmax = std::min<long long>(pmax, cap > 1 ? cap : kMaxSegments);
   pmax = std::min<long long>(pmax, kMaxSegments);
   const int warm_steps = g_split_warm_steps.load(std::memory_order_relaxed);
   const long long warm = ((warm_steps > 0 ? warm_steps : kDefaultWarmSteps) + tile - 1) / tile;
   long long best_p = 1;
-  double best_cost = (double)ntiles;
+  const double unsplit_cost = (double)ntiles * crowd(ctas * wpc);
+  double best_cost = unsplit_cost;
   for (long long pseg = 2; pseg <= pmax; ++pseg) {
     const long long seg = (ntiles + pseg - 1) / pseg;
     if (seg < warm || seg * (pseg - 1) >= ntiles) continue;  // warm-up would reach before t = 0 / an empty last segment
-    const double cost = (double)(seg + warm) * (ctas * wpc * pseg > schedulers ? two_warps : 1.0);
+    const double cost = (double)(seg + warm) * crowd(ctas * wpc * pseg);
     if (cost < best_cost) {
       best_cost = cost;
       best_p = pseg;
     }
   }
-  // worth two launches only if a quarter of the serial chain goes away (an explicit cap > 1 is obeyed as is)
-  if (best_p > 1 && (cap > 1 || best_cost * 4 <= (double)ntiles * 3)) {
+  // worth two launches only if a fifth of the time goes away (an explicit cap > 1 is obeyed as is)
+  if (best_p > 1 && (cap > 1 || best_cost <= 0.8 * unsplit_cost)) {
     ts.nseg = (int)best_p;
     ts.seg_tiles = (int)((ntiles + best_p - 1) / best_p);
     ts.warm_tiles = (int)warm;

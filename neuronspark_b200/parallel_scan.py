@@ -193,9 +193,9 @@ def _launch_rowparam_fwd(beta_row32, u, vth_row32, v_init32, *, want_spike, want
 
 
 #: Scans over at most this many columns and at least this many steps are given scratch memory,
-#: which lets the library cut them along time (see nsb_set_time_split); 592 warp schedulers x 2
+#: which lets the library cut them along time (see nsb_set_time_split); 592 warp schedulers x 4
 #: warps / 2 segments x 32 columns, and a scan several warm-ups long.
-TIME_SPLIT_MAX_COLS = 18944
+TIME_SPLIT_MAX_COLS = 37888
 TIME_SPLIT_MIN_STEPS = 4096
 
 
