@@ -203,6 +203,14 @@ int nsb_last_launch_info(int32_t out[8]);
 int nsb_scan_plan_query(int backward, int nstreams, int elem_size, int64_t T, int64_t cols,
                         int tile, int32_t out[5]);
 
+/* How the time axis of a scan would be divided on a B200, computed on the host: out[0..2] = segments,
+ * tiles per segment and warm-up tiles of the time split a row-parameter scan of this shape takes when it
+ * is given scratch (1, 0, 0: none); out[3] = chained chunks of a backward launch over these columns
+ * (1: none; the modulated kernels' rule is evaluated for CTAs of warps_per_cta warps, three per SM).
+ * lanes / warps_per_cta: the launch shape (nsb_scan_plan_query). */
+int nsb_time_plan_query(int backward, int modulated, int64_t T, int64_t cols, int tile, int lanes,
+                        int warps_per_cta, int32_t out[4]);
+
 /*
  * Selective PLIF forward scan. Replaces _TritonPLIFForward.forward /
  * _fused_plif_fwd_kernel (atomic_ops/parallel_scan.py:196-232, 706-735).

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "nsb_last_launch_info": (c_int, [ctypes.POINTER(c_int32)]),
     "nsb_scan_plan_query": (c_int, [c_int, c_int, c_int, c_int64, c_int64, c_int,
                                     ctypes.POINTER(c_int32)]),
+    "nsb_time_plan_query": (c_int, [c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, ctypes.POINTER(c_int32)]),
     "nsb_plif_selective_fwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_void_p]),
     "nsb_plif_selective_bwd": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int,
                                                           c_float, c_void_p, c_void_p]),
@@ -191,6 +192,16 @@ def scan_plan(backward: bool, nstreams: int, elem_size: int, T: int, cols: int, 
     check(lib().nsb_scan_plan_query(int(backward), nstreams, elem_size, T, cols, tile, out),
           "nsb_scan_plan_query")
     return dict(zip(("lanes_per_thread", "warps_per_cta", "stages", "grid", "smem_bytes"), out))
+
+
+def time_plan(backward: bool, T: int, cols: int, tile: int = 32, lanes: int = 1, warps_per_cta: int = 1,
+              modulated: bool = False) -> dict:
+    """How the library would divide the time axis of such a scan on a B200 (host arithmetic only): the time
+    split of a row-parameter scan and the chained chunks of a backward launch."""
+    out = (c_int32 * 4)()
+    check(lib().nsb_time_plan_query(int(backward), int(modulated), T, cols, tile, lanes, warps_per_cta, out),
+          "nsb_time_plan_query")
+    return dict(zip(("segments", "seg_tiles", "warm_tiles", "chain_chunks"), out))
 
 
 def convert(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:

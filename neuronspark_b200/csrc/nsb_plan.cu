@@ -352,6 +352,26 @@ extern "C" int nsb_last_time_split(int32_t out[3]) {
   return NSB_OK;
 }
 
+extern "C" int nsb_time_plan_query(int backward, int modulated, int64_t T, int64_t cols, int tile, int lanes,
+                                   int warps_per_cta, int32_t out[4]) {
+  if (!out || T < 0 || cols <= 0 || (tile != 8 && tile != 16 && tile != 32) || lanes < 1 || lanes > 4 ||
+      warps_per_cta < 1 || warps_per_cta > 32)
+    return NSB_ERR_INVALID_ARG;
+  const nsb::TimeSplit ts = nsb::plan_time_split(nsb::b200_device_info(), T, cols, tile, lanes, warps_per_cta,
+                                                 backward != 0);
+  out[0] = ts.nseg;
+  out[1] = ts.seg_tiles;
+  out[2] = ts.warm_tiles;
+  // chained chunks a backward launch over these columns would take (selective / resonate-and-fire / linear
+  // scans by their width; with the modulation fused in, where the launch exceeds the GPU: 444 places of 4 warps)
+  const int ntiles = (int)((T + tile - 1) / tile);
+  const long long warps = (cols + 32LL * lanes - 1) / (32LL * lanes);
+  const bool eligible = modulated ? (warps + warps_per_cta - 1) / warps_per_cta > 3LL * nsb::b200_device_info().sm_count
+                                  : cols >= 49152;
+  out[3] = backward ? nsb::plan_chain_chunks(eligible, ntiles, (modulated ? 1024 : (cols >= 98304 ? 128 : 512)) / tile) : 1;
+  return NSB_OK;
+}
+
 extern "C" int nsb_scan_plan_query(int backward, int nstreams, int elem_size, int64_t T, int64_t cols,
                                    int tile, int32_t out[5]) {
   if (!out || T < 0 || cols <= 0 || nstreams < 1 || nstreams > 6 || (elem_size != 2 && elem_size != 4) ||

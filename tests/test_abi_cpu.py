@@ -103,3 +103,30 @@ def test_launch_planner(built_lib):
     _lib.set_tuning()
     # a single tile never asks for a deep ring; tiny problems still get a plan
     assert _lib.scan_plan(False, 1, 4, 5, 7)["grid"] == 1
+
+
+def test_time_axis_planning(built_lib):
+    """The division of the time axis - segments of the row-parameter time split, chained chunks of a
+    backward launch - is host arithmetic; the measured cases it was fitted to, without a GPU."""
+    from neuronspark_b200 import _lib
+    split = lambda bwd, cols, T=8192: _lib.time_plan(bwd, T, cols, tile=32)["segments"]
+    # forward / backward segments at T = 8192 (one lane per thread, 32-step tiles, warm-up 1024 steps)
+    assert (split(False, 6144), split(True, 6144)) == (8, 6)      # config 1: 192 column warps for 592 schedulers
+    assert (split(False, 1536), split(True, 1536)) == (8, 8)
+    assert (split(False, 12288), split(True, 12288)) == (6, 3)
+    assert (split(False, 24576), split(True, 24576)) == (3, 2)
+    assert (split(False, 36864), split(True, 36864)) == (2, 1)
+    assert (split(False, 49152), split(True, 49152)) == (1, 1)    # too wide: left alone
+    assert split(False, 6144, T=1024) == 1                         # too short for a warm-up of 1024 steps
+    p = _lib.time_plan(False, 8192, 6144, tile=32)
+    assert p["seg_tiles"] * p["segments"] >= 256 > p["seg_tiles"] * (p["segments"] - 1) and p["warm_tiles"] == 32
+    # chained chunks of the backward: 128-step chunks from 98 304 columns on, 512-step chunks from 49 152
+    chain = lambda cols, **k: _lib.time_plan(True, 8192, cols, tile=8, **k)["chain_chunks"]
+    assert chain(196608, lanes=4, warps_per_cta=2) == 64
+    assert chain(98304, lanes=2, warps_per_cta=2) == 64
+    assert chain(49152, lanes=2) == 16
+    assert chain(24576) == 1
+    assert _lib.time_plan(False, 8192, 196608, tile=8, lanes=4, warps_per_cta=4)["chain_chunks"] == 1  # forward: never
+    # modulation fused in: only where the launch has more CTAs than the GPU holds (768 for 444)
+    assert chain(196608, lanes=2, warps_per_cta=4, modulated=True) == 8
+    assert chain(98304, lanes=2, warps_per_cta=4, modulated=True) == 1
