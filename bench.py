@@ -184,6 +184,8 @@ class ScanStep:
         self.g_v0 = torch.empty((B, D), dtype=torch.float32, device=dev)
         # a few KB that let a backward launch of more CTAs than the GPU holds chain chunks of the time axis
         self.chain = ps._chain_scratch(T, B * D, dev)
+        # scratch that lets the library cut a forward scan over few columns along time (None for the others)
+        self.split = ps._split_scratch(T, B * D, dev)
         if rf:
             self.ckpt_w = torch.empty_like(self.ckpt)
             self.w_last, self.g_w0, self.w0 = (torch.zeros((B, D), dtype=torch.float32, device=dev)
@@ -197,13 +199,13 @@ class ScanStep:
             self._lib.check(self.L.nsb_plif_rf_fwd(
                 p(i["beta"]), p(i["gain"]), p(i["cur"]), p(i["vth"]), p(i["v0"]), p(self.w0), p(self.spike),
                 None, None, None, p(self.ckpt), p(self.ckpt_w), p(self.v_last), p(self.w_last), self.T,
-                self.cols, self._lib.BF16, self.C, self.stream), "nsb_plif_rf_fwd")
+                self.cols, self._lib.BF16, self.C, p(self.split), self.stream), "nsb_plif_rf_fwd")
             if self.launch_fwd is None:
                 self.launch_fwd = self._lib.last_launch_info()
             return
         self._lib.check(self.L.nsb_plif_selective_fwd(
             p(i["beta"]), p(i["cur"]), p(i["gain"]), p(i["vth"]), p(i["v0"]), p(self.spike), None, None,
-            p(self.ckpt), p(self.v_last), self.T, self.cols, self._lib.BF16, self.C, self.stream),
+            p(self.ckpt), p(self.v_last), self.T, self.cols, self._lib.BF16, self.C, p(self.split), self.stream),
             "nsb_plif_selective_fwd")
         if self.launch_fwd is None:
             self.launch_fwd = self._lib.last_launch_info()
@@ -523,12 +525,13 @@ def run_modulated(args):
     g_w0 = torch.empty_like(v_last) if rf else None
     stream = _lib.stream_ptr(dev)
     info = {}
+    split_scratch = ps._split_scratch(T, cols, dev)  # few columns: the forward may be cut along time
 
     def fwd():
         _lib.check(L.nsb_plif_modulated_fwd(
             p(raw_beta), p(raw_alpha), p(raw_th), p(raw_omega), p(cur), p(bias[0]), p(bias[1]), p(bias[2]),
             p(bias[3]), 0.1, D, p(v0), p(w0), p(spike), None, p(ckv), p(ckw), p(v_last), p(w_last), 4.0, 0.4,
-            None, None, T, cols, _lib.BF16, C, stream), "nsb_plif_modulated_fwd")
+            None, None, T, cols, _lib.BF16, C, p(split_scratch), stream), "nsb_plif_modulated_fwd")
         info.setdefault("fwd", _lib.last_launch_info())
 
     def bwd():
@@ -717,7 +720,7 @@ def run_inference(args):
                 _lib.check(L.nsb_plif_selective_fwd(
                     inp["beta"].data_ptr() + off, inp["cur"].data_ptr() + off, inp["gain"].data_ptr() + off,
                     inp["vth"].data_ptr() + off, p(src), None, packed.data_ptr() + c * T * words * 4, None,
-                    None, p(dst), T, cols, _lib.BF16, tile_steps, st), "selective_fwd")
+                    None, p(dst), T, cols, _lib.BF16, tile_steps, None, st), "selective_fwd")
                 src, dst = dst, src
 
     def barrier():

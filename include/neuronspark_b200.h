@@ -116,7 +116,11 @@ int nsb_selftest_wait_timeout(void* stream);
 int nsb_convert(const void* src, void* dst, int64_t n, int src_dtype, int dst_dtype, void* stream);
 
 /*
- * Time split of the row-parameter forward scans over few columns. A scan over a few thousand
+ * Time split of scans over few columns: the row-parameter scans by default, and - forward only, and only
+ * on request (nsb_set_time_split with max_segments above 1) - the selective u-form, resonate-and-fire and
+ * modulated scans, whose `split_scratch` argument has the same meaning (a single sequence of the 768-wide
+ * model is 6 144 columns of hidden neurons; those neurons' memory can be longer than any affordable warm-up,
+ * see below, so the caller who knows their dynamics decides). A scan over a few thousand
  * columns occupies a few hundred warps while each warp is bound by its own serial chain over T;
  * the other SMs idle. Given scratch memory (`split_scratch` of nsb_plif_rowparam_fwd,
  * nsb_plif_rowparam_residual_fwd, nsb_plif_rowparam_pattern_fwd, nsb_plif_rowparam_bwd and
@@ -137,13 +141,23 @@ int nsb_convert(const void* src, void* dst, int64_t n, int src_dtype, int dst_dt
  * association: equal to the serial sums to fp32 rounding, and deterministic). The reference has no counterpart (its kernels walk T serially, one program per 128
  * columns, atomic_ops/parallel_scan.py:496-530).
  *
+ * A neuron whose beta has been trained close to 1 forgets more slowly than the warm-up is long; its
+ * segments are rescanned and the two launches cost more than the plain scan. In automatic mode each
+ * split launch therefore copies its rescan counters to pinned host memory (asynchronously, 8 bytes),
+ * and the next launch with the same beta_row vector, T, cols and direction reads what has arrived:
+ * when one warp had to rescan more segments than the split saved, that neuron's scans run unsplit for
+ * the next 64 calls and then try again. The results do not depend on any of this.
+ *
  * nsb_set_time_split      max_segments: 0 = automatic, 1 = never split, 2..16 = at most that many
- *                         (and split even where the planner expects little gain); warm_steps: 0 =
- *                         default (1024). Process-global, read at each launch.
+ *                         (and split even where the planner expects little gain, without the
+ *                         feedback above); warm_steps: 0 = default (1024). Process-global, read at
+ *                         each launch; a call also forgets what earlier launches rescanned.
  * nsb_last_time_split     {segments, tiles per segment, warm-up tiles} of the calling thread's last
  *                         forward scan launch (segments = 1: it was not split). After a split
  *                         launch the number of rescanned (warp, segment) pairs is the uint32 at
- *                         split_scratch[2*segments*cols] (forward) / [4*segments*cols] (backward).
+ *                         split_scratch[k*segments*cols], k = 2 for a first-order forward, 4 for a
+ *                         resonate-and-fire forward and for the backward; the uint32 after it is
+ *                         the largest number of segments any one warp rescanned.
  */
 int nsb_set_time_split(int max_segments, int warm_steps);
 int64_t nsb_time_split_scratch_floats(int64_t cols);
@@ -239,7 +253,7 @@ int nsb_plif_selective_fwd(const void* beta, const void* u_or_cur, const void* g
                            const void* v_th, const float* v_init, void* spike_dense,
                            uint32_t* spike_packed, void* v_post, float* v_ckpt,
                            float* v_last, int64_t T, int64_t cols, int dtype,
-                           int ckpt_interval, void* stream);
+                           int ckpt_interval, float* split_scratch, void* stream);
 
 /*
  * Reverse-time surrogate-gradient pass of the selective scan. Replaces
@@ -306,7 +320,7 @@ int nsb_plif_rf_fwd(const void* beta, const void* omega, const void* u, const vo
                     const float* v_init, const float* w_init, void* spike_dense,
                     uint32_t* spike_packed, void* v_post, void* w_out, float* v_ckpt,
                     float* w_ckpt, float* v_last, float* w_last, int64_t T, int64_t cols,
-                    int dtype, int ckpt_interval, void* stream);
+                    int dtype, int ckpt_interval, float* split_scratch, void* stream);
 
 /*
  * Reverse pass of the resonate-and-fire scan. Replaces _fused_rf_plif_bwd_kernel and
@@ -448,7 +462,8 @@ int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const vo
                            const float* w_init, void* spike_dense, uint32_t* spike_packed,
                            float* v_ckpt, float* w_ckpt, float* v_last, float* w_last,
                            float alpha0, float sigma0, double* u_stats, float* alpha_out, int64_t T,
-                           int64_t cols, int dtype, int ckpt_interval, void* stream);
+                           int64_t cols, int dtype, int ckpt_interval, float* split_scratch,
+                           void* stream);
 
 /* Floats of scratch nsb_plif_modulated_bwd needs when any bias gradient is asked for. */
 int64_t nsb_plif_modulated_bwd_scratch_floats(int64_t cols);

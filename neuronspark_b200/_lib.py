@@ -36,7 +36,7 @@ _SIGNATURES = {
     "nsb_scan_plan_query": (c_int, [c_int, c_int, c_int, c_int64, c_int64, c_int,
                                     ctypes.POINTER(c_int32)]),
     "nsb_time_plan_query": (c_int, [c_int, c_int, c_int64, c_int64, c_int, c_int, c_int, ctypes.POINTER(c_int32)]),
-    "nsb_plif_selective_fwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_plif_selective_fwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nsb_plif_selective_bwd": (c_int, [c_void_p] * 12 + [c_int64, c_int64, c_int, c_int, c_int,
                                                           c_float, c_void_p, c_void_p]),
     "nsb_chain_scratch_words": (c_int64, [c_int64]),
@@ -49,12 +49,12 @@ _SIGNATURES = {
     "nsb_last_time_split": (c_int, [ctypes.POINTER(c_int32)]),
     "nsb_plif_rowparam_bwd": (c_int, [c_void_p] * 10 + [c_int64, c_int64, c_int, c_int, c_int,
                                                          c_float, c_void_p, c_void_p]),
-    "nsb_plif_rf_fwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_void_p]),
+    "nsb_plif_rf_fwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nsb_plif_rf_bwd": (c_int, [c_void_p] * 14 + [c_int64, c_int64, c_int, c_int, c_int, c_float,
                                                    c_void_p, c_void_p]),
     "nsb_plif_modulated_fwd_stats_doubles": (c_int64, [c_int64]),
     "nsb_plif_modulated_fwd": (c_int, [c_void_p] * 9 + [c_float, c_int64] + [c_void_p] * 8 +
-                               [c_float, c_float, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
+                               [c_float, c_float, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nsb_plif_modulated_bwd_scratch_floats": (c_int64, [c_int64]),
     "nsb_plif_modulated_bwd": (c_int, [c_void_p] * 9 + [c_float, c_int64] + [c_void_p] * 15 +
                                [c_int64, c_int64, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),

@@ -13,6 +13,8 @@
 #include <algorithm>
 #include <atomic>
 #include <cmath>
+#include <cstring>
+#include <mutex>
 
 #include "nsb_scan.cuh"
 
@@ -232,10 +234,19 @@ long long time_split_scratch_floats(long long cols) {
 }
 
 TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, int tile, int lanes, int wpc,
-                          bool backward) {
+                          bool backward, int family) {
   TimeSplit ts;
   const int cap = g_split_max_segments.load(std::memory_order_relaxed);
   if (cap == 1 || tile <= 0 || cols > kSplitMaxCols) return ts;
+  // The scans of the layers' hidden neurons forget as slowly as their largest beta lets them (0.99 at the
+  // reference's initialisation: 1 650 steps to lose 24 bits), and a resonate-and-fire column whose
+  // beta^2 + omega^2 sits at the stability clamp contracts by 0.999 a step: a 1 024-step warm-up then
+  // leaves segments to rescan, and one rescanned segment undoes the gain. Measured, forward at T = 8192,
+  // 6 144 columns: resonate-and-fire 313 -> 142 us with 6 segments, first order with the modulation 561 ->
+  // 288 us with 4, both without a rescan on short-memory parameters; resonate-and-fire with the modulation
+  // 892 -> 945-1000 us because 1-3 % of the warps rescanned. So these split only where the caller, who
+  // knows the dynamics, asks for it.
+  if (family != 0 && cap <= 1) return ts;
   const long long ntiles = (T + tile - 1) / tile;
   const long long nwarps = (cols + 32LL * lanes - 1) / (32LL * lanes);
   const long long ctas = (nwarps + wpc - 1) / wpc;
@@ -276,8 +287,90 @@ TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, in
     ts.nseg = (int)best_p;
     ts.seg_tiles = (int)((ntiles + best_p - 1) / best_p);
     ts.warm_tiles = (int)warm;
+    // the second launch lasts as long as its busiest warp rescans, at a lone warp's pace
+    ts.allow_rescans = (int)std::max(0.0, std::floor((unsplit_cost - best_cost) / (double)ts.seg_tiles));
   }
   return ts;
+}
+
+// ---- what split launches had to rescan, fed back
+//
+// The split pays while segments merge with the exact trajectory inside the warm-up. A neuron trained
+// to a long memory (beta near 1) does not, and then the two launches cost more than the plain scan.
+// Each automatic split launch therefore copies its two counter words to pinned host memory, and the
+// next launch for the same neuron reads them - whatever has arrived by then, without waiting: if one
+// warp had to rescan more segments than the split saved, that neuron's scans go unsplit for the next
+// 64 calls and then try again.
+namespace {
+struct FeedbackEntry {
+  const void* neuron;
+  long long T, cols;
+  int backward, allow, skip_left;
+};
+constexpr int kFeedbackSlots = 256;
+constexpr int kBackoffCalls = 64;
+FeedbackEntry g_fb[kFeedbackSlots];
+int g_fb_used = 0, g_fb_next = 0;
+unsigned int* g_fb_host = nullptr;  // pinned, two words per slot
+bool g_fb_failed = false;
+std::mutex g_fb_mu;
+
+int feedback_find(const void* neuron, long long T, long long cols, bool backward) {
+  for (int i = 0; i < g_fb_used; ++i)
+    if (g_fb[i].neuron == neuron && g_fb[i].T == T && g_fb[i].cols == cols && g_fb[i].backward == (int)backward) return i;
+  return -1;
+}
+}  // namespace
+
+bool time_split_automatic() { return g_split_max_segments.load(std::memory_order_relaxed) == 0; }
+
+bool split_feedback_allows(const void* neuron, long long T, long long cols, bool backward) {
+  std::lock_guard<std::mutex> lk(g_fb_mu);
+  const int i = feedback_find(neuron, T, cols, backward);
+  if (i < 0 || !g_fb_host) return true;
+  FeedbackEntry& e = g_fb[i];
+  if (e.skip_left > 0) {
+    --e.skip_left;
+    return false;
+  }
+  volatile unsigned int* h = g_fb_host + 2 * i;
+  if ((long long)h[1] > (long long)e.allow) {
+    h[0] = h[1] = 0;
+    e.skip_left = kBackoffCalls - 1;
+    return false;
+  }
+  return true;
+}
+
+void split_feedback_record(const void* neuron, long long T, long long cols, bool backward,
+                           const unsigned int* dev_words, int allow_rescans, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(g_fb_mu);
+  if (g_fb_failed) return;
+  if (!g_fb_host) {
+    void* h = nullptr;
+    if (cudaHostAlloc(&h, sizeof(unsigned int) * 2 * kFeedbackSlots, cudaHostAllocPortable) != cudaSuccess) {
+      cudaGetLastError();  // no feedback then; the split stays exact, only its choice is blind
+      g_fb_failed = true;
+      return;
+    }
+    memset(h, 0, sizeof(unsigned int) * 2 * kFeedbackSlots);
+    g_fb_host = static_cast<unsigned int*>(h);
+  }
+  int i = feedback_find(neuron, T, cols, backward);
+  if (i < 0) {
+    if (g_fb_used < kFeedbackSlots) {
+      i = g_fb_used++;
+    } else {  // oldest first
+      i = g_fb_next;
+      g_fb_next = (g_fb_next + 1) % kFeedbackSlots;
+    }
+    g_fb[i] = FeedbackEntry{neuron, T, cols, (int)backward, allow_rescans, 0};
+    g_fb_host[2 * i] = g_fb_host[2 * i + 1] = 0;
+  }
+  g_fb[i].allow = allow_rescans;
+  if (cudaMemcpyAsync(g_fb_host + 2 * i, dev_words, 2 * sizeof(unsigned int), cudaMemcpyDeviceToHost, stream) !=
+      cudaSuccess)
+    cudaGetLastError();
 }
 
 // ---- chained chunks of a backward launch
@@ -336,6 +429,10 @@ extern "C" int nsb_set_time_split(int max_segments, int warm_steps) {
   if (max_segments < 0 || max_segments > 16 || warm_steps < 0) return NSB_ERR_INVALID_ARG;
   nsb::g_split_max_segments.store(max_segments, std::memory_order_relaxed);
   nsb::g_split_warm_steps.store(warm_steps, std::memory_order_relaxed);
+  {  // a new setting starts without memory of what earlier launches rescanned
+    std::lock_guard<std::mutex> lk(nsb::g_fb_mu);
+    nsb::g_fb_used = nsb::g_fb_next = 0;
+  }
   return NSB_OK;
 }
 
@@ -358,7 +455,7 @@ extern "C" int nsb_time_plan_query(int backward, int modulated, int64_t T, int64
       warps_per_cta < 1 || warps_per_cta > 32)
     return NSB_ERR_INVALID_ARG;
   const nsb::TimeSplit ts = nsb::plan_time_split(nsb::b200_device_info(), T, cols, tile, lanes, warps_per_cta,
-                                                 backward != 0);
+                                                 backward != 0, modulated ? 2 : 0);
   out[0] = ts.nseg;
   out[1] = ts.seg_tiles;
   out[2] = ts.warm_tiles;

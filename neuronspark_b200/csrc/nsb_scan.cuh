@@ -181,10 +181,22 @@ Plan plan_scan(const DeviceInfo& dev, const PlanQuery& q, const Tuning& tune);
 // Time split of a forward scan over few columns (nseg == 1: none). Host arithmetic (nsb_plan.cu).
 struct TimeSplit {
   int nseg = 1, seg_tiles = 0, warm_tiles = 0;
+  int allow_rescans = 0;  // segments one warp may have to rescan before the split costs more than it saves
 };
+// family: 0 = row-parameter scans (split wherever the model below says it pays); 1 = scans with per-step
+// parameters, 2 = those with the modulation fused in (split only on request: nsb_set_time_split with a
+// segment count above 1)
 TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, int tile, int lanes, int wpc,
-                          bool backward);
+                          bool backward, int family);
 TimeSplit& last_time_split();  // of the calling thread's last forward launch
+// What earlier split launches of one neuron had to rescan, fed back into the automatic choice. `neuron`
+// is any pointer that names the call site (the per-row parameter vector). _allows: false while that
+// neuron's dynamics forget too slowly for the split to pay. _record: queues the copy of the launch's two
+// counter words {segments rescanned, most by one warp} to the host.
+bool time_split_automatic();
+bool split_feedback_allows(const void* neuron, long long T, long long cols, bool backward);
+void split_feedback_record(const void* neuron, long long T, long long cols, bool backward,
+                           const unsigned int* dev_words, int allow_rescans, cudaStream_t stream);
 // floats of scratch a time-split launch over `cols` columns may need (boundary states + a counter)
 long long time_split_scratch_floats(long long cols);
 
@@ -409,6 +421,8 @@ struct FwdParams {
   int nseg, seg_tiles, warm_tiles, fixup;
   float* vspec;
   float* vend;
+  float* wspec;  // the same for the second state of the resonate-and-fire scans
+  float* wend;
   unsigned int* fix_count;
 };
 
@@ -907,15 +921,19 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
   // SPLIT is a template parameter: the kernels of ordinary launches carry none of this (with the
   // choice made at run time the packed row-parameter scan took 16 instead of 13 instructions per
   // step and half as long again).
-  static_assert(!SPLIT || (!MT::kSecond && !MT::kStats && !MT::kMod), "no time split for this mode");
+  static_assert(!SPLIT || !MT::kStats, "no time split for the kernels that accumulate moments");
   constexpr bool split = SPLIT;
   const int seg_lo = split ? (p.fixup ? 1 : (int)blockIdx.y) : 0;
   const int seg_hi = split ? (p.fixup ? p.nseg : (int)blockIdx.y + 1) : 1;
-  float carry[V];
+  float carry[V], carryw[V];
   if (split && p.fixup) {
 #pragma unroll
-    for (int j = 0; j < V; ++j) carry[j] = valid[j] ? p.vend[colj[j]] : 0.0f;
+    for (int j = 0; j < V; ++j) {
+      carry[j] = valid[j] ? p.vend[colj[j]] : 0.0f;
+      carryw[j] = (MT::kSecond && valid[j]) ? p.wend[colj[j]] : 0.0f;
+    }
   }
+  unsigned int rescans = 0;
   for (int seg = seg_lo; seg < seg_hi && !failed; ++seg) {
     int tile_begin = 0, tile_emit = 0, tile_end = ntiles_total;
     if (split) {
@@ -925,22 +943,34 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
         bool differs = false;
 #pragma unroll
         for (int j = 0; j < V; ++j)
-          if (valid[j])
+          if (valid[j]) {
             differs |= __float_as_uint(p.vspec[(long long)seg * row_elems + colj[j]]) != __float_as_uint(carry[j]);
+            if (MT::kSecond)
+              differs |= __float_as_uint(p.wspec[(long long)seg * row_elems + colj[j]]) != __float_as_uint(carryw[j]);
+          }
         if (!__any_sync(0xffffffffu, differs)) {  // the speculation held: this segment's results stand
 #pragma unroll
-          for (int j = 0; j < V; ++j) carry[j] = valid[j] ? p.vend[(long long)seg * row_elems + colj[j]] : 0.0f;
+          for (int j = 0; j < V; ++j) {
+            carry[j] = valid[j] ? p.vend[(long long)seg * row_elems + colj[j]] : 0.0f;
+            carryw[j] = (MT::kSecond && valid[j]) ? p.wend[(long long)seg * row_elems + colj[j]] : 0.0f;
+          }
           continue;
         }
-        if (lane == 0 && p.fix_count) atomicAdd(p.fix_count, 1u);
+        if (lane == 0 && p.fix_count) {
+          atomicAdd(p.fix_count, 1u);
+          atomicMax(p.fix_count + 1, ++rescans);  // the warp with the most rescans sets the second launch's time
+        }
         tile_begin = tile_emit;
 #pragma unroll
-        for (int j = 0; j < V; ++j) v[j] = carry[j];
+        for (int j = 0; j < V; ++j) {
+          v[j] = carry[j];
+          w[j] = carryw[j];
+        }
       } else {
         tile_begin = seg == 0 ? 0 : tile_emit - p.warm_tiles;
         if (seg > 0) {
 #pragma unroll
-          for (int j = 0; j < V; ++j) v[j] = 0.0f;
+          for (int j = 0; j < V; ++j) v[j] = w[j] = 0.0f;
         }
       }
     }
@@ -962,7 +992,10 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
       if (split && !p.fixup && seg > 0 && ia == tile_emit) {  // warmed up: what this segment assumes it starts from
 #pragma unroll
         for (int j = 0; j < V; ++j)
-          if (valid[j]) p.vspec[(long long)seg * row_elems + colj[j]] = v[j];
+          if (valid[j]) {
+            p.vspec[(long long)seg * row_elems + colj[j]] = v[j];
+            if (MT::kSecond) p.wspec[(long long)seg * row_elems + colj[j]] = w[j];
+          }
       }
       if constexpr (MODE == MODE_ROWPAT) {
         if (p.pat_in && i + 1 < nt) load_patterns(ia + 1, pin_nxt);
@@ -1042,16 +1075,16 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
       __syncwarp();
     }
     if (split && !failed) {
-      if (p.fixup) {
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
+      for (int j = 0; j < V; ++j) {
+        if (p.fixup) {
           carry[j] = v[j];
-          if (valid[j]) p.vend[(long long)seg * row_elems + colj[j]] = v[j];
+          carryw[j] = w[j];
         }
-      } else {
-#pragma unroll
-        for (int j = 0; j < V; ++j)
-          if (valid[j]) p.vend[(long long)seg * row_elems + colj[j]] = v[j];
+        if (valid[j]) {
+          p.vend[(long long)seg * row_elems + colj[j]] = v[j];
+          if (MT::kSecond) p.wend[(long long)seg * row_elems + colj[j]] = w[j];
+        }
       }
     }
   }
@@ -1073,7 +1106,10 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
   }
   if (split && p.fixup) {
 #pragma unroll
-    for (int j = 0; j < V; ++j) v[j] = carry[j];
+    for (int j = 0; j < V; ++j) {
+      v[j] = carry[j];
+      w[j] = carryw[j];
+    }
   }
   if (!split || p.fixup) {
 #pragma unroll
@@ -1812,6 +1848,7 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
     }
   }
   bool primed = false;  // whether any copy was issued (a CTA that gives up before has nothing in flight)
+  [[maybe_unused]] unsigned int rescans = 0;
   for (int seg = seg_first; seg >= seg_last && !failed; --seg) {
     primed = true;
     int tile_lo = 0, tile_top = ntiles, tile_emit_top = ntiles;  // walk tiles tile_top-1 .. tile_lo; emit below tile_emit_top
@@ -1838,7 +1875,10 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
           }
           continue;
         }
-        if (lane == 0 && p.fix_count) atomicAdd(p.fix_count, 1u);
+        if (lane == 0 && p.fix_count) {
+          atomicAdd(p.fix_count, 1u);
+          atomicMax(p.fix_count + 1, ++rescans);
+        }
         tile_top = tile_emit_top;
 #pragma unroll
         for (int j = 0; j < V; ++j) acc[j] = carry[j];
@@ -2142,10 +2182,16 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
   // Few columns: cut the time axis into segments that run side by side (see the kernel); needs the
   // caller's scratch for the segment boundary states.
   TimeSplit ts;
-  // built for: row-parameter family, tiled copies, one lane per thread, tiles of 16 or 32 steps
-  constexpr bool kSplitBuilt = (MODE == MODE_ROW || MODE == MODE_ROWRES || MODE == MODE_ROWPAT) && TMA && V == 1 &&
-                               (C == 16 || C == 32);
-  if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc, false);
+  // built for: the row-parameter family, and the selective, resonate-and-fire and modulated scans of the
+  // layers' hidden neurons (a single sequence is 6 144 columns there); tiled copies, one lane per thread,
+  // tiles of 16 or 32 steps
+  constexpr bool kSplitBuilt = (MODE == MODE_ROW || MODE == MODE_ROWRES || MODE == MODE_ROWPAT || MODE == MODE_U ||
+                                MODE == MODE_RF || MODE == MODE_MOD || MODE == MODE_RFMOD) &&
+                               TMA && V == 1 && (C == 16 || C == 32);
+  if (kSplitBuilt && a.split_scratch)
+    ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc, false, MT::kMod ? 2 : (MT::kRow ? 0 : 1));
+  const bool feedback = ts.nseg > 1 && time_split_automatic();
+  if (feedback && !split_feedback_allows(a.beta_row, a.T, a.cols, false)) ts = TimeSplit();
   last_time_split() = ts;
   if (ts.nseg > 1) {
     if constexpr (kSplitBuilt) {
@@ -2153,16 +2199,20 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
       NSB_CUDA_TRY(cudaFuncSetAttribute(skern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem),
                    "cudaFuncSetAttribute(fwd split)");
       p.nseg = ts.nseg; p.seg_tiles = ts.seg_tiles; p.warm_tiles = ts.warm_tiles;
+      const size_t plane = (size_t)ts.nseg * a.cols;
       p.vspec = a.split_scratch;
-      p.vend = a.split_scratch + (size_t)ts.nseg * a.cols;
-      p.fix_count = reinterpret_cast<unsigned int*>(a.split_scratch + 2 * (size_t)ts.nseg * a.cols);
-      NSB_CUDA_TRY(cudaMemsetAsync(p.fix_count, 0, sizeof(unsigned int), a.stream), "clear the rescan counter");
+      p.vend = a.split_scratch + plane;
+      p.wspec = a.split_scratch + 2 * plane;
+      p.wend = a.split_scratch + 3 * plane;
+      p.fix_count = reinterpret_cast<unsigned int*>(a.split_scratch + (MT::kSecond ? 4 : 2) * plane);
+      NSB_CUDA_TRY(cudaMemsetAsync(p.fix_count, 0, 2 * sizeof(unsigned int), a.stream), "clear the rescan counters");
       p.fixup = 0;
       skern<<<dim3(plan.grid, ts.nseg), plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
       NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_split_kernel");
       p.fixup = 1;
       skern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
       NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_split_kernel (check)");
+      if (feedback) split_feedback_record(a.beta_row, a.T, a.cols, false, p.fix_count, ts.allow_rescans, a.stream);
     }
   } else {
     kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
@@ -2259,7 +2309,9 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
   // Few columns: the time axis cut into segments that run side by side (see the kernel)
   TimeSplit ts;
   constexpr bool kSplitBuilt = MODE == MODE_ROW && TMA && !HAS_GV && V == 1 && (C == 16 || C == 32);
-  if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc, true);
+  if (kSplitBuilt && a.split_scratch) ts = plan_time_split(dev, a.T, a.cols, C, V, plan.wpc, true, 0);
+  const bool feedback = ts.nseg > 1 && time_split_automatic();
+  if (feedback && !split_feedback_allows(a.beta_row, a.T, a.cols, true)) ts = TimeSplit();
   last_time_split() = ts;
   set_last_chain_chunks(1);
   int launched_grid = plan.grid;
@@ -2273,7 +2325,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
       p.aspec = a.split_scratch; p.aend = a.split_scratch + n;
       p.partb = a.split_scratch + 2 * n; p.partt = a.split_scratch + 3 * n;
       p.fix_count = reinterpret_cast<unsigned int*>(a.split_scratch + 4 * n);
-      NSB_CUDA_TRY(cudaMemsetAsync(p.fix_count, 0, sizeof(unsigned int), a.stream), "clear the rescan counter");
+      NSB_CUDA_TRY(cudaMemsetAsync(p.fix_count, 0, 2 * sizeof(unsigned int), a.stream), "clear the rescan counters");
       p.fixup = 0;
       skern<<<dim3(plan.grid, ts.nseg), plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6],
                                                                                 tm[7], tm[8], tm[9], tm[10], tm[11]);
@@ -2282,6 +2334,7 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
       skern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8],
                                                                 tm[9], tm[10], tm[11]);
       NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel (time-split check)");
+      if (feedback) split_feedback_record(a.beta_row, a.T, a.cols, true, p.fix_count, ts.allow_rescans, a.stream);
     }
   } else {
     // More CTAs than fit on the GPU at once: chunks of the time axis chained through the per-column

@@ -90,11 +90,11 @@ extern "C" {
 int nsb_plif_selective_fwd(const void* beta, const void* u_or_cur, const void* gain, const void* v_th,
                            const float* v_init, void* spike_dense, uint32_t* spike_packed, void* v_post,
                            float* v_ckpt, float* v_last, int64_t T, int64_t cols, int dtype,
-                           int ckpt_interval, void* stream) {
+                           int ckpt_interval, float* split_scratch, void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
   if (!v_init || !v_last || !f32_aligned(v_init) || !f32_aligned(v_last) || !f32_aligned(v_ckpt) ||
-      !f32_aligned(spike_packed))
+      !f32_aligned(spike_packed) || !f32_aligned(split_scratch))
     return NSB_ERR_INVALID_ARG;
   if (T == 0) {  // nothing to scan: the final state is the initial state
     NSB_CUDA_TRY(cudaMemcpyAsync(v_last, v_init, sizeof(float) * cols, cudaMemcpyDeviceToDevice,
@@ -109,6 +109,7 @@ int nsb_plif_selective_fwd(const void* beta, const void* u_or_cur, const void* g
   a.beta = beta; a.drive = u_or_cur; a.gain = gain; a.vth = v_th; a.v_init = v_init;
   a.spike = spike_dense; a.packed = spike_packed; a.vpost = v_post; a.ckpt = v_ckpt; a.vlast = v_last;
   a.T = T; a.cols = cols; a.mode = gain ? nsb::MODE_AI : nsb::MODE_U; a.tile = ckpt_interval;
+  a.split_scratch = split_scratch;
   a.stream = static_cast<cudaStream_t>(stream);
   return run_fwd(a, dtype);
 }
@@ -226,12 +227,13 @@ int nsb_plif_rowparam_bwd_dalpha(const float* beta_row, const void* u, const flo
 int nsb_plif_rf_fwd(const void* beta, const void* omega, const void* u, const void* v_th,
                     const float* v_init, const float* w_init, void* spike_dense, uint32_t* spike_packed,
                     void* v_post, void* w_out, float* v_ckpt, float* w_ckpt, float* v_last, float* w_last,
-                    int64_t T, int64_t cols, int dtype, int ckpt_interval, void* stream) {
+                    int64_t T, int64_t cols, int dtype, int ckpt_interval, float* split_scratch,
+                    void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || !tile_ok(ckpt_interval)) return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
   if (!v_init || !w_init || !v_last || !w_last) return NSB_ERR_INVALID_ARG;
   if ((v_ckpt == nullptr) != (w_ckpt == nullptr)) return NSB_ERR_INVALID_ARG;
-  const void* fp[] = {v_init, w_init, v_last, w_last, v_ckpt, w_ckpt, spike_packed};
+  const void* fp[] = {v_init, w_init, v_last, w_last, v_ckpt, w_ckpt, spike_packed, split_scratch};
   for (const void* p : fp)
     if (!f32_aligned(p)) return NSB_ERR_INVALID_ARG;
   if (T == 0) {
@@ -251,6 +253,7 @@ int nsb_plif_rf_fwd(const void* beta, const void* omega, const void* u, const vo
   a.spike = spike_dense; a.packed = spike_packed; a.vpost = v_post; a.w_out = w_out;
   a.ckpt = v_ckpt; a.ckpt_w = w_ckpt; a.vlast = v_last; a.wlast = w_last;
   a.T = T; a.cols = cols; a.mode = nsb::MODE_RF; a.tile = ckpt_interval;
+  a.split_scratch = split_scratch;
   a.stream = static_cast<cudaStream_t>(stream);
   return run_fwd(a, dtype);
 }
@@ -316,7 +319,8 @@ int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const vo
                            int64_t channels, const float* v_init, const float* w_init, void* spike_dense,
                            uint32_t* spike_packed, float* v_ckpt, float* w_ckpt, float* v_last,
                            float* w_last, float alpha0, float sigma0, double* u_stats, float* alpha_out,
-                           int64_t T, int64_t cols, int dtype, int ckpt_interval, void* stream) {
+                           int64_t T, int64_t cols, int dtype, int ckpt_interval, float* split_scratch,
+                           void* stream) {
   if (T < 0 || cols < 0 || !dtype_ok(dtype) || (ckpt_interval != 8 && ckpt_interval != 32))
     return NSB_ERR_INVALID_ARG;
   if (cols == 0) return NSB_OK;
@@ -352,6 +356,8 @@ int nsb_plif_modulated_fwd(const void* raw_beta, const void* raw_alpha, const vo
   a.ckpt = v_ckpt; a.ckpt_w = w_ckpt; a.vlast = v_last; a.wlast = w_last;
   a.u_stats = u_stats; a.alpha_out = alpha_out; a.alpha0 = alpha0; a.sigma0 = sigma0;
   a.T = T; a.cols = cols; a.mode = rf ? nsb::MODE_RFMOD : nsb::MODE_MOD; a.tile = ckpt_interval;
+  if (!f32_aligned(split_scratch)) return NSB_ERR_INVALID_ARG;
+  a.split_scratch = u_stats ? nullptr : split_scratch;  // (the kernels that accumulate moments are not split)
   a.stream = st;
   return run_mod_fwd(a, dtype);
 }

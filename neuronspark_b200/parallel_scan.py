@@ -166,8 +166,8 @@ def _launch_selective_fwd(beta, drive, gain, v_th, v_init32, *, want_spike, want
         _lib.check(_lib.lib().nsb_plif_selective_fwd(
             _lib.ptr(beta), _lib.ptr(drive), _lib.ptr(gain), _lib.ptr(v_th), _lib.ptr(v_init32),
             _lib.ptr(spike), _lib.ptr(packed), _lib.ptr(vpost), _lib.ptr(ckpt), _lib.ptr(v_last),
-            T, cols, _lib.dtype_code(dt), C, _lib.stream_ptr(dev)),
-            "nsb_plif_selective_fwd")
+            T, cols, _lib.dtype_code(dt), C, _lib.ptr(None if gain is not None else _split_scratch(T, cols, dev)),
+            _lib.stream_ptr(dev)), "nsb_plif_selective_fwd")
     return spike, packed, vpost, ckpt, v_last, C
 
 
@@ -503,7 +503,7 @@ def _rf_forward(ctx, beta, omega, u, v_th, v_init, w_init, alpha, want_states):
             _lib.ptr(beta_c), _lib.ptr(omega_c), _lib.ptr(u_c), _lib.ptr(vth_c), _lib.ptr(v0), _lib.ptr(w0),
             _lib.ptr(spike), None, _lib.ptr(vpost), _lib.ptr(wout), _lib.ptr(ckv), _lib.ptr(ckw),
             _lib.ptr(v_last), _lib.ptr(w_last), T, cols, _lib.dtype_code(dt), C,
-            _lib.stream_ptr(dev)), "nsb_plif_rf_fwd")
+            _lib.ptr(_split_scratch(T, cols, dev)), _lib.stream_ptr(dev)), "nsb_plif_rf_fwd")
     if needs_grad:
         ctx.save_for_backward(beta_c, omega_c, u_c, vth_c, ckv, ckw)
     ctx.alpha, ctx.alpha_t = _split_alpha(alpha)

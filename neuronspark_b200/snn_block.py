@@ -122,7 +122,8 @@ class ModulatedPLIFScan(torch.autograd.Function):
                 _lib.ptr(biases[1]), _lib.ptr(biases[2]), _lib.ptr(biases[3]), float(v_th_min), ch,
                 _lib.ptr(v0), _lib.ptr(w0), _lib.ptr(spike), None, _lib.ptr(ckv), _lib.ptr(ckw),
                 _lib.ptr(v_last), _lib.ptr(w_last), float(alpha), float(sigma0 or 0.0), _lib.ptr(stats),
-                _lib.ptr(alpha_t), T, cols, _lib.dtype_code(dt), C, _lib.stream_ptr(dev)),
+                _lib.ptr(alpha_t), T, cols, _lib.dtype_code(dt), C,
+                _lib.ptr(None if stats is not None else ps._split_scratch(T, cols, dev)), _lib.stream_ptr(dev)),
                 "nsb_plif_modulated_fwd")
         ctx.alpha_t = alpha_t
         if needs_grad:

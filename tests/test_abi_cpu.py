@@ -47,11 +47,11 @@ def test_argument_validation_needs_no_gpu(built_lib):
     from neuronspark_b200 import _lib
     L = _lib.lib()
     z = ctypes.c_void_p(0)
-    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, -1, 8, 0, 8, z) == 1
-    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 8, 7, 8, z) == 1   # dtype
-    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 8, 0, 5, z) == 1   # interval
-    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 8, 0, 8, z) == 1   # nulls
-    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 0, 0, 8, z) == 0   # empty
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, -1, 8, 0, 8, z, z) == 1
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 8, 7, 8, z, z) == 1   # dtype
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 8, 0, 5, z, z) == 1   # interval
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 8, 0, 8, z, z) == 1   # nulls
+    assert L.nsb_plif_selective_fwd(z, z, z, z, z, z, z, z, z, z, 8, 0, 0, 8, z, z) == 0   # empty
     assert L.nsb_plif_selective_bwd(z, z, z, z, z, z, z, z, z, z, z, z, 8, 8, 0, 8, 9, 1.0, z, z) == 1
     assert L.nsb_plif_rowparam_fwd(z, z, z, z, z, z, z, z, z, 4, 4, 0, 8, z, z) == 1
     assert L.nsb_fp16_encode(z, z, 1, 1, 0, 0, 0, z) == 0

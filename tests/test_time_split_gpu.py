@@ -191,3 +191,74 @@ def test_several_warps_per_scheduler():
     assert nsb.last_time_split()["segments"] >= 2 and nsb.last_launch_info()["launches"] == 2
     ref_packed, ref_v = unsplit(lambda: ps.plif_rowparam_forward_packed(br, u, tr, v0))
     assert torch.equal(packed, ref_packed) and torch.equal(v_last, ref_v)
+
+
+# ---- the scans of the hidden neurons (per-step parameters; forward only)
+
+
+def _hidden_forward(kind, T, B, D, seed, want_grad=False):
+    """(callable returning the scan's outputs as a tuple of tensors) for one of the hidden-neuron scans."""
+    from neuronspark_b200 import snn_block as sb
+    from test_modulated_gpu import mod_inputs
+    from test_rf_gpu import rf_inputs
+    from util import selective_inputs
+    if kind == "u":
+        beta, cur, _, vth, v0 = selective_inputs(T, B, D, torch.bfloat16, DEV, seed=seed, zero_init=False)
+        return lambda: ps.plif_selective_forward_packed(beta, cur, vth, v0)
+    if kind == "rf":
+        beta, omega, u, vth, v0, w0 = rf_inputs(T, B, D, torch.bfloat16, seed)
+        return lambda: ps.rf_plif_parallel_forward_recompute(beta, omega, u, vth, v0, w0)
+    rf = kind == "rfmod"
+    d, b, v0, w0 = mod_inputs(T, B, D, torch.bfloat16, seed, rf)
+    args = (d["raw_beta"], b["b_beta"], d["raw_alpha"], b["b_alpha"], d["raw_th"], b["b_th"], 0.1, d["cur"])
+    if rf:
+        return lambda: sb.modulated_rf_plif_forward(*args, d["raw_omega"], b["b_omega"], v0, w0)
+    return lambda: sb.modulated_plif_forward(*args, v0)
+
+
+@pytest.mark.parametrize("kind", ["u", "rf", "mod", "rfmod"])
+@pytest.mark.parametrize("segments,warm", [(0, 0), (4, 0), (7, 64), (3, 32)])
+def test_hidden_neuron_scans_split_equal_unsplit(kind, segments, warm):
+    """A single sequence of the 768-wide model is 6 144 columns of hidden neurons: on request the
+    selective, resonate-and-fire and modulated forward scans are cut along time as the row-parameter
+    ones are, with both states (V, W) compared at every boundary; short warm-ups force rescans."""
+    T, B, D = 4096 + 40, 2, 768 if kind != "u" else 1024
+    run = _hidden_forward(kind, T, B, D, seed=31)
+    nsb.set_time_split(segments, warm)
+    with torch.no_grad():
+        got = run()
+    ts = nsb.last_time_split()
+    if segments == 0:  # these neurons' memory may outlast any warm-up: split only on request
+        assert ts["segments"] == 1 and nsb.last_launch_info()["launches"] == 1, ts
+    else:
+        assert ts["segments"] >= 2 and nsb.last_launch_info()["launches"] == 2, ts
+    with torch.no_grad():
+        ref = unsplit(run)
+    for a, b in zip(got, ref):
+        if a is not None:
+            assert torch.equal(a, b)
+
+
+def test_a_neuron_that_forgets_slowly_is_left_unsplit_after_one_try():
+    """beta = 0.9995 keeps a difference alive for 30 000 steps: every segment of the first split launch
+    is rescanned; the launch reports that to the host, and the next calls for the same neuron scan
+    unsplit - while a neuron with a short memory, same shape, keeps its split. Results are exact
+    throughout."""
+    T, B, D = 8192, 8, 768
+    br, u, tr, v0 = rowparam_inputs(T, B, D, torch.bfloat16, DEV, seed=77)
+    slow = torch.full_like(br, 0.9995)
+    u_small = (u.float() * 0.02).to(u.dtype)  # so that the slow neuron spikes now and then, not every step
+    ref = unsplit(lambda: ps.plif_rowparam_forward_packed(slow, u_small, tr, v0))
+    nsb.set_time_split()  # forget earlier launches
+    first = ps.plif_rowparam_forward_packed(slow, u_small, tr, v0)
+    assert nsb.last_time_split()["segments"] >= 2
+    torch.cuda.synchronize()  # the counters have reached the host
+    for _ in range(3):
+        again = ps.plif_rowparam_forward_packed(slow, u_small, tr, v0)
+        assert nsb.last_time_split()["segments"] == 1
+        assert torch.equal(again[0], ref[0]) and torch.equal(again[1], ref[1])
+    assert torch.equal(first[0], ref[0]) and torch.equal(first[1], ref[1])
+    for _ in range(3):  # another neuron of the same shape is judged by its own launches
+        ps.plif_rowparam_forward_packed(br, u, tr, v0)
+        assert nsb.last_time_split()["segments"] >= 2
+        torch.cuda.synchronize()
