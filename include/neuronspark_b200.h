@@ -146,7 +146,10 @@ int nsb_convert(const void* src, void* dst, int64_t n, int src_dtype, int dst_dt
  * split launch therefore copies its rescan counters to pinned host memory (asynchronously, 8 bytes),
  * and the next launch with the same beta_row vector, T, cols and direction reads what has arrived:
  * when one warp had to rescan more segments than the split saved, that neuron's scans run unsplit for
- * the next 64 calls and then try again. The results do not depend on any of this.
+ * the next 64 calls and then try again. The results do not depend on any of this. (The neuron is known
+ * by the address of its beta_row vector: a caller that rebuilds the vector every step gets the feedback
+ * where its allocator hands out the same address again, as a caching allocator does in a steady loop.
+ * The first automatic split launch allocates 2 KB of pinned memory; inside a stream capture it skips that.)
  *
  * nsb_set_time_split      max_segments: 0 = automatic, 1 = never split, 2..16 = at most that many
  *                         (and split even where the planner expects little gain, without the

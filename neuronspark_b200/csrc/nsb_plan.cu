@@ -347,6 +347,12 @@ void split_feedback_record(const void* neuron, long long T, long long cols, bool
   std::lock_guard<std::mutex> lk(g_fb_mu);
   if (g_fb_failed) return;
   if (!g_fb_host) {
+    // (pinned memory cannot be allocated while the stream is being captured into a graph)
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      return;
+    }
     void* h = nullptr;
     if (cudaHostAlloc(&h, sizeof(unsigned int) * 2 * kFeedbackSlots, cudaHostAllocPortable) != cudaSuccess) {
       cudaGetLastError();  // no feedback then; the split stays exact, only its choice is blind
