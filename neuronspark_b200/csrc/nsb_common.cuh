@@ -191,6 +191,31 @@ __device__ __forceinline__ void counter_publish(unsigned int* counter, unsigned 
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(counter), "r"(value) : "memory");
 }
 
+// ---- a launch that follows another on the same stream and reads what it wrote
+// Launched with launch_dependent(), the second kernel's CTAs may become resident while the first still
+// runs - as soon as every CTA of the first has called grid_dependents_may_launch() or exited - and must
+// call grid_dependency_wait() before they touch anything the first wrote: it returns when the first grid
+// has completed and its writes are visible. This takes the launch latency between the two (4-5 us) off
+// pairs of launches that are short themselves. In a kernel launched the ordinary way both calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // After a give-up: one shared allowance of `limit_ns` for all of a warp's stages whose loads may
 // still be in flight, so that they can land before the CTA's shared memory is released.
 __device__ __forceinline__ void mbar_drain(uint32_t bar0, int stages, int s_idx, uint32_t phase,

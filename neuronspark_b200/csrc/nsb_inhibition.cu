@@ -62,6 +62,7 @@ __global__ void li_bwd_kernel(const T* __restrict__ g_out, const T* __restrict__
                               const TG* __restrict__ gain, T* __restrict__ g_x,
                               float* __restrict__ partial, long long rows, int D, float eps) {
   extern __shared__ float acc_smem[];  // [warps][D]
+  grid_dependents_may_launch();  // the reduction of the partial rows may take its places while this runs
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
   const int wpc = blockDim.x >> 5;
@@ -178,6 +179,7 @@ __global__ void li_bwd_cached_kernel(const T* __restrict__ g_out, const T* __res
                                      const TG* __restrict__ gain, T* __restrict__ g_x,
                                      float* __restrict__ partial, long long rows, int D, float eps) {
   extern __shared__ float acc_smem[];  // [warps][D], summed over the CTA's warps at the end
+  grid_dependents_may_launch();
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
   const int wpc = blockDim.x >> 5;
@@ -349,6 +351,7 @@ __global__ void __launch_bounds__(kWideWarps * 32)
 li_bwd_wide_kernel(const T* __restrict__ g_out, const T* __restrict__ x, const TG* __restrict__ gain,
                    T* __restrict__ g_x, float* __restrict__ partial, long long rows, int D, float eps) {
   __shared__ float sums[2][2][kWideWarps];
+  grid_dependents_may_launch();
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const float inv_d = 1.0f / (float)D;
   float acc[NV][VE];
@@ -434,6 +437,7 @@ __global__ void li_bwd_reduce_kernel(const float* __restrict__ partial, float* _
   __shared__ float part[8][33];
   const int c = threadIdx.x & 31, g = threadIdx.x >> 5;
   const int d = blockIdx.x * 32 + c;
+  grid_dependency_wait();  // the partial rows are the launch before's
   float s = 0.0f;
   if (d < D)
     for (int p = g; p < nparts; p += 8) s += partial[(size_t)p * D + d];
@@ -532,8 +536,9 @@ int li_bwd_launch(const void* g_out, const void* x, const void* gain, void* g_x,
     NSB_LI_BWD((li_bwd_kernel<T, TG, 1>))
 #undef NSB_LI_BWD
   NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_kernel");
-  li_bwd_reduce_kernel<<<(int)((D + 31) / 32), 256, 0, st>>>(partial, g_gain, grid, (int)D);
-  NSB_CUDA_TRY(cudaGetLastError(), "launch li_bwd_reduce_kernel");
+  NSB_CUDA_TRY(launch_dependent(li_bwd_reduce_kernel, dim3((unsigned)((D + 31) / 32)), dim3(256), 0, st, partial, g_gain,
+                                grid, (int)D),
+               "launch li_bwd_reduce_kernel");
   return NSB_OK;
 }
 

@@ -1154,6 +1154,8 @@ __global__ void plif_fwd_split_kernel(const FwdParams p, const __grid_constant__
                                       const __grid_constant__ CUtensorMap tm3,
                                       const __grid_constant__ CUtensorMap tm4,
                                       const __grid_constant__ CUtensorMap tm_spike) {
+  // the checking launch is a dependent launch: its CTAs take their places while the segments still run
+  if (p.fixup) grid_dependency_wait(); else grid_dependents_may_launch();
   plif_fwd_body<ST, MODE, PACKED, V, C, TMA, true>(p, tm0, tm1, tm2, tm3, tm4, tm_spike);
 }
 
@@ -1323,6 +1325,9 @@ __global__ void __maxnreg__((TMA && C * V <= 16) ? ((MODE == MODE_RF || MODE == 
   using MT = ModeTraits<MODE>;
   using E = Elem<ST>;
   using IO = VecIO<ST, V>;
+  if constexpr (SPLIT) {  // the checking launch is a dependent launch (see plif_fwd_split_kernel)
+    if (p.fixup) grid_dependency_wait(); else grid_dependents_may_launch();
+  }
   constexpr int NF = MT::kFwdStreams;  // forward inputs; then g_spike, then optional g_vpost
   constexpr int kGS = NF, kGV = NF + 1;
   constexpr int G = BwdBox<MODE, V, C, TMA>::kWarps;  // warps per TMA box
@@ -2210,8 +2215,9 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
       skern<<<dim3(plan.grid, ts.nseg), plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
       NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_split_kernel");
       p.fixup = 1;
-      skern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
-      NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_split_kernel (check)");
+      NSB_CUDA_TRY(launch_dependent(skern, dim3(plan.grid), dim3(plan.wpc * 32), plan.smem, a.stream, p, tm[0], tm[1], tm[2],
+                                    tm[3], tm[4], tm[5]),
+                   "launch plif_fwd_split_kernel (check)");
       if (feedback) split_feedback_record(a.beta_row, a.T, a.cols, false, p.fix_count, ts.allow_rescans, a.stream);
     }
   } else {
@@ -2331,9 +2337,9 @@ int launch_bwd_impl(const BwdArgs& a, const DeviceInfo& dev, const Tuning& tune,
                                                                                 tm[7], tm[8], tm[9], tm[10], tm[11]);
       NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel (time-split)");
       p.fixup = 1;
-      skern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5], tm[6], tm[7], tm[8],
-                                                                tm[9], tm[10], tm[11]);
-      NSB_CUDA_TRY(cudaGetLastError(), "launch plif_bwd_kernel (time-split check)");
+      NSB_CUDA_TRY(launch_dependent(skern, dim3(plan.grid), dim3(plan.wpc * 32), plan.smem, a.stream, p, tm[0], tm[1], tm[2],
+                                    tm[3], tm[4], tm[5], tm[6], tm[7], tm[8], tm[9], tm[10], tm[11]),
+                   "launch plif_bwd_kernel (time-split check)");
       if (feedback) split_feedback_record(a.beta_row, a.T, a.cols, true, p.fix_count, ts.allow_rescans, a.stream);
     }
   } else {
