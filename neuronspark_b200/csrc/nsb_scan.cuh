@@ -1146,7 +1146,7 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
 }
 
 // The same scan cut along time (few columns): grid.y = segment in the first launch, and the checking
-// launch (p.fixup) afterwards. Built for the row-parameter family with one lane per thread only.
+// launch (p.fixup) afterwards. Built with one lane per thread only (see kSplitBuilt in launch_fwd_one).
 template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
 __global__ void plif_fwd_split_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tm0,
                                       const __grid_constant__ CUtensorMap tm1,
