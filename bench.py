@@ -67,6 +67,7 @@ MODULATED_WORKLOADS = {
     "rfmod-b8": dict(rf=True, B=8, T=8192, D=6144),
     "mod-b16": dict(rf=False, B=16, T=8192, D=6144),
     "rfmod-b16": dict(rf=True, B=16, T=8192, D=6144),
+    "rfmod-b8-short": dict(rf=True, B=8, T=2048, D=6144),  # a quarter of the time steps: profiler captures
 }
 INFERENCE_WORKLOADS = {
     "c1": dict(kind="row", B=8, T=8192, D=768, shard=False, calls=1, bytes_per_ns=2.125),
