@@ -175,7 +175,7 @@ __global__ void li_fwd_cached_kernel(const T* __restrict__ x, const TG* __restri
 }
 
 template <typename T, typename TG, int VE, int NV>
-__global__ void li_bwd_cached_kernel(const T* __restrict__ g_out, const T* __restrict__ x,
+__global__ void __launch_bounds__(kWarpsPerCta * 32, NV <= 3 ? 2 : 1) li_bwd_cached_kernel(const T* __restrict__ g_out, const T* __restrict__ x,
                                      const TG* __restrict__ gain, T* __restrict__ g_x,
                                      float* __restrict__ partial, long long rows, int D, float eps) {
   extern __shared__ float acc_smem[];  // [warps][D], summed over the CTA's warps at the end
@@ -511,6 +511,8 @@ int li_bwd_launch(const void* g_out, const void* x, const void* gain, void* g_x,
       D <= 32 * VMAX * kCacheVecs) {
     if (D <= 32 * VMAX * 2)
       NSB_LI_BWD((li_bwd_cached_kernel<T, TG, VMAX, 2>))
+    else if (D <= 32 * VMAX * 3)  // (768 channels of 16 bits: few enough registers for two CTAs per SM)
+      NSB_LI_BWD((li_bwd_cached_kernel<T, TG, VMAX, 3>))
     else if (D <= 32 * VMAX * 4)
       NSB_LI_BWD((li_bwd_cached_kernel<T, TG, VMAX, 4>))
     else
@@ -583,6 +585,8 @@ int nsb_lateral_inhibition_fwd(const void* x, const void* gain, void* out, int64
         };
         if (D <= 32 * VMAX * 2)
           launch(li_fwd_cached_kernel<T, TG, VMAX, 2>);
+        else if (D <= 32 * VMAX * 3)  // (768 channels of 16 bits)
+          launch(li_fwd_cached_kernel<T, TG, VMAX, 3>);
         else if (D <= 32 * VMAX * 4)
           launch(li_fwd_cached_kernel<T, TG, VMAX, 4>);
         else
