@@ -130,3 +130,16 @@ def test_time_axis_planning(built_lib):
     # modulation fused in: only where the launch has more CTAs than the GPU holds (768 for 444)
     assert chain(196608, lanes=2, warps_per_cta=4, modulated=True) == 8
     assert chain(98304, lanes=2, warps_per_cta=4, modulated=True) == 1
+    # the hidden neurons' scans (per-step parameters; a memory that may outlast any warm-up) are cut along
+    # time only on request
+    L = _lib.lib()
+    hidden = lambda: _lib.time_plan(False, 8192, 6144, tile=32, modulated=True)["segments"]
+    assert hidden() == 1
+    try:
+        assert L.nsb_set_time_split(4, 0) == 0
+        assert 2 <= hidden() <= 4 and 2 <= split(False, 6144) <= 4  # at most that many
+        assert L.nsb_set_time_split(1, 0) == 0
+        assert hidden() == 1 and split(False, 6144) == 1
+        assert L.nsb_set_time_split(17, 0) == 1 and L.nsb_set_time_split(2, -1) == 1  # invalid arguments
+    finally:
+        assert L.nsb_set_time_split(0, 0) == 0
