@@ -114,6 +114,9 @@ def parse_args():
                          "reference's per-layer activation checkpointing) instead of the forward alone")
     ap.add_argument("--no-chain", action="store_true",
                     help="backward launches walk all of T in one CTA per column block (no chained chunks)")
+    ap.add_argument("--rotation", type=int, default=0,
+                    help="modulated forward scans over few columns: warps that take a column group's tiles in turn "
+                         "(0 = the library's choice, 1 = none, 2..4)")
     ap.add_argument("--no-split", action="store_true",
                     help="few-column workloads (c1, res): run the scan as one serial launch, not cut along time")
     return ap.parse_args()
@@ -533,7 +536,7 @@ def run_modulated(args):
             p(raw_beta), p(raw_alpha), p(raw_th), p(raw_omega), p(cur), p(bias[0]), p(bias[1]), p(bias[2]),
             p(bias[3]), 0.1, D, p(v0), p(w0), p(spike), None, p(ckv), p(ckw), p(v_last), p(w_last), 4.0, 0.4,
             None, None, T, cols, _lib.BF16, C, p(split_scratch), stream), "nsb_plif_modulated_fwd")
-        info.setdefault("fwd", _lib.last_launch_info())
+        info.setdefault("fwd", dict(_lib.last_launch_info(), rotation=_lib.last_scan_rotation()))
 
     def bwd():
         _lib.check(L.nsb_plif_modulated_bwd(
@@ -1067,6 +1070,9 @@ def main():
     if args.no_chain:
         from neuronspark_b200 import _lib as _nsb_lib
         _nsb_lib.set_chain_chunks(1)
+    if args.rotation:
+        from neuronspark_b200 import _lib as _nsb_lib
+        _nsb_lib.set_scan_rotation(args.rotation)
     if args.workload in MODULATED_WORKLOADS:
         run_modulated(args)
         return

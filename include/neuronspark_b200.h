@@ -197,6 +197,33 @@ int64_t nsb_chain_scratch_words(int64_t cols);
 int nsb_set_chain_chunks(int chunks);
 int nsb_last_chain_chunks(void);
 
+/*
+ * Rotation of forward scans with the modulation fused in (nsb_plif_modulated_fwd without the moments of
+ * u) over few columns. Two thirds of such a scan's instructions - sigmoid, softplus, the stability
+ * rescale - depend on the step's inputs only; the recurrence itself is a handful per step. Over few
+ * columns (49 152 for one batch of 8 sequences of the 768-wide model: 2.5 warps per warp scheduler,
+ * 56 % of the issue slots busy) the launch is bound by how few warps there are, so R = 2..4 warps of a
+ * CTA share each group of 32 columns and take its tiles in turn: a warp evaluates its tile's modulation,
+ * then waits (bounded, see nsb_set_wait_limit_ns) for the membrane state its predecessor left after the
+ * tile before, runs the tile's steps and hands the state on through shared memory. Per column the
+ * operations and their order are those of the one-warp scan: every output is bit-identical. The
+ * reference has no counterpart (modulation and scan are separate passes there,
+ * atomic_ops/snn_block.py:52-76 and atomic_ops/parallel_scan.py:1655-1715).
+ *
+ * Measured (B200, bf16, T = 8192, 6 144 channels, forward ms on 32-step tiles with one warp per group ->
+ * rotating on 8-step tiles): resonate-and-fire, one sequence (6 144 columns) 0.89 -> 0.50, two 0.89 -> 0.57,
+ * four 1.00 -> 0.88; first order, one sequence 0.62 -> 0.43. At 49 152 columns, where every scheduler has
+ * 2.6 warps already, it is a loss (1.43 -> 1.80 ms) and is not used. Built for 8-step tiles (ckpt_interval
+ * 8), one lane per thread (the library's choice for such calls up to 32 768 columns).
+ *
+ * nsb_set_scan_rotation   0 = automatic (up to 1.5 column warps per warp scheduler, i.e. 28 416 columns:
+ *                         about five warps per scheduler, at most 4 per group, all CTAs resident),
+ *                         1 = never, 2..4 = that many warps per column group. Process-global.
+ * nsb_last_scan_rotation  warps per column group of the calling thread's last forward scan launch (1 = none).
+ */
+int nsb_set_scan_rotation(int warps);
+int nsb_last_scan_rotation(void);
+
 /* Tuning override for the scan kernels, used by sweeps and tests. Any field
  * <= 0 keeps the built-in heuristic. warps_per_cta: warps of one CTA (each
  * warp owns 32*lanes_per_thread columns and its own TMA pipeline); stages:

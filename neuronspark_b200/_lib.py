@@ -42,6 +42,8 @@ _SIGNATURES = {
     "nsb_chain_scratch_words": (c_int64, [c_int64]),
     "nsb_set_chain_chunks": (c_int, [c_int]),
     "nsb_last_chain_chunks": (c_int, []),
+    "nsb_set_scan_rotation": (c_int, [c_int]),
+    "nsb_last_scan_rotation": (c_int, []),
     "nsb_plif_rowparam_fwd": (c_int, [c_void_p] * 9 + [c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nsb_convert": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "nsb_set_time_split": (c_int, [c_int, c_int]),
@@ -241,6 +243,16 @@ def set_chain_chunks(chunks: int = 0) -> None:
 
 def last_chain_chunks() -> int:
     return int(lib().nsb_last_chain_chunks())
+
+
+def set_scan_rotation(warps: int = 0) -> None:
+    """Warps that take the tiles of a column group in turn in a modulated forward scan over few columns:
+    0 = automatic, 1 = never, 2..4. Process-global."""
+    check(lib().nsb_set_scan_rotation(int(warps)), "nsb_set_scan_rotation")
+
+
+def last_scan_rotation() -> int:
+    return int(lib().nsb_last_scan_rotation())
 
 
 def set_wait_limit_ns(ns: int = 0) -> None:

@@ -186,6 +186,33 @@ __device__ __forceinline__ bool counter_wait_bounded(const unsigned int* counter
   }
   return seen != kCounterPoisoned;
 }
+// The same on a word of shared memory that another warp of the CTA advances (smem_flag_publish): a
+// plain polling loop, because the waiter sits on a serial chain and has to notice within tens of cycles
+// (a suspended mbarrier wait took about a microsecond to resume, measured through a hand-off per 8 steps).
+__device__ __forceinline__ bool smem_flag_wait_bounded(uint32_t flag, uint32_t want, uint32_t* err_word, uint32_t code,
+                                                       unsigned long long limit_ns) {
+  auto peek = [&] {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(flag) : "memory");
+    return v;
+  };
+  if (peek() >= want) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t it = 0;
+  while (peek() < want) {
+    if ((++it & 0x3F) == 0) {
+      if (global_timer_ns() - t0 > limit_ns || it > (1u << 28)) {
+        if (err_word) atomicOr(reinterpret_cast<unsigned int*>(err_word), code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void smem_flag_publish(uint32_t flag, uint32_t value) {
+  asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(flag), "r"(value) : "memory");
+}
+
 // Makes the calling thread's earlier global writes visible to a thread that then sees `value`.
 __device__ __forceinline__ void counter_publish(unsigned int* counter, unsigned int value) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(counter), "r"(value) : "memory");

@@ -379,6 +379,40 @@ void split_feedback_record(const void* neuron, long long T, long long cols, bool
     cudaGetLastError();
 }
 
+// ---- rotation of a forward scan with the modulation fused in
+//
+// With few columns there are too few warps for the issue slots: 49 152 columns of the resonate-and-fire
+// scan with one lane per thread are 1 536 warps for 592 schedulers, each warp issuing one instruction
+// every 4.6 cycles (56 % of the issue slots busy, special-function pipe 46 %, DRAM 44 %). Two thirds of
+// those instructions - the modulation - do not depend on the membrane state, so R warps share a column
+// group and take its tiles in turn; only the recurrence's own few instructions per step wait for the
+// predecessor. R is chosen for about five warps per scheduler.
+namespace {
+std::atomic<int> g_rotation{0};  // 0 = automatic, 1 = never, 2..4 = that many warps per column group
+thread_local int g_last_rotation = 1;
+}  // namespace
+
+int& last_rotation() { return g_last_rotation; }
+bool get_rotation_forced() { return g_rotation.load(std::memory_order_relaxed) > 1; }
+
+int plan_rotation(const DeviceInfo& dev, long long column_warps, int ntiles) {
+  const int forced = g_rotation.load(std::memory_order_relaxed);
+  if (forced == 1 || column_warps <= 0) return 1;
+  long long r = forced;
+  if (forced == 0) {
+    const long long schedulers = 4LL * std::max(1, dev.sm_count);
+    // Measured (resonate-and-fire, T = 8192, bf16, forward ms, one warp per group on 32-step tiles -> rotating
+    // on 8-step tiles): 192 column warps 0.89 -> 0.50 (3 warps per group; 0.67 with 2, 0.51 with 4), 384:
+    // 0.89 -> 0.57 (4), 768: 1.00 -> 0.88 (3; 0.90 with 2 or 4); first order 192: 0.62 -> 0.43. With 1 536
+    // column warps (2.6 per scheduler already) two warps per group are a loss: 1.43 -> 1.80 ms.
+    if (2 * column_warps > 3 * schedulers) return 1;
+    r = (5 * schedulers + column_warps / 2) / column_warps;
+  }
+  r = std::min<long long>(4, std::max<long long>(1, r));
+  while (r > 1 && ntiles < 4 * r) --r;  // every warp of a group gets a few tiles
+  return (int)r;
+}
+
 // ---- chained chunks of a backward launch
 //
 // A backward launch over many columns has more CTAs than fit on the GPU at once, and a CTA walks all
@@ -422,6 +456,13 @@ int plan_chain_chunks(bool eligible, int ntiles, int target_tiles) {
 }
 
 }  // namespace nsb
+
+extern "C" int nsb_set_scan_rotation(int warps) {
+  if (warps < 0 || warps > 4) return NSB_ERR_INVALID_ARG;
+  nsb::g_rotation.store(warps, std::memory_order_relaxed);
+  return NSB_OK;
+}
+extern "C" int nsb_last_scan_rotation(void) { return nsb::last_rotation(); }
 
 extern "C" int nsb_set_chain_chunks(int chunks) {
   if (chunks < 0 || chunks > 1024) return NSB_ERR_INVALID_ARG;

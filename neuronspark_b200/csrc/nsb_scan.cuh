@@ -189,6 +189,11 @@ struct TimeSplit {
 TimeSplit plan_time_split(const DeviceInfo& dev, long long T, long long cols, int tile, int lanes, int wpc,
                           bool backward, int family);
 TimeSplit& last_time_split();  // of the calling thread's last forward launch
+// Warps that take the tiles of a column group in turn in a forward scan with the modulation fused in over
+// few columns (1 = none). Host arithmetic (nsb_plan.cu).
+int plan_rotation(const DeviceInfo& dev, long long column_warps, int ntiles);
+bool get_rotation_forced();  // a count set through nsb_set_scan_rotation is used whether or not all CTAs fit
+int& last_rotation();  // of the calling thread's last forward launch
 // What earlier split launches of one neuron had to rescan, fed back into the automatic choice. `neuron`
 // is any pointer that names the call site (the per-row parameter vector). _allows: false while that
 // neuron's dynamics forget too slowly for the split to pay. _record: queues the copy of the launch's two
@@ -424,6 +429,9 @@ struct FwdParams {
   float* wspec;  // the same for the second state of the resonate-and-fire scans
   float* wend;
   unsigned int* fix_count;
+  // Rotation (few columns, modulation fused in): rot > 1 warps of a CTA own the same 32*V columns and take
+  // the tiles in turn; the membrane state goes from warp to warp through shared memory (see plif_fwd_body).
+  int rot;
 };
 
 template <int MODE_>
@@ -506,7 +514,7 @@ __device__ __forceinline__ void rf_step(float (&v)[V], float (&w)[V], const floa
 // The forward scan. A device function so that it can sit behind two kernel entry points: one
 // without a register limit (ptxas' own choice; giving it an explicit 255 made it spend 30-100 more
 // registers on every variant), one held to 160 registers.
-template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA, bool SPLIT = false>
+template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA, bool SPLIT = false, bool ROT = false>
 __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensorMap& tm0, const CUtensorMap& tm1,
                                               const CUtensorMap& tm2, const CUtensorMap& tm3,
                                               const CUtensorMap& tm4, const CUtensorMap& tm_spike) {
@@ -531,7 +539,38 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int wpc = blockDim.x >> 5;
-  const long long col0 = ((long long)blockIdx.x * wpc + warp) * (32 * V);
+  // ---- rotation. The modulation of a tile (two thirds of a modulated scan's instructions) depends on
+  // nothing but the tile's inputs; only the few instructions of the recurrence itself form the serial
+  // chain over T. With few columns there are too few warps to fill the issue slots (2.5 per scheduler at
+  // 49 152 columns), so R warps share a column group: warp r takes tiles r, r+R, r+2R, ..., evaluates a
+  // tile's modulation, THEN waits for the state its predecessor left after the tile before, runs the tile's
+  // steps, and hands the state on - through 2*32*V floats of shared memory and one counter per warp, which
+  // its predecessor advances each time it has a state for it (bounded wait like every other). Arithmetic
+  // and its order per column are those of the one-warp scan: the results are the same bits.
+  static_assert(!ROT || (!SPLIT && TMA && !ModeTraits<MODE>::kStats), "rotation: tiled copies, no time split, no moments");
+  const int R = ROT ? p.rot : 1;
+  const int rw = ROT ? warp % R : 0;
+  const long long col0 = ROT ? ((long long)blockIdx.x * (wpc / R) + warp / R) * (32 * V)
+                             : ((long long)blockIdx.x * wpc + warp) * (32 * V);
+  uint32_t hbar_mine = 0, hbar_next = 0;  // rotation: this warp's counter of states received and its successor's,
+  volatile uint32_t* hfail = nullptr;      // the group's give-up flag,
+  float* hstate = nullptr;                 // and the state in transit: V then W, 32*V floats each
+  if constexpr (ROT) {
+    constexpr uint32_t kHandHeader = 48u;  // up to 4 counters (8 bytes apart), the flag
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t data_base = (base + (uint32_t)(wpc * p.stages) * 8u + 127u) & ~127u;
+    const uint32_t hand = data_base + (uint32_t)(wpc * p.stages) * STAGE_BYTES +
+                          (uint32_t)(warp / R) * (kHandHeader + 8u * 32u * V);
+    hbar_mine = hand + 8u * (uint32_t)rw;
+    hbar_next = hand + 8u * (uint32_t)((rw + 1) % R);
+    hfail = reinterpret_cast<volatile uint32_t*>(smem_raw + (hand + 32u - base));
+    hstate = reinterpret_cast<float*>(smem_raw + (hand + kHandHeader - base));
+    if (lane == 0) {
+      smem_flag_publish(hbar_mine, 0u);
+      if (rw == 0) *hfail = 0u;
+    }
+    __syncthreads();  // (before any warp leaves: every thread of the CTA takes part)
+  }
   if (col0 >= p.cols) return;
 
   long long colj[V];
@@ -642,6 +681,49 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
             if (valid[j]) dst[q].v[j] = p.pat_in[tok * row_elems + colj[j]];
         }
       }
+    }
+  };
+
+  // Rotation: what happens between a tile's modulation and its first step (state_in, called from inside
+  // the tile), and after its last step (state_out).
+  int cur_tile = 0;               // absolute index of the tile in hand
+  uint32_t cur_handoff = 0, sent = 0;  // states this warp has received / handed on
+  bool rot_failed = false;
+  auto state_in = [&]() {
+    if constexpr (ROT) {
+      if (cur_tile > 0) {
+        bool ok = smem_flag_wait_bounded(hbar_mine, ++cur_handoff, p.err, 1u, p.wait_ns);
+        ok = ok && *hfail == 0u;  // (a predecessor that gave up still advances the counter, with the flag set)
+        if (!__all_sync(0xffffffffu, ok)) {
+          rot_failed = true;  // this tile's results are wasted; the loop ends after it
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            v[j] = hstate[V * lane + j];
+            if (MT::kSecond) w[j] = hstate[32 * V + V * lane + j];
+          }
+        }
+      }
+      if (p.ckpt && valid[0]) {
+        VecIO<float, V>::store(p.ckpt + (long long)cur_tile * row_elems + colj[0], v);
+        if (MT::kSecond) VecIO<float, V>::store(p.ckpt_w + (long long)cur_tile * row_elems + colj[0], w);
+      }
+    }
+  };
+  auto state_out = [&](bool gave_up) {
+    if constexpr (ROT) {
+      if (gave_up) {
+        *hfail = 1u;
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          hstate[V * lane + j] = v[j];
+          if (MT::kSecond) hstate[32 * V + V * lane + j] = w[j];
+        }
+      }
+      __syncwarp();
+      ++sent;
+      if (lane == 0) smem_flag_publish(hbar_next, gave_up ? 0x7fffffffu : sent);
     }
   };
 
@@ -787,6 +869,24 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
           th[j] = mth[k % CH][j];
           dr[j] = mu[k % CH][j];
           om[j] = mom[k % CH][j];
+        }
+      }
+      if constexpr (ROT) {
+        if (k == 0) {
+          // The tile's modulation has to be finished BEFORE the wait for the state, or nothing overlaps: left
+          // to itself the compiler evaluates beta, u, v_th, omega of a step right before the step uses them,
+          // i.e. after the wait (measured: 1.80 ms instead of 1.43 at 49 152 columns). Volatile statements
+          // keep their order, so one that reads the values pins their evaluation in front of the wait.
+          if constexpr (MT::kMod) {
+#pragma unroll
+            for (int kk = 0; kk < CH; ++kk)
+              if (FULL || kk < nsteps) {
+#pragma unroll
+                for (int j = 0; j < V; ++j)
+                  asm volatile("" ::"f"(mb[kk][j]), "f"(mu[kk][j]), "f"(mth[kk][j]), "f"(mom[kk][j]));
+              }
+          }
+          state_in();  // now the state the tile starts from
         }
       }
       if constexpr (MT::kSecond) {
@@ -974,18 +1074,21 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
         }
       }
     }
-    const int nt = tile_end - tile_begin;
+    // (rotation: this warp's tiles are rw, rw + R, ...)
+    const int nt = ROT ? (tile_end - tile_begin > rw ? (tile_end - tile_begin - rw + R - 1) / R : 0) : tile_end - tile_begin;
+    auto abs_tile = [&](int i) { return ROT ? tile_begin + rw + i * R : tile_begin + i; };
     if constexpr (TMA) {
       if (lane == 0) {  // prime the ring from the stage that is consumed next
         const int pre = nt < stages ? nt : stages;
-        for (int q = 0; q < pre; ++q) issue(tile_begin + q, (s_idx + q) % stages);
+        for (int q = 0; q < pre; ++q) issue(abs_tile(q), (s_idx + q) % stages);
       }
     }
     if constexpr (MODE == MODE_ROWPAT) {
       if (p.pat_in) load_patterns(tile_begin, pin_cur);
     }
     for (int i = 0; i < nt; ++i) {
-      const int ia = tile_begin + i;  // absolute tile index
+      const int ia = abs_tile(i);  // absolute tile index
+      cur_tile = ia;
       t0 = (long long)ia * C;
       const bool emit = !split || ia >= tile_emit;
       const int nsteps = (p.T - t0) < C ? (int)(p.T - t0) : C;
@@ -1008,7 +1111,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
         }
         sp = reinterpret_cast<const ST*>(data_ptr + (size_t)s_idx * STAGE_BYTES) + V * lane;
       }
-      if (p.ckpt && emit) {
+      if (p.ckpt && emit && !ROT) {  // (rotation: written once the tile's starting state has arrived)
         if constexpr (VEC) {
           if (valid[0]) VecIO<float, V>::store(p.ckpt + (long long)ia * row_elems + colj[0], v);
           if (MT::kSecond && valid[0]) VecIO<float, V>::store(p.ckpt_w + (long long)ia * row_elems + colj[0], w);
@@ -1033,6 +1136,13 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
       } else {
         tile(std::false_type{}, std::true_type{}, std::true_type{}, nsteps);
       }
+      if constexpr (ROT) {
+        if (rot_failed) {
+          failed = true;
+          break;
+        }
+        state_out(false);
+      }
       if constexpr (MODE == MODE_ROWPAT) {
 #pragma unroll
         for (int q = 0; q < TOK; ++q) pin_cur[q] = pin_nxt[q];
@@ -1054,14 +1164,14 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
             // never stands still behind its own store.
             bulk_wait_read_keep1();
             const int sp_idx = s_idx == 0 ? stages - 1 : s_idx - 1;
-            if (i >= 1 && i - 1 + stages < nt) issue(ia - 1 + stages, sp_idx);
+            if (i >= 1 && i - 1 + stages < nt) issue(abs_tile(i - 1 + stages), sp_idx);
           } else if (p.defer && DENSE_TMA && p.spike != nullptr) {
             // (a warm-up tile of a deferring launch: nothing was stored, keep the refill order)
             const int sp_idx = s_idx == 0 ? stages - 1 : s_idx - 1;
-            if (i >= 1 && i - 1 + stages < nt) issue(ia - 1 + stages, sp_idx);
+            if (i >= 1 && i - 1 + stages < nt) issue(abs_tile(i - 1 + stages), sp_idx);
           } else {
             if (store_spikes) bulk_wait_read_all();  // the stage is refilled next
-            if (i + stages < nt) issue(ia + stages, s_idx);
+            if (i + stages < nt) issue(abs_tile(i + stages), s_idx);
           }
         }
         if (++s_idx == stages) {
@@ -1091,6 +1201,7 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
 
   if constexpr (TMA) {
     if (failed) {
+      state_out(true);  // (rotation: the warps waiting for this one's state give up at once)
       // Give every load that may still be in flight a bounded chance to land before the CTA's
       // shared memory is released, and leave NaN in the per-column outputs: the error word says
       // why, and nothing downstream can mistake unwritten memory for a result.
@@ -1111,7 +1222,8 @@ __device__ __forceinline__ void plif_fwd_body(const FwdParams& p, const CUtensor
       w[j] = carryw[j];
     }
   }
-  if (!split || p.fixup) {
+  // (rotation: the final state is the one of the warp that ran the last tile)
+  if ((!split || p.fixup) && (!ROT || (ntiles_total > 0 ? (ntiles_total - 1) % R == rw : rw == 0))) {
 #pragma unroll
     for (int j = 0; j < V; ++j)
       if (valid[j]) {
@@ -1143,6 +1255,17 @@ __global__ void plif_fwd_kernel(const FwdParams p, const __grid_constant__ CUten
                                 const __grid_constant__ CUtensorMap tm4,
                                 const __grid_constant__ CUtensorMap tm_spike) {
   plif_fwd_body<ST, MODE, PACKED, V, C, TMA>(p, tm0, tm1, tm2, tm3, tm4, tm_spike);
+}
+
+// The same scan with the tiles of a column group taken in turn by several warps (see plif_fwd_body).
+template <typename ST, int MODE, bool PACKED, int V, int C, bool TMA>
+__global__ void __maxnreg__(80) plif_fwd_rot_kernel(const FwdParams p, const __grid_constant__ CUtensorMap tm0,
+                                    const __grid_constant__ CUtensorMap tm1,
+                                    const __grid_constant__ CUtensorMap tm2,
+                                    const __grid_constant__ CUtensorMap tm3,
+                                    const __grid_constant__ CUtensorMap tm4,
+                                    const __grid_constant__ CUtensorMap tm_spike) {
+  plif_fwd_body<ST, MODE, PACKED, V, C, TMA, false, true>(p, tm0, tm1, tm2, tm3, tm4, tm_spike);
 }
 
 // The same scan cut along time (few columns): grid.y = segment in the first launch, and the checking
@@ -2221,8 +2344,44 @@ int launch_fwd_one(const FwdArgs& a, const DeviceInfo& dev, const Tuning& tune, 
       if (feedback) split_feedback_record(a.beta_row, a.T, a.cols, false, p.fix_count, ts.allow_rescans, a.stream);
     }
   } else {
-    kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
-    NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_kernel");
+    // Few columns and the modulation fused in: several warps take the tiles of a column group in turn
+    // (see plif_fwd_body). Built for one lane per thread, tiled copies, tiles of 8 steps.
+    constexpr bool kRotBuilt = (MODE == MODE_MOD || MODE == MODE_RFMOD) && TMA && V == 1 && C == 8;
+    int rot = 1;
+    if constexpr (kRotBuilt) rot = plan_rotation(dev, nwarps, p.ntiles);
+    [[maybe_unused]] const size_t per_warp = (plan.smem - 256) / plan.wpc;  // a warp's ring at the planned depth
+    if constexpr (kRotBuilt) {
+      // One CTA per column group, and all of them resident at once: a CTA walks all of T, so a second
+      // round of CTAs would cost as much as the first (measured at 49 152 columns with 768 CTAs for 740
+      // places: 1.42 -> 1.80 ms). Fewer warps per group until they fit.
+      auto rkern = plif_fwd_rot_kernel<ST, MODE, PACKED, V, C, TMA>;
+      for (; rot > 1; --rot) {
+        const size_t smem = per_warp * rot + 256 + 48 + 8 * 32 * V;
+        if (cudaFuncSetAttribute(rkern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+          cudaGetLastError();
+          continue;
+        }
+        int blocks = 0;
+        NSB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, rkern, rot * 32, smem),
+                     "cudaOccupancyMaxActiveBlocksPerMultiprocessor(fwd rotation)");
+        if ((long long)blocks * std::max(1, dev.sm_count) >= nwarps || get_rotation_forced()) break;
+      }
+    }
+    last_rotation() = rot;
+    if (rot > 1) {
+      if constexpr (kRotBuilt) {
+        auto rkern = plif_fwd_rot_kernel<ST, MODE, PACKED, V, C, TMA>;
+        plan.wpc = rot;
+        plan.smem = per_warp * rot + 256 + 48 + 8 * 32 * V;
+        plan.grid = (int)nwarps;
+        p.rot = rot;
+        rkern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
+        NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_rot_kernel");
+      }
+    } else {
+      kern<<<plan.grid, plan.wpc * 32, plan.smem, a.stream>>>(p, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
+      NSB_CUDA_TRY(cudaGetLastError(), "launch plif_fwd_kernel");
+    }
   }
   if (MT::kStats && a.u_stats && a.alpha_out) {
     // u is never stored, so its standard deviation is taken at fp32 (no rounding to a storage dtype)
@@ -2548,6 +2707,9 @@ int scan_mod_fwd_dispatch(const FwdArgs& a) {
       tune.lanes_per_thread = 2; tune.warps_per_cta = 4; tune.stages = a.mode == MODE_RFMOD ? 2 : 3;
     }
   }
+  // Fewer columns, 8-step tiles, no moments of u: one lane per thread, which is what the rotation among
+  // warps is built for (see plif_fwd_body).
+  if (a.tile == 8 && tune.lanes_per_thread <= 0 && a.cols <= 32768 && !a.u_stats) tune.lanes_per_thread = 1;
   bool tma = tma_ok_common<ST>(dev, a.T, a.cols, tune);
   const void* ptrs[] = {a.beta, a.drive, a.gain, a.vth, a.extra, a.spike, a.ckpt, a.ckpt_w};
   for (const void* q : ptrs) tma = tma && aligned16(q);

@@ -77,6 +77,11 @@ def _fused_modulation_rf(raw_beta, b_beta, raw_alpha, b_alpha, raw_th, b_th, v_t
                               raw_omega, b_omega, out_dtype=out_dtype)
 
 
+# widest no-grad forward that runs on 8-step tiles so that the library can rotate it among warps
+ROTATE_MAX_COLS_RF = 24576
+ROTATE_MAX_COLS = 12288
+
+
 class ModulatedPLIFScan(torch.autograd.Function):
     """Modulation + scan. Inputs: raw_beta, raw_alpha, raw_th, I, raw_omega (or None), b_beta,
     b_alpha, b_th, b_omega (or None), v_init, w_init (or None), v_th_min, alpha, surrogate.
@@ -101,7 +106,15 @@ class ModulatedPLIFScan(torch.autograd.Function):
         v0 = ps._row_f32(v_init, shape)
         w0 = ps._row_f32(w_init, shape) if rf else None
         needs_grad = any(ctx.needs_input_grad[:11])
-        C = ctx.interval = 32 if ps._interval(cols) == 32 else 8
+        C = 32 if ps._interval(cols) == 32 else 8
+        # Inference over few columns: with 8-step tiles several warps take a column group's tiles in turn
+        # (nsb_set_scan_rotation). T=8192, 6144 channels, bf16, forward ms with 32-step tiles -> rotating:
+        # resonate-and-fire 0.89 -> 0.50 (one sequence), 0.89 -> 0.57 (two), 1.00 -> 0.88 (four).
+        # Wider ones, up to the 49 152 columns of a batch of 8: 32-step tiles (1.22 against 1.46 ms; the 8-step
+        # tiles chosen above are for the backward's sake).
+        if not needs_grad and ps.CKPT_INTERVAL is None:
+            C = 8 if cols <= (ROTATE_MAX_COLS_RF if rf else ROTATE_MAX_COLS) else (32 if cols <= 49152 else C)
+        ctx.interval = C
         spike = torch.empty_like(ci)
         ckv = ckw = None
         if needs_grad:

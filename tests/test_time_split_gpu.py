@@ -224,6 +224,8 @@ def test_hidden_neuron_scans_split_equal_unsplit(kind, segments, warm):
     ones are, with both states (V, W) compared at every boundary; short warm-ups force rescans."""
     T, B, D = 4096 + 40, 2, 768 if kind != "u" else 1024
     run = _hidden_forward(kind, T, B, D, seed=31)
+    if kind in ("mod", "rfmod"):
+        ps.CKPT_INTERVAL = 32  # (a no-grad modulated forward over few columns takes 8-step tiles by default, which rotate among warps instead)
     nsb.set_time_split(segments, warm)
     with torch.no_grad():
         got = run()
