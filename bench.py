@@ -68,6 +68,13 @@ MODULATED_WORKLOADS = {
     "mod-b16": dict(rf=False, B=16, T=8192, D=6144),
     "rfmod-b16": dict(rf=True, B=16, T=8192, D=6144),
     "rfmod-b8-short": dict(rf=True, B=8, T=2048, D=6144),  # a quarter of the time steps: profiler captures
+    # one, two and four sequences of the 768-wide model (6 144 - 24 576 columns): the rotation among warps
+    # (--tile 8, which inference takes there; --rotation 1 switches it off)
+    "rfmod-b1": dict(rf=True, B=1, T=8192, D=6144),
+    "rfmod-b2": dict(rf=True, B=2, T=8192, D=6144),
+    "rfmod-b4": dict(rf=True, B=4, T=8192, D=6144),
+    "mod-b1": dict(rf=False, B=1, T=8192, D=6144),
+    "mod-b2": dict(rf=False, B=2, T=8192, D=6144),
 }
 INFERENCE_WORKLOADS = {
     "c1": dict(kind="row", B=8, T=8192, D=768, shard=False, calls=1, bytes_per_ns=2.125),
@@ -117,6 +124,8 @@ def parse_args():
     ap.add_argument("--rotation", type=int, default=0,
                     help="modulated forward scans over few columns: warps that take a column group's tiles in turn "
                          "(0 = the library's choice, 1 = none, 2..4)")
+    ap.add_argument("--tile", type=int, default=0, choices=[0, 8, 16, 32],
+                    help="steps per tile and checkpoint (0 = what the public API picks for a training step)")
     ap.add_argument("--no-split", action="store_true",
                     help="few-column workloads (c1, res): run the scan as one serial launch, not cut along time")
     return ap.parse_args()
@@ -1073,6 +1082,9 @@ def main():
     if args.rotation:
         from neuronspark_b200 import _lib as _nsb_lib
         _nsb_lib.set_scan_rotation(args.rotation)
+    if args.tile:
+        from neuronspark_b200 import parallel_scan as _nsb_ps
+        _nsb_ps.CKPT_INTERVAL = args.tile
     if args.workload in MODULATED_WORKLOADS:
         run_modulated(args)
         return
