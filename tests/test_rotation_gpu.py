@@ -71,3 +71,40 @@ def test_gradients_from_a_rotated_forward_are_the_same_bits(rf, rotation):
     assert len(got) == len(ref) >= 6
     for a, e in zip(got, ref):
         assert torch.equal(a, e)
+
+
+@pytest.mark.parametrize("rf", [False, True])
+@pytest.mark.parametrize("rotation", [1, 0, 3])
+def test_bit_packed_spikes_of_a_rotated_forward(rf, rotation):
+    """The same call through the C ABI with bit-packed spikes out (32 columns per word, ballots kept per
+    tile): the words spell the dense spikes of the unrotated launch."""
+    from neuronspark_b200 import _lib
+    T, B, D = 1024 + 8, 2, 768
+    cols = B * D
+    d, b, v0, w0 = mod_inputs(T, B, D, torch.bfloat16, 9, rf)
+    L, p = _lib.lib(), _lib.ptr
+    bias = [b["b_beta"].float().contiguous(), b["b_alpha"].float().contiguous(), b["b_th"].float().contiguous(),
+            (b["b_omega"].float().contiguous() if rf else None)]
+    v0f = v0.float().contiguous()
+    w0f = w0.float().contiguous() if rf else None
+    v_last = torch.empty_like(v0f)
+    w_last = torch.empty_like(v0f) if rf else None
+
+    def call(dense, packed):
+        _lib.check(L.nsb_plif_modulated_fwd(
+            p(d["raw_beta"]), p(d["raw_alpha"]), p(d["raw_th"]), p(d["raw_omega"]) if rf else None, p(d["cur"]),
+            p(bias[0]), p(bias[1]), p(bias[2]), p(bias[3]) if rf else None, 0.1, D, p(v0f), p(w0f) if rf else None,
+            p(dense), p(packed), None, None, p(v_last), p(w_last) if rf else None, 4.0, 0.0, None, None, T, cols,
+            _lib.BF16, 8, None, _lib.stream_ptr(DEV)), "nsb_plif_modulated_fwd")
+        torch.cuda.synchronize()
+
+    nsb.set_scan_rotation(1)
+    dense = torch.empty((T, B, D), dtype=torch.bfloat16, device=DEV)
+    call(dense, None)
+    want_v = v_last.clone()
+    nsb.set_scan_rotation(rotation)
+    packed = torch.zeros((T, (cols + 31) // 32), dtype=torch.int32, device=DEV)
+    call(None, packed)
+    assert nsb.last_scan_rotation() == (1 if rotation == 1 else (4 if rotation == 0 else 3))
+    assert torch.equal(ps.unpack_spikes(packed, (B, D)), dense.float())
+    assert torch.equal(v_last, want_v)
