@@ -58,6 +58,10 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert L.nsb_fp16_encode(z, z, 1, 1, 4, 0, 0, z) == 1
     assert L.nsb_set_tuning(64, 0, 0, 0) == 1 and L.nsb_set_tuning(0, 0, 3, 0) == 1
     assert L.nsb_set_tuning(0, 0, 0, 0) == 0
+    assert L.nsb_set_scan_rotation(5) == 1 and L.nsb_set_scan_rotation(-1) == 1
+    assert L.nsb_set_scan_rotation(3) == 0 and L.nsb_set_scan_rotation(0) == 0
+    assert L.nsb_last_scan_rotation() == 1  # no forward scan launched by this thread yet
+    assert L.nsb_set_chain_chunks(1025) == 1 and L.nsb_set_chain_chunks(0) == 0
 
 
 def test_no_cpu_fallback(built_lib):
