@@ -245,10 +245,20 @@ def last_chain_chunks() -> int:
     return int(lib().nsb_last_chain_chunks())
 
 
+_scan_rotation = 0
+
+
 def set_scan_rotation(warps: int = 0) -> None:
     """Warps that take the tiles of a column group in turn in a modulated forward scan over few columns:
     0 = automatic, 1 = never, 2..4. Process-global."""
+    global _scan_rotation
     check(lib().nsb_set_scan_rotation(int(warps)), "nsb_set_scan_rotation")
+    _scan_rotation = int(warps)
+
+
+def scan_rotation_setting() -> int:
+    """What was last set through set_scan_rotation (the Python layer picks its tile length by it)."""
+    return _scan_rotation
 
 
 def last_scan_rotation() -> int:

@@ -113,7 +113,8 @@ class ModulatedPLIFScan(torch.autograd.Function):
         # Wider ones, up to the 49 152 columns of a batch of 8: 32-step tiles (1.22 against 1.46 ms; the 8-step
         # tiles chosen above are for the backward's sake).
         if not needs_grad and ps.CKPT_INTERVAL is None:
-            C = 8 if cols <= (ROTATE_MAX_COLS_RF if rf else ROTATE_MAX_COLS) else (32 if cols <= 49152 else C)
+            rotating = _lib.scan_rotation_setting() != 1 and cols <= (ROTATE_MAX_COLS_RF if rf else ROTATE_MAX_COLS)
+            C = 8 if rotating else (32 if cols <= 49152 else C)
         ctx.interval = C
         spike = torch.empty_like(ci)
         ckv = ckw = None
