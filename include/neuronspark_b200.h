@@ -220,9 +220,13 @@ int nsb_last_chain_chunks(void);
  *                         about five warps per scheduler, at most 4 per group, all CTAs resident),
  *                         1 = never, 2..4 = that many warps per column group. Process-global.
  * nsb_last_scan_rotation  warps per column group of the calling thread's last forward scan launch (1 = none).
+ * nsb_scan_rotation_query what the current setting gives a scan of T steps over `cols` columns (one lane per
+ *                         thread, `tile` steps per tile) on a B200, before the check that all CTAs are
+ *                         resident; host arithmetic, needs no GPU. 0 for invalid arguments.
  */
 int nsb_set_scan_rotation(int warps);
 int nsb_last_scan_rotation(void);
+int nsb_scan_rotation_query(int64_t T, int64_t cols, int tile);
 
 /* Tuning override for the scan kernels, used by sweeps and tests. Any field
  * <= 0 keeps the built-in heuristic. warps_per_cta: warps of one CTA (each

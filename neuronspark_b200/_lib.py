@@ -44,6 +44,7 @@ _SIGNATURES = {
     "nsb_last_chain_chunks": (c_int, []),
     "nsb_set_scan_rotation": (c_int, [c_int]),
     "nsb_last_scan_rotation": (c_int, []),
+    "nsb_scan_rotation_query": (c_int, [c_int64, c_int64, c_int]),
     "nsb_plif_rowparam_fwd": (c_int, [c_void_p] * 9 + [c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "nsb_convert": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "nsb_set_time_split": (c_int, [c_int, c_int]),

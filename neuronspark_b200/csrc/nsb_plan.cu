@@ -463,6 +463,10 @@ extern "C" int nsb_set_scan_rotation(int warps) {
   return NSB_OK;
 }
 extern "C" int nsb_last_scan_rotation(void) { return nsb::last_rotation(); }
+extern "C" int nsb_scan_rotation_query(int64_t T, int64_t cols, int tile) {
+  if (T < 0 || cols <= 0 || tile <= 0) return 0;
+  return nsb::plan_rotation(nsb::b200_device_info(), (cols + 31) / 32, (int)((T + tile - 1) / tile));
+}
 
 extern "C" int nsb_set_chain_chunks(int chunks) {
   if (chunks < 0 || chunks > 1024) return NSB_ERR_INVALID_ARG;

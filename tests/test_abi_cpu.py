@@ -147,3 +147,13 @@ def test_time_axis_planning(built_lib):
         assert L.nsb_set_time_split(17, 0) == 1 and L.nsb_set_time_split(2, -1) == 1  # invalid arguments
     finally:
         assert L.nsb_set_time_split(0, 0) == 0
+    # rotation of a modulated forward among the warps of a CTA: about five warps per scheduler, at most four
+    # per column group, none beyond 1.5 column warps per scheduler, every warp of a group with a few tiles
+    rot = lambda cols, T=8192: L.nsb_scan_rotation_query(T, cols, 8)
+    assert [rot(c) for c in (6144, 12288, 24576, 28416, 28448, 49152)] == [4, 4, 4, 3, 1, 1]
+    assert rot(6144, T=64) == 2 and rot(6144, T=24) == 1 and rot(0) == 0
+    try:
+        assert L.nsb_set_scan_rotation(1) == 0 and rot(6144) == 1
+        assert L.nsb_set_scan_rotation(3) == 0 and rot(49152) == 3  # (as asked, whether or not it pays)
+    finally:
+        assert L.nsb_set_scan_rotation(0) == 0
