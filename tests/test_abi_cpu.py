@@ -60,7 +60,7 @@ def test_argument_validation_needs_no_gpu(built_lib):
     assert L.nsb_set_tuning(0, 0, 0, 0) == 0
     assert L.nsb_set_scan_rotation(5) == 1 and L.nsb_set_scan_rotation(-1) == 1
     assert L.nsb_set_scan_rotation(3) == 0 and L.nsb_set_scan_rotation(0) == 0
-    assert L.nsb_last_scan_rotation() == 1  # no forward scan launched by this thread yet
+    assert 1 <= L.nsb_last_scan_rotation() <= 4  # (1 while this thread has launched no forward scan)
     assert L.nsb_set_chain_chunks(1025) == 1 and L.nsb_set_chain_chunks(0) == 0
 
 
